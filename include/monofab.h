@@ -1,0 +1,152 @@
+/* monofab.h — C ABI of the B200-native MonoFab MoE hot path.
+ *
+ * Every entry point is plain C: pointers, sizes and integer handles, no C++
+ * or torch types.  Device pointers are ordinary `void*` values valid on the
+ * current CUDA device; `stream` is a `cudaStream_t` passed as `void*` (NULL =
+ * the legacy default stream).  All functions return 0 on success and a negative
+ * MONOFAB_E* code on failure; `monofab_last_error()` then describes the failure
+ * for the calling thread.  Nothing here falls back to the CPU: without a CUDA
+ * device the compute entry points fail with MONOFAB_ECUDA.
+ *
+ * Each declaration cites the interface of the reference (MonoServe) that it
+ * stands in for, by the file's path inside that project.
+ */
+#ifndef MONOFAB_H_
+#define MONOFAB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MONOFAB_OK 0
+#define MONOFAB_EINVAL (-1)   /* bad argument (the message names it) */
+#define MONOFAB_ECUDA (-2)    /* a CUDA runtime / driver call failed */
+#define MONOFAB_EDEVICE (-3)  /* a kernel reported an error in its status word */
+
+/* Bits of a layer's device status word (monofab_moe_status). */
+#define MONOFAB_STATUS_WAIT_TIMEOUT 1  /* a bounded in-kernel wait ran out */
+#define MONOFAB_STATUS_PLAN_OVERFLOW 2 /* more GEMM tiles than the plan buffers hold */
+
+/* Region ids of the expert indirection table (monoserve/runtime/kinds.py:16-18). */
+#define MONOFAB_REGION_HOST 0
+#define MONOFAB_REGION_HOT 1
+
+int monofab_version(void);
+const char* monofab_last_error(void);
+
+/* Field layouts of the operand structs, as JSON
+ * {"Name": [sizeof, {"field": [offset, "u64"|"u32"|"f32"]}]}.
+ * Replaces _C.struct_layouts() (csrc/bindings.cpp:66-168). */
+const char* monofab_struct_layouts_json(void);
+
+/* Device alias of a pinned, mapped host address.
+ * Replaces _C.host_device_pointer (csrc/bindings.cpp:173-178). */
+int monofab_host_device_pointer(const void* host, uint64_t* device);
+
+/* Pinned + mapped host memory for the host-resident expert stacks and for the
+ * staging buffers of the host-buffer entry points
+ * (monoserve/runtime/weights.py:57-58 `pin`, csrc/host/fabric.cpp:71-73). */
+int monofab_host_alloc(size_t bytes, void** host);
+int monofab_host_free(void* host);
+
+/* ---- kernel-level entry points (device pointers) ------------------------ */
+
+/* Router projection logits[t][e] = sum_h x[t][h] * wr[e][h] in fp32 with a
+ * fixed summation order (H a multiple of 256).  Stands in for the router GEMM
+ * stage of a lane program (monoserve/runtime/lane.py:340-342). */
+int monofab_router_logits(const void* x_bf16, const void* wr_bf16, float* logits, int T, int H, int E,
+                          void* stream);
+
+/* Routing scores, top-K, renormalisation and per-expert counts: the router tile
+ * (csrc/fabric/tiles/aux.cuh:326-417, RouterArgs csrc/fabric/model_types.h:147-159).
+ * scoring 0 = softmax, 1 = sigmoid (+ selection bias).  `counts` (int32 [E]) is
+ * accumulated; `chunk_counts` (int32 [ceil(T/32)][E]) and `pair_rank`
+ * (int32 [T][K]) feed the stable pack and may be NULL.  E <= 256, K <= 16. */
+int monofab_router_topk(float* logits, const float* bias, int32_t* topk_ids, float* topk_w, int32_t* counts,
+                        int32_t* chunk_counts, int32_t* pair_rank, int T, int E, int K, int scoring, int renorm,
+                        float scale, int zero_logits, void* stream);
+
+/* Un-permute + weighted combine (+ optional following RMSNorm): the AddNorm tile
+ * together with the weighted-add GEMM epilogue (csrc/fabric/tiles/aux.cuh:137-188,
+ * csrc/fabric/tiles/gemm.cuh:310-319).  y fp32 [P][H]; x2 / norm_w / normed may be NULL. */
+int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w, const void* x2_bf16,
+                    void* x_bf16, const void* norm_w_bf16, void* normed_bf16, int T, int K, int H, float eps,
+                    void* stream);
+
+/* ---- one MoE layer ------------------------------------------------------- */
+
+typedef struct monofab_moe monofab_moe;
+
+typedef struct monofab_moe_config {
+  int32_t hidden;        /* H, multiple of 256 */
+  int32_t intermediate;  /* I, multiple of 64 */
+  int32_t experts;       /* E <= 256 */
+  int32_t top_k;         /* K <= 16 */
+  int32_t max_tokens;    /* workspace size */
+  int32_t scoring;       /* 0 softmax, 1 sigmoid */
+  int32_t renorm;        /* renormalise the selected weights */
+  float routed_scale;    /* multiplies the routing weights */
+  int32_t fp8;           /* expert weights are e4m3 bytes with fp32 per-row scales */
+  int32_t reserved[7];
+} monofab_moe_config;
+
+/* Allocates every workspace of the layer; nothing is allocated afterwards
+ * (csrc/host/fabric.h:134-137).  Uses the current CUDA device. */
+int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out);
+int monofab_moe_destroy(monofab_moe* m);
+
+/* Router weight bf16 [E][H] (device) and optional fp32 [E] selection bias. */
+int monofab_moe_set_router(monofab_moe* m, const void* wr_bf16, const float* bias);
+
+/* Expert weight stacks of one region: w13 [slots][2I][H], w2 [slots][H][I]
+ * (bf16, or e4m3 bytes).  Region MONOFAB_REGION_HOST takes HOST addresses of
+ * pinned mapped memory, read in place over the host link; MONOFAB_REGION_HOT
+ * takes device addresses (monoserve/runtime/weights.py:100-143). */
+int monofab_moe_set_region(monofab_moe* m, int region, const void* w13, const void* w2, int slots);
+
+/* FP8 per-output-channel scales, fp32 [E][2I] and [E][H] on the device, indexed by
+ * expert id wherever the expert's weights are (monoserve/runtime/weights.py:103-104). */
+int monofab_moe_set_scales(monofab_moe* m, const float* s13, const float* s2);
+
+/* Hot-tier placement: int32 [E][2] = (region, slot) per expert, host memory
+ * (monoserve/runtime/weights.py:127-158 `set_location`).  Copied on `stream`. */
+int monofab_moe_set_table(monofab_moe* m, const int32_t* table, void* stream);
+
+/* The part of a published plan this layer consumes (csrc/bindings.cpp:211-232
+ * `Fabric.publish`): `ctas` = SMs given to the lane (0 = all), `credits` = link
+ * slots (CTAs that may read host memory at once), `form` = row-block height of
+ * host-resident experts, 16/32/64/128, or 0 for the weight-stationary form. */
+int monofab_moe_set_plan(monofab_moe* m, int ctas, int credits, int form);
+
+/* One layer pass on device buffers: xn bf16 [T][H] (normalised input), x2 bf16
+ * [T][H] residual or NULL, out bf16 [T][H] = bf16(x2 + moe(xn)).  Asynchronous on
+ * `stream`.  The per-layer chain router -> expand -> permute -> experts -> add
+ * of monoserve/runtime/lane.py:340-380. */
+int monofab_moe_forward(monofab_moe* m, const void* xn, const void* x2, void* out, int T, void* stream);
+
+/* The same pass from and to HOST buffers (pinned for full speed): copies xn and
+ * x2 to the device, runs the layer, copies `out` back and waits for it. */
+int monofab_moe_forward_host(monofab_moe* m, const void* xn_host, const void* x2_host, void* out_host, int T,
+                             void* stream);
+
+/* Reads and clears the device status word (synchronises `stream`). */
+int monofab_moe_status(monofab_moe* m, int32_t* status, void* stream);
+
+/* Device address and size of a named workspace, for inspection:
+ * "logits" "topk_ids" "topk_w" "counts" "starts" "pair_token" "pair_weight"
+ * "pair_pos" "xp" "h" "y" "queues" (monoserve/runtime/lane.py:101-122). */
+int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* bytes);
+
+/* Per-kernel device times of the LAST forward, in milliseconds, measured with
+ * CUDA events on the launching stream when profiling is on:
+ * [0] router logits [1] router top-k [2] plan [3] pack [4] w13 [5] w2 [6] combine. */
+int monofab_moe_set_profile(monofab_moe* m, int on);
+int monofab_moe_last_times(monofab_moe* m, float ms[7]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONOFAB_H_ */

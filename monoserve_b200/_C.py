@@ -1,0 +1,95 @@
+"""ctypes binding of libmonofab.so: the module that stands where the reference
+keeps its native extension `monoserve._C` (csrc/bindings.cpp:171-384).
+
+Raw 64-bit addresses cross this boundary, as in the reference (tensors are
+`.data_ptr()`'d in Python, monoserve/fabric/args.py:28-29).  There is no CPU
+fallback: if the shared library is missing or cannot be loaded, importing this
+module raises, and every compute call needs a CUDA device.
+"""
+import ctypes
+import json
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmonofab.so")
+
+# Every symbol include/monofab.h declares; tests check that all of them resolve.
+EXPORTS = [
+    "monofab_version", "monofab_last_error", "monofab_struct_layouts_json", "monofab_host_device_pointer",
+    "monofab_host_alloc", "monofab_host_free", "monofab_router_logits", "monofab_router_topk", "monofab_combine",
+    "monofab_moe_create", "monofab_moe_destroy", "monofab_moe_set_router", "monofab_moe_set_region",
+    "monofab_moe_set_scales", "monofab_moe_set_table", "monofab_moe_set_plan", "monofab_moe_forward",
+    "monofab_moe_forward_host", "monofab_moe_status", "monofab_moe_workspace", "monofab_moe_set_profile",
+    "monofab_moe_last_times",
+]
+
+
+class MoEConfigC(ctypes.Structure):
+    """struct monofab_moe_config of include/monofab.h."""
+    _fields_ = [("hidden", ctypes.c_int32), ("intermediate", ctypes.c_int32), ("experts", ctypes.c_int32),
+                ("top_k", ctypes.c_int32), ("max_tokens", ctypes.c_int32), ("scoring", ctypes.c_int32),
+                ("renorm", ctypes.c_int32), ("routed_scale", ctypes.c_float), ("fp8", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 7)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m monoserve_b200.build` "
+                          "(there is no CPU fallback)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, f32, u64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_uint64
+    lib.monofab_last_error.restype = ctypes.c_char_p
+    lib.monofab_struct_layouts_json.restype = ctypes.c_char_p
+    lib.monofab_host_device_pointer.argtypes = [vp, ctypes.POINTER(u64)]
+    lib.monofab_host_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp)]
+    lib.monofab_host_free.argtypes = [vp]
+    lib.monofab_router_logits.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    lib.monofab_router_topk.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp]
+    lib.monofab_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
+    lib.monofab_moe_create.argtypes = [ctypes.POINTER(MoEConfigC), ctypes.POINTER(vp)]
+    lib.monofab_moe_destroy.argtypes = [vp]
+    lib.monofab_moe_set_router.argtypes = [vp, vp, vp]
+    lib.monofab_moe_set_region.argtypes = [vp, i32, vp, vp, i32]
+    lib.monofab_moe_set_scales.argtypes = [vp, vp, vp]
+    lib.monofab_moe_set_table.argtypes = [vp, vp, vp]
+    lib.monofab_moe_set_plan.argtypes = [vp, i32, i32, i32]
+    lib.monofab_moe_forward.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.monofab_moe_forward_host.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.monofab_moe_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    lib.monofab_moe_workspace.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
+    lib.monofab_moe_set_profile.argtypes = [vp, i32]
+    lib.monofab_moe_last_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float * 7)]
+    return lib
+
+
+lib = _load()
+
+
+def check(code):
+    """Raise RuntimeError("monofab: ...") on a failing return code, as the
+    reference's native layer does (csrc/host/fabric.cpp:15-18)."""
+    if code != 0:
+        raise RuntimeError(lib.monofab_last_error().decode())
+    return code
+
+
+def struct_layouts():
+    """{name: (sizeof, {field: (offset, "u64" | "u32" | "f32")})}
+    (csrc/bindings.cpp:66-168)."""
+    raw = json.loads(lib.monofab_struct_layouts_json().decode())
+    return {k: (v[0], {f: (o, t) for f, (o, t) in v[1].items()}) for k, v in raw.items()}
+
+
+def host_device_pointer(host_addr):
+    out = ctypes.c_uint64()
+    check(lib.monofab_host_device_pointer(ctypes.c_void_p(host_addr), ctypes.byref(out)))
+    return out.value
+
+
+def gemm_args(out, ld_out, k_tiles, epi, bm, n_limit, pair_token=0, pair_weight=0, residual=0, ld_res=0, bias=0,
+              up_offset=0, w_fp8=0):
+    """Packed GemmArgs block (csrc/bindings.cpp:332-356)."""
+    from monoserve_b200.fabric.args import pack
+    return pack("GemmArgs", out=out, ld_out=ld_out, k_tiles=k_tiles, epi=epi, bm=bm, n_limit=n_limit,
+                pair_token=pair_token, pair_weight=pair_weight, residual=residual, ld_res=ld_res, bias=bias,
+                up_offset=up_offset, w_fp8=w_fp8)

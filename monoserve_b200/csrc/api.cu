@@ -1,0 +1,581 @@
+// extern "C" entry points of libmonofab (see include/monofab.h) and the host
+// side of one MoE layer: workspace ownership, tensor-map encoding, the launch
+// chain, host-buffer staging and per-kernel event timing.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/monofab.h"
+#include "kernels.h"
+#include "operands.h"
+
+namespace mf {
+
+
+thread_local std::string g_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_error = std::string("monofab: ") + buf;
+  return code;
+}
+
+#define MF_CUDA(expr)                                                                          \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess) return fail(MONOFAB_ECUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table, so the
+// library needs no link-time dependency on libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// dims/strides innermost first; strides has rank-1 entries, in bytes.
+int encode_map(CUtensorMap* map, int dtype, const void* base, int rank, const uint64_t* dims,
+               const uint64_t* strides, const uint32_t* box, int swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MONOFAB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const CUtensorMapDataType dt = dtype == 0   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapSwizzle sw = swizzle == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                : CU_TENSOR_MAP_SWIZZLE_NONE;
+  cuuint64_t d[5], s[4];
+  cuuint32_t b[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) s[i] = strides[i];
+  }
+  const CUresult r = fn(map, dt, rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MONOFAB_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MONOFAB_OK;
+}
+
+constexpr int kNumTimes = 7;
+
+}  // namespace mf
+
+using namespace mf;
+
+struct monofab_moe {
+  monofab_moe_config cfg{};
+  std::mutex mu;
+  int device = 0, num_sms = 0;
+  int ctas = 0, credits = 8, form = 64;
+  // weights
+  const void* router_w = nullptr;
+  const float* router_bias = nullptr;
+  const void* w13[2] = {nullptr, nullptr};   // device-visible addresses per region
+  const void* w2[2] = {nullptr, nullptr};
+  int slots[2] = {0, 0};
+  const float* s13 = nullptr;
+  const float* s2 = nullptr;
+  // workspaces (device)
+  float* logits = nullptr;
+  int* topk_ids = nullptr;
+  float* topk_w = nullptr;
+  int* counts = nullptr;
+  int* starts = nullptr;
+  int* chunk_counts = nullptr;
+  int* pair_rank = nullptr;
+  int* pair_token = nullptr;
+  float* pair_weight = nullptr;
+  int* pair_pos = nullptr;
+  int* table = nullptr;
+  int* hist = nullptr;
+  void* xp = nullptr;
+  void* h = nullptr;
+  float* y = nullptr;
+  void* xin = nullptr;    // staging of the host-buffer entry point
+  void* x2in = nullptr;
+  void* xout = nullptr;
+  GemmTile* tiles[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};
+  GemmQueues* queues = nullptr;
+  int* status = nullptr;
+  int* status_host = nullptr;
+  int tile_cap = 0;
+  size_t pairs_cap = 0;
+  bool maps_dirty = true;
+  GemmParams gp13{}, gp2{};
+  bool profile = false;
+  cudaEvent_t ev[kNumTimes + 1] = {};
+  float times[kNumTimes] = {};
+  bool times_valid = false;
+  std::vector<void*> owned;
+};
+
+namespace mf {
+
+int dev_alloc(monofab_moe* m, void** p, size_t bytes) {
+  MF_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+  MF_CUDA(cudaMemset(*p, 0, bytes ? bytes : 16));
+  m->owned.push_back(*p);
+  return MONOFAB_OK;
+}
+
+int build_maps(monofab_moe* m) {
+  const monofab_moe_config& c = m->cfg;
+  const int H = c.hidden, I = c.intermediate;
+  const int esz = c.fp8 ? 1 : 2;
+  for (int phase = 0; phase < 2; ++phase) {
+    GemmParams& gp = phase == 0 ? m->gp13 : m->gp2;
+    std::memset(&gp, 0, sizeof gp);
+    const uint64_t K = phase == 0 ? H : I, rows = phase == 0 ? 2 * I : H;
+    for (int region = 0; region < 2; ++region) {
+      const void* base = phase == 0 ? m->w13[region] : m->w2[region];
+      int slots = m->slots[region];
+      if (!base) {   // region unused: encode a valid map over the other region so prefetch is harmless
+        base = phase == 0 ? m->w13[1 - region] : m->w2[1 - region];
+        slots = m->slots[1 - region];
+      }
+      if (!base) return fail(MONOFAB_EINVAL, "no expert weights set (monofab_moe_set_region)");
+      const uint64_t dims[3] = {K, rows, static_cast<uint64_t>(slots)};
+      const uint64_t strides[2] = {K * esz, rows * K * esz};
+      const uint32_t box[3] = {static_cast<uint32_t>(c.fp8 ? 128 : 64), 128, 1};
+      if (int r = encode_map(&gp.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, 128)) return r;
+    }
+    const void* act = phase == 0 ? m->xp : m->h;
+    for (int i = 0; i < kActBoxes; ++i) {
+      const uint64_t dims[2] = {K, m->pairs_cap};
+      const uint64_t strides[1] = {K * 2};
+      const uint32_t box[2] = {64, static_cast<uint32_t>(16 << i)};
+      if (int r = encode_map(&gp.act_map[i], 0, act, 2, dims, strides, box, 128)) return r;
+    }
+    gp.tiles[0] = m->tiles[phase][0];
+    gp.tiles[1] = m->tiles[phase][1];
+    gp.q = m->queues;
+    gp.scale = phase == 0 ? m->s13 : m->s2;
+    gp.out = phase == 0 ? m->h : static_cast<void*>(m->y);
+    gp.status = m->status;
+    gp.phase = phase;
+    gp.k_tiles = static_cast<int>(K / 64);
+    gp.up_offset = I;
+    gp.n_limit = phase == 0 ? I : H;
+    gp.ld_out = phase == 0 ? I : H;
+    gp.scale_ld = phase == 0 ? 2 * I : H;
+  }
+  m->maps_dirty = false;
+  return MONOFAB_OK;
+}
+
+int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, int T, cudaStream_t st) {
+  const monofab_moe_config& c = m->cfg;
+  if (T < 0 || T > c.max_tokens) return fail(MONOFAB_EINVAL, "T=%d outside [0, max_tokens=%d]", T, c.max_tokens);
+  if (T == 0) return MONOFAB_OK;
+  if (!xn || !out) return fail(MONOFAB_EINVAL, "xn and out must not be NULL");
+  if (!m->router_w) return fail(MONOFAB_EINVAL, "router weight not set (monofab_moe_set_router)");
+  if (c.fp8) return fail(MONOFAB_EINVAL, "FP8 expert weights are not supported by this build of the layer");
+  if (m->maps_dirty)
+    if (int r = build_maps(m)) return r;
+  const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
+  const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
+  const int ctas = m->ctas > 0 && m->ctas < m->num_sms ? m->ctas : m->num_sms;
+  const bool prof = m->profile;
+  int evi = 0;
+  auto mark = [&]() -> cudaError_t { return prof ? cudaEventRecord(m->ev[evi++], st) : cudaSuccess; };
+
+  MF_CUDA(mark());
+  MF_CUDA(launch_router_logits(xn, m->router_w, m->logits, T, H, E, st));
+  MF_CUDA(mark());
+  RouterParams rp{m->logits, m->router_bias, m->topk_ids, m->topk_w, nullptr, m->chunk_counts, m->pair_rank,
+                  T, E, K, c.scoring, c.renorm, c.routed_scale, 0};
+  MF_CUDA(launch_router_topk(rp, st));
+  MF_CUDA(mark());
+  PlanParams pp{};
+  pp.chunk_counts = m->chunk_counts;
+  pp.counts = m->counts;
+  pp.starts = m->starts;
+  pp.table = m->table;
+  pp.hist = m->hist;
+  for (int ph = 0; ph < 2; ++ph)
+    for (int q = 0; q < 2; ++q) pp.tiles[ph][q] = m->tiles[ph][q];
+  pp.q = m->queues;
+  pp.status = m->status;
+  pp.chunks = chunks;
+  pp.E = E;
+  pp.H = H;
+  pp.I = I;
+  pp.form = m->form;
+  pp.tile_cap = m->tile_cap;
+  MF_CUDA(launch_plan(pp, st));
+  MF_CUDA(mark());
+  PackParams kp{m->topk_ids, m->topk_w, m->pair_rank, m->chunk_counts, m->starts, static_cast<const bf16*>(xn),
+                static_cast<bf16*>(m->xp), m->pair_token,
+                m->pair_weight, m->pair_pos, T, E, K, H};
+  MF_CUDA(launch_pack(kp, st));
+  MF_CUDA(mark());
+  m->gp13.cap = m->credits;
+  m->gp2.cap = m->credits;
+  MF_CUDA(launch_expert_gemm(m->gp13, kGemmModeW13, ctas, st));
+  MF_CUDA(mark());
+  MF_CUDA(launch_expert_gemm(m->gp2, kGemmModeW2, ctas, st));
+  MF_CUDA(mark());
+  CombineParams cp{m->y, m->pair_pos, m->topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(out),
+                   nullptr, nullptr, T, K, H, 0.f};
+  MF_CUDA(launch_combine(cp, st));
+  MF_CUDA(mark());
+  m->times_valid = prof;
+  return MONOFAB_OK;
+}
+
+template <class T>
+void layout_field(std::string& s, const char* name, size_t off, const char* type, bool& first) {
+  char buf[160];
+  snprintf(buf, sizeof buf, "%s\"%s\": [%zu, \"%s\"]", first ? "" : ", ", name, off, type);
+  s += buf;
+  first = false;
+}
+
+#define MF_JSON_U64(name) layout_field<S>(s, #name, offsetof(S, name), "u64", first);
+#define MF_JSON_U32(name) layout_field<S>(s, #name, offsetof(S, name), "u32", first);
+#define MF_JSON_F32(name) layout_field<S>(s, #name, offsetof(S, name), "f32", first);
+#define MF_JSON_STRUCT(Name, LIST)                                              \
+  {                                                                             \
+    using S = Name;                                                             \
+    bool first = true;                                                          \
+    char head[96];                                                              \
+    snprintf(head, sizeof head, "%s\"%s\": [%zu, {", any ? ", " : "", #Name, sizeof(S)); \
+    s += head;                                                                  \
+    LIST(MF_JSON_U64, MF_JSON_U32, MF_JSON_F32)                                 \
+    s += "}]";                                                                  \
+    any = true;                                                                 \
+  }
+
+const std::string& layouts_json() {
+  static const std::string json = [] {
+    std::string s = "{";
+    bool any = false;
+    MF_JSON_STRUCT(GemmArgs, MF_GEMM_ARGS)
+    MF_JSON_STRUCT(AttnArgs, MF_ATTN_ARGS)
+    MF_JSON_STRUCT(NormArgs, MF_NORM_ARGS)
+    MF_JSON_STRUCT(StepArgs, MF_STEP_ARGS)
+    MF_JSON_STRUCT(QkArgs, MF_QK_ARGS)
+    MF_JSON_STRUCT(RouterArgs, MF_ROUTER_ARGS)
+    MF_JSON_STRUCT(ExpandArgs, MF_EXPAND_ARGS)
+    MF_JSON_STRUCT(ReduceArgs, MF_REDUCE_ARGS)
+    MF_JSON_STRUCT(PermuteArgs, MF_PERMUTE_ARGS)
+    MF_JSON_STRUCT(SampleArgs, MF_SAMPLE_ARGS)
+    MF_JSON_STRUCT(AttnPlanArgs, MF_ATTN_PLAN_ARGS)
+    s += "}";
+    return s;
+  }();
+  return json;
+}
+
+}  // namespace mf
+
+extern "C" {
+
+int monofab_version(void) { return 100; }
+
+const char* monofab_last_error(void) { return g_error.c_str(); }
+
+const char* monofab_struct_layouts_json(void) { return layouts_json().c_str(); }
+
+int monofab_host_device_pointer(const void* host, uint64_t* device) {
+  if (!host || !device) return fail(MONOFAB_EINVAL, "host_device_pointer: NULL argument");
+  void* d = nullptr;
+  MF_CUDA(cudaHostGetDevicePointer(&d, const_cast<void*>(host), 0));
+  *device = reinterpret_cast<uint64_t>(d);
+  return MONOFAB_OK;
+}
+
+int monofab_host_alloc(size_t bytes, void** host) {
+  if (!host) return fail(MONOFAB_EINVAL, "host_alloc: NULL argument");
+  MF_CUDA(cudaHostAlloc(host, bytes ? bytes : 16, cudaHostAllocMapped | cudaHostAllocPortable));
+  return MONOFAB_OK;
+}
+
+int monofab_host_free(void* host) {
+  if (host) MF_CUDA(cudaFreeHost(host));
+  return MONOFAB_OK;
+}
+
+int monofab_router_logits(const void* x, const void* wr, float* logits, int T, int H, int E, void* stream) {
+  if (!x || !wr || !logits) return fail(MONOFAB_EINVAL, "router_logits: NULL argument");
+  if (T < 0 || E <= 0 || H <= 0 || H % 256) return fail(MONOFAB_EINVAL, "router_logits: H=%d must be a positive multiple of 256", H);
+  MF_CUDA(launch_router_logits(x, wr, logits, T, H, E, static_cast<cudaStream_t>(stream)));
+  return MONOFAB_OK;
+}
+
+int monofab_router_topk(float* logits, const float* bias, int32_t* topk_ids, float* topk_w, int32_t* counts,
+                        int32_t* chunk_counts, int32_t* pair_rank, int T, int E, int K, int scoring, int renorm,
+                        float scale, int zero_logits, void* stream) {
+  if (!logits || !topk_ids || !topk_w) return fail(MONOFAB_EINVAL, "router_topk: NULL argument");
+  if (E < 1 || E > kMaxExperts) return fail(MONOFAB_EINVAL, "router_topk: E=%d outside [1, %d]", E, kMaxExperts);
+  if (K < 1 || K > kMaxTopK || K > E) return fail(MONOFAB_EINVAL, "router_topk: K=%d outside [1, min(E, %d)]", K, kMaxTopK);
+  if (T < 0) return fail(MONOFAB_EINVAL, "router_topk: negative T");
+  RouterParams rp{logits, bias, topk_ids, topk_w, counts, chunk_counts, pair_rank, T, E, K, scoring, renorm, scale,
+                  zero_logits};
+  MF_CUDA(launch_router_topk(rp, static_cast<cudaStream_t>(stream)));
+  return MONOFAB_OK;
+}
+
+int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w, const void* x2, void* x,
+                    const void* norm_w, void* normed, int T, int K, int H, float eps, void* stream) {
+  if (!y || !pair_pos || !topk_w || !x) return fail(MONOFAB_EINVAL, "combine: NULL argument");
+  if (norm_w && !normed) return fail(MONOFAB_EINVAL, "combine: norm_w given without an output");
+  if (K < 1 || K > 32 || H <= 0 || H % 8) return fail(MONOFAB_EINVAL, "combine: bad K=%d or H=%d", K, H);
+  CombineParams cp{y, pair_pos, topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(x),
+                   static_cast<const bf16*>(norm_w), static_cast<bf16*>(normed), T, K, H, eps};
+  MF_CUDA(launch_combine(cp, static_cast<cudaStream_t>(stream)));
+  return MONOFAB_OK;
+}
+
+int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
+  if (!cfg || !out) return fail(MONOFAB_EINVAL, "moe_create: NULL argument");
+  const monofab_moe_config& c = *cfg;
+  if (c.hidden <= 0 || c.hidden % 256) return fail(MONOFAB_EINVAL, "hidden=%d must be a positive multiple of 256", c.hidden);
+  if (c.intermediate <= 0 || c.intermediate % 64) return fail(MONOFAB_EINVAL, "intermediate=%d must be a positive multiple of 64", c.intermediate);
+  if (c.experts < 1 || c.experts > kMaxExperts) return fail(MONOFAB_EINVAL, "experts=%d outside [1, %d]", c.experts, kMaxExperts);
+  if (c.top_k < 1 || c.top_k > kMaxTopK || c.top_k > c.experts) return fail(MONOFAB_EINVAL, "top_k=%d outside [1, min(E, %d)]", c.top_k, kMaxTopK);
+  if (c.max_tokens < 1) return fail(MONOFAB_EINVAL, "max_tokens=%d must be positive", c.max_tokens);
+  int dev = 0;
+  MF_CUDA(cudaGetDevice(&dev));
+  cudaDeviceProp prop;
+  MF_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) return fail(MONOFAB_ECUDA, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+  monofab_moe* m = new monofab_moe();
+  m->cfg = c;
+  m->device = dev;
+  m->num_sms = prop.multiProcessorCount;
+  const size_t T = c.max_tokens, H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
+  const size_t P = T * K, chunks = (T + kChunkTokens - 1) / kChunkTokens;
+  // Packed rows are addressed by TMA boxes of up to 128 rows; pad so a box that
+  // starts at the last row stays inside the allocation.
+  m->pairs_cap = P + 128;
+  // Row blocks: at most P/16 + E blocks of >= 16 rows (form 16) in the worst case.
+  const size_t blocks_max = P / 16 + E;
+  m->tile_cap = static_cast<int>(blocks_max * std::max((I + 127) / 128, (H + 127) / 128));
+  int r = 0;
+  auto A = [&](auto** p, size_t bytes) { if (!r) r = dev_alloc(m, reinterpret_cast<void**>(p), bytes); };
+  A(&m->logits, T * E * 4);
+  A(&m->topk_ids, P * 4);
+  A(&m->topk_w, P * 4);
+  A(&m->counts, E * 4);
+  A(&m->starts, (E + 1) * 4);
+  A(&m->chunk_counts, chunks * E * 4);
+  A(&m->pair_rank, P * 4);
+  A(&m->pair_token, m->pairs_cap * 4);
+  A(&m->pair_weight, m->pairs_cap * 4);
+  A(&m->pair_pos, P * 4);
+  A(&m->table, E * 2 * 4);
+  A(&m->hist, E * 4);
+  A(&m->xp, m->pairs_cap * H * 2);
+  A(&m->h, m->pairs_cap * I * 2);
+  A(&m->y, m->pairs_cap * H * 4);
+  A(&m->xin, T * H * 2);
+  A(&m->x2in, T * H * 2);
+  A(&m->xout, T * H * 2);
+  for (int ph = 0; ph < 2; ++ph)
+    for (int q = 0; q < 2; ++q) A(&m->tiles[ph][q], static_cast<size_t>(m->tile_cap) * sizeof(GemmTile));
+  A(&m->queues, sizeof(GemmQueues));
+  A(&m->status, 4);
+  if (!r && cudaHostAlloc(reinterpret_cast<void**>(&m->status_host), 64, cudaHostAllocDefault) != cudaSuccess)
+    r = fail(MONOFAB_ECUDA, "cudaHostAlloc of the status mirror failed");
+  for (int i = 0; !r && i <= kNumTimes; ++i)
+    if (cudaEventCreate(&m->ev[i]) != cudaSuccess) r = fail(MONOFAB_ECUDA, "cudaEventCreate failed");
+  if (r) {
+    monofab_moe_destroy(m);
+    return r;
+  }
+  // default placement: every expert in the hot tier, slot = expert id
+  std::vector<int> table(2 * E);
+  for (size_t e = 0; e < E; ++e) {
+    table[2 * e] = MONOFAB_REGION_HOT;
+    table[2 * e + 1] = static_cast<int>(e);
+  }
+  if (cudaMemcpy(m->table, table.data(), table.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+    monofab_moe_destroy(m);
+    return fail(MONOFAB_ECUDA, "copy of the default placement table failed");
+  }
+  *out = m;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_destroy(monofab_moe* m) {
+  if (!m) return MONOFAB_OK;
+  cudaDeviceSynchronize();
+  for (void* p : m->owned) cudaFree(p);
+  if (m->status_host) cudaFreeHost(m->status_host);
+  for (cudaEvent_t e : m->ev)
+    if (e) cudaEventDestroy(e);
+  delete m;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_router(monofab_moe* m, const void* wr, const float* bias) {
+  if (!m || !wr) return fail(MONOFAB_EINVAL, "set_router: NULL argument");
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->router_w = wr;
+  m->router_bias = bias;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_region(monofab_moe* m, int region, const void* w13, const void* w2, int slots) {
+  if (!m) return fail(MONOFAB_EINVAL, "set_region: NULL handle");
+  if (region != MONOFAB_REGION_HOST && region != MONOFAB_REGION_HOT)
+    return fail(MONOFAB_EINVAL, "set_region: region %d is neither host (0) nor hot (1)", region);
+  if (!w13 || !w2 || slots < 1) return fail(MONOFAB_EINVAL, "set_region: NULL weights or slots=%d < 1", slots);
+  std::lock_guard<std::mutex> lock(m->mu);
+  if (region == MONOFAB_REGION_HOST) {
+    void *d13 = nullptr, *d2 = nullptr;
+    MF_CUDA(cudaHostGetDevicePointer(&d13, const_cast<void*>(w13), 0));
+    MF_CUDA(cudaHostGetDevicePointer(&d2, const_cast<void*>(w2), 0));
+    w13 = d13;
+    w2 = d2;
+  }
+  if ((reinterpret_cast<uintptr_t>(w13) | reinterpret_cast<uintptr_t>(w2)) & 15)
+    return fail(MONOFAB_EINVAL, "set_region: weight stacks must be 16-byte aligned");
+  m->w13[region] = w13;
+  m->w2[region] = w2;
+  m->slots[region] = slots;
+  m->maps_dirty = true;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_scales(monofab_moe* m, const float* s13, const float* s2) {
+  if (!m) return fail(MONOFAB_EINVAL, "set_scales: NULL handle");
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->s13 = s13;
+  m->s2 = s2;
+  m->maps_dirty = true;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_table(monofab_moe* m, const int32_t* table, void* stream) {
+  if (!m || !table) return fail(MONOFAB_EINVAL, "set_table: NULL argument");
+  std::lock_guard<std::mutex> lock(m->mu);
+  const int E = m->cfg.experts;
+  for (int e = 0; e < E; ++e) {
+    const int region = table[2 * e], slot = table[2 * e + 1];
+    if (region != MONOFAB_REGION_HOST && region != MONOFAB_REGION_HOT)
+      return fail(MONOFAB_EINVAL, "set_table: expert %d has region %d (host 0 / hot 1 expected)", e, region);
+    if (slot < 0 || slot >= m->slots[region])
+      return fail(MONOFAB_EINVAL, "set_table: expert %d slot %d outside region %d (%d slots)", e, slot, region,
+                  m->slots[region]);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MF_CUDA(cudaMemcpyAsync(m->table, table, static_cast<size_t>(E) * 8, cudaMemcpyHostToDevice, st));
+  MF_CUDA(cudaStreamSynchronize(st));
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_plan(monofab_moe* m, int ctas, int credits, int form) {
+  if (!m) return fail(MONOFAB_EINVAL, "set_plan: NULL handle");
+  if (ctas < 0) return fail(MONOFAB_EINVAL, "set_plan: ctas=%d is negative", ctas);
+  if (credits < 0) return fail(MONOFAB_EINVAL, "set_plan: credits=%d is negative", credits);
+  if (form != 0 && form != 16 && form != 32 && form != 64 && form != 128)
+    return fail(MONOFAB_EINVAL, "set_plan: form=%d is not one of 0, 16, 32, 64, 128", form);
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->ctas = ctas;
+  m->credits = credits;
+  m->form = form;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_forward(monofab_moe* m, const void* xn, const void* x2, void* out, int T, void* stream) {
+  if (!m) return fail(MONOFAB_EINVAL, "forward: NULL handle");
+  std::lock_guard<std::mutex> lock(m->mu);
+  return forward_locked(m, xn, x2, out, T, static_cast<cudaStream_t>(stream));
+}
+
+int monofab_moe_forward_host(monofab_moe* m, const void* xn_host, const void* x2_host, void* out_host, int T,
+                             void* stream) {
+  if (!m) return fail(MONOFAB_EINVAL, "forward_host: NULL handle");
+  if (!xn_host || !out_host) return fail(MONOFAB_EINVAL, "forward_host: NULL buffer");
+  std::lock_guard<std::mutex> lock(m->mu);
+  if (T < 0 || T > m->cfg.max_tokens) return fail(MONOFAB_EINVAL, "T=%d outside [0, max_tokens=%d]", T, m->cfg.max_tokens);
+  if (T == 0) return MONOFAB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t bytes = static_cast<size_t>(T) * m->cfg.hidden * 2;
+  MF_CUDA(cudaMemcpyAsync(m->xin, xn_host, bytes, cudaMemcpyHostToDevice, st));
+  if (x2_host) MF_CUDA(cudaMemcpyAsync(m->x2in, x2_host, bytes, cudaMemcpyHostToDevice, st));
+  if (int r = forward_locked(m, m->xin, x2_host ? m->x2in : nullptr, m->xout, T, st)) return r;
+  MF_CUDA(cudaMemcpyAsync(out_host, m->xout, bytes, cudaMemcpyDeviceToHost, st));
+  MF_CUDA(cudaStreamSynchronize(st));
+  return MONOFAB_OK;
+}
+
+int monofab_moe_status(monofab_moe* m, int32_t* status, void* stream) {
+  if (!m || !status) return fail(MONOFAB_EINVAL, "status: NULL argument");
+  std::lock_guard<std::mutex> lock(m->mu);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MF_CUDA(cudaMemcpyAsync(m->status_host, m->status, 4, cudaMemcpyDeviceToHost, st));
+  MF_CUDA(cudaMemsetAsync(m->status, 0, 4, st));
+  MF_CUDA(cudaStreamSynchronize(st));
+  *status = *m->status_host;
+  if (*status) return fail(MONOFAB_EDEVICE, "device status 0x%x%s%s", *status,
+                           (*status & MONOFAB_STATUS_WAIT_TIMEOUT) ? " (a bounded wait timed out)" : "",
+                           (*status & MONOFAB_STATUS_PLAN_OVERFLOW) ? " (GEMM plan overflow)" : "");
+  return MONOFAB_OK;
+}
+
+int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* bytes) {
+  if (!m || !name || !ptr || !bytes) return fail(MONOFAB_EINVAL, "workspace: NULL argument");
+  const monofab_moe_config& c = m->cfg;
+  const size_t T = c.max_tokens, H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k, P = T * K;
+  struct Entry { const char* name; void* p; size_t bytes; };
+  const Entry entries[] = {
+      {"logits", m->logits, T * E * 4},        {"topk_ids", m->topk_ids, P * 4},
+      {"topk_w", m->topk_w, P * 4},            {"counts", m->counts, E * 4},
+      {"starts", m->starts, (E + 1) * 4},      {"pair_token", m->pair_token, P * 4},
+      {"pair_weight", m->pair_weight, P * 4},  {"pair_pos", m->pair_pos, P * 4},
+      {"xp", m->xp, P * H * 2},                {"h", m->h, P * I * 2},
+      {"y", m->y, P * H * 4},                  {"queues", m->queues, sizeof(GemmQueues)},
+      {"hist", m->hist, E * 4},                {"table", m->table, E * 8},
+  };
+  for (const Entry& e : entries)
+    if (!std::strcmp(e.name, name)) {
+      *ptr = e.p;
+      *bytes = e.bytes;
+      return MONOFAB_OK;
+    }
+  return fail(MONOFAB_EINVAL, "workspace: unknown name '%s'", name);
+}
+
+int monofab_moe_set_profile(monofab_moe* m, int on) {
+  if (!m) return fail(MONOFAB_EINVAL, "set_profile: NULL handle");
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->profile = on != 0;
+  m->times_valid = false;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_last_times(monofab_moe* m, float ms[7]) {
+  if (!m || !ms) return fail(MONOFAB_EINVAL, "last_times: NULL argument");
+  std::lock_guard<std::mutex> lock(m->mu);
+  if (!m->times_valid) return fail(MONOFAB_EINVAL, "last_times: no profiled forward to report (monofab_moe_set_profile)");
+  MF_CUDA(cudaEventSynchronize(m->ev[kNumTimes]));
+  for (int i = 0; i < kNumTimes; ++i) MF_CUDA(cudaEventElapsedTime(&ms[i], m->ev[i], m->ev[i + 1]));
+  return MONOFAB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,76 @@
+// Parameter blocks and launchers of the layer's kernels, shared by the kernel
+// files and the host entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "types.h"
+
+namespace mf {
+
+using bf16 = __nv_bfloat16;
+
+struct RouterParams {
+  float* logits;            // fp32 [T][E]; zeroed after reading when zero_logits is set
+  const float* bias;        // fp32 [E] selection bias (sigmoid scoring) or null
+  int* topk_ids;            // int32 [T][K]
+  float* topk_w;            // fp32 [T][K]
+  int* counts;              // int32 [E], accumulated with integer atomics, or null
+  int* chunk_counts;        // int32 [chunks][E] pairs of each chunk per expert, or null
+  int* pair_rank;           // int32 [T][K] stable rank inside (chunk, expert), or null
+  int T, E, K;
+  int scoring;              // 0 softmax, 1 sigmoid
+  int renorm;
+  float scale;
+  int zero_logits;
+};
+
+struct PlanParams {
+  int* chunk_counts;        // in: [chunks][E] counts; out: exclusive prefix over chunks per expert
+  int* counts;              // out int32 [E]
+  int* starts;              // out int32 [E + 1]
+  const int* table;         // int32 [E][2] = (region, slot): region 0 host, 1 hot tier
+  int* hist;                // int32 [E] activation histogram (+=), or null
+  GemmTile* tiles[2][2];    // [phase][0 = link, 1 = hbm]
+  GemmQueues* q;
+  int* status;
+  int chunks, E, H, I;
+  int form;                 // row-block height of host-resident experts: 16/32/64/128; 0 = 128
+  int tile_cap;             // capacity of each tile list
+};
+
+struct PackParams {
+  const int* topk_ids;      // [T][K]
+  const float* topk_w;      // [T][K]
+  const int* pair_rank;     // [T][K]
+  const int* chunk_prefix;  // [chunks][E]
+  const int* starts;        // [E + 1]
+  const bf16* src;          // [T][H]
+  bf16* dst;                // [P][H]
+  int* pair_token;          // [P]
+  float* pair_weight;       // [P]
+  int* pair_pos;            // [T][K] packed row of every (token, pick)
+  int T, E, K, H;
+};
+
+struct CombineParams {
+  const float* y;           // fp32 [P][H] expert outputs of every pair
+  const int* pair_pos;      // [T][K]
+  const float* topk_w;      // [T][K]
+  const bf16* x2;           // bf16 [T][H] residual, or null (treated as zero)
+  bf16* x;                  // bf16 [T][H] out: bf16(x2 + moe)
+  const bf16* norm_w;       // bf16 [H] weight of the following RMSNorm, or null
+  bf16* normed;             // bf16 [T][H] out: rmsnorm(x) * norm_w (when norm_w is set)
+  int T, K, H;
+  float eps;
+};
+
+cudaError_t launch_router_logits(const void* x, const void* wr, float* logits, int T, int H, int E,
+                                 cudaStream_t stream);
+cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream);
+cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream);
+cudaError_t launch_pack(const PackParams& A, cudaStream_t stream);
+cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
+cudaError_t launch_expert_gemm(const GemmParams& p, int mode, int ctas, cudaStream_t stream);
+
+}  // namespace mf

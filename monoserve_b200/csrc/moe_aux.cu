@@ -1,0 +1,445 @@
+// Routing, planning, packing and combining kernels of one MoE layer.  These
+// are HBM/latency-bound integer and byte kernels built on warp primitives; no
+// tensor cores.  Their results are defined exactly (see detmath.cuh) so that a
+// CPU oracle can be compared bit for bit:
+//
+//   router_logits   logits[t][e] = sum_h x[t][h] * Wr[e][h]   fp32, fixed order
+//   router_topk     softmax / sigmoid(+bias), K rounds of arg-max with the
+//                   lowest index winning ties, renormalisation, scale
+//                   (csrc/fabric/tiles/aux.cuh:326-417), plus the stable rank of
+//                   every (token, pick) pair inside its 32-token chunk
+//   plan            per-expert counts, exclusive prefix sums (aux.cuh:423-450),
+//                   per-chunk bases, and the grouped-GEMM tile lists chosen
+//                   through the layer's (region, slot) table (aux.cuh:453-616)
+//   pack            expert-sorted activation rows and pair lists
+//                   (aux.cuh:648-684).  The reference orders an expert's rows by
+//                   atomic arrival; here the order is fixed: token ascending,
+//                   then pick ascending.
+//   combine         x[t] = bf16(x2[t] + sum_k w[t][k] * y[pos(t,k)]) in pick
+//                   order, optionally followed by the next RMSNorm
+//                   (aux.cuh:137-188; the reference sums with fp32 atomics).
+#include <cuda_bf16.h>
+
+#include "detmath.cuh"
+#include "kernels.h"
+
+namespace mf {
+
+__device__ __forceinline__ void unpack8(const uint4& u, float f[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float f[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// ------------------------------------------------------------ router logits
+// One warp computes the logits of one token against kExpertsPerWarp experts.
+// Lane l owns elements h = 256 j + 8 l + i (j outer, i = 0..7 inner) and
+// accumulates them in that order with fused multiply-adds into one fp32
+// partial; the 32 partials are summed by the xor butterfly 16, 8, 4, 2, 1.
+constexpr int kExpertsPerWarp = 16;
+
+template <int J>
+__global__ void __launch_bounds__(256) router_logits_kernel(const bf16* __restrict__ x, const bf16* __restrict__ wr,
+                                                            float* __restrict__ logits, int T, int H, int E) {
+  const int lane = threadIdx.x & 31;
+  const int groups = (E + kExpertsPerWarp - 1) / kExpertsPerWarp;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= static_cast<long long>(T) * groups) return;
+  const int t = static_cast<int>(unit / groups), eg = static_cast<int>(unit % groups);
+  const int nj = J > 0 ? J : H / 256;
+  const uint4* x4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
+  float xr[J > 0 ? J : 1][8];
+  if (J > 0) {
+#pragma unroll
+    for (int j = 0; j < J; ++j) unpack8(x4[32 * j + lane], xr[j]);
+  }
+  const int e_hi = min(E, (eg + 1) * kExpertsPerWarp);
+  for (int e = eg * kExpertsPerWarp; e < e_hi; ++e) {
+    const uint4* w4 = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * H);
+    float acc = 0.f;
+    if (J > 0) {
+      uint4 wv[J > 0 ? J : 1];
+#pragma unroll
+      for (int j = 0; j < J; ++j) wv[j] = __ldg(w4 + 32 * j + lane);
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        float wf[8];
+        unpack8(wv[j], wf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = __fmaf_rn(xr[j][i], wf[i], acc);
+      }
+    } else {
+      for (int j = 0; j < nj; ++j) {
+        float xf[8], wf[8];
+        unpack8(x4[32 * j + lane], xf);
+        unpack8(__ldg(w4 + 32 * j + lane), wf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = __fmaf_rn(xf[i], wf[i], acc);
+      }
+    }
+    acc = warp_sum_xor(acc);
+    if (lane == (e & 31)) logits[static_cast<size_t>(t) * E + e] = acc;
+  }
+}
+
+// -------------------------------------------------------------- router top-k
+// One block per chunk of 32 tokens, one warp per token.
+
+__global__ void __launch_bounds__(1024) router_topk_kernel(const RouterParams A) {
+  __shared__ int s_ids[kChunkTokens * kMaxTopK];
+  __shared__ int s_hist[kMaxExperts];
+  constexpr int kMaxPer = kMaxExperts / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int E = A.E, K = A.K;
+  const int r = blockIdx.x * kChunkTokens + warp;
+  if (threadIdx.x < kMaxExperts) s_hist[threadIdx.x] = 0;
+  if (r < A.T) {
+    float* lg = A.logits + static_cast<size_t>(r) * E;
+    float p[kMaxPer], sel[kMaxPer];
+#pragma unroll
+    for (int i = 0; i < kMaxPer; ++i) {
+      const int e = lane + 32 * i;
+      p[i] = e < E ? lg[e] : -1e30f;
+    }
+    if (A.zero_logits) {
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i)
+        if (lane + 32 * i < E) lg[lane + 32 * i] = 0.f;
+    }
+    if (A.scoring == 0) {
+      float mx = -1e30f;
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) mx = fmaxf(mx, p[i]);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        p[i] = det_expf(__fsub_rn(p[i], mx));
+        s = __fadd_rn(s, p[i]);
+      }
+      s = warp_sum_xor(s);
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        p[i] = __fdiv_rn(p[i], s);
+        sel[i] = lane + 32 * i < E ? p[i] : -1e30f;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        const int e = lane + 32 * i;
+        p[i] = det_sigmoidf(p[i]);
+        sel[i] = e < E ? __fadd_rn(p[i], A.bias ? A.bias[e] : 0.f) : -1e30f;
+      }
+    }
+    int my_id = 0;
+    float my_w = 0.f, wsum = 0.f;
+    for (int k = 0; k < K; ++k) {
+      float bv = -1e30f;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        const int e = lane + 32 * i;
+        if (sel[i] > bv || (sel[i] == bv && e < bi)) {
+          bv = sel[i];
+          bi = e;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      float mine = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMaxPer; ++i) {
+        if (i == (bi >> 5)) {
+          mine = p[i];
+          if (lane == (bi & 31)) sel[i] = -1e30f;
+        }
+      }
+      const float w = __shfl_sync(0xffffffffu, mine, bi & 31);
+      if (lane == k) {
+        my_id = bi;
+        my_w = w;
+      }
+      wsum = __fadd_rn(wsum, w);
+    }
+    if (lane < K) {
+      A.topk_ids[static_cast<size_t>(r) * K + lane] = my_id;
+      A.topk_w[static_cast<size_t>(r) * K + lane] =
+          __fmul_rn(A.renorm ? __fdiv_rn(my_w, wsum) : my_w, A.scale);
+      s_ids[warp * K + lane] = my_id;
+    }
+  }
+  __syncthreads();
+  const int rows = min(kChunkTokens, A.T - blockIdx.x * kChunkTokens);
+  const int pairs = rows * K;
+  if (static_cast<int>(threadIdx.x) < pairs) {
+    const int me = s_ids[threadIdx.x];
+    int rank = 0;
+    for (int q = 0; q < static_cast<int>(threadIdx.x); ++q) rank += s_ids[q] == me;
+    if (A.pair_rank) A.pair_rank[static_cast<size_t>(blockIdx.x) * kChunkTokens * K + threadIdx.x] = rank;
+    atomicAdd(&s_hist[me], 1);
+  }
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < E) {
+    const int c = s_hist[threadIdx.x];
+    if (A.chunk_counts) A.chunk_counts[static_cast<size_t>(blockIdx.x) * E + threadIdx.x] = c;
+    if (A.counts && c) atomicAdd(A.counts + threadIdx.x, c);
+  }
+}
+
+// ---------------------------------------------------------------------- plan
+
+// Exclusive scan of one int per thread over a 256-thread block; returns the
+// exclusive prefix and writes the block total.
+__device__ __forceinline__ int block_scan_256(int v, int* s_warp, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += y;
+  }
+  __syncthreads();
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int base = 0;
+  total = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const int s = s_warp[w];
+    if (w < warp) base += s;
+    total += s;
+  }
+  return base + incl - v;
+}
+
+__global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
+  __shared__ int s_warp[8];
+  const int e = threadIdx.x;
+  const int E = A.E;
+  int cnt = 0;
+  if (e < E) {
+    for (int c = 0; c < A.chunks; ++c) {
+      int* cell = A.chunk_counts + static_cast<size_t>(c) * E + e;
+      const int v = *cell;
+      *cell = cnt;
+      cnt += v;
+    }
+    A.counts[e] = cnt;
+    if (A.hist) A.hist[e] += cnt;
+  }
+  int total;
+  const int start = block_scan_256(cnt, s_warp, total);
+  if (e < E) A.starts[e] = start;
+  if (e == 0) A.starts[E] = total;
+
+  int tier = kTierHot, z = 0, bh = 128, nb = 0;
+  if (e < E && cnt > 0) {
+    tier = A.table[2 * e] == 0 ? kTierHost : kTierHot;
+    z = A.table[2 * e + 1];
+    if (tier == kTierHost && A.form) bh = A.form;
+    nb = (cnt + bh - 1) / bh;
+  }
+  const int f13 = (A.I + 127) / 128, f2 = (A.H + 127) / 128;
+  int first[2][2], totals[2][2];
+  for (int ph = 0; ph < 2; ++ph)
+    for (int tq = 0; tq < 2; ++tq) {
+      const int mine = (nb && tier == tq) ? nb * (ph == 0 ? f13 : f2) : 0;
+      first[ph][tq] = block_scan_256(mine, s_warp, totals[ph][tq]);
+    }
+  bool overflow = false;
+  for (int ph = 0; ph < 2; ++ph)
+    for (int tq = 0; tq < 2; ++tq) overflow |= totals[ph][tq] > A.tile_cap;
+  if (e == 0) {
+    for (int ph = 0; ph < 2; ++ph)
+      for (int tq = 0; tq < 2; ++tq) {
+        A.q->n_tiles[ph][tq] = overflow ? 0 : totals[ph][tq];
+        A.q->head[ph][tq] = 0;
+      }
+    A.q->slots[0] = A.q->slots[1] = 0;
+    if (overflow) atomicOr(A.status, kErrPlanOverflow);
+  }
+  if (overflow || nb == 0) return;
+  for (int ph = 0; ph < 2; ++ph) {
+    GemmTile* out = A.tiles[ph][tier] + first[ph][tier];
+    const int nf = ph == 0 ? f13 : f2;
+    for (int b = 0; b < nb; ++b) {
+      const int rows = min(bh, cnt - b * bh);
+      int n = 16;
+      while (n < rows) n <<= 1;
+      for (int f = 0; f < nf; ++f) {
+        GemmTile t;
+        t.w_row0 = f * 128;
+        t.act_row0 = start + b * bh;
+        t.rows = rows;
+        t.n = n;
+        t.z = z;
+        t.tier = tier;
+        t.expert = e;
+        t.pad = 0;
+        *out++ = t;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------- pack
+
+__global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= A.T) return;
+  const int K = A.K;
+  int pos = 0;
+  if (lane < K) {
+    const int e = A.topk_ids[static_cast<size_t>(t) * K + lane];
+    pos = A.starts[e] + A.chunk_prefix[static_cast<size_t>(t / kChunkTokens) * A.E + e] +
+          A.pair_rank[static_cast<size_t>(t) * K + lane];
+    A.pair_token[pos] = t;
+    A.pair_weight[pos] = A.topk_w[static_cast<size_t>(t) * K + lane];
+    A.pair_pos[static_cast<size_t>(t) * K + lane] = pos;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(A.src + static_cast<size_t>(t) * A.H);
+  const int n16 = A.H / 8;
+  for (int c0 = 0; c0 < n16; c0 += 32 * 8) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c0 + 32 * i + lane < n16) v[i] = src[c0 + 32 * i + lane];
+    for (int k = 0; k < K; ++k) {
+      const int pk = __shfl_sync(0xffffffffu, pos, k);
+      uint4* dst = reinterpret_cast<uint4*>(A.dst + static_cast<size_t>(pk) * A.H);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + 32 * i + lane < n16) dst[c0 + 32 * i + lane] = v[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------- combine
+
+__global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= A.T) return;
+  const int K = A.K, H = A.H, n16 = H / 8;
+  int pos = 0;
+  float w = 0.f;
+  if (lane < K) {
+    pos = A.pair_pos[static_cast<size_t>(t) * K + lane];
+    w = A.topk_w[static_cast<size_t>(t) * K + lane];
+  }
+  const uint4* x2 = A.x2 ? reinterpret_cast<const uint4*>(A.x2 + static_cast<size_t>(t) * H) : nullptr;
+  uint4* xo = reinterpret_cast<uint4*>(A.x + static_cast<size_t>(t) * H);
+  float ss = 0.f;
+  for (int c = lane; c < n16; c += 32) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int pk = __shfl_sync(0xffffffffu, pos, k);
+      const float wk = __shfl_sync(0xffffffffu, w, k);
+      const float4* yr = reinterpret_cast<const float4*>(A.y + static_cast<size_t>(pk) * H) + 2 * c;
+      const float4 a = __ldcs(yr), b = __ldcs(yr + 1);
+      acc[0] = __fmaf_rn(wk, a.x, acc[0]);
+      acc[1] = __fmaf_rn(wk, a.y, acc[1]);
+      acc[2] = __fmaf_rn(wk, a.z, acc[2]);
+      acc[3] = __fmaf_rn(wk, a.w, acc[3]);
+      acc[4] = __fmaf_rn(wk, b.x, acc[4]);
+      acc[5] = __fmaf_rn(wk, b.y, acc[5]);
+      acc[6] = __fmaf_rn(wk, b.z, acc[6]);
+      acc[7] = __fmaf_rn(wk, b.w, acc[7]);
+    }
+    float f[8];
+    if (x2) {
+      unpack8(x2[c], f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      f[j] = round_bf16(__fadd_rn(f[j], acc[j]));
+      ss = __fmaf_rn(f[j], f[j], ss);
+    }
+    xo[c] = pack8(f);
+  }
+  if (!A.norm_w) return;
+  // RMSNorm of the row this warp just wrote: out = bf16(bf16(x * inv) * w).
+  ss = warp_sum_xor(ss);
+  const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(ss, static_cast<float>(H)), A.eps));
+  __syncwarp();
+  const uint4* w4 = reinterpret_cast<const uint4*>(A.norm_w);
+  uint4* out = reinterpret_cast<uint4*>(A.normed + static_cast<size_t>(t) * H);
+  for (int c = lane; c < n16; c += 32) {
+    float f[8], g[8];
+    unpack8(xo[c], f);
+    unpack8(w4[c], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(round_bf16(__fmul_rn(f[j], inv)), g[j]);
+    out[c] = pack8(f);
+  }
+}
+
+// ------------------------------------------------------------------ launchers
+cudaError_t launch_router_logits(const void* x, const void* wr, float* logits, int T, int H, int E,
+                                 cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  const int groups = (E + kExpertsPerWarp - 1) / kExpertsPerWarp;
+  const long long units = static_cast<long long>(T) * groups;
+  const int blocks = static_cast<int>((units + 7) / 8);
+  const bf16* xb = static_cast<const bf16*>(x);
+  const bf16* wb = static_cast<const bf16*>(wr);
+  switch (H / 256) {
+    case 2: router_logits_kernel<2><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+    case 4: router_logits_kernel<4><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+    case 8: router_logits_kernel<8><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+    case 16: router_logits_kernel<16><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+    default: router_logits_kernel<0><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream) {
+  if (A.T == 0) return cudaSuccess;
+  router_topk_kernel<<<(A.T + kChunkTokens - 1) / kChunkTokens, 1024, 0, stream>>>(A);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream) {
+  plan_kernel<<<1, 256, 0, stream>>>(A);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack(const PackParams& A, cudaStream_t stream) {
+  if (A.T == 0) return cudaSuccess;
+  pack_kernel<<<(A.T + 7) / 8, 256, 0, stream>>>(A);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream) {
+  if (A.T == 0) return cudaSuccess;
+  combine_kernel<<<(A.T + 7) / 8, 256, 0, stream>>>(A);
+  return cudaGetLastError();
+}
+
+}  // namespace mf

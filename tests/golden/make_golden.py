@@ -1,0 +1,145 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own torch oracle.
+
+Run in a container that has the reference checkout (default /root/reference,
+or $MONOSERVE_REFERENCE):
+
+    python tests/golden/make_golden.py
+
+It imports the reference's test modules tests/test_fabric_model.py and
+tests/test_fabric_model_glm.py and calls their `reference_logits` unchanged.
+Those functions hard-code device="cuda" and expect the reference's native
+module; so, for the duration of the call only, a stub `monoserve._C` is put in
+sys.modules and the torch factory functions they use are wrapped to place
+tensors on the CPU (Tensor.cuda becomes the identity).  No reference source is
+copied: the functions run from where they lie.
+
+Weights are drawn from a seeded generator in a fixed order (see `make_weights`)
+so the tests can regenerate them; the fixture stores their CRC-32 values.
+"""
+import importlib
+import os
+import sys
+import types
+import zlib
+from contextlib import contextmanager
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("MONOSERVE_REFERENCE", "/root/reference")
+
+
+@contextmanager
+def reference_on_cpu():
+    """Make the reference's test oracles importable and runnable without a GPU."""
+    stub = types.ModuleType("monoserve._C")
+    saved_mod = sys.modules.get("monoserve._C")
+    sys.modules["monoserve._C"] = stub
+    sys.path[:0] = [REF, os.path.join(REF, "tests")]
+    names = ["tensor", "arange", "zeros", "ones"]
+    saved = {n: getattr(torch, n) for n in names}
+    saved_cuda = torch.Tensor.cuda
+
+    def on_cpu(fn):
+        def wrapped(*a, **k):
+            if k.get("device") == "cuda":
+                k["device"] = "cpu"
+            return fn(*a, **k)
+        return wrapped
+
+    for n in names:
+        setattr(torch, n, on_cpu(saved[n]))
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        yield
+    finally:
+        for n in names:
+            setattr(torch, n, saved[n])
+        torch.Tensor.cuda = saved_cuda
+        del sys.path[:2]
+        if saved_mod is None:
+            sys.modules.pop("monoserve._C", None)
+        else:
+            sys.modules["monoserve._C"] = saved_mod
+
+
+def bf16_bits(t):
+    return t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def make_weights(cfg, seed):
+    """Random bf16 weights of a tiny Qwen3-style model, drawn in this order."""
+    g = torch.Generator().manual_seed(seed)
+    H, I, E, L, V = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.num_layers, cfg.vocab
+    hq, hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16)
+
+    w = types.SimpleNamespace()
+    w.embed = rnd(V, H)
+    w.lm_head = rnd(V, H, scale=H ** -0.5)
+    w.final_norm = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    for name in ("in_norm", "qkv", "q_norm", "k_norm", "o", "post_norm", "router", "host_w13", "host_w2"):
+        setattr(w, name, [])
+    for _ in range(L):
+        w.in_norm.append((1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16))
+        w.qkv.append(rnd((hq + 2 * hkv) * D, H, scale=H ** -0.5))
+        w.q_norm.append((1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16))
+        w.k_norm.append((1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16))
+        w.o.append(rnd(H, hq * D, scale=(hq * D) ** -0.5))
+        w.post_norm.append((1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16))
+        w.router.append(rnd(E, H, scale=H ** -0.5))
+        w.host_w13.append(rnd(E, 2 * I, H, scale=H ** -0.5))
+        w.host_w2.append(rnd(E, H, I, scale=I ** -0.5))
+    return w
+
+
+def qwen_fixture():
+    with reference_on_cpu():
+        ref = importlib.import_module("test_fabric_model")
+        cfg = ref.CFG   # hidden 512, intermediate 256, 16 experts top-4, 2 layers, 4/2 heads, vocab 1024
+        w = make_weights(cfg, seed=11)
+        g = torch.Generator().manual_seed(3)
+        tokens = torch.randint(0, cfg.vocab, (41,), generator=g).tolist()
+        logits = ref.reference_logits(w, cfg, tokens)
+    out = {"tokens": np.array(tokens, dtype=np.int32), "logits": logits.numpy().astype(np.float32),
+           "cfg": np.array([cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, cfg.num_layers,
+                            cfg.num_heads, cfg.num_kv_heads, cfg.vocab], dtype=np.int64),
+           "rope_theta": np.float64(cfg.rope_theta), "rms_eps": np.float64(cfg.rms_eps)}
+    # The weights are NOT stored (24 MB); tests rebuild them with make_weights(cfg, 11)
+    # and compare these CRC-32 values first, so a drift of torch's RNG stream is
+    # reported as such instead of as a parity failure.
+    crc = {}
+    for name in ("embed", "lm_head", "final_norm"):
+        crc[name] = zlib.crc32(bf16_bits(getattr(w, name)).tobytes())
+    for name in ("in_norm", "qkv", "q_norm", "k_norm", "o", "post_norm", "router", "host_w13", "host_w2"):
+        crc[name] = zlib.crc32(np.stack([bf16_bits(t) for t in getattr(w, name)]).tobytes())
+    out["crc_names"] = np.array(sorted(crc))
+    out["crc_values"] = np.array([crc[k] for k in sorted(crc)], dtype=np.uint32)
+    out["weights_seed"] = np.int64(11)
+    np.savez_compressed(os.path.join(HERE, "qwen_tiny_reference_logits.npz"), **out)
+    print("qwen fixture: logits", logits.shape, "max |logit|", float(logits.abs().max()))
+
+
+def helper_fixture():
+    """bf / rms / rope of the reference on seeded inputs (tests/test_fabric_model.py:26-42)."""
+    with reference_on_cpu():
+        ref = importlib.import_module("test_fabric_model")
+        g = torch.Generator().manual_seed(5)
+        x = torch.randn(7, 512, generator=g).to(torch.bfloat16).float()
+        wn = (1 + 0.1 * torch.randn(512, generator=g)).to(torch.bfloat16)
+        q = torch.randn(7, 4, 128, generator=g)
+        pos = torch.tensor([0, 1, 2, 3, 100, 1000, 4095])
+        out = {"x": x.numpy(), "norm_w": bf16_bits(wn), "rms": ref.rms(x, wn, 1e-6).numpy(),
+               "q": q.numpy(), "pos": pos.numpy(), "rope_full": ref.rope(q, pos, 1e6, 128).numpy(),
+               "rope_half": ref.rope(q, pos, 1e4, 64).numpy()}
+    np.savez_compressed(os.path.join(HERE, "helpers_reference.npz"), **out)
+    print("helper fixture written")
+
+
+if __name__ == "__main__":
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    qwen_fixture()
+    helper_fixture()
