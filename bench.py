@@ -191,6 +191,24 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_profile_target(args):
+    """A short, quiet run of the layer for `ncu` (one GPU)."""
+    from monoserve_b200.moe import MoELayer
+    H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
+    wl = make_workload()
+    layer = MoELayer(H, I, E, K, BATCH)
+    layer.set_router(wl["wr"].cuda())
+    layer.set_experts(wl["w13"], wl["w2"], list(range(E)) if args.all_hot else wl["hot"])
+    layer.set_plan(0, CREDITS, FORM)
+    out = torch.empty(BATCH, H, dtype=torch.bfloat16, device="cuda")
+    xs, x2s = [x.cuda() for x in wl["xs"]], [x.cuda() for x in wl["x2s"]]
+    for i in range(args.warmup + args.steps):
+        layer.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out)
+    torch.cuda.synchronize()
+    layer.status()
+    layer.close()
+
+
 def run_ours(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -343,12 +361,17 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ncu", action="store_true",
+                    help="profiling target: only W warm-up + K device-resident steps, no JSON line")
+    ap.add_argument("--all-hot", action="store_true", help="with --ncu: place all 128 experts in HBM")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.ncu:
+        run_profile_target(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
