@@ -69,6 +69,19 @@ int monofab_router_topk(float* logits, const float* bias, int32_t* topk_ids, flo
                         int32_t* chunk_counts, int32_t* pair_rank, int T, int E, int K, int scoring, int renorm,
                         float scale, int zero_logits, void* stream);
 
+/* Stable pack from given routing: per-expert counts, exclusive prefix sums
+ * (starts[0..E]) and the expert-sorted pair lists; with src/dst also the packed
+ * activation rows dst[pos] = src[token].  Inside an expert's segment the order is
+ * token ascending, then pick ascending.  The expander's prefix sum and the
+ * permute tile (csrc/fabric/tiles/aux.cuh:423-450, 648-684; PermuteArgs
+ * csrc/fabric/model_types.h:207-216).  `scratch` is device memory of at least
+ * monofab_pack_scratch_bytes(T, E, K) bytes that the call may overwrite. */
+size_t monofab_pack_scratch_bytes(int T, int E, int K);
+int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int E, int K, int H,
+                       const void* src_bf16, void* dst_bf16, int32_t* counts, int32_t* starts,
+                       int32_t* pair_token, float* pair_weight, int32_t* pair_pos, void* scratch,
+                       size_t scratch_bytes, void* stream);
+
 /* Un-permute + weighted combine (+ optional following RMSNorm): the AddNorm tile
  * together with the weighted-add GEMM epilogue (csrc/fabric/tiles/aux.cuh:137-188,
  * csrc/fabric/tiles/gemm.cuh:310-319).  y fp32 [P][H]; x2 / norm_w / normed may be NULL. */

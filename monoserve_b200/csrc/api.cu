@@ -349,6 +349,31 @@ int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w
   return MONOFAB_OK;
 }
 
+size_t monofab_pack_scratch_bytes(int T, int E, int K) {
+  if (T < 0 || E < 1 || K < 1) return 0;
+  return pack_scratch_bytes(T, E, K);
+}
+
+int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int E, int K, int H, const void* src,
+                       void* dst, int32_t* counts, int32_t* starts, int32_t* pair_token, float* pair_weight,
+                       int32_t* pair_pos, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!topk_ids || !topk_w || !counts || !starts || !pair_token || !pair_weight || !pair_pos)
+    return fail(MONOFAB_EINVAL, "pack_pairs: NULL argument");
+  if (E < 1 || E > kMaxExperts) return fail(MONOFAB_EINVAL, "pack_pairs: E=%d outside [1, %d]", E, kMaxExperts);
+  if (K < 1 || K > kMaxTopK) return fail(MONOFAB_EINVAL, "pack_pairs: K=%d outside [1, %d]", K, kMaxTopK);
+  if (T < 0) return fail(MONOFAB_EINVAL, "pack_pairs: negative T");
+  if ((src == nullptr) != (dst == nullptr)) return fail(MONOFAB_EINVAL, "pack_pairs: src and dst go together");
+  if (src && (H <= 0 || H % 8)) return fail(MONOFAB_EINVAL, "pack_pairs: H=%d must be a positive multiple of 8", H);
+  if (!scratch || scratch_bytes < pack_scratch_bytes(T, E, K))
+    return fail(MONOFAB_EINVAL, "pack_pairs: scratch of %zu bytes is smaller than the %zu needed", scratch_bytes,
+                pack_scratch_bytes(T, E, K));
+  if (reinterpret_cast<uintptr_t>(scratch) & 3) return fail(MONOFAB_EINVAL, "pack_pairs: scratch must be 4-byte aligned");
+  MF_CUDA(launch_pack_chain(topk_ids, topk_w, T, E, K, H, static_cast<const bf16*>(src), static_cast<bf16*>(dst),
+                            counts, starts, pair_token, pair_weight, pair_pos, scratch,
+                            static_cast<cudaStream_t>(stream)));
+  return MONOFAB_OK;
+}
+
 int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   if (!cfg || !out) return fail(MONOFAB_EINVAL, "moe_create: NULL argument");
   const monofab_moe_config& c = *cfg;

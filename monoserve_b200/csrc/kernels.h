@@ -68,9 +68,18 @@ struct CombineParams {
 cudaError_t launch_router_logits(const void* x, const void* wr, float* logits, int T, int H, int E,
                                  cudaStream_t stream);
 cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream);
+cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_counts, int T, int E, int K,
+                              cudaStream_t stream);
 cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream);
 cudaError_t launch_pack(const PackParams& A, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
 cudaError_t launch_expert_gemm(const GemmParams& p, int mode, int ctas, cudaStream_t stream);
+
+// The stable pack from given routing: ranks -> scan -> pair lists (and, when src
+// is set, the packed rows).  `scratch` holds pack_scratch_bytes(T, E, K) bytes.
+size_t pack_scratch_bytes(int T, int E, int K);
+cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, int E, int K, int H, const bf16* src,
+                              bf16* dst, int* counts, int* starts, int* pair_token, float* pair_weight,
+                              int* pair_pos, void* scratch, cudaStream_t stream);
 
 }  // namespace mf

@@ -206,6 +206,35 @@ __global__ void __launch_bounds__(1024) router_topk_kernel(const RouterParams A)
   }
 }
 
+// ------------------------------------------------------------- chunk ranks
+// The rank step of the stable pack on its own, for routing that was computed
+// elsewhere: one block per chunk of 32 tokens; thread p = (token, pick) counts
+// the earlier pairs of the chunk that chose the same expert, and the block
+// writes the chunk's per-expert pair counts.
+__global__ void __launch_bounds__(kChunkTokens * kMaxTopK) chunk_rank_kernel(const int* __restrict__ topk_ids,
+                                                                             int* __restrict__ pair_rank,
+                                                                             int* __restrict__ chunk_counts,
+                                                                             int T, int E, int K) {
+  __shared__ int s_ids[kChunkTokens * kMaxTopK];
+  __shared__ int s_hist[kMaxExperts];
+  const int rows = min(kChunkTokens, T - static_cast<int>(blockIdx.x) * kChunkTokens);
+  const int pairs = rows * K;
+  const int p = threadIdx.x;
+  const size_t base = static_cast<size_t>(blockIdx.x) * kChunkTokens * K;
+  if (p < kMaxExperts) s_hist[p] = 0;
+  if (p < pairs) s_ids[p] = topk_ids[base + p];
+  __syncthreads();
+  if (p < pairs) {
+    const int me = s_ids[p];
+    int rank = 0;
+    for (int q = 0; q < p; ++q) rank += s_ids[q] == me;
+    pair_rank[base + p] = rank;
+    atomicAdd(&s_hist[me], 1);
+  }
+  __syncthreads();
+  for (int e = p; e < E; e += blockDim.x) chunk_counts[static_cast<size_t>(blockIdx.x) * E + e] = s_hist[e];
+}
+
 // ---------------------------------------------------------------------- plan
 
 // Exclusive scan of one int per thread over a 256-thread block; returns the
@@ -252,6 +281,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   if (e < E) A.starts[e] = start;
   if (e == 0) A.starts[E] = total;
 
+  if (!A.q) return;   // scan only: counts, starts and chunk prefixes
   int tier = kTierHot, z = 0, bh = 128, nb = 0;
   if (e < E && cnt > 0) {
     tier = A.table[2 * e] == 0 ? kTierHost : kTierHot;
@@ -318,6 +348,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
     A.pair_weight[pos] = A.topk_w[static_cast<size_t>(t) * K + lane];
     A.pair_pos[static_cast<size_t>(t) * K + lane] = pos;
   }
+  if (!A.src) return;   // pair lists only
   const uint4* src = reinterpret_cast<const uint4*>(A.src + static_cast<size_t>(t) * A.H);
   const int n16 = A.H / 8;
   for (int c0 = 0; c0 < n16; c0 += 32 * 8) {
@@ -425,6 +456,14 @@ cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_counts, int T, int E, int K,
+                              cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  chunk_rank_kernel<<<(T + kChunkTokens - 1) / kChunkTokens, kChunkTokens * kMaxTopK, 0, stream>>>(
+      topk_ids, pair_rank, chunk_counts, T, E, K);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream) {
   plan_kernel<<<1, 256, 0, stream>>>(A);
   return cudaGetLastError();
@@ -434,6 +473,32 @@ cudaError_t launch_pack(const PackParams& A, cudaStream_t stream) {
   if (A.T == 0) return cudaSuccess;
   pack_kernel<<<(A.T + 7) / 8, 256, 0, stream>>>(A);
   return cudaGetLastError();
+}
+
+size_t pack_scratch_bytes(int T, int E, int K) {
+  const size_t chunks = (static_cast<size_t>(T) + kChunkTokens - 1) / kChunkTokens;
+  return chunks * E * sizeof(int) + static_cast<size_t>(T) * K * sizeof(int);
+}
+
+cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, int E, int K, int H, const bf16* src,
+                              bf16* dst, int* counts, int* starts, int* pair_token, float* pair_weight,
+                              int* pair_pos, void* scratch, cudaStream_t stream) {
+  const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
+  int* chunk_counts = static_cast<int*>(scratch);
+  int* pair_rank = chunk_counts + static_cast<size_t>(chunks) * E;
+  cudaError_t err = launch_chunk_rank(topk_ids, pair_rank, chunk_counts, T, E, K, stream);
+  if (err != cudaSuccess) return err;
+  PlanParams pp{};
+  pp.chunk_counts = chunk_counts;
+  pp.counts = counts;
+  pp.starts = starts;
+  pp.chunks = chunks;
+  pp.E = E;
+  err = launch_plan(pp, stream);
+  if (err != cudaSuccess) return err;
+  PackParams kp{topk_ids, topk_w, pair_rank, chunk_counts, starts, src, dst, pair_token, pair_weight, pair_pos,
+                T, E, K, H};
+  return launch_pack(kp, stream);
 }
 
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream) {

@@ -284,3 +284,71 @@ def test_qwen3_layer_config1_ragged_batch():
     out_p = m.forward(xn[perm].contiguous().cuda())
     assert torch.equal(out_p.cpu(), out.cpu()[perm])
     m.close()
+
+
+# ------------------------------------------------------ pack from given routing
+def random_routing(T, E, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32) if T else \
+        torch.zeros(0, K, dtype=torch.int32)
+    w = torch.rand(T, K, generator=g)
+    return ids, w
+
+
+def run_pack_pairs(fn_name, ids, w, E, x=None, with_scratch=True):
+    from monoserve_b200 import _C
+    T, K = ids.shape
+    P = T * K
+    d = dict(counts=torch.full((E,), -1, dtype=torch.int32, device="cuda"),
+             starts=torch.full((E + 1,), -1, dtype=torch.int32, device="cuda"),
+             pair_token=torch.full((max(P, 1),), -1, dtype=torch.int32, device="cuda"),
+             pair_weight=torch.zeros(max(P, 1), device="cuda"),
+             pair_pos=torch.full((max(P, 1),), -1, dtype=torch.int32, device="cuda"))
+    ids_d, w_d = ids.cuda(), w.cuda()
+    H = x.shape[1] if x is not None else 0
+    x_d = x.cuda() if x is not None else None
+    xp = torch.zeros(max(P, 1), H, dtype=torch.bfloat16, device="cuda") if x is not None else None
+    args = [ids_d.data_ptr(), w_d.data_ptr(), T, E, K, H, x_d.data_ptr() if x is not None else None,
+            xp.data_ptr() if x is not None else None, d["counts"].data_ptr(), d["starts"].data_ptr(),
+            d["pair_token"].data_ptr(), d["pair_weight"].data_ptr(), d["pair_pos"].data_ptr()]
+    if with_scratch:
+        nbytes = _C.lib.monofab_pack_scratch_bytes(T, E, K)
+        scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device="cuda")
+        args += [scratch.data_ptr(), nbytes]
+    _C.check(getattr(_C.lib, fn_name)(*args, None))
+    torch.cuda.synchronize()
+    d["xp"] = xp
+    return {k: (v.cpu() if v is not None else None) for k, v in d.items()}
+
+
+def check_pack_against_oracle(r, ids, w, E, x=None):
+    T, K = ids.shape
+    P = T * K
+    counts = np.bincount(ids.numpy().ravel(), minlength=E).astype(np.int32)
+    starts = oracle.scan(counts)
+    pt, pw, pp = oracle.pack(ids.numpy(), w.numpy(), starts)
+    assert np.array_equal(r["counts"].numpy(), counts)
+    assert np.array_equal(r["starts"].numpy(), starts)
+    assert np.array_equal(r["pair_token"].numpy()[:P], pt)
+    assert np.array_equal(r["pair_weight"].numpy()[:P].view(np.int32), pw.view(np.int32))
+    assert np.array_equal(r["pair_pos"].numpy()[:P], pp.ravel())
+    if x is not None and P:
+        assert np.array_equal(bits(r["xp"][:P]), oracle.permute_rows(bits(x), pt))
+
+
+@pytest.mark.parametrize("T,E,K,H", [(1, 8, 2, 0), (33, 16, 4, 256), (300, 128, 8, 512), (64, 256, 16, 0),
+                                     (0, 8, 2, 0), (1000, 24, 3, 64)])
+def test_pack_pairs_bit_exact(T, E, K, H):
+    ids, w = random_routing(T, E, K, seed=T + E)
+    x = torch.randn(T, H).to(torch.bfloat16) if H else None
+    r = run_pack_pairs("monofab_pack_pairs", ids, w, E, x)
+    check_pack_against_oracle(r, ids, w, E, x)
+
+
+def test_pack_pairs_rejects_small_scratch():
+    from monoserve_b200 import _C
+    ids, w = random_routing(40, 8, 2, 0)
+    z = torch.zeros(256, dtype=torch.int32, device="cuda")
+    rc = _C.lib.monofab_pack_pairs(ids.cuda().data_ptr(), w.cuda().data_ptr(), 40, 8, 2, 0, None, None, z.data_ptr(),
+                                   z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 16, None)
+    assert rc == -1 and b"scratch" in _C.lib.monofab_last_error()
