@@ -357,7 +357,7 @@ size_t monofab_pack_scratch_bytes(int T, int E, int K) {
 int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int E, int K, int H, const void* src,
                        void* dst, int32_t* counts, int32_t* starts, int32_t* pair_token, float* pair_weight,
                        int32_t* pair_pos, void* scratch, size_t scratch_bytes, void* stream) {
-  if (!topk_ids || !topk_w || !counts || !starts || !pair_token || !pair_weight || !pair_pos)
+  if (!counts || !starts || (T > 0 && (!topk_ids || !topk_w || !pair_token || !pair_weight || !pair_pos)))
     return fail(MONOFAB_EINVAL, "pack_pairs: NULL argument");
   if (E < 1 || E > kMaxExperts) return fail(MONOFAB_EINVAL, "pack_pairs: E=%d outside [1, %d]", E, kMaxExperts);
   if (K < 1 || K > kMaxTopK) return fail(MONOFAB_EINVAL, "pack_pairs: K=%d outside [1, %d]", K, kMaxTopK);
