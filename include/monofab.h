@@ -82,6 +82,22 @@ int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int 
                        int32_t* pair_token, float* pair_weight, int32_t* pair_pos, void* scratch,
                        size_t scratch_bytes, void* stream);
 
+/* The same pack with NO allocation anywhere: the scratch lives in a fixed array
+ * inside the library image (about 384 KB per GPU, held until the process exits)
+ * instead of being passed in.  It has no counterpart in the reference.  It is for
+ * callers that cannot allocate device memory when they need to pack - a process
+ * with a persistent kernel resident (cudaMalloc/cudaFree would wait for it), a
+ * component with a fixed memory budget and no allocator, a latency path that
+ * cannot afford an allocation's device-wide synchronisation.
+ * Limits: T <= MONOFAB_PACK_STATIC_MAX_TOKENS, else MONOFAB_EINVAL.  All calls on
+ * a device share the array: calls whose kernels overlap on the GPU race, so keep
+ * them on one stream.  The first call on each device looks up the array's
+ * address; make that call outside any stream capture. */
+#define MONOFAB_PACK_STATIC_MAX_TOKENS 4096
+int monofab_pack_pairs_static(const int32_t* topk_ids, const float* topk_w, int T, int E, int K, int H,
+                              const void* src_bf16, void* dst_bf16, int32_t* counts, int32_t* starts,
+                              int32_t* pair_token, float* pair_weight, int32_t* pair_pos, void* stream);
+
 /* Un-permute + weighted combine (+ optional following RMSNorm): the AddNorm tile
  * together with the weighted-add GEMM epilogue (csrc/fabric/tiles/aux.cuh:137-188,
  * csrc/fabric/tiles/gemm.cuh:310-319).  y fp32 [P][H]; x2 / norm_w / normed may be NULL. */
