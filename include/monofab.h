@@ -147,7 +147,8 @@ int monofab_moe_set_table(monofab_moe* m, const int32_t* table, void* stream);
 /* The part of a published plan this layer consumes (csrc/bindings.cpp:211-232
  * `Fabric.publish`): `ctas` = SMs given to the lane (0 = all), `credits` = link
  * slots (CTAs that may read host memory at once), `form` = row-block height of
- * host-resident experts, 16/32/64/128, or 0 for the weight-stationary form. */
+ * host-resident experts, 16/32/64/128, or 0 for the weight-stationary form (one
+ * pass over the weights for up to 256 rows of an expert). */
 int monofab_moe_set_plan(monofab_moe* m, int ctas, int credits, int form);
 
 /* One layer pass on device buffers: xn bf16 [T][H] (normalised input), x2 bf16
@@ -171,9 +172,10 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
 
 /* Per-kernel device times of the LAST forward, in milliseconds, measured with
  * CUDA events on the launching stream when profiling is on:
- * [0] router logits [1] router top-k [2] plan [3] pack [4] w13 [5] w2 [6] combine. */
+ * [0] router logits [1] router top-k [2] plan [3] pack [4] expert GEMMs (w13 + w2, one launch)
+ * [5] combine. */
 int monofab_moe_set_profile(monofab_moe* m, int on);
-int monofab_moe_last_times(monofab_moe* m, float ms[7]);
+int monofab_moe_last_times(monofab_moe* m, float ms[6]);
 
 #ifdef __cplusplus
 }

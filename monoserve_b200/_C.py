@@ -62,7 +62,7 @@ def _load():
     lib.monofab_moe_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.monofab_moe_workspace.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
     lib.monofab_moe_set_profile.argtypes = [vp, i32]
-    lib.monofab_moe_last_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float * 7)]
+    lib.monofab_moe_last_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float * 6)]
     return lib
 
 

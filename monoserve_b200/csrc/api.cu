@@ -78,7 +78,7 @@ int encode_map(CUtensorMap* map, int dtype, const void* base, int rank, const ui
   return MONOFAB_OK;
 }
 
-constexpr int kNumTimes = 7;
+constexpr int kNumTimes = 6;
 
 }  // namespace mf
 
@@ -116,14 +116,16 @@ struct monofab_moe {
   void* xin = nullptr;    // staging of the host-buffer entry point
   void* x2in = nullptr;
   void* xout = nullptr;
-  GemmTile* tiles[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};
+  GemmTile* tiles[2] = {nullptr, nullptr};
   GemmQueues* queues = nullptr;
+  int* done = nullptr;
+  int block_cap = 0;
   int* status = nullptr;
   int* status_host = nullptr;
   int tile_cap = 0;
   size_t pairs_cap = 0;
   bool maps_dirty = true;
-  GemmParams gp13{}, gp2{};
+  GemmParams gp{};
   bool profile = false;
   cudaEvent_t ev[kNumTimes + 1] = {};
   float times[kNumTimes] = {};
@@ -144,43 +146,45 @@ int build_maps(monofab_moe* m) {
   const monofab_moe_config& c = m->cfg;
   const int H = c.hidden, I = c.intermediate;
   const int esz = c.fp8 ? 1 : 2;
+  GemmParams& gp = m->gp;
+  std::memset(&gp, 0, sizeof gp);
   for (int phase = 0; phase < 2; ++phase) {
-    GemmParams& gp = phase == 0 ? m->gp13 : m->gp2;
-    std::memset(&gp, 0, sizeof gp);
+    GemmPhaseParams& ph = gp.ph[phase];
     const uint64_t K = phase == 0 ? H : I, rows = phase == 0 ? 2 * I : H;
     for (int region = 0; region < 2; ++region) {
       const void* base = phase == 0 ? m->w13[region] : m->w2[region];
       int slots = m->slots[region];
-      if (!base) {   // region unused: encode a valid map over the other region so prefetch is harmless
+      if (!base) {   // region unused: encode a valid map over the other region
         base = phase == 0 ? m->w13[1 - region] : m->w2[1 - region];
         slots = m->slots[1 - region];
       }
       if (!base) return fail(MONOFAB_EINVAL, "no expert weights set (monofab_moe_set_region)");
       const uint64_t dims[3] = {K, rows, static_cast<uint64_t>(slots)};
       const uint64_t strides[2] = {K * esz, rows * K * esz};
-      const uint32_t box[3] = {static_cast<uint32_t>(c.fp8 ? 128 : 64), 128, 1};
-      if (int r = encode_map(&gp.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, 128)) return r;
+      const uint32_t box[3] = {64, 16, 1};
+      if (int r = encode_map(&ph.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, c.fp8 ? 0 : 128)) return r;
     }
     const void* act = phase == 0 ? m->xp : m->h;
     for (int i = 0; i < kActBoxes; ++i) {
       const uint64_t dims[2] = {K, m->pairs_cap};
       const uint64_t strides[1] = {K * 2};
       const uint32_t box[2] = {64, static_cast<uint32_t>(16 << i)};
-      if (int r = encode_map(&gp.act_map[i], 0, act, 2, dims, strides, box, 128)) return r;
+      if (int r = encode_map(&ph.act_map[i], 0, act, 2, dims, strides, box, 128)) return r;
     }
-    gp.tiles[0] = m->tiles[phase][0];
-    gp.tiles[1] = m->tiles[phase][1];
-    gp.q = m->queues;
-    gp.scale = phase == 0 ? m->s13 : m->s2;
-    gp.out = phase == 0 ? m->h : static_cast<void*>(m->y);
-    gp.status = m->status;
-    gp.phase = phase;
-    gp.k_tiles = static_cast<int>(K / 64);
-    gp.up_offset = I;
-    gp.n_limit = phase == 0 ? I : H;
-    gp.ld_out = phase == 0 ? I : H;
-    gp.scale_ld = phase == 0 ? 2 * I : H;
+    ph.scale = phase == 0 ? m->s13 : m->s2;
+    ph.out = phase == 0 ? m->h : static_cast<void*>(m->y);
+    ph.k_tiles = static_cast<int>(K / 64);
+    ph.up_offset = I;
+    ph.n_limit = phase == 0 ? I : H;
+    ph.ld_out = phase == 0 ? I : H;
+    ph.scale_ld = phase == 0 ? 2 * I : H;
+    ph.epi = phase == 0 ? 1 : 2;   // kEpiSiluMul / kEpiRowsF32
   }
+  gp.tiles[0] = m->tiles[0];
+  gp.tiles[1] = m->tiles[1];
+  gp.q = m->queues;
+  gp.done = m->done;
+  gp.status = m->status;
   m->maps_dirty = false;
   return MONOFAB_OK;
 }
@@ -214,8 +218,10 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
   pp.starts = m->starts;
   pp.table = m->table;
   pp.hist = m->hist;
-  for (int ph = 0; ph < 2; ++ph)
-    for (int q = 0; q < 2; ++q) pp.tiles[ph][q] = m->tiles[ph][q];
+  pp.tiles[0] = m->tiles[0];
+  pp.tiles[1] = m->tiles[1];
+  pp.done = m->done;
+  pp.block_cap = m->block_cap;
   pp.q = m->queues;
   pp.status = m->status;
   pp.chunks = chunks;
@@ -231,11 +237,8 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
                 m->pair_weight, m->pair_pos, T, E, K, H};
   MF_CUDA(launch_pack(kp, st));
   MF_CUDA(mark());
-  m->gp13.cap = m->credits;
-  m->gp2.cap = m->credits;
-  MF_CUDA(launch_expert_gemm(m->gp13, kGemmModeW13, ctas, st));
-  MF_CUDA(mark());
-  MF_CUDA(launch_expert_gemm(m->gp2, kGemmModeW2, ctas, st));
+  m->gp.cap = m->credits;
+  MF_CUDA(launch_expert_gemm(m->gp, ctas, st));
   MF_CUDA(mark());
   CombineParams cp{m->y, m->pair_pos, m->topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(out),
                    nullptr, nullptr, T, K, H, 0.f};
@@ -393,12 +396,13 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   m->num_sms = prop.multiProcessorCount;
   const size_t T = c.max_tokens, H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;
   const size_t P = T * K, chunks = (T + kChunkTokens - 1) / kChunkTokens;
-  // Packed rows are addressed by TMA boxes of up to 128 rows; pad so a box that
+  // Packed rows are addressed by TMA boxes of up to 256 rows; pad so a box that
   // starts at the last row stays inside the allocation.
-  m->pairs_cap = P + 128;
-  // Row blocks: at most P/16 + E blocks of >= 16 rows (form 16) in the worst case.
+  m->pairs_cap = P + 256;
+  // Row blocks: at most P/16 + E blocks (form 16, every expert with a ragged tail).
   const size_t blocks_max = P / 16 + E;
-  m->tile_cap = static_cast<int>(blocks_max * std::max((I + 127) / 128, (H + 127) / 128));
+  m->block_cap = static_cast<int>(blocks_max);
+  m->tile_cap = static_cast<int>(blocks_max * ((I + 63) / 64 + (H + 127) / 128));
   int r = 0;
   auto A = [&](auto** p, size_t bytes) { if (!r) r = dev_alloc(m, reinterpret_cast<void**>(p), bytes); };
   A(&m->logits, T * E * 4);
@@ -419,9 +423,9 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   A(&m->xin, T * H * 2);
   A(&m->x2in, T * H * 2);
   A(&m->xout, T * H * 2);
-  for (int ph = 0; ph < 2; ++ph)
-    for (int q = 0; q < 2; ++q) A(&m->tiles[ph][q], static_cast<size_t>(m->tile_cap) * sizeof(GemmTile));
+  for (int q = 0; q < 2; ++q) A(&m->tiles[q], static_cast<size_t>(m->tile_cap) * sizeof(GemmTile));
   A(&m->queues, sizeof(GemmQueues));
+  A(&m->done, static_cast<size_t>(m->block_cap) * 4);
   A(&m->status, 4);
   if (!r && cudaHostAlloc(reinterpret_cast<void**>(&m->status_host), 64, cudaHostAllocDefault) != cudaSuccess)
     r = fail(MONOFAB_ECUDA, "cudaHostAlloc of the status mirror failed");
@@ -594,7 +598,7 @@ int monofab_moe_set_profile(monofab_moe* m, int on) {
   return MONOFAB_OK;
 }
 
-int monofab_moe_last_times(monofab_moe* m, float ms[7]) {
+int monofab_moe_last_times(monofab_moe* m, float ms[6]) {
   if (!m || !ms) return fail(MONOFAB_EINVAL, "last_times: NULL argument");
   std::lock_guard<std::mutex> lock(m->mu);
   if (!m->times_valid) return fail(MONOFAB_EINVAL, "last_times: no profiled forward to report (monofab_moe_set_profile)");

@@ -1,63 +1,43 @@
-// Grouped SwiGLU expert GEMM for sm_100a: tcgen05.mma with TMEM accumulators,
-// operands staged by TMA, one persistent CTA per SM.
+// Grouped SwiGLU expert GEMM of one MoE layer as ONE persistent launch
+// (1 CTA per SM) on the tile functions of gemm_core.cuh.
 //
-// Operand roles follow the reference's GEMM tile (csrc/fabric/tiles/gemm.cuh:1-18,
-// 133-346): the WEIGHT slice is the MMA's M operand (128 output features) and
-// the expert's packed ACTIVATION rows are the N operand (16..128 tokens), so a
-// decode batch of a few tokens per expert still fills a full-height MMA.  Both
-// operands are K-major with the 128-byte swizzle; one K step is 64 elements.
-//
-// Two modes (csrc/fabric/model_types.h:29-35 epilogues kEpiSiluMul / kEpiWeightedAdd):
-//   w13: two accumulators per tile, gate rows [f, f+128) and up rows
-//        [I+f, I+f+128) of the same expert, sharing the activation operand;
-//        epilogue h[m][f] = bf16(silu(g) * u).
-//   w2 : one accumulator; the epilogue stores the fp32 rows y[m][n] of every
-//        routed pair.  The weighted un-permute happens in the combine kernel in
-//        pick order, which makes the layer output deterministic (the reference
-//        adds with atomics in arrival order).
+// Work comes from two queues the plan kernel filled, one per weight tier (host
+// link / HBM); each holds the layer's w13 tiles followed by its w2 tiles.
+//   w13 tile: 64 gate + 64 up rows of one expert x one row block, epilogue
+//             h = bf16(silu(g) * u)                       (kEpiSiluMul)
+//   w2 tile : 128 output rows x the same row block over h, epilogue stores the
+//             fp32 rows y[pos][n] of every routed pair     (kEpiRowsF32)
+// A w2 tile may start only when every w13 tile of its row block has stored h:
+// the epilogue warps of w13 tiles count into done[block] (release), and the
+// producer of a w2 tile waits (bounded) for the count before it issues the first
+// load of h.  Tiles are claimed in queue order, so whatever a waiting CTA waits
+// for has already been claimed by a CTA that is running: no deadlock.
 //
 // Warp roles (192 threads): warp 0 = tile claim + TMA producer, warp 1 = TMEM
-// owner + MMA issue, warps 2..5 = epilogue (TMEM lane quadrant = warp % 4).
-// Accumulators are double-buffered in TMEM, so the epilogue of tile i overlaps
-// the loads and MMAs of tile i+1.
+// owner + MMA issue, warps 2..5 = epilogue.  Accumulators are double-buffered in
+// TMEM so the epilogue of tile i overlaps the loads and MMAs of tile i+1, across
+// tile and phase boundaries.
 //
-// Link credits (csrc/fabric/runtime.cuh:415-423,451-485): tiles whose weights
-// are in pinned host memory sit in a separate queue and are taken only by a
-// CTA that holds one of `cap` slots; the other CTAs work on HBM tiles.
+// Link credits (csrc/fabric/runtime.cuh:415-423,451-485): a CTA takes link
+// tiles only while it holds one of `cap` slots; others work on the HBM queue and
+// leave when it is drained.
 //
-// Every wait is bounded: when one runs out the CTA raises kErrWaitTimeout in
-// the status word and leaves through the common exit, freeing its TMEM.
+// Every wait is bounded; on a timeout the CTA raises kErrWaitTimeout in the
+// status word and leaves through the common exit, freeing its TMEM.
 #include <cuda_bf16.h>
 
+#include "gemm_core.cuh"
 #include "kernels.h"
-#include "ptx.cuh"
 
 namespace mf {
 
 constexpr int kGemmThreads = 192;
-constexpr int kBlockK = 64;                       // elements per K step (128 bytes of bf16)
-constexpr int kSliceBytes = 128 * kBlockK * 2;    // one 128-row operand tile: 16 KB
-constexpr int kMaxN = 128;
-constexpr int kTmemCols = 512;
-constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s
-
-template <int MODE>
-struct GemmCfg {
-  static constexpr int kABytes = MODE == kGemmModeW13 ? 2 * kSliceBytes : kSliceBytes;
-  static constexpr int kBBytes = kMaxN * kBlockK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = MODE == kGemmModeW13 ? 4 : 6;
-  static constexpr int kAccCols = MODE == kGemmModeW13 ? 256 : 128;   // TMEM columns per buffer
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
-};
 
 struct GemmShared {
-  uint64_t full[8];
-  uint64_t empty[8];
+  GemmBarriers bar;
   uint64_t tile_ready[2];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
-  GemmTile tile[2];
+  GemmWork work[2];
+  int block[2];        // row block of the tile in the slot (w13: to count; -1 otherwise)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -72,11 +52,7 @@ __device__ __forceinline__ bool try_acquire_slot(int* slots, int cap) {
   return false;
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
-
-template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = GemmCfg<MODE>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ GemmShared sh;
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -85,15 +61,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
   volatile int* abort_flag = &sh.abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::kStages; ++i) {
-      mbar_init(&sh.full[i], 1);
-      mbar_init(&sh.empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh.tile_ready[i], 1);
-      mbar_init(&sh.acc_full[i], 1);
-      mbar_init(&sh.acc_empty[i], 4);
-    }
+    gemm_barriers_init(sh.bar);
+    mbar_init(&sh.tile_ready[0], 1);
+    mbar_init(&sh.tile_ready[1], 1);
     sh.abort_flag = 0;
     fence_barrier_init();
   }
@@ -105,71 +75,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh.tmem_base;
-  const int k_tiles = p.k_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------ claim + TMA producer
     if (lane == 0) {
-      prefetch_tensormap(&p.w_map[0]);
-      prefetch_tensormap(&p.w_map[1]);
       GemmQueues* q = p.q;
-      const int n_link = q->n_tiles[p.phase][0], n_hbm = q->n_tiles[p.phase][1];
+      const int n_link = q->n_tiles[0], n_hbm = q->n_tiles[1], need = q->need;
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       bool have_slot = false, link_left = n_link > 0, hbm_left = n_hbm > 0;
-      int stage = 0;
-      uint32_t phase = 0;
+      GemmPipe pipe;
       for (int it = 0;; ++it) {
         const int buf = it & 1;
-        if (!mbar_wait_bounded(&sh.acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, kWaitBudgetNs)) break;
+        if (!mbar_wait_bounded(&sh.bar.acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, kWaitBudgetNs)) break;
         const GemmTile* t = nullptr;
         if (link_left) {
-          if (!have_slot) have_slot = try_acquire_slot(&q->slots[p.phase], p.cap);
+          if (!have_slot) have_slot = try_acquire_slot(&q->slots, p.cap);
           if (have_slot) {
-            const int i = atomicAdd(&q->head[p.phase][0], 1);
+            const int i = atomicAdd(&q->head[0], 1);
             if (i < n_link) {
               t = p.tiles[0] + i;
             } else {
               link_left = false;
-              atomicSub(&q->slots[p.phase], 1);
+              atomicSub(&q->slots, 1);
               have_slot = false;
             }
           }
         }
         if (!t && hbm_left) {
-          const int i = atomicAdd(&q->head[p.phase][1], 1);
+          const int i = atomicAdd(&q->head[1], 1);
           if (i < n_hbm) t = p.tiles[1] + i; else hbm_left = false;
         }
+        GemmWork& w = sh.work[buf];
         if (!t) {
-          // Nothing this CTA may take: either both queues are drained, or the
-          // remaining link tiles belong to the CTAs that hold the slots.
-          sh.tile[buf].n = -1;
+          // Nothing this CTA may take: both queues are drained, or the remaining
+          // link tiles belong to the CTAs that hold the slots.
+          w.valid = 0;
           mbar_arrive(&sh.tile_ready[buf]);
           break;
         }
         const GemmTile tile = *t;
-        sh.tile[buf] = tile;
-        mbar_arrive(&sh.tile_ready[buf]);
+        const GemmPhaseParams& ph = p.ph[tile.phase];
         int box = 0;
         while ((16 << box) < tile.n) ++box;
-        const CUtensorMap* wmap = &p.w_map[tile.tier];
-        const CUtensorMap* xmap = &p.act_map[box];
-        const uint32_t bytes = Cfg::kABytes + tile.n * kBlockK * 2;
-        bool ok = true;
-        for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!mbar_wait_bounded(&sh.empty[stage], phase ^ 1, abort_flag, kWaitBudgetNs)) { ok = false; break; }
-          uint8_t* a = stages + stage * Cfg::kStageBytes;
-          uint8_t* b = a + Cfg::kABytes;
-          mbar_arrive_expect_tx(&sh.full[stage], bytes);
-          tma_load_3d(a, wmap, &sh.full[stage], kt * kBlockK, tile.w_row0, tile.z, pol_w);
-          if (MODE == kGemmModeW13)
-            tma_load_3d(a + kSliceBytes, wmap, &sh.full[stage], kt * kBlockK, p.up_offset + tile.w_row0,
-                        tile.z, pol_w);
-          tma_load_2d(b, xmap, &sh.full[stage], kt * kBlockK, tile.act_row0, pol_x);
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        w.a_map = &ph.w_map[tile.tier];
+        w.b_map = &ph.act_map[box];
+        w.out = ph.out;
+        w.scale = nullptr;
+        w.bias = nullptr;
+        w.residual = nullptr;
+        w.a_row_lo = tile.w_row0;
+        w.a_row_hi = ph.up_offset + tile.w_row0;
+        w.a_z = tile.z;
+        w.b_row0 = tile.act_row0;
+        w.rows = tile.rows;
+        w.n = tile.n;
+        w.k0 = 0;
+        w.k_tiles = ph.k_tiles;
+        w.epi = ph.epi;
+        w.ld_out = ph.ld_out;
+        w.ld_res = 0;
+        w.n_limit = ph.n_limit;
+        w.valid = 1;
+        sh.block[buf] = tile.phase == 0 ? tile.block : -1;
+        mbar_arrive(&sh.tile_ready[buf]);
+        if (tile.phase == 1) {
+          // h of this row block must be complete before TMA reads it
+          const int* flag = p.done + tile.block;
+          if (ld_acquire_gpu(reinterpret_cast<const uint32_t*>(flag)) < static_cast<uint32_t>(need)) {
+            const unsigned long long t0 = globaltimer_ns();
+            bool ok = true;
+            while (ld_acquire_gpu(reinterpret_cast<const uint32_t*>(flag)) < static_cast<uint32_t>(need)) {
+              __nanosleep(64);
+              if (*abort_flag || globaltimer_ns() - t0 > kWaitBudgetNs) {
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+          }
+          fence_proxy_async_all();
         }
-        if (!ok) break;
+        if (!gemm_produce(w, stages, sh.bar, pipe, abort_flag, pol_w, pol_x)) break;
       }
-      if (have_slot) atomicSub(&q->slots[p.phase], 1);
+      if (have_slot) atomicSub(&q->slots, 1);
       if (*abort_flag) {
         // Let copies that are still in flight land before the block retires.
         const unsigned long long t0 = globaltimer_ns();
@@ -178,108 +167,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issue
-    int stage = 0;
-    uint32_t phase = 0;
+    GemmPipe pipe;
     for (int it = 0;; ++it) {
       const int buf = it & 1;
-      const uint32_t use_parity = (it >> 1) & 1;
-      if (!mbar_wait_bounded(&sh.tile_ready[buf], use_parity, abort_flag, kWaitBudgetNs)) break;
-      const int n = sh.tile[buf].n;
-      if (n < 0) break;
-      if (!mbar_wait_bounded(&sh.acc_empty[buf], use_parity ^ 1, abort_flag, kWaitBudgetNs)) break;
-      tc_fence_after_sync();
-      const uint32_t idesc = umma_idesc_bf16(128, n);
-      const uint32_t acc = tmem_base + buf * Cfg::kAccCols;
-      bool ok = true;
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        if (!mbar_wait_bounded(&sh.full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (lane == 0) {
-          const uint32_t a = smem_u32(stages + stage * Cfg::kStageBytes);
-          const uint32_t b = a + Cfg::kABytes;
-          const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(b);
-          const uint64_t du = umma_desc_sw128(a + kSliceBytes);
-#pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            const uint32_t accum = (kt | k) != 0;
-            umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, accum);
-            if (MODE == kGemmModeW13) umma_bf16(acc + kMaxN, du + 2 * k, db + 2 * k, idesc, accum);
-          }
-          umma_commit(&sh.empty[stage]);
-        }
-        __syncwarp();
-        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
-      }
-      if (!ok) break;
-      if (lane == 0) umma_commit(&sh.acc_full[buf]);
-      __syncwarp();
+      const uint32_t parity = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&sh.tile_ready[buf], parity, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[buf].valid) break;
+      if (!gemm_mma(sh.work[buf], stages, sh.bar, pipe, tmem_base, buf, parity, abort_flag)) break;
     }
   } else {
     // -------------------------------------------------------------- epilogue
-    const int quad = warp & 3;
     for (int it = 0;; ++it) {
       const int buf = it & 1;
-      const uint32_t use_parity = (it >> 1) & 1;
-      if (!mbar_wait_bounded(&sh.tile_ready[buf], use_parity, abort_flag, kWaitBudgetNs)) break;
-      const GemmTile tile = sh.tile[buf];
-      if (tile.n < 0) break;
-      if (!mbar_wait_bounded(&sh.acc_full[buf], use_parity, abort_flag, kWaitBudgetNs)) break;
-      tc_fence_after_sync();
-      const int f = tile.w_row0 + quad * 32 + lane;   // output feature of this thread
-      const bool f_ok = f < p.n_limit;
-      const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols;
-      float sg = 1.f, su = 1.f;
-      if (p.scale) {
-        const float* sc = p.scale + static_cast<size_t>(tile.expert) * p.scale_ld;
-        if (f_ok) {
-          sg = sc[f];
-          if (MODE == kGemmModeW13) su = sc[p.up_offset + f];
+      const uint32_t parity = (it >> 1) & 1;
+      if (!mbar_wait_bounded(&sh.tile_ready[buf], parity, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[buf].valid) break;
+      const int block = sh.block[buf];
+      const GemmWork w = sh.work[buf];
+      // the slot is released by acc_empty inside gemm_epilogue; publish h first
+      if (block >= 0) {
+        // run the epilogue body, then count this warp's part of the row block
+        if (!gemm_epilogue_body(w, sh.bar, tmem_base, buf, parity, abort_flag)) break;
+        __threadfence();
+        fence_proxy_async_all();
+        __syncwarp();
+        if (lane == 0) {
+          atomicAdd(p.done + block, 1);
+          mbar_arrive(&sh.bar.acc_empty[buf]);
         }
+      } else {
+        if (!gemm_epilogue(w, sh.bar, tmem_base, buf, parity, abort_flag)) break;
       }
-      for (int c0 = 0; c0 < tile.n; c0 += 32) {
-        uint32_t g[32], u[32];
-        if (tile.n - c0 >= 32) {
-          tmem_ld_32x32(tacc + c0, g);
-          if (MODE == kGemmModeW13) tmem_ld_32x32(tacc + kMaxN + c0, u);
-        } else {
-          uint32_t g16[16], u16[16];
-          tmem_ld_32x16(tacc + c0, g16);
-          if (MODE == kGemmModeW13) tmem_ld_32x16(tacc + kMaxN + c0, u16);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            g[j] = g16[j];
-            if (MODE == kGemmModeW13) u[j] = u16[j];
-            g[16 + j] = 0;
-            u[16 + j] = 0;
-          }
-        }
-        tmem_ld_wait();
-        const int m_hi = min(32, tile.rows - c0);
-        if (MODE == kGemmModeW13) {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) +
-                               static_cast<size_t>(tile.act_row0 + c0) * p.ld_out + f;
-          if (f_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < m_hi) {
-                const float h = silu_mul(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su);
-                out[static_cast<size_t>(j) * p.ld_out] = __float2bfloat16(h);
-              }
-            }
-          }
-        } else {
-          float* out = reinterpret_cast<float*>(p.out) + static_cast<size_t>(tile.act_row0 + c0) * p.ld_out + f;
-          if (f_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < m_hi) out[static_cast<size_t>(j) * p.ld_out] = __uint_as_float(g[j]) * sg;
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.acc_empty[buf]);
     }
   }
 
@@ -293,27 +211,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
   }
 }
 
-cudaError_t launch_expert_gemm(const GemmParams& p, int mode, int ctas, cudaStream_t stream) {
-  cudaError_t err;
-  if (mode == kGemmModeW13) {
-    static bool attr13 = false;
-    if (!attr13) {
-      err = cudaFuncSetAttribute(expert_gemm_kernel<kGemmModeW13>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 GemmCfg<kGemmModeW13>::kSmemBytes);
-      if (err != cudaSuccess) return err;
-      attr13 = true;
-    }
-    expert_gemm_kernel<kGemmModeW13><<<ctas, kGemmThreads, GemmCfg<kGemmModeW13>::kSmemBytes, stream>>>(p);
-  } else {
-    static bool attr2 = false;
-    if (!attr2) {
-      err = cudaFuncSetAttribute(expert_gemm_kernel<kGemmModeW2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 GemmCfg<kGemmModeW2>::kSmemBytes);
-      if (err != cudaSuccess) return err;
-      attr2 = true;
-    }
-    expert_gemm_kernel<kGemmModeW2><<<ctas, kGemmThreads, GemmCfg<kGemmModeW2>::kSmemBytes, stream>>>(p);
+cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream) {
+  static bool attr = false;
+  if (!attr) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(expert_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (err != cudaSuccess) return err;
+    attr = true;
   }
+  expert_gemm_kernel<<<ctas, kGemmThreads, kGemmSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,236 @@
+// The weight x activation GEMM tile on tcgen05 / TMEM / TMA, as three warp-role
+// device functions shared by the stand-alone grouped expert GEMM kernel and by
+// the persistent fabric worker.
+//
+// One tile (the reference's GEMM tile, csrc/fabric/tiles/gemm.cuh:1-18,133-346,
+// csrc/fabric/model_types.h:37-49): 128 weight rows (output features) as the MMA
+// M operand times up to 256 activation rows as the N operand, over a range of
+// 64-element K steps; fp32 accumulation in TMEM.  Both operands are K-major with
+// the 128-byte swizzle.  The weight slice is fetched as eight TMA boxes of 16
+// rows, which lets a SwiGLU tile interleave 64 gate rows and 64 up rows in groups
+// of 16: TMEM lane 32q+i (i < 16) then holds gate feature 16q+i and lane 32q+16+i
+// the matching up feature, so the epilogue pairs them with a warp shuffle instead
+// of a trip through shared memory.
+//
+// Roles: produce() runs in ONE thread (TMA issue), mma() in one warp (one lane
+// issues tcgen05.mma / tcgen05.commit), epilogue() in the four warps whose
+// warp index modulo 4 covers the four TMEM lane quadrants.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "types.h"
+
+namespace mf {
+
+constexpr int kBlockK = 64;                      // elements per K step (128 bytes of bf16)
+constexpr int kATileBytes = 128 * kBlockK * 2;   // 16 KB
+constexpr int kGemmMaxN = 256;
+constexpr int kBTileBytes = kGemmMaxN * kBlockK * 2;   // 32 KB
+constexpr int kStageBytes = kATileBytes + kBTileBytes; // 48 KB
+constexpr int kGemmStages = 4;
+constexpr int kGemmSmemBytes = kGemmStages * kStageBytes + 1024;
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = 256;                    // TMEM columns per accumulator buffer (two buffers)
+constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s of device time per wait
+
+// Epilogues (csrc/fabric/model_types.h:29-35).
+constexpr int kEpiStoreBf16 = 0;   // out[m][n] = bf16(acc (+ bias[n]) (+ residual[m][n]))
+constexpr int kEpiSiluMul = 1;     // 64 gate + 64 up rows: out[m][f] = bf16(silu(g) * u)
+constexpr int kEpiRowsF32 = 2;     // out32[m][n] = acc : per-pair rows for the deterministic combine
+constexpr int kEpiStoreF32 = 3;    // out32[m][n] = acc (+ bias[n])
+constexpr int kEpiAtomicF32 = 4;   // out32[m][n] += acc : K-split partial sums
+
+// Everything the three roles need to know about one tile; lives in shared memory.
+struct GemmWork {
+  const CUtensorMap* a_map;   // weights: dims (K, rows, Z), box (64, 16, 1)
+  const CUtensorMap* b_map;   // activations: dims (K, rows), box (64, n)
+  void* out;
+  const float* scale;         // fp32 per weight row (FP8 weights), or null
+  const __nv_bfloat16* bias;      // per output feature, or null
+  const __nv_bfloat16* residual;  // [rows][ld_res], or null
+  int32_t a_row_lo;           // first weight row
+  int32_t a_row_hi;           // kEpiSiluMul: first up row; otherwise ignored
+  int32_t a_z;
+  int32_t b_row0;             // first activation row
+  int32_t rows;               // valid activation rows (<= n)
+  int32_t n;                  // MMA N: 16, 32, 64, 128 or 256
+  int32_t k0, k_tiles;        // K steps [k0, k0 + k_tiles)
+  int32_t epi;
+  int32_t ld_out, ld_res;
+  int32_t n_limit;            // valid output features
+  int32_t valid;              // 0: no tile (the consumer roles stop or skip)
+  int32_t pad[3];
+};
+
+struct GemmPipe {   // per-role cursor over the shared-memory stages
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance() {
+    if (++stage == kGemmStages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+};
+
+struct GemmBarriers {
+  uint64_t full[kGemmStages];
+  uint64_t empty[kGemmStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+};
+
+__device__ __forceinline__ void gemm_barriers_init(GemmBarriers& b) {
+  for (int i = 0; i < kGemmStages; ++i) {
+    mbar_init(&b.full[i], 1);
+    mbar_init(&b.empty[i], 1);
+  }
+  for (int i = 0; i < 2; ++i) {
+    mbar_init(&b.acc_full[i], 1);
+    mbar_init(&b.acc_empty[i], 4);
+  }
+}
+
+// TMA issue for one tile (one thread).  Returns false when a wait was abandoned.
+__device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* stages, GemmBarriers& bar, GemmPipe& pipe,
+                                             volatile int* abort_flag, uint64_t pol_w, uint64_t pol_x) {
+  const uint32_t bytes = kATileBytes + w.n * kBlockK * 2;
+  const bool interleave = w.epi == kEpiSiluMul;
+  for (int kt = 0; kt < w.k_tiles; ++kt) {
+    if (!mbar_wait_bounded(&bar.empty[pipe.stage], pipe.phase ^ 1, abort_flag, kWaitBudgetNs)) return false;
+    uint8_t* a = stages + pipe.stage * kStageBytes;
+    uint8_t* b = a + kATileBytes;
+    uint64_t* full = &bar.full[pipe.stage];
+    mbar_arrive_expect_tx(full, bytes);
+    const int x = (w.k0 + kt) * kBlockK;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int row = interleave ? ((j & 1) ? w.a_row_hi : w.a_row_lo) + 16 * (j >> 1) : w.a_row_lo + 16 * j;
+      tma_load_3d(a + j * 2048, w.a_map, full, x, row, w.a_z, pol_w);
+    }
+    tma_load_2d(b, w.b_map, full, x, w.b_row0, pol_x);
+    pipe.advance();
+  }
+  return true;
+}
+
+// MMA issue for one tile into accumulator buffer `buf` (whole warp calls; lane 0 issues).
+__device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* stages, GemmBarriers& bar, GemmPipe& pipe,
+                                         uint32_t tmem_base, int buf, uint32_t acc_parity, volatile int* abort_flag) {
+  const int lane = threadIdx.x & 31;
+  if (!mbar_wait_bounded(&bar.acc_empty[buf], acc_parity ^ 1, abort_flag, kWaitBudgetNs)) return false;
+  tc_fence_after_sync();
+  const uint32_t idesc = umma_idesc_bf16(128, w.n);
+  const uint32_t acc = tmem_base + buf * kAccCols;
+  for (int kt = 0; kt < w.k_tiles; ++kt) {
+    if (!mbar_wait_bounded(&bar.full[pipe.stage], pipe.phase, abort_flag, kWaitBudgetNs)) return false;
+    tc_fence_after_sync();
+    if (lane == 0) {
+      const uint32_t a = smem_u32(stages + pipe.stage * kStageBytes);
+      const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(a + kATileBytes);
+#pragma unroll
+      for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+      umma_commit(&bar.empty[pipe.stage]);
+    }
+    __syncwarp();
+    pipe.advance();
+  }
+  if (lane == 0) umma_commit(&bar.acc_full[buf]);
+  __syncwarp();
+  return true;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+
+// Epilogue of one tile from accumulator buffer `buf` (the four epilogue warps
+// call): everything except handing the buffer back to the MMA warp.
+__device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
+                                                   uint32_t acc_parity, volatile int* abort_flag) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = warp & 3;
+  if (!mbar_wait_bounded(&bar.acc_full[buf], acc_parity, abort_flag, kWaitBudgetNs)) return false;
+  tc_fence_after_sync();
+  const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kAccCols;
+  const bool silu = w.epi == kEpiSiluMul;
+  // output feature of this lane, and the weight row its accumulator row came from
+  int f, wrow;
+  if (silu) {
+    f = w.a_row_lo + 16 * quad + (lane & 15);
+    wrow = (lane < 16 ? w.a_row_lo : w.a_row_hi) + 16 * quad + (lane & 15);
+  } else {
+    f = w.a_row_lo + 32 * quad + lane;
+    wrow = f;
+  }
+  const bool f_ok = f < w.n_limit;
+  const float sc = (w.scale && f_ok) ? w.scale[wrow] : 1.f;
+  const float bias = (w.bias && f_ok && w.k0 == 0) ? __bfloat162float(w.bias[f]) : 0.f;
+  for (int c0 = 0; c0 < w.n; c0 += 32) {
+    uint32_t r[32];
+    if (w.n - c0 >= 32) {
+      tmem_ld_32x32(tacc + c0, r);
+    } else {
+      uint32_t r16[16];
+      tmem_ld_32x16(tacc + c0, r16);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        r[j] = r16[j];
+        r[16 + j] = 0;
+      }
+    }
+    tmem_ld_wait();
+    if (c0 >= w.rows) continue;
+    if (silu) {
+      // lanes < 16 own gate rows, lanes >= 16 the matching up rows; exchange halves
+      const bool lo = lane < 16;
+      const int t0 = c0 + (lo ? 0 : 16);
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(w.out) + static_cast<size_t>(w.b_row0 + t0) * w.ld_out + f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float mine_keep = __uint_as_float(lo ? r[j] : r[16 + j]) * sc;
+        const float send = __uint_as_float(lo ? r[16 + j] : r[j]) * sc;
+        const float other = __shfl_xor_sync(0xffffffffu, send, 16);
+        const float g = lo ? mine_keep : other, u = lo ? other : mine_keep;
+        if (f_ok && t0 + j < w.rows) out[static_cast<size_t>(j) * w.ld_out] = __float2bfloat16(silu_mul(g, u));
+      }
+    } else if (w.epi == kEpiStoreBf16) {
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
+      const __nv_bfloat16* res =
+          w.residual ? w.residual + static_cast<size_t>(w.b_row0 + c0) * w.ld_res + f : nullptr;
+      if (f_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (c0 + j < w.rows) {
+            float v = __uint_as_float(r[j]) * sc + bias;
+            if (res) v += __bfloat162float(res[static_cast<size_t>(j) * w.ld_res]);
+            out[static_cast<size_t>(j) * w.ld_out] = __float2bfloat16(v);
+          }
+        }
+      }
+    } else {
+      float* out = reinterpret_cast<float*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
+      if (f_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (c0 + j < w.rows) {
+            const float v = __uint_as_float(r[j]) * sc + bias;
+            if (w.epi == kEpiAtomicF32) atomicAdd(out + static_cast<size_t>(j) * w.ld_out, v);
+            else out[static_cast<size_t>(j) * w.ld_out] = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncwarp();
+  return true;
+}
+
+__device__ __forceinline__ bool gemm_epilogue(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
+                                              uint32_t acc_parity, volatile int* abort_flag) {
+  if (!gemm_epilogue_body(w, bar, tmem_base, buf, acc_parity, abort_flag)) return false;
+  if ((threadIdx.x & 31) == 0) mbar_arrive(&bar.acc_empty[buf]);
+  return true;
+}
+
+}  // namespace mf

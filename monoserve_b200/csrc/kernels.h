@@ -31,12 +31,14 @@ struct PlanParams {
   int* starts;              // out int32 [E + 1]
   const int* table;         // int32 [E][2] = (region, slot): region 0 host, 1 hot tier
   int* hist;                // int32 [E] activation histogram (+=), or null
-  GemmTile* tiles[2][2];    // [phase][0 = link, 1 = hbm]
+  GemmTile* tiles[2];       // [0 = link, 1 = hbm]: w13 tiles, then w2 tiles; null q = scan only
   GemmQueues* q;
+  int* done;                // int32 [block_cap] row-block counters (zeroed here)
   int* status;
   int chunks, E, H, I;
-  int form;                 // row-block height of host-resident experts: 16/32/64/128; 0 = 128
+  int form;                 // row-block height of host-resident experts: 16..128; 0 = 256 (one pass up to 256 rows)
   int tile_cap;             // capacity of each tile list
+  int block_cap;            // capacity of done[]
 };
 
 struct PackParams {
@@ -73,7 +75,7 @@ cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_co
 cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream);
 cudaError_t launch_pack(const PackParams& A, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
-cudaError_t launch_expert_gemm(const GemmParams& p, int mode, int ctas, cudaStream_t stream);
+cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream);
 
 // The stable pack from given routing: ranks -> scan -> pair lists (and, when src
 // is set, the packed rows).  `scratch` holds pack_scratch_bytes(T, E, K) bytes.

@@ -286,48 +286,54 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   if (e < E && cnt > 0) {
     tier = A.table[2 * e] == 0 ? kTierHost : kTierHot;
     z = A.table[2 * e + 1];
-    if (tier == kTierHost && A.form) bh = A.form;
+    if (tier == kTierHost) bh = A.form ? A.form : 256;
     nb = (cnt + bh - 1) / bh;
   }
-  const int f13 = (A.I + 127) / 128, f2 = (A.H + 127) / 128;
-  int first[2][2], totals[2][2];
-  for (int ph = 0; ph < 2; ++ph)
-    for (int tq = 0; tq < 2; ++tq) {
-      const int mine = (nb && tier == tq) ? nb * (ph == 0 ? f13 : f2) : 0;
-      first[ph][tq] = block_scan_256(mine, s_warp, totals[ph][tq]);
-    }
-  bool overflow = false;
-  for (int ph = 0; ph < 2; ++ph)
-    for (int tq = 0; tq < 2; ++tq) overflow |= totals[ph][tq] > A.tile_cap;
+  const int f13 = (A.I + 63) / 64, f2 = (A.H + 127) / 128;
+  // per tier: [w13 tiles of every expert][w2 tiles of every expert]; row blocks numbered over all experts
+  int first13[2], first2[2], total13[2], total2[2], blocks_total;
+  const int block0 = block_scan_256(nb, s_warp, blocks_total);
+  for (int tq = 0; tq < 2; ++tq) {
+    const int mine = tier == tq ? nb : 0;
+    first13[tq] = block_scan_256(mine * f13, s_warp, total13[tq]);
+    first2[tq] = block_scan_256(mine * f2, s_warp, total2[tq]);
+  }
+  bool overflow = blocks_total > A.block_cap;
+  for (int tq = 0; tq < 2; ++tq) overflow |= total13[tq] + total2[tq] > A.tile_cap;
+  for (int b = e; b < blocks_total && !overflow; b += blockDim.x) A.done[b] = 0;
   if (e == 0) {
-    for (int ph = 0; ph < 2; ++ph)
-      for (int tq = 0; tq < 2; ++tq) {
-        A.q->n_tiles[ph][tq] = overflow ? 0 : totals[ph][tq];
-        A.q->head[ph][tq] = 0;
-      }
-    A.q->slots[0] = A.q->slots[1] = 0;
+    for (int tq = 0; tq < 2; ++tq) {
+      A.q->n_tiles[tq] = overflow ? 0 : total13[tq] + total2[tq];
+      A.q->head[tq] = 0;
+    }
+    A.q->slots = 0;
+    A.q->n_blocks = blocks_total;
+    A.q->need = 4 * f13;   // four epilogue warps arrive per w13 tile
     if (overflow) atomicOr(A.status, kErrPlanOverflow);
   }
   if (overflow || nb == 0) return;
-  for (int ph = 0; ph < 2; ++ph) {
-    GemmTile* out = A.tiles[ph][tier] + first[ph][tier];
-    const int nf = ph == 0 ? f13 : f2;
-    for (int b = 0; b < nb; ++b) {
-      const int rows = min(bh, cnt - b * bh);
-      int n = 16;
-      while (n < rows) n <<= 1;
-      for (int f = 0; f < nf; ++f) {
-        GemmTile t;
-        t.w_row0 = f * 128;
-        t.act_row0 = start + b * bh;
-        t.rows = rows;
-        t.n = n;
-        t.z = z;
-        t.tier = tier;
-        t.expert = e;
-        t.pad = 0;
-        *out++ = t;
-      }
+  GemmTile* out13 = A.tiles[tier] + first13[tier];
+  GemmTile* out2 = A.tiles[tier] + total13[tier] + first2[tier];
+  for (int b = 0; b < nb; ++b) {
+    const int rows = min(bh, cnt - b * bh);
+    int n = 16;
+    while (n < rows) n <<= 1;
+    GemmTile t;
+    t.act_row0 = start + b * bh;
+    t.rows = rows;
+    t.n = n;
+    t.z = z;
+    t.tier = tier;
+    t.block = block0 + b;
+    t.phase = 0;
+    for (int f = 0; f < f13; ++f) {
+      t.w_row0 = f * 64;
+      *out13++ = t;
+    }
+    t.phase = 1;
+    for (int f = 0; f < f2; ++f) {
+      t.w_row0 = f * 128;
+      *out2++ = t;
     }
   }
 }

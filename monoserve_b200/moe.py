@@ -152,9 +152,9 @@ class MoELayer:
 
     def last_times(self):
         """Milliseconds of the last profiled forward, by kernel."""
-        ms = (ctypes.c_float * 7)()
+        ms = (ctypes.c_float * 6)()
         _C.check(_C.lib.monofab_moe_last_times(self._h, ctypes.byref(ms)))
-        names = ["router_logits", "router_topk", "plan", "pack", "w13", "w2", "combine"]
+        names = ["router_logits", "router_topk", "plan", "pack", "experts", "combine"]
         return dict(zip(names, list(ms)))
 
 

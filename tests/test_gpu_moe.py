@@ -158,7 +158,7 @@ def test_layer_empty_batch_and_bounds():
 def test_skewed_routing_many_rows_per_expert():
     """Almost every token picks the same experts: segments longer than one row
     block, and many experts with no rows at all."""
-    T, H, I, E, K = 300, 256, 128, 16, 2
+    T, H, I, E, K = 400, 256, 128, 16, 2
     m, wr, w13, w2 = make_layer(T, H, I, E, K, hot=[0, 5], seed=3)
     wr = wr.clone()
     wr[3] = 0
@@ -168,9 +168,11 @@ def test_skewed_routing_many_rows_per_expert():
     wr[3] = 0.25   # experts 3 and 9 win almost everywhere
     wr[9] = 0.2
     m.set_router(wr.cuda())
-    check_layer_against_c_oracle(m, wr, w13, w2, xn, x2, K)
+    for form in (64, 128, 0):   # 0: one 256-row pass over a host-resident expert
+        m.set_plan(0, 4, form)
+        check_layer_against_c_oracle(m, wr, w13, w2, xn, x2, K)
     counts = m.workspace("counts")[:E].cpu()
-    assert counts[3] > 128 and (counts == 0).sum() >= 1
+    assert counts[3] > 256 and (counts == 0).sum() >= 1
     m.close()
 
 
