@@ -294,7 +294,7 @@ def run_ours(args):
     if rank == 0:
         layer_hot = MoELayer(H, I, E, K, BATCH)
         layer_hot.set_router(wl["wr"].cuda())
-        layer_hot.set_region(1, wl["w13"].cuda(), wl["w2"].cuda())
+        layer_hot.set_region(1, layer_hot.pack_w13(wl["w13"].cuda()), wl["w2"].cuda(), packed=True)
         tbl = torch.ones(E, 2, dtype=torch.int32)
         tbl[:, 1] = torch.arange(E)
         layer_hot.set_table(tbl)

@@ -136,6 +136,17 @@ int monofab_moe_set_router(monofab_moe* m, const void* wr_bf16, const float* bia
  * takes device addresses (monoserve/runtime/weights.py:100-143). */
 int monofab_moe_set_region(monofab_moe* m, int region, const void* w13, const void* w2, int slots);
 
+/* The HBM hot tier is this library's own copy of the hot experts, so it may store
+ * w13 in the order the tensor core wants: for every 16 features, 16 gate rows then
+ * the 16 matching up rows ("packed"), which makes a SwiGLU tile one contiguous
+ * 128-row TMA box.  monofab_pack_w13 makes such a copy of n stacks [2I][H] (src may
+ * be the device alias of pinned host memory: the copy is then the placement
+ * transfer itself, monoserve/runtime/weights.py:112-113); monofab_moe_set_w13_packed
+ * tells the layer which regions hold packed w13.  The host region normally keeps
+ * the reference's row order (gate rows, then up rows) and is gathered on the fly. */
+int monofab_pack_w13(const void* src, void* dst, int n, int intermediate, int hidden, int elt_bytes, void* stream);
+int monofab_moe_set_w13_packed(monofab_moe* m, int region, int packed);
+
 /* FP8 per-output-channel scales, fp32 [E][2I] and [E][H] on the device, indexed by
  * expert id wherever the expert's weights are (monoserve/runtime/weights.py:103-104). */
 int monofab_moe_set_scales(monofab_moe* m, const float* s13, const float* s2);
@@ -174,7 +185,7 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
  * CUDA events on the launching stream when profiling is on:
  * [0] router logits [1] router top-k [2] plan [3] pack [4] expert GEMMs (w13 + w2, one launch)
  * [5] combine. */
-int monofab_moe_set_profile(monofab_moe* m, int on);
+int monofab_moe_set_profile(monofab_moe* m, int on);   /* bit 0: event times; bit 1: in-kernel role trace */
 int monofab_moe_last_times(monofab_moe* m, float ms[6]);
 
 #ifdef __cplusplus

@@ -95,6 +95,8 @@ struct monofab_moe {
   const void* w13[2] = {nullptr, nullptr};   // device-visible addresses per region
   const void* w2[2] = {nullptr, nullptr};
   int slots[2] = {0, 0};
+  int packed[2] = {0, 0};                    // w13 of the region is in the packed SwiGLU row order
+  bool trace_on = false;
   const float* s13 = nullptr;
   const float* s2 = nullptr;
   // workspaces (device)
@@ -119,6 +121,7 @@ struct monofab_moe {
   GemmTile* tiles[2] = {nullptr, nullptr};
   GemmQueues* queues = nullptr;
   int* done = nullptr;
+  unsigned long long* trace = nullptr;
   int block_cap = 0;
   int* status = nullptr;
   int* status_host = nullptr;
@@ -162,7 +165,10 @@ int build_maps(monofab_moe* m) {
       const uint64_t dims[3] = {K, rows, static_cast<uint64_t>(slots)};
       const uint64_t strides[2] = {K * esz, rows * K * esz};
       const uint32_t box[3] = {64, 16, 1};
+      const uint32_t box_big[3] = {64, 128, 1};
       if (int r = encode_map(&ph.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, c.fp8 ? 0 : 128)) return r;
+      if (int r = encode_map(&ph.w_map_big[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box_big, c.fp8 ? 0 : 128))
+        return r;
     }
     const void* act = phase == 0 ? m->xp : m->h;
     for (int i = 0; i < kActBoxes; ++i) {
@@ -179,6 +185,8 @@ int build_maps(monofab_moe* m) {
     ph.ld_out = phase == 0 ? I : H;
     ph.scale_ld = phase == 0 ? 2 * I : H;
     ph.epi = phase == 0 ? 1 : 2;   // kEpiSiluMul / kEpiRowsF32
+    ph.packed[0] = m->packed[0];
+    ph.packed[1] = m->packed[1];
   }
   gp.tiles[0] = m->tiles[0];
   gp.tiles[1] = m->tiles[1];
@@ -238,6 +246,7 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
   MF_CUDA(launch_pack(kp, st));
   MF_CUDA(mark());
   m->gp.cap = m->credits;
+  m->gp.trace = m->trace_on ? m->trace : nullptr;
   MF_CUDA(launch_expert_gemm(m->gp, ctas, st));
   MF_CUDA(mark());
   CombineParams cp{m->y, m->pair_pos, m->topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(out),
@@ -426,6 +435,7 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   for (int q = 0; q < 2; ++q) A(&m->tiles[q], static_cast<size_t>(m->tile_cap) * sizeof(GemmTile));
   A(&m->queues, sizeof(GemmQueues));
   A(&m->done, static_cast<size_t>(m->block_cap) * 4);
+  A(&m->trace, 4096 * 8);
   A(&m->status, 4);
   if (!r && cudaHostAlloc(reinterpret_cast<void**>(&m->status_host), 64, cudaHostAllocDefault) != cudaSuccess)
     r = fail(MONOFAB_ECUDA, "cudaHostAlloc of the status mirror failed");
@@ -487,6 +497,27 @@ int monofab_moe_set_region(monofab_moe* m, int region, const void* w13, const vo
   m->w2[region] = w2;
   m->slots[region] = slots;
   m->maps_dirty = true;
+  return MONOFAB_OK;
+}
+
+int monofab_moe_set_w13_packed(monofab_moe* m, int region, int packed) {
+  if (!m) return fail(MONOFAB_EINVAL, "set_w13_packed: NULL handle");
+  if (region != MONOFAB_REGION_HOST && region != MONOFAB_REGION_HOT)
+    return fail(MONOFAB_EINVAL, "set_w13_packed: region %d is neither host (0) nor hot (1)", region);
+  std::lock_guard<std::mutex> lock(m->mu);
+  m->packed[region] = packed != 0;
+  m->maps_dirty = true;
+  return MONOFAB_OK;
+}
+
+int monofab_pack_w13(const void* src, void* dst, int n, int intermediate, int hidden, int elt_bytes, void* stream) {
+  if (!src || !dst) return fail(MONOFAB_EINVAL, "pack_w13: NULL argument");
+  if (n < 0 || intermediate <= 0 || intermediate % 16) return fail(MONOFAB_EINVAL, "pack_w13: intermediate=%d must be a positive multiple of 16", intermediate);
+  if ((elt_bytes != 1 && elt_bytes != 2) || hidden <= 0 || (hidden * elt_bytes) % 16)
+    return fail(MONOFAB_EINVAL, "pack_w13: rows of %d x %d bytes are not a whole number of 16-byte vectors", hidden, elt_bytes);
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)
+    return fail(MONOFAB_EINVAL, "pack_w13: buffers must be 16-byte aligned");
+  MF_CUDA(launch_pack_w13(src, dst, n, intermediate, hidden, elt_bytes, static_cast<cudaStream_t>(stream)));
   return MONOFAB_OK;
 }
 
@@ -580,6 +611,7 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
       {"xp", m->xp, P * H * 2},                {"h", m->h, P * I * 2},
       {"y", m->y, P * H * 4},                  {"queues", m->queues, sizeof(GemmQueues)},
       {"hist", m->hist, E * 4},                {"table", m->table, E * 8},
+      {"trace", m->trace, 4096 * 8},
   };
   for (const Entry& e : entries)
     if (!std::strcmp(e.name, name)) {
@@ -593,7 +625,8 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
 int monofab_moe_set_profile(monofab_moe* m, int on) {
   if (!m) return fail(MONOFAB_EINVAL, "set_profile: NULL handle");
   std::lock_guard<std::mutex> lock(m->mu);
-  m->profile = on != 0;
+  m->profile = (on & 1) != 0;
+  m->trace_on = (on & 2) != 0;
   m->times_valid = false;
   return MONOFAB_OK;
 }

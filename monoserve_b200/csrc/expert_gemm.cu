@@ -9,14 +9,18 @@
 //             fp32 rows y[pos][n] of every routed pair     (kEpiRowsF32)
 // A w2 tile may start only when every w13 tile of its row block has stored h:
 // the epilogue warps of w13 tiles count into done[block] (release), and the
-// producer of a w2 tile waits (bounded) for the count before it issues the first
-// load of h.  Tiles are claimed in queue order, so whatever a waiting CTA waits
+// scheduler waits (bounded) for the count before it hands a w2 tile to the
+// producer.  Tiles are claimed in queue order, so whatever a waiting CTA waits
 // for has already been claimed by a CTA that is running: no deadlock.
 //
-// Warp roles (192 threads): warp 0 = tile claim + TMA producer, warp 1 = TMEM
-// owner + MMA issue, warps 2..5 = epilogue.  Accumulators are double-buffered in
-// TMEM so the epilogue of tile i overlaps the loads and MMAs of tile i+1, across
-// tile and phase boundaries.
+// Warp roles (224 threads):
+//   warp 6  scheduler: claims tiles (link credits, queue heads), reads the tile
+//           record, checks the row-block dependency, and fills a 4-deep ring of
+//           work records, running ahead of the data path so that its global-memory
+//           round trips never stall the copies;
+//   warp 0  TMA producer;  warp 1  TMEM owner + MMA issue;  warps 2..5  epilogue.
+// Accumulators are double-buffered in TMEM so the epilogue of tile i overlaps the
+// loads and MMAs of tile i+1, across tile and phase boundaries.
 //
 // Link credits (csrc/fabric/runtime.cuh:415-423,451-485): a CTA takes link
 // tiles only while it holds one of `cap` slots; others work on the HBM queue and
@@ -31,13 +35,14 @@
 
 namespace mf {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;
+constexpr int kWorkSlots = 4;
 
 struct GemmShared {
   GemmBarriers bar;
-  uint64_t tile_ready[2];
-  GemmWork work[2];
-  int block[2];        // row block of the tile in the slot (w13: to count; -1 otherwise)
+  uint64_t work_full[kWorkSlots];    // scheduler -> producer, MMA, epilogue
+  uint64_t work_empty[kWorkSlots];   // 6 arrivals: producer, MMA, four epilogue warps
+  GemmWork work[kWorkSlots];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -52,18 +57,27 @@ __device__ __forceinline__ bool try_acquire_slot(int* slots, int cap) {
   return false;
 }
 
+// Debug trace of CTA 0: slot [role][it][event] <- device time.
+// role 0 scheduler, 1 producer, 2 MMA, 3 epilogue warp 2.
+__device__ __forceinline__ void trace_ev(const GemmParams& p, int role, int it, int ev) {
+  if (p.trace && blockIdx.x == 0 && it < 32 && (threadIdx.x & 31) == 0)
+    p.trace[(role * 32 + it) * 4 + ev] = globaltimer_ns();
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ GemmShared sh;
-  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~static_cast<uintptr_t>(1023));
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
 
   if (threadIdx.x == 0) {
     gemm_barriers_init(sh.bar);
-    mbar_init(&sh.tile_ready[0], 1);
-    mbar_init(&sh.tile_ready[1], 1);
+    for (int i = 0; i < kWorkSlots; ++i) {
+      mbar_init(&sh.work_full[i], 1);
+      mbar_init(&sh.work_empty[i], 6);
+    }
     sh.abort_flag = 0;
     fence_barrier_init();
   }
@@ -76,17 +90,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
   tc_fence_after_sync();
   const uint32_t tmem_base = sh.tmem_base;
 
-  if (warp == 0) {
-    // ------------------------------------------------ claim + TMA producer
+  if (warp == 6) {
+    // ------------------------------------------------------------ scheduler
     if (lane == 0) {
       GemmQueues* q = p.q;
       const int n_link = q->n_tiles[0], n_hbm = q->n_tiles[1], need = q->need;
-      const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       bool have_slot = false, link_left = n_link > 0, hbm_left = n_hbm > 0;
-      GemmPipe pipe;
       for (int it = 0;; ++it) {
-        const int buf = it & 1;
-        if (!mbar_wait_bounded(&sh.bar.acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, kWaitBudgetNs)) break;
+        const int slot = it % kWorkSlots;
+        trace_ev(p, 0, it, 0);
+        if (!mbar_wait_bounded(&sh.work_empty[slot], ((it / kWorkSlots) & 1) ^ 1, abort_flag, kWaitBudgetNs)) break;
         const GemmTile* t = nullptr;
         if (link_left) {
           if (!have_slot) have_slot = try_acquire_slot(&q->slots, p.cap);
@@ -105,19 +118,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
           const int i = atomicAdd(&q->head[1], 1);
           if (i < n_hbm) t = p.tiles[1] + i; else hbm_left = false;
         }
-        GemmWork& w = sh.work[buf];
+        GemmWork& w = sh.work[slot];
         if (!t) {
           // Nothing this CTA may take: both queues are drained, or the remaining
           // link tiles belong to the CTAs that hold the slots.
           w.valid = 0;
-          mbar_arrive(&sh.tile_ready[buf]);
+          mbar_arrive(&sh.work_full[slot]);
           break;
         }
         const GemmTile tile = *t;
+        trace_ev(p, 0, it, 1);
         const GemmPhaseParams& ph = p.ph[tile.phase];
         int box = 0;
         while ((16 << box) < tile.n) ++box;
-        w.a_map = &ph.w_map[tile.tier];
+        const bool packed = tile.phase == 0 && ph.packed[tile.tier];
+        w.a_map = (tile.phase == 0 && !packed) ? &ph.w_map[tile.tier] : &ph.w_map_big[tile.tier];
         w.b_map = &ph.act_map[box];
         w.out = ph.out;
         w.scale = nullptr;
@@ -136,15 +151,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
         w.ld_res = 0;
         w.n_limit = ph.n_limit;
         w.valid = 1;
-        sh.block[buf] = tile.phase == 0 ? tile.block : -1;
-        mbar_arrive(&sh.tile_ready[buf]);
+        w.a_packed = packed;
+        w.block = tile.phase == 0 ? tile.block : -1;
         if (tile.phase == 1) {
           // h of this row block must be complete before TMA reads it
-          const int* flag = p.done + tile.block;
-          if (ld_acquire_gpu(reinterpret_cast<const uint32_t*>(flag)) < static_cast<uint32_t>(need)) {
+          const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.done + tile.block);
+          bool ok = true;
+          if (ld_acquire_gpu(flag) < static_cast<uint32_t>(need)) {
             const unsigned long long t0 = globaltimer_ns();
-            bool ok = true;
-            while (ld_acquire_gpu(reinterpret_cast<const uint32_t*>(flag)) < static_cast<uint32_t>(need)) {
+            while (ld_acquire_gpu(flag) < static_cast<uint32_t>(need)) {
               __nanosleep(64);
               if (*abort_flag || globaltimer_ns() - t0 > kWaitBudgetNs) {
                 *abort_flag = 1;
@@ -152,52 +167,79 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
                 break;
               }
             }
-            if (!ok) break;
           }
+          if (!ok) break;
           fence_proxy_async_all();
         }
-        if (!gemm_produce(w, stages, sh.bar, pipe, abort_flag, pol_w, pol_x)) break;
+        trace_ev(p, 0, it, 2);
+        mbar_arrive(&sh.work_full[slot]);
       }
       if (have_slot) atomicSub(&q->slots, 1);
-      if (*abort_flag) {
-        // Let copies that are still in flight land before the block retires.
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 50000ull) __nanosleep(1000);
-      }
+    }
+  } else if (warp == 0) {
+    // --------------------------------------------------------- TMA producer
+    const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+    GemmPipe pipe;
+    GemmInflight inflight;
+    for (int it = 0;; ++it) {
+      const int slot = it % kWorkSlots;
+      if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[slot].valid) break;
+      trace_ev(p, 1, it, 0);
+      if (!gemm_produce(sh.work[slot], ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x)) break;
+      trace_ev(p, 1, it, 1);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.work_empty[slot]);
+    }
+    if (lane == 0 && *abort_flag) {
+      // Let copies that are still in flight land before the block retires.
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 50000ull) __nanosleep(1000);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issue
     GemmPipe pipe;
     for (int it = 0;; ++it) {
-      const int buf = it & 1;
-      const uint32_t parity = (it >> 1) & 1;
-      if (!mbar_wait_bounded(&sh.tile_ready[buf], parity, abort_flag, kWaitBudgetNs)) break;
-      if (!sh.work[buf].valid) break;
-      if (!gemm_mma(sh.work[buf], stages, sh.bar, pipe, tmem_base, buf, parity, abort_flag)) break;
+      const int slot = it % kWorkSlots, buf = it & 1;
+      if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[slot].valid) break;
+      trace_ev(p, 2, it, 0);
+      long long waited[2] = {0, 0};
+      if (!gemm_mma(sh.work[slot], ring, sh.bar, pipe, tmem_base, buf, (it >> 1) & 1, abort_flag,
+                    p.trace ? waited : nullptr))
+        break;
+      trace_ev(p, 2, it, 1);
+      if (lane == 0) {
+        mbar_arrive(&sh.work_empty[slot]);
+        if (p.trace && blockIdx.x == 0 && it < 32) {
+          p.trace[(2 * 32 + it) * 4 + 2] = sh.work[slot].n;
+          p.trace[(2 * 32 + it) * 4 + 3] = waited[0];
+          p.trace[(4 * 32 + it) * 4 + 0] = waited[1];
+        }
+      }
     }
   } else {
     // -------------------------------------------------------------- epilogue
     for (int it = 0;; ++it) {
-      const int buf = it & 1;
-      const uint32_t parity = (it >> 1) & 1;
-      if (!mbar_wait_bounded(&sh.tile_ready[buf], parity, abort_flag, kWaitBudgetNs)) break;
-      if (!sh.work[buf].valid) break;
-      const int block = sh.block[buf];
-      const GemmWork w = sh.work[buf];
-      // the slot is released by acc_empty inside gemm_epilogue; publish h first
-      if (block >= 0) {
-        // run the epilogue body, then count this warp's part of the row block
-        if (!gemm_epilogue_body(w, sh.bar, tmem_base, buf, parity, abort_flag)) break;
+      const int slot = it % kWorkSlots, buf = it & 1;
+      if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[slot].valid) break;
+      const GemmWork w = sh.work[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.work_empty[slot]);   // the record is copied: the slot may be refilled
+      if (warp == 2) trace_ev(p, 3, it, 0);
+      unsigned long long* seen =
+          (p.trace && blockIdx.x == 0 && warp == 2 && it < 32) ? &p.trace[(3 * 32 + it) * 4 + 3] : nullptr;
+      if (!gemm_epilogue(w, sh.bar, tmem_base, buf, (it >> 1) & 1, abort_flag, seen)) break;
+      if (warp == 2) trace_ev(p, 3, it, 1);
+      if (w.block >= 0) {
+        // publish this warp's part of h, then count it into the row block
         __threadfence();
         fence_proxy_async_all();
         __syncwarp();
-        if (lane == 0) {
-          atomicAdd(p.done + block, 1);
-          mbar_arrive(&sh.bar.acc_empty[buf]);
-        }
-      } else {
-        if (!gemm_epilogue(w, sh.bar, tmem_base, buf, parity, abort_flag)) break;
+        if (lane == 0) atomicAdd(p.done + w.block, 1);
       }
+      if (warp == 2) trace_ev(p, 3, it, 2);
     }
   }
 
@@ -209,6 +251,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// Copy w13 stacks [n][2I][H] into the packed SwiGLU order: for every group of 16
+// features, 16 gate rows then the 16 matching up rows, so that a tile of 64
+// features is one contiguous block of 128 rows.  One warp per row.
+__global__ void __launch_bounds__(256) pack_w13_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                       long long rows_total, int I, int row_vec) {
+  const long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows_total) return;
+  const int lane = threadIdx.x & 31;
+  const long long z = r / (2 * I);
+  const int in_row = static_cast<int>(r % (2 * I));
+  const int up = in_row >= I, f = up ? in_row - I : in_row;
+  const long long out_row = z * 2 * I + 32LL * (f / 16) + 16 * up + (f % 16);
+  const uint4* s = src + r * row_vec;
+  uint4* d = dst + out_row * row_vec;
+  for (int c = lane; c < row_vec; c += 32) d[c] = ld_nc_stream16(s + c);
+}
+
+cudaError_t launch_pack_w13(const void* src, void* dst, int n, int I, int H, int elt_bytes, cudaStream_t stream) {
+  const long long rows = static_cast<long long>(n) * 2 * I;
+  if (rows == 0) return cudaSuccess;
+  const int row_vec = H * elt_bytes / 16;
+  pack_w13_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, I, row_vec);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream) {

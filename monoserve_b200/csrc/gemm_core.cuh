@@ -26,10 +26,13 @@ namespace mf {
 constexpr int kBlockK = 64;                      // elements per K step (128 bytes of bf16)
 constexpr int kATileBytes = 128 * kBlockK * 2;   // 16 KB
 constexpr int kGemmMaxN = 256;
-constexpr int kBTileBytes = kGemmMaxN * kBlockK * 2;   // 32 KB
-constexpr int kStageBytes = kATileBytes + kBTileBytes; // 48 KB
-constexpr int kGemmStages = 4;
-constexpr int kGemmSmemBytes = kGemmStages * kStageBytes + 1024;
+// Operand stages live in one byte ring: a stage takes 16 KB for the weight tile
+// plus n * 128 bytes for the activation tile, so small-n (decode) tiles keep up
+// to 12 stages in flight (about 200 KB per SM, which is what it takes to cover
+// the loaded HBM latency) and n = 256 tiles still get four.
+constexpr int kRingBytes = 216 * 1024;
+constexpr int kGemmStages = 12;                  // most stages in flight (barrier pairs)
+constexpr int kGemmSmemBytes = kRingBytes + 1024;
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;                    // TMEM columns per accumulator buffer (two buffers)
 constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s of device time per wait
@@ -43,7 +46,7 @@ constexpr int kEpiAtomicF32 = 4;   // out32[m][n] += acc : K-split partial sums
 
 // Everything the three roles need to know about one tile; lives in shared memory.
 struct GemmWork {
-  const CUtensorMap* a_map;   // weights: dims (K, rows, Z), box (64, 16, 1)
+  const CUtensorMap* a_map;   // weights: dims (K, rows, Z); box (64, 16, 1) for SwiGLU tiles, else (64, 128, 1)
   const CUtensorMap* b_map;   // activations: dims (K, rows), box (64, n)
   void* out;
   const float* scale;         // fp32 per weight row (FP8 weights), or null
@@ -60,18 +63,46 @@ struct GemmWork {
   int32_t ld_out, ld_res;
   int32_t n_limit;            // valid output features
   int32_t valid;              // 0: no tile (the consumer roles stop or skip)
-  int32_t pad[3];
+  int32_t a_packed;           // kEpiSiluMul: the weight rows are already interleaved in memory (one 128-row box)
+  int32_t block;              // row block whose counter the epilogue bumps, or -1
+  int32_t pad[1];
 };
 
-struct GemmPipe {   // per-role cursor over the shared-memory stages
-  int stage = 0;
-  uint32_t phase = 0;
+struct GemmPipe {   // a role's cursor over the stage ring; producer and MMA warp replay the same sequence
+  uint32_t vwr = 0;     // virtual write position in bytes (wraps modulo 2^32; only differences are used)
+  uint32_t phys = 0;    // ring offset of the next stage
+  uint32_t slot = 0;    // barrier pair of the next stage
+  uint32_t parity = 0;  // parity of that pair's current use
+  uint32_t i = 0;       // stages allocated so far
+  // Next stage of `size` bytes (a multiple of 1024): its offset in the ring, and
+  // the virtual interval it covers (including a skipped tail when it wraps).
+  __device__ __forceinline__ uint32_t alloc(uint32_t size, uint32_t& vbegin, uint32_t& vend) {
+    vbegin = vwr;
+    if (phys + size > kRingBytes) {
+      vwr += kRingBytes - phys;
+      phys = 0;
+    }
+    const uint32_t at = phys;
+    phys += size;
+    vwr += size;
+    vend = vwr;
+    return at;
+  }
   __device__ __forceinline__ void advance() {
-    if (++stage == kGemmStages) {
-      stage = 0;
-      phase ^= 1;
+    ++i;
+    if (++slot == kGemmStages) {
+      slot = 0;
+      parity ^= 1;
     }
   }
+};
+
+// Producer-only bookkeeping of the stages in flight.
+struct GemmInflight {
+  uint32_t vbegin[kGemmStages];
+  uint32_t tail = 0;          // oldest stage not yet known to be consumed
+  uint32_t tail_slot = 0;
+  uint32_t tail_parity = 0;
 };
 
 struct GemmBarriers {
@@ -92,64 +123,111 @@ __device__ __forceinline__ void gemm_barriers_init(GemmBarriers& b) {
   }
 }
 
-// TMA issue for one tile (one thread).  Returns false when a wait was abandoned.
-__device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* stages, GemmBarriers& bar, GemmPipe& pipe,
-                                             volatile int* abort_flag, uint64_t pol_w, uint64_t pol_x) {
-  const uint32_t bytes = kATileBytes + w.n * kBlockK * 2;
-  const bool interleave = w.epi == kEpiSiluMul;
+// TMA issue for one tile.  The WHOLE producer warp calls it: every lane keeps
+// the same bookkeeping, lane 0 arms the barrier, and the copies of one stage go
+// out as a single warp-wide instruction (lanes 0..7 the weight boxes, lane 8 the
+// activation box), which costs one issue slot instead of nine.
+// Returns false when a wait was abandoned.
+__device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
+                                             GemmInflight& fl, volatile int* abort_flag, uint64_t pol_w,
+                                             uint64_t pol_x) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t size = kATileBytes + w.n * kBlockK * 2;
+  // SwiGLU tiles of a tensor in the reference row order gather eight 16-row boxes;
+  // every other tile is one 128-row box (a packed SwiGLU tensor stores gate/up
+  // groups of 16 rows alternately, so its tile starts at row 2 * a_row_lo).
+  const bool gather = w.epi == kEpiSiluMul && !w.a_packed;
+  const int a_row = gather ? ((lane & 1) ? w.a_row_hi : w.a_row_lo) + 16 * ((lane & 7) >> 1)
+                           : (w.epi == kEpiSiluMul ? 2 * w.a_row_lo : w.a_row_lo);
+  const int n_a = gather ? 8 : 1;
   for (int kt = 0; kt < w.k_tiles; ++kt) {
-    if (!mbar_wait_bounded(&bar.empty[pipe.stage], pipe.phase ^ 1, abort_flag, kWaitBudgetNs)) return false;
-    uint8_t* a = stages + pipe.stage * kStageBytes;
-    uint8_t* b = a + kATileBytes;
-    uint64_t* full = &bar.full[pipe.stage];
-    mbar_arrive_expect_tx(full, bytes);
-    const int x = (w.k0 + kt) * kBlockK;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int row = interleave ? ((j & 1) ? w.a_row_hi : w.a_row_lo) + 16 * (j >> 1) : w.a_row_lo + 16 * j;
-      tma_load_3d(a + j * 2048, w.a_map, full, x, row, w.a_z, pol_w);
+    uint32_t vb, ve;
+    const uint32_t phys = pipe.alloc(size, vb, ve);
+    // room in the ring and a free barrier pair: retire the oldest stages as needed
+    while (pipe.i - fl.tail >= kGemmStages || (pipe.i != fl.tail && ve - fl.vbegin[fl.tail_slot] > kRingBytes)) {
+      if (!mbar_wait_bounded(&bar.empty[fl.tail_slot], fl.tail_parity, abort_flag, kWaitBudgetNs)) return false;
+      ++fl.tail;
+      if (++fl.tail_slot == kGemmStages) {
+        fl.tail_slot = 0;
+        fl.tail_parity ^= 1;
+      }
     }
-    tma_load_2d(b, w.b_map, full, x, w.b_row0, pol_x);
+    const uint32_t slot = pipe.slot;
+    fl.vbegin[slot] = vb;
+    uint8_t* a = ring + phys;
+    uint64_t* full = &bar.full[slot];
+    if (lane == 0) mbar_arrive_expect_tx(full, size);
+    __syncwarp();
+    const int x = (w.k0 + kt) * kBlockK;
+    if (lane < n_a) {
+      tma_load_3d(a + lane * 2048, w.a_map, full, x, a_row, w.a_z, pol_w);
+    } else if (lane == 8) {
+      tma_load_2d(a + kATileBytes, w.b_map, full, x, w.b_row0, pol_x);
+    }
     pipe.advance();
   }
   return true;
 }
 
-// MMA issue for one tile into accumulator buffer `buf` (whole warp calls; lane 0 issues).
-__device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* stages, GemmBarriers& bar, GemmPipe& pipe,
-                                         uint32_t tmem_base, int buf, uint32_t acc_parity, volatile int* abort_flag) {
+// MMA issue for one tile into accumulator buffer `buf`.  The whole MMA warp calls
+// it, but lane 0 alone runs the K loop (wait for a stage, four tcgen05.mma, one
+// commit): nothing in the loop needs the other lanes, and a warp-wide barrier per
+// stage would only add to the issue path, which is what bounds small-N tiles.
+__device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
+                                         uint32_t tmem_base, int buf, uint32_t acc_parity, volatile int* abort_flag,
+                                         long long* wait_cycles = nullptr) {
   const int lane = threadIdx.x & 31;
-  if (!mbar_wait_bounded(&bar.acc_empty[buf], acc_parity ^ 1, abort_flag, kWaitBudgetNs)) return false;
-  tc_fence_after_sync();
-  const uint32_t idesc = umma_idesc_bf16(128, w.n);
-  const uint32_t acc = tmem_base + buf * kAccCols;
-  for (int kt = 0; kt < w.k_tiles; ++kt) {
-    if (!mbar_wait_bounded(&bar.full[pipe.stage], pipe.phase, abort_flag, kWaitBudgetNs)) return false;
+  int ok = 1;
+  if (lane == 0) {
+    if (!mbar_wait_bounded(&bar.acc_empty[buf], acc_parity ^ 1, abort_flag, kWaitBudgetNs)) ok = 0;
     tc_fence_after_sync();
-    if (lane == 0) {
-      const uint32_t a = smem_u32(stages + pipe.stage * kStageBytes);
-      const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(a + kATileBytes);
+    const uint32_t idesc = umma_idesc_bf16(128, w.n);
+    const uint32_t acc = tmem_base + buf * kAccCols;
+    const uint32_t size = kATileBytes + w.n * kBlockK * 2;
+    const uint32_t ring_addr = smem_u32(ring);
+    const uint64_t desc0 = umma_desc_sw128(0);
+    for (int kt = 0; ok && kt < w.k_tiles; ++kt) {
+      uint32_t vb, ve;
+      const uint32_t phys = pipe.alloc(size, vb, ve);
+      const long long tw = wait_cycles ? clock64() : 0;
+      if (!mbar_wait_bounded(&bar.full[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) {
+        ok = 0;
+        break;
+      }
+      if (wait_cycles) wait_cycles[0] += clock64() - tw;
+      const long long ti = wait_cycles ? clock64() : 0;
+      const uint64_t da = desc0 + ((ring_addr + phys) >> 4);
+      const uint64_t db = da + (kATileBytes >> 4);
 #pragma unroll
       for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
-      umma_commit(&bar.empty[pipe.stage]);
+      umma_commit(&bar.empty[pipe.slot]);
+      if (wait_cycles) wait_cycles[1] += clock64() - ti;
+      pipe.advance();
     }
-    __syncwarp();
-    pipe.advance();
+    if (ok) umma_commit(&bar.acc_full[buf]);
   }
-  if (lane == 0) umma_commit(&bar.acc_full[buf]);
-  __syncwarp();
-  return true;
+  // every lane follows lane 0's cursor, so that any lane could take over and the
+  // warp stays convergent at tile boundaries
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  pipe.vwr = __shfl_sync(0xffffffffu, pipe.vwr, 0);
+  pipe.phys = __shfl_sync(0xffffffffu, pipe.phys, 0);
+  pipe.slot = __shfl_sync(0xffffffffu, pipe.slot, 0);
+  pipe.parity = __shfl_sync(0xffffffffu, pipe.parity, 0);
+  pipe.i = __shfl_sync(0xffffffffu, pipe.i, 0);
+  return ok != 0;
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 // Epilogue of one tile from accumulator buffer `buf` (the four epilogue warps
 // call): everything except handing the buffer back to the MMA warp.
 __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
-                                                   uint32_t acc_parity, volatile int* abort_flag) {
+                                                   uint32_t acc_parity, volatile int* abort_flag,
+                                                   unsigned long long* acc_seen = nullptr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = warp & 3;
   if (!mbar_wait_bounded(&bar.acc_full[buf], acc_parity, abort_flag, kWaitBudgetNs)) return false;
   tc_fence_after_sync();
+  if (acc_seen && lane == 0) *acc_seen = globaltimer_ns();
   const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kAccCols;
   const bool silu = w.epi == kEpiSiluMul;
   // output feature of this lane, and the weight row its accumulator row came from
@@ -184,14 +262,20 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
       // lanes < 16 own gate rows, lanes >= 16 the matching up rows; exchange halves
       const bool lo = lane < 16;
       const int t0 = c0 + (lo ? 0 : 16);
-      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(w.out) + static_cast<size_t>(w.b_row0 + t0) * w.ld_out + f;
+      unsigned short* out = reinterpret_cast<unsigned short*>(w.out) + static_cast<size_t>(w.b_row0 + t0) * w.ld_out + f;
+      unsigned short hv[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float mine_keep = __uint_as_float(lo ? r[j] : r[16 + j]) * sc;
         const float send = __uint_as_float(lo ? r[16 + j] : r[j]) * sc;
         const float other = __shfl_xor_sync(0xffffffffu, send, 16);
-        const float g = lo ? mine_keep : other, u = lo ? other : mine_keep;
-        if (f_ok && t0 + j < w.rows) out[static_cast<size_t>(j) * w.ld_out] = __float2bfloat16(silu_mul(g, u));
+        hv[j] = __bfloat16_as_ushort(__float2bfloat16(silu_mul(lo ? mine_keep : other, lo ? other : mine_keep)));
+      }
+      if (f_ok) {
+        const int m_hi = w.rows - t0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < m_hi) out[static_cast<size_t>(j) * w.ld_out] = hv[j];
       }
     } else if (w.epi == kEpiStoreBf16) {
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
@@ -203,21 +287,25 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
           if (c0 + j < w.rows) {
             float v = __uint_as_float(r[j]) * sc + bias;
             if (res) v += __bfloat162float(res[static_cast<size_t>(j) * w.ld_res]);
-            out[static_cast<size_t>(j) * w.ld_out] = __float2bfloat16(v);
+            __stcs(reinterpret_cast<unsigned short*>(out + static_cast<size_t>(j) * w.ld_out),
+                   __bfloat16_as_ushort(__float2bfloat16(v)));
           }
         }
       }
-    } else {
+    } else if (w.epi == kEpiAtomicF32) {
       float* out = reinterpret_cast<float*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
       if (f_ok) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (c0 + j < w.rows) {
-            const float v = __uint_as_float(r[j]) * sc + bias;
-            if (w.epi == kEpiAtomicF32) atomicAdd(out + static_cast<size_t>(j) * w.ld_out, v);
-            else out[static_cast<size_t>(j) * w.ld_out] = v;
-          }
-        }
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < w.rows) atomicAdd(out + static_cast<size_t>(j) * w.ld_out, __uint_as_float(r[j]) * sc + bias);
+      }
+    } else {
+      // fp32 rows that are read once, later (per-pair expert outputs, logits): streaming stores
+      float* out = reinterpret_cast<float*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
+      if (f_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < w.rows) __stcs(out + static_cast<size_t>(j) * w.ld_out, __uint_as_float(r[j]) * sc + bias);
       }
     }
   }
@@ -227,8 +315,9 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
 }
 
 __device__ __forceinline__ bool gemm_epilogue(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
-                                              uint32_t acc_parity, volatile int* abort_flag) {
-  if (!gemm_epilogue_body(w, bar, tmem_base, buf, acc_parity, abort_flag)) return false;
+                                              uint32_t acc_parity, volatile int* abort_flag,
+                                              unsigned long long* acc_seen = nullptr) {
+  if (!gemm_epilogue_body(w, bar, tmem_base, buf, acc_parity, abort_flag, acc_seen)) return false;
   if ((threadIdx.x & 31) == 0) mbar_arrive(&bar.acc_empty[buf]);
   return true;
 }

@@ -76,6 +76,7 @@ cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream);
 cudaError_t launch_pack(const PackParams& A, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
 cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream);
+cudaError_t launch_pack_w13(const void* src, void* dst, int n, int I, int H, int elt_bytes, cudaStream_t stream);
 
 // The stable pack from given routing: ranks -> scan -> pair lists (and, when src
 // is set, the packed rows).  `scratch` holds pack_scratch_bytes(T, E, K) bytes.

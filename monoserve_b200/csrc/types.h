@@ -46,6 +46,7 @@ constexpr int kActBoxes = 5;      // activation tensor maps with box heights 16,
 
 struct GemmPhaseParams {
   CUtensorMap w_map[2];            // [tier]: dims (K, rows, Z), box (64, 16, 1), 128-byte swizzle
+  CUtensorMap w_map_big[2];        // the same tensors with box (64, 128, 1), for tiles without interleave
   CUtensorMap act_map[kActBoxes];  // dims (K, P), box (64, 16 << i), 128-byte swizzle
   const float* scale;              // FP8: fp32 [E][rows] per-output-channel scales, else null
   void* out;                       // w13: bf16 [P][ld_out]; w2: fp32 [P][ld_out]
@@ -55,7 +56,8 @@ struct GemmPhaseParams {
   int32_t ld_out;
   int32_t scale_ld;                // row length of `scale`
   int32_t epi;
-  int32_t pad[10];
+  int32_t packed[2];               // [tier] w13 only: rows stored as alternating 16-row gate / up groups
+  int32_t pad[8];
 };
 
 struct GemmParams {
@@ -65,7 +67,8 @@ struct GemmParams {
   int* done;                       // per row block: w13 epilogue arrivals
   int* status;                     // device error word (0 = ok)
   int32_t cap;                     // link credits: CTAs allowed to read host memory at once
-  int32_t pad[5];
+  int32_t pad[3];
+  unsigned long long* trace;       // debug: per-role event times of CTA 0 (u64 [4096]), or null
 };
 
 // Error bits in the device status word.

@@ -21,7 +21,7 @@ _WORKSPACES = {"logits": torch.float32, "topk_ids": torch.int32, "topk_w": torch
                "counts": torch.int32, "starts": torch.int32, "pair_token": torch.int32,
                "pair_weight": torch.float32, "pair_pos": torch.int32, "xp": torch.bfloat16,
                "h": torch.bfloat16, "y": torch.float32, "queues": torch.int32, "hist": torch.int32,
-               "table": torch.int32}
+               "table": torch.int32, "trace": torch.int32}
 
 
 def _stream_ptr(stream=None):
@@ -59,7 +59,7 @@ class MoELayer:
         self.table = None
 
     def close(self):
-        if getattr(self, "_h", None) and self._h.value:
+        if getattr(self, "_h", None) and self._h.value and _C is not None and _C.lib is not None:
             _C.lib.monofab_moe_destroy(self._h)
             self._h = ctypes.c_void_p()
 
@@ -73,9 +73,10 @@ class MoELayer:
         self._keep["router"] = (wr, bias)
         _C.check(_C.lib.monofab_moe_set_router(self._h, wr.data_ptr(), bias.data_ptr() if bias is not None else None))
 
-    def set_region(self, region, w13, w2):
+    def set_region(self, region, w13, w2, packed=False):
         """Register the weight stacks of one region: pinned host tensors for
-        REGION_HOST, CUDA tensors for REGION_HOT."""
+        REGION_HOST, CUDA tensors for REGION_HOT.  packed: w13 is already in the
+        packed SwiGLU row order (see pack_w13)."""
         assert w13.shape[1:] == (2 * self.I, self.H) and w2.shape[1:] == (self.H, self.I)
         assert w13.shape[0] == w2.shape[0] and w13.is_contiguous() and w2.is_contiguous()
         if region == REGION_HOST:
@@ -84,6 +85,17 @@ class MoELayer:
             assert w13.is_cuda and w2.is_cuda
         self._keep[("region", region)] = (w13, w2)
         _C.check(_C.lib.monofab_moe_set_region(self._h, region, w13.data_ptr(), w2.data_ptr(), w13.shape[0]))
+        _C.check(_C.lib.monofab_moe_set_w13_packed(self._h, region, int(packed)))
+
+    def pack_w13(self, w13):
+        """HBM copy of w13 stacks [n, 2I, H] (pinned host or CUDA) in the packed
+        SwiGLU row order: 16 gate rows, then their 16 up rows, per group of 16 features."""
+        n = w13.shape[0]
+        dst = torch.empty(w13.shape, dtype=w13.dtype, device="cuda")
+        src = w13.data_ptr() if w13.is_cuda else _C.host_device_pointer(w13.data_ptr())
+        _C.check(_C.lib.monofab_pack_w13(src, dst.data_ptr(), n, self.I, self.H, w13.element_size(), _stream_ptr()))
+        torch.cuda.current_stream().synchronize()
+        return dst
 
     def set_table(self, table):
         """table: int32 [E, 2] = (region, slot) per expert (monoserve/runtime/weights.py:127-158)."""
@@ -92,9 +104,10 @@ class MoELayer:
         _C.check(_C.lib.monofab_moe_set_table(self._h, t.data_ptr(), _stream_ptr()))
         self.table = t
 
-    def set_experts(self, w13, w2, hot):
+    def set_experts(self, w13, w2, hot, pack_hot=True):
         """The reference's placement: the FULL expert set in pinned host memory,
-        and a copy of the `hot` experts in HBM (monoserve/runtime/weights.py:100-115)."""
+        and a copy of the `hot` experts in HBM (monoserve/runtime/weights.py:100-115).
+        pack_hot: store the hot tier's w13 in the packed SwiGLU row order."""
         hot = list(hot)
         host13, host2 = (w13 if w13.is_pinned() else pin(w13.cpu())), (w2 if w2.is_pinned() else pin(w2.cpu()))
         self.set_region(REGION_HOST, host13, host2)
@@ -102,7 +115,10 @@ class MoELayer:
         table[:, 1] = torch.arange(self.E)
         if hot:
             idx = torch.tensor(hot)
-            self.set_region(REGION_HOT, host13[idx].cuda(), host2[idx].cuda())
+            hot13 = host13[idx].cuda()
+            if pack_hot:
+                hot13 = self.pack_w13(hot13)
+            self.set_region(REGION_HOT, hot13, host2[idx].cuda(), packed=pack_hot)
             table[idx, 0] = REGION_HOT
             table[idx, 1] = torch.arange(len(hot), dtype=torch.int32)
         self.hot = hot
