@@ -164,7 +164,7 @@ int build_maps(monofab_moe* m) {
       if (!base) return fail(MONOFAB_EINVAL, "no expert weights set (monofab_moe_set_region)");
       const uint64_t dims[3] = {K, rows, static_cast<uint64_t>(slots)};
       const uint64_t strides[2] = {K * esz, rows * K * esz};
-      const uint32_t box[3] = {64, 16, 1};
+      const uint32_t box[3] = {64, 16, 1};       // 64 elements of K: 128 bytes of bf16, 64 bytes of e4m3
       const uint32_t box_big[3] = {64, 128, 1};
       if (int r = encode_map(&ph.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, c.fp8 ? 0 : 128)) return r;
       if (int r = encode_map(&ph.w_map_big[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box_big, c.fp8 ? 0 : 128))
@@ -187,6 +187,7 @@ int build_maps(monofab_moe* m) {
     ph.epi = phase == 0 ? 1 : 2;   // kEpiSiluMul / kEpiRowsF32
     ph.packed[0] = m->packed[0];
     ph.packed[1] = m->packed[1];
+    ph.w_fp8 = c.fp8;
   }
   gp.tiles[0] = m->tiles[0];
   gp.tiles[1] = m->tiles[1];
@@ -203,7 +204,7 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
   if (T == 0) return MONOFAB_OK;
   if (!xn || !out) return fail(MONOFAB_EINVAL, "xn and out must not be NULL");
   if (!m->router_w) return fail(MONOFAB_EINVAL, "router weight not set (monofab_moe_set_router)");
-  if (c.fp8) return fail(MONOFAB_EINVAL, "FP8 expert weights are not supported by this build of the layer");
+  if (c.fp8 && (!m->s13 || !m->s2)) return fail(MONOFAB_EINVAL, "FP8 experts need their scales (monofab_moe_set_scales)");
   if (m->maps_dirty)
     if (int r = build_maps(m)) return r;
   const int H = c.hidden, I = c.intermediate, E = c.experts, K = c.top_k;

@@ -36,6 +36,7 @@
 namespace mf {
 
 constexpr int kGemmThreads = 224;
+constexpr int kGemmThreadsFp8 = 352;   // + four converter warps (7..10)
 constexpr int kWorkSlots = 4;
 
 struct GemmShared {
@@ -64,7 +65,9 @@ __device__ __forceinline__ void trace_ev(const GemmParams& p, int role, int it, 
     p.trace[(role * 32 + it) * 4 + ev] = globaltimer_ns();
 }
 
-__global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __grid_constant__ GemmParams p) {
+template <bool FP8>
+__global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
+    expert_gemm_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ GemmShared sh;
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -76,7 +79,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
     gemm_barriers_init(sh.bar);
     for (int i = 0; i < kWorkSlots; ++i) {
       mbar_init(&sh.work_full[i], 1);
-      mbar_init(&sh.work_empty[i], 6);
+      mbar_init(&sh.work_empty[i], FP8 ? 10 : 6);
     }
     sh.abort_flag = 0;
     fence_barrier_init();
@@ -128,14 +131,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
         }
         const GemmTile tile = *t;
         trace_ev(p, 0, it, 1);
-        const GemmPhaseParams& ph = p.ph[tile.phase];
+        const int tier = tile.tier_phase & 0xff, phase = tile.tier_phase >> 8;
+        const GemmPhaseParams& ph = p.ph[phase];
         int box = 0;
         while ((16 << box) < tile.n) ++box;
-        const bool packed = tile.phase == 0 && ph.packed[tile.tier];
-        w.a_map = (tile.phase == 0 && !packed) ? &ph.w_map[tile.tier] : &ph.w_map_big[tile.tier];
+        const bool packed = phase == 0 && ph.packed[tier];
+        w.a_map = (phase == 0 && !packed) ? &ph.w_map[tier] : &ph.w_map_big[tier];
         w.b_map = &ph.act_map[box];
         w.out = ph.out;
-        w.scale = nullptr;
+        w.scale = ph.scale ? ph.scale + static_cast<size_t>(tile.expert) * ph.scale_ld : nullptr;
+        w.w_fp8 = ph.w_fp8;
         w.bias = nullptr;
         w.residual = nullptr;
         w.a_row_lo = tile.w_row0;
@@ -152,8 +157,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
         w.n_limit = ph.n_limit;
         w.valid = 1;
         w.a_packed = packed;
-        w.block = tile.phase == 0 ? tile.block : -1;
-        if (tile.phase == 1) {
+        w.block = phase == 0 ? tile.block : -1;
+        if (phase == 1) {
           // h of this row block must be complete before TMA reads it
           const uint32_t* flag = reinterpret_cast<const uint32_t*>(p.done + tile.block);
           bool ok = true;
@@ -217,6 +222,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) expert_gemm_kernel(const __gr
           p.trace[(4 * 32 + it) * 4 + 0] = waited[1];
         }
       }
+    }
+  } else if (FP8 && warp >= 7) {
+    // ------------------------------------------------- e4m3 -> bf16 converters
+    GemmPipe pipe;
+    const int row = threadIdx.x - 7 * 32;
+    for (int it = 0;; ++it) {
+      const int slot = it % kWorkSlots;
+      if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
+      if (!sh.work[slot].valid) break;
+      if (!gemm_convert(sh.work[slot], ring, sh.bar, pipe, row, abort_flag)) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.work_empty[slot]);
     }
   } else {
     // -------------------------------------------------------------- epilogue
@@ -282,12 +299,18 @@ cudaError_t launch_pack_w13(const void* src, void* dst, int n, int I, int H, int
 cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    const cudaError_t err =
-        cudaFuncSetAttribute(expert_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kGemmSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(expert_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kGemmSmemBytes);
     if (err != cudaSuccess) return err;
     attr = true;
   }
-  expert_gemm_kernel<<<ctas, kGemmThreads, kGemmSmemBytes, stream>>>(p);
+  if (p.ph[0].w_fp8)
+    expert_gemm_kernel<true><<<ctas, kGemmThreadsFp8, kGemmSmemBytes, stream>>>(p);
+  else
+    expert_gemm_kernel<false><<<ctas, kGemmThreads, kGemmSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@
 // warp index modulo 4 covers the four TMEM lane quadrants.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "ptx.cuh"
 #include "types.h"
@@ -25,6 +26,7 @@ namespace mf {
 
 constexpr int kBlockK = 64;                      // elements per K step (128 bytes of bf16)
 constexpr int kATileBytes = 128 * kBlockK * 2;   // 16 KB
+constexpr int kRawTileBytes = 128 * kBlockK;     // 8 KB: the e4m3 image of a weight tile
 constexpr int kGemmMaxN = 256;
 // Operand stages live in one byte ring: a stage takes 16 KB for the weight tile
 // plus n * 128 bytes for the activation tile, so small-n (decode) tiles keep up
@@ -65,7 +67,7 @@ struct GemmWork {
   int32_t valid;              // 0: no tile (the consumer roles stop or skip)
   int32_t a_packed;           // kEpiSiluMul: the weight rows are already interleaved in memory (one 128-row box)
   int32_t block;              // row block whose counter the epilogue bumps, or -1
-  int32_t pad[1];
+  int32_t w_fp8;              // the weight tensor holds e4m3 bytes: W8A16 (exact e4m3 -> bf16 in shared memory)
 };
 
 struct GemmPipe {   // a role's cursor over the stage ring; producer and MMA warp replay the same sequence
@@ -105,8 +107,15 @@ struct GemmInflight {
   uint32_t tail_parity = 0;
 };
 
+// Bytes of one stage: weight tile (bf16), activation tile, and for FP8 weights the
+// raw e4m3 tile the converter warps expand.
+__device__ __forceinline__ uint32_t gemm_stage_bytes(const GemmWork& w) {
+  return kATileBytes + w.n * kBlockK * 2 + (w.w_fp8 ? kRawTileBytes : 0);
+}
+
 struct GemmBarriers {
   uint64_t full[kGemmStages];
+  uint64_t conv[kGemmStages];    // FP8: converter warps -> MMA (4 arrivals)
   uint64_t empty[kGemmStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
@@ -115,6 +124,7 @@ struct GemmBarriers {
 __device__ __forceinline__ void gemm_barriers_init(GemmBarriers& b) {
   for (int i = 0; i < kGemmStages; ++i) {
     mbar_init(&b.full[i], 1);
+    mbar_init(&b.conv[i], 4);
     mbar_init(&b.empty[i], 1);
   }
   for (int i = 0; i < 2; ++i) {
@@ -132,7 +142,11 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
                                              GemmInflight& fl, volatile int* abort_flag, uint64_t pol_w,
                                              uint64_t pol_x) {
   const int lane = threadIdx.x & 31;
-  const uint32_t size = kATileBytes + w.n * kBlockK * 2;
+  const uint32_t size = gemm_stage_bytes(w);
+  const uint32_t b_bytes = w.n * kBlockK * 2;
+  // FP8 weights land as raw bytes behind the activation tile (64-byte rows, no swizzle)
+  const uint32_t a_off = w.w_fp8 ? kATileBytes + b_bytes : 0;
+  const uint32_t a_box = w.w_fp8 ? 1024 : 2048;   // bytes of one 16-row box
   // SwiGLU tiles of a tensor in the reference row order gather eight 16-row boxes;
   // every other tile is one 128-row box (a packed SwiGLU tensor stores gate/up
   // groups of 16 rows alternately, so its tile starts at row 2 * a_row_lo).
@@ -156,11 +170,11 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
     fl.vbegin[slot] = vb;
     uint8_t* a = ring + phys;
     uint64_t* full = &bar.full[slot];
-    if (lane == 0) mbar_arrive_expect_tx(full, size);
+    if (lane == 0) mbar_arrive_expect_tx(full, (w.w_fp8 ? kRawTileBytes : kATileBytes) + b_bytes);
     __syncwarp();
     const int x = (w.k0 + kt) * kBlockK;
     if (lane < n_a) {
-      tma_load_3d(a + lane * 2048, w.a_map, full, x, a_row, w.a_z, pol_w);
+      tma_load_3d(a + a_off + lane * a_box, w.a_map, full, x, a_row, w.a_z, pol_w);
     } else if (lane == 8) {
       tma_load_2d(a + kATileBytes, w.b_map, full, x, w.b_row0, pol_x);
     }
@@ -183,14 +197,15 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
     tc_fence_after_sync();
     const uint32_t idesc = umma_idesc_bf16(128, w.n);
     const uint32_t acc = tmem_base + buf * kAccCols;
-    const uint32_t size = kATileBytes + w.n * kBlockK * 2;
+    const uint32_t size = gemm_stage_bytes(w);
+    uint64_t* ready = w.w_fp8 ? bar.conv : bar.full;
     const uint32_t ring_addr = smem_u32(ring);
     const uint64_t desc0 = umma_desc_sw128(0);
     for (int kt = 0; ok && kt < w.k_tiles; ++kt) {
       uint32_t vb, ve;
       const uint32_t phys = pipe.alloc(size, vb, ve);
       const long long tw = wait_cycles ? clock64() : 0;
-      if (!mbar_wait_bounded(&bar.full[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) {
+      if (!mbar_wait_bounded(&ready[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) {
         ok = 0;
         break;
       }
@@ -215,6 +230,49 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
   pipe.parity = __shfl_sync(0xffffffffu, pipe.parity, 0);
   pipe.i = __shfl_sync(0xffffffffu, pipe.i, 0);
   return ok != 0;
+}
+
+// FP8 weights (W8A16, csrc/fabric/tiles/gemm.cuh:14-18,73-94): the four converter
+// warps expand the raw e4m3 tile of every stage into the bf16 weight tile with the
+// 128-byte swizzle.  Every e4m3 value is exactly a bf16 value, so the MMA sees the
+// exact weights; the per-output-channel fp32 scale is applied in the epilogue.
+// Thread t converts row t: 64 bytes in, 128 bytes out in eight 16-byte chunks,
+// chunk c of row r going to chunk c ^ (r & 7).
+__device__ __forceinline__ bool gemm_convert(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
+                                             int row, volatile int* abort_flag) {
+  const uint32_t size = gemm_stage_bytes(w);
+  const uint32_t raw_off = kATileBytes + w.n * kBlockK * 2;
+  for (int kt = 0; kt < w.k_tiles; ++kt) {
+    uint32_t vb, ve;
+    const uint32_t phys = pipe.alloc(size, vb, ve);
+    if (!mbar_wait_bounded(&bar.full[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) return false;
+    const uint4* src = reinterpret_cast<const uint4*>(ring + phys + raw_off + row * kBlockK);
+    uint8_t* dst = ring + phys + row * 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 v = src[c];
+      const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+      uint32_t out[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[i] & 0xffffu), __NV_E4M3);
+        const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[i] >> 16), __NV_E4M3);
+        const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+        const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+        const __nv_bfloat162 bl = __floats2bfloat162_rn(fl.x, fl.y), bh = __floats2bfloat162_rn(fh.x, fh.y);
+        out[2 * i] = *reinterpret_cast<const uint32_t*>(&bl);
+        out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&bh);
+      }
+      // 16 input bytes -> 32 output bytes = chunks 2c and 2c + 1 of the row
+      *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(out[0], out[1], out[2], out[3]);
+      *reinterpret_cast<uint4*>(dst + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(out[4], out[5], out[6], out[7]);
+    }
+    fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's operand reads
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(&bar.conv[pipe.slot]);
+    pipe.advance();
+  }
+  return true;
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }

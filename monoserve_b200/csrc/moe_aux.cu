@@ -323,14 +323,14 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
     t.rows = rows;
     t.n = n;
     t.z = z;
-    t.tier = tier;
+    t.tier_phase = tier;
+    t.expert = e;
     t.block = block0 + b;
-    t.phase = 0;
     for (int f = 0; f < f13; ++f) {
       t.w_row0 = f * 64;
       *out13++ = t;
     }
-    t.phase = 1;
+    t.tier_phase = tier | (1 << 8);
     for (int f = 0; f < f2; ++f) {
       t.w_row0 = f * 128;
       *out2++ = t;

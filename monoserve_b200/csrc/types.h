@@ -24,8 +24,8 @@ struct GemmTile {
   int32_t rows;       // valid activation rows, 1..n
   int32_t n;          // MMA N = height of the activation box: 16/32/64/128/256
   int32_t z;          // slot of the expert inside its tier's weight tensor
-  int32_t tier;       // kTierHost / kTierHot
-  int32_t phase;      // 0 = w13, 1 = w2
+  int32_t tier_phase; // kTierHost / kTierHot in bits 0..7, phase (0 = w13, 1 = w2) in bits 8..15
+  int32_t expert;     // expert id (FP8 scale rows)
   int32_t block;      // row block id: w13 tiles count into done[block], w2 tiles wait on it
 };
 static_assert(sizeof(GemmTile) == 32, "GemmTile is 32 bytes");
@@ -57,7 +57,8 @@ struct GemmPhaseParams {
   int32_t scale_ld;                // row length of `scale`
   int32_t epi;
   int32_t packed[2];               // [tier] w13 only: rows stored as alternating 16-row gate / up groups
-  int32_t pad[8];
+  int32_t w_fp8;                   // weights are e4m3 bytes (converted to bf16 in shared memory)
+  int32_t pad[7];
 };
 
 struct GemmParams {

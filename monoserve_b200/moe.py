@@ -52,6 +52,7 @@ class MoELayer:
         cfg = _C.MoEConfigC(hidden=hidden, intermediate=intermediate, experts=experts, top_k=top_k,
                             max_tokens=max_tokens, scoring={"softmax": 0, "sigmoid": 1}[scoring],
                             renorm=int(bool(renorm)), routed_scale=float(routed_scale), fp8=int(bool(fp8)))
+        self.fp8 = bool(fp8)
         self._h = ctypes.c_void_p()
         _C.check(_C.lib.monofab_moe_create(ctypes.byref(cfg), ctypes.byref(self._h)))
         self._keep = {}
@@ -79,6 +80,8 @@ class MoELayer:
         packed SwiGLU row order (see pack_w13)."""
         assert w13.shape[1:] == (2 * self.I, self.H) and w2.shape[1:] == (self.H, self.I)
         assert w13.shape[0] == w2.shape[0] and w13.is_contiguous() and w2.is_contiguous()
+        want = torch.uint8 if self.fp8 else torch.bfloat16
+        assert w13.dtype == want and w2.dtype == want, f"expert weights must be {want}"
         if region == REGION_HOST:
             assert w13.is_pinned() and w2.is_pinned(), "host-resident experts must be in pinned memory"
         else:
@@ -97,6 +100,14 @@ class MoELayer:
         torch.cuda.current_stream().synchronize()
         return dst
 
+    def set_scales(self, s13, s2):
+        """FP8: fp32 per-output-channel scales [E, 2I] and [E, H] on the GPU, indexed by expert id."""
+        assert s13.is_cuda and s2.is_cuda and s13.dtype == torch.float32 and s2.dtype == torch.float32
+        assert s13.shape == (self.E, 2 * self.I) and s2.shape == (self.E, self.H)
+        assert s13.is_contiguous() and s2.is_contiguous()
+        self._keep["scales"] = (s13, s2)
+        _C.check(_C.lib.monofab_moe_set_scales(self._h, s13.data_ptr(), s2.data_ptr()))
+
     def set_table(self, table):
         """table: int32 [E, 2] = (region, slot) per expert (monoserve/runtime/weights.py:127-158)."""
         t = torch.as_tensor(table, dtype=torch.int32).contiguous().cpu()
@@ -104,11 +115,13 @@ class MoELayer:
         _C.check(_C.lib.monofab_moe_set_table(self._h, t.data_ptr(), _stream_ptr()))
         self.table = t
 
-    def set_experts(self, w13, w2, hot, pack_hot=True):
+    def set_experts(self, w13, w2, hot, pack_hot=True, scales=None):
         """The reference's placement: the FULL expert set in pinned host memory,
         and a copy of the `hot` experts in HBM (monoserve/runtime/weights.py:100-115).
         pack_hot: store the hot tier's w13 in the packed SwiGLU row order."""
         hot = list(hot)
+        if scales is not None:
+            self.set_scales(scales[0].cuda().contiguous(), scales[1].cuda().contiguous())
         host13, host2 = (w13 if w13.is_pinned() else pin(w13.cpu())), (w2 if w2.is_pinned() else pin(w2.cpu()))
         self.set_region(REGION_HOST, host13, host2)
         table = torch.zeros(self.E, 2, dtype=torch.int32)

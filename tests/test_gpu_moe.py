@@ -354,3 +354,56 @@ def test_pack_pairs_rejects_small_scratch():
     rc = _C.lib.monofab_pack_pairs(ids.cuda().data_ptr(), w.cuda().data_ptr(), 40, 8, 2, 0, None, None, z.data_ptr(),
                                    z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 16, None)
     assert rc == -1 and b"scratch" in _C.lib.monofab_last_error()
+
+
+# --------------------------------------------------------------- FP8 (W8A16)
+TOL_FP8 = 3e-2   # rel-L2 of a layer output, FP8-e4m3 weights with per-output-channel scales
+
+
+def make_fp8_layer(T, H, I, E, K, hot, seed, pack_hot=True):
+    from monoserve_b200.moe import MoELayer
+    wr, w13, w2 = make_weights(H, I, E, seed)
+    q13, s13, d13 = tp.quantize_fp8(w13.float())
+    q2, s2, d2 = tp.quantize_fp8(w2.float())
+    m = MoELayer(H, I, E, K, T, fp8=True)
+    m.set_router(wr.cuda())
+    m.set_experts(q13, q2, hot, pack_hot=pack_hot, scales=(s13, s2))
+    return m, wr, d13, d2
+
+
+@pytest.mark.parametrize("hot,pack_hot,form", [("all", True, 64), ("half", True, 64), ("none", True, 0),
+                                               ("all", False, 64), ("half", False, 128)])
+def test_fp8_layer_against_dequantised_reference(hot, pack_hot, form):
+    """FP8 experts in the hot tier (packed or reference row order) and in pinned
+    host memory: output against the reference's path on the de-quantised weights
+    (tests/test_fabric_model_glm.py:57-67, tests/test_fabric_gemm.py:246-251)."""
+    T, H, I, E, K = 150, 512, 256, 16, 4
+    hot_list = {"all": list(range(E)), "half": list(range(0, E, 2)), "none": []}[hot]
+    m, wr, d13, d2 = make_fp8_layer(T, H, I, E, K, hot_list, seed=21, pack_hot=pack_hot)
+    m.set_plan(0, 4, form)
+    xn, x2 = acts(T, H, 22)
+    out = m.forward(xn.cuda(), x2.cuda())
+    torch.cuda.synchronize()
+    assert m.status() == 0
+    ids = m.workspace("topk_ids")[:T * K].cpu().view(T, K).long()
+    w = m.workspace("topk_w")[:T * K].cpu().view(T, K)
+    ref, _, _ = tp.moe_layer(xn.float(), x2.float(), wr, d13, d2, K, routing=(w, ids))
+    assert rel_l2(out.float().cpu(), ref) < TOL_FP8
+    # W8A16 is exact in the weights: the only differences are accumulation order and bf16 rounding of h
+    assert rel_l2(out.float().cpu(), ref) < 2e-3
+    m.close()
+
+
+def test_fp8_qwen_shape_prefill_rows():
+    """GLM-like FP8 at a larger shape with long expert segments (prefill-sized rows)."""
+    T, H, I, E, K = 600, 1024, 384, 8, 2
+    m, wr, d13, d2 = make_fp8_layer(T, H, I, E, K, list(range(4)), seed=23)
+    xn, x2 = acts(T, H, 24)
+    out = m.forward(xn.cuda(), x2.cuda())
+    torch.cuda.synchronize()
+    assert m.status() == 0
+    ids = m.workspace("topk_ids")[:T * K].cpu().view(T, K).long()
+    w = m.workspace("topk_w")[:T * K].cpu().view(T, K)
+    ref, _, _ = tp.moe_layer(xn.float(), x2.float(), wr, d13, d2, K, routing=(w, ids))
+    assert rel_l2(out.float().cpu(), ref) < TOL_FP8
+    m.close()
