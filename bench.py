@@ -165,7 +165,9 @@ def config_dict(n_gpus):
                         "host memory read in place, decode batch 256, Zipf(1.1)+N(0,1) router logits",
             "hidden": SHAPE["H"], "expert_intermediate": SHAPE["I"], "experts": SHAPE["E"], "top_k": SHAPE["K"],
             "tokens_per_step_per_gpu": BATCH, "hot_experts": N_HOT, "credits": CREDITS, "form": FORM,
-            "parallelism": "1 GPU" if n_gpus == 1 else f"{n_gpus} independent replicas",
+            "parallelism": "1 GPU" if n_gpus == 1 else
+            f"ep{n_gpus}: {SHAPE['E'] // n_gpus} experts per GPU (up to {N_HOT} of them in HBM, the rest in pinned host "
+            f"memory), {BATCH} tokens per GPU per step, NCCL all-to-all dispatch/return",
             "l2": "weights streamed per step (302 MB HBM hot tier + host reads) exceed the 126 MB L2; "
                   f"{N_BATCHES} input batches rotate"}
 
@@ -209,6 +211,90 @@ def run_profile_target(args):
     layer.close()
 
 
+def run_ours_ep(args, wl, world, rank, local):
+    """N > 1: experts partitioned over the ranks; every rank brings its own batch of
+    BATCH tokens per step (weak scaling); dispatch and return over NCCL."""
+    import torch.distributed as dist
+    from monoserve_b200.ep import ExpertParallelMoE
+    H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
+    El = E // world
+    lo = rank * El
+    layer = ExpertParallelMoE(H, I, E, K, BATCH)
+    layer.set_router(wl["wr"].cuda())
+    # the HBM hot tier keeps its per-GPU capacity: the N_HOT most probable local experts
+    prior_local = wl["prior"][lo:lo + El]
+    hot = sorted(torch.argsort(prior_local, descending=True)[:min(N_HOT, El)].tolist())
+    layer.set_local_experts(wl["w13"][lo:lo + El].contiguous(), wl["w2"][lo:lo + El].contiguous(), hot)
+    layer.set_plan(0, CREDITS, FORM)
+    g = torch.Generator().manual_seed(50 + rank)
+    xs, x2s = [], []
+    for _ in range(N_BATCHES):
+        x = torch.randn(BATCH, H, generator=g)
+        x[:, 0] = 1.0
+        xs.append(x.to(torch.bfloat16).cuda())
+        x2s.append(torch.randn(BATCH, H, generator=g).to(torch.bfloat16).cuda())
+    xs_h = [x.cpu().pin_memory() for x in xs]
+    x2s_h = [x.cpu().pin_memory() for x in x2s]
+    out = torch.empty(BATCH, H, dtype=torch.bfloat16, device="cuda")
+    out_h = torch.empty(BATCH, H, dtype=torch.bfloat16, pin_memory=True)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i):
+        layer.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out)
+
+    def step_e2e(i):
+        xs[0].copy_(xs_h[i % N_BATCHES], non_blocking=True)
+        x2s[0].copy_(x2s_h[i % N_BATCHES], non_blocking=True)
+        layer.forward(xs[0], x2s[0], out)
+        out_h.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    b.record()
+    barrier()
+    ms = torch.tensor([a.elapsed_time(b)], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else {}
+    layer.local.status()
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step_e2e(i)
+    barrier()
+    sec = torch.tensor([time.perf_counter() - t0], device="cuda")
+    dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+    layer.local.status()
+    if rank == 0:
+        tokens = BATCH * world
+        ms_dev, sec_e2e = float(ms.item()), float(sec.item())
+        line = {"metric": "moe_layer_tokens_per_s", "value": tokens * args.steps / (ms_dev * 1e-3), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": config_dict(world), "clocks": clocks,
+                "e2e": {"value": tokens * args.steps / sec_e2e, "unit": "tokens/s",
+                        "h2d_bytes_per_step": 2 * BATCH * H * 2, "d2h_bytes_per_step": BATCH * H * 2},
+                "gpu_launches": 7 * args.steps,
+                "roofline": None, "cpu_baseline": None,
+                "note": "per-rank kernel roofline and the CPU baseline are reported by the N=1 run"}
+        print(json.dumps(line), flush=True)
+    layer.close()
+    dist.destroy_process_group()
+
+
 def run_ours(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -220,6 +306,8 @@ def run_ours(args):
     from monoserve_b200.moe import MoELayer
     H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
     wl = make_workload()
+    if world > 1:
+        return run_ours_ep(args, wl, world, rank, local)
     layer = MoELayer(H, I, E, K, BATCH)
     layer.set_router(wl["wr"].cuda())
     layer.set_experts(wl["w13"], wl["w2"], wl["hot"])

@@ -168,6 +168,17 @@ int monofab_moe_set_plan(monofab_moe* m, int ctas, int credits, int form);
  * of monoserve/runtime/lane.py:340-380. */
 int monofab_moe_forward(monofab_moe* m, const void* xn, const void* x2, void* out, int T, void* stream);
 
+/* The expert FFN alone, over rows the caller placed in the layer's packed-row
+ * workspace "xp" (for example the receive buffer of an all-to-all): segment s
+ * holds seg_counts[s] consecutive rows (device int32 [n_seg]) that all belong to
+ * expert seg_expert[s] (device int32 [n_seg], NULL = segment index), n_seg <= 256.
+ * Results: fp32 rows in workspace "y", bf16 hidden rows in "h", segment offsets in
+ * "starts".  The total must not exceed max_tokens * top_k rows.  This is the
+ * per-expert w13 -> w2 stage chain of monoserve/runtime/lane.py:352-363 on its own,
+ * which expert parallelism needs between dispatch and return. */
+int monofab_moe_experts(monofab_moe* m, const int32_t* seg_counts, const int32_t* seg_expert, int n_seg,
+                        void* stream);
+
 /* The same pass from and to HOST buffers (pinned for full speed): copies xn and
  * x2 to the device, runs the layer, copies `out` back and waits for it. */
 int monofab_moe_forward_host(monofab_moe* m, const void* xn_host, const void* x2_host, void* out_host, int T,

@@ -18,7 +18,7 @@ EXPORTS = [
     "monofab_version", "monofab_last_error", "monofab_struct_layouts_json", "monofab_host_device_pointer",
     "monofab_host_alloc", "monofab_host_free", "monofab_router_logits", "monofab_router_topk", "monofab_combine", "monofab_pack_scratch_bytes", "monofab_pack_pairs", "monofab_pack_pairs_static",
     "monofab_moe_create", "monofab_moe_destroy", "monofab_moe_set_router", "monofab_moe_set_region",
-    "monofab_moe_set_scales", "monofab_pack_w13", "monofab_moe_set_w13_packed", "monofab_moe_set_table", "monofab_moe_set_plan", "monofab_moe_forward",
+    "monofab_moe_set_scales", "monofab_pack_w13", "monofab_moe_set_w13_packed", "monofab_moe_set_table", "monofab_moe_set_plan", "monofab_moe_forward", "monofab_moe_experts",
     "monofab_moe_forward_host", "monofab_moe_status", "monofab_moe_workspace", "monofab_moe_set_profile",
     "monofab_moe_last_times",
 ]
@@ -60,6 +60,7 @@ def _load():
     lib.monofab_moe_set_table.argtypes = [vp, vp, vp]
     lib.monofab_moe_set_plan.argtypes = [vp, i32, i32, i32]
     lib.monofab_moe_forward.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.monofab_moe_experts.argtypes = [vp, vp, vp, i32, vp]
     lib.monofab_moe_forward_host.argtypes = [vp, vp, vp, vp, i32, vp]
     lib.monofab_moe_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.monofab_moe_workspace.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]

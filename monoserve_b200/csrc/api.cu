@@ -258,6 +258,39 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
   return MONOFAB_OK;
 }
 
+// Expert FFN over caller-described segments of the layer's packed-row buffer.
+int experts_locked(monofab_moe* m, const int* seg_counts, const int* seg_expert, int n_seg, cudaStream_t st) {
+  const monofab_moe_config& c = m->cfg;
+  if (n_seg < 1 || n_seg > kMaxExperts) return fail(MONOFAB_EINVAL, "experts: n_seg=%d outside [1, %d]", n_seg, kMaxExperts);
+  if (!seg_counts) return fail(MONOFAB_EINVAL, "experts: seg_counts must not be NULL");
+  if (c.fp8 && (!m->s13 || !m->s2)) return fail(MONOFAB_EINVAL, "FP8 experts need their scales (monofab_moe_set_scales)");
+  if (m->maps_dirty)
+    if (int r = build_maps(m)) return r;
+  const int ctas = m->ctas > 0 && m->ctas < m->num_sms ? m->ctas : m->num_sms;
+  PlanParams pp{};
+  pp.seg_counts = seg_counts;
+  pp.seg_expert = seg_expert;
+  pp.counts = m->counts;
+  pp.starts = m->starts;
+  pp.table = m->table;
+  pp.tiles[0] = m->tiles[0];
+  pp.tiles[1] = m->tiles[1];
+  pp.done = m->done;
+  pp.block_cap = m->block_cap;
+  pp.q = m->queues;
+  pp.status = m->status;
+  pp.E = n_seg;
+  pp.H = c.hidden;
+  pp.I = c.intermediate;
+  pp.form = m->form;
+  pp.tile_cap = m->tile_cap;
+  MF_CUDA(launch_plan(pp, st));
+  m->gp.cap = m->credits;
+  m->gp.trace = nullptr;
+  MF_CUDA(launch_expert_gemm(m->gp, ctas, st));
+  return MONOFAB_OK;
+}
+
 template <class T>
 void layout_field(std::string& s, const char* name, size_t off, const char* type, bool& first) {
   char buf[160];
@@ -418,8 +451,8 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   A(&m->logits, T * E * 4);
   A(&m->topk_ids, P * 4);
   A(&m->topk_w, P * 4);
-  A(&m->counts, E * 4);
-  A(&m->starts, (E + 1) * 4);
+  A(&m->counts, kMaxExperts * 4);            // also used per segment by monofab_moe_experts
+  A(&m->starts, (kMaxExperts + 1) * 4);
   A(&m->chunk_counts, chunks * E * 4);
   A(&m->pair_rank, P * 4);
   A(&m->pair_token, m->pairs_cap * 4);
@@ -566,6 +599,12 @@ int monofab_moe_forward(monofab_moe* m, const void* xn, const void* x2, void* ou
   if (!m) return fail(MONOFAB_EINVAL, "forward: NULL handle");
   std::lock_guard<std::mutex> lock(m->mu);
   return forward_locked(m, xn, x2, out, T, static_cast<cudaStream_t>(stream));
+}
+
+int monofab_moe_experts(monofab_moe* m, const int32_t* seg_counts, const int32_t* seg_expert, int n_seg, void* stream) {
+  if (!m) return fail(MONOFAB_EINVAL, "experts: NULL handle");
+  std::lock_guard<std::mutex> lock(m->mu);
+  return experts_locked(m, seg_counts, seg_expert, n_seg, static_cast<cudaStream_t>(stream));
 }
 
 int monofab_moe_forward_host(monofab_moe* m, const void* xn_host, const void* x2_host, void* out_host, int T,

@@ -26,6 +26,8 @@ struct RouterParams {
 };
 
 struct PlanParams {
+  const int* seg_counts;    // if set: rows per segment are given (no chunk sums); E is then the segment count
+  const int* seg_expert;    // if set: expert id of every segment (table row, scale row); else identity
   int* chunk_counts;        // in: [chunks][E] counts; out: exclusive prefix over chunks per expert
   int* counts;              // out int32 [E]
   int* starts;              // out int32 [E + 1]

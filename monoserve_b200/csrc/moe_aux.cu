@@ -266,7 +266,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   const int e = threadIdx.x;
   const int E = A.E;
   int cnt = 0;
-  if (e < E) {
+  if (e < E && A.seg_counts) {
+    cnt = A.seg_counts[e];
+    A.counts[e] = cnt;
+  } else if (e < E) {
     for (int c = 0; c < A.chunks; ++c) {
       int* cell = A.chunk_counts + static_cast<size_t>(c) * E + e;
       const int v = *cell;
@@ -283,9 +286,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
 
   if (!A.q) return;   // scan only: counts, starts and chunk prefixes
   int tier = kTierHot, z = 0, bh = 128, nb = 0;
+  const int expert = (e < E && A.seg_expert) ? A.seg_expert[e] : e;
   if (e < E && cnt > 0) {
-    tier = A.table[2 * e] == 0 ? kTierHost : kTierHot;
-    z = A.table[2 * e + 1];
+    tier = A.table[2 * expert] == 0 ? kTierHost : kTierHot;
+    z = A.table[2 * expert + 1];
     if (tier == kTierHost) bh = A.form ? A.form : 256;
     nb = (cnt + bh - 1) / bh;
   }
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
     t.n = n;
     t.z = z;
     t.tier_phase = tier;
-    t.expert = e;
+    t.expert = expert;
     t.block = block0 + b;
     for (int f = 0; f < f13; ++f) {
       t.w_row0 = f * 64;

@@ -152,6 +152,17 @@ class MoELayer:
                                             out.data_ptr(), T, _stream_ptr()))
         return out
 
+    def experts(self, seg_counts, seg_expert=None):
+        """Expert FFN over the rows already in workspace("xp"): segment s = seg_counts[s]
+        consecutive rows of expert seg_expert[s] (int32 CUDA tensors).  Results in
+        workspace("y") (fp32 rows) and workspace("h")."""
+        assert seg_counts.is_cuda and seg_counts.dtype == torch.int32 and seg_counts.is_contiguous()
+        if seg_expert is not None:
+            assert seg_expert.is_cuda and seg_expert.dtype == torch.int32 and seg_expert.numel() == seg_counts.numel()
+        _C.check(_C.lib.monofab_moe_experts(self._h, seg_counts.data_ptr(),
+                                            seg_expert.data_ptr() if seg_expert is not None else None,
+                                            seg_counts.numel(), _stream_ptr()))
+
     def forward_host(self, xn_host, x2_host, out_host):
         """Host buffers in, host buffer out (synchronous)."""
         T = xn_host.shape[0]
