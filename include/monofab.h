@@ -199,6 +199,95 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
 int monofab_moe_set_profile(monofab_moe* m, int on);   /* bit 0: event times; bit 1: in-kernel role trace */
 int monofab_moe_last_times(monofab_moe* m, float ms[6]);
 
+/* ---- the persistent fabric ------------------------------------------------- */
+
+/* Error bits a running fabric reports through its host mirror (monofab_fabric_progress). */
+#define MONOFAB_FABRIC_ERR_RING_WAIT 1
+#define MONOFAB_FABRIC_ERR_WORKLIST 2
+#define MONOFAB_FABRIC_ERR_DEADLINE 4
+#define MONOFAB_FABRIC_ERR_BAD_TILE 8
+#define MONOFAB_FABRIC_ERR_TILE_WAIT 16
+
+typedef struct monofab_fabric monofab_fabric;
+
+/* The fabric on one GPU: device state, a program pool of pool_bytes (0 = 1 GiB),
+ * pinned staging and a host mirror.  num_workers 0 = one worker per SM.  Nothing is
+ * allocated after this call.  class Fabric of csrc/bindings.cpp:184-187,
+ * csrc/host/fabric.h:31-62. */
+int monofab_fabric_create(int num_workers, int device, size_t pool_bytes, monofab_fabric** out);
+int monofab_fabric_destroy(monofab_fabric* f);
+int monofab_fabric_info(monofab_fabric* f, int32_t* num_workers, int32_t* num_sms, int32_t* running, uint64_t* epoch);
+
+/* Launch / stop the persistent kernel (Fabric.start / stop, csrc/bindings.cpp:188-191).
+ * The device state survives a stop, so lanes resume at the next start. */
+int monofab_fabric_start(monofab_fabric* f);
+int monofab_fabric_stop(monofab_fabric* f);
+
+/* Longest idle back-off of a worker (Fabric.set_idle_cap, csrc/host/fabric.h:50), and
+ * the run-time limit after which the kernel leaves on its own with
+ * MONOFAB_FABRIC_ERR_DEADLINE (default 120 s, 0 = no limit; no counterpart in the
+ * reference, whose kernel can only be stopped by the host). */
+int monofab_fabric_set_limits(monofab_fabric* f, uint32_t idle_cap_ns, uint64_t max_run_ns);
+
+/* A packed program: tiles int64 [n_tiles][8], stages int32 [n_stages][8] =
+ * (first, count, succ_first, succ_count, deps_init, flags, mark, 0), successors
+ * int32 [n_succ]; host pointers.  Returns the device address of the program
+ * descriptor.  Fabric.upload / release / program_info / generation,
+ * csrc/bindings.cpp:199-210, csrc/host/fabric.cpp:252-315. */
+int monofab_fabric_upload(monofab_fabric* f, const int64_t* tiles, int n_tiles, const int32_t* stages, int n_stages,
+                          const int32_t* succ, int n_succ, int first_stage, int reset_stage, int iterations,
+                          uint64_t* handle);
+int monofab_fabric_release(monofab_fabric* f, uint64_t handle);
+/* info = gen, n_tiles, n_stages, first_stage, reset_stage, iterations */
+int monofab_fabric_program_info(monofab_fabric* f, uint64_t handle, uint32_t info[6]);
+
+/* Publish a plan as a new epoch: map[w] = lane of worker w or 255; per lane the
+ * link credits, the borrowing order, the program handle (0 = none) and the kernel
+ * form of host-resident experts (NULL = 64 everywhere).
+ * Fabric.publish, csrc/bindings.cpp:211-232, csrc/host/fabric.cpp:317-355. */
+int monofab_fabric_publish(monofab_fabric* f, const int32_t* map, int n_map, const uint32_t* caps, const int32_t* order,
+                           const uint64_t* programs, int n_lanes, const uint32_t* forms, uint64_t* epoch_out);
+
+/* The host mirror: per lane (iterations, gen, running, mark, mark_ns); per worker
+ * the last epoch seen and when (256 entries each, may be NULL); the device error
+ * bits.  Fabric.progress, csrc/bindings.cpp:26-62. */
+int monofab_fabric_progress(monofab_fabric* f, uint64_t lanes[4][5], uint64_t* worker_epoch, uint64_t* worker_epoch_ns,
+                            uint64_t* error);
+/* stats = slots, inflight, inflight_max, running, tag, iter_in_prog, gen
+ * (Fabric.lane_stats / reset_inflight_max, csrc/host/fabric.cpp:357-378). */
+int monofab_fabric_lane_stats(monofab_fabric* f, int lane, uint32_t stats[7]);
+int monofab_fabric_reset_inflight_max(monofab_fabric* f, int lane);
+
+/* Copies to and from device memory that are safe while the kernel runs, and small
+ * allocations from the program pool (Fabric.read / write / blob_alloc / blob_free,
+ * csrc/host/fabric.cpp:122-148,405-450). */
+int monofab_fabric_read(monofab_fabric* f, uint64_t src, void* dst, size_t bytes);
+int monofab_fabric_write(monofab_fabric* f, uint64_t dst, const void* src, size_t bytes);
+int monofab_fabric_blob_alloc(monofab_fabric* f, size_t bytes, uint64_t* addr);
+int monofab_fabric_blob_free(monofab_fabric* f, uint64_t addr);
+
+/* Stage-event tracing into a caller-provided device buffer of capacity records of
+ * two u64 (stage | lane << 32 | event << 40 | tag << 48, device time);
+ * capacity 0 turns it off (Fabric.set_trace / trace_count, csrc/host/fabric.cpp:165-179). */
+int monofab_fabric_set_trace(monofab_fabric* f, uint64_t ptr, uint32_t capacity);
+int monofab_fabric_trace_count(monofab_fabric* f, uint32_t* count);
+
+/* What every worker is doing, for hang diagnosis: 256 state words and the device
+ * time each state began (Fabric.worker_tiles, csrc/bindings.cpp:266-281). */
+int monofab_fabric_worker_tiles(monofab_fabric* f, uint64_t* words, uint64_t* since_ns);
+
+/* Device end times of `count` iterations of a lane after iteration `start`, taken
+ * from the in-kernel timer (Fabric.iteration_times, csrc/host/fabric.cpp:380-403). */
+int monofab_fabric_iteration_times(monofab_fabric* f, int lane, uint64_t start, int count, double timeout_s,
+                                   uint64_t* end_ns);
+
+/* A TMA tensor map in the fabric's table; returns the device address of its
+ * record.  dims / strides (bytes, rank - 1 of them) / box innermost first; dtype
+ * 0 bf16, 1 f32, 2 u8; swizzle 0/32/64/128 (Fabric.tensor_map,
+ * csrc/bindings.cpp:283-296, csrc/host/tensor_map.cpp:8-50). */
+int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* dims, const uint64_t* strides_bytes,
+                              const uint32_t* box, int rank, int dtype, int swizzle, uint64_t* handle);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,12 @@ EXPORTS = [
     "monofab_moe_set_scales", "monofab_pack_w13", "monofab_moe_set_w13_packed", "monofab_moe_set_table", "monofab_moe_set_plan", "monofab_moe_forward", "monofab_moe_experts",
     "monofab_moe_forward_host", "monofab_moe_status", "monofab_moe_workspace", "monofab_moe_set_profile",
     "monofab_moe_last_times",
+    "monofab_fabric_create", "monofab_fabric_destroy", "monofab_fabric_info", "monofab_fabric_start",
+    "monofab_fabric_stop", "monofab_fabric_set_limits", "monofab_fabric_upload", "monofab_fabric_release",
+    "monofab_fabric_program_info", "monofab_fabric_publish", "monofab_fabric_progress", "monofab_fabric_lane_stats",
+    "monofab_fabric_reset_inflight_max", "monofab_fabric_read", "monofab_fabric_write", "monofab_fabric_blob_alloc",
+    "monofab_fabric_blob_free", "monofab_fabric_set_trace", "monofab_fabric_trace_count",
+    "monofab_fabric_worker_tiles", "monofab_fabric_iteration_times", "monofab_fabric_tensor_map",
 ]
 
 
@@ -66,6 +72,30 @@ def _load():
     lib.monofab_moe_workspace.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
     lib.monofab_moe_set_profile.argtypes = [vp, i32]
     lib.monofab_moe_last_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float * 6)]
+    u32, sz = ctypes.c_uint32, ctypes.c_size_t
+    P = ctypes.POINTER
+    lib.monofab_fabric_create.argtypes = [i32, i32, sz, P(vp)]
+    lib.monofab_fabric_destroy.argtypes = [vp]
+    lib.monofab_fabric_info.argtypes = [vp, P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32), P(u64)]
+    lib.monofab_fabric_start.argtypes = [vp]
+    lib.monofab_fabric_stop.argtypes = [vp]
+    lib.monofab_fabric_set_limits.argtypes = [vp, u32, u64]
+    lib.monofab_fabric_upload.argtypes = [vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, P(u64)]
+    lib.monofab_fabric_release.argtypes = [vp, u64]
+    lib.monofab_fabric_program_info.argtypes = [vp, u64, P(u32 * 6)]
+    lib.monofab_fabric_publish.argtypes = [vp, vp, i32, vp, vp, vp, i32, vp, P(u64)]
+    lib.monofab_fabric_progress.argtypes = [vp, vp, vp, vp, P(u64)]
+    lib.monofab_fabric_lane_stats.argtypes = [vp, i32, P(u32 * 7)]
+    lib.monofab_fabric_reset_inflight_max.argtypes = [vp, i32]
+    lib.monofab_fabric_read.argtypes = [vp, u64, vp, sz]
+    lib.monofab_fabric_write.argtypes = [vp, u64, vp, sz]
+    lib.monofab_fabric_blob_alloc.argtypes = [vp, sz, P(u64)]
+    lib.monofab_fabric_blob_free.argtypes = [vp, u64]
+    lib.monofab_fabric_set_trace.argtypes = [vp, u64, u32]
+    lib.monofab_fabric_trace_count.argtypes = [vp, P(u32)]
+    lib.monofab_fabric_worker_tiles.argtypes = [vp, vp, vp]
+    lib.monofab_fabric_iteration_times.argtypes = [vp, i32, u64, i32, ctypes.c_double, vp]
+    lib.monofab_fabric_tensor_map.argtypes = [vp, u64, vp, vp, vp, i32, i32, i32, P(u64)]
     return lib
 
 

@@ -139,7 +139,45 @@ def helper_fixture():
     print("helper fixture written")
 
 
+def program_spec(mod):
+    """The same two programs built through any Program/Tile implementation."""
+    out = {}
+    p = mod.Program()
+    a = p.stage([mod.Tile(mod.KIND["spin"], i=(i, 0), a=(1000 + i, 77)) for i in range(5)])
+    b = p.stage([mod.Tile(33, i=(1, 2, 3, 4), a=(5, 6, 7, 8, 9), flags=3)], link=True, mark=0x201)
+    c = p.stage(mod.tile_array(32, i0=np.arange(7) * 128, i1=3, i2=9, i3=1, a0=111, a1=222, a2=333))
+    d = p.stage()
+    p.after(a, b)
+    p.after(a, c)
+    p.after(b, d)
+    p.after(c, d)
+    p.reserve(11)
+    out["dag"] = p.pack(a, iterations=3, reset_tiles=4)
+    q = mod.Program()
+    q.stage([mod.Tile(mod.KIND["nop"])] * 40)
+    out["flat"] = q.pack(0, iterations=0)
+    return out
+
+
+def program_fixture():
+    """Wire format of packed programs from the reference's own monoserve/fabric/program.py."""
+    sys.path.insert(0, REF)
+    try:
+        ref = importlib.import_module("monoserve.fabric.program")
+    finally:
+        sys.path.pop(0)
+    out = {}
+    for name, (tiles, stages, succ, first, reset, it) in program_spec(ref).items():
+        out[name + "_tiles"] = tiles.numpy()
+        out[name + "_stages"] = stages.numpy()
+        out[name + "_succ"] = succ.numpy()
+        out[name + "_meta"] = np.array([first, reset, it], dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "program_pack_reference.npz"), **out)
+    print("program fixture written")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     qwen_fixture()
     helper_fixture()
+    program_fixture()
