@@ -184,7 +184,7 @@ int build_maps(monofab_moe* m) {
     ph.n_limit = phase == 0 ? I : H;
     ph.ld_out = phase == 0 ? I : H;
     ph.scale_ld = phase == 0 ? 2 * I : H;
-    ph.epi = phase == 0 ? 1 : 2;   // kEpiSiluMul / kEpiRowsF32
+    ph.epi = phase == 0 ? 1 : 5;   // kEpiSiluMul / kEpiRowsF32
     ph.packed[0] = m->packed[0];
     ph.packed[1] = m->packed[1];
     ph.w_fp8 = c.fp8;

@@ -143,6 +143,8 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
         w.w_fp8 = ph.w_fp8;
         w.bias = nullptr;
         w.residual = nullptr;
+        w.pair_token = nullptr;
+        w.pair_weight = nullptr;
         w.a_row_lo = tile.w_row0;
         w.a_row_hi = ph.up_offset + tile.w_row0;
         w.a_z = tile.z;

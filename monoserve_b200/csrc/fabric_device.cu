@@ -17,7 +17,10 @@
 // What differs from the reference, on purpose:
 //   * a worker is warp-specialised: warp 0 schedules and runs AHEAD of the data
 //     path through a two-deep ring of work records, so claims, descriptor loads
-//     and epoch refreshes overlap the previous tile; warps 1..4 execute;
+//     and epoch refreshes overlap the previous tile; warps 1..4 execute tiles and
+//     are the epilogue of GEMM tiles; warp 5 issues the TMA copies and warp 6 owns
+//     TMEM and issues tcgen05.mma (gemm_core.cuh), with accumulators double-buffered
+//     across consecutive GEMM tiles;
 //   * no wait is unbounded and nothing traps: a ring publication that waits too
 //     long, a full worklist or an unknown tile kind raise an error bit that the
 //     host reads from the mirror, and the kernel leaves by itself after
@@ -25,6 +28,8 @@
 #include <cuda_runtime.h>
 
 #include "fabric_types.h"
+#include "gemm_core.cuh"
+#include "operands.h"
 #include "ptx.cuh"
 
 namespace mf {
@@ -38,7 +43,7 @@ constexpr int kWorklistCap = 512;
 constexpr uint32_t kMaxBatch = 8;
 constexpr uint32_t kBatchDivisor = 128;
 constexpr int kExecThreads = 128;
-constexpr int kWorkerThreads = 32 + kExecThreads;
+constexpr int kWorkerThreads = 32 + kExecThreads + 64;   // scheduler, exec/epilogue, TMA producer, MMA
 constexpr unsigned long long kRingWaitBudgetNs = 2000000000ull;
 
 enum : uint32_t { kCmdRun = 0, kCmdIdle = 1, kCmdExit = 2 };
@@ -88,9 +93,56 @@ struct WorkerState {
 
 struct WorkSlot {
   TileDesc tile;
+  GemmWork gemm;          // filled by the scheduler for GEMM tiles
   const ProgramDesc* prog;
-  uint32_t stage, tile_lane, link, index, cmd, worker_lane;
+  uint32_t stage, tile_lane, link, index, cmd, worker_lane, is_gemm, pad;
 };
+
+// A GEMM tile (kind 32) in the reference's operand convention
+// (csrc/fabric/model_types.h:37-49): a[0] GemmArgs*, a[1] weight map record,
+// a[2] activation map record, a[3] K range = first K tile | K tiles << 16 (0 = all),
+// a[4] fp32 scale per weight row; i0 first weight row, i1 first activation row,
+// i2 valid activation rows, i3 weight z (expert or slot).  A map record is three
+// CUtensorMaps (monofab_fabric_tensor_map): [0] the caller's box, [1] box
+// (64, 16, 1), [2] box (64, 128, 1).
+__device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
+  GemmArgs A;
+  const uint4* src = reinterpret_cast<const uint4*>(t.a[0]);
+  uint4* dst = reinterpret_cast<uint4*>(&A);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = __ldcg(src + i);
+  if (A.w_fp8) return false;   // FP8 tiles need the converter warps of the stand-alone kernel
+  if (A.bm < 16 || A.bm > kGemmMaxN || (A.bm & (A.bm - 1))) return false;
+  const CUtensorMap* wrec = reinterpret_cast<const CUtensorMap*>(t.a[1]);
+  const CUtensorMap* xrec = reinterpret_cast<const CUtensorMap*>(t.a[2]);
+  const bool silu = A.epi == kEpiSiluMul;
+  w.a_map = silu ? wrec + 1 : wrec + 2;
+  w.b_map = xrec;
+  w.out = reinterpret_cast<void*>(A.out);
+  w.scale = reinterpret_cast<const float*>(t.a[4]);
+  w.bias = reinterpret_cast<const __nv_bfloat16*>(A.bias);
+  w.residual = reinterpret_cast<const __nv_bfloat16*>(A.residual);
+  w.pair_token = reinterpret_cast<const int32_t*>(A.pair_token);
+  w.pair_weight = reinterpret_cast<const float*>(A.pair_weight);
+  w.a_row_lo = t.i0;
+  w.a_row_hi = A.up_offset + t.i0;
+  w.a_z = t.i3;
+  w.b_row0 = t.i1;
+  w.rows = t.i2 < A.bm ? t.i2 : A.bm;
+  w.n = A.bm;
+  const uint32_t k0 = static_cast<uint32_t>(t.a[3] & 0xffff), kn = static_cast<uint32_t>((t.a[3] >> 16) & 0xffff);
+  w.k0 = kn ? k0 : 0;
+  w.k_tiles = kn ? kn : A.k_tiles;
+  w.epi = A.epi;
+  w.ld_out = A.ld_out;
+  w.ld_res = A.ld_res;
+  w.n_limit = A.n_limit;
+  w.valid = 1;
+  w.a_packed = 0;
+  w.block = -1;
+  w.w_fp8 = 0;
+  return w.k_tiles > 0 && A.epi <= kEpiAtomicF32;
+}
 
 __device__ void trace_stage(DeviceState& S, uint32_t lane, uint32_t s, uint32_t event, uint32_t tag) {
   const uint32_t cap = ld_volatile(&S.trace_cap);
@@ -512,14 +564,19 @@ __device__ void note_tile(DeviceState& S, uint32_t worker, const WorkSlot& w, un
 
 struct WorkerShared {
   uint64_t slot_full[2], slot_empty[2];
+  GemmBarriers bar;
   WorkSlot slot[2];
   WorkerState ws;
   unsigned long long t0;
+  uint32_t tmem_base;
   int abort_flag;
 };
 
 __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* Sp, uint32_t first_worker) {
+  extern __shared__ uint8_t smem_raw[];
   __shared__ WorkerShared sh;
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
   DeviceState& S = *Sp;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t worker = first_worker + blockIdx.x;
@@ -527,8 +584,9 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.slot_full[i], 1);
-      mbar_init(&sh.slot_empty[i], 1);
+      mbar_init(&sh.slot_empty[i], 3);   // exec thread 0, producer, MMA
     }
+    gemm_barriers_init(sh.bar);
     sh.abort_flag = 0;
     sh.ws.epoch = ~0ull;
     sh.ws.worker = worker;
@@ -539,7 +597,15 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     sh.ws.left = 0;
     fence_barrier_init();
   }
+  if (warp == 6) {
+    tmem_alloc(&sh.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
   __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh.tmem_base;
+  constexpr unsigned long long kForever = ~0ull >> 1;   // the scheduler's exit record ends these waits
 
   if (warp == 0) {
     // ------------------------------------------------------------ scheduler
@@ -548,7 +614,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
       const unsigned long long t_start = globaltimer_ns();
       for (uint32_t n = 0;; ++n) {
         const int s = n & 1;
-        if (!mbar_wait_bounded(&sh.slot_empty[s], ((n >> 1) & 1) ^ 1, abort_flag, ~0ull >> 1)) break;
+        if (!mbar_wait_bounded(&sh.slot_empty[s], ((n >> 1) & 1) ^ 1, abort_flag, kForever)) break;
         uint32_t cmd = kCmdRun;
         if (ws.left == 0) {
           for (;;) {
@@ -583,6 +649,15 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           w.link = ws.link;
           w.index = ws.next_index;
           w.worker_lane = ws.lane;
+          w.is_gemm = 0;
+          if (w.tile.kind == kTileGemm) {
+            if (make_gemm_work(w.tile, w.gemm)) {
+              w.is_gemm = 1;
+            } else {
+              raise_error(S, kFabErrBadTile);
+              w.tile.kind = kTileNop;   // completes without running, so the program still ends
+            }
+          }
           ++ws.next_index;
           --ws.left;
         }
@@ -590,12 +665,46 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         if (cmd == kCmdExit) break;
       }
     }
-  } else {
-    // ----------------------------------------------------------------- exec
-    const int tid = threadIdx.x - 32;
+  } else if (warp == 5) {
+    // --------------------------------------------------------- TMA producer
+    const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+    GemmPipe pipe;
+    GemmInflight inflight;
     for (uint32_t n = 0;; ++n) {
       const int s = n & 1;
-      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, ~0ull >> 1)) break;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
+      const WorkSlot& w = sh.slot[s];
+      if (w.cmd == kCmdExit) break;
+      bool ok = true;
+      if (w.is_gemm) ok = gemm_produce(w.gemm, ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.slot_empty[s]);
+      if (!ok) break;
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ MMA issue
+    GemmPipe pipe;
+    uint32_t g = 0;   // GEMM tiles seen: accumulator buffer and parity
+    for (uint32_t n = 0;; ++n) {
+      const int s = n & 1;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
+      const WorkSlot& w = sh.slot[s];
+      if (w.cmd == kCmdExit) break;
+      bool ok = true;
+      if (w.is_gemm) {
+        ok = gemm_mma(w.gemm, ring, sh.bar, pipe, tmem_base, g & 1, (g >> 1) & 1, abort_flag);
+        ++g;
+      }
+      if (lane == 0) mbar_arrive(&sh.slot_empty[s]);
+      if (!ok) break;
+    }
+  } else {
+    // ------------------------------------------------------ exec / epilogue
+    const int tid = threadIdx.x - 32;
+    uint32_t g = 0;
+    for (uint32_t n = 0;; ++n) {
+      const int s = n & 1;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       if (tid == 0) {
@@ -606,7 +715,13 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         }
         note_tile(S, worker, w, 1ull << 63);
       }
-      if (!run_core_tile(w, tid, worker, &sh.t0) && tid == 0) raise_error(S, kFabErrBadTile);
+      if (w.is_gemm) {
+        if (!gemm_epilogue(w.gemm, sh.bar, tmem_base, g & 1, (g >> 1) & 1, abort_flag) && tid == 0)
+          raise_error(S, kFabErrTileWait);
+        ++g;
+      } else if (!run_core_tile(w, tid, worker, &sh.t0) && tid == 0) {
+        raise_error(S, kFabErrBadTile);
+      }
       exec_sync();
       if (tid == 0) {
         if (w.link) atomicSub(&S.lane[w.tile_lane].inflight, 1u);
@@ -618,10 +733,25 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
       }
     }
   }
+  // a bounded wait that ran out inside a GEMM role is reported, and every role leaves
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && sh.abort_flag) raise_error(S, kFabErrTileWait);
+  if (warp == 6) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 cudaError_t launch_fabric(DeviceState* S, int workers, uint32_t first_worker, cudaStream_t stream) {
-  fabric_kernel<<<workers, kWorkerThreads, 0, stream>>>(S, first_worker);
+  static bool attr = false;
+  if (!attr) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(fabric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (err != cudaSuccess) return err;
+    attr = true;
+  }
+  fabric_kernel<<<workers, kWorkerThreads, kGemmSmemBytes, stream>>>(S, first_worker);
   return cudaGetLastError();
 }
 

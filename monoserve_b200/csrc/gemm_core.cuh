@@ -42,9 +42,10 @@ constexpr unsigned long long kWaitBudgetNs = 4000000000ull;   // 4 s of device t
 // Epilogues (csrc/fabric/model_types.h:29-35).
 constexpr int kEpiStoreBf16 = 0;   // out[m][n] = bf16(acc (+ bias[n]) (+ residual[m][n]))
 constexpr int kEpiSiluMul = 1;     // 64 gate + 64 up rows: out[m][f] = bf16(silu(g) * u)
-constexpr int kEpiRowsF32 = 2;     // out32[m][n] = acc : per-pair rows for the deterministic combine
+constexpr int kEpiWeightedAdd = 2;  // out32[pair_token[m]][n] += pair_weight[m] * acc (fp32 atomics, arrival order)
 constexpr int kEpiStoreF32 = 3;    // out32[m][n] = acc (+ bias[n])
 constexpr int kEpiAtomicF32 = 4;   // out32[m][n] += acc : K-split partial sums
+constexpr int kEpiRowsF32 = 5;     // out32[m][n] = acc : per-pair rows for the deterministic combine (not in the reference)
 
 // Everything the three roles need to know about one tile; lives in shared memory.
 struct GemmWork {
@@ -54,6 +55,8 @@ struct GemmWork {
   const float* scale;         // fp32 per weight row (FP8 weights), or null
   const __nv_bfloat16* bias;      // per output feature, or null
   const __nv_bfloat16* residual;  // [rows][ld_res], or null
+  const int32_t* pair_token;      // kEpiWeightedAdd: token of every activation row
+  const float* pair_weight;       // kEpiWeightedAdd: routing weight of every activation row
   int32_t a_row_lo;           // first weight row
   int32_t a_row_hi;           // kEpiSiluMul: first up row; otherwise ignored
   int32_t a_z;
@@ -347,6 +350,18 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
             if (res) v += __bfloat162float(res[static_cast<size_t>(j) * w.ld_res]);
             __stcs(reinterpret_cast<unsigned short*>(out + static_cast<size_t>(j) * w.ld_out),
                    __bfloat16_as_ushort(__float2bfloat16(v)));
+          }
+        }
+      }
+    } else if (w.epi == kEpiWeightedAdd) {
+      float* out = reinterpret_cast<float*>(w.out) + f;
+      if (f_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (c0 + j < w.rows) {
+            const int m = w.b_row0 + c0 + j;
+            atomicAdd(out + static_cast<size_t>(w.pair_token[m]) * w.ld_out,
+                      w.pair_weight[m] * (__uint_as_float(r[j]) * sc));
           }
         }
       }

@@ -1,0 +1,188 @@
+"""GEMM tiles inside the persistent fabric against torch, with the weights in HBM
+and in pinned host memory read over the link: the scenarios of the reference's
+tests/test_fabric_gemm.py:71-165,372-400 (dense store with residual for every tile
+height, the expert FFN with the SiLU-and-multiply and weighted-add epilogues,
+K-split partial sums), in the reference's tile operand convention."""
+import time
+
+import pytest
+import torch
+
+from monoserve_b200 import _C
+from monoserve_b200.fabric import Fabric, Program, Tile
+
+pytestmark = pytest.mark.gpu
+
+KIND_GEMM = 32
+EPI_STORE, EPI_SILU_MUL, EPI_WADD, EPI_F32, EPI_ATOMIC = 0, 1, 2, 3, 4
+
+
+def pinned_alias(t):
+    """Pinned host copy of t and its device address (zero copy)."""
+    pin = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    pin.copy_(t)
+    return pin, _C.host_device_pointer(pin.data_ptr())
+
+
+def weight_map(fab, base, shape):   # (E, rows, K) bf16
+    E, rows, K = shape
+    return fab.tensor_map(base, [K, rows, E], [K * 2, rows * K * 2], [64, 64, 1])
+
+
+def act_map(fab, x, bm):            # (M, K) bf16
+    M, K = x.shape
+    return fab.tensor_map(x.data_ptr(), [K, M], [x.stride(0) * 2], [64, bm])
+
+
+def args_tensor(**kw):
+    return torch.frombuffer(bytearray(_C.gemm_args(**kw)), dtype=torch.uint8).cuda()
+
+
+@pytest.fixture
+def fab():
+    f = Fabric(pool_bytes=128 << 20)
+    f.set_max_run(60)
+    yield f
+    f.stop()
+    f.close()
+
+
+def run_program(fab, p, first, caps=(0,)):
+    h = p.upload(fab, first=first)
+    fab.start()
+    fab.publish(map=[0] * fab.num_workers, caps=list(caps), order=[0], programs=[h])
+    t0 = time.time()
+    while fab.progress()["lanes"][0]["iterations"] < 1:
+        assert time.time() - t0 < 30, f"program did not finish: {fab.progress()['error']}"
+        time.sleep(1e-3)
+    fab.stop()
+    assert fab.progress()["error"] == 0
+
+
+@pytest.mark.parametrize("where", ["hbm", "cpu"])
+@pytest.mark.parametrize("bm", [16, 32, 64, 128, 256])
+def test_dense_store(fab, where, bm):
+    torch.manual_seed(0)
+    E, N, K, M = 2, 256, 512, 200
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    x = torch.randn(M + 256, K, device="cuda").to(torch.bfloat16)[:M]
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    keep, base = (None, w.data_ptr()) if where == "hbm" else pinned_alias(w)
+    e = 1
+    args = args_tensor(out=out.data_ptr(), ld_out=N, k_tiles=K // 64, epi=EPI_STORE, bm=bm, n_limit=N,
+                       residual=res.data_ptr(), ld_res=N)
+    wm, xm = weight_map(fab, base, w.shape), act_map(fab, x, bm)
+    tiles = [Tile(KIND_GEMM, i=(n0, m0, min(bm, M - m0), e), a=(args.data_ptr(), wm, xm))
+             for n0 in range(0, N, 128) for m0 in range(0, M, bm)]
+    p = Program()
+    s = p.stage(tiles, link=(where == "cpu"))
+    run_program(fab, p, s, caps=(4,))
+    ref = x.float() @ w[e].float().t() + res.float()
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.05 * ref.abs().max().item(), err
+    rel = float((out.float() - ref).norm() / ref.norm())
+    assert rel < 1e-2, rel
+    del keep
+
+
+@pytest.mark.parametrize("where", ["hbm", "cpu"])
+def test_expert_ffn(fab, where):
+    """w13 tiles with the SiLU-and-multiply epilogue, then w2 tiles that add
+    routing-weighted outputs into the tokens' fp32 accumulators; the w2 stage
+    depends on the w13 stage through the program's DAG."""
+    torch.manual_seed(1)
+    E, H, I, T, TOPK = 8, 512, 256, 64, 2
+    w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device="cuda") * 0.05).to(torch.bfloat16)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    topk = torch.stack([torch.randperm(E, device="cuda")[:TOPK] for _ in range(T)])
+    tw = torch.rand(T, TOPK, device="cuda")
+    pairs = sorted((int(topk[t, k]), t, float(tw[t, k])) for t in range(T) for k in range(TOPK))
+    xp = torch.zeros(len(pairs) + 64, H, device="cuda", dtype=torch.bfloat16)
+    xp[:len(pairs)] = torch.stack([x[t] for _, t, _ in pairs])
+    ptok = torch.tensor([t for _, t, _ in pairs], dtype=torch.int32, device="cuda")
+    pw = torch.tensor([wt for _, _, wt in pairs], dtype=torch.float32, device="cuda")
+    starts = {}
+    for i, (e, _, _) in enumerate(pairs):
+        starts.setdefault(e, [i, 0])[1] += 1
+    hbuf = torch.zeros(len(pairs) + 64, I, device="cuda", dtype=torch.bfloat16)
+    out32 = torch.zeros(T, H, device="cuda", dtype=torch.float32)
+    if where == "cpu":
+        k1, b13 = pinned_alias(w13)
+        k2, b2 = pinned_alias(w2)
+    else:
+        k1 = k2 = None
+        b13, b2 = w13.data_ptr(), w2.data_ptr()
+    bm = 16
+    a13 = args_tensor(out=hbuf.data_ptr(), ld_out=I, k_tiles=H // 64, epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I)
+    a2 = args_tensor(out=out32.data_ptr(), ld_out=H, k_tiles=I // 64, epi=EPI_WADD, bm=bm, n_limit=H,
+                     pair_token=ptok.data_ptr(), pair_weight=pw.data_ptr())
+    m13, m2 = weight_map(fab, b13, w13.shape), weight_map(fab, b2, w2.shape)
+    mx, mh = act_map(fab, xp, bm), act_map(fab, hbuf, bm)
+    t13, t2 = [], []
+    for e, (s0, cnt) in starts.items():
+        for m0 in range(s0, s0 + cnt, bm):
+            mv = min(bm, s0 + cnt - m0)
+            t13 += [Tile(KIND_GEMM, i=(f0, m0, mv, e), a=(a13.data_ptr(), m13, mx)) for f0 in range(0, I, 64)]
+            t2 += [Tile(KIND_GEMM, i=(n0, m0, mv, e), a=(a2.data_ptr(), m2, mh)) for n0 in range(0, H, 128)]
+    p = Program()
+    s13 = p.stage(t13, link=(where == "cpu"))
+    s2 = p.stage(t2, link=(where == "cpu"))
+    p.after(s13, s2)
+    run_program(fab, p, s13, caps=(8,))
+    ref = torch.zeros(T, H, device="cuda")
+    for t in range(T):
+        for k in range(TOPK):
+            e = int(topk[t, k])
+            g = x[t].float() @ w13[e, :I].float().t()
+            u = x[t].float() @ w13[e, I:].float().t()
+            hh = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).float()
+            ref[t] += float(tw[t, k]) * (hh @ w2[e].float().t())
+    err = (out32 - ref).abs().max().item()
+    assert err < 0.03 * ref.abs().max().item(), err
+    assert float((out32 - ref).norm() / ref.norm()) < 1e-2
+    del k1, k2
+
+
+@pytest.mark.parametrize("bm", [16, 64])
+def test_dense_split_k(fab, bm):
+    """A K-split GEMM: every tile takes one K range and adds its partial sums into an
+    fp32 output, the tile of the first range with the bias."""
+    torch.manual_seed(5)
+    E, N, K, M = 2, 256, 1024, 40
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    x = torch.randn(M + 64, K, device="cuda").to(torch.bfloat16)[:M]
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    e = 1
+    args = args_tensor(out=out.data_ptr(), ld_out=N, k_tiles=K // 64, epi=EPI_ATOMIC, bm=bm, n_limit=N,
+                       bias=bias.data_ptr())
+    wm, xm = weight_map(fab, w.data_ptr(), w.shape), act_map(fab, x, bm)
+    ranges = [(0, 5), (5, 5), (10, 6)]   # uneven ranges over the 16 K tiles
+    tiles = [Tile(KIND_GEMM, i=(n0, m0, min(bm, M - m0), e), a=(args.data_ptr(), wm, xm, k0 | (kn << 16)))
+             for n0 in range(0, N, 128) for m0 in range(0, M, bm) for k0, kn in ranges]
+    p = Program()
+    s = p.stage(tiles)
+    run_program(fab, p, s)
+    ref = x.float() @ w[e].float().t() + bias.float()
+    assert (out - ref).abs().max().item() < 0.02 * ref.abs().max().item()
+
+
+def test_unsupported_gemm_tile_is_reported(fab):
+    """An FP8 tile (needs the converter warps of the stand-alone kernel) and a bad tile
+    height are reported through the error word; the program still ends."""
+    z = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    args = args_tensor(out=z.data_ptr(), ld_out=64, k_tiles=1, epi=EPI_STORE, bm=24, n_limit=64)
+    xm = act_map(fab, z, 16)
+    p = Program()
+    s = p.stage([Tile(KIND_GEMM, i=(0, 0, 16, 0), a=(args.data_ptr(), xm, xm))])
+    h = p.upload(fab, first=s)
+    fab.start()
+    fab.publish(map=[0] * fab.num_workers, caps=[0], order=[0], programs=[h])
+    t0 = time.time()
+    while fab.progress()["lanes"][0]["iterations"] < 1:
+        assert time.time() - t0 < 30
+        time.sleep(1e-3)
+    fab.stop()
+    assert fab.progress()["error"] & 8
