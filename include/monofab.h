@@ -105,6 +105,20 @@ int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w
                     void* x_bf16, const void* norm_w_bf16, void* normed_bf16, int T, int K, int H, float eps,
                     void* stream);
 
+/* Paged-KV GQA attention for prefill and decode rows, head_dim 128: the attention
+ * tiles (csrc/fabric/tiles/attention.cuh:174-395, AttnArgs csrc/fabric/model_types.h:68-96).
+ * q / out bf16 [tokens][hq][128]; k_cache, v_cache bf16 [n_pages][page_size][hkv][128]
+ * (monoserve/runtime/kv.py:8-11, with the page size a parameter: 8..128, dividing 128);
+ * block_table int32 [requests][bt_stride]; scale_log2 = log2(e) / sqrt(128).
+ * items int32 [n_items][8] on the device, one work item per (request, KV head, block of
+ * query tokens): {block-table row, kv head, first query token, query tokens
+ * (<= 128 / (hq / hkv)), position of the first query token, keys visible to the
+ * request, 0, 0}; a decode row is an item with one query token.  `status` is a device
+ * int32 that receives MONOFAB_STATUS_WAIT_TIMEOUT if a bounded wait ran out. */
+int monofab_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* block_table,
+                      int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
+                      int n_pages, float scale_log2, int32_t* status, void* stream);
+
 /* ---- one MoE layer ------------------------------------------------------- */
 
 typedef struct monofab_moe monofab_moe;

@@ -420,6 +420,47 @@ int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int 
   return MONOFAB_OK;
 }
 
+int monofab_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* block_table,
+                      int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
+                      int n_pages, float scale_log2, int32_t* status, void* stream) {
+  if (!q || !k_cache || !v_cache || !out || !block_table || !status || (n_items > 0 && !items))
+    return fail(MONOFAB_EINVAL, "attention: NULL argument");
+  if (hkv < 1 || hq < hkv || hq % hkv) return fail(MONOFAB_EINVAL, "attention: hq=%d must be a multiple of hkv=%d", hq, hkv);
+  const int group = hq / hkv;
+  if (group > 128) return fail(MONOFAB_EINVAL, "attention: GQA group %d exceeds 128 rows", group);
+  if (page_size < 8 || page_size > 128 || 128 % page_size) return fail(MONOFAB_EINVAL, "attention: page_size=%d must divide 128 and be at least 8", page_size);
+  if (tokens < 1 || n_pages < 1 || n_items < 0 || bt_stride < 1) return fail(MONOFAB_EINVAL, "attention: bad sizes");
+  AttnParams p;
+  std::memset(&p, 0, sizeof p);
+  const int tok_box = 128 / group;
+  {
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(hq), static_cast<uint64_t>(tokens)};
+    const uint64_t strides[2] = {256, static_cast<uint64_t>(hq) * 256};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(group), static_cast<uint32_t>(tok_box)};
+    if (int r = encode_map(&p.q_map, 0, q, 3, dims, strides, box, 128)) return r;
+  }
+  for (int i = 0; i < 2; ++i) {
+    const uint64_t dims[4] = {128, static_cast<uint64_t>(hkv), static_cast<uint64_t>(page_size), static_cast<uint64_t>(n_pages)};
+    const uint64_t strides[3] = {256, static_cast<uint64_t>(hkv) * 256, static_cast<uint64_t>(page_size) * hkv * 256};
+    const uint32_t box[4] = {64, 1, static_cast<uint32_t>(page_size), 1};
+    if (int r = encode_map(i == 0 ? &p.k_map : &p.v_map, 0, i == 0 ? k_cache : v_cache, 4, dims, strides, box, 128)) return r;
+  }
+  p.items = reinterpret_cast<const AttnItem*>(items);
+  p.block_table = block_table;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.scale_log2 = scale_log2;
+  p.bt_stride = bt_stride;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.group = group;
+  p.page = page_size;
+  p.n_items = n_items;
+  p.q_box_rows = tok_box * group;
+  MF_CUDA(launch_attention(p, static_cast<cudaStream_t>(stream)));
+  return MONOFAB_OK;
+}
+
 int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   if (!cfg || !out) return fail(MONOFAB_EINVAL, "moe_create: NULL argument");
   const monofab_moe_config& c = *cfg;

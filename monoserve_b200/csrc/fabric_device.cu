@@ -31,6 +31,7 @@
 #include "gemm_core.cuh"
 #include "operands.h"
 #include "ptx.cuh"
+#include "rowwise.cuh"
 
 namespace mf {
 namespace fab {
@@ -499,6 +500,9 @@ __device__ void trace_tile(unsigned long long base, uint32_t idx, unsigned long 
   atomicAdd(&r->count, 1u);
 }
 
+__device__ void tile_router(const TileDesc& t, int tid);
+__device__ void tile_norm(const TileDesc& t, int tid, bool add);
+
 // tid: index among the exec threads.
 __device__ bool run_core_tile(const WorkSlot& w, int tid, uint32_t worker, unsigned long long* sh_t0) {
   const TileDesc& t = w.tile;
@@ -548,8 +552,89 @@ __device__ bool run_core_tile(const WorkSlot& w, int tid, uint32_t worker, unsig
       }
       __threadfence();
       return true;
+    case kTileRouter:
+      tile_router(t, tid);
+      return true;
+    case kTileRmsNorm:
+      tile_norm(t, tid, false);
+      return true;
+    case kTileAddNorm:
+      tile_norm(t, tid, true);
+      return true;
     default:
       return false;
+  }
+}
+
+// ----------------------------------------------------------- row-wise model tiles
+// Row-wise tiles name rows [i0, i0 + i1); a[0] is the operand block.  One warp per
+// row, the four exec warps striding over the rows.
+
+// Router tile (kind 38, csrc/fabric/tiles/aux.cuh:326-417, RouterArgs): scores,
+// top-K, renormalisation, per-expert counts; the logits row is zeroed once read.
+__device__ void tile_router(const TileDesc& t, int tid) {
+  const RouterArgs& A = *reinterpret_cast<const RouterArgs*>(t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int E = static_cast<int>(A.E), K = static_cast<int>(A.K);
+  if (E < 1 || E > kMaxExperts || K < 1 || K > kMaxTopK) return;
+  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+    int id;
+    float w;
+    route_row(reinterpret_cast<float*>(A.logits) + static_cast<size_t>(r) * E, reinterpret_cast<const float*>(A.bias),
+              E, K, static_cast<int>(A.scoring), static_cast<int>(A.renorm), A.scale, 1, id, w);
+    if (lane < K) {
+      reinterpret_cast<int*>(A.topk_ids)[static_cast<size_t>(r) * K + lane] = id;
+      reinterpret_cast<float*>(A.topk_w)[static_cast<size_t>(r) * K + lane] = w;
+      atomicAdd(reinterpret_cast<int*>(A.counts) + id, 1);
+    }
+  }
+}
+
+// RMSNorm tile (kind 36) and AddNorm tile (kind 41), NormArgs
+// (csrc/fabric/tiles/aux.cuh:124-188): AddNorm first forms x = bf16(x2 + acc), stores
+// it, zeroes the fp32 accumulator rows, then normalises; gather >= 0 copies the
+// normalised row to out2[gather].
+__device__ void tile_norm(const TileDesc& t, int tid, bool add) {
+  const NormArgs& A = *reinterpret_cast<const NormArgs*>(t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int H = static_cast<int>(A.H), n16 = H / 8;
+  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+    const size_t o = static_cast<size_t>(r) * A.ld;
+    uint4* x = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(A.x) + o);
+    float ss = 0.f;
+    if (add) {
+      const uint4* x2 = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(A.x2) + o);
+      float4* acc = reinterpret_cast<float4*>(reinterpret_cast<float*>(A.acc) + static_cast<size_t>(r) * H);
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = lane; c < n16; c += 32) {
+        float f[8];
+        unpack8(x2[c], f);
+        const float4 a0 = acc[2 * c], a1 = acc[2 * c + 1];
+        const float sv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          f[j] = round_bf16(__fadd_rn(f[j], sv[j]));
+          ss = __fmaf_rn(f[j], f[j], ss);
+        }
+        acc[2 * c] = zero;
+        acc[2 * c + 1] = zero;
+        x[c] = pack8(f);
+      }
+    } else {
+      for (int c = lane; c < n16; c += 32) {
+        float f[8];
+        unpack8(x[c], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = __fmaf_rn(f[j], f[j], ss);
+      }
+    }
+    __nv_bfloat16* out2 = nullptr;
+    if (A.gather) {
+      const int gi = reinterpret_cast<const int*>(A.gather)[r];
+      if (gi >= 0) out2 = reinterpret_cast<__nv_bfloat16*>(A.out2) + static_cast<size_t>(gi) * H;
+    }
+    norm_store_row(x, ss, reinterpret_cast<const __nv_bfloat16*>(A.w), reinterpret_cast<__nv_bfloat16*>(A.out) + o,
+                   out2, H, A.eps);
   }
 }
 

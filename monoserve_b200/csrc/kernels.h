@@ -80,6 +80,33 @@ cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
 cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream);
 cudaError_t launch_pack_w13(const void* src, void* dst, int n, int I, int H, int elt_bytes, cudaStream_t stream);
 
+// Paged-KV attention (attention.cu).
+struct AttnItem {
+  int32_t req;        // row of the block table
+  int32_t kv_head;
+  int32_t q_row0;     // first query token (row of q / out)
+  int32_t q_tokens;   // query tokens in this block (q_tokens * group <= 128)
+  int32_t pos0;       // position of the first query token
+  int32_t kv_len;     // keys visible to the request: positions 0 .. kv_len - 1
+  int32_t pad[2];
+};
+
+struct AttnParams {
+  CUtensorMap q_map;    // dims (128, hq, T), box (64, group, tokens per block)
+  CUtensorMap k_map;    // dims (128, hkv, page, pages), box (64, 1, page, 1)
+  CUtensorMap v_map;
+  const AttnItem* items;
+  const int32_t* block_table;
+  __nv_bfloat16* out;   // [T][hq][128]
+  int* status;
+  float scale_log2;     // softmax scale * log2(e)
+  int32_t bt_stride, hq, hkv, group, page, n_items;
+  int32_t q_box_rows;   // rows of the q box: group * tokens per block (the bytes one q copy delivers)
+  int32_t pad;
+};
+
+cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream);
+
 // The stable pack from given routing: ranks -> scan -> pair lists (and, when src
 // is set, the packed rows).  `scratch` holds pack_scratch_bytes(T, E, K) bytes.
 size_t pack_scratch_bytes(int T, int E, int K);

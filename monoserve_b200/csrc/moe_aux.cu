@@ -22,26 +22,9 @@
 
 #include "detmath.cuh"
 #include "kernels.h"
+#include "rowwise.cuh"
 
 namespace mf {
-
-__device__ __forceinline__ void unpack8(const uint4& u, float f[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-__device__ __forceinline__ uint4 pack8(const float f[8]) {
-  uint4 u;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  return u;
-}
 
 // ------------------------------------------------------------ router logits
 // One warp computes the logits of one token against kExpertsPerWarp experts.
@@ -100,91 +83,18 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const bf16* __restri
 __global__ void __launch_bounds__(1024) router_topk_kernel(const RouterParams A) {
   __shared__ int s_ids[kChunkTokens * kMaxTopK];
   __shared__ int s_hist[kMaxExperts];
-  constexpr int kMaxPer = kMaxExperts / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int E = A.E, K = A.K;
   const int r = blockIdx.x * kChunkTokens + warp;
   if (threadIdx.x < kMaxExperts) s_hist[threadIdx.x] = 0;
   if (r < A.T) {
-    float* lg = A.logits + static_cast<size_t>(r) * E;
-    float p[kMaxPer], sel[kMaxPer];
-#pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      const int e = lane + 32 * i;
-      p[i] = e < E ? lg[e] : -1e30f;
-    }
-    if (A.zero_logits) {
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i)
-        if (lane + 32 * i < E) lg[lane + 32 * i] = 0.f;
-    }
-    if (A.scoring == 0) {
-      float mx = -1e30f;
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) mx = fmaxf(mx, p[i]);
-#pragma unroll
-      for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) {
-        p[i] = det_expf(__fsub_rn(p[i], mx));
-        s = __fadd_rn(s, p[i]);
-      }
-      s = warp_sum_xor(s);
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) {
-        p[i] = __fdiv_rn(p[i], s);
-        sel[i] = lane + 32 * i < E ? p[i] : -1e30f;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) {
-        const int e = lane + 32 * i;
-        p[i] = det_sigmoidf(p[i]);
-        sel[i] = e < E ? __fadd_rn(p[i], A.bias ? A.bias[e] : 0.f) : -1e30f;
-      }
-    }
-    int my_id = 0;
-    float my_w = 0.f, wsum = 0.f;
-    for (int k = 0; k < K; ++k) {
-      float bv = -1e30f;
-      int bi = 0x7fffffff;
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) {
-        const int e = lane + 32 * i;
-        if (sel[i] > bv || (sel[i] == bv && e < bi)) {
-          bv = sel[i];
-          bi = e;
-        }
-      }
-#pragma unroll
-      for (int o = 16; o; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
-          bv = ov;
-          bi = oi;
-        }
-      }
-      float mine = 0.f;
-#pragma unroll
-      for (int i = 0; i < kMaxPer; ++i) {
-        if (i == (bi >> 5)) {
-          mine = p[i];
-          if (lane == (bi & 31)) sel[i] = -1e30f;
-        }
-      }
-      const float w = __shfl_sync(0xffffffffu, mine, bi & 31);
-      if (lane == k) {
-        my_id = bi;
-        my_w = w;
-      }
-      wsum = __fadd_rn(wsum, w);
-    }
+    int my_id;
+    float my_w;
+    route_row(A.logits + static_cast<size_t>(r) * E, A.bias, E, K, A.scoring, A.renorm, A.scale, A.zero_logits, my_id,
+              my_w);
     if (lane < K) {
       A.topk_ids[static_cast<size_t>(r) * K + lane] = my_id;
-      A.topk_w[static_cast<size_t>(r) * K + lane] =
-          __fmul_rn(A.renorm ? __fdiv_rn(my_w, wsum) : my_w, A.scale);
+      A.topk_w[static_cast<size_t>(r) * K + lane] = my_w;
       s_ids[warp * K + lane] = my_id;
     }
   }
@@ -425,20 +335,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
     xo[c] = pack8(f);
   }
   if (!A.norm_w) return;
-  // RMSNorm of the row this warp just wrote: out = bf16(bf16(x * inv) * w).
-  ss = warp_sum_xor(ss);
-  const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(ss, static_cast<float>(H)), A.eps));
-  __syncwarp();
-  const uint4* w4 = reinterpret_cast<const uint4*>(A.norm_w);
-  uint4* out = reinterpret_cast<uint4*>(A.normed + static_cast<size_t>(t) * H);
-  for (int c = lane; c < n16; c += 32) {
-    float f[8], g[8];
-    unpack8(xo[c], f);
-    unpack8(w4[c], g);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(round_bf16(__fmul_rn(f[j], inv)), g[j]);
-    out[c] = pack8(f);
-  }
+  norm_store_row(xo, ss, A.norm_w, A.normed + static_cast<size_t>(t) * H, nullptr, H, A.eps);
 }
 
 // ------------------------------------------------------------------ launchers

@@ -1,0 +1,102 @@
+"""Paged-KV GQA attention against dense torch softmax: the scenarios of the
+reference's tests/test_fabric_attention.py:81-168 (prefill with (hq, hkv) in
+{(32, 4), (12, 4)}, lengths 300 / 777, shuffled pages; decode lengths 100 / 513 /
+1000), with the page size as a parameter (16 and 64) and the GLM head layout (96, 8).
+Tolerance: the reference's, absolute error < 2e-2."""
+import pytest
+import torch
+
+from oracle import torch_path as tp
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def make_cache(lens, hkv, page, seed):
+    """Shuffled pages; returns k_cache, v_cache [pages, page, hkv, 128], block table, dense k/v per request."""
+    g = torch.Generator().manual_seed(seed)
+    need = [-(-n // page) for n in lens]
+    n_pages = sum(need) + 3
+    perm = torch.randperm(n_pages - 1, generator=g) + 1      # page 0 stays a sink
+    kc = torch.randn(n_pages, page, hkv, 128, generator=g).to(torch.bfloat16)
+    vc = torch.randn(n_pages, page, hkv, 128, generator=g).to(torch.bfloat16)
+    bt = torch.zeros(len(lens), max(need), dtype=torch.int32)
+    dense = []
+    at = 0
+    for r, n in enumerate(lens):
+        pages = perm[at:at + need[r]]
+        at += need[r]
+        bt[r, :need[r]] = pages.to(torch.int32)
+        k = kc[pages].reshape(-1, hkv, 128)[:n]
+        v = vc[pages].reshape(-1, hkv, 128)[:n]
+        dense.append((k.float(), v.float()))
+    return kc, vc, bt, dense
+
+
+def dense_reference(q, k, v, hq, hkv, pos0):
+    """q [n, hq, 128] at positions pos0 .. pos0 + n - 1 over keys 0 .. len(k) - 1 (causal)."""
+    n, L = q.shape[0], k.shape[0]
+    kk, vv = k.repeat_interleave(hq // hkv, 1), v.repeat_interleave(hq // hkv, 1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) / 128 ** 0.5
+    qpos = pos0 + torch.arange(n)
+    mask = torch.arange(L)[None, :] > qpos[:, None]
+    s = s.masked_fill(mask[None], float("-inf"))
+    return tp.bf(torch.einsum("hqk,khd->qhd", s.softmax(-1), vv))
+
+
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("hq,hkv", [(32, 4), (12, 4), (96, 8)])
+def test_prefill(hq, hkv, page):
+    from monoserve_b200.attention import paged_attention
+    lens = [300, 777]
+    kc, vc, bt, dense = make_cache(lens, hkv, page, seed=hq + page)
+    g = torch.Generator().manual_seed(1)
+    T = sum(lens)
+    q = torch.randn(T, hq, 128, generator=g).to(torch.bfloat16)
+    req_info, row = [], 0
+    for n in lens:
+        req_info.append((row, 0, n, n))
+        row += n
+    out = paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), req_info).float().cpu()
+    row = 0
+    for r, n in enumerate(lens):
+        ref = dense_reference(q[row:row + n].float(), dense[r][0], dense[r][1], hq, hkv, 0)
+        err = (out[row:row + n] - ref).abs().max().item()
+        assert err < TOL, (r, err)
+        row += n
+
+
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("hq,hkv", [(32, 4), (96, 8)])
+def test_decode_and_chunked_prefill(hq, hkv, page):
+    """Decode rows (one query token at the end of contexts of 100 / 513 / 1000 keys) mixed
+    with a prefill chunk that continues a request at position 200."""
+    from monoserve_b200.attention import paged_attention
+    lens = [100, 513, 1000, 260]
+    kc, vc, bt, dense = make_cache(lens, hkv, page, seed=7 + page)
+    g = torch.Generator().manual_seed(2)
+    rows = [1, 1, 1, 60]                      # the last request prefills positions 200 .. 259
+    T = sum(rows)
+    q = torch.randn(T, hq, 128, generator=g).to(torch.bfloat16)
+    req_info, row = [], 0
+    for n, L in zip(rows, lens):
+        req_info.append((row, L - n, n, L))
+        row += n
+    out = paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), req_info).float().cpu()
+    row = 0
+    for r, (n, L) in enumerate(zip(rows, lens)):
+        ref = dense_reference(q[row:row + n].float(), dense[r][0], dense[r][1], hq, hkv, L - n)
+        err = (out[row:row + n] - ref).abs().max().item()
+        assert err < TOL, (r, err)
+        row += n
+
+
+def test_attention_rejects_bad_shapes():
+    from monoserve_b200 import _C
+    z = torch.zeros(8, device="cuda", dtype=torch.int32)
+    rc = _C.lib.monofab_attention(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, z.data_ptr(),
+                                  1, 1, 12, 5, 16, 1, 1.0, z.data_ptr(), None)
+    assert rc == -1 and b"multiple of hkv" in _C.lib.monofab_last_error()
+    rc = _C.lib.monofab_attention(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, z.data_ptr(),
+                                  1, 1, 8, 4, 24, 1, 1.0, z.data_ptr(), None)
+    assert rc == -1 and b"page_size" in _C.lib.monofab_last_error()
