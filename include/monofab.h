@@ -302,6 +302,11 @@ int monofab_fabric_iteration_times(monofab_fabric* f, int lane, uint64_t start, 
 int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* dims, const uint64_t* strides_bytes,
                               const uint32_t* box, int rank, int dtype, int swizzle, uint64_t* handle);
 
+/* Marks the weight tensor behind a map record as stored in the packed SwiGLU row
+ * order (monofab_pack_w13), so its SwiGLU tiles load one 128-row box.  No
+ * counterpart in the reference, whose weights have one row order. */
+int monofab_fabric_tensor_map_packed(monofab_fabric* f, uint64_t handle, int packed);
+
 #ifdef __cplusplus
 }
 #endif

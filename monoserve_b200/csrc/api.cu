@@ -329,6 +329,8 @@ const std::string& layouts_json() {
     MF_JSON_STRUCT(PermuteArgs, MF_PERMUTE_ARGS)
     MF_JSON_STRUCT(SampleArgs, MF_SAMPLE_ARGS)
     MF_JSON_STRUCT(AttnPlanArgs, MF_ATTN_PLAN_ARGS)
+    MF_JSON_STRUCT(LogitsArgs, MF_LOGITS_ARGS)
+    MF_JSON_STRUCT(CombineArgs, MF_COMBINE_ARGS)
     s += "}";
     return s;
   }();

@@ -103,9 +103,10 @@ struct WorkSlot {
 // (csrc/fabric/model_types.h:37-49): a[0] GemmArgs*, a[1] weight map record,
 // a[2] activation map record, a[3] K range = first K tile | K tiles << 16 (0 = all),
 // a[4] fp32 scale per weight row; i0 first weight row, i1 first activation row,
-// i2 valid activation rows, i3 weight z (expert or slot).  A map record is three
-// CUtensorMaps (monofab_fabric_tensor_map): [0] the caller's box, [1] box
-// (64, 16, 1), [2] box (64, 128, 1).
+// i2 valid activation rows, i3 weight z (expert or slot).  A map record is four
+// 128-byte slots (monofab_fabric_tensor_map): [0] the caller's box, [1] box
+// (64, 16, 1), [2] box (64, 128, 1), [3] flags: word 0 = 1 when a w13 tensor is
+// stored in the packed SwiGLU row order (monofab_pack_w13).
 __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   GemmArgs A;
   const uint4* src = reinterpret_cast<const uint4*>(t.a[0]);
@@ -117,7 +118,8 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   const CUtensorMap* wrec = reinterpret_cast<const CUtensorMap*>(t.a[1]);
   const CUtensorMap* xrec = reinterpret_cast<const CUtensorMap*>(t.a[2]);
   const bool silu = A.epi == kEpiSiluMul;
-  w.a_map = silu ? wrec + 1 : wrec + 2;
+  const bool packed = silu && __ldcg(reinterpret_cast<const unsigned int*>(wrec + 3)) != 0;
+  w.a_map = (silu && !packed) ? wrec + 1 : wrec + 2;
   w.b_map = xrec;
   w.out = reinterpret_cast<void*>(A.out);
   w.scale = reinterpret_cast<const float*>(t.a[4]);
@@ -139,10 +141,10 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   w.ld_res = A.ld_res;
   w.n_limit = A.n_limit;
   w.valid = 1;
-  w.a_packed = 0;
+  w.a_packed = packed;
   w.block = -1;
   w.w_fp8 = 0;
-  return w.k_tiles > 0 && A.epi <= kEpiAtomicF32;
+  return w.k_tiles > 0 && A.epi <= kEpiRowsF32;
 }
 
 __device__ void trace_stage(DeviceState& S, uint32_t lane, uint32_t s, uint32_t event, uint32_t tag) {
@@ -502,9 +504,13 @@ __device__ void trace_tile(unsigned long long base, uint32_t idx, unsigned long 
 
 __device__ void tile_router(const TileDesc& t, int tid);
 __device__ void tile_norm(const TileDesc& t, int tid, bool add);
+__device__ void tile_router_logits(const TileDesc& t, int tid);
+__device__ void tile_permute(const TileDesc& t, int tid);
+__device__ void tile_combine(const TileDesc& t, int tid);
+__device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid);
 
 // tid: index among the exec threads.
-__device__ bool run_core_tile(const WorkSlot& w, int tid, uint32_t worker, unsigned long long* sh_t0) {
+__device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32_t worker, unsigned long long* sh_t0) {
   const TileDesc& t = w.tile;
   switch (t.kind) {
     case kTileNop:
@@ -555,6 +561,18 @@ __device__ bool run_core_tile(const WorkSlot& w, int tid, uint32_t worker, unsig
     case kTileRouter:
       tile_router(t, tid);
       return true;
+    case kTileRouterLogits:
+      tile_router_logits(t, tid);
+      return true;
+    case kTilePermute:
+      tile_permute(t, tid);
+      return true;
+    case kTileCombine:
+      tile_combine(t, tid);
+      return true;
+    case kTileExpand:
+      tile_expand(t, w.prog, S, tid);
+      return true;
     case kTileRmsNorm:
       tile_norm(t, tid, false);
       return true;
@@ -572,11 +590,21 @@ __device__ bool run_core_tile(const WorkSlot& w, int tid, uint32_t worker, unsig
 
 // Router tile (kind 38, csrc/fabric/tiles/aux.cuh:326-417, RouterArgs): scores,
 // top-K, renormalisation, per-expert counts; the logits row is zeroed once read.
+// With chunk_counts / pair_rank set (fields this library adds) the tile must cover
+// one chunk of kFabChunk rows starting at a multiple of kFabChunk; it then also
+// writes the stable rank of every (token, pick) pair inside (chunk, expert) and the
+// chunk's per-expert pair counts, which make the pack order deterministic.
 __device__ void tile_router(const TileDesc& t, int tid) {
+  __shared__ int s_ids[kFabChunk * kMaxTopK];
+  __shared__ int s_hist[kMaxExperts];
   const RouterArgs& A = *reinterpret_cast<const RouterArgs*>(t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int E = static_cast<int>(A.E), K = static_cast<int>(A.K);
   if (E < 1 || E > kMaxExperts || K < 1 || K > kMaxTopK) return;
+  const bool ranks = A.chunk_counts != 0 && A.pair_rank != 0 && t.i1 <= kFabChunk;
+  if (ranks) {
+    for (int e = tid; e < kMaxExperts; e += kExecThreads) s_hist[e] = 0;
+  }
   for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
     int id;
     float w;
@@ -585,9 +613,302 @@ __device__ void tile_router(const TileDesc& t, int tid) {
     if (lane < K) {
       reinterpret_cast<int*>(A.topk_ids)[static_cast<size_t>(r) * K + lane] = id;
       reinterpret_cast<float*>(A.topk_w)[static_cast<size_t>(r) * K + lane] = w;
-      atomicAdd(reinterpret_cast<int*>(A.counts) + id, 1);
+      if (A.counts) atomicAdd(reinterpret_cast<int*>(A.counts) + id, 1);
+      if (ranks) s_ids[(r - t.i0) * K + lane] = id;
     }
   }
+  if (!ranks) return;
+  exec_sync();
+  const int pairs = static_cast<int>(t.i1) * K;
+  int* pair_rank = reinterpret_cast<int*>(A.pair_rank) + static_cast<size_t>(t.i0) * K;
+  for (int p = tid; p < pairs; p += kExecThreads) {
+    const int me = s_ids[p];
+    int rank = 0;
+    for (int q = 0; q < p; ++q) rank += s_ids[q] == me;
+    pair_rank[p] = rank;
+    atomicAdd(&s_hist[me], 1);
+  }
+  exec_sync();
+  int* cc = reinterpret_cast<int*>(A.chunk_counts) + static_cast<size_t>(t.i0 / kFabChunk) * E;
+  for (int e = tid; e < E; e += kExecThreads) cc[e] = s_hist[e];
+}
+
+// Router projection tile (kind 48; not in the reference, whose router GEMM sums
+// K-split partials with atomics): logits[t][e] for rows [i0, i0 + i1) and all
+// experts, lane l summing h = 256 j + 8 l + i in order with fmaf, then the xor
+// butterfly: the same bits as the stream kernel and the oracle.
+__device__ void tile_router_logits(const TileDesc& t, int tid) {
+  const LogitsArgs& A = *reinterpret_cast<const LogitsArgs*>(t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int H = static_cast<int>(A.H), E = static_cast<int>(A.E), nj = H / 256;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(A.x);
+  const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(A.wr);
+  float* logits = reinterpret_cast<float*>(A.logits);
+  // unit = (row, group of 16 experts); the four warps stride over the units
+  const int groups = (E + 15) / 16;
+  for (int u = warp; u < static_cast<int>(t.i1) * groups; u += kExecThreads / 32) {
+    const int r = t.i0 + u / groups, eg = u % groups;
+    const uint4* x4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
+    for (int e = eg * 16; e < min(E, eg * 16 + 16); ++e) {
+      const uint4* w4 = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * H);
+      float acc = 0.f;
+      for (int j = 0; j < nj; ++j) {
+        float xf[8], wf[8];
+        unpack8(x4[32 * j + lane], xf);
+        unpack8(__ldg(w4 + 32 * j + lane), wf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = __fmaf_rn(xf[i], wf[i], acc);
+      }
+      acc = warp_sum_xor(acc);
+      if (lane == (e & 31)) logits[static_cast<size_t>(r) * E + e] = acc;
+    }
+  }
+}
+
+// Permute tile (kind 40, csrc/fabric/tiles/aux.cuh:648-684, PermuteArgs) for rows
+// [i0, i0 + i1) of one chunk: pair lists and expert-sorted activation rows.  With
+// pair_rank / chunk_prefix set the position is starts[e] + chunk prefix + rank
+// (token ascending, pick ascending); otherwise the reference's arrival order through
+// atomicAdd(fill[e]).  pair_pos (optional) receives the packed row of every pair.
+__device__ void tile_permute(const TileDesc& t, int tid) {
+  const PermuteArgs& A = *reinterpret_cast<const PermuteArgs*>(t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int K = static_cast<int>(A.K), H = static_cast<int>(A.H), E = static_cast<int>(A.E), n16 = H / 8;
+  const int* ids = reinterpret_cast<const int*>(A.topk_ids);
+  const float* tw = reinterpret_cast<const float*>(A.topk_w);
+  const int* starts = reinterpret_cast<const int*>(A.starts);
+  const bool stable = A.pair_rank != 0 && A.chunk_prefix != 0;
+  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+    int pos = 0;
+    if (lane < K) {
+      const int e = ids[static_cast<size_t>(r) * K + lane];
+      if (stable)
+        pos = starts[e] + reinterpret_cast<const int*>(A.chunk_prefix)[static_cast<size_t>(r / kFabChunk) * E + e] +
+              reinterpret_cast<const int*>(A.pair_rank)[static_cast<size_t>(r) * K + lane];
+      else
+        pos = starts[e] + atomicAdd(reinterpret_cast<int*>(A.fill) + e, 1);
+      reinterpret_cast<int*>(A.pair_token)[pos] = r;
+      reinterpret_cast<float*>(A.pair_weight)[pos] = tw[static_cast<size_t>(r) * K + lane];
+      if (A.pair_pos) reinterpret_cast<int*>(A.pair_pos)[static_cast<size_t>(r) * K + lane] = pos;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(A.src) + static_cast<size_t>(r) * H);
+    for (int c = lane; c < n16; c += 32) {
+      const uint4 v = src[c];
+      for (int k = 0; k < K; ++k) {
+        const int pk = __shfl_sync(0xffffffffu, pos, k);
+        reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(A.dst) + static_cast<size_t>(pk) * H)[c] = v;
+      }
+    }
+  }
+}
+
+// Combine tile (kind 47; not in the reference, which adds with fp32 atomics in the
+// w2 epilogue and finishes in AddNorm): x[t] = bf16(x2[t] + sum_k w[t][k] * y[pos(t,k)])
+// with the sum in pick order, then optionally out = rmsnorm(x) * w.
+__device__ void tile_combine(const TileDesc& t, int tid) {
+  const CombineArgs& A = *reinterpret_cast<const CombineArgs*>(t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const int K = static_cast<int>(A.K), H = static_cast<int>(A.H), n16 = H / 8;
+  const float* y = reinterpret_cast<const float*>(A.y);
+  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+    int pos = 0;
+    float w = 0.f;
+    if (lane < K) {
+      pos = reinterpret_cast<const int*>(A.pair_pos)[static_cast<size_t>(r) * K + lane];
+      w = reinterpret_cast<const float*>(A.topk_w)[static_cast<size_t>(r) * K + lane];
+    }
+    const uint4* x2 = A.x2 ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(A.x2) + static_cast<size_t>(r) * H) : nullptr;
+    uint4* xo = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(A.x) + static_cast<size_t>(r) * H);
+    float ss = 0.f;
+    for (int c = lane; c < n16; c += 32) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int pk = __shfl_sync(0xffffffffu, pos, k);
+        const float wk = __shfl_sync(0xffffffffu, w, k);
+        const float4* yr = reinterpret_cast<const float4*>(y + static_cast<size_t>(pk) * H) + 2 * c;
+        const float4 a = __ldcs(yr), b = __ldcs(yr + 1);
+        const float yv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wk, yv[j], acc[j]);
+      }
+      float f[8];
+      if (x2) {
+        unpack8(x2[c], f);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[j] = round_bf16(__fadd_rn(f[j], acc[j]));
+        ss = __fmaf_rn(f[j], f[j], ss);
+      }
+      xo[c] = pack8(f);
+    }
+    if (A.w)
+      norm_store_row(xo, ss, reinterpret_cast<const __nv_bfloat16*>(A.w),
+                     reinterpret_cast<__nv_bfloat16*>(A.out) + static_cast<size_t>(r) * H, nullptr, H, A.eps);
+  }
+}
+
+// Expand tile (kind 39, csrc/fabric/tiles/aux.cuh:453-616, ExpandArgs), one per lane
+// and MoE layer: per-expert counts -> exclusive prefix sums, then for every routed
+// expert the GEMM tiles of its w13 and w2 stages, written into the program's dynamic
+// region, with the stage records (first, count, link flag); unrouted experts are
+// flagged kStageSkip and taken off the join stage's dependency count.  Differences
+// from the reference: counts may come from the router tiles' chunk counts (then the
+// per-chunk prefixes are produced too, for the stable pack); form 0 maps to 256-row
+// blocks (one pass over the weights) instead of K-split tiles with a reduce stage;
+// an overflow of the dynamic region raises an error bit instead of trapping.
+__device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid) {
+  __shared__ int s_cnt[kMaxExperts], s_start[kMaxExperts + 1], s_n[kMaxExperts], s_off[kMaxExperts + 1];
+  __shared__ int s_form, s_active, s_skipped, s_overflow;
+  const ExpandArgs& A = *reinterpret_cast<const ExpandArgs*>(t.a[0]);
+  const int E = static_cast<int>(A.E);
+  if (E < 1 || E > kMaxExperts) return;
+  int* counts = reinterpret_cast<int*>(A.counts);
+  int* starts = reinterpret_cast<int*>(A.starts);
+  for (int e = tid; e < E; e += kExecThreads) {
+    int cnt = 0;
+    if (A.chunk_counts) {
+      int* cc = reinterpret_cast<int*>(A.chunk_counts);
+      for (uint32_t c = 0; c < A.chunks; ++c) {
+        const int v = cc[static_cast<size_t>(c) * E + e];
+        cc[static_cast<size_t>(c) * E + e] = cnt;   // exclusive prefix over the chunks
+        cnt += v;
+      }
+    } else {
+      cnt = counts[e];
+    }
+    s_cnt[e] = cnt;
+  }
+  if (tid == 0) {
+    s_skipped = 0;
+    s_overflow = 0;
+    unsigned long long ep = ld_acq(&S.published);
+    uint32_t f;
+    for (;;) {
+      f = ld_volatile(&S.snap[ep & 1].form[A.lane & 3]);
+      const unsigned long long e2 = ld_acq(&S.published);
+      if (e2 == ep) break;
+      ep = e2;
+    }
+    s_form = (f == 0 || f == 16 || f == 32 || f == 64 || f == 128) ? static_cast<int>(f) : 64;
+  }
+  exec_sync();
+  auto scan = [&](const int* v, int* out) {   // exclusive prefix sums by thread 0 (E <= 256)
+    if (tid == 0) {
+      int run = 0, act = 0;
+      for (int e = 0; e < E; ++e) {
+        out[e] = run;
+        run += v[e];
+        act += v[e] != 0;
+      }
+      out[E] = run;
+      s_active = act;
+    }
+  };
+  scan(s_cnt, s_start);
+  exec_sync();
+  const int active = s_active;
+  for (int e = tid; e <= E; e += kExecThreads) starts[e] = s_start[e];
+  const int* table = reinterpret_cast<const int*>(A.table);
+  const int f13 = static_cast<int>(A.I) / 64, f2 = static_cast<int>(A.H) / 128;
+  auto block_rows = [&](int M, bool link) {
+    if (link) return s_form ? s_form : 256;
+    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  };
+  for (int e = tid; e < E; e += kExecThreads) {
+    const int M = s_cnt[e];
+    const bool link = table[2 * e] == static_cast<int>(A.host_region);
+    const int bm = block_rows(M, link);
+    s_n[e] = M > 0 ? ((M + bm - 1) / bm) * (f13 + f2) : 0;
+  }
+  exec_sync();
+  scan(s_n, s_off);
+  // close the expert stages' previous activation before their tiles and counts change
+  for (int e = tid; e < E; e += kExecThreads) {
+    atomicExch(&P->runtime[A.w13_stage0 + e].tag_next, 0ull);
+    atomicExch(&P->runtime[A.red_stage0 + e].tag_next, 0ull);
+    atomicExch(&P->runtime[A.w2_stage0 + e].tag_next, 0ull);
+  }
+  __threadfence();
+  exec_sync();
+  if (s_off[E] > static_cast<int>(A.dyn_cap)) {
+    if (tid == 0) raise_error(S, kFabErrDynOverflow);
+    s_overflow = 1;   // every thread writes the same value
+  }
+  exec_sync();
+  const unsigned long long* w13_args = reinterpret_cast<const unsigned long long*>(A.w13_args);
+  const unsigned long long* w2_args = reinterpret_cast<const unsigned long long*>(A.w2_args);
+  const unsigned long long* xp_maps = reinterpret_cast<const unsigned long long*>(A.xp_maps);
+  const unsigned long long* h_maps = reinterpret_cast<const unsigned long long*>(A.h_maps);
+  const unsigned long long* w13_maps = reinterpret_cast<const unsigned long long*>(A.w13_maps);
+  const unsigned long long* w2_maps = reinterpret_cast<const unsigned long long*>(A.w2_maps);
+  for (int e = tid; e < E; e += kExecThreads) {
+    const int M = s_overflow ? 0 : s_cnt[e];
+    const int region = table[2 * e], slot = table[2 * e + 1];
+    const bool link = region == static_cast<int>(A.host_region);
+    const uint32_t base = A.dyn_first + s_off[e];
+    StageStatic& s13 = P->stages[A.w13_stage0 + e];
+    StageStatic& sr = P->stages[A.red_stage0 + e];
+    StageStatic& s2 = P->stages[A.w2_stage0 + e];
+    const int bm = block_rows(M, link);
+    int cls = 0;
+    while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
+    const int blocks = M > 0 ? (M + bm - 1) / bm : 0;
+    const int n13 = blocks * f13, n2 = blocks * f2;
+    TileDesc d{};
+    d.kind = kTileGemm;
+    uint32_t k = base;
+    for (int b = 0; b < blocks; ++b) {
+      d.i1 = s_start[e] + b * bm;
+      d.i2 = min(bm, M - b * bm);
+      d.i3 = slot;
+      d.a[0] = w13_args[cls];
+      d.a[1] = w13_maps[region];
+      d.a[2] = xp_maps[cls];
+      d.a[4] = A.w13_scale ? A.w13_scale + static_cast<unsigned long long>(e) * 2 * A.I * 4 : 0;
+      for (int f = 0; f < f13; ++f) {
+        d.i0 = f * 64;
+        P->tiles[k++] = d;
+      }
+    }
+    for (int b = 0; b < blocks; ++b) {
+      d.i1 = s_start[e] + b * bm;
+      d.i2 = min(bm, M - b * bm);
+      d.i3 = slot;
+      d.a[0] = w2_args[cls];
+      d.a[1] = w2_maps[region];
+      d.a[2] = h_maps[cls];
+      d.a[4] = A.w2_scale ? A.w2_scale + static_cast<unsigned long long>(e) * A.H * 4 : 0;
+      for (int n = 0; n < f2; ++n) {
+        d.i0 = n * 128;
+        P->tiles[k++] = d;
+      }
+    }
+    s13.first = base;
+    s13.count = n13;
+    s13.flags = link ? kStageLink : 0u;
+    if (M == 0 && active > 0) {   // an unrouted expert: its chain is passed over
+      s13.flags = kStageSkip;
+      atomicAdd(&s_skipped, 1);
+    }
+    sr.first = base + n13;
+    sr.count = 0;
+    sr.flags = 0u;
+    s2.first = base + n13;
+    s2.count = n2;
+    s2.flags = link ? kStageLink : 0u;
+    if (A.hist && M > 0) atomicAdd(reinterpret_cast<int*>(A.hist) + e, M);
+    counts[e] = 0;
+    if (A.fill) reinterpret_cast<int*>(A.fill)[e] = 0;
+  }
+  __threadfence();
+  exec_sync();
+  if (tid == 0 && s_skipped > 0) atomicSub(&P->runtime[A.join_stage].deps, static_cast<unsigned int>(s_skipped));
 }
 
 // RMSNorm tile (kind 36) and AddNorm tile (kind 41), NormArgs
@@ -804,7 +1125,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         if (!gemm_epilogue(w.gemm, sh.bar, tmem_base, g & 1, (g >> 1) & 1, abort_flag) && tid == 0)
           raise_error(S, kFabErrTileWait);
         ++g;
-      } else if (!run_core_tile(w, tid, worker, &sh.t0) && tid == 0) {
+      } else if (!run_core_tile(S, w, tid, worker, &sh.t0) && tid == 0) {
         raise_error(S, kFabErrBadTile);
       }
       exec_sync();

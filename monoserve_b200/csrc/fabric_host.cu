@@ -67,7 +67,7 @@ struct monofab_fabric {
   uint32_t next_gen = 1;
   std::map<uint64_t, ProgramRecord> programs;
   std::map<uint64_t, size_t> blobs;      // device address -> size
-  CUtensorMap* map_table = nullptr;      // device: records of 3 maps each
+  CUtensorMap* map_table = nullptr;      // device: records of 4 slots each
   int map_count = 0, map_cap = 4096;
   uint64_t lane_handle[kMaxLanes] = {0, 0, 0, 0};
 };
@@ -169,7 +169,7 @@ int monofab_fabric_create(int num_workers, int device, size_t pool_bytes, monofa
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&f->state), sizeof(DeviceState));
   if (e == cudaSuccess) e = cudaMemset(f->state, 0, sizeof(DeviceState));
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&f->pool), f->pool_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&f->map_table), sizeof(CUtensorMap) * 3 * f->map_cap);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&f->map_table), sizeof(CUtensorMap) * 4 * f->map_cap);
   if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&f->mirror), sizeof(HostMirror), cudaHostAllocMapped | cudaHostAllocPortable);
   if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&f->staging), f->staging_bytes, cudaHostAllocDefault);
   if (e != cudaSuccess) {
@@ -510,7 +510,7 @@ int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* 
   // Record = three encodings of the same tensor: [0] the caller's box; for rank-3
   // weight tensors also [1] box (64, 16, 1) and [2] box (64, 128, 1), which the
   // B200 GEMM tile uses instead of the 64-row box the reference's tile asks for.
-  CUtensorMap rec[3];
+  CUtensorMap rec[4];   // [3] holds flags (monofab_fabric_tensor_map_packed)
   std::memset(rec, 0, sizeof rec);
   if (int r = encode_map(&rec[0], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, box, swizzle)) return r;
   if (rank == 3) {
@@ -518,11 +518,21 @@ int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* 
     if (int r = encode_map(&rec[1], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b16, swizzle)) return r;
     if (int r = encode_map(&rec[2], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b128, swizzle)) return r;
   }
-  CUtensorMap* dst = f->map_table + 3 * f->map_count;
+  CUtensorMap* dst = f->map_table + 4 * f->map_count;
   if (int r = to_device(f, dst, rec, sizeof rec)) return r;
   ++f->map_count;
   *handle = reinterpret_cast<uint64_t>(dst);
   return MONOFAB_OK;
+}
+
+int monofab_fabric_tensor_map_packed(monofab_fabric* f, uint64_t handle, int packed) {
+  if (!f) return fail(MONOFAB_EINVAL, "fabric_tensor_map_packed: NULL handle");
+  std::lock_guard<std::mutex> lock(f->mu);
+  const uint64_t lo = reinterpret_cast<uint64_t>(f->map_table), hi = reinterpret_cast<uint64_t>(f->map_table + 4 * f->map_count);
+  if (handle < lo || handle >= hi || (handle - lo) % (4 * sizeof(CUtensorMap)))
+    return fail(MONOFAB_EINVAL, "fabric_tensor_map_packed: not a map record of this fabric");
+  const unsigned int flag = packed != 0;
+  return to_device(f, reinterpret_cast<CUtensorMap*>(handle) + 3, &flag, 4);
 }
 
 }  // extern "C"

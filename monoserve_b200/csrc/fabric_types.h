@@ -27,9 +27,13 @@ enum TileKind : uint16_t {
   kTileGemm = 32,
   kTileRmsNorm = 36,
   kTileRouter = 38,
+  kTileExpand = 39,
   kTilePermute = 40,
   kTileAddNorm = 41,
+  kTileCombine = 47,        // not in the reference: un-permute + weighted combine in pick order (+ RMSNorm)
+  kTileRouterLogits = 48,   // not in the reference: router projection with a defined summation order
 };
+constexpr int kFabChunk = 16;   // rows per router / permute tile = rank chunk of the stable pack
 
 enum StageFlags : uint32_t {
   kStageLink = 1u << 0,   // tiles read host memory: taken only under a link slot
@@ -102,6 +106,7 @@ constexpr unsigned long long kFabErrWorklist = 2;     // more simultaneously com
 constexpr unsigned long long kFabErrDeadline = 4;     // the kernel reached its run-time limit and left
 constexpr unsigned long long kFabErrBadTile = 8;      // a tile kind this build does not execute
 constexpr unsigned long long kFabErrTileWait = 16;    // a bounded wait inside a tile ran out
+constexpr unsigned long long kFabErrDynOverflow = 32; // the expander needs more tiles than the dynamic region holds
 
 struct alignas(128) Ring {
   unsigned long long head;

@@ -33,19 +33,19 @@ namespace mf {
 
 #define MF_ROUTER_ARGS(U64, U32, F32) \
   U64(logits) U64(topk_ids) U64(topk_w) U64(counts) U64(bias) U32(E) U32(K) U32(scoring) U32(renorm) \
-  F32(scale)
+  F32(scale) U32(reserved0) U64(chunk_counts) U64(pair_rank)
 
 #define MF_EXPAND_ARGS(U64, U32, F32) \
   U64(counts) U64(starts) U64(fill) U64(table) U64(w13_maps) U64(w2_maps) U64(xp_maps) U64(h_maps) \
   U64(w13_args) U64(w2_args) U64(hist) U64(w13_asym_args) U64(w2_asym_args) U64(red_args) \
   U64(w13_scale) U64(w2_scale) U32(E) U32(H) U32(I) U32(host_region) U32(w13_stage0) U32(w2_stage0) \
-  U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage)
+  U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage) U32(chunks) U64(chunk_counts)
 
 #define MF_REDUCE_ARGS(U64, U32, F32) U64(ws) U64(out) U32(I) U32(ld_ws) U32(ld_out)
 
 #define MF_PERMUTE_ARGS(U64, U32, F32) \
   U64(topk_ids) U64(topk_w) U64(starts) U64(fill) U64(pair_token) U64(pair_weight) U64(src) U64(dst) \
-  U32(K) U32(H)
+  U32(K) U32(H) U64(pair_rank) U64(chunk_prefix) U64(pair_pos) U32(E)
 
 #define MF_SAMPLE_ARGS(U64, U32, F32) \
   U64(logits) U64(temperature) U64(last_token) U64(steps) U64(host_tokens) U64(host_steps) U64(seed) \
@@ -54,6 +54,13 @@ namespace mf {
 #define MF_ATTN_PLAN_ARGS(U64, U32, F32) \
   U64(attn) U64(req_info) U32(rows) U32(hkv) U32(chunk_keys) U32(stage_attn) U32(stage_comb) \
   U32(dyn_first) U32(dyn_cap)
+
+/* Not in the reference: the deterministic router projection and the deterministic
+ * un-permute + weighted combine as fabric tiles. */
+#define MF_LOGITS_ARGS(U64, U32, F32) U64(x) U64(wr) U64(logits) U32(T) U32(H) U32(E)
+
+#define MF_COMBINE_ARGS(U64, U32, F32) \
+  U64(y) U64(pair_pos) U64(topk_w) U64(x2) U64(x) U64(w) U64(out) U32(K) U32(H) F32(eps)
 
 #define MF_FIELD_U64(name) unsigned long long name;
 #define MF_FIELD_U32(name) uint32_t name;
@@ -70,11 +77,13 @@ MF_DECLARE(AttnArgs, MF_ATTN_ARGS, 128)
 MF_DECLARE(NormArgs, MF_NORM_ARGS, 128)
 MF_DECLARE(StepArgs, MF_STEP_ARGS, 64)
 MF_DECLARE(QkArgs, MF_QK_ARGS, 128)
-MF_DECLARE(RouterArgs, MF_ROUTER_ARGS, 64)
+MF_DECLARE(RouterArgs, MF_ROUTER_ARGS, 128)
 MF_DECLARE(ExpandArgs, MF_EXPAND_ARGS, 192)
 MF_DECLARE(ReduceArgs, MF_REDUCE_ARGS, 64)
 MF_DECLARE(PermuteArgs, MF_PERMUTE_ARGS, 128)
 MF_DECLARE(SampleArgs, MF_SAMPLE_ARGS, 64)
 MF_DECLARE(AttnPlanArgs, MF_ATTN_PLAN_ARGS, 64)
+MF_DECLARE(LogitsArgs, MF_LOGITS_ARGS, 64)
+MF_DECLARE(CombineArgs, MF_COMBINE_ARGS, 128)
 
 }  // namespace mf

@@ -154,11 +154,13 @@ class Fabric:
                             kind=(w >> 44) & 0xfff, stage=(w >> 24) & 0xfffff, tile=w & 0xffffff, since_ns=t))
         return out
 
-    def tensor_map(self, base, dims, strides_bytes, box, dtype=0, swizzle=128):
+    def tensor_map(self, base, dims, strides_bytes, box, dtype=0, swizzle=128, packed=False):
         rank = len(dims)
         d = (ctypes.c_uint64 * rank)(*dims)
         s = (ctypes.c_uint64 * max(1, rank - 1))(*strides_bytes)
         b = (ctypes.c_uint32 * rank)(*box)
         h = ctypes.c_uint64()
         self._C.check(self._lib.monofab_fabric_tensor_map(self._h, base, d, s, b, rank, dtype, swizzle, ctypes.byref(h)))
+        if packed:
+            self._C.check(self._lib.monofab_fabric_tensor_map_packed(self._h, h.value, 1))
         return h.value

@@ -1,0 +1,171 @@
+"""Lane programs for the MoE layer: the layer's stage chain as a fabric program.
+
+The reference builds, per layer, router_gemm -> router -> expand -> permute ->
+per expert (w13 -> red -> w2) -> add_norm (monoserve/runtime/lane.py:340-380), with
+the expert stages filled at run time by the expand tile and flagged as link stages
+when the layer's (region, slot) table places the expert in pinned host memory.
+`MoELane` builds the same chain on this library's tiles:
+
+  router_logits (48) -> router (38, with stable ranks) -> expand (39) -> permute (40)
+  -> per expert: w13[e] (GEMM tiles, SiLU-mul) -> red[e] (empty) -> w2[e] (GEMM tiles,
+  fp32 rows) -> combine (47: un-permute + weighted sum in pick order + residual)
+
+All device memory is allocated here, before the fabric starts
+(monoserve/runtime/lane.py:101-122 lists the same workspaces).
+"""
+import torch
+
+from monoserve_b200 import _C
+from monoserve_b200.fabric import Program, Tile, tile_array
+from monoserve_b200.fabric.args import pack
+
+K_GEMM, K_ROUTER, K_EXPAND, K_PERMUTE, K_COMBINE, K_LOGITS = 32, 38, 39, 40, 47, 48
+REGION_HOST, REGION_HOT = 0, 1
+CHUNK = 16
+EPI_SILU_MUL, EPI_ROWS_F32 = 1, 5
+
+
+def _block(name, **fields):
+    return torch.frombuffer(bytearray(pack(name, **fields)), dtype=torch.uint8).cuda()
+
+
+def _u64(values):
+    return torch.tensor([int(v) for v in values], dtype=torch.int64).cuda()
+
+
+def _row_tiles(kind, args, rows, per):
+    return [Tile(kind, i=(r0, min(per, rows - r0)), a=(args.data_ptr(),)) for r0 in range(0, rows, per)]
+
+
+class MoELane:
+    """lane = MoELane(fab, lane_id, H, I, E, K, max_tokens, wr, w13, w2, hot)
+    lane.set_input(xn, x2); h = lane.build(T, iterations=1); fab.publish(..., programs=[h]) ..."""
+
+    def __init__(self, fab, lane_id, hidden, intermediate, experts, top_k, max_tokens, wr, w13, w2, hot,
+                 pack_hot=True):
+        self.fab, self.lane_id = fab, lane_id
+        self.H, self.I, self.E, self.K, self.T = hidden, intermediate, experts, top_k, max_tokens
+        H, I, E, K, T = hidden, intermediate, experts, top_k, max_tokens
+        P = T * K
+        dev = "cuda"
+        self.wr = wr.to(torch.bfloat16).contiguous().cuda()
+        # placement (monoserve/runtime/weights.py:100-143): the full set pinned, the hot experts copied to HBM
+        self.host_w13 = w13 if w13.is_pinned() else w13.contiguous().pin_memory()
+        self.host_w2 = w2 if w2.is_pinned() else w2.contiguous().pin_memory()
+        self.hot = list(hot)
+        idx = torch.tensor(self.hot if self.hot else [0])
+        hot13 = self.host_w13[idx].cuda()
+        if pack_hot:
+            packed = torch.empty_like(hot13)
+            _C.check(_C.lib.monofab_pack_w13(hot13.data_ptr(), packed.data_ptr(), hot13.shape[0], I, H, 2, None))
+            torch.cuda.synchronize()
+            hot13 = packed
+        self.hot_w13, self.hot_w2 = hot13, self.host_w2[idx].cuda()
+        table = torch.zeros(E, 2, dtype=torch.int32)
+        table[:, 1] = torch.arange(E)
+        if self.hot:
+            table[idx, 0] = REGION_HOT
+            table[idx, 1] = torch.arange(len(self.hot), dtype=torch.int32)
+        self.table = table.cuda()
+
+        def wmap(t, base, packed=False):
+            z, rows, k = t.shape
+            return fab.tensor_map(base, [k, rows, z], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
+
+        self.w13_maps = _u64([wmap(self.host_w13, _C.host_device_pointer(self.host_w13.data_ptr())),
+                              wmap(self.hot_w13, self.hot_w13.data_ptr(), packed=pack_hot)])
+        self.w2_maps = _u64([wmap(self.host_w2, _C.host_device_pointer(self.host_w2.data_ptr())),
+                             wmap(self.hot_w2, self.hot_w2.data_ptr())])
+        # workspaces
+        z = lambda *shape, dt=torch.int32: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
+        self.xn, self.x2, self.x = (z(T, H, dt=torch.bfloat16) for _ in range(3))
+        self.logits = z(T, E, dt=torch.float32)
+        self.topk_ids, self.topk_w = z(T, K), z(T, K, dt=torch.float32)
+        self.counts, self.fill, self.starts = z(E), z(E), z(E + 1)
+        self.chunks = -(-T // CHUNK)
+        self.chunk_counts, self.pair_rank = z(self.chunks, E), z(T, K)
+        self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
+        self.xp, self.h = z(P + 256, H, dt=torch.bfloat16), z(P + 256, I, dt=torch.bfloat16)
+        self.y = z(P + 256, H, dt=torch.float32)
+        self.hist = z(E)
+        # operand blocks
+        self.logits_args = None
+        self.router_args = _block("RouterArgs", logits=self.logits, topk_ids=self.topk_ids, topk_w=self.topk_w,
+                                  counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
+                                  chunk_counts=self.chunk_counts, pair_rank=self.pair_rank)
+        self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
+                                   fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
+                                   src=self.xn, dst=self.xp, K=K, H=H, pair_rank=self.pair_rank,
+                                   chunk_prefix=self.chunk_counts, pair_pos=self.pair_pos, E=E)
+        self.combine_args = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2,
+                                   x=self.x, K=K, H=H, eps=0.0)
+        heights = [16, 32, 64, 128, 256]
+        self.xp_maps = _u64([fab.tensor_map(self.xp.data_ptr(), [H, P + 256], [H * 2], [64, bm]) for bm in heights])
+        self.h_maps = _u64([fab.tensor_map(self.h.data_ptr(), [I, P + 256], [I * 2], [64, bm]) for bm in heights])
+        self._gemm_blocks = []
+        a13, a2 = [], []
+        for bm in heights:
+            b13 = torch.frombuffer(bytearray(_C.gemm_args(out=self.h.data_ptr(), ld_out=I, k_tiles=H // 64,
+                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I)),
+                                   dtype=torch.uint8).cuda()
+            b2 = torch.frombuffer(bytearray(_C.gemm_args(out=self.y.data_ptr(), ld_out=H, k_tiles=I // 64,
+                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H)),
+                                  dtype=torch.uint8).cuda()
+            self._gemm_blocks += [b13, b2]
+            a13.append(b13.data_ptr())
+            a2.append(b2.data_ptr())
+        self.w13_args, self.w2_args = _u64(a13), _u64(a2)
+        self._keep = []
+
+    def set_input(self, xn, x2=None):
+        """Copy the batch into the lane's input buffers (before the program runs)."""
+        T = xn.shape[0]
+        self.xn[:T].copy_(xn)
+        if x2 is not None:
+            self.x2[:T].copy_(x2)
+        else:
+            self.x2[:T].zero_()
+
+    def dynamic_tiles(self, T):
+        """Most GEMM tiles the expander can write for T tokens (form 16, ragged tails)."""
+        return (T * self.K // 16 + self.E) * (self.I // 64 + self.H // 128)
+
+    def build(self, T, iterations=1, mark_layer=0):
+        """Upload the one-layer program for a batch of T tokens; returns its handle."""
+        assert 0 < T <= self.T
+        H, E = self.H, self.E
+        nw = self.fab.num_workers
+        p = Program()
+        logits_args = _block("LogitsArgs", x=self.xn, wr=self.wr, logits=self.logits, T=T, H=H, E=E)
+        per_lg = max(1, -(-T // (2 * nw)))
+        s_lg = p.stage(_row_tiles(K_LOGITS, logits_args, T, per_lg), label=("router_logits", mark_layer))
+        s_rt = p.stage(_row_tiles(K_ROUTER, self.router_args, T, CHUNK), label=("router", mark_layer))
+        p.after(s_lg, s_rt)
+        ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
+        s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", mark_layer))
+        p.after(s_rt, s_ex)
+        s_pm = p.stage(_row_tiles(K_PERMUTE, self.permute_args, T, CHUNK), label=("permute", mark_layer))
+        p.after(s_ex, s_pm)
+        w13 = [p.stage(label=("w13", mark_layer)) for _ in range(E)]
+        red = [p.stage(label=("red", mark_layer)) for _ in range(E)]
+        w2 = [p.stage(label=("w2", mark_layer)) for _ in range(E)]
+        per_cb = max(1, -(-T // (2 * nw)))
+        s_cb = p.stage(_row_tiles(K_COMBINE, self.combine_args, T, per_cb), mark=(mark_layer << 8) | 3,
+                       label=("combine", mark_layer))
+        for e in range(E):
+            p.after(s_pm, w13[e])
+            p.after(w13[e], red[e])
+            p.after(red[e], w2[e])
+            p.after(w2[e], s_cb)
+        dyn = self.dynamic_tiles(T)
+        p.reserve(dyn)
+        blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.table,
+                    w13_maps=self.w13_maps, w2_maps=self.w2_maps, xp_maps=self.xp_maps, h_maps=self.h_maps,
+                    w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist, E=E, H=H, I=self.I,
+                    host_region=REGION_HOST, w13_stage0=w13[0], w2_stage0=w2[0], red_stage0=red[0],
+                    dyn_first=p.dynamic_first, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb,
+                    chunks=-(-T // CHUNK), chunk_counts=self.chunk_counts)
+        ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
+        torch.cuda.synchronize()
+        self._keep += [logits_args, ex]
+        return p.upload(self.fab, first=s_lg, iterations=iterations)

@@ -1,0 +1,119 @@
+"""One MoE layer as a fabric program (MoELane): routing / packing bit-exact against
+the oracle, expert outputs within tolerance, the combine exact given y, with half of
+the experts hot and half read from pinned host memory through link-gated stages; then
+a prefill lane and a repeating decode lane side by side on disjoint SM floors
+(the arrangement of the reference's tests/test_fabric_model.py:86-123)."""
+import time
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def weights(H, I, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    wr = (torch.randn(E, H, generator=g) * H ** -0.5).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    return wr, w13, w2
+
+
+def acts(T, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(T, H, generator=g).to(torch.bfloat16), torch.randn(T, H, generator=g).to(torch.bfloat16)
+
+
+def wait_iterations(fab, lane, n, timeout=30):
+    t0 = time.time()
+    while fab.progress()["lanes"][lane]["iterations"] < n:
+        assert time.time() - t0 < timeout, fab.progress()
+        time.sleep(1e-3)
+
+
+def check_lane(lane, wr, w13, w2, xn, x2, K):
+    T, H = xn.shape
+    P = T * K
+    r = oracle.moe_layer(*(oracle.bf16_bits(t) for t in (xn, x2, wr, w13, w2)), K)
+    E, I = wr.shape[0], w13.shape[1] // 2
+    assert np.array_equal(lane.topk_ids[:T].cpu().numpy(), r["topk_ids"])
+    assert np.array_equal(lane.topk_w[:T].cpu().numpy().view(np.int32), r["topk_w"].view(np.int32))
+    assert np.array_equal(lane.starts.cpu().numpy(), r["starts"])
+    assert np.array_equal(lane.pair_token[:P].cpu().numpy(), r["pair_token"])
+    assert np.array_equal(lane.pair_weight[:P].cpu().numpy().view(np.int32), r["pair_weight"].view(np.int32))
+    assert np.array_equal(lane.pair_pos[:T].cpu().numpy(), r["pair_pos"])
+    assert np.array_equal(oracle.bf16_bits(lane.xp[:P]), r["xp"])
+    y = lane.y[:P].cpu()
+    rel = float((y - torch.from_numpy(r["y"])).norm() / torch.from_numpy(r["y"]).norm())
+    assert rel < 1e-2, rel
+    want = oracle.combine(y.numpy(), r["pair_pos"], r["topk_w"], oracle.bf16_bits(x2))
+    assert np.array_equal(oracle.bf16_bits(lane.x[:T]), want)
+    ref = torch.from_numpy(oracle.bits_to_f32(r["out"]))
+    assert float((lane.x[:T].float().cpu() - ref).norm() / ref.norm()) < 1e-2
+    assert int(lane.counts.abs().sum()) == 0, "the expander zeroes the counts for the next layer"
+
+
+@pytest.mark.parametrize("form", [64, 0])
+@pytest.mark.parametrize("pack_hot", [True, False])
+def test_moe_layer_program(form, pack_hot):
+    from monoserve_b200.fabric import Fabric
+    from monoserve_b200.lane import MoELane
+    T, H, I, E, K = 70, 512, 256, 16, 4
+    wr, w13, w2 = weights(H, I, E, 1)
+    xn, x2 = acts(T, H, 2)
+    fab = Fabric(pool_bytes=128 << 20)
+    fab.set_max_run(60)
+    try:
+        lane = MoELane(fab, 0, H, I, E, K, 96, wr, w13, w2, hot=list(range(0, E, 2)), pack_hot=pack_hot)
+        lane.set_input(xn.cuda(), x2.cuda())
+        h = lane.build(T, iterations=2)
+        fab.start()
+        fab.reset_inflight_max(0)
+        fab.publish(map=[0] * fab.num_workers, caps=[4], order=[0], programs=[h], forms=[form])
+        wait_iterations(fab, 0, 2)
+        stats = fab.lane_stats(0)
+        fab.stop()
+        assert fab.progress()["error"] == 0
+        assert 1 <= stats["inflight_max"] <= 4
+        check_lane(lane, wr, w13, w2, xn, x2, K)
+    finally:
+        fab.stop()
+        fab.close()
+
+
+def test_prefill_and_decode_lanes_side_by_side():
+    from monoserve_b200.fabric import Fabric
+    from monoserve_b200.lane import MoELane
+    H, I, E, K = 512, 256, 16, 4
+    wr, w13, w2 = weights(H, I, E, 3)
+    xp_in, xp_res = acts(600, H, 4)
+    xd_in, xd_res = acts(24, H, 5)
+    fab = Fabric(pool_bytes=256 << 20)
+    fab.set_max_run(60)
+    try:
+        hot = list(range(8))
+        pre = MoELane(fab, 0, H, I, E, K, 600, wr, w13, w2, hot=hot)
+        dec = MoELane(fab, 1, H, I, E, K, 32, wr, w13, w2, hot=hot)
+        pre.set_input(xp_in.cuda(), xp_res.cuda())
+        dec.set_input(xd_in.cuda(), xd_res.cuda())
+        hp = pre.build(600, iterations=3)
+        hd = dec.build(24, iterations=0)      # the decode lane repeats until replaced
+        n = fab.num_workers
+        lanes = [0] * (n // 2) + [1] * (n - n // 2)
+        fab.start()
+        fab.publish(map=lanes, caps=[8, 4], order=[0, 1], programs=[hp, hd], forms=[64, 64])
+        ends = fab.iteration_times(1, 0, 6, timeout=30)
+        wait_iterations(fab, 0, 3)
+        fab.stop()
+        assert fab.progress()["error"] == 0
+        assert all(b > a for a, b in zip(ends, ends[1:]))
+        check_lane(pre, wr, w13, w2, xp_in, xp_res, K)
+        # the decode lane stopped mid-iteration; its last complete results are still those of its batch
+        r = oracle.moe_layer(*(oracle.bf16_bits(t) for t in (xd_in, xd_res, wr, w13, w2)), K)
+        assert np.array_equal(dec.topk_ids[:24].cpu().numpy(), r["topk_ids"])
+    finally:
+        fab.stop()
+        fab.close()
