@@ -119,6 +119,12 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
                       int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
                       int n_pages, float scale_log2, int32_t* status, void* stream);
 
+/* Diagnostics of the attention kernel (no counterpart in the reference): enable or
+ * disable the phase trace of work item 0, and read the last one (out may be NULL):
+ * cycles waiting for S, in the max pass, in exp + P store, waiting for P V, folding
+ * into O; then the item's KV tiles and its total nanoseconds.  Synchronises the device. */
+int monofab_attention_trace(int enable, uint64_t out[8]);
+
 /* ---- one MoE layer ------------------------------------------------------- */
 
 typedef struct monofab_moe monofab_moe;

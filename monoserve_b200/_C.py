@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("MONOFAB_LIB") or os.path.join(_HERE, "libmonofab.so")
 # Every symbol include/monofab.h declares; tests check that all of them resolve.
 EXPORTS = [
     "monofab_version", "monofab_last_error", "monofab_struct_layouts_json", "monofab_host_device_pointer",
-    "monofab_host_alloc", "monofab_host_free", "monofab_router_logits", "monofab_router_topk", "monofab_combine", "monofab_attention", "monofab_pack_scratch_bytes", "monofab_pack_pairs", "monofab_pack_pairs_static",
+    "monofab_host_alloc", "monofab_host_free", "monofab_router_logits", "monofab_router_topk", "monofab_combine", "monofab_attention", "monofab_attention_trace", "monofab_pack_scratch_bytes", "monofab_pack_pairs", "monofab_pack_pairs_static",
     "monofab_moe_create", "monofab_moe_destroy", "monofab_moe_set_router", "monofab_moe_set_region",
     "monofab_moe_set_scales", "monofab_pack_w13", "monofab_moe_set_w13_packed", "monofab_moe_set_table", "monofab_moe_set_plan", "monofab_moe_forward", "monofab_moe_experts",
     "monofab_moe_forward_host", "monofab_moe_status", "monofab_moe_workspace", "monofab_moe_set_profile",
@@ -56,6 +56,7 @@ def _load():
     lib.monofab_pack_pairs.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
     lib.monofab_pack_pairs_static.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.monofab_attention.argtypes = [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    lib.monofab_attention_trace.argtypes = [i32, vp]
     lib.monofab_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
     lib.monofab_moe_create.argtypes = [ctypes.POINTER(MoEConfigC), ctypes.POINTER(vp)]
     lib.monofab_moe_destroy.argtypes = [vp]

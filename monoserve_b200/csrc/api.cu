@@ -422,6 +422,19 @@ int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int 
   return MONOFAB_OK;
 }
 
+static int g_attention_trace = 0;
+
+int monofab_attention_trace(int enable, uint64_t out[8]) {
+  g_attention_trace = enable != 0;
+  if (out) {
+    unsigned long long v[8];
+    MF_CUDA(cudaDeviceSynchronize());
+    MF_CUDA(read_attention_trace(v));
+    for (int i = 0; i < 8; ++i) out[i] = v[i];
+  }
+  return MONOFAB_OK;
+}
+
 int monofab_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* block_table,
                       int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
                       int n_pages, float scale_log2, int32_t* status, void* stream) {
@@ -459,6 +472,7 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
   p.page = page_size;
   p.n_items = n_items;
   p.q_box_rows = tok_box * group;
+  p.pad = g_attention_trace;
   MF_CUDA(launch_attention(p, static_cast<cudaStream_t>(stream)));
   return MONOFAB_OK;
 }

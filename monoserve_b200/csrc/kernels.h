@@ -106,6 +106,7 @@ struct AttnParams {
 };
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream);
+cudaError_t read_attention_trace(unsigned long long out[8]);
 
 // The stable pack from given routing: ranks -> scan -> pair lists (and, when src
 // is set, the packed rows).  `scratch` holds pack_scratch_bytes(T, E, K) bytes.
