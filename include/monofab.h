@@ -110,19 +110,31 @@ int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w
  * q / out bf16 [tokens][hq][128]; k_cache, v_cache bf16 [n_pages][page_size][hkv][128]
  * (monoserve/runtime/kv.py:8-11, with the page size a parameter: 8..128, dividing 128);
  * block_table int32 [requests][bt_stride]; scale_log2 = log2(e) / sqrt(128).
- * items int32 [n_items][8] on the device, one work item per (request, KV head, block of
- * query tokens): {block-table row, kv head, first query token, query tokens
+ * items int32 [n_items][12] on the device, one work item per (request, KV head, block of
+ * query tokens, key range): {block-table row, kv head, first query token, query tokens
  * (<= 128 / (hq / hkv)), position of the first query token, keys visible to the
- * request, 0, 0}; a decode row is an item with one query token.  `status` is a device
- * int32 that receives MONOFAB_STATUS_WAIT_TIMEOUT if a bounded wait ran out. */
+ * request, first key covered (a multiple of 128), one past the last key covered (<= 0:
+ * no limit), first workspace row or -1, 0, 0, 0}; a decode row is an item with one
+ * query token.  An item whose workspace row is -1 covers all keys and writes `out`
+ * directly.  Items that split one (request, KV head, block) over key ranges (the
+ * reference's KV chunks, csrc/fabric/tiles/attention.cuh:286-395) each leave
+ * query tokens x (hq / hkv) unnormalised fp32 rows in `ws` from their workspace row on;
+ * `ws` holds ws_rows x 130 floats (rows of 128, then (max, sum) pairs).  merge_items
+ * int32 [n_merge][8]: {first query token, query tokens, kv head, workspace row of
+ * part 0, parts, workspace rows from one part to the next, 0, 0}; the parts are merged
+ * in part order after the main kernel, on the same stream.  ws / merge_items may be
+ * NULL when no item is split.  `status` is a device int32 that receives
+ * MONOFAB_STATUS_WAIT_TIMEOUT if a bounded wait ran out. */
 int monofab_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* block_table,
                       int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
-                      int n_pages, float scale_log2, int32_t* status, void* stream);
+                      int n_pages, float scale_log2, float* ws, int ws_rows, const int32_t* merge_items, int n_merge,
+                      int32_t* status, void* stream);
 
 /* Diagnostics of the attention kernel (no counterpart in the reference): enable or
  * disable the phase trace of work item 0, and read the last one (out may be NULL):
- * cycles waiting for S, in the max pass, in exp + P store, waiting for P V, folding
- * into O; then the item's KV tiles and its total nanoseconds.  Synchronises the device. */
+ * cycles waiting for S, in the max pass, in exp + P store, rescaling O (tiles where a
+ * row maximum grew), in the final wait for P V; then the item's KV tiles and its total
+ * nanoseconds.  Synchronises the device. */
 int monofab_attention_trace(int enable, uint64_t out[8]);
 
 /* ---- one MoE layer ------------------------------------------------------- */

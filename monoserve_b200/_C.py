@@ -55,7 +55,7 @@ def _load():
     lib.monofab_pack_scratch_bytes.argtypes = [i32, i32, i32]
     lib.monofab_pack_pairs.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
     lib.monofab_pack_pairs_static.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
-    lib.monofab_attention.argtypes = [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp]
+    lib.monofab_attention.argtypes = [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, i32, vp, i32, vp, vp]
     lib.monofab_attention_trace.argtypes = [i32, vp]
     lib.monofab_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]
     lib.monofab_moe_create.argtypes = [ctypes.POINTER(MoEConfigC), ctypes.POINTER(vp)]

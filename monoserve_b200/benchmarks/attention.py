@@ -7,14 +7,15 @@ decode : `seqs` sequences, contexts uniform in [512, 8192], one query token each
          reported as K+V GB/s = sum(ctx) * hkv * 128 * 2 * 2 bytes / time (HBM-bound).
 prefill: 4 prompts of 2048 tokens; reported as TFLOP/s with
          FLOPs = 4 * hq * 128 * sum over prompts of n (n + 1) / 2 (tensor-pipe-bound).
-Synthetic, seeded data; times are CUDA-event means after warm-up; one JSON line.
+Synthetic, seeded data; the work list is planned once outside the timed region; times are
+CUDA-event means of the launches (main kernel + merge of split parts) after warm-up; one JSON line.
 """
 import argparse
 import json
 
 import torch
 
-from monoserve_b200.attention import paged_attention
+from monoserve_b200.attention import AttentionPlan
 
 
 def make_batch(lens, q_rows, hq, hkv, page, seed):
@@ -56,6 +57,7 @@ def main():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--seqs", type=int, default=128)
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--part-tiles", type=int, default=None, help="128-key tiles per split part (default: planned)")
     ap.add_argument("--quick", action="store_true", help="small case for profiling")
     args = ap.parse_args()
     hq, hkv = 32, 4
@@ -64,17 +66,22 @@ def main():
     lens = torch.randint(512, 8193, (seqs,), generator=g).tolist()
     q, kc, vc, bt, info = make_batch(lens, [1] * seqs, hq, hkv, args.page, 1)
     out = torch.empty_like(q)
-    sec = timed(lambda: paged_attention(q, kc, vc, bt, info, out=out), args.reps)
+    plan = AttentionPlan(info, hq, hkv, part_tiles=args.part_tiles)
+    sec = timed(lambda: plan.run(q, kc, vc, bt, out=out, check=False), args.reps)
+    assert int(plan.status.item()) == 0
     kv_bytes = sum(lens) * hkv * 128 * 2 * 2
-    line = {"decode": {"seqs": seqs, "ctx_sum": sum(lens), "page": args.page, "us": sec * 1e6,
+    line = {"decode": {"seqs": seqs, "ctx_sum": sum(lens), "page": args.page, "items": int(plan.items.shape[0]),
+                       "us": sec * 1e6,
                        "kv_gbs": kv_bytes / sec / 1e9, "kv_bytes": kv_bytes}}
     if not args.quick:
         plens = [2048] * 4
         q, kc, vc, bt, info = make_batch(plens, plens, hq, hkv, args.page, 2)
         out = torch.empty_like(q)
-        sec = timed(lambda: paged_attention(q, kc, vc, bt, info, out=out), max(3, args.reps // 4))
+        plan = AttentionPlan(info, hq, hkv, part_tiles=args.part_tiles)
+        sec = timed(lambda: plan.run(q, kc, vc, bt, out=out, check=False), max(3, args.reps // 4))
+        assert int(plan.status.item()) == 0
         flops = 4 * hq * 128 * sum(n * (n + 1) // 2 for n in plens)
-        line["prefill"] = {"prompts": plens, "page": args.page, "us": sec * 1e6, "tflops": flops / sec / 1e12}
+        line["prefill"] = {"prompts": plens, "page": args.page, "items": int(plan.items.shape[0]), "us": sec * 1e6, "tflops": flops / sec / 1e12}
     print(json.dumps(line))
 
 

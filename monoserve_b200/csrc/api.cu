@@ -437,9 +437,12 @@ int monofab_attention_trace(int enable, uint64_t out[8]) {
 
 int monofab_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* block_table,
                       int bt_stride, const int32_t* items, int n_items, int tokens, int hq, int hkv, int page_size,
-                      int n_pages, float scale_log2, int32_t* status, void* stream) {
+                      int n_pages, float scale_log2, float* ws, int ws_rows, const int32_t* merge_items, int n_merge,
+                      int32_t* status, void* stream) {
   if (!q || !k_cache || !v_cache || !out || !block_table || !status || (n_items > 0 && !items))
     return fail(MONOFAB_EINVAL, "attention: NULL argument");
+  if (ws_rows < 0 || n_merge < 0 || (n_merge > 0 && (!merge_items || !ws || ws_rows < 1)))
+    return fail(MONOFAB_EINVAL, "attention: split items need a workspace and a merge list");
   if (hkv < 1 || hq < hkv || hq % hkv) return fail(MONOFAB_EINVAL, "attention: hq=%d must be a multiple of hkv=%d", hq, hkv);
   const int group = hq / hkv;
   if (group > 128) return fail(MONOFAB_EINVAL, "attention: GQA group %d exceeds 128 rows", group);
@@ -453,6 +456,11 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
     const uint64_t strides[2] = {256, static_cast<uint64_t>(hq) * 256};
     const uint32_t box[3] = {64, static_cast<uint32_t>(group), static_cast<uint32_t>(tok_box)};
     if (int r = encode_map(&p.q_map, 0, q, 3, dims, strides, box, 128)) return r;
+    if (32 % group == 0) {
+      const uint32_t small[3] = {64, static_cast<uint32_t>(group), static_cast<uint32_t>(32 / group)};
+      if (int r = encode_map(&p.q_map_small, 0, q, 3, dims, strides, small, 128)) return r;
+      p.rep_ok = 1;
+    }
   }
   for (int i = 0; i < 2; ++i) {
     const uint64_t dims[4] = {128, static_cast<uint64_t>(hkv), static_cast<uint64_t>(page_size), static_cast<uint64_t>(n_pages)};
@@ -473,7 +481,11 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
   p.n_items = n_items;
   p.q_box_rows = tok_box * group;
   p.pad = g_attention_trace;
+  p.ws_o = ws;
+  p.ws_ml = ws ? reinterpret_cast<float2*>(ws + static_cast<size_t>(ws_rows) * 128) : nullptr;
   MF_CUDA(launch_attention(p, static_cast<cudaStream_t>(stream)));
+  MF_CUDA(launch_attention_combine(merge_items, n_merge, p.ws_o, p.ws_ml, p.out, hq, group,
+                                   static_cast<cudaStream_t>(stream)));
   return MONOFAB_OK;
 }
 

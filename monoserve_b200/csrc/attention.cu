@@ -21,7 +21,17 @@
 //   * V is used in place from the cache layout as an MN-major B operand (keys are the
 //     contraction dimension), so no transposed copy of V exists anywhere;
 //   * the page size is a parameter (16 and 64 are tested); pages of one 128-key tile
-//     are fetched by parallel lanes of the producer warp.
+//     are fetched by parallel lanes of the producer warp;
+//   * an item with at most 32 rows (decode: one token x GQA group) loads its rows into
+//     all four 32-lane quadrants of the MMA's M dimension; softmax warp w then handles
+//     key columns [32 w, 32 w + 32) of every tile with its own running (max, sum) and
+//     its own O rows, and the four partial results are merged once at the end of the
+//     item.  That spreads a decode row's exponentials over four warps without any
+//     cross-warp traffic inside the tile loop;
+//   * an item may cover a key range [key_begin, key_end) only (split KV for load
+//     balance, as the reference's KV chunks: csrc/fabric/tiles/attention.cuh:286-395);
+//     it then leaves its unnormalised fp32 O rows and (max, sum) in a workspace and
+//     attention_combine_kernel merges the parts in part order.
 //
 // Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issue,
 // warps 2..5 softmax / output (TMEM lane quadrant = warp % 4).  Every wait is
@@ -53,7 +63,9 @@ struct AttnShared {
   uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
+  float2 ml[4][32];   // (max, sum) of the four column quarters of a quad-replicated item
 };
+constexpr int kPartLd = 132;   // fp32 row stride of the merge scratch (conflict-free float4 access)
 
 // K-major SW128 descriptor of a 128-row tile with two 64-element column halves;
 // step = one of the eight 16-element K steps.
@@ -117,6 +129,280 @@ __device__ __forceinline__ void tma_load_3d_plain(void* smem, const void* map, u
       : "memory");
 }
 
+struct SoftmaxCtx {
+  AttnShared* sh;
+  uint8_t* sP;
+  float* scratch;       // >= 4 * 32 * kPartLd floats, free once the last P V has completed
+  uint32_t tmem_base;
+  int n_tiles, rows, kv_end;
+};
+
+__device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
+// A bounded wait whose outcome is the same in every lane of the warp, so that the
+// warp-wide TMEM instructions that follow are never reached by a part of a warp.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long budget_ns) {
+  return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, abort_flag, budget_ns));
+}
+
+// The softmax / output role of the four warps 2..5.  NC = key columns of a tile one
+// thread handles: 128 (a thread owns one of 128 query rows) or 32 (quad-replicated item:
+// the thread's row is lane, its columns are quarter `quad` of the tile).
+template <int NC>
+__device__ __forceinline__ void softmax_role(const AttnParams& p, const AttnItem& item, const SoftmaxCtx& c) {
+  constexpr bool kRep = NC == 32;
+  AttnShared& sh = *c.sh;
+  volatile int* abort_flag = &sh.abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad = warp & 3;
+  const int r = quad * 32 + lane;                 // TMEM lane = row of S, P and O
+  const int lr = kRep ? lane : r;                 // row of the item
+  const bool row_ok = lr < c.rows;
+  const bool warp_active = kRep || quad * 32 < c.rows;
+  const int group = p.group;
+  const int token = lr / group, head = item.kv_head * group + lr % group;
+  const int qpos = item.pos0 + token;
+  const int c_lo = kRep ? quad * 32 : 0;
+  const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+  const uint32_t tmem_o = c.tmem_base + 256 + lane_off;
+  const int n_tiles = c.n_tiles;
+  float m = -1e30f, l = 0.f;
+  bool ok = true;
+  const bool tr = p.pad && blockIdx.x == 0 && warp == 2 && lane == 0;
+  long long tc[5] = {0, 0, 0, 0, 0}, t_prev = clock64();
+  const unsigned long long t_begin = globaltimer_ns();
+  auto lap = [&](int i) {
+    if (tr) {
+      const long long now = clock64();
+      tc[i] += now - t_prev;
+      t_prev = now;
+    }
+  };
+  if (kRep) {
+    // columns outside this thread's quarter stay zero in both P buffers
+    for (int b = 0; b < 2; ++b)
+      for (int h = 0; h < 2; ++h) {
+        uint4* row = reinterpret_cast<uint4*>(c.sP + b * kTileBytes + h * kHalfBytes + r * 128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
+      }
+  }
+  for (int j = 0; ok && j < n_tiles; ++j) {
+    const int s = j & 1;
+    if (!warp_wait(&sh.s_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+    tc_fence_after_sync();
+    lap(0);
+    if (!warp_active) {   // no row of this warp exists: keep the barrier protocol only
+      mbar_arrive(&sh.p_full[s]);
+      continue;
+    }
+    const uint32_t tmem_s = c.tmem_base + s * 128 + lane_off + c_lo;
+    const int key0 = item.key_begin + j * kKeysPerTile + c_lo;
+    // keys this thread may use among its NC columns: [0, lim)
+    const int lim = row_ok ? min(min(c.kv_end, qpos + 1) - key0, NC) : 0;
+    uint32_t v[NC];
+    __syncwarp();
+#pragma unroll
+    for (int c0 = 0; c0 < NC; c0 += 32) tmem_ld_32x32(tmem_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
+    tmem_ld_wait();
+    float mx = m;
+    if (lim >= NC) {
+#pragma unroll
+      for (int i = 0; i < NC; ++i) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NC; ++i)
+        if (i < lim) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+    }
+    lap(1);
+    // a row whose maximum grew rescales its part of O in TMEM, once the previous P V has landed
+    if (j > 0 && __any_sync(0xffffffffu, mx > m)) {
+      if (!warp_wait(&sh.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+      tc_fence_after_sync();
+      const float alpha = fast_exp2(m - mx);
+#pragma unroll
+      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+        uint32_t o[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_o + c0, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32(tmem_o + c0, o);
+      }
+      tmem_st_wait();
+      l *= alpha;
+    }
+    m = mx;
+    lap(3);
+    // the P buffer is free once P V of tile j - 2 has completed
+    if (j >= 2 && !warp_wait(&sh.o_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+    const float neg_mx = -mx;
+    // P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
+    float sum0 = 0.f, sum1 = 0.f;
+    uint8_t* p_tile = c.sP + s * kTileBytes;
+#pragma unroll
+    for (int c0 = 0; c0 < NC; c0 += 32) {
+      uint32_t packed[16];
+      if (c0 + 32 <= lim) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx));
+          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
+          sum0 += __uint_as_float(u << 16);
+          sum1 += __uint_as_float(u & 0xffff0000u);
+          packed[i >> 1] = u;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = c0 + i < lim ? fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx)) : 0.f;
+          const float p1 = c0 + i + 1 < lim ? fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx)) : 0.f;
+          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
+          sum0 += __uint_as_float(u << 16);
+          sum1 += __uint_as_float(u & 0xffff0000u);
+          packed[i >> 1] = u;
+        }
+      }
+      // 32 keys = four 16-byte chunks of this row in key half col / 64
+      const int col = c_lo + c0;
+      uint8_t* row_base = p_tile + (col >> 6) * kHalfBytes + r * 128;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int chunk = ((col & 63) >> 3) + q;
+        *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) =
+            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+    }
+    l += sum0 + sum1;
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    mbar_arrive(&sh.p_full[s]);
+    lap(2);
+  }
+  if (ok && n_tiles > 0)
+    ok = warp_wait(&sh.o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, kAttnWaitNs);
+  tc_fence_after_sync();
+  lap(4);
+  if (tr) {
+    for (int i = 0; i < 5; ++i) g_attn_trace[i] = tc[i];
+    g_attn_trace[5] = n_tiles;
+    g_attn_trace[6] = globaltimer_ns() - t_begin;
+  }
+  const bool split = item.ws_row0 >= 0;
+  if (!kRep) {
+    // The TMEM loads are warp-wide (.sync.aligned): they sit in code every lane of the warp
+    // runs, apart from anything that depends on the lane's row, and a warp barrier separates
+    // them from the per-row stores so that the two cannot be merged into one divergent region.
+    if (ok && warp_active) {
+      uint32_t o[kHeadDim];
+      if (n_tiles > 0) {
+#pragma unroll
+        for (int c0 = 0; c0 < kHeadDim; c0 += 32) tmem_ld_32x32(tmem_o + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < kHeadDim; ++i) o[i] = 0;
+      }
+      __syncwarp();
+      if (row_ok) {
+        if (split) {
+          float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim);
+          p.ws_ml[item.ws_row0 + lr] = make_float2(m, l);
+#pragma unroll
+          for (int i = 0; i < kHeadDim / 4; ++i)
+            wdst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                                  __uint_as_float(o[4 * i + 3]));
+        } else {
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim);
+#pragma unroll
+          for (int q = 0; q < kHeadDim / 8; ++q) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              h[i] = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2 * i]) * inv, __uint_as_float(o[8 * q + 2 * i + 1]) * inv);
+            dst[q] = *reinterpret_cast<const uint4*>(h);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    return;
+  }
+  // quad-replicated item: merge the four column quarters.  Every thread takes part in
+  // both barriers, also after a timeout, so that none of them can be left waiting.
+  sh.ml[quad][lane] = make_float2(m, l);
+  named_barrier_128(1);
+  float M = -1e30f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) M = fmaxf(M, sh.ml[q][lane].x);
+  float L = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) L += sh.ml[q][lane].y * fast_exp2(sh.ml[q][lane].x - M);
+  {
+    const float f = fast_exp2(m - M);
+    float4* mine = reinterpret_cast<float4*>(c.scratch + (quad * 32 + lane) * kPartLd);
+#pragma unroll
+    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+      uint32_t o[32];
+      __syncwarp();
+      if (ok && n_tiles > 0) {
+        tmem_ld_32x32(tmem_o + c0, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        mine[(c0 >> 2) + i] = make_float4(__uint_as_float(o[4 * i]) * f, __uint_as_float(o[4 * i + 1]) * f,
+                                          __uint_as_float(o[4 * i + 2]) * f, __uint_as_float(o[4 * i + 3]) * f);
+    }
+  }
+  named_barrier_128(2);
+  if (ok && row_ok) {
+    // this thread: row `lane`, output columns [32 quad, 32 quad + 32), quarters added in order
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4* src = reinterpret_cast<const float4*>(c.scratch + (q * 32 + lane) * kPartLd + quad * 32);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 t = src[i];
+        acc[4 * i] += t.x;
+        acc[4 * i + 1] += t.y;
+        acc[4 * i + 2] += t.z;
+        acc[4 * i + 3] += t.w;
+      }
+    }
+    if (split) {
+      float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim + quad * 32);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) wdst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+      if (quad == 0) p.ws_ml[item.ws_row0 + lr] = make_float2(M, L);
+    } else {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim +
+                                            quad * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[8 * q + 2 * i] * inv, acc[8 * q + 2 * i + 1] * inv);
+        dst[q] = *reinterpret_cast<const uint4*>(h);
+      }
+    }
+  }
+}
+
+
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
@@ -130,9 +416,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   const AttnItem item = p.items[blockIdx.x];
   const int group = p.group;
   const int rows = item.q_tokens * group;
-  // keys this block can see: up to the position of its last query token
-  const int kv_end = min(item.kv_len, item.pos0 + item.q_tokens);
-  const int n_tiles = (kv_end + kKeysPerTile - 1) / kKeysPerTile;
+  // keys this item covers: from key_begin up to the position of its last query token
+  // (and key_end, when the item is one part of a split)
+  int kv_end = min(item.kv_len, item.pos0 + item.q_tokens);
+  if (item.key_end > 0) kv_end = min(kv_end, item.key_end);
+  const int n_tiles = max(0, (kv_end - item.key_begin + kKeysPerTile - 1) / kKeysPerTile);
+  const bool rep = p.rep_ok && rows <= 32;
 
   if (threadIdx.x == 0) {
     mbar_init(&sh.q_full, 1);
@@ -161,29 +450,40 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   if (warp == 0) {
     // --------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&sh.q_full, 2u * p.q_box_rows * 128u);
-      tma_load_3d_plain(sQ, &p.q_map, &sh.q_full, 0, item.kv_head * group, item.q_row0);
-      tma_load_3d_plain(sQ + kHalfBytes, &p.q_map, &sh.q_full, 64, item.kv_head * group, item.q_row0);
+      if (rep) {
+        // the same 32 rows into every lane quadrant of the M dimension
+        mbar_arrive_expect_tx(&sh.q_full, kTileBytes);
+        for (int q = 0; q < 4; ++q) {
+          tma_load_3d_plain(sQ + q * 4096, &p.q_map_small, &sh.q_full, 0, item.kv_head * group, item.q_row0);
+          tma_load_3d_plain(sQ + kHalfBytes + q * 4096, &p.q_map_small, &sh.q_full, 64, item.kv_head * group,
+                            item.q_row0);
+        }
+      } else {
+        mbar_arrive_expect_tx(&sh.q_full, 2u * p.q_box_rows * 128u);
+        tma_load_3d_plain(sQ, &p.q_map, &sh.q_full, 0, item.kv_head * group, item.q_row0);
+        tma_load_3d_plain(sQ + kHalfBytes, &p.q_map, &sh.q_full, 64, item.kv_head * group, item.q_row0);
+      }
     }
     const int pages_per_tile = kKeysPerTile / p.page;
     const int page_bytes = p.page * 128;   // one d half of one page
     const int last_page = (kv_end - 1) / p.page;
+    const int tile0 = item.key_begin / kKeysPerTile;
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j & 1;
       const uint32_t prev = ((j >> 1) - 1) & 1;
-      if (j >= 2 && !mbar_wait_bounded(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) break;
+      if (j >= 2 && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) break;
       if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
       __syncwarp();
       int page_id = 0;
       if (lane < pages_per_tile) {
         // pages past the visible range repeat the last visible page; their keys are masked
-        const int pg = min(j * pages_per_tile + lane, last_page);
+        const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
         page_id = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
         uint8_t* k = sK + s * kTileBytes + lane * page_bytes;
         tma_load_4d(k, &p.k_map, &sh.k_full[s], 0, item.kv_head, 0, page_id);
         tma_load_4d(k + kHalfBytes, &p.k_map, &sh.k_full[s], 64, item.kv_head, 0, page_id);
       }
-      if (j >= 2 && !mbar_wait_bounded(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) break;
+      if (j >= 2 && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) break;
       if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
       __syncwarp();
       if (lane < pages_per_tile) {
@@ -194,7 +494,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issue
-    if (lane == 0) {
+    if (lane == 0) {   // one thread issues: its waits are the plain per-thread ones
       // S = Q K^T: both K-major; O += P V: A K-major, B (V) MN-major
       const uint32_t idesc_s = umma_idesc_bf16(128, 128);
       const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
@@ -233,134 +533,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
     __syncwarp();
   } else {
     // ------------------------------------------------------ softmax / output
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;              // query row = TMEM lane
-    const bool row_ok = r < rows;
-    const int token = r / group, head = item.kv_head * group + r % group;
-    const int qpos = item.pos0 + token;
-    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    float m = -1e30f, l = 0.f;
-    bool ok = true;
-    const bool tr = p.pad && blockIdx.x == 0 && warp == 2 && lane == 0;
-    long long tc[5] = {0, 0, 0, 0, 0}, t_prev = clock64();
-    const unsigned long long t_begin = globaltimer_ns();
-    auto lap = [&](int i) {
-      if (tr) {
-        const long long now = clock64();
-        tc[i] += now - t_prev;
-        t_prev = now;
-      }
-    };
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait_bounded(&sh.s_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-      tc_fence_after_sync();
-      lap(0);
-      const uint32_t tmem_s = tmem_base + s * 128 + lane_off;
-      const int key0 = j * kKeysPerTile;
-      // keys this row may attend to inside the tile: [0, lim)
-      const int lim = row_ok ? min(min(item.kv_len, qpos + 1) - key0, kKeysPerTile) : 0;
-      // pass 1: row maximum of the scaled scores
-      float mx = m;
-#pragma unroll
-      for (int c0 = 0; c0 < kKeysPerTile; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c0 + i < lim) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
-      }
-      lap(1);
-      // a row whose maximum grew rescales its part of O in TMEM, once the previous P V has landed
-      if (j > 0 && __any_sync(0xffffffffu, mx > m)) {
-        if (!mbar_wait_bounded(&sh.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-        tc_fence_after_sync();
-        const float alpha = fast_exp2(m - mx);
-#pragma unroll
-        for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_o + lane_off + c0, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tmem_o + lane_off + c0, v);
-        }
-        tmem_st_wait();
-        l *= alpha;
-      } else if (j == 0) {
-        l = 0.f;
-      }
-      m = mx;
-      lap(3);
-      // the P buffer is free once P V of tile j - 2 has completed
-      if (j >= 2 && !mbar_wait_bounded(&sh.o_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-      const float neg_mx = -mx;
-      // pass 2: P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
-      float sum = 0.f;
-      uint8_t* p_tile = sP + s * kTileBytes;
-#pragma unroll
-      for (int c0 = 0; c0 < kKeysPerTile; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_s + c0, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = c0 + i < lim ? fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, neg_mx)) : 0.f;
-          const float p1 = c0 + i + 1 < lim ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, neg_mx)) : 0.f;
-          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          sum += __bfloat162float(b.x) + __bfloat162float(b.y);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&b);
-        }
-        // 32 keys = four 16-byte chunks of this row in key half c0 / 64
-        uint8_t* row_base = p_tile + (c0 >> 6) * kHalfBytes + r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c0 & 63) >> 3) + q;
-          *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      }
-      l += sum;
-      tc_fence_before_sync();
-      fence_proxy_async_smem();
-      mbar_arrive(&sh.p_full[s]);
-      lap(2);
-    }
-    if (ok && n_tiles > 0) ok = mbar_wait_bounded(&sh.o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, kAttnWaitNs);
-    tc_fence_after_sync();
-    lap(4);
-    if (tr) {
-      for (int i = 0; i < 5; ++i) g_attn_trace[i] = tc[i];
-      g_attn_trace[5] = n_tiles;
-      g_attn_trace[6] = globaltimer_ns() - t_begin;
-    }
-    if (ok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim);
-#pragma unroll
-      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-        uint32_t v[32];
-        if (n_tiles > 0) {
-          tmem_ld_32x32(tmem_o + lane_off + c0, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            __nv_bfloat162 h[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              h[i] = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * i]) * inv, __uint_as_float(v[8 * c + 2 * i + 1]) * inv);
-            dst[(c0 >> 3) + c] = *reinterpret_cast<const uint4*>(h);
-          }
-        }
-      }
-    }
+    SoftmaxCtx c;
+    c.sh = &sh;
+    c.sP = sP;
+    c.scratch = reinterpret_cast<float*>(sK);
+    c.tmem_base = tmem_base;
+    c.n_tiles = n_tiles;
+    c.rows = rows;
+    c.kv_end = kv_end;
+    if (rep) softmax_role<32>(p, item, c);
+    else softmax_role<128>(p, item, c);
   }
 
   tc_fence_before_sync();
@@ -370,6 +552,45 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kAttnTmemCols);
   }
+}
+
+// Merge of split items: one warp per output row (token, q head); the parts are added in
+// part order.  items: {first query token, query tokens, kv head, first workspace row,
+// parts, workspace rows per part, 0, 0}.
+__global__ void attention_combine_kernel(const int32_t* __restrict__ items, int n_items, const float* __restrict__ ws_o,
+                                         const float2* __restrict__ ws_ml, __nv_bfloat16* __restrict__ out, int hq,
+                                         int group) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int32_t* it = items + static_cast<size_t>(blockIdx.x) * 8;
+  const int q_row0 = it[0], q_tokens = it[1], kv_head = it[2], ws_row0 = it[3], parts = it[4], stride = it[5];
+  for (int row = wid; row < q_tokens * group; row += blockDim.x >> 5) {
+    float M = -1e30f;
+    for (int q = 0; q < parts; ++q) M = fmaxf(M, ws_ml[ws_row0 + q * stride + row].x);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < parts; ++q) {
+      const float2 ml = ws_ml[ws_row0 + q * stride + row];
+      const float w = fast_exp2(ml.x - M);
+      L += ml.y * w;
+      const float4 t = reinterpret_cast<const float4*>(ws_o + static_cast<size_t>(ws_row0 + q * stride + row) * kHeadDim)[lane];
+      acc.x += t.x * w;
+      acc.y += t.y * w;
+      acc.z += t.z * w;
+      acc.w += t.w * w;
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int token = row / group, head = kv_head * group + row % group;
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(acc.x * inv, acc.y * inv), __floats2bfloat162_rn(acc.z * inv, acc.w * inv)};
+    reinterpret_cast<uint2*>(out + (static_cast<size_t>(q_row0 + token) * hq + head) * kHeadDim)[lane] =
+        *reinterpret_cast<const uint2*>(h);
+  }
+}
+
+cudaError_t launch_attention_combine(const int32_t* items, int n_items, const float* ws_o, const float2* ws_ml,
+                                     __nv_bfloat16* out, int hq, int group, cudaStream_t stream) {
+  if (n_items == 0) return cudaSuccess;
+  attention_combine_kernel<<<n_items, 256, 0, stream>>>(items, n_items, ws_o, ws_ml, out, hq, group);
+  return cudaGetLastError();
 }
 
 cudaError_t read_attention_trace(unsigned long long out[8]) {

@@ -88,13 +88,18 @@ struct AttnItem {
   int32_t q_tokens;   // query tokens in this block (q_tokens * group <= 128)
   int32_t pos0;       // position of the first query token
   int32_t kv_len;     // keys visible to the request: positions 0 .. kv_len - 1
-  int32_t pad[2];
+  int32_t key_begin;  // first key this item covers (a multiple of 128)
+  int32_t key_end;    // one past the last key it covers; <= 0: no limit
+  int32_t ws_row0;    // >= 0: the item is one part of a split and leaves fp32 rows there
+  int32_t pad[3];
 };
+static_assert(sizeof(AttnItem) == 48, "AttnItem is twelve int32");
 
 struct AttnParams {
   CUtensorMap q_map;    // dims (128, hq, T), box (64, group, tokens per block)
   CUtensorMap k_map;    // dims (128, hkv, page, pages), box (64, 1, page, 1)
   CUtensorMap v_map;
+  CUtensorMap q_map_small;   // box (64, group, 32 / group): items of at most 32 rows
   const AttnItem* items;
   const int32_t* block_table;
   __nv_bfloat16* out;   // [T][hq][128]
@@ -102,10 +107,16 @@ struct AttnParams {
   float scale_log2;     // softmax scale * log2(e)
   int32_t bt_stride, hq, hkv, group, page, n_items;
   int32_t q_box_rows;   // rows of the q box: group * tokens per block (the bytes one q copy delivers)
-  int32_t pad;
+  int32_t pad;          // nonzero: record the phase trace of item 0
+  float* ws_o;          // split items: unnormalised O rows, fp32 [rows][128]
+  float2* ws_ml;        // and their (max, sum)
+  int32_t rep_ok;       // q_map_small is valid (the group divides 32)
+  int32_t pad2;
 };
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream);
+cudaError_t launch_attention_combine(const int32_t* items, int n_items, const float* ws_o, const float2* ws_ml,
+                                     __nv_bfloat16* out, int hq, int group, cudaStream_t stream);
 cudaError_t read_attention_trace(unsigned long long out[8]);
 
 // The stable pack from given routing: ranks -> scan -> pair lists (and, when src

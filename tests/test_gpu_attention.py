@@ -95,8 +95,42 @@ def test_attention_rejects_bad_shapes():
     from monoserve_b200 import _C
     z = torch.zeros(8, device="cuda", dtype=torch.int32)
     rc = _C.lib.monofab_attention(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, z.data_ptr(),
-                                  1, 1, 12, 5, 16, 1, 1.0, z.data_ptr(), None)
+                                  1, 1, 12, 5, 16, 1, 1.0, None, 0, None, 0, z.data_ptr(), None)
     assert rc == -1 and b"multiple of hkv" in _C.lib.monofab_last_error()
     rc = _C.lib.monofab_attention(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, z.data_ptr(),
-                                  1, 1, 8, 4, 24, 1, 1.0, z.data_ptr(), None)
+                                  1, 1, 8, 4, 24, 1, 1.0, None, 0, None, 0, z.data_ptr(), None)
     assert rc == -1 and b"page_size" in _C.lib.monofab_last_error()
+    rc = _C.lib.monofab_attention(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 1, z.data_ptr(),
+                                  1, 1, 8, 4, 16, 1, 1.0, None, 0, z.data_ptr(), 1, z.data_ptr(), None)
+    assert rc == -1 and b"workspace" in _C.lib.monofab_last_error()
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 4), (12, 4), (96, 8)])
+@pytest.mark.parametrize("part_tiles", [4, 7])
+def test_split_kv_matches_dense_and_unsplit(hq, hkv, part_tiles):
+    """Long contexts split over key ranges and merged: decode rows of 3000 / 1100 / 5000 keys
+    (quad-replicated items where the group divides 32) and a 300-token prefill chunk at the
+    end of a 2300-key request.  The split result must agree with dense softmax and, to
+    rounding of the merge, with the unsplit run of the same kernel."""
+    from monoserve_b200.attention import paged_attention, plan_items
+    lens = [3000, 1100, 5000, 2300]
+    rows = [1, 1, 1, 300]
+    kc, vc, bt, dense = make_cache(lens, hkv, 16, seed=11 + hq)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(sum(rows), hq, 128, generator=g).to(torch.bfloat16)
+    req_info, row = [], 0
+    for n, L in zip(rows, lens):
+        req_info.append((row, L - n, n, L))
+        row += n
+    items, merge, ws_rows = plan_items(req_info, hq, hkv, part_tiles=part_tiles)
+    assert merge.shape[0] > 0 and ws_rows > 0 and (items[:, 8] >= 0).sum() > merge.shape[0]
+    args = (q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), req_info)
+    out = paged_attention(*args, part_tiles=part_tiles).float().cpu()
+    whole = paged_attention(*args, split=False).float().cpu()
+    assert (out - whole).abs().max().item() < 4e-3
+    row = 0
+    for r, (n, L) in enumerate(zip(rows, lens)):
+        ref = dense_reference(q[row:row + n].float(), dense[r][0], dense[r][1], hq, hkv, L - n)
+        assert (out[row:row + n] - ref).abs().max().item() < TOL, r
+        assert (whole[row:row + n] - ref).abs().max().item() < TOL, r
+        row += n
