@@ -2,6 +2,7 @@
 (Qwen3-30B-A3B: 32 query heads, 4 KV heads, head_dim 128, page size 16).
 
     python -m monoserve_b200.benchmarks.attention [--page 16] [--seqs 128] [--reps 20] [--quick]
+                                                  [--mode both|decode|prefill] [--part-tiles N]
 
 decode : `seqs` sequences, contexts uniform in [512, 8192], one query token each;
          reported as K+V GB/s = sum(ctx) * hkv * 128 * 2 * 2 bytes / time (HBM-bound).
@@ -58,30 +59,33 @@ def main():
     ap.add_argument("--seqs", type=int, default=128)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--part-tiles", type=int, default=None, help="128-key tiles per split part (default: planned)")
-    ap.add_argument("--quick", action="store_true", help="small case for profiling")
+    ap.add_argument("--mode", choices=["both", "decode", "prefill"], default="both")
+    ap.add_argument("--quick", action="store_true", help="small case for profiling: 32 sequences / 1 prompt")
     args = ap.parse_args()
     hq, hkv = 32, 4
-    g = torch.Generator().manual_seed(0)
-    seqs = 32 if args.quick else args.seqs
-    lens = torch.randint(512, 8193, (seqs,), generator=g).tolist()
-    q, kc, vc, bt, info = make_batch(lens, [1] * seqs, hq, hkv, args.page, 1)
-    out = torch.empty_like(q)
-    plan = AttentionPlan(info, hq, hkv, part_tiles=args.part_tiles)
-    sec = timed(lambda: plan.run(q, kc, vc, bt, out=out, check=False), args.reps)
-    assert int(plan.status.item()) == 0
-    kv_bytes = sum(lens) * hkv * 128 * 2 * 2
-    line = {"decode": {"seqs": seqs, "ctx_sum": sum(lens), "page": args.page, "items": int(plan.items.shape[0]),
-                       "us": sec * 1e6,
-                       "kv_gbs": kv_bytes / sec / 1e9, "kv_bytes": kv_bytes}}
-    if not args.quick:
-        plens = [2048] * 4
+    line = {}
+    if args.mode in ("both", "decode"):
+        g = torch.Generator().manual_seed(0)
+        seqs = 32 if args.quick else args.seqs
+        lens = torch.randint(512, 8193, (seqs,), generator=g).tolist()
+        q, kc, vc, bt, info = make_batch(lens, [1] * seqs, hq, hkv, args.page, 1)
+        out = torch.empty_like(q)
+        plan = AttentionPlan(info, hq, hkv, part_tiles=args.part_tiles)
+        sec = timed(lambda: plan.run(q, kc, vc, bt, out=out, check=False), args.reps)
+        assert int(plan.status.item()) == 0
+        kv_bytes = sum(lens) * hkv * 128 * 2 * 2
+        line["decode"] = {"seqs": seqs, "ctx_sum": sum(lens), "page": args.page, "items": int(plan.items.shape[0]),
+                          "us": sec * 1e6, "kv_gbs": kv_bytes / sec / 1e9, "kv_bytes": kv_bytes}
+    if args.mode in ("both", "prefill"):
+        plens = [2048] * (1 if args.quick else 4)
         q, kc, vc, bt, info = make_batch(plens, plens, hq, hkv, args.page, 2)
         out = torch.empty_like(q)
         plan = AttentionPlan(info, hq, hkv, part_tiles=args.part_tiles)
         sec = timed(lambda: plan.run(q, kc, vc, bt, out=out, check=False), max(3, args.reps // 4))
         assert int(plan.status.item()) == 0
         flops = 4 * hq * 128 * sum(n * (n + 1) // 2 for n in plens)
-        line["prefill"] = {"prompts": plens, "page": args.page, "items": int(plan.items.shape[0]), "us": sec * 1e6, "tflops": flops / sec / 1e12}
+        line["prefill"] = {"prompts": plens, "page": args.page, "items": int(plan.items.shape[0]), "us": sec * 1e6,
+                           "tflops": flops / sec / 1e12}
     print(json.dumps(line))
 
 
