@@ -36,406 +36,47 @@
 // Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issue,
 // warps 2..5 softmax / output (TMEM lane quadrant = warp % 4).  Every wait is
 // bounded; a timeout raises the status word and the CTA leaves, freeing its TMEM.
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-
-#include "kernels.h"
-#include "ptx.cuh"
+#include "attention_core.cuh"
 
 namespace mf {
 
-constexpr int kAttnThreads = 192;
-constexpr int kHeadDim = 128;
-constexpr int kKeysPerTile = 128;
-constexpr int kHalfBytes = 128 * 128;            // 128 rows x 64 bf16: one swizzle atom column, 16 KB
-constexpr int kTileBytes = 2 * kHalfBytes;       // 128 x 128 bf16
-constexpr int kAttnSmemBytes = kTileBytes * 7 + 1024;   // Q, K x2, V x2, P x2
-constexpr int kAttnTmemCols = 512;               // S x2 (256) + O (128), allocated as a power of two
-constexpr unsigned long long kAttnWaitNs = 4000000000ull;
-
-// Diagnostics: phase times of work item 0's softmax warp 2, lane 0 (cycles summed over the
-// item's KV tiles): [0] wait for S, [1] max pass, [2] exp + P store, [3] rescale of O
-// (tiles where a maximum grew), [4] final wait for O, [5] tiles, [6] total ns.  Written when AttnParams::pad is nonzero.
+// Diagnostics: phase times of work item 0's softmax lane of quadrant 2 (cycles summed over
+// the item's KV tiles): [0] wait for S, [1] max pass, [2] exp + P store, [3] rescale of O
+// (tiles where a maximum grew), [4] final wait for O, [5] tiles, [6] total ns.  Written when
+// AttnParams::pad is nonzero.
 __device__ unsigned long long g_attn_trace[8];
-
-struct AttnShared {
-  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_full[2];
-  uint32_t tmem_base;
-  int abort_flag;
-  float2 ml[4][32];   // (max, sum) of the four column quarters of a quad-replicated item
-};
-constexpr int kPartLd = 132;   // fp32 row stride of the merge scratch (conflict-free float4 access)
-
-// K-major SW128 descriptor of a 128-row tile with two 64-element column halves;
-// step = one of the eight 16-element K steps.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int step) {
-  return umma_desc_sw128(tile_addr + (step >> 2) * kHalfBytes + (step & 3) * 32);
-}
-
-// MN-major SW128 descriptor of V: rows are keys (the K dimension), 128 bytes = 64 d
-// elements per row, eight-key groups 1024 bytes apart (SBO), the second d half one
-// 16 KB half-tile further (LBO).  step = one of the eight 16-key K steps.
-__device__ __forceinline__ uint64_t desc_v_mnmajor(uint32_t tile_addr, int step) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>(((tile_addr + step * 2048) & 0x3ffffu) >> 4);
-  d |= static_cast<uint64_t>(kHalfBytes >> 4) << 16;   // leading byte offset: next 64 d elements
-  d |= static_cast<uint64_t>(1024u >> 4) << 32;        // stride byte offset: next 8 keys
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-// 2^x by the special-function unit (one instruction; the scores are already scaled
-// into the exp2 domain, as in the reference's tiles).
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      :
-      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_4d(void* smem, const void* map, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      :
-      : "r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
-        "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ void tma_load_3d_plain(void* smem, const void* map, uint64_t* bar, int c0, int c1,
-                                                  int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];"
-      :
-      : "r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-
-struct SoftmaxCtx {
-  AttnShared* sh;
-  uint8_t* sP;
-  float* scratch;       // >= 4 * 32 * kPartLd floats, free once the last P V has completed
-  uint32_t tmem_base;
-  int n_tiles, rows, kv_end;
-};
-
-__device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
-
-// A bounded wait whose outcome is the same in every lane of the warp, so that the
-// warp-wide TMEM instructions that follow are never reached by a part of a warp.
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned long long budget_ns) {
-  return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, abort_flag, budget_ns));
-}
-
-// The softmax / output role of the four warps 2..5.  NC = key columns of a tile one
-// thread handles: 128 (a thread owns one of 128 query rows) or 32 (quad-replicated item:
-// the thread's row is lane, its columns are quarter `quad` of the tile).
-template <int NC>
-__device__ __forceinline__ void softmax_role(const AttnParams& p, const AttnItem& item, const SoftmaxCtx& c) {
-  constexpr bool kRep = NC == 32;
-  AttnShared& sh = *c.sh;
-  volatile int* abort_flag = &sh.abort_flag;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int quad = warp & 3;
-  const int r = quad * 32 + lane;                 // TMEM lane = row of S, P and O
-  const int lr = kRep ? lane : r;                 // row of the item
-  const bool row_ok = lr < c.rows;
-  const bool warp_active = kRep || quad * 32 < c.rows;
-  const int group = p.group;
-  const int token = lr / group, head = item.kv_head * group + lr % group;
-  const int qpos = item.pos0 + token;
-  const int c_lo = kRep ? quad * 32 : 0;
-  const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-  const uint32_t tmem_o = c.tmem_base + 256 + lane_off;
-  const int n_tiles = c.n_tiles;
-  float m = -1e30f, l = 0.f;
-  bool ok = true;
-  const bool tr = p.pad && blockIdx.x == 0 && warp == 2 && lane == 0;
-  long long tc[5] = {0, 0, 0, 0, 0}, t_prev = clock64();
-  const unsigned long long t_begin = globaltimer_ns();
-  auto lap = [&](int i) {
-    if (tr) {
-      const long long now = clock64();
-      tc[i] += now - t_prev;
-      t_prev = now;
-    }
-  };
-  if (kRep) {
-    // columns outside this thread's quarter stay zero in both P buffers
-    for (int b = 0; b < 2; ++b)
-      for (int h = 0; h < 2; ++h) {
-        uint4* row = reinterpret_cast<uint4*>(c.sP + b * kTileBytes + h * kHalfBytes + r * 128);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
-      }
-  }
-  for (int j = 0; ok && j < n_tiles; ++j) {
-    const int s = j & 1;
-    if (!warp_wait(&sh.s_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-    tc_fence_after_sync();
-    lap(0);
-    if (!warp_active) {   // no row of this warp exists: keep the barrier protocol only
-      mbar_arrive(&sh.p_full[s]);
-      continue;
-    }
-    const uint32_t tmem_s = c.tmem_base + s * 128 + lane_off + c_lo;
-    const int key0 = item.key_begin + j * kKeysPerTile + c_lo;
-    // keys this thread may use among its NC columns: [0, lim)
-    const int lim = row_ok ? min(min(c.kv_end, qpos + 1) - key0, NC) : 0;
-    uint32_t v[NC];
-    __syncwarp();
-#pragma unroll
-    for (int c0 = 0; c0 < NC; c0 += 32) tmem_ld_32x32(tmem_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
-    tmem_ld_wait();
-    float mx = m;
-    if (lim >= NC) {
-#pragma unroll
-      for (int i = 0; i < NC; ++i) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
-    } else {
-#pragma unroll
-      for (int i = 0; i < NC; ++i)
-        if (i < lim) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
-    }
-    lap(1);
-    // a row whose maximum grew rescales its part of O in TMEM, once the previous P V has landed
-    if (j > 0 && __any_sync(0xffffffffu, mx > m)) {
-      if (!warp_wait(&sh.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-      tc_fence_after_sync();
-      const float alpha = fast_exp2(m - mx);
-#pragma unroll
-      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-        uint32_t o[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_o + c0, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_32x32(tmem_o + c0, o);
-      }
-      tmem_st_wait();
-      l *= alpha;
-    }
-    m = mx;
-    lap(3);
-    // the P buffer is free once P V of tile j - 2 has completed
-    if (j >= 2 && !warp_wait(&sh.o_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-    const float neg_mx = -mx;
-    // P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
-    float sum0 = 0.f, sum1 = 0.f;
-    uint8_t* p_tile = c.sP + s * kTileBytes;
-#pragma unroll
-    for (int c0 = 0; c0 < NC; c0 += 32) {
-      uint32_t packed[16];
-      if (c0 + 32 <= lim) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx));
-          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
-          sum0 += __uint_as_float(u << 16);
-          sum1 += __uint_as_float(u & 0xffff0000u);
-          packed[i >> 1] = u;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = c0 + i < lim ? fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx)) : 0.f;
-          const float p1 = c0 + i + 1 < lim ? fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx)) : 0.f;
-          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
-          sum0 += __uint_as_float(u << 16);
-          sum1 += __uint_as_float(u & 0xffff0000u);
-          packed[i >> 1] = u;
-        }
-      }
-      // 32 keys = four 16-byte chunks of this row in key half col / 64
-      const int col = c_lo + c0;
-      uint8_t* row_base = p_tile + (col >> 6) * kHalfBytes + r * 128;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int chunk = ((col & 63) >> 3) + q;
-        *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) =
-            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      }
-    }
-    l += sum0 + sum1;
-    tc_fence_before_sync();
-    fence_proxy_async_smem();
-    mbar_arrive(&sh.p_full[s]);
-    lap(2);
-  }
-  if (ok && n_tiles > 0)
-    ok = warp_wait(&sh.o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, kAttnWaitNs);
-  tc_fence_after_sync();
-  lap(4);
-  if (tr) {
-    for (int i = 0; i < 5; ++i) g_attn_trace[i] = tc[i];
-    g_attn_trace[5] = n_tiles;
-    g_attn_trace[6] = globaltimer_ns() - t_begin;
-  }
-  const bool split = item.ws_row0 >= 0;
-  if (!kRep) {
-    // The TMEM loads are warp-wide (.sync.aligned): they sit in code every lane of the warp
-    // runs, apart from anything that depends on the lane's row, and a warp barrier separates
-    // them from the per-row stores so that the two cannot be merged into one divergent region.
-    if (ok && warp_active) {
-      uint32_t o[kHeadDim];
-      if (n_tiles > 0) {
-#pragma unroll
-        for (int c0 = 0; c0 < kHeadDim; c0 += 32) tmem_ld_32x32(tmem_o + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < kHeadDim; ++i) o[i] = 0;
-      }
-      __syncwarp();
-      if (row_ok) {
-        if (split) {
-          float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim);
-          p.ws_ml[item.ws_row0 + lr] = make_float2(m, l);
-#pragma unroll
-          for (int i = 0; i < kHeadDim / 4; ++i)
-            wdst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
-                                  __uint_as_float(o[4 * i + 3]));
-        } else {
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim);
-#pragma unroll
-          for (int q = 0; q < kHeadDim / 8; ++q) {
-            __nv_bfloat162 h[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              h[i] = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2 * i]) * inv, __uint_as_float(o[8 * q + 2 * i + 1]) * inv);
-            dst[q] = *reinterpret_cast<const uint4*>(h);
-          }
-        }
-      }
-      __syncwarp();
-    }
-    return;
-  }
-  // quad-replicated item: merge the four column quarters.  Every thread takes part in
-  // both barriers, also after a timeout, so that none of them can be left waiting.
-  sh.ml[quad][lane] = make_float2(m, l);
-  named_barrier_128(1);
-  float M = -1e30f;
-#pragma unroll
-  for (int q = 0; q < 4; ++q) M = fmaxf(M, sh.ml[q][lane].x);
-  float L = 0.f;
-#pragma unroll
-  for (int q = 0; q < 4; ++q) L += sh.ml[q][lane].y * fast_exp2(sh.ml[q][lane].x - M);
-  {
-    const float f = fast_exp2(m - M);
-    float4* mine = reinterpret_cast<float4*>(c.scratch + (quad * 32 + lane) * kPartLd);
-#pragma unroll
-    for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
-      uint32_t o[32];
-      __syncwarp();
-      if (ok && n_tiles > 0) {
-        tmem_ld_32x32(tmem_o + c0, o);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0;
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        mine[(c0 >> 2) + i] = make_float4(__uint_as_float(o[4 * i]) * f, __uint_as_float(o[4 * i + 1]) * f,
-                                          __uint_as_float(o[4 * i + 2]) * f, __uint_as_float(o[4 * i + 3]) * f);
-    }
-  }
-  named_barrier_128(2);
-  if (ok && row_ok) {
-    // this thread: row `lane`, output columns [32 quad, 32 quad + 32), quarters added in order
-    float acc[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float4* src = reinterpret_cast<const float4*>(c.scratch + (q * 32 + lane) * kPartLd + quad * 32);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 t = src[i];
-        acc[4 * i] += t.x;
-        acc[4 * i + 1] += t.y;
-        acc[4 * i + 2] += t.z;
-        acc[4 * i + 3] += t.w;
-      }
-    }
-    if (split) {
-      float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim + quad * 32);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) wdst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-      if (quad == 0) p.ws_ml[item.ws_row0 + lr] = make_float2(M, L);
-    } else {
-      const float inv = L > 0.f ? 1.f / L : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim +
-                                            quad * 32);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        __nv_bfloat162 h[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[8 * q + 2 * i] * inv, acc[8 * q + 2 * i + 1] * inv);
-        dst[q] = *reinterpret_cast<const uint4*>(h);
-      }
-    }
-  }
-}
-
 
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = base;
-  uint8_t* sK = base + kTileBytes;          // two stages
-  uint8_t* sV = base + 3 * kTileBytes;      // two stages
-  uint8_t* sP = base + 5 * kTileBytes;      // two buffers
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  volatile int* abort_flag = &sh.abort_flag;
-  const AttnItem item = p.items[blockIdx.x];
-  const int group = p.group;
-  const int rows = item.q_tokens * group;
-  // keys this item covers: from key_begin up to the position of its last query token
-  // (and key_end, when the item is one part of a split)
-  int kv_end = min(item.kv_len, item.pos0 + item.q_tokens);
-  if (item.key_end > 0) kv_end = min(kv_end, item.key_end);
-  const int n_tiles = max(0, (kv_end - item.key_begin + kKeysPerTile - 1) / kKeysPerTile);
-  const bool rep = p.rep_ok && rows <= 32;
+  AttnWork w;
+  w.q_map = &p.q_map;
+  w.q_map_small = &p.q_map_small;
+  w.k_map = &p.k_map;
+  w.v_map = &p.v_map;
+  w.block_table = p.block_table;
+  w.out = p.out;
+  w.ws_o = p.ws_o;
+  w.ws_ml = p.ws_ml;
+  w.trace = (p.pad && blockIdx.x == 0) ? g_attn_trace : nullptr;
+  w.scale_log2 = p.scale_log2;
+  w.bt_stride = p.bt_stride;
+  w.hq = p.hq;
+  w.group = p.group;
+  w.page = p.page;
+  w.q_box_rows = p.q_box_rows;
+  w.rep_ok = p.rep_ok;
+  w.item = p.items[blockIdx.x];
+  AttnCtx c;
+  c.sh = &sh;
+  c.abort_flag = &sh.abort_flag;
+  c.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  attn_derive(w, c);
 
   if (threadIdx.x == 0) {
-    mbar_init(&sh.q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh.k_full[i], 1);
-      mbar_init(&sh.v_full[i], 1);
-      mbar_init(&sh.k_empty[i], 1);
-      mbar_init(&sh.v_empty[i], 1);
-      mbar_init(&sh.s_full[i], 1);
-      mbar_init(&sh.p_full[i], 128);
-      mbar_init(&sh.o_full[i], 1);   // P V of tile j completes phase j / 2 of o_full[j % 2]
-    }
     sh.abort_flag = 0;
-    fence_barrier_init();
+    attn_barriers_init(sh);
   }
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, kAttnTmemCols);
@@ -444,105 +85,17 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = sh.tmem_base;
-  const uint32_t tmem_o = tmem_base + 256;   // S buffers at columns 0 and 128
+  c.tmem_base = sh.tmem_base;
 
   if (warp == 0) {
-    // --------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      if (rep) {
-        // the same 32 rows into every lane quadrant of the M dimension
-        mbar_arrive_expect_tx(&sh.q_full, kTileBytes);
-        for (int q = 0; q < 4; ++q) {
-          tma_load_3d_plain(sQ + q * 4096, &p.q_map_small, &sh.q_full, 0, item.kv_head * group, item.q_row0);
-          tma_load_3d_plain(sQ + kHalfBytes + q * 4096, &p.q_map_small, &sh.q_full, 64, item.kv_head * group,
-                            item.q_row0);
-        }
-      } else {
-        mbar_arrive_expect_tx(&sh.q_full, 2u * p.q_box_rows * 128u);
-        tma_load_3d_plain(sQ, &p.q_map, &sh.q_full, 0, item.kv_head * group, item.q_row0);
-        tma_load_3d_plain(sQ + kHalfBytes, &p.q_map, &sh.q_full, 64, item.kv_head * group, item.q_row0);
-      }
-    }
-    const int pages_per_tile = kKeysPerTile / p.page;
-    const int page_bytes = p.page * 128;   // one d half of one page
-    const int last_page = (kv_end - 1) / p.page;
-    const int tile0 = item.key_begin / kKeysPerTile;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
-      const uint32_t prev = ((j >> 1) - 1) & 1;
-      if (j >= 2 && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) break;
-      if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
-      __syncwarp();
-      int page_id = 0;
-      if (lane < pages_per_tile) {
-        // pages past the visible range repeat the last visible page; their keys are masked
-        const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
-        page_id = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
-        uint8_t* k = sK + s * kTileBytes + lane * page_bytes;
-        tma_load_4d(k, &p.k_map, &sh.k_full[s], 0, item.kv_head, 0, page_id);
-        tma_load_4d(k + kHalfBytes, &p.k_map, &sh.k_full[s], 64, item.kv_head, 0, page_id);
-      }
-      if (j >= 2 && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) break;
-      if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
-      __syncwarp();
-      if (lane < pages_per_tile) {
-        uint8_t* v = sV + s * kTileBytes + lane * page_bytes;
-        tma_load_4d(v, &p.v_map, &sh.v_full[s], 0, item.kv_head, 0, page_id);
-        tma_load_4d(v + kHalfBytes, &p.v_map, &sh.v_full[s], 64, item.kv_head, 0, page_id);
-      }
-    }
+    attn_produce(w, c);
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issue
-    if (lane == 0) {   // one thread issues: its waits are the plain per-thread ones
-      // S = Q K^T: both K-major; O += P V: A K-major, B (V) MN-major
-      const uint32_t idesc_s = umma_idesc_bf16(128, 128);
-      const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
-      const uint32_t q_addr = smem_u32(sQ);
-      bool ok = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnWaitNs);
-      auto mma_s = [&](int j) {
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&sh.k_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) return false;
-        // S[s] is free once the softmax threads have turned tile j - 2 into P
-        if (j >= 2 && !mbar_wait_bounded(&sh.p_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) return false;
-        tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          umma_bf16(tmem_base + s * 128, desc_kmajor(q_addr, i), desc_kmajor(k_addr, i), idesc_s, i != 0);
-        umma_commit(&sh.s_full[s]);
-        umma_commit(&sh.k_empty[s]);
-        return true;
-      };
-      if (ok && n_tiles > 0) ok = mma_s(0);
-      if (ok && n_tiles > 1) ok = mma_s(1);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&sh.v_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) break;
-        if (!mbar_wait_bounded(&sh.p_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) break;
-        tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + s * kTileBytes);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          umma_bf16(tmem_o, desc_kmajor(p_addr, i), desc_v_mnmajor(v_addr, i), idesc_o, (j | i) != 0);
-        umma_commit(&sh.o_full[s]);
-        umma_commit(&sh.v_empty[s]);
-        if (j + 2 < n_tiles && !mma_s(j + 2)) break;
-      }
-    }
+    if (lane == 0) attn_mma(w, c);
     __syncwarp();
+  } else if (c.rep) {
+    softmax_role<32>(w, c);
   } else {
-    // ------------------------------------------------------ softmax / output
-    SoftmaxCtx c;
-    c.sh = &sh;
-    c.sP = sP;
-    c.scratch = reinterpret_cast<float*>(sK);
-    c.tmem_base = tmem_base;
-    c.n_tiles = n_tiles;
-    c.rows = rows;
-    c.kv_end = kv_end;
-    if (rep) softmax_role<32>(p, item, c);
-    else softmax_role<128>(p, item, c);
+    softmax_role<128>(w, c);
   }
 
   tc_fence_before_sync();
@@ -550,7 +103,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   if (threadIdx.x == 0 && sh.abort_flag) atomicOr(p.status, kErrWaitTimeout);
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kAttnTmemCols);
+    tmem_dealloc(c.tmem_base, kAttnTmemCols);
   }
 }
 
