@@ -308,6 +308,14 @@ int monofab_fabric_trace_count(monofab_fabric* f, uint32_t* count);
  * time each state began (Fabric.worker_tiles, csrc/bindings.cpp:266-281). */
 int monofab_fabric_worker_tiles(monofab_fabric* f, uint64_t* words, uint64_t* since_ns);
 
+/* Where each worker's roles were waiting when the worker left after a bounded wait ran
+ * out: 256 x 4 words (zero for workers that never did): [0] TMA producer, [1] MMA, [2] first
+ * exec warp, each record << 48 | q phases << 40 | phases[0] << 32 | phases[1] << 24 |
+ * tile << 8 | wait site; [3] records finished by the exec warps | by the MMA warp << 32.
+ * The counterpart of the reference's per-warp wait notes (wait_note_address,
+ * csrc/bindings.cpp:182, csrc/fabric/runtime.cuh:511-555). */
+int monofab_fabric_wait_notes(monofab_fabric* f, uint64_t* notes);
+
 /* Device end times of `count` iterations of a lane after iteration `start`, taken
  * from the in-kernel timer (Fabric.iteration_times, csrc/host/fabric.cpp:380-403). */
 int monofab_fabric_iteration_times(monofab_fabric* f, int lane, uint64_t start, int count, double timeout_s,

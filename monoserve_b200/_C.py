@@ -24,7 +24,7 @@ EXPORTS = [
     "monofab_fabric_create", "monofab_fabric_destroy", "monofab_fabric_info", "monofab_fabric_start",
     "monofab_fabric_stop", "monofab_fabric_set_limits", "monofab_fabric_upload", "monofab_fabric_release",
     "monofab_fabric_program_info", "monofab_fabric_publish", "monofab_fabric_progress", "monofab_fabric_lane_stats",
-    "monofab_fabric_reset_inflight_max", "monofab_fabric_read", "monofab_fabric_write", "monofab_fabric_blob_alloc",
+    "monofab_fabric_reset_inflight_max", "monofab_fabric_wait_notes", "monofab_fabric_read", "monofab_fabric_write", "monofab_fabric_blob_alloc",
     "monofab_fabric_blob_free", "monofab_fabric_set_trace", "monofab_fabric_trace_count",
     "monofab_fabric_worker_tiles", "monofab_fabric_iteration_times", "monofab_fabric_tensor_map", "monofab_fabric_tensor_map_packed",
 ]
@@ -96,6 +96,7 @@ def _load():
     lib.monofab_fabric_set_trace.argtypes = [vp, u64, u32]
     lib.monofab_fabric_trace_count.argtypes = [vp, P(u32)]
     lib.monofab_fabric_worker_tiles.argtypes = [vp, vp, vp]
+    lib.monofab_fabric_wait_notes.argtypes = [vp, vp]
     lib.monofab_fabric_iteration_times.argtypes = [vp, i32, u64, i32, ctypes.c_double, vp]
     lib.monofab_fabric_tensor_map.argtypes = [vp, u64, vp, vp, vp, i32, i32, i32, P(u64)]
     lib.monofab_fabric_tensor_map_packed.argtypes = [vp, u64, i32]

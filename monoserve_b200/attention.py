@@ -107,3 +107,31 @@ def paged_attention(q, k_cache, v_cache, block_table, req_info, out=None, stream
     every (request, block, KV head) in one work item.  Returns bf16 [T, hq, 128]."""
     plan = AttentionPlan(req_info, q.shape[1], k_cache.shape[2], split=split, part_tiles=part_tiles)
     return plan.run(q, k_cache, v_cache, block_table, out=out, stream=stream)
+
+
+K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE = 33, 34, 35
+
+
+def fabric_maps(fab, q, k_cache, v_cache):
+    """Tensor maps of q and the paged caches in a fabric's table: (q_map, q_map_small or 0, k_map, v_map)."""
+    T, hq, _ = q.shape
+    n_pages, page, hkv, _ = k_cache.shape
+    group = hq // hkv
+    dims, strides = [128, hq, T], [256, hq * 256]
+    q_map = fab.tensor_map(q.data_ptr(), dims, strides, [64, group, 128 // group])
+    q_small = fab.tensor_map(q.data_ptr(), dims, strides, [64, group, 32 // group]) if 32 % group == 0 else 0
+    kd, ks, kb = [128, hkv, page, n_pages], [256, hkv * 256, page * hkv * 256], [64, 1, page, 1]
+    return q_map, q_small, fab.tensor_map(k_cache.data_ptr(), kd, ks, kb), fab.tensor_map(v_cache.data_ptr(), kd, ks, kb)
+
+
+def fabric_tiles(items, merge, args_ptr, kind=K_ATTN_PREFILL):
+    """The work list of plan_items as fabric tiles: (attention item tiles, merge tiles).
+    Tile fields: see make_attn_work / tile_attn_merge in csrc/fabric_seq_tiles.cuh."""
+    from monoserve_b200.fabric import Tile
+    tiles = []
+    for req, h, row0, n, pos0, kv_len, k0, k1, ws, *_ in items.tolist():
+        tiles.append(Tile(kind, i=(row0, n | (h << 16), k0, max(k1, 0)),
+                          a=(args_ptr, req | ((ws + 1) << 32), pos0 | (kv_len << 32))))
+    merges = [Tile(K_ATTN_MERGE, i=(row0, n | (h << 16), ws, parts | (stride << 16)), a=(args_ptr,))
+              for row0, n, h, ws, parts, stride, *_ in merge.tolist()]
+    return tiles, merges

@@ -72,10 +72,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   c.sh = &sh;
   c.abort_flag = &sh.abort_flag;
   c.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  c.q_phase = 0;
+  c.note = nullptr;
+  c.base[0] = c.base[1] = 0;
   attn_derive(w, c);
 
   if (threadIdx.x == 0) {
     sh.abort_flag = 0;
+    sh.fail_site = 0;
     attn_barriers_init(sh);
   }
   if (warp == 1) {
@@ -90,12 +94,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   if (warp == 0) {
     attn_produce(w, c);
   } else if (warp == 1) {
-    if (lane == 0) attn_mma(w, c);
+    if (lane == 0) attn_mma<2>(w, c);
     __syncwarp();
   } else if (c.rep) {
-    softmax_role<32>(w, c);
+    softmax_role<32, 2>(w, c);
   } else {
-    softmax_role<128>(w, c);
+    softmax_role<128, 2>(w, c);
   }
 
   tc_fence_before_sync();
@@ -113,30 +117,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
 __global__ void attention_combine_kernel(const int32_t* __restrict__ items, int n_items, const float* __restrict__ ws_o,
                                          const float2* __restrict__ ws_ml, __nv_bfloat16* __restrict__ out, int hq,
                                          int group) {
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int32_t* it = items + static_cast<size_t>(blockIdx.x) * 8;
-  const int q_row0 = it[0], q_tokens = it[1], kv_head = it[2], ws_row0 = it[3], parts = it[4], stride = it[5];
-  for (int row = wid; row < q_tokens * group; row += blockDim.x >> 5) {
-    float M = -1e30f;
-    for (int q = 0; q < parts; ++q) M = fmaxf(M, ws_ml[ws_row0 + q * stride + row].x);
-    float L = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int q = 0; q < parts; ++q) {
-      const float2 ml = ws_ml[ws_row0 + q * stride + row];
-      const float w = fast_exp2(ml.x - M);
-      L += ml.y * w;
-      const float4 t = reinterpret_cast<const float4*>(ws_o + static_cast<size_t>(ws_row0 + q * stride + row) * kHeadDim)[lane];
-      acc.x += t.x * w;
-      acc.y += t.y * w;
-      acc.z += t.z * w;
-      acc.w += t.w * w;
-    }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    const int token = row / group, head = kv_head * group + row % group;
-    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(acc.x * inv, acc.y * inv), __floats2bfloat162_rn(acc.z * inv, acc.w * inv)};
-    reinterpret_cast<uint2*>(out + (static_cast<size_t>(q_row0 + token) * hq + head) * kHeadDim)[lane] =
-        *reinterpret_cast<const uint2*>(h);
-  }
+  attn_merge_rows(it[0], it[1], it[2], it[3], it[4], it[5], ws_o, ws_ml, out, hq, group, threadIdx.x >> 5, blockDim.x >> 5);
 }
 
 cudaError_t launch_attention_combine(const int32_t* items, int n_items, const float* ws_o, const float2* ws_ml,

@@ -25,7 +25,17 @@ struct AttnShared {
   uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
+  unsigned int fail_site;   // diagnostics: which wait gave up first (kAttnSite*), 0 = none
 };
+// Wait sites, for the diagnostics word.
+enum : unsigned int {
+  kAttnSiteProdK = 1, kAttnSiteProdV, kAttnSiteMmaQ, kAttnSiteMmaK, kAttnSiteMmaSFree, kAttnSiteMmaV, kAttnSiteMmaP,
+  kAttnSiteSmaxS, kAttnSiteSmaxRescale, kAttnSiteSmaxPFree, kAttnSiteSmaxFinal, kAttnSiteMmaTail,
+};
+__device__ __forceinline__ bool attn_gave_up(AttnShared& sh, unsigned int site) {
+  atomicCAS(&sh.fail_site, 0u, site);
+  return false;
+}
 constexpr int kPartLd = 132;   // fp32 row stride of the merge scratch (conflict-free float4 access)
 constexpr int kPartFloats = 4 * 32 * kPartLd;   // then float2 [4][32]: (max, sum) of the four column quarters
 
@@ -53,7 +63,26 @@ struct AttnCtx {
   uint32_t tmem_base;     // 384 columns: S x2, O
   int n_tiles, rows, kv_end;
   bool rep;
+  // Phases the barriers have completed before this item: the barriers are armed once per
+  // CTA and a CTA that works on many items (a fabric worker) carries the counts along.
+  uint32_t q_phase;       // q_full
+  uint32_t base[2];       // every per-tile barrier [s]: tiles of parity s so far
+  volatile unsigned int* note;   // this role's wait note (tile << 8 | site), or NULL
 };
+
+__device__ __forceinline__ void attn_note(const AttnCtx& c, int j, unsigned int site) {
+  if (c.note) *c.note = (static_cast<unsigned int>(j) << 8) | site;
+}
+
+// Parity of the phase that tile j of the current item completes on a per-tile barrier [j & 1].
+__device__ __forceinline__ uint32_t attn_parity(const AttnCtx& c, int j) { return (c.base[j & 1] + (j >> 1)) & 1u; }
+
+// After an item of n_tiles tiles, every role advances its copy of the phase counts.
+__device__ __forceinline__ void attn_advance(int n_tiles, uint32_t& q_phase, uint32_t (&base)[2]) {
+  q_phase += 1;
+  base[0] += (n_tiles + 1) >> 1;
+  base[1] += n_tiles >> 1;
+}
 
 __device__ __forceinline__ void attn_derive(const AttnWork& w, AttnCtx& c) {
   const AttnItem& item = w.item;
@@ -67,7 +96,7 @@ __device__ __forceinline__ void attn_derive(const AttnWork& w, AttnCtx& c) {
   c.rep = w.rep_ok && c.rows <= 32;
 }
 
-// By one thread, while no other thread uses the barriers; followed by a CTA-level hand-over.
+// By one thread, once per CTA, before a CTA-wide barrier.
 __device__ __forceinline__ void attn_barriers_init(AttnShared& sh) {
   mbar_init(&sh.q_full, 1);
   for (int i = 0; i < 2; ++i) {
@@ -183,8 +212,9 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
   const int tile0 = item.key_begin / kKeysPerTile;
   for (int j = 0; j < n_tiles; ++j) {
     const int s = j & 1;
-    const uint32_t prev = ((j >> 1) - 1) & 1;
-    if (j >= 2 && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) break;
+    const uint32_t prev = j >= 2 ? attn_parity(c, j - 2) : 0u;   // the stage's previous use: tile j - 2
+    if (lane == 0) attn_note(c, j, kAttnSiteProdK);
+    if (j >= 2 && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
     if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
     __syncwarp();
     int page_id = 0;
@@ -196,7 +226,8 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
       tma_load_4d(k, p.k_map, &sh.k_full[s], 0, item.kv_head, 0, page_id);
       tma_load_4d(k + kHalfBytes, p.k_map, &sh.k_full[s], 64, item.kv_head, 0, page_id);
     }
-    if (j >= 2 && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) break;
+    if (lane == 0) attn_note(c, j, kAttnSiteProdV);
+    if (j >= 2 && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
     if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
     __syncwarp();
     if (lane < pages_per_tile) {
@@ -208,6 +239,9 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
 }
 
 // The MMA role: one thread calls it; its waits are the plain per-thread ones.
+// PB = P buffers in shared memory (2: the stand-alone kernel; 1: inside the fabric
+// worker, whose operand ring holds six 32 KB tiles).
+template <int PB>
 __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
@@ -222,12 +256,16 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
     const uint32_t idesc_s = umma_idesc_bf16(128, 128);
     const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
     const uint32_t q_addr = smem_u32(sQ);
-    bool ok = mbar_wait_bounded(&sh.q_full, 0, abort_flag, kAttnWaitNs);
+    attn_note(c, 0, kAttnSiteMmaQ);
+    bool ok = mbar_wait_bounded(&sh.q_full, c.q_phase & 1u, abort_flag, kAttnWaitNs) || attn_gave_up(sh, kAttnSiteMmaQ);
     auto mma_s = [&](int j) {
       const int s = j & 1;
-      if (!mbar_wait_bounded(&sh.k_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) return false;
+      attn_note(c, j, kAttnSiteMmaK);
+      if (!mbar_wait_bounded(&sh.k_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) return attn_gave_up(sh, kAttnSiteMmaK);
+      attn_note(c, j, kAttnSiteMmaSFree);
       // S[s] is free once the softmax threads have turned tile j - 2 into P
-      if (j >= 2 && !mbar_wait_bounded(&sh.p_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) return false;
+      if (j >= 2 && !mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j - 2), abort_flag, kAttnWaitNs))
+        return attn_gave_up(sh, kAttnSiteMmaSFree);
       tc_fence_after_sync();
       const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
 #pragma unroll
@@ -241,16 +279,27 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
     if (ok && n_tiles > 1) ok = mma_s(1);
     for (int j = 0; ok && j < n_tiles; ++j) {
       const int s = j & 1;
-      if (!mbar_wait_bounded(&sh.v_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) break;
-      if (!mbar_wait_bounded(&sh.p_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) break;
+      attn_note(c, j, kAttnSiteMmaV);
+      if (!mbar_wait_bounded(&sh.v_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaV); break; }
+      attn_note(c, j, kAttnSiteMmaP);
+      if (!mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaP); break; }
       tc_fence_after_sync();
-      const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + s * kTileBytes);
+      const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + (j % PB) * kTileBytes);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         umma_bf16(tmem_o, desc_kmajor(p_addr, i), desc_v_mnmajor(v_addr, i), idesc_o, (j | i) != 0);
       umma_commit(&sh.o_full[s]);
       umma_commit(&sh.v_empty[s]);
       if (j + 2 < n_tiles && !mma_s(j + 2)) break;
+    }
+    // Leave only after the last commits have arrived on their barriers: a caller that re-arms
+    // the barriers for its next item must not see a late arrival from this one.
+    for (int j = max(0, n_tiles - 2); ok && j < n_tiles; ++j) {
+      attn_note(c, j, kAttnSiteMmaTail);
+      ok = (mbar_wait_bounded(&sh.k_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+            attn_gave_up(sh, kAttnSiteMmaTail)) &&
+           (mbar_wait_bounded(&sh.v_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+            attn_gave_up(sh, kAttnSiteMmaTail + 16));
     }
   }
 }
@@ -260,7 +309,7 @@ __device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sy
 // The softmax / output role of the four warps 2..5.  NC = key columns of a tile one
 // thread handles: 128 (a thread owns one of 128 query rows) or 32 (quad-replicated item:
 // the thread's row is lane, its columns are quarter `quad` of the tile).
-template <int NC>
+template <int NC, int PB>
 __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c) {
   constexpr bool kRep = NC == 32;
   AttnShared& sh = *c.sh;
@@ -297,7 +346,7 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   };
   if (kRep) {
     // columns outside this thread's quarter stay zero in both P buffers
-    for (int b = 0; b < 2; ++b)
+    for (int b = 0; b < PB; ++b)
       for (int h = 0; h < 2; ++h) {
         uint4* row = reinterpret_cast<uint4*>(sP + b * kTileBytes + h * kHalfBytes + r * 128);
 #pragma unroll
@@ -306,7 +355,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   }
   for (int j = 0; ok && j < n_tiles; ++j) {
     const int s = j & 1;
-    if (!warp_wait(&sh.s_full[s], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+    if (lane == 0) attn_note(c, j, kAttnSiteSmaxS);
+    if (!warp_wait(&sh.s_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxS); break; }
     tc_fence_after_sync();
     lap(0);
     if (!warp_active) {   // no row of this warp exists: keep the barrier protocol only
@@ -334,7 +384,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     lap(1);
     // a row whose maximum grew rescales its part of O in TMEM, once the previous P V has landed
     if (j > 0 && __any_sync(0xffffffffu, mx > m)) {
-      if (!warp_wait(&sh.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+      if (lane == 0) attn_note(c, j, kAttnSiteSmaxRescale);
+      if (!warp_wait(&sh.o_full[s ^ 1], attn_parity(c, j - 1), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxRescale); break; }
       tc_fence_after_sync();
       const float alpha = fast_exp2(m - mx);
 #pragma unroll
@@ -352,12 +403,13 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     }
     m = mx;
     lap(3);
-    // the P buffer is free once P V of tile j - 2 has completed
-    if (j >= 2 && !warp_wait(&sh.o_full[s], ((j >> 1) - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+    // the P buffer is free once P V of tile j - PB has completed
+    if (lane == 0) attn_note(c, j, kAttnSiteSmaxPFree);
+    if (j >= PB && !warp_wait(&sh.o_full[(j - PB) & 1], attn_parity(c, j - PB), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxPFree); break; }
     const float neg_mx = -mx;
     // P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
     float sum0 = 0.f, sum1 = 0.f;
-    uint8_t* p_tile = sP + s * kTileBytes;
+    uint8_t* p_tile = sP + (j % PB) * kTileBytes;
 #pragma unroll
     for (int c0 = 0; c0 < NC; c0 += 32) {
       uint32_t packed[16];
@@ -400,8 +452,10 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     mbar_arrive(&sh.p_full[s]);
     lap(2);
   }
+  if (lane == 0) attn_note(c, n_tiles, kAttnSiteSmaxFinal);
   if (ok && n_tiles > 0)
-    ok = warp_wait(&sh.o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, kAttnWaitNs);
+    ok = warp_wait(&sh.o_full[(n_tiles - 1) & 1], attn_parity(c, n_tiles - 1), abort_flag, kAttnWaitNs) ||
+         attn_gave_up(sh, kAttnSiteSmaxFinal);
   tc_fence_after_sync();
   lap(4);
   if (tr) {
@@ -519,5 +573,35 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
 }
 
 
+
+// Merge of the parts of one split (request, block, KV head): one warp per output row
+// (token, q head of the group), parts added in part order.  `warp` of `n_warps` warps.
+__device__ __forceinline__ void attn_merge_rows(int q_row0, int q_tokens, int kv_head, int ws_row0, int parts, int stride,
+                                                const float* __restrict__ ws_o, const float2* __restrict__ ws_ml,
+                                                __nv_bfloat16* __restrict__ out, int hq, int group, int warp,
+                                                int n_warps) {
+  const int lane = threadIdx.x & 31;
+  for (int row = warp; row < q_tokens * group; row += n_warps) {
+    float M = -1e30f;
+    for (int q = 0; q < parts; ++q) M = fmaxf(M, ws_ml[ws_row0 + q * stride + row].x);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < parts; ++q) {
+      const float2 ml = ws_ml[ws_row0 + q * stride + row];
+      const float w = fast_exp2(ml.x - M);
+      L += ml.y * w;
+      const float4 t = reinterpret_cast<const float4*>(ws_o + static_cast<size_t>(ws_row0 + q * stride + row) * kHeadDim)[lane];
+      acc.x += t.x * w;
+      acc.y += t.y * w;
+      acc.z += t.z * w;
+      acc.w += t.w * w;
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int token = row / group, head = kv_head * group + row % group;
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(acc.x * inv, acc.y * inv), __floats2bfloat162_rn(acc.z * inv, acc.w * inv)};
+    reinterpret_cast<uint2*>(out + (static_cast<size_t>(q_row0 + token) * hq + head) * kHeadDim)[lane] =
+        *reinterpret_cast<const uint2*>(h);
+  }
+}
 
 }  // namespace mf

@@ -20,13 +20,16 @@
 //     and epoch refreshes overlap the previous tile; warps 1..4 execute tiles and
 //     are the epilogue of GEMM tiles; warp 5 issues the TMA copies and warp 6 owns
 //     TMEM and issues tcgen05.mma (gemm_core.cuh), with accumulators double-buffered
-//     across consecutive GEMM tiles;
+//     across consecutive GEMM tiles; an attention work item (attention_core.cuh) uses
+//     the same three roles with the operand ring as its Q / K / V / P tiles, after the
+//     worker's earlier tiles have drained;
 //   * no wait is unbounded and nothing traps: a ring publication that waits too
 //     long, a full worklist or an unknown tile kind raise an error bit that the
 //     host reads from the mirror, and the kernel leaves by itself after
 //     max_run_ns, so a fabric that owns every SM can always be stopped.
 #include <cuda_runtime.h>
 
+#include "attention_core.cuh"
 #include "fabric_types.h"
 #include "gemm_core.cuh"
 #include "operands.h"
@@ -95,8 +98,9 @@ struct WorkerState {
 struct WorkSlot {
   TileDesc tile;
   GemmWork gemm;          // filled by the scheduler for GEMM tiles
+  AttnWork attn;          // filled by the scheduler for attention work items
   const ProgramDesc* prog;
-  uint32_t stage, tile_lane, link, index, cmd, worker_lane, is_gemm, pad;
+  uint32_t stage, tile_lane, link, index, cmd, worker_lane, is_gemm, is_attn;
 };
 
 // A GEMM tile (kind 32) in the reference's operand convention
@@ -489,6 +493,16 @@ __device__ uint32_t schedule(DeviceState& S, WorkerState& ws) {
 
 // ---------------------------------------------------------------- core tiles
 __device__ __forceinline__ void exec_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kExecThreads) : "memory"); }
+// Barrier of the exec threads that also tells each whether `v` held in all of them.
+__device__ __forceinline__ bool exec_all(bool v) {
+  int r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred p, 1, %2, q;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<int>(v)), "n"(kExecThreads)
+      : "memory");
+  return r != 0;
+}
 
 __device__ void trace_tile(unsigned long long base, uint32_t idx, unsigned long long t0, unsigned long long t1,
                            uint32_t lane, uint32_t worker) {
@@ -501,6 +515,17 @@ __device__ void trace_tile(unsigned long long base, uint32_t idx, unsigned long 
   r->lane = lane;
   atomicAdd(&r->count, 1u);
 }
+
+// Scratch of the tile the exec warps are running; tiles run one at a time per worker,
+// so they share one block instead of each holding static shared memory of its own.
+constexpr int kExecScratchInts = 4 * (kMaxExperts + 1) + 16;
+__shared__ int s_exec_scratch[kExecScratchInts];
+
+}  // namespace fab
+}  // namespace mf
+#include "fabric_seq_tiles.cuh"
+namespace mf {
+namespace fab {
 
 __device__ void tile_router(const TileDesc& t, int tid);
 __device__ void tile_norm(const TileDesc& t, int tid, bool add);
@@ -579,6 +604,21 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
     case kTileAddNorm:
       tile_norm(t, tid, true);
       return true;
+    case kTileAttnMerge:
+      tile_attn_merge(t, tid);
+      return true;
+    case kTileQkRope:
+      tile_qk_rope(t, tid);
+      return true;
+    case kTileEmbed:
+      tile_embed(t, tid);
+      return true;
+    case kTileSample:
+      tile_sample(t, tid);
+      return true;
+    case kTileAttnPlan:
+      tile_attn_plan(t, w.prog, S, tid);
+      return true;
     default:
       return false;
   }
@@ -595,8 +635,9 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
 // writes the stable rank of every (token, pick) pair inside (chunk, expert) and the
 // chunk's per-expert pair counts, which make the pack order deterministic.
 __device__ void tile_router(const TileDesc& t, int tid) {
-  __shared__ int s_ids[kFabChunk * kMaxTopK];
-  __shared__ int s_hist[kMaxExperts];
+  int* const s_ids = s_exec_scratch;                             // [kFabChunk * kMaxTopK]
+  int* const s_hist = s_exec_scratch + kFabChunk * kMaxTopK;     // [kMaxExperts]
+  static_assert(kFabChunk * kMaxTopK + kMaxExperts <= kExecScratchInts, "router scratch");
   const RouterArgs& A = *reinterpret_cast<const RouterArgs*>(t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int E = static_cast<int>(A.E), K = static_cast<int>(A.K);
@@ -763,8 +804,14 @@ __device__ void tile_combine(const TileDesc& t, int tid) {
 // blocks (one pass over the weights) instead of K-split tiles with a reduce stage;
 // an overflow of the dynamic region raises an error bit instead of trapping.
 __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid) {
-  __shared__ int s_cnt[kMaxExperts], s_start[kMaxExperts + 1], s_n[kMaxExperts], s_off[kMaxExperts + 1];
-  __shared__ int s_form, s_active, s_skipped, s_overflow;
+  int* const s_cnt = s_exec_scratch;                              // [kMaxExperts]
+  int* const s_start = s_cnt + kMaxExperts + 1;                   // [kMaxExperts + 1]
+  int* const s_n = s_start + kMaxExperts + 1;                     // [kMaxExperts]
+  int* const s_off = s_n + kMaxExperts + 1;                       // [kMaxExperts + 1]
+  int& s_form = s_exec_scratch[4 * (kMaxExperts + 1)];
+  int& s_active = s_exec_scratch[4 * (kMaxExperts + 1) + 1];
+  int& s_skipped = s_exec_scratch[4 * (kMaxExperts + 1) + 2];
+  int& s_overflow = s_exec_scratch[4 * (kMaxExperts + 1) + 3];
   const ExpandArgs& A = *reinterpret_cast<const ExpandArgs*>(t.a[0]);
   const int E = static_cast<int>(A.E);
   if (E < 1 || E > kMaxExperts) return;
@@ -968,9 +1015,54 @@ __device__ void note_tile(DeviceState& S, uint32_t worker, const WorkSlot& w, un
   if (state) S.worker_tile_ns[worker] = globaltimer_ns();
 }
 
+// Wait (whole warp or a single thread) until a counter in shared memory that another
+// role of this worker advances has reached `target`; bounded like every other wait.
+__device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, volatile int* abort_flag) {
+  const volatile unsigned int* c = counter;
+  if (static_cast<int>(*c - target) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t spins = 0;; ++spins) {
+    if (static_cast<int>(*c - target) >= 0) return true;
+    __nanosleep(32);
+    if ((spins & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kAttnWaitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ unsigned long long role_ctx(uint32_t rec, uint32_t q_phase, const uint32_t (&base)[2]) {
+  return (static_cast<unsigned long long>(rec & 0xffffu) << 48) | (static_cast<unsigned long long>(q_phase & 0xffu) << 40) |
+         (static_cast<unsigned long long>(base[0] & 0xffu) << 32) | (static_cast<unsigned long long>(base[1] & 0xffu) << 24);
+}
+
+__device__ __forceinline__ AttnCtx attn_ctx(const AttnWork& w, AttnShared& sh, volatile int* abort_flag, uint8_t* ring,
+                                            uint32_t tmem_base, uint32_t q_phase, const uint32_t (&base)[2],
+                                            volatile unsigned int* note) {
+  AttnCtx c;
+  c.note = note;
+  c.q_phase = q_phase;
+  c.base[0] = base[0];
+  c.base[1] = base[1];
+  c.sh = &sh;
+  c.abort_flag = abort_flag;
+  c.smem = ring;
+  c.tmem_base = tmem_base;
+  attn_derive(w, c);
+  return c;
+}
+
 struct WorkerShared {
   uint64_t slot_full[2], slot_empty[2];
   GemmBarriers bar;
+  AttnShared attn;              // barriers of attention items, armed once; every role counts their phases
+  unsigned int wait_note[3];    // producer, MMA, first exec warp: tile << 8 | site of the current wait
+  unsigned long long wait_ctx[3];   // and the record / phase counts the role had then
+  unsigned int tiles_done;      // work records the exec warps have finished
+  unsigned int mma_done;        // work records the MMA warp has finished
   WorkSlot slot[2];
   WorkerState ws;
   unsigned long long t0;
@@ -994,6 +1086,12 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     }
     gemm_barriers_init(sh.bar);
     sh.abort_flag = 0;
+    sh.attn.fail_site = 0;
+    sh.wait_note[0] = sh.wait_note[1] = sh.wait_note[2] = 0;
+    sh.wait_ctx[0] = sh.wait_ctx[1] = sh.wait_ctx[2] = 0;
+    attn_barriers_init(sh.attn);
+    sh.tiles_done = 0;
+    sh.mma_done = 0;
     sh.ws.epoch = ~0ull;
     sh.ws.worker = worker;
     sh.ws.slot_lane = kNoLane;
@@ -1056,7 +1154,15 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           w.index = ws.next_index;
           w.worker_lane = ws.lane;
           w.is_gemm = 0;
-          if (w.tile.kind == kTileGemm) {
+          w.is_attn = 0;
+          if (w.tile.kind == kTileAttnPrefill || w.tile.kind == kTileAttnDecode) {
+            if (make_attn_work(w.tile, w.attn)) {
+              w.is_attn = 1;
+            } else {
+              raise_error(S, kFabErrBadTile);
+              w.tile.kind = kTileNop;
+            }
+          } else if (w.tile.kind == kTileGemm) {
             if (make_gemm_work(w.tile, w.gemm)) {
               w.is_gemm = 1;
             } else {
@@ -1076,13 +1182,32 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
     GemmPipe pipe;
     GemmInflight inflight;
+    bool prev_attn = false;
+    uint32_t aq = 0, ab[2] = {0, 0};   // phases the attention barriers have completed
     for (uint32_t n = 0;; ++n) {
       const int s = n & 1;
       if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       bool ok = true;
-      if (w.is_gemm) ok = gemm_produce(w.gemm, ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x);
+      // An attention item uses the whole operand ring and TMEM outside the GEMM pipe's
+      // bookkeeping: it starts once every earlier record of this worker is finished, and
+      // the record after it waits for it in the same way.
+      if ((w.is_attn || prev_attn) && lane == 0) {
+        sh.wait_note[0] = 13;
+        sh.wait_ctx[0] = role_ctx(n, aq, ab);
+      }
+      if (w.is_attn || prev_attn)
+        ok = __all_sync(0xffffffffu, (wait_counter(&sh.tiles_done, n, abort_flag) || attn_gave_up(sh.attn, 13)) &&
+                                         (wait_counter(&sh.mma_done, n, abort_flag) || attn_gave_up(sh.attn, 14)));
+      prev_attn = w.is_attn != 0;
+      if (ok && w.is_attn) {
+        AttnCtx c = attn_ctx(w.attn, sh.attn, abort_flag, ring, tmem_base, aq, ab, &sh.wait_note[0]);
+        attn_produce(w.attn, c);
+        attn_advance(c.n_tiles, aq, ab);
+      } else if (ok && w.is_gemm) {
+        ok = gemm_produce(w.gemm, ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.slot_empty[s]);
       if (!ok) break;
@@ -1091,23 +1216,36 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     // ------------------------------------------------------------ MMA issue
     GemmPipe pipe;
     uint32_t g = 0;   // GEMM tiles seen: accumulator buffer and parity
+    uint32_t aq = 0, ab[2] = {0, 0};
     for (uint32_t n = 0;; ++n) {
       const int s = n & 1;
       if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       bool ok = true;
-      if (w.is_gemm) {
+      if (w.is_attn) {
+        // the item's loads are issued only after the worker's earlier records have drained,
+        // so waiting for them is all the ordering this role needs
+        AttnCtx c = attn_ctx(w.attn, sh.attn, abort_flag, ring, tmem_base, aq, ab, &sh.wait_note[1]);
+        if (lane == 0) sh.wait_ctx[1] = role_ctx(n, aq, ab);
+        if (lane == 0) attn_mma<1>(w.attn, c);
+        __syncwarp();
+        attn_advance(c.n_tiles, aq, ab);
+      } else if (w.is_gemm) {
         ok = gemm_mma(w.gemm, ring, sh.bar, pipe, tmem_base, g & 1, (g >> 1) & 1, abort_flag);
         ++g;
       }
-      if (lane == 0) mbar_arrive(&sh.slot_empty[s]);
+      if (lane == 0) {
+        *reinterpret_cast<volatile unsigned int*>(&sh.mma_done) = n + 1;
+        mbar_arrive(&sh.slot_empty[s]);
+      }
       if (!ok) break;
     }
   } else {
     // ------------------------------------------------------ exec / epilogue
     const int tid = threadIdx.x - 32;
     uint32_t g = 0;
+    uint32_t aq = 0, ab[2] = {0, 0};
     for (uint32_t n = 0;; ++n) {
       const int s = n & 1;
       if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
@@ -1121,7 +1259,13 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         }
         note_tile(S, worker, w, 1ull << 63);
       }
-      if (w.is_gemm) {
+      if (w.is_attn) {
+        AttnCtx c = attn_ctx(w.attn, sh.attn, abort_flag, ring, tmem_base, aq, ab, warp == 1 ? &sh.wait_note[2] : nullptr);
+        if (tid == 0) sh.wait_ctx[2] = role_ctx(n, aq, ab);
+        if (c.rep) softmax_role<32, 1>(w.attn, c);
+        else softmax_role<128, 1>(w.attn, c);
+        attn_advance(c.n_tiles, aq, ab);
+      } else if (w.is_gemm) {
         if (!gemm_epilogue(w.gemm, sh.bar, tmem_base, g & 1, (g >> 1) & 1, abort_flag) && tid == 0)
           raise_error(S, kFabErrTileWait);
         ++g;
@@ -1135,6 +1279,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         note_tile(S, worker, w, 1ull << 62);
         complete_tile(S, w.tile_lane, w.prog, w.stage, 1);
         note_tile(S, worker, w, 0);
+        *reinterpret_cast<volatile unsigned int*>(&sh.tiles_done) = n + 1;
         mbar_arrive(&sh.slot_empty[s]);
       }
     }
@@ -1142,7 +1287,14 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
   // a bounded wait that ran out inside a GEMM role is reported, and every role leaves
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0 && sh.abort_flag) raise_error(S, kFabErrTileWait);
+  // the wait that gave up first inside an attention item is reported in bits 32.. of the error word
+  if (threadIdx.x == 0 && sh.abort_flag) {
+    for (int i = 0; i < 3; ++i) S.worker_wait[worker][i] = sh.wait_ctx[i] | (sh.wait_note[i] & 0xffffffull);
+    S.worker_wait[worker][3] = sh.tiles_done | (static_cast<unsigned long long>(sh.mma_done) << 32);
+  }
+  if (threadIdx.x == 0 && sh.abort_flag)
+    raise_error(S, kFabErrTileWait | (static_cast<unsigned long long>(sh.attn.fail_site) << 32) |
+                       (static_cast<unsigned long long>(sh.tiles_done & 0xffffu) << 48));
   if (warp == 6) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);

@@ -478,6 +478,12 @@ int monofab_fabric_worker_tiles(monofab_fabric* f, uint64_t* words, uint64_t* si
   return MONOFAB_OK;
 }
 
+int monofab_fabric_wait_notes(monofab_fabric* f, uint64_t* notes) {
+  if (!f || !notes) return fail(MONOFAB_EINVAL, "fabric_wait_notes: NULL argument");
+  std::lock_guard<std::mutex> lock(f->mu);
+  return from_device(f, notes, f->state->worker_wait, sizeof(uint64_t) * kMaxWorkers * 4);
+}
+
 int monofab_fabric_iteration_times(monofab_fabric* f, int lane, uint64_t start, int count, double timeout_s,
                                    uint64_t* end_ns) {
   if (!f || !end_ns || lane < 0 || lane >= kMaxLanes || count < 1) return fail(MONOFAB_EINVAL, "fabric_iteration_times: bad argument");
@@ -508,12 +514,12 @@ int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* 
   std::lock_guard<std::mutex> lock(f->mu);
   if (f->map_count >= f->map_cap) return fail(MONOFAB_EINVAL, "fabric_tensor_map: the table of %d maps is full", f->map_cap);
   // Record = three encodings of the same tensor: [0] the caller's box; for rank-3
-  // weight tensors also [1] box (64, 16, 1) and [2] box (64, 128, 1), which the
+  // weight tensors (box of one z slice) also [1] box (64, 16, 1) and [2] box (64, 128, 1), which the
   // B200 GEMM tile uses instead of the 64-row box the reference's tile asks for.
   CUtensorMap rec[4];   // [3] holds flags (monofab_fabric_tensor_map_packed)
   std::memset(rec, 0, sizeof rec);
   if (int r = encode_map(&rec[0], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, box, swizzle)) return r;
-  if (rank == 3) {
+  if (rank == 3 && box[2] == 1) {
     const uint32_t b16[3] = {box[0], 16, 1}, b128[3] = {box[0], 128, 1};
     if (int r = encode_map(&rec[1], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b16, swizzle)) return r;
     if (int r = encode_map(&rec[2], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b128, swizzle)) return r;

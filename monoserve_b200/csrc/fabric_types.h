@@ -25,11 +25,18 @@ enum TileKind : uint16_t {
   kTileProbe = 3,         // a[0] chain base, i0 loads, a[1] result, i1 result index
   kTileZeroRuntime = 4,   // re-arm stages [i0, i1) except i2
   kTileGemm = 32,
+  kTileAttnPrefill = 33,    // an attention work item (prefill and decode items share one code path)
+  kTileAttnDecode = 34,
+  kTileAttnMerge = 35,      // merge of the key ranges of a split item
   kTileRmsNorm = 36,
+  kTileQkRope = 37,
   kTileRouter = 38,
   kTileExpand = 39,
   kTilePermute = 40,
   kTileAddNorm = 41,
+  kTileEmbed = 42,
+  kTileSample = 43,
+  kTileAttnPlan = 44,
   kTileCombine = 47,        // not in the reference: un-permute + weighted combine in pick order (+ RMSNorm)
   kTileRouterLogits = 48,   // not in the reference: router projection with a defined summation order
 };
@@ -144,6 +151,12 @@ struct alignas(128) DeviceState {
   HostMirror* mirror;
   unsigned long long worker_tile[kMaxWorkers];
   unsigned long long worker_tile_ns[kMaxWorkers];
+  // Written when a worker leaves after a bounded wait ran out: where its roles were waiting.
+  // Four words per worker: [0] TMA producer, [1] MMA, [2] first exec warp, each
+  // record << 48 | q phases << 40 | phases[0] << 32 | phases[1] << 24 | tile << 8 | site
+  // (sites in attention_core.cuh; 13 = the producer's drain), [3] records finished by the
+  // exec warps | by the MMA warp << 32.
+  unsigned long long worker_wait[kMaxWorkers][4];
 };
 
 // Per-tile trace record of the test tiles (csrc/fabric/core_tiles.cuh:10-17).

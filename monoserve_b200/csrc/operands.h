@@ -17,7 +17,7 @@ namespace mf {
 #define MF_ATTN_ARGS(U64, U32, F32) \
   U64(q_map) U64(k_map) U64(v_map) U64(out) U64(ws_o) U64(ws_m) U64(ws_l) U64(block_table) U64(req_info) \
   F32(scale_log2) U32(bt_stride) U32(hq) U32(hkv) U32(group) U32(chunk_blocks) U32(max_chunks) \
-  U32(page_size)
+  U32(page_size) U64(q_map_small)
 
 #define MF_NORM_ARGS(U64, U32, F32) \
   U64(x) U64(x2) U64(acc) U64(w) U64(out) U64(embed) U64(tokens) U64(gather) U64(out2) U64(step) \
@@ -25,7 +25,7 @@ namespace mf {
 
 #define MF_STEP_ARGS(U64, U32, F32) \
   U64(row_req) U64(last_token) U64(seq_len) U64(block_table) U64(tok_pos) U64(tok_slot) U64(req_info) \
-  U32(bt_stride)
+  U32(bt_stride) U32(page_size)
 
 #define MF_QK_ARGS(U64, U32, F32) \
   U64(qkv) U64(q_out) U64(k_cache) U64(v_cache) U64(q_norm) U64(k_norm) U64(tok_pos) U64(tok_slot) \
@@ -53,7 +53,7 @@ namespace mf {
 
 #define MF_ATTN_PLAN_ARGS(U64, U32, F32) \
   U64(attn) U64(req_info) U32(rows) U32(hkv) U32(chunk_keys) U32(stage_attn) U32(stage_comb) \
-  U32(dyn_first) U32(dyn_cap)
+  U32(dyn_first) U32(dyn_cap) U32(workers) U32(reserved0) U64(row_req)
 
 /* Not in the reference: the deterministic router projection and the deterministic
  * un-permute + weighted combine as fabric tiles. */

@@ -154,6 +154,21 @@ class Fabric:
                             kind=(w >> 44) & 0xfff, stage=(w >> 24) & 0xfffff, tile=w & 0xffffff, since_ns=t))
         return out
 
+    def wait_notes(self):
+        """Per worker that left after a bounded wait ran out: where its producer, MMA and first
+        exec warp were waiting (record, phase counts, tile, site) and the records finished."""
+        words = (ctypes.c_uint64 * 1024)()
+        self._C.check(self._lib.monofab_fabric_wait_notes(self._h, words))
+        out = {}
+        for i in range(self.num_workers):
+            w = list(words[4 * i:4 * i + 4])
+            if any(w):
+                f = lambda v: dict(record=v >> 48, q=(v >> 40) & 0xff, ph0=(v >> 32) & 0xff, ph1=(v >> 24) & 0xff,  # noqa: E731
+                                   tile=(v >> 8) & 0xff, site=v & 0xff)
+                out[i] = dict(producer=f(w[0]), mma=f(w[1]), exec=f(w[2]), exec_done=w[3] & 0xffffffff,
+                              mma_done=w[3] >> 32)
+        return out
+
     def tensor_map(self, base, dims, strides_bytes, box, dtype=0, swizzle=128, packed=False):
         rank = len(dims)
         d = (ctypes.c_uint64 * rank)(*dims)
