@@ -1,0 +1,441 @@
+"""A Qwen3-MoE-style decoder as fabric lane programs.
+
+The reference builds one program per lane whose per-layer chain is
+qkv GEMM -> rope -> attention -> o GEMM -> norm -> router -> expand -> permute ->
+per expert (w13 -> red -> w2) -> add_norm, then lm_head and sample
+(monoserve/runtime/lane.py:309-420), over the workspaces of lane.py:101-122 and the
+weight placement of monoserve/runtime/weights.py:100-158.  `ModelLane` builds the same
+chain on this library's tiles:
+
+  embed (42) -> per layer [ qkv GEMM (32) -> qk_rope (37) -> attention items (33/34, planned
+  on the host for prefill and by the plan tile 44 for decode) -> merge (35) -> o GEMM (32,
+  + residual) -> RMSNorm (36) -> router_logits (48) -> router (38) -> expand (39) ->
+  permute (40) -> experts (32, SiLU-mul / fp32 rows) -> combine (47, + next norm) ]
+  -> final norm with gather (36) -> lm_head GEMM (32, fp32) -> sample (43)
+
+All device memory is allocated when the lane is built, before the fabric starts.
+"""
+import math
+import types
+
+import torch
+
+from monoserve_b200 import _C
+from monoserve_b200.attention import SCALE_LOG2, fabric_maps, fabric_tiles, plan_items
+from monoserve_b200.fabric import Program, Tile, tile_array
+from monoserve_b200.fabric.args import pack
+
+K_GEMM, K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE, K_RMSNORM, K_QKROPE = 32, 33, 34, 35, 36, 37
+K_ROUTER, K_EXPAND, K_PERMUTE, K_EMBED, K_SAMPLE, K_ATTN_PLAN, K_COMBINE, K_LOGITS = 38, 39, 40, 42, 43, 44, 47, 48
+EPI_STORE, EPI_SILU_MUL, EPI_F32, EPI_ROWS_F32 = 0, 1, 3, 5
+REGION_HOST, REGION_HOT = 0, 1
+CHUNK = 16            # rows per router / permute tile = rank chunk of the stable pack
+ROPE_ITEMS = 48       # (row, head) items per qk_rope tile (monoserve/runtime/lane.py:27)
+HEIGHTS = [16, 32, 64, 128, 256]
+
+
+def _block(name, **fields):
+    return torch.frombuffer(bytearray(pack(name, **fields)), dtype=torch.uint8).cuda()
+
+
+def _u64(values):
+    return torch.tensor([int(v) for v in values], dtype=torch.int64).cuda()
+
+
+def _bm(rows):
+    """Row-block height of a dense GEMM over `rows` activation rows."""
+    for h in HEIGHTS:
+        if rows <= h:
+            return h
+    return HEIGHTS[-1]
+
+
+def rope_table(theta, rot_dim, max_pos):
+    """cos/sin fp32 [max_pos][rot_dim / 2][2], computed as the reference's oracle does
+    (tests/test_fabric_model.py:35-42; the lane's host table: monoserve/runtime/lane.py:36-48)."""
+    half = rot_dim // 2
+    j = torch.arange(half, dtype=torch.float32)
+    inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2 * j / rot_dim)
+    ang = torch.arange(max_pos, dtype=torch.float32)[:, None] * inv[None]
+    return torch.stack([ang.cos(), ang.sin()], -1).contiguous()
+
+
+class ModelWeights:
+    """Weights of the decoder on the device, expert stacks placed as the reference places them
+    (monoserve/runtime/weights.py:100-158): the full expert set of every layer in pinned host
+    memory (region 0, slot = expert id), the layer's hot experts copied to HBM (region 1,
+    w13 in the packed SwiGLU row order), and a per-layer (region, slot) table.
+
+    w: an object with CPU bf16 tensors embed [V,H], lm_head [V,H], final_norm [H] and per-layer
+    lists in_norm, qkv, q_norm, k_norm, o, post_norm, router, host_w13 [E,2I,H], host_w2 [E,H,I].
+    hot: per layer, the expert ids kept in HBM (default: all)."""
+
+    def __init__(self, cfg, w, hot=None):
+        self.cfg = cfg
+        L, E, I, H = cfg.num_layers, cfg.num_experts, cfg.intermediate, cfg.hidden
+        d = lambda t: t.to(torch.bfloat16).contiguous().cuda()  # noqa: E731
+        self.embed, self.lm_head, self.final_norm = d(w.embed), d(w.lm_head), d(w.final_norm)
+        for name in ("in_norm", "qkv", "q_norm", "k_norm", "o", "post_norm", "router"):
+            setattr(self, name, [d(t) for t in getattr(w, name)])
+        self.host_w13 = [t if t.is_pinned() else t.contiguous().pin_memory() for t in w.host_w13]
+        self.host_w2 = [t if t.is_pinned() else t.contiguous().pin_memory() for t in w.host_w2]
+        self.hot = [list(h) for h in hot] if hot is not None else [list(range(E)) for _ in range(L)]
+        self.hot_w13, self.hot_w2, self.table = [], [], []
+        for l in range(L):
+            idx = torch.tensor(self.hot[l] if self.hot[l] else [0])
+            h13 = self.host_w13[l][idx].cuda()
+            packed = torch.empty_like(h13)
+            _C.check(_C.lib.monofab_pack_w13(h13.data_ptr(), packed.data_ptr(), h13.shape[0], I, H, 2, None))
+            torch.cuda.synchronize()
+            self.hot_w13.append(packed)
+            self.hot_w2.append(self.host_w2[l][idx].cuda())
+            table = torch.zeros(E, 2, dtype=torch.int32)
+            table[:, 1] = torch.arange(E)
+            if self.hot[l]:
+                table[idx, 0] = REGION_HOT
+                table[idx, 1] = torch.arange(len(self.hot[l]), dtype=torch.int32)
+            self.table.append(table.cuda())
+
+
+class KVCache:
+    """Paged K and V per layer, bf16 [pages][page_size][hkv][128] (monoserve/runtime/kv.py:8-11 with
+    the page size a parameter).  Page 0 is a write sink (monoserve/engine.py:113)."""
+
+    def __init__(self, cfg, n_pages, page_size=16):
+        self.n_pages, self.page = n_pages, page_size
+        shape = (n_pages, page_size, cfg.num_kv_heads, 128)
+        self.k = [torch.zeros(shape, dtype=torch.bfloat16, device="cuda") for _ in range(cfg.num_layers)]
+        self.v = [torch.zeros(shape, dtype=torch.bfloat16, device="cuda") for _ in range(cfg.num_layers)]
+
+
+class ModelLane:
+    """One lane of the fabric running the decoder: buffers, operand blocks and tensor maps are
+    made once; `build_prefill` / `build_decode` upload programs over them.
+
+    Request state lives in slot-indexed arrays (block table row, sequence length, last token),
+    as in the reference's lane (StepArgs, csrc/fabric/model_types.h:116-128)."""
+
+    def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None):
+        self.fab, self.lane_id, self.cfg, self.w, self.kv = fab, lane_id, cfg, weights, kv
+        self.T, self.S, self.bt_stride, self.max_chunks = max_tokens, max_slots, bt_stride, max_chunks
+        H, I, E, K, L, V = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, cfg.num_layers, cfg.vocab
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        self.qkv_dim = (hq + 2 * hkv) * 128
+        T, S, P = max_tokens, max_slots, max_tokens * K
+        dev = "cuda"
+        z = lambda *shape, dt=torch.int32: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
+        bf = torch.bfloat16
+        # residual stream and projections (monoserve/runtime/lane.py:101-122)
+        self.x, self.x2, self.xn = z(T, H, dt=bf), z(T, H, dt=bf), z(T, H, dt=bf)
+        self.qkv = z(T, self.qkv_dim, dt=bf)
+        self.q, self.ao = z(T, hq, 128, dt=bf), z(T, hq, 128, dt=bf)
+        self.xlast, self.logits = z(max(T, S), H, dt=bf), z(max(T, S), V, dt=torch.float32)
+        # routing and expert workspaces
+        self.rl = z(T, E, dt=torch.float32)
+        self.topk_ids, self.topk_w = z(T, K), z(T, K, dt=torch.float32)
+        self.counts, self.fill, self.starts, self.hist = z(E), z(E), z(E + 1), z(L, E)
+        self.chunk_counts, self.pair_rank = z(-(-T // CHUNK), E), z(T, K)
+        self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
+        self.xp, self.h = z(P + 256, H, dt=bf), z(P + 256, I, dt=bf)
+        self.y = z(P + 256, H, dt=torch.float32)
+        # token and request state
+        self.tokens, self.tok_pos, self.tok_slot, self.gather = z(T), z(T), z(T), z(T)
+        self.req_info = z(max(T, S), 4)
+        self.row_req = z(max(T, S))
+        self.bt = z(S, bt_stride)
+        self.seq_len, self.last_token, self.steps = z(S), z(S), z(S)
+        self.temperature = z(S, dt=torch.float32)
+        self.ring = 64
+        self.host_tokens = torch.zeros(S, self.ring, dtype=torch.int32).pin_memory()
+        self.host_steps = torch.zeros(S, dtype=torch.int64).pin_memory()
+        # attention split workspace: (max, sum) pairs after the fp32 rows
+        self.ws_rows = max(max_chunks * S * hq, 4 * T * hq // 8 + 1024)
+        self.ws = z(self.ws_rows * 130, dt=torch.float32)
+        max_pos = max_pos or bt_stride * kv.page
+        self.max_pos = max_pos
+        self.cos_sin = rope_table(cfg.rope_theta, cfg.rotary_dim, max_pos).cuda()
+        self._keep = []
+        self._maps()
+
+    # ------------------------------------------------------------------ maps and operand blocks
+    def _wmap(self, t, base=None, packed=False):
+        if t.dim() == 2:
+            rows, k, zdim = t.shape[0], t.shape[1], 1
+        else:
+            zdim, rows, k = t.shape
+        return self.fab.tensor_map(base if base is not None else t.data_ptr(), [k, rows, zdim], [k * 2, rows * k * 2],
+                                   [64, 64, 1], packed=packed)
+
+    def _amaps(self, t, rows, k):
+        """Activation maps of a [rows][k] bf16 buffer for every row-block height."""
+        return [self.fab.tensor_map(t.data_ptr(), [k, rows], [k * 2], [64, bm]) for bm in HEIGHTS]
+
+    def _maps(self):
+        cfg, w, fab = self.cfg, self.w, self.fab
+        H, I, E, K, L = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, cfg.num_layers
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        T, P = self.T, self.T * K
+        self.m_xn = self._amaps(self.xn, T, H)
+        self.m_ao = self._amaps(self.ao, T, hq * 128)
+        self.m_xlast = self._amaps(self.xlast, self.xlast.shape[0], H)
+        self.m_qkv = [self._wmap(w.qkv[l]) for l in range(L)]
+        self.m_o = [self._wmap(w.o[l]) for l in range(L)]
+        self.m_lm = self._wmap(w.lm_head)
+        self.w13_maps = [_u64([self._wmap(w.host_w13[l], _C.host_device_pointer(w.host_w13[l].data_ptr())),
+                               self._wmap(w.hot_w13[l], packed=True)]) for l in range(L)]
+        self.w2_maps = [_u64([self._wmap(w.host_w2[l], _C.host_device_pointer(w.host_w2[l].data_ptr())),
+                              self._wmap(w.hot_w2[l])]) for l in range(L)]
+        self.xp_maps = _u64(self._amaps(self.xp, P + 256, H))
+        self.h_maps = _u64(self._amaps(self.h, P + 256, I))
+        a13, a2 = [], []
+        for bm in HEIGHTS:
+            b13 = torch.frombuffer(bytearray(_C.gemm_args(out=self.h.data_ptr(), ld_out=I, k_tiles=H // 64,
+                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I)),
+                                   dtype=torch.uint8).cuda()
+            b2 = torch.frombuffer(bytearray(_C.gemm_args(out=self.y.data_ptr(), ld_out=H, k_tiles=I // 64,
+                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H)), dtype=torch.uint8).cuda()
+            self._keep += [b13, b2]
+            a13.append(b13.data_ptr())
+            a2.append(b2.data_ptr())
+        self.w13_args, self.w2_args = _u64(a13), _u64(a2)
+        # attention: one AttnArgs block per layer (the layer's cache maps)
+        self.attn_args = []
+        group = hq // hkv
+        for l in range(L):
+            q_map, q_small, k_map, v_map = fabric_maps(fab, self.q, self.kv.k[l], self.kv.v[l])
+            self.attn_args.append(_block(
+                "AttnArgs", q_map=q_map, k_map=k_map, v_map=v_map, out=self.ao, ws_o=self.ws,
+                ws_m=self.ws.data_ptr() + self.ws_rows * 512, block_table=self.bt, req_info=self.req_info,
+                scale_log2=SCALE_LOG2, bt_stride=self.bt_stride, hq=hq, hkv=hkv, group=group,
+                max_chunks=self.max_chunks, page_size=self.kv.page, q_map_small=q_small))
+        self.router_args = _block("RouterArgs", logits=self.rl, topk_ids=self.topk_ids, topk_w=self.topk_w,
+                                  counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
+                                  chunk_counts=self.chunk_counts, pair_rank=self.pair_rank)
+        self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
+                                   fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
+                                   src=self.xn, dst=self.xp, K=K, H=H, pair_rank=self.pair_rank,
+                                   chunk_prefix=self.chunk_counts, pair_pos=self.pair_pos, E=E)
+        self.step_args = _block("StepArgs", row_req=self.row_req, last_token=self.last_token, seq_len=self.seq_len,
+                                block_table=self.bt, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
+                                req_info=self.req_info, bt_stride=self.bt_stride, page_size=self.kv.page)
+        self.sample_args = _block("SampleArgs", logits=self.logits, temperature=self.temperature,
+                                  last_token=self.last_token, steps=self.steps,
+                                  host_tokens=_C.host_device_pointer(self.host_tokens.data_ptr()),
+                                  host_steps=_C.host_device_pointer(self.host_steps.data_ptr()), seed=0x5eed,
+                                  V=cfg.vocab, ring=self.ring)
+
+    # ------------------------------------------------------------------ stage builders
+    def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None):
+        bm = _bm(rows)
+        args = torch.frombuffer(bytearray(_C.gemm_args(
+            out=out.data_ptr(), ld_out=ld_out, k_tiles=k // 64, epi=epi, bm=bm, n_limit=n_out,
+            residual=residual.data_ptr() if residual is not None else 0, ld_res=ld_res)), dtype=torch.uint8).cuda()
+        self._keep.append(args)
+        xm = amaps[HEIGHTS.index(bm)]
+        tiles = [Tile(K_GEMM, i=(n0, m0, min(bm, rows - m0), 0), a=(args.data_ptr(), wmap, xm))
+                 for m0 in range(0, rows, bm) for n0 in range(0, n_out, 128)]
+        return p.stage(tiles, mark=mark, label=label)
+
+    def _rows(self, kind, args, rows, per):
+        return [Tile(kind, i=(r0, min(per, rows - r0)), a=(args.data_ptr(),)) for r0 in range(0, rows, per)]
+
+    def _moe(self, p, l, T, prev, norm_w, expands):
+        """Stages of layer l's MoE block after `prev` (xn, x2 ready); returns the combine stage."""
+        cfg = self.cfg
+        H, E = cfg.hidden, cfg.num_experts
+        nw = self.fab.num_workers
+        lg = _block("LogitsArgs", x=self.xn, wr=self.w.router[l], logits=self.rl, T=T, H=H, E=E)
+        cb = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2, x=self.x,
+                    w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps)
+        ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
+        self._keep += [lg, cb, ex]
+        per = max(1, -(-T // (2 * nw)))
+        s_lg = p.stage(self._rows(K_LOGITS, lg, T, per), label=("router_logits", l))
+        s_rt = p.stage(self._rows(K_ROUTER, self.router_args, T, CHUNK), label=("router", l))
+        s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", l))
+        s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, CHUNK), label=("permute", l))
+        p.after(prev, s_lg)
+        p.after(s_lg, s_rt)
+        p.after(s_rt, s_ex)
+        p.after(s_ex, s_pm)
+        w13 = [p.stage(label=("w13", l)) for _ in range(E)]
+        red = [p.stage(label=("red", l)) for _ in range(E)]
+        w2 = [p.stage(label=("w2", l)) for _ in range(E)]
+        s_cb = p.stage(self._rows(K_COMBINE, cb, T, per), mark=(l << 8) | 3, label=("combine", l))
+        for e in range(E):
+            p.after(s_pm, w13[e])
+            p.after(w13[e], red[e])
+            p.after(red[e], w2[e])
+            p.after(w2[e], s_cb)
+        dyn = (T * cfg.top_k // 16 + E) * (cfg.intermediate // 64 + H // 128)
+        expands.append((ex, l, T, w13[0], red[0], w2[0], s_cb, dyn))
+        return s_cb
+
+    def _finish_dynamic(self, p, expands, plans):
+        """Hand each expand / plan tile its part of the dynamic region, now that every static tile is counted."""
+        at = p.dynamic_first
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn in expands:
+            p.reserve(dyn)
+        for blob, fields, dyn in plans:
+            p.reserve(dyn)
+        cfg = self.cfg
+        at = p.dynamic_first
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn in expands:
+            blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.w.table[l],
+                        w13_maps=self.w13_maps[l], w2_maps=self.w2_maps[l], xp_maps=self.xp_maps, h_maps=self.h_maps,
+                        w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
+                        I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
+                        dyn_first=at, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb, chunks=-(-T // CHUNK),
+                        chunk_counts=self.chunk_counts)
+            ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
+            at += dyn
+        for blob, fields, dyn in plans:
+            blob.copy_(torch.frombuffer(bytearray(pack("AttnPlanArgs", dyn_first=at, dyn_cap=dyn, **fields)),
+                                        dtype=torch.uint8))
+            at += dyn
+        torch.cuda.synchronize()
+
+    def _layers(self, p, T, first_stage, attention, sample_rows, n_rows):
+        """The decoder after the embedding stage; `attention(p, l, prev)` adds layer l's attention
+        stages after `prev` and returns the stage that completes `ao`.  Returns the last stage."""
+        cfg, w = self.cfg, self.w
+        H, L = cfg.hidden, cfg.num_layers
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        heads = hq + 2 * hkv
+        prev = first_stage
+        expands = []
+        for l in range(L):
+            s_qkv = self._gemm(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv, self.qkv_dim, EPI_STORE,
+                               ("qkv", l))
+            p.after(prev, s_qkv)
+            qk = _block("QkArgs", qkv=self.qkv, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
+                        q_norm=w.q_norm[l], k_norm=w.k_norm[l], tok_pos=self.tok_pos, tok_slot=self.tok_slot,
+                        cos_sin=self.cos_sin, ld_qkv=self.qkv_dim, hq=hq, hkv=hkv, rot_dim=cfg.rotary_dim,
+                        theta=cfg.rope_theta, eps=cfg.rms_eps, max_pos=self.max_pos)
+            self._keep.append(qk)
+            s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, ROPE_ITEMS), mark=(l << 8) | 1, label=("rope", l))
+            p.after(s_qkv, s_rope)
+            s_attn = attention(p, l, s_rope)
+            s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
+                             residual=self.x, ld_res=H, mark=(l << 8) | 2)
+            p.after(s_attn, s_o)
+            nrm = _block("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
+            self._keep.append(nrm)
+            s_norm = p.stage(self._rows(K_RMSNORM, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
+                             label=("norm", l))
+            p.after(s_o, s_norm)
+            next_norm = w.in_norm[l + 1] if l + 1 < L else None
+            prev = self._moe(p, l, T, s_norm, next_norm, expands)
+        # final norm of the rows that continue (gather), lm_head over those rows, next tokens
+        R = n_rows
+        fin = _block("NormArgs", x=self.x, w=w.final_norm, out=self.xn, gather=self.gather, out2=self.xlast, H=H, ld=H,
+                     eps=cfg.rms_eps)
+        self._keep.append(fin)
+        s_fin = p.stage(self._rows(K_RMSNORM, fin, T, max(1, -(-T // (2 * self.fab.num_workers)))), label=("final_norm", L))
+        p.after(prev, s_fin)
+        s_lm = self._gemm(p, self.m_lm, self.m_xlast, R, cfg.vocab, H, self.logits, cfg.vocab, EPI_F32, ("lm_head", L))
+        p.after(s_fin, s_lm)
+        s_sample = p.stage([Tile(K_SAMPLE, i=(row, slot), a=(self.sample_args.data_ptr(),)) for row, slot in sample_rows],
+                           label=("sample", L))
+        p.after(s_lm, s_sample)
+        return s_sample, expands
+
+    # ------------------------------------------------------------------ programs
+    def build_prefill(self, batch, iterations=1, all_logits=False):
+        """batch: list of (slot, tokens, pos0): the request in `slot` appends `tokens` at positions
+        pos0 .. (its pages must already be in the lane's block table row `slot`).  The program
+        computes the batch, appends K/V to the caches, and samples one next token per request.
+        all_logits: keep the logits of every row (row r of `logits`), not only each request's last."""
+        page = self.kv.page
+        tokens, pos, slots, req_info, sample_rows = [], [], [], [], []
+        gather = []
+        bt = self.bt.cpu()
+        row = 0
+        for r, (slot, toks, pos0) in enumerate(batch):
+            n = len(toks)
+            req_info.append((row, pos0, n, pos0 + n))
+            for i, t in enumerate(toks):
+                ppos = pos0 + i
+                tokens.append(t)
+                pos.append(ppos)
+                slots.append(int(bt[slot, ppos // page]) * page + ppos % page)
+                gather.append(row + i if all_logits else (r if i == n - 1 else -1))
+            sample_rows.append((row + n - 1 if all_logits else r, slot))
+            row += n
+        T = row
+        assert 0 < T <= self.T
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()  # noqa: E731
+        self.tokens[:T], self.tok_pos[:T], self.tok_slot[:T], self.gather[:T] = i32(tokens), i32(pos), i32(slots), i32(gather)
+        self.req_info[:len(batch)] = i32(req_info)
+        cfg = self.cfg
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        items, merge, ws_rows = plan_items(req_info, hq, hkv, sms=self.fab.num_workers)
+        assert ws_rows <= self.ws_rows, "attention split workspace too small"
+        slot_of = torch.tensor([b[0] for b in batch], dtype=torch.int32)
+        items[:, 0] = slot_of[items[:, 0].long()]
+        p = Program()
+        emb = _block("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, tokens=self.tokens,
+                     H=cfg.hidden, ld=cfg.hidden, eps=cfg.rms_eps)
+        self._keep.append(emb)
+        s_embed = p.stage(self._rows(K_EMBED, emb, T, CHUNK), label=("embed", 0))
+
+        def attention(p, l, prev):
+            tiles, merges = fabric_tiles(items, merge, self.attn_args[l].data_ptr(), K_ATTN_PREFILL)
+            s_a = p.stage(tiles, label=("attn", l))
+            s_m = p.stage(merges, label=("attn_merge", l))
+            p.after(prev, s_a)
+            p.after(s_a, s_m)
+            return s_m
+
+        n_rows = T if all_logits else len(batch)
+        last, expands = self._layers(p, T, s_embed, attention, sample_rows, n_rows)
+        self._finish_dynamic(p, expands, [])
+        self.rows_out = n_rows
+        return p.upload(self.fab, first=s_embed, iterations=iterations)
+
+    def build_decode(self, slots, iterations=1, chunk_keys=0):
+        """One decode step per iteration for the requests in `slots` (row r = slots[r]): the
+        embedding tiles take each request's last token and advance its length, the plan tile
+        writes the step's attention items, and the sample tiles publish the next tokens."""
+        cfg = self.cfg
+        R = len(slots)
+        assert 0 < R <= min(self.T, 256)
+        self.row_req[:R] = torch.tensor(slots, dtype=torch.int32).cuda()
+        self.gather[:R] = torch.arange(R, dtype=torch.int32).cuda()
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        p = Program()
+        emb = _block("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, step=self.step_args,
+                     H=cfg.hidden, ld=cfg.hidden, eps=cfg.rms_eps)
+        self._keep.append(emb)
+        s_embed = p.stage(self._rows(K_EMBED, emb, R, CHUNK), label=("embed", 0))
+        plans = []
+
+        def attention(p, l, prev):
+            blob = torch.zeros(_C.struct_layouts()["AttnPlanArgs"][0], dtype=torch.uint8, device="cuda")
+            self._keep.append(blob)
+            s_plan = p.stage(tile_array(K_ATTN_PLAN, a0=blob.data_ptr()), label=("attn_plan", l))
+            s_a = p.stage(label=("attn", l))
+            s_m = p.stage(label=("attn_merge", l))
+            p.after(prev, s_plan)
+            p.after(s_plan, s_a)
+            p.after(s_a, s_m)
+            fields = dict(attn=self.attn_args[l].data_ptr(), req_info=self.req_info.data_ptr(), rows=R, hkv=hkv,
+                          chunk_keys=chunk_keys, stage_attn=s_a, stage_comb=s_m, workers=self.fab.num_workers,
+                          row_req=self.row_req.data_ptr())
+            plans.append((blob, fields, R * hkv * (self.max_chunks + 1)))
+            return s_m
+
+        last, expands = self._layers(p, R, s_embed, attention, [(r, s) for r, s in enumerate(slots)], R)
+        self._finish_dynamic(p, expands, plans)
+        self.rows_out = R
+        return p.upload(self.fab, first=s_embed, iterations=iterations)
+
+    # ------------------------------------------------------------------ request state
+    def set_pages(self, slot, pages):
+        row = torch.zeros(self.bt_stride, dtype=torch.int32)
+        row[:len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        self.bt[slot] = row.cuda()
+
+    def set_request(self, slot, seq_len, last_token, temperature=0.0):
+        self.seq_len[slot], self.last_token[slot], self.steps[slot] = seq_len, last_token, 0
+        self.temperature[slot] = temperature
