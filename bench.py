@@ -443,10 +443,28 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": BATCH / sec, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
                                     "sample": f"{len(cpu_times)} batches of {BATCH} tokens, whole layer, "
                                               "oracle/torch_path.py on the host CPU"}
+        if world == 1 and not args.no_mixed_lane:
+            line["mixed_lane"] = mixed_lane_run()
         print(json.dumps(line), flush=True)
     layer.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def mixed_lane_run():
+    """The second metric BASELINE.json names, mixed-lane decode TPOT p50, on config 3 (the full
+    48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a 128-sequence decode
+    lane in one persistent kernel): run by monoserve_b200/benchmarks/mixed_lane.py in a process
+    of its own (it pins 58 GB of host memory for the expert stacks), about a minute and a half."""
+    cmd = [sys.executable, "-m", "monoserve_b200.benchmarks.mixed_lane", "--steps", "6"]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=os.path.dirname(os.path.abspath(__file__)))
+        last = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+        if out.returncode != 0 or not last:
+            return {"error": (out.stderr or out.stdout)[-300:]}
+        return json.loads(last[-1])
+    except Exception as exc:   # the headline line is printed regardless
+        return {"error": repr(exc)[:300]}
 
 
 def main():
@@ -458,6 +476,8 @@ def main():
     ap.add_argument("--ncu", action="store_true",
                     help="profiling target: only W warm-up + K device-resident steps, no JSON line")
     ap.add_argument("--all-hot", action="store_true", help="with --ncu: place all 128 experts in HBM")
+    ap.add_argument("--no-mixed-lane", action="store_true",
+                    help="skip the config-3 mixed-lane TPOT run that the N=1 line carries as `mixed_lane`")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.ncu:

@@ -125,13 +125,14 @@ def fabric_maps(fab, q, k_cache, v_cache):
 
 
 def fabric_tiles(items, merge, args_ptr, kind=K_ATTN_PREFILL):
-    """The work list of plan_items as fabric tiles: (attention item tiles, merge tiles).
-    Tile fields: see make_attn_work / tile_attn_merge in csrc/fabric_seq_tiles.cuh."""
-    from monoserve_b200.fabric import Tile
-    tiles = []
-    for req, h, row0, n, pos0, kv_len, k0, k1, ws, *_ in items.tolist():
-        tiles.append(Tile(kind, i=(row0, n | (h << 16), k0, max(k1, 0)),
-                          a=(args_ptr, req | ((ws + 1) << 32), pos0 | (kv_len << 32))))
-    merges = [Tile(K_ATTN_MERGE, i=(row0, n | (h << 16), ws, parts | (stride << 16)), a=(args_ptr,))
-              for row0, n, h, ws, parts, stride, *_ in merge.tolist()]
+    """The work list of plan_items as fabric tiles: (attention item tiles, merge tiles), each a
+    uint64 [n, 8] array.  Tile fields: see make_attn_work / tile_attn_merge in csrc/fabric_seq_tiles.cuh."""
+    import numpy as np
+    from monoserve_b200.fabric import tile_array
+    it = items.numpy().astype(np.int64).reshape(-1, 12)
+    tiles = tile_array(kind, i0=it[:, 2], i1=it[:, 3] | (it[:, 1] << 16), i2=it[:, 6], i3=np.maximum(it[:, 7], 0),
+                       a0=args_ptr, a1=it[:, 0] | ((it[:, 8] + 1) << 32), a2=it[:, 4] | (it[:, 5] << 32))
+    mg = merge.numpy().astype(np.int64).reshape(-1, 8)
+    merges = tile_array(K_ATTN_MERGE, i0=mg[:, 0], i1=mg[:, 1] | (mg[:, 2] << 16), i2=mg[:, 3],
+                        i3=mg[:, 4] | (mg[:, 5] << 16), a0=args_ptr)
     return tiles, merges

@@ -1,0 +1,197 @@
+"""Mixed-lane benchmark on the shapes of BASELINE config 3: a random-init Qwen3-30B-A3B-shaped
+decoder (48 layers, hidden 2048, 32 / 4 heads of 128, 128 experts top-8 of width 768, vocabulary
+151936, BF16) with a prefill lane (4 prompts of 2048 tokens) and a decode lane (128 sequences,
+paged KV with page size 16, contexts uniform in [512, 8192]) running concurrently inside one
+persistent fabric kernel, half of every layer's experts in the HBM hot tier and all of them in
+pinned host memory.
+
+    python -m monoserve_b200.benchmarks.mixed_lane [--layers 48] [--distinct 48] [--decode 128]
+        [--prompts 4] [--prompt-len 2048] [--hot 64] [--sm-decode 74] [--caps 4,4] [--forms 64,0]
+        [--steps 8] [--decode-only] [--quick]
+
+Reported (one JSON line): decode TPOT p50 = median of the decode lane's iteration end-time deltas
+(the in-kernel timer, as monoserve/calibrate/calibrator.py:309-319 and Fabric.iteration_times),
+taken while the prefill lane's program repeats on its share of the SMs; the prefill lane's tokens/s;
+the SM split, link credits and kernel forms that were published.
+
+Synthetic, seeded data stand in for everything.  The default holds 48 distinct layers' weights: 58 GB
+of pinned host memory, 29 GB of hot tier and 57 GB of KV cache in HBM.  `--distinct D` makes only D
+distinct layers' weights and cycles them over the layers, for hosts with less memory (every layer still
+streams its own experts' bytes per step: one layer's hot tier, 604 MB, is far larger than the 126 MB
+L2); the output states it.  The default plan (74 + 74 SMs, 4 + 4 link credits, row-block form 64 for the
+decode lane and the one-pass form for the prefill lane) is one point of the plan space the reference's
+control plane searches; other points are a flag away.
+"""
+import argparse
+import json
+import time
+import types
+
+import numpy as np
+import torch
+
+from monoserve_b200.fabric import Fabric
+from monoserve_b200.model import KVCache, ModelLane, ModelWeights
+
+
+def q_config(layers):
+    return types.SimpleNamespace(hidden=2048, intermediate=768, num_experts=128, top_k=8, num_layers=layers,
+                                 num_heads=32, num_kv_heads=4, head_dim=128, vocab=151936, rope_theta=1e6,
+                                 rms_eps=1e-6, rotary_dim=128)
+
+
+def make_weights(cfg, distinct, seed=0):
+    """Random bf16 weights, N(0, 0.02); the expert stacks go to pinned host memory."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    H, I, E, V = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.vocab
+    qkv_dim = (cfg.num_heads + 2 * cfg.num_kv_heads) * 128
+
+    def rnd(*shape, scale=0.02):
+        return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+    def pinned(*shape):
+        out = torch.empty(*shape, dtype=torch.bfloat16, pin_memory=True)
+        for e in range(shape[0]):
+            out[e].copy_(rnd(*shape[1:]))
+        return out
+
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device="cuda")  # noqa: E731
+    layers = []
+    for _ in range(distinct):
+        layers.append(dict(in_norm=ones(H), qkv=rnd(qkv_dim, H), q_norm=ones(128), k_norm=ones(128),
+                           o=rnd(H, cfg.num_heads * 128), post_norm=ones(H), router=rnd(E, H, scale=H ** -0.5),
+                           host_w13=pinned(E, 2 * I, H), host_w2=pinned(E, H, I)))
+    torch.cuda.synchronize()
+    w = types.SimpleNamespace(embed=rnd(V, H, scale=1.0), lm_head=rnd(V, H), final_norm=ones(H))
+    for name in layers[0]:
+        setattr(w, name, [layers[l % distinct][name] for l in range(cfg.num_layers)])
+    return w
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--distinct", type=int, default=48)
+    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--prompts", type=int, default=4)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--ctx-lo", type=int, default=512)
+    ap.add_argument("--ctx-hi", type=int, default=8192)
+    ap.add_argument("--hot", type=int, default=64)
+    ap.add_argument("--sm-decode", type=int, default=74)
+    ap.add_argument("--caps", default="4,4")
+    ap.add_argument("--forms", default="64,0")
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--decode-only", action="store_true", help="no prefill lane: every SM decodes")
+    ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
+    args = ap.parse_args()
+    if args.quick:
+        args.layers, args.distinct, args.decode, args.prompts, args.prompt_len = 2, 1, 16, 1, 256
+        args.ctx_lo, args.ctx_hi, args.steps = 128, 1024, 4
+    cfg = q_config(args.layers)
+    caps = [int(v) for v in args.caps.split(",")]
+    forms = [int(v) for v in args.forms.split(",")]
+    t_setup = time.time()
+    w = make_weights(cfg, min(args.distinct, args.layers))
+    rng = np.random.default_rng(0)
+    hot = [sorted(rng.permutation(cfg.num_experts)[:args.hot].tolist()) for _ in range(cfg.num_layers)]
+    weights = ModelWeights(cfg, w, hot=hot)
+    page = args.page
+    ctx = rng.integers(args.ctx_lo, args.ctx_hi + 1, size=args.decode).tolist()
+    grow = args.steps + 16
+    pages_dec = [-(-(c + grow) // page) for c in ctx]
+    pages_pre = -(-args.prompt_len // page)
+    n_pages = 1 + sum(pages_dec) + args.prompts * pages_pre
+    kv = KVCache(cfg, n_pages, page)
+    for l in range(cfg.num_layers):
+        kv.k[l].normal_(0, 1)
+        kv.v[l].normal_(0, 1)
+    bt_stride = max(max(pages_dec), pages_pre)
+    fab = Fabric(pool_bytes=2 << 30)
+    fab.set_max_run(600)
+    min_form = min([f for f in forms if f] + [64])
+    dec = ModelLane(fab, 0, cfg, weights, kv, max_tokens=args.decode, max_slots=args.decode, bt_stride=bt_stride,
+                    logit_rows=args.decode, min_form=min_form)
+    at = 1
+    perm = rng.permutation(n_pages - 1) + 1          # shuffled pages, page 0 stays the sink
+    for s, n in enumerate(pages_dec):
+        dec.set_pages(s, perm[at - 1:at - 1 + n].tolist())
+        at += n
+        dec.set_request(s, seq_len=ctx[s], last_token=int(rng.integers(0, cfg.vocab)))
+    h_dec = dec.build_decode(list(range(args.decode)), iterations=0)
+    programs, lanes_map = [h_dec], [0] * fab.num_workers
+    pre = None
+    if not args.decode_only:
+        T = args.prompts * args.prompt_len
+        pre = ModelLane(fab, 1, cfg, weights, kv, max_tokens=T, max_slots=args.prompts, bt_stride=bt_stride,
+                        logit_rows=args.prompts, min_form=min_form)
+        batch = []
+        for s in range(args.prompts):
+            pre.set_pages(s, perm[at - 1:at - 1 + pages_pre].tolist())
+            at += pages_pre
+            batch.append((s, rng.integers(0, cfg.vocab, size=args.prompt_len).tolist(), 0))
+        programs.append(pre.build_prefill(batch, iterations=0))
+        lanes_map = [0] * args.sm_decode + [1] * (fab.num_workers - args.sm_decode)
+    torch.cuda.synchronize()
+    t_setup = time.time() - t_setup
+    fab.start()
+    fab.publish(map=lanes_map, caps=caps[:len(programs)], order=list(range(len(programs))), programs=programs,
+                forms=forms[:len(programs)])
+    warm = 2
+    ends = fab.iteration_times(0, 0, warm + args.steps, timeout=600)
+    pre_ends = fab.iteration_times(1, fab.progress()["lanes"][1]["iterations"], 2, timeout=600) if pre else []
+    prog = fab.progress()
+    err = prog["error"]
+    notes = fab.wait_notes() if err else {}
+    fab.stop()
+    torch.cuda.synchronize()
+    deltas = np.diff(np.array(ends[warm - 1:], dtype=np.float64)) * 1e-6    # ms per decode step
+    hist = dec.hist.cpu().numpy()
+    iters = warm + args.steps
+    line = {"workload": "config 3: Qwen3-30B-A3B-shaped decoder, prefill + decode lanes in one fabric kernel",
+            "layers": cfg.num_layers, "distinct_weight_layers": min(args.distinct, args.layers),
+            "decode_seqs": args.decode, "ctx_sum": int(sum(ctx)), "prefill": f"{args.prompts}x{args.prompt_len}",
+            "hot_experts_per_layer": args.hot, "page_size": page,
+            "sm_split": {"decode": args.sm_decode if pre else fab.num_workers,
+                         "prefill": fab.num_workers - args.sm_decode if pre else 0},
+            "caps": caps[:len(programs)], "forms": forms[:len(programs)],
+            "decode_tpot_ms_p50": float(np.median(deltas)), "decode_tpot_ms_min": float(deltas.min()),
+            "decode_tpot_ms_max": float(deltas.max()), "decode_tokens_per_s": args.decode / float(np.median(deltas)) * 1e3,
+            "decode_steps_timed": int(len(deltas)),
+            "activated_experts_per_layer_step": float((hist > 0).sum() / max(1, cfg.num_layers)),
+            "routed_rows_per_layer_step": float(hist.sum() / max(1, cfg.num_layers) / iters),
+            "setup_s": round(t_setup, 1), "error": err}
+    # Host-link traffic: every activated cold expert's 3 H I weights cross the link once per pass over
+    # its rows (row blocks of `form` rows; form 0 = 256-row blocks), per layer.
+    expert_bytes = 3 * cfg.hidden * cfg.intermediate * 2
+
+    def link_bytes(lane, form, iterations):
+        h = lane.hist.cpu().numpy().astype(np.float64) / max(1, iterations)     # rows per expert, layer, iteration
+        total = 0.0
+        for l in range(cfg.num_layers):
+            cold = np.ones(cfg.num_experts, dtype=bool)
+            cold[hot[l]] = False
+            total += float(np.ceil(h[l][cold] / (form or 256)).sum()) * expert_bytes
+        return total
+
+    dec_iters = prog["lanes"][0]["iterations"]
+    dec_link = link_bytes(dec, forms[0], dec_iters)
+    line["decode_link_bytes_per_step"] = dec_link
+    link_rate = dec_link / (float(np.median(deltas)) * 1e-3)
+    if pre is not None and len(pre_ends) >= 2:
+        pre_ms = (pre_ends[-1] - pre_ends[-2]) * 1e-6
+        line["prefill_iteration_ms"] = pre_ms
+        line["prefill_tokens_per_s"] = args.prompts * args.prompt_len / pre_ms * 1e3
+        pre_link = link_bytes(pre, forms[1], prog["lanes"][1]["iterations"])
+        line["prefill_link_bytes_per_iteration"] = pre_link
+        link_rate += pre_link / (pre_ms * 1e-3)
+    line["host_link_gbs"] = link_rate / 1e9
+    if notes:
+        line["wait_notes"] = {str(k): v for k, v in list(notes.items())[:4]}
+    print(json.dumps(line))
+    fab.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -15,9 +15,7 @@ chain on this library's tiles:
 
 All device memory is allocated when the lane is built, before the fabric starts.
 """
-import math
-import types
-
+import numpy as np
 import torch
 
 from monoserve_b200 import _C
@@ -73,22 +71,38 @@ class ModelWeights:
     def __init__(self, cfg, w, hot=None):
         self.cfg = cfg
         L, E, I, H = cfg.num_layers, cfg.num_experts, cfg.intermediate, cfg.hidden
-        d = lambda t: t.to(torch.bfloat16).contiguous().cuda()  # noqa: E731
+        # A tensor object that appears for several layers (a benchmark that cycles a few distinct
+        # layers' weights) is placed once.
+        dev_cache, pin_cache, hot_cache = {}, {}, {}
+
+        def d(t):
+            if id(t) not in dev_cache:
+                dev_cache[id(t)] = t.to(torch.bfloat16).contiguous().cuda()
+            return dev_cache[id(t)]
+
+        def pin(t):
+            if id(t) not in pin_cache:
+                pin_cache[id(t)] = t if t.is_pinned() else t.contiguous().pin_memory()
+            return pin_cache[id(t)]
+
         self.embed, self.lm_head, self.final_norm = d(w.embed), d(w.lm_head), d(w.final_norm)
         for name in ("in_norm", "qkv", "q_norm", "k_norm", "o", "post_norm", "router"):
             setattr(self, name, [d(t) for t in getattr(w, name)])
-        self.host_w13 = [t if t.is_pinned() else t.contiguous().pin_memory() for t in w.host_w13]
-        self.host_w2 = [t if t.is_pinned() else t.contiguous().pin_memory() for t in w.host_w2]
+        self.host_w13 = [pin(t) for t in w.host_w13]
+        self.host_w2 = [pin(t) for t in w.host_w2]
         self.hot = [list(h) for h in hot] if hot is not None else [list(range(E)) for _ in range(L)]
         self.hot_w13, self.hot_w2, self.table = [], [], []
         for l in range(L):
             idx = torch.tensor(self.hot[l] if self.hot[l] else [0])
-            h13 = self.host_w13[l][idx].cuda()
-            packed = torch.empty_like(h13)
-            _C.check(_C.lib.monofab_pack_w13(h13.data_ptr(), packed.data_ptr(), h13.shape[0], I, H, 2, None))
-            torch.cuda.synchronize()
-            self.hot_w13.append(packed)
-            self.hot_w2.append(self.host_w2[l][idx].cuda())
+            key = (id(w.host_w13[l]), id(w.host_w2[l]), tuple(self.hot[l]))
+            if key not in hot_cache:
+                h13 = self.host_w13[l][idx].cuda()
+                packed = torch.empty_like(h13)
+                _C.check(_C.lib.monofab_pack_w13(h13.data_ptr(), packed.data_ptr(), h13.shape[0], I, H, 2, None))
+                torch.cuda.synchronize()
+                hot_cache[key] = (packed, self.host_w2[l][idx].cuda())
+            self.hot_w13.append(hot_cache[key][0])
+            self.hot_w2.append(hot_cache[key][1])
             table = torch.zeros(E, 2, dtype=torch.int32)
             table[:, 1] = torch.arange(E)
             if self.hot[l]:
@@ -115,9 +129,14 @@ class ModelLane:
     Request state lives in slot-indexed arrays (block table row, sequence length, last token),
     as in the reference's lane (StepArgs, csrc/fabric/model_types.h:116-128)."""
 
-    def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None):
+    def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None,
+                 logit_rows=None, min_form=16):
         self.fab, self.lane_id, self.cfg, self.w, self.kv = fab, lane_id, cfg, weights, kv
         self.T, self.S, self.bt_stride, self.max_chunks = max_tokens, max_slots, bt_stride, max_chunks
+        # rows of the lm_head (requests that continue; every row when a caller wants all logits), and the
+        # smallest row-block height the published plans will use for host-resident experts
+        self.logit_rows = logit_rows or max(max_tokens, max_slots)
+        self.min_form = min_form
         H, I, E, K, L, V = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, cfg.num_layers, cfg.vocab
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
         self.qkv_dim = (hq + 2 * hkv) * 128
@@ -129,7 +148,7 @@ class ModelLane:
         self.x, self.x2, self.xn = z(T, H, dt=bf), z(T, H, dt=bf), z(T, H, dt=bf)
         self.qkv = z(T, self.qkv_dim, dt=bf)
         self.q, self.ao = z(T, hq, 128, dt=bf), z(T, hq, 128, dt=bf)
-        self.xlast, self.logits = z(max(T, S), H, dt=bf), z(max(T, S), V, dt=torch.float32)
+        self.xlast, self.logits = z(self.logit_rows, H, dt=bf), z(self.logit_rows, V, dt=torch.float32)
         # routing and expert workspaces
         self.rl = z(T, E, dt=torch.float32)
         self.topk_ids, self.topk_w = z(T, K), z(T, K, dt=torch.float32)
@@ -232,12 +251,13 @@ class ModelLane:
             residual=residual.data_ptr() if residual is not None else 0, ld_res=ld_res)), dtype=torch.uint8).cuda()
         self._keep.append(args)
         xm = amaps[HEIGHTS.index(bm)]
-        tiles = [Tile(K_GEMM, i=(n0, m0, min(bm, rows - m0), 0), a=(args.data_ptr(), wmap, xm))
-                 for m0 in range(0, rows, bm) for n0 in range(0, n_out, 128)]
+        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
+        tiles = tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm)
         return p.stage(tiles, mark=mark, label=label)
 
     def _rows(self, kind, args, rows, per):
-        return [Tile(kind, i=(r0, min(per, rows - r0)), a=(args.data_ptr(),)) for r0 in range(0, rows, per)]
+        r0 = np.arange(0, rows, per)
+        return tile_array(kind, i0=r0, i1=np.minimum(per, rows - r0), a0=args.data_ptr())
 
     def _moe(self, p, l, T, prev, norm_w, expands):
         """Stages of layer l's MoE block after `prev` (xn, x2 ready); returns the combine stage."""
@@ -267,7 +287,7 @@ class ModelLane:
             p.after(w13[e], red[e])
             p.after(red[e], w2[e])
             p.after(w2[e], s_cb)
-        dyn = (T * cfg.top_k // 16 + E) * (cfg.intermediate // 64 + H // 128)
+        dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
         expands.append((ex, l, T, w13[0], red[0], w2[0], s_cb, dyn))
         return s_cb
 
@@ -363,7 +383,7 @@ class ModelLane:
             sample_rows.append((row + n - 1 if all_logits else r, slot))
             row += n
         T = row
-        assert 0 < T <= self.T
+        assert 0 < T <= self.T and (T if all_logits else len(batch)) <= self.logit_rows
         i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()  # noqa: E731
         self.tokens[:T], self.tok_pos[:T], self.tok_slot[:T], self.gather[:T] = i32(tokens), i32(pos), i32(slots), i32(gather)
         self.req_info[:len(batch)] = i32(req_info)
@@ -399,7 +419,7 @@ class ModelLane:
         writes the step's attention items, and the sample tiles publish the next tokens."""
         cfg = self.cfg
         R = len(slots)
-        assert 0 < R <= min(self.T, 256)
+        assert 0 < R <= min(self.T, 256, self.logit_rows)
         self.row_req[:R] = torch.tensor(slots, dtype=torch.int32).cuda()
         self.gather[:R] = torch.arange(R, dtype=torch.int32).cuda()
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
