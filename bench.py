@@ -444,21 +444,25 @@ def run_ours(args):
                                     "sample": f"{len(cpu_times)} batches of {BATCH} tokens, whole layer, "
                                               "oracle/torch_path.py on the host CPU"}
         if world == 1 and not args.no_mixed_lane:
-            line["mixed_lane"] = mixed_lane_run()
+            line["fabric_layer"] = side_run(["monoserve_b200.benchmarks.fabric_layer"], 300)
+            line["mixed_lane"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--steps", "6"], 900)
         print(json.dumps(line), flush=True)
     layer.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def mixed_lane_run():
-    """The second metric BASELINE.json names, mixed-lane decode TPOT p50, on config 3 (the full
-    48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a 128-sequence decode
-    lane in one persistent kernel): run by monoserve_b200/benchmarks/mixed_lane.py in a process
-    of its own (it pins 58 GB of host memory for the expert stacks), about a minute and a half."""
-    cmd = [sys.executable, "-m", "monoserve_b200.benchmarks.mixed_lane", "--steps", "6"]
+def side_run(module_args, timeout_s):
+    """Two more measurements ride on the N = 1 line, each made by a module of
+    monoserve_b200/benchmarks in a process of its own: `fabric_layer`, the same MoE layer as a
+    repeating fabric program timed by the in-kernel iteration timer (the reference's protocol for
+    MoE-layer tokens/s), and `mixed_lane`, the second metric BASELINE.json names: decode TPOT p50
+    on config 3 (the full 48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a
+    128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory)."""
+    cmd = [sys.executable, "-m"] + module_args
     try:
-        out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=os.path.dirname(os.path.abspath(__file__)))
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s,
+                             cwd=os.path.dirname(os.path.abspath(__file__)))
         last = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
         if out.returncode != 0 or not last:
             return {"error": (out.stderr or out.stdout)[-300:]}
@@ -477,7 +481,7 @@ def main():
                     help="profiling target: only W warm-up + K device-resident steps, no JSON line")
     ap.add_argument("--all-hot", action="store_true", help="with --ncu: place all 128 experts in HBM")
     ap.add_argument("--no-mixed-lane", action="store_true",
-                    help="skip the config-3 mixed-lane TPOT run that the N=1 line carries as `mixed_lane`")
+                    help="skip the fabric-path runs that the N=1 line carries as `fabric_layer` and `mixed_lane`")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.ncu:

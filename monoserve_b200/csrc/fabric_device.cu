@@ -16,7 +16,7 @@
 //     seqlock-style double read.
 // What differs from the reference, on purpose:
 //   * a worker is warp-specialised: warp 0 schedules and runs AHEAD of the data
-//     path through a two-deep ring of work records, so claims, descriptor loads
+//     path through a four-deep ring of work records, so claims, descriptor loads
 //     and epoch refreshes overlap the previous tile; warps 1..4 execute tiles and
 //     are the epilogue of GEMM tiles; warp 5 issues the TMA copies and warp 6 owns
 //     TMEM and issues tcgen05.mma (gemm_core.cuh), with accumulators double-buffered
@@ -47,6 +47,7 @@ constexpr int kWorklistCap = 512;
 constexpr uint32_t kMaxBatch = 8;
 constexpr uint32_t kBatchDivisor = 128;
 constexpr int kExecThreads = 128;
+constexpr int kSlots = 4;   // work records the scheduler may run ahead of the exec warps
 constexpr int kWorkerThreads = 32 + kExecThreads + 64;   // scheduler, exec/epilogue, TMA producer, MMA
 constexpr unsigned long long kRingWaitBudgetNs = 2000000000ull;
 
@@ -350,6 +351,101 @@ __device__ void drain(DeviceState& S, uint32_t lane, const ProgramDesc* P, Workl
   if (wl.overflow) raise_error(S, kFabErrWorklist);
 }
 
+// The same bookkeeping by one warp (the first exec warp): lane 0 owns the worklist, the
+// iteration boundary and the host mirror; the successors of a completed stage are counted
+// down and armed by the 32 lanes side by side, so that a stage with 128 successors (the
+// permute stage of an MoE layer) releases them in a few microseconds instead of one global
+// round trip after another.  Every lane of the warp must call it.
+__device__ void drain_warp(DeviceState& S, uint32_t lane_id, const ProgramDesc* P, Worklist& wl) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  LaneState& L = S.lane[lane_id];
+  for (;;) {
+    uint32_t sf = 0, sc = 0, tag = 0;
+    int have = 0;
+    if (lane == 0) {
+      while (wl.n > 0) {
+        const uint32_t s = wl.pop();
+        trace_stage(S, lane_id, s, 1, ld_volatile(&L.tag));
+        const StageStatic& st = P->stages[s];
+        const uint32_t flags = ld_volatile(&st.flags);
+        if (flags & kStageMark) mirror_lane(S, lane_id, 3, ld_volatile(&st.mark));
+        if (flags & kStageReset) {
+          P = end_iteration(S, lane_id, P, wl);
+          continue;
+        }
+        tag = ld_volatile(&L.tag) & kTagMask;
+        sf = ld_volatile(&st.succ_first);
+        sc = ld_volatile(&st.succ_count);
+        have = 1;
+        break;
+      }
+    }
+    have = __shfl_sync(kFull, have, 0);
+    if (!have) break;
+    sf = __shfl_sync(kFull, sf, 0);
+    sc = __shfl_sync(kFull, sc, 0);
+    tag = __shfl_sync(kFull, tag, 0);
+    const ProgramDesc* Pw =
+        reinterpret_cast<const ProgramDesc*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(P), 0));
+    for (uint32_t k0 = 0; k0 < sc; k0 += 32) {
+      const uint32_t k = k0 + lane;
+      int kind = 0;   // 1 ungated ring entry, 2 link ring entry, 3 an empty stage: completes at once
+      uint32_t entry = 0, j = 0;
+      if (k < sc) {
+        j = Pw->succ[sf + k];
+        const uint32_t flags = ld_volatile(&Pw->stages[j].flags);
+        if (!(flags & kStageSkip) && atomicSub(&Pw->runtime[j].deps, 1u) == 1u) {
+          trace_stage(S, lane_id, j, 0, tag);
+          if (ld_volatile(&Pw->stages[j].count) == 0) {
+            kind = 3;
+          } else {
+            atomicExch(&Pw->runtime[j].tag_next, static_cast<unsigned long long>(tag & kTagMask) << 32);
+            __threadfence();   // armed before lane 0 publishes the entry
+            entry = make_entry(j, tag);
+            kind = (ld_volatile(&Pw->stages[j].flags) & kStageLink) ? 2 : 1;
+          }
+        }
+      }
+      for (int want = 1; want <= 3; ++want) {
+        unsigned mask = __ballot_sync(kFull, kind == want);
+        uint32_t batch[32];
+        int n = 0;
+        while (mask) {
+          const int src = __ffs(mask) - 1;
+          mask &= mask - 1;
+          const uint32_t v = __shfl_sync(kFull, want == 3 ? j : entry, src);
+          if (lane == 0) {
+            if (want == 3) wl.push(v);
+            else batch[n++] = v;
+          }
+        }
+        if (lane == 0 && want != 3) ring_push_n(S, L, want == 2, batch, n);
+      }
+    }
+  }
+  if (lane == 0 && wl.overflow) raise_error(S, kFabErrWorklist);
+}
+
+__device__ void complete_tile_warp(DeviceState& S, uint32_t lane_id, const ProgramDesc* P, uint32_t s, uint32_t n,
+                                   Worklist& wl) {
+  int last = 0;
+  if ((threadIdx.x & 31) == 0) {
+    const unsigned int d = atomicAdd(&P->runtime[s].done, n) + n;
+    last = d == ld_volatile(&P->stages[s].count);
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  __threadfence();   // acquire the other workers' tiles of the stage before releasing its successors
+  if ((threadIdx.x & 31) == 0) {
+    wl.n = 0;
+    wl.overflow = false;
+    wl.push(s);
+  }
+  __syncwarp();
+  drain_warp(S, lane_id, P, wl);
+}
+
 __device__ void complete_tile(DeviceState& S, uint32_t lane, const ProgramDesc* P, uint32_t s, uint32_t n) {
   const unsigned int d = atomicAdd(&P->runtime[s].done, n) + n;
   if (d == ld_volatile(&P->stages[s].count)) {
@@ -518,8 +614,8 @@ __device__ void trace_tile(unsigned long long base, uint32_t idx, unsigned long 
 
 // Scratch of the tile the exec warps are running; tiles run one at a time per worker,
 // so they share one block instead of each holding static shared memory of its own.
-constexpr int kExecScratchInts = 4 * (kMaxExperts + 1) + 16;
-__shared__ int s_exec_scratch[kExecScratchInts];
+constexpr int kExecScratchInts = 5 * (kMaxExperts + 1) + 16 + 64;
+__shared__ __align__(16) int s_exec_scratch[kExecScratchInts];
 
 }  // namespace fab
 }  // namespace mf
@@ -630,22 +726,17 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
 
 // Router tile (kind 38, csrc/fabric/tiles/aux.cuh:326-417, RouterArgs): scores,
 // top-K, renormalisation, per-expert counts; the logits row is zeroed once read.
-// With chunk_counts / pair_rank set (fields this library adds) the tile must cover
-// one chunk of kFabChunk rows starting at a multiple of kFabChunk; it then also
-// writes the stable rank of every (token, pick) pair inside (chunk, expert) and the
-// chunk's per-expert pair counts, which make the pack order deterministic.
+// With chunk_counts set (a field this library adds) the tile counts every pick into
+// chunk_counts[row / kFabChunk][expert] instead of counts[expert]: integer adds, so the
+// result does not depend on the order in which tiles run; the expand tile turns these
+// per-chunk counts into prefixes and the permute tiles into the stable pack order.
 __device__ void tile_router(const TileDesc& t, int tid) {
-  int* const s_ids = s_exec_scratch;                             // [kFabChunk * kMaxTopK]
-  int* const s_hist = s_exec_scratch + kFabChunk * kMaxTopK;     // [kMaxExperts]
-  static_assert(kFabChunk * kMaxTopK + kMaxExperts <= kExecScratchInts, "router scratch");
-  const RouterArgs& A = *reinterpret_cast<const RouterArgs*>(t.a[0]);
+  RouterArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int E = static_cast<int>(A.E), K = static_cast<int>(A.K);
   if (E < 1 || E > kMaxExperts || K < 1 || K > kMaxTopK) return;
-  const bool ranks = A.chunk_counts != 0 && A.pair_rank != 0 && t.i1 <= kFabChunk;
-  if (ranks) {
-    for (int e = tid; e < kMaxExperts; e += kExecThreads) s_hist[e] = 0;
-  }
+  int* chunk_counts = reinterpret_cast<int*>(A.chunk_counts);
   for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
     int id;
     float w;
@@ -654,80 +745,142 @@ __device__ void tile_router(const TileDesc& t, int tid) {
     if (lane < K) {
       reinterpret_cast<int*>(A.topk_ids)[static_cast<size_t>(r) * K + lane] = id;
       reinterpret_cast<float*>(A.topk_w)[static_cast<size_t>(r) * K + lane] = w;
-      if (A.counts) atomicAdd(reinterpret_cast<int*>(A.counts) + id, 1);
-      if (ranks) s_ids[(r - t.i0) * K + lane] = id;
+      if (chunk_counts) atomicAdd(chunk_counts + static_cast<size_t>(r / kFabChunk) * E + id, 1);
+      else if (A.counts) atomicAdd(reinterpret_cast<int*>(A.counts) + id, 1);
     }
   }
-  if (!ranks) return;
-  exec_sync();
-  const int pairs = static_cast<int>(t.i1) * K;
-  int* pair_rank = reinterpret_cast<int*>(A.pair_rank) + static_cast<size_t>(t.i0) * K;
-  for (int p = tid; p < pairs; p += kExecThreads) {
-    const int me = s_ids[p];
-    int rank = 0;
-    for (int q = 0; q < p; ++q) rank += s_ids[q] == me;
-    pair_rank[p] = rank;
-    atomicAdd(&s_hist[me], 1);
-  }
-  exec_sync();
-  int* cc = reinterpret_cast<int*>(A.chunk_counts) + static_cast<size_t>(t.i0 / kFabChunk) * E;
-  for (int e = tid; e < E; e += kExecThreads) cc[e] = s_hist[e];
 }
 
 // Router projection tile (kind 48; not in the reference, whose router GEMM sums
-// K-split partials with atomics): logits[t][e] for rows [i0, i0 + i1) and all
-// experts, lane l summing h = 256 j + 8 l + i in order with fmaf, then the xor
-// butterfly: the same bits as the stream kernel and the oracle.
+// K-split partials with atomics): logits[t][e] for rows [i0, i0 + i1) and experts
+// [i2, i2 + i3) (i3 = 0: all), lane l summing h = 256 j + 8 l + i in order with fmaf, then
+// the xor butterfly: the same bits as the stream kernel and the oracle.  A warp keeps one
+// expert's weight row in registers and walks the tile's rows, so the weights are read
+// once per tile and the activation rows come from L1.
+template <int J>
+__device__ __forceinline__ void router_logits_rows(const __nv_bfloat16* x, const __nv_bfloat16* wr, float* logits, int H,
+                                                   int E, int r0, int rows, int e_lo, int e_hi, int warp, int lane) {
+  if constexpr (J > 0) {
+    // two experts' weight rows in registers, two activation rows at a time: four independent
+    // fmaf chains per lane, each in the defined order
+    for (int e = e_lo + 2 * warp; e < e_hi; e += 2 * (kExecThreads / 32)) {
+      const bool two_e = e + 1 < e_hi;
+      const uint4* wa = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * H);
+      const uint4* wb = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(two_e ? e + 1 : e) * H);
+      uint4 wva[J > 0 ? J : 1], wvb[J > 0 ? J : 1];
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        wva[j] = __ldg(wa + 32 * j + lane);
+        wvb[j] = __ldg(wb + 32 * j + lane);
+      }
+      for (int r = r0; r < r0 + rows; r += 2) {
+        const bool two_r = r + 1 < r0 + rows;
+        const uint4* xa = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
+        const uint4* xb = reinterpret_cast<const uint4*>(x + static_cast<size_t>(two_r ? r + 1 : r) * H);
+        float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;   // a[row][expert]
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          float x0[8], x1[8], w0[8], w1[8];
+          unpack8(xa[32 * j + lane], x0);
+          unpack8(xb[32 * j + lane], x1);
+          unpack8(wva[j], w0);
+          unpack8(wvb[j], w1);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a00 = __fmaf_rn(x0[i], w0[i], a00);
+            a01 = __fmaf_rn(x0[i], w1[i], a01);
+            a10 = __fmaf_rn(x1[i], w0[i], a10);
+            a11 = __fmaf_rn(x1[i], w1[i], a11);
+          }
+        }
+        a00 = warp_sum_xor(a00);
+        a01 = warp_sum_xor(a01);
+        a10 = warp_sum_xor(a10);
+        a11 = warp_sum_xor(a11);
+        if (lane == (e & 31)) {
+          logits[static_cast<size_t>(r) * E + e] = a00;
+          if (two_r) logits[static_cast<size_t>(r + 1) * E + e] = a10;
+        }
+        if (two_e && lane == ((e + 1) & 31)) {
+          logits[static_cast<size_t>(r) * E + e + 1] = a01;
+          if (two_r) logits[static_cast<size_t>(r + 1) * E + e + 1] = a11;
+        }
+      }
+    }
+  } else {
+    const int nj = H / 256;
+    for (int e = e_lo + warp; e < e_hi; e += kExecThreads / 32) {
+      const uint4* w4 = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * H);
+      for (int r = r0; r < r0 + rows; ++r) {
+        const uint4* x4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
+        float acc = 0.f;
+        for (int j = 0; j < nj; ++j) {
+          float xf[8], wf[8];
+          unpack8(x4[32 * j + lane], xf);
+          unpack8(__ldg(w4 + 32 * j + lane), wf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc = __fmaf_rn(xf[i], wf[i], acc);
+        }
+        acc = warp_sum_xor(acc);
+        if (lane == (e & 31)) logits[static_cast<size_t>(r) * E + e] = acc;
+      }
+    }
+  }
+}
+
 __device__ void tile_router_logits(const TileDesc& t, int tid) {
-  const LogitsArgs& A = *reinterpret_cast<const LogitsArgs*>(t.a[0]);
+  LogitsArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
-  const int H = static_cast<int>(A.H), E = static_cast<int>(A.E), nj = H / 256;
+  const int H = static_cast<int>(A.H), E = static_cast<int>(A.E);
   const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(A.x);
   const __nv_bfloat16* wr = reinterpret_cast<const __nv_bfloat16*>(A.wr);
   float* logits = reinterpret_cast<float*>(A.logits);
-  // unit = (row, group of 16 experts); the four warps stride over the units
-  const int groups = (E + 15) / 16;
-  for (int u = warp; u < static_cast<int>(t.i1) * groups; u += kExecThreads / 32) {
-    const int r = t.i0 + u / groups, eg = u % groups;
-    const uint4* x4 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
-    for (int e = eg * 16; e < min(E, eg * 16 + 16); ++e) {
-      const uint4* w4 = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * H);
-      float acc = 0.f;
-      for (int j = 0; j < nj; ++j) {
-        float xf[8], wf[8];
-        unpack8(x4[32 * j + lane], xf);
-        unpack8(__ldg(w4 + 32 * j + lane), wf);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc = __fmaf_rn(xf[i], wf[i], acc);
-      }
-      acc = warp_sum_xor(acc);
-      if (lane == (e & 31)) logits[static_cast<size_t>(r) * E + e] = acc;
-    }
+  const int e_lo = static_cast<int>(t.i2), e_hi = t.i3 ? min(E, e_lo + static_cast<int>(t.i3)) : E;
+  const int r0 = static_cast<int>(t.i0), rows = static_cast<int>(t.i1);
+  switch (H / 256) {
+    case 2: router_logits_rows<2>(x, wr, logits, H, E, r0, rows, e_lo, e_hi, warp, lane); break;
+    case 4: router_logits_rows<4>(x, wr, logits, H, E, r0, rows, e_lo, e_hi, warp, lane); break;
+    case 8: router_logits_rows<8>(x, wr, logits, H, E, r0, rows, e_lo, e_hi, warp, lane); break;
+    default: router_logits_rows<0>(x, wr, logits, H, E, r0, rows, e_lo, e_hi, warp, lane); break;
   }
 }
 
 // Permute tile (kind 40, csrc/fabric/tiles/aux.cuh:648-684, PermuteArgs) for rows
-// [i0, i0 + i1) of one chunk: pair lists and expert-sorted activation rows.  With
-// pair_rank / chunk_prefix set the position is starts[e] + chunk prefix + rank
-// (token ascending, pick ascending); otherwise the reference's arrival order through
-// atomicAdd(fill[e]).  pair_pos (optional) receives the packed row of every pair.
+// [i0, i0 + i1) of ONE chunk of kFabChunk rows: pair lists and expert-sorted activation rows.
+// With chunk_prefix set the position of pair (token, pick) is
+//   starts[e] + pairs of e in earlier chunks + pairs of e earlier in this chunk
+// (token ascending, pick ascending: the stable pack), the last term counted here from
+// the chunk's ids; otherwise the reference's arrival order through atomicAdd(fill[e]).
+// pair_pos (optional) receives the packed row of every pair.
 __device__ void tile_permute(const TileDesc& t, int tid) {
-  const PermuteArgs& A = *reinterpret_cast<const PermuteArgs*>(t.a[0]);
+  int* const s_ids = s_exec_scratch;   // ids of the chunk's rows up to the end of this tile
+  PermuteArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int K = static_cast<int>(A.K), H = static_cast<int>(A.H), E = static_cast<int>(A.E), n16 = H / 8;
   const int* ids = reinterpret_cast<const int*>(A.topk_ids);
   const float* tw = reinterpret_cast<const float*>(A.topk_w);
   const int* starts = reinterpret_cast<const int*>(A.starts);
-  const bool stable = A.pair_rank != 0 && A.chunk_prefix != 0;
+  const bool stable = A.chunk_prefix != 0;
+  const uint32_t chunk0 = (t.i0 / kFabChunk) * kFabChunk;
+  if (stable) {
+    const int n = static_cast<int>(t.i0 + t.i1 - chunk0) * K;
+    for (int p = tid; p < n; p += kExecThreads) s_ids[p] = ids[static_cast<size_t>(chunk0) * K + p];
+    exec_sync();
+  }
   for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
     int pos = 0;
     if (lane < K) {
       const int e = ids[static_cast<size_t>(r) * K + lane];
-      if (stable)
-        pos = starts[e] + reinterpret_cast<const int*>(A.chunk_prefix)[static_cast<size_t>(r / kFabChunk) * E + e] +
-              reinterpret_cast<const int*>(A.pair_rank)[static_cast<size_t>(r) * K + lane];
-      else
+      if (stable) {
+        const int me = static_cast<int>(r - chunk0) * K + lane;
+        int rank = 0;
+        for (int q = 0; q < me; ++q) rank += s_ids[q] == e;
+        pos = starts[e] + reinterpret_cast<const int*>(A.chunk_prefix)[static_cast<size_t>(r / kFabChunk) * E + e] + rank;
+      } else {
         pos = starts[e] + atomicAdd(reinterpret_cast<int*>(A.fill) + e, 1);
+      }
       reinterpret_cast<int*>(A.pair_token)[pos] = r;
       reinterpret_cast<float*>(A.pair_weight)[pos] = tw[static_cast<size_t>(r) * K + lane];
       if (A.pair_pos) reinterpret_cast<int*>(A.pair_pos)[static_cast<size_t>(r) * K + lane] = pos;
@@ -747,11 +900,16 @@ __device__ void tile_permute(const TileDesc& t, int tid) {
 // w2 epilogue and finishes in AddNorm): x[t] = bf16(x2[t] + sum_k w[t][k] * y[pos(t,k)])
 // with the sum in pick order, then optionally out = rmsnorm(x) * w.
 __device__ void tile_combine(const TileDesc& t, int tid) {
-  const CombineArgs& A = *reinterpret_cast<const CombineArgs*>(t.a[0]);
+  CombineArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int K = static_cast<int>(A.K), H = static_cast<int>(A.H), n16 = H / 8;
   const float* y = reinterpret_cast<const float*>(A.y);
-  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+  // Without a following norm nothing ties a row to one warp: the four warps then share every
+  // row, each taking a quarter of its 8-element column groups (the sums per element are the same).
+  const bool split = A.w == 0;
+  const int c_begin = split ? warp * 32 + lane : lane, c_step = split ? kExecThreads : 32;
+  for (uint32_t r = t.i0 + (split ? 0 : warp); r < t.i0 + t.i1; r += split ? 1 : kExecThreads / 32) {
     int pos = 0;
     float w = 0.f;
     if (lane < K) {
@@ -761,7 +919,7 @@ __device__ void tile_combine(const TileDesc& t, int tid) {
     const uint4* x2 = A.x2 ? reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(A.x2) + static_cast<size_t>(r) * H) : nullptr;
     uint4* xo = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(A.x) + static_cast<size_t>(r) * H);
     float ss = 0.f;
-    for (int c = lane; c < n16; c += 32) {
+    for (int c = c_begin; c < n16; c += c_step) {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -802,7 +960,8 @@ __device__ void tile_combine(const TileDesc& t, int tid) {
 // from the reference: counts may come from the router tiles' chunk counts (then the
 // per-chunk prefixes are produced too, for the stable pack); form 0 maps to 256-row
 // blocks (one pass over the weights) instead of K-split tiles with a reduce stage;
-// an overflow of the dynamic region raises an error bit instead of trapping.
+// an overflow of the dynamic region raises an error bit instead of trapping; red_stage0 =
+// 0xffffffff says the program has no reduce stages (w2[e] follows w13[e] directly).
 __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid) {
   int* const s_cnt = s_exec_scratch;                              // [kMaxExperts]
   int* const s_start = s_cnt + kMaxExperts + 1;                   // [kMaxExperts + 1]
@@ -812,19 +971,46 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   int& s_active = s_exec_scratch[4 * (kMaxExperts + 1) + 1];
   int& s_skipped = s_exec_scratch[4 * (kMaxExperts + 1) + 2];
   int& s_overflow = s_exec_scratch[4 * (kMaxExperts + 1) + 3];
-  const ExpandArgs& A = *reinterpret_cast<const ExpandArgs*>(t.a[0]);
+  int* const s_info = s_exec_scratch + 4 * (kMaxExperts + 1) + 16;   // [kMaxExperts]: slot << 12 | region << 4 | height class
+  // [28] u64: GemmArgs and activation maps per height class (w13, w2), weight maps per region (w13, w2)
+  unsigned long long* const s_tab = reinterpret_cast<unsigned long long*>(s_exec_scratch + 5 * (kMaxExperts + 1) + 16 + 1);
+  ExpandArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int E = static_cast<int>(A.E);
   if (E < 1 || E > kMaxExperts) return;
+  // the program's arrays, read once: the descriptor itself lives in global memory
+  TileDesc* const p_tiles = P->tiles;
+  StageStatic* const p_stages = P->stages;
+  StageRuntime* const p_runtime = P->runtime;
+  // diagnostics: with no reduce stages, red_args may name 8 u64 words for phase time stamps
+  unsigned long long* stamps = (A.red_stage0 == 0xffffffffu && tid == 0) ? reinterpret_cast<unsigned long long*>(A.red_args) : nullptr;
+  int n_stamp = 0;
+  auto stamp = [&]() {
+    if (stamps && n_stamp < 8) stamps[n_stamp++] = globaltimer_ns();
+  };
+  stamp();
   int* counts = reinterpret_cast<int*>(A.counts);
   int* starts = reinterpret_cast<int*>(A.starts);
   for (int e = tid; e < E; e += kExecThreads) {
     int cnt = 0;
     if (A.chunk_counts) {
+      // exclusive prefix over the chunks into chunk_prefix (the same buffer when none is given);
+      // the counts are cleared for the next iteration's router tiles
       int* cc = reinterpret_cast<int*>(A.chunk_counts);
-      for (uint32_t c = 0; c < A.chunks; ++c) {
-        const int v = cc[static_cast<size_t>(c) * E + e];
-        cc[static_cast<size_t>(c) * E + e] = cnt;   // exclusive prefix over the chunks
-        cnt += v;
+      int* cp = A.chunk_prefix ? reinterpret_cast<int*>(A.chunk_prefix) : cc;
+      for (uint32_t c0 = 0; c0 < A.chunks; c0 += 16) {
+        int v[16];
+        const uint32_t n = min(16u, A.chunks - c0);
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) v[i] = i < n ? cc[static_cast<size_t>(c0 + i) * E + e] : 0;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; ++i) {
+          if (i < n) {
+            if (cp != cc) cc[static_cast<size_t>(c0 + i) * E + e] = 0;
+            cp[static_cast<size_t>(c0 + i) * E + e] = cnt;
+            cnt += v[i];
+          }
+        }
       }
     } else {
       cnt = counts[e];
@@ -845,6 +1031,7 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
     s_form = (f == 0 || f == 16 || f == 32 || f == 64 || f == 128) ? static_cast<int>(f) : 64;
   }
   exec_sync();
+  stamp();
   auto scan = [&](const int* v, int* out) {   // exclusive prefix sums by thread 0 (E <= 256)
     if (tid == 0) {
       int run = 0, act = 0;
@@ -859,6 +1046,7 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   };
   scan(s_cnt, s_start);
   exec_sync();
+  stamp();
   const int active = s_active;
   for (int e = tid; e <= E; e += kExecThreads) starts[e] = s_start[e];
   const int* table = reinterpret_cast<const int*>(A.table);
@@ -869,73 +1057,101 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   };
   for (int e = tid; e < E; e += kExecThreads) {
     const int M = s_cnt[e];
-    const bool link = table[2 * e] == static_cast<int>(A.host_region);
+    const int region = table[2 * e], slot = table[2 * e + 1];
+    const bool link = region == static_cast<int>(A.host_region);
     const int bm = block_rows(M, link);
+    int cls = 0;
+    while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
     s_n[e] = M > 0 ? ((M + bm - 1) / bm) * (f13 + f2) : 0;
+    s_info[e] = (slot << 12) | ((region & 0xff) << 4) | cls;
+  }
+  if (tid < 5) {
+    s_tab[tid] = reinterpret_cast<const unsigned long long*>(A.w13_args)[tid];
+    s_tab[5 + tid] = reinterpret_cast<const unsigned long long*>(A.w2_args)[tid];
+    s_tab[10 + tid] = reinterpret_cast<const unsigned long long*>(A.xp_maps)[tid];
+    s_tab[15 + tid] = reinterpret_cast<const unsigned long long*>(A.h_maps)[tid];
+  } else if (tid >= 32 && tid < 36) {   // weight maps of regions 0..3 (host, hot tier, two staging buffers)
+    s_tab[20 + tid - 32] = reinterpret_cast<const unsigned long long*>(A.w13_maps)[tid - 32];
+    s_tab[24 + tid - 32] = reinterpret_cast<const unsigned long long*>(A.w2_maps)[tid - 32];
   }
   exec_sync();
+  stamp();
   scan(s_n, s_off);
   // close the expert stages' previous activation before their tiles and counts change
+  const bool has_red = A.red_stage0 != 0xffffffffu;   // the reduce stages of the reference's chain are optional here
   for (int e = tid; e < E; e += kExecThreads) {
-    atomicExch(&P->runtime[A.w13_stage0 + e].tag_next, 0ull);
-    atomicExch(&P->runtime[A.red_stage0 + e].tag_next, 0ull);
-    atomicExch(&P->runtime[A.w2_stage0 + e].tag_next, 0ull);
+    atomicExch(&p_runtime[A.w13_stage0 + e].tag_next, 0ull);
+    if (has_red) atomicExch(&p_runtime[A.red_stage0 + e].tag_next, 0ull);
+    atomicExch(&p_runtime[A.w2_stage0 + e].tag_next, 0ull);
   }
   __threadfence();
   exec_sync();
+  stamp();
   if (s_off[E] > static_cast<int>(A.dyn_cap)) {
     if (tid == 0) raise_error(S, kFabErrDynOverflow);
     s_overflow = 1;   // every thread writes the same value
   }
   exec_sync();
-  const unsigned long long* w13_args = reinterpret_cast<const unsigned long long*>(A.w13_args);
-  const unsigned long long* w2_args = reinterpret_cast<const unsigned long long*>(A.w2_args);
-  const unsigned long long* xp_maps = reinterpret_cast<const unsigned long long*>(A.xp_maps);
-  const unsigned long long* h_maps = reinterpret_cast<const unsigned long long*>(A.h_maps);
+  stamp();
   const unsigned long long* w13_maps = reinterpret_cast<const unsigned long long*>(A.w13_maps);
   const unsigned long long* w2_maps = reinterpret_cast<const unsigned long long*>(A.w2_maps);
+  // The tiles of one expert are contiguous (blocks x (f13 + f2) descriptors of 64 bytes): a warp
+  // writes them as consecutive 16-byte pieces, one expert after the other, so the stores coalesce.
+  {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int e = warp; e < E; e += kExecThreads / 32) {
+      const int M = s_overflow ? 0 : s_cnt[e];
+      if (M == 0) continue;
+      const int info = s_info[e];
+      const int slot = info >> 12, region = (info >> 4) & 0xff, cls = info & 0xf;
+      const int bm = 16 << cls;
+      const int blocks = (M + bm - 1) / bm;
+      const int n13 = blocks * f13, total = blocks * (f13 + f2);
+      uint4* dst = reinterpret_cast<uint4*>(p_tiles + A.dyn_first + s_off[e]);
+      for (int q = lane; q < total * 4; q += 32) {
+        const int ti = q >> 2, part = q & 3;
+        const bool is13 = ti < n13;
+        const int local = is13 ? ti : ti - n13, per = is13 ? f13 : f2;
+        const int blk = local / per, f = local - blk * per;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (part == 0) {          // kind | lane | flags, stage, i0 first weight row, i1 first activation row
+          v.x = kTileGemm;
+          v.z = static_cast<uint32_t>(is13 ? f * 64 : f * 128);
+          v.w = static_cast<uint32_t>(s_start[e] + blk * bm);
+        } else if (part == 1) {   // i2 rows, i3 weight slot, a[0] GemmArgs
+          const unsigned long long a0 = s_tab[(is13 ? 0 : 5) + cls];
+          v.x = static_cast<uint32_t>(min(bm, M - blk * bm));
+          v.y = static_cast<uint32_t>(slot);
+          v.z = static_cast<uint32_t>(a0);
+          v.w = static_cast<uint32_t>(a0 >> 32);
+        } else if (part == 2) {   // a[1] weight map, a[2] activation map
+          const unsigned long long a1 = region < 4 ? s_tab[(is13 ? 20 : 24) + region] : (is13 ? w13_maps[region] : w2_maps[region]);
+          const unsigned long long a2 = s_tab[(is13 ? 10 : 15) + cls];
+          v = make_uint4(static_cast<uint32_t>(a1), static_cast<uint32_t>(a1 >> 32), static_cast<uint32_t>(a2),
+                         static_cast<uint32_t>(a2 >> 32));
+        } else {                  // a[3] K range (all), a[4] fp32 scale per weight row
+          unsigned long long a4 = 0;
+          if (is13 && A.w13_scale) a4 = A.w13_scale + static_cast<unsigned long long>(e) * 2 * A.I * 4;
+          if (!is13 && A.w2_scale) a4 = A.w2_scale + static_cast<unsigned long long>(e) * A.H * 4;
+          v.z = static_cast<uint32_t>(a4);
+          v.w = static_cast<uint32_t>(a4 >> 32);
+        }
+        dst[q] = v;
+      }
+    }
+  }
   for (int e = tid; e < E; e += kExecThreads) {
     const int M = s_overflow ? 0 : s_cnt[e];
-    const int region = table[2 * e], slot = table[2 * e + 1];
+    const int region = table[2 * e];
     const bool link = region == static_cast<int>(A.host_region);
     const uint32_t base = A.dyn_first + s_off[e];
-    StageStatic& s13 = P->stages[A.w13_stage0 + e];
-    StageStatic& sr = P->stages[A.red_stage0 + e];
-    StageStatic& s2 = P->stages[A.w2_stage0 + e];
+    StageStatic& s13 = p_stages[A.w13_stage0 + e];
+    StageStatic& s2 = p_stages[A.w2_stage0 + e];
     const int bm = block_rows(M, link);
     int cls = 0;
     while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
     const int blocks = M > 0 ? (M + bm - 1) / bm : 0;
     const int n13 = blocks * f13, n2 = blocks * f2;
-    TileDesc d{};
-    d.kind = kTileGemm;
-    uint32_t k = base;
-    for (int b = 0; b < blocks; ++b) {
-      d.i1 = s_start[e] + b * bm;
-      d.i2 = min(bm, M - b * bm);
-      d.i3 = slot;
-      d.a[0] = w13_args[cls];
-      d.a[1] = w13_maps[region];
-      d.a[2] = xp_maps[cls];
-      d.a[4] = A.w13_scale ? A.w13_scale + static_cast<unsigned long long>(e) * 2 * A.I * 4 : 0;
-      for (int f = 0; f < f13; ++f) {
-        d.i0 = f * 64;
-        P->tiles[k++] = d;
-      }
-    }
-    for (int b = 0; b < blocks; ++b) {
-      d.i1 = s_start[e] + b * bm;
-      d.i2 = min(bm, M - b * bm);
-      d.i3 = slot;
-      d.a[0] = w2_args[cls];
-      d.a[1] = w2_maps[region];
-      d.a[2] = h_maps[cls];
-      d.a[4] = A.w2_scale ? A.w2_scale + static_cast<unsigned long long>(e) * A.H * 4 : 0;
-      for (int n = 0; n < f2; ++n) {
-        d.i0 = n * 128;
-        P->tiles[k++] = d;
-      }
-    }
     s13.first = base;
     s13.count = n13;
     s13.flags = link ? kStageLink : 0u;
@@ -943,9 +1159,12 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
       s13.flags = kStageSkip;
       atomicAdd(&s_skipped, 1);
     }
-    sr.first = base + n13;
-    sr.count = 0;
-    sr.flags = 0u;
+    if (has_red) {
+      StageStatic& sr = p_stages[A.red_stage0 + e];
+      sr.first = base + n13;
+      sr.count = 0;
+      sr.flags = 0u;
+    }
     s2.first = base + n13;
     s2.count = n2;
     s2.flags = link ? kStageLink : 0u;
@@ -955,7 +1174,8 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   }
   __threadfence();
   exec_sync();
-  if (tid == 0 && s_skipped > 0) atomicSub(&P->runtime[A.join_stage].deps, static_cast<unsigned int>(s_skipped));
+  stamp();
+  if (tid == 0 && s_skipped > 0) atomicSub(&p_runtime[A.join_stage].deps, static_cast<unsigned int>(s_skipped));
 }
 
 // RMSNorm tile (kind 36) and AddNorm tile (kind 41), NormArgs
@@ -963,7 +1183,8 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
 // it, zeroes the fp32 accumulator rows, then normalises; gather >= 0 copies the
 // normalised row to out2[gather].
 __device__ void tile_norm(const TileDesc& t, int tid, bool add) {
-  const NormArgs& A = *reinterpret_cast<const NormArgs*>(t.a[0]);
+  NormArgs A;   // a copy in registers: the block lives in global memory
+  load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int H = static_cast<int>(A.H), n16 = H / 8;
   for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
@@ -1056,14 +1277,15 @@ __device__ __forceinline__ AttnCtx attn_ctx(const AttnWork& w, AttnShared& sh, v
 }
 
 struct WorkerShared {
-  uint64_t slot_full[2], slot_empty[2];
+  uint64_t slot_full[kSlots], slot_empty[kSlots];
   GemmBarriers bar;
+  Worklist wl;                  // completed stages the first exec warp still has to release
   AttnShared attn;              // barriers of attention items, armed once; every role counts their phases
   unsigned int wait_note[3];    // producer, MMA, first exec warp: tile << 8 | site of the current wait
   unsigned long long wait_ctx[3];   // and the record / phase counts the role had then
   unsigned int tiles_done;      // work records the exec warps have finished
   unsigned int mma_done;        // work records the MMA warp has finished
-  WorkSlot slot[2];
+  WorkSlot slot[kSlots];
   WorkerState ws;
   unsigned long long t0;
   uint32_t tmem_base;
@@ -1080,7 +1302,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
   const uint32_t worker = first_worker + blockIdx.x;
   volatile int* abort_flag = &sh.abort_flag;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kSlots; ++i) {
       mbar_init(&sh.slot_full[i], 1);
       mbar_init(&sh.slot_empty[i], 3);   // exec thread 0, producer, MMA
     }
@@ -1117,8 +1339,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
       WorkerState& ws = sh.ws;
       const unsigned long long t_start = globaltimer_ns();
       for (uint32_t n = 0;; ++n) {
-        const int s = n & 1;
-        if (!mbar_wait_bounded(&sh.slot_empty[s], ((n >> 1) & 1) ^ 1, abort_flag, kForever)) break;
+        const int s = n % kSlots;
+        if (!mbar_wait_bounded(&sh.slot_empty[s], ((n / kSlots) & 1) ^ 1, abort_flag, kForever)) break;
         uint32_t cmd = kCmdRun;
         if (ws.left == 0) {
           for (;;) {
@@ -1185,8 +1407,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     bool prev_attn = false;
     uint32_t aq = 0, ab[2] = {0, 0};   // phases the attention barriers have completed
     for (uint32_t n = 0;; ++n) {
-      const int s = n & 1;
-      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
+      const int s = n % kSlots;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n / kSlots) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       bool ok = true;
@@ -1218,8 +1440,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     uint32_t g = 0;   // GEMM tiles seen: accumulator buffer and parity
     uint32_t aq = 0, ab[2] = {0, 0};
     for (uint32_t n = 0;; ++n) {
-      const int s = n & 1;
-      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
+      const int s = n % kSlots;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n / kSlots) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       bool ok = true;
@@ -1247,8 +1469,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     uint32_t g = 0;
     uint32_t aq = 0, ab[2] = {0, 0};
     for (uint32_t n = 0;; ++n) {
-      const int s = n & 1;
-      if (!mbar_wait_bounded(&sh.slot_full[s], (n >> 1) & 1, abort_flag, kForever)) break;
+      const int s = n % kSlots;
+      if (!mbar_wait_bounded(&sh.slot_full[s], (n / kSlots) & 1, abort_flag, kForever)) break;
       const WorkSlot& w = sh.slot[s];
       if (w.cmd == kCmdExit) break;
       if (tid == 0) {
@@ -1273,14 +1495,19 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         raise_error(S, kFabErrBadTile);
       }
       exec_sync();
-      if (tid == 0) {
-        if (w.link) atomicSub(&S.lane[w.tile_lane].inflight, 1u);
-        __threadfence();   // this worker's writes are visible device-wide before the tile counts as done
-        note_tile(S, worker, w, 1ull << 62);
-        complete_tile(S, w.tile_lane, w.prog, w.stage, 1);
-        note_tile(S, worker, w, 0);
-        *reinterpret_cast<volatile unsigned int*>(&sh.tiles_done) = n + 1;
-        mbar_arrive(&sh.slot_empty[s]);
+      if (tid < 32) {   // the first exec warp does the completion bookkeeping
+        if (tid == 0) {
+          if (w.link) atomicSub(&S.lane[w.tile_lane].inflight, 1u);
+          __threadfence();   // this worker's writes are visible device-wide before the tile counts as done
+          note_tile(S, worker, w, 1ull << 62);
+        }
+        __syncwarp();
+        complete_tile_warp(S, w.tile_lane, w.prog, w.stage, 1, sh.wl);
+        if (tid == 0) {
+          note_tile(S, worker, w, 0);
+          *reinterpret_cast<volatile unsigned int*>(&sh.tiles_done) = n + 1;
+          mbar_arrive(&sh.slot_empty[s]);
+        }
       }
     }
   }

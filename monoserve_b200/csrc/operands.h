@@ -39,7 +39,8 @@ namespace mf {
   U64(counts) U64(starts) U64(fill) U64(table) U64(w13_maps) U64(w2_maps) U64(xp_maps) U64(h_maps) \
   U64(w13_args) U64(w2_args) U64(hist) U64(w13_asym_args) U64(w2_asym_args) U64(red_args) \
   U64(w13_scale) U64(w2_scale) U32(E) U32(H) U32(I) U32(host_region) U32(w13_stage0) U32(w2_stage0) \
-  U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage) U32(chunks) U64(chunk_counts)
+  U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage) U32(chunks) U64(chunk_counts) \
+  U64(chunk_prefix)
 
 #define MF_REDUCE_ARGS(U64, U32, F32) U64(ws) U64(out) U32(I) U32(ld_ws) U32(ld_out)
 

@@ -7,8 +7,9 @@ when the layer's (region, slot) table places the expert in pinned host memory.
 `MoELane` builds the same chain on this library's tiles:
 
   router_logits (48) -> router (38, with stable ranks) -> expand (39) -> permute (40)
-  -> per expert: w13[e] (GEMM tiles, SiLU-mul) -> red[e] (empty) -> w2[e] (GEMM tiles,
-  fp32 rows) -> combine (47: un-permute + weighted sum in pick order + residual)
+  -> per expert: w13[e] (GEMM tiles, SiLU-mul) -> w2[e] (GEMM tiles, fp32 rows; no reduce
+  stage between them: nothing is K-split) -> combine (47: un-permute + weighted sum in pick
+  order + residual)
 
 All device memory is allocated here, before the fabric starts
 (monoserve/runtime/lane.py:101-122 lists the same workspaces).
@@ -21,7 +22,9 @@ from monoserve_b200.fabric.args import pack
 
 K_GEMM, K_ROUTER, K_EXPAND, K_PERMUTE, K_COMBINE, K_LOGITS = 32, 38, 39, 40, 47, 48
 REGION_HOST, REGION_HOT = 0, 1
-CHUNK = 16
+CHUNK = 16    # rows of one rank chunk of the stable pack (kFabChunk)
+SUB = 4       # rows per router / permute tile: one per exec warp; divides CHUNK, so a tile stays inside a chunk
+LOGIT_ROWS, LOGIT_EXPERTS = 8, 16   # a router-projection tile: rows x experts
 EPI_SILU_MUL, EPI_ROWS_F32 = 1, 5
 
 
@@ -31,6 +34,14 @@ def _block(name, **fields):
 
 def _u64(values):
     return torch.tensor([int(v) for v in values], dtype=torch.int64).cuda()
+
+
+def logits_tiles(args_ptr, T, E):
+    """Router-projection tiles (kind 48): blocks of LOGIT_ROWS rows x LOGIT_EXPERTS experts."""
+    import numpy as np
+    r0, e0 = np.meshgrid(np.arange(0, T, LOGIT_ROWS), np.arange(0, E, LOGIT_EXPERTS), indexing="ij")
+    return tile_array(K_LOGITS, i0=r0, i1=np.minimum(LOGIT_ROWS, T - r0), i2=e0, i3=np.minimum(LOGIT_EXPERTS, E - e0),
+                      a0=args_ptr)
 
 
 def _row_tiles(kind, args, rows, per):
@@ -83,20 +94,21 @@ class MoELane:
         self.topk_ids, self.topk_w = z(T, K), z(T, K, dt=torch.float32)
         self.counts, self.fill, self.starts = z(E), z(E), z(E + 1)
         self.chunks = -(-T // CHUNK)
-        self.chunk_counts, self.pair_rank = z(self.chunks, E), z(T, K)
+        self.chunk_counts, self.chunk_prefix = z(self.chunks, E), z(self.chunks, E)
         self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
         self.xp, self.h = z(P + 256, H, dt=torch.bfloat16), z(P + 256, I, dt=torch.bfloat16)
         self.y = z(P + 256, H, dt=torch.float32)
         self.hist = z(E)
+        self.expand_stamps = torch.zeros(8, dtype=torch.int64, device=dev)   # phase time stamps of the expand tile
         # operand blocks
         self.logits_args = None
         self.router_args = _block("RouterArgs", logits=self.logits, topk_ids=self.topk_ids, topk_w=self.topk_w,
                                   counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
-                                  chunk_counts=self.chunk_counts, pair_rank=self.pair_rank)
+                                  chunk_counts=self.chunk_counts)
         self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
                                    fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
-                                   src=self.xn, dst=self.xp, K=K, H=H, pair_rank=self.pair_rank,
-                                   chunk_prefix=self.chunk_counts, pair_pos=self.pair_pos, E=E)
+                                   src=self.xn, dst=self.xp, K=K, H=H, chunk_prefix=self.chunk_prefix,
+                                   pair_pos=self.pair_pos, E=E)
         self.combine_args = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2,
                                    x=self.x, K=K, H=H, eps=0.0)
         heights = [16, 32, 64, 128, 256]
@@ -137,34 +149,32 @@ class MoELane:
         nw = self.fab.num_workers
         p = Program()
         logits_args = _block("LogitsArgs", x=self.xn, wr=self.wr, logits=self.logits, T=T, H=H, E=E)
-        per_lg = max(1, -(-T // (2 * nw)))
-        s_lg = p.stage(_row_tiles(K_LOGITS, logits_args, T, per_lg), label=("router_logits", mark_layer))
-        s_rt = p.stage(_row_tiles(K_ROUTER, self.router_args, T, CHUNK), label=("router", mark_layer))
+        s_lg = p.stage(logits_tiles(logits_args.data_ptr(), T, E), label=("router_logits", mark_layer))
+        s_rt = p.stage(_row_tiles(K_ROUTER, self.router_args, T, SUB), label=("router", mark_layer))
         p.after(s_lg, s_rt)
         ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
         s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", mark_layer))
         p.after(s_rt, s_ex)
-        s_pm = p.stage(_row_tiles(K_PERMUTE, self.permute_args, T, CHUNK), label=("permute", mark_layer))
+        s_pm = p.stage(_row_tiles(K_PERMUTE, self.permute_args, T, SUB), label=("permute", mark_layer))
         p.after(s_ex, s_pm)
         w13 = [p.stage(label=("w13", mark_layer)) for _ in range(E)]
-        red = [p.stage(label=("red", mark_layer)) for _ in range(E)]
         w2 = [p.stage(label=("w2", mark_layer)) for _ in range(E)]
-        per_cb = max(1, -(-T // (2 * nw)))
+        per_cb = max(2, -(-T // (2 * nw)))
         s_cb = p.stage(_row_tiles(K_COMBINE, self.combine_args, T, per_cb), mark=(mark_layer << 8) | 3,
                        label=("combine", mark_layer))
         for e in range(E):
             p.after(s_pm, w13[e])
-            p.after(w13[e], red[e])
-            p.after(red[e], w2[e])
+            p.after(w13[e], w2[e])
             p.after(w2[e], s_cb)
         dyn = self.dynamic_tiles(T)
         p.reserve(dyn)
         blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.table,
                     w13_maps=self.w13_maps, w2_maps=self.w2_maps, xp_maps=self.xp_maps, h_maps=self.h_maps,
                     w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist, E=E, H=H, I=self.I,
-                    host_region=REGION_HOST, w13_stage0=w13[0], w2_stage0=w2[0], red_stage0=red[0],
+                    host_region=REGION_HOST, w13_stage0=w13[0], w2_stage0=w2[0], red_stage0=0xffffffff,
                     dyn_first=p.dynamic_first, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb,
-                    chunks=-(-T // CHUNK), chunk_counts=self.chunk_counts)
+                    chunks=-(-T // CHUNK), chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix,
+                    red_args=self.expand_stamps)
         ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
         torch.cuda.synchronize()
         self._keep += [logits_args, ex]

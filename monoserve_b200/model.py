@@ -22,6 +22,7 @@ from monoserve_b200 import _C
 from monoserve_b200.attention import SCALE_LOG2, fabric_maps, fabric_tiles, plan_items
 from monoserve_b200.fabric import Program, Tile, tile_array
 from monoserve_b200.fabric.args import pack
+from monoserve_b200.lane import SUB, logits_tiles
 
 K_GEMM, K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE, K_RMSNORM, K_QKROPE = 32, 33, 34, 35, 36, 37
 K_ROUTER, K_EXPAND, K_PERMUTE, K_EMBED, K_SAMPLE, K_ATTN_PLAN, K_COMBINE, K_LOGITS = 38, 39, 40, 42, 43, 44, 47, 48
@@ -153,7 +154,7 @@ class ModelLane:
         self.rl = z(T, E, dt=torch.float32)
         self.topk_ids, self.topk_w = z(T, K), z(T, K, dt=torch.float32)
         self.counts, self.fill, self.starts, self.hist = z(E), z(E), z(E + 1), z(L, E)
-        self.chunk_counts, self.pair_rank = z(-(-T // CHUNK), E), z(T, K)
+        self.chunk_counts, self.chunk_prefix = z(-(-T // CHUNK), E), z(-(-T // CHUNK), E)
         self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
         self.xp, self.h = z(P + 256, H, dt=bf), z(P + 256, I, dt=bf)
         self.y = z(P + 256, H, dt=torch.float32)
@@ -229,11 +230,11 @@ class ModelLane:
                 max_chunks=self.max_chunks, page_size=self.kv.page, q_map_small=q_small))
         self.router_args = _block("RouterArgs", logits=self.rl, topk_ids=self.topk_ids, topk_w=self.topk_w,
                                   counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
-                                  chunk_counts=self.chunk_counts, pair_rank=self.pair_rank)
+                                  chunk_counts=self.chunk_counts)
         self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
                                    fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
-                                   src=self.xn, dst=self.xp, K=K, H=H, pair_rank=self.pair_rank,
-                                   chunk_prefix=self.chunk_counts, pair_pos=self.pair_pos, E=E)
+                                   src=self.xn, dst=self.xp, K=K, H=H, chunk_prefix=self.chunk_prefix,
+                                   pair_pos=self.pair_pos, E=E)
         self.step_args = _block("StepArgs", row_req=self.row_req, last_token=self.last_token, seq_len=self.seq_len,
                                 block_table=self.bt, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
                                 req_info=self.req_info, bt_stride=self.bt_stride, page_size=self.kv.page)
@@ -269,26 +270,24 @@ class ModelLane:
                     w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps)
         ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
         self._keep += [lg, cb, ex]
-        per = max(1, -(-T // (2 * nw)))
-        s_lg = p.stage(self._rows(K_LOGITS, lg, T, per), label=("router_logits", l))
-        s_rt = p.stage(self._rows(K_ROUTER, self.router_args, T, CHUNK), label=("router", l))
+        per = max(2, -(-T // (2 * nw)))
+        s_lg = p.stage(logits_tiles(lg.data_ptr(), T, E), label=("router_logits", l))
+        s_rt = p.stage(self._rows(K_ROUTER, self.router_args, T, SUB), label=("router", l))
         s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", l))
-        s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, CHUNK), label=("permute", l))
+        s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, SUB), label=("permute", l))
         p.after(prev, s_lg)
         p.after(s_lg, s_rt)
         p.after(s_rt, s_ex)
         p.after(s_ex, s_pm)
         w13 = [p.stage(label=("w13", l)) for _ in range(E)]
-        red = [p.stage(label=("red", l)) for _ in range(E)]
         w2 = [p.stage(label=("w2", l)) for _ in range(E)]
         s_cb = p.stage(self._rows(K_COMBINE, cb, T, per), mark=(l << 8) | 3, label=("combine", l))
         for e in range(E):
             p.after(s_pm, w13[e])
-            p.after(w13[e], red[e])
-            p.after(red[e], w2[e])
+            p.after(w13[e], w2[e])
             p.after(w2[e], s_cb)
         dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
-        expands.append((ex, l, T, w13[0], red[0], w2[0], s_cb, dyn))
+        expands.append((ex, l, T, w13[0], 0xffffffff, w2[0], s_cb, dyn))
         return s_cb
 
     def _finish_dynamic(self, p, expands, plans):
@@ -306,7 +305,7 @@ class ModelLane:
                         w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
                         I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
                         dyn_first=at, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb, chunks=-(-T // CHUNK),
-                        chunk_counts=self.chunk_counts)
+                        chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix)
             ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
             at += dyn
         for blob, fields, dyn in plans:
