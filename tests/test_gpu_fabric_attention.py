@@ -73,3 +73,55 @@ def test_attention_items_in_fabric(fab, hq, hkv, page, part_tiles):
         ref = dense_reference(q[row:row + n].float(), dense[r][0], dense[r][1], hq, hkv, L - n)
         assert (got[row:row + n] - ref).abs().max().item() < TOL, r
         row += n
+
+
+@pytest.mark.parametrize("hq,hkv,chunk_keys", [(32, 4, 0), (32, 4, 1024), (96, 8, 0)])
+def test_decode_plan_tile(fab, hq, hkv, chunk_keys):
+    """The per-step plan of the decode attention (kind 44): from req_info = {row, position, 1, keys}
+    the tile writes one work item per (request, KV head, key range) and the merge tiles of split
+    requests into the program's dynamic region; two iterations of the program give the same,
+    correct result (the stages are re-planned every iteration)."""
+    from monoserve_b200 import _C
+    from monoserve_b200.fabric import tile_array
+    lens = [3000, 1100, 5000, 700, 129]
+    R, page, max_chunks = len(lens), 16, 8
+    kc, vc, bt, dense = make_cache(lens, hkv, page, seed=3 + hq)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(R, hq, 128, generator=g).to(torch.bfloat16)
+    qd, kcd, vcd, btd = q.cuda(), kc.cuda(), vc.cuda(), bt.cuda()
+    out = torch.zeros_like(qd)
+    req_info = torch.tensor([(r, L - 1, 1, L) for r, L in enumerate(lens)], dtype=torch.int32).cuda()
+    ws_rows = max_chunks * R * hq
+    ws = torch.zeros(ws_rows * 130, dtype=torch.float32, device="cuda")
+    q_map, q_small, k_map, v_map = fabric_maps(fab, qd, kcd, vcd)
+    args = torch.frombuffer(bytearray(pack(
+        "AttnArgs", q_map=q_map, k_map=k_map, v_map=v_map, out=out, ws_o=ws, ws_m=ws.data_ptr() + ws_rows * 512,
+        block_table=btd, req_info=req_info, scale_log2=SCALE_LOG2, bt_stride=btd.shape[1], hq=hq, hkv=hkv,
+        group=hq // hkv, max_chunks=max_chunks, page_size=page, q_map_small=q_small)), dtype=torch.uint8).cuda()
+    blob = torch.zeros(_C.struct_layouts()["AttnPlanArgs"][0], dtype=torch.uint8, device="cuda")
+    p = Program()
+    s_plan = p.stage(tile_array(44, a0=blob.data_ptr()))
+    s_attn = p.stage()
+    s_merge = p.stage()
+    p.after(s_plan, s_attn)
+    p.after(s_attn, s_merge)
+    dyn = R * hkv * (max_chunks + 1)
+    p.reserve(dyn)
+    blob.copy_(torch.frombuffer(bytearray(pack(
+        "AttnPlanArgs", attn=args.data_ptr(), req_info=req_info.data_ptr(), rows=R, hkv=hkv, chunk_keys=chunk_keys,
+        stage_attn=s_attn, stage_comb=s_merge, dyn_first=p.dynamic_first, dyn_cap=dyn, workers=fab.num_workers)),
+        dtype=torch.uint8))
+    torch.cuda.synchronize()
+    h = p.upload(fab, first=s_plan, iterations=2)
+    fab.start()
+    fab.publish(map=[0] * fab.num_workers, caps=[0], order=[0], programs=[h])
+    t0 = time.time()
+    while fab.progress()["lanes"][0]["iterations"] < 2:
+        assert time.time() - t0 < 30, (fab.progress()["error"], fab.wait_notes())
+        time.sleep(1e-3)
+    fab.stop()
+    assert fab.progress()["error"] == 0
+    got = out.float().cpu()
+    for r, L in enumerate(lens):
+        ref = dense_reference(q[r:r + 1].float(), dense[r][0], dense[r][1], hq, hkv, L - 1)
+        assert (got[r:r + 1] - ref).abs().max().item() < TOL, r
