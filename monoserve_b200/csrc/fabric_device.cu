@@ -20,7 +20,8 @@
 //     and epoch refreshes overlap the previous tile; warps 1..4 execute tiles and
 //     are the epilogue of GEMM tiles; warp 5 issues the TMA copies and warp 6 owns
 //     TMEM and issues tcgen05.mma (gemm_core.cuh), with accumulators double-buffered
-//     across consecutive GEMM tiles; an attention work item (attention_core.cuh) uses
+//     across consecutive GEMM tiles; for FP8-e4m3 weights the exec warps are also the
+//     converters of every operand stage (W8A16); an attention work item (attention_core.cuh) uses
 //     the same three roles with the operand ring as its Q / K / V / P tiles, after the
 //     worker's earlier tiles have drained;
 //   * no wait is unbounded and nothing traps: a ring publication that waits too
@@ -118,7 +119,6 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   uint4* dst = reinterpret_cast<uint4*>(&A);
 #pragma unroll
   for (int i = 0; i < 8; ++i) dst[i] = __ldcg(src + i);
-  if (A.w_fp8) return false;   // FP8 tiles need the converter warps of the stand-alone kernel
   if (A.bm < 16 || A.bm > kGemmMaxN || (A.bm & (A.bm - 1))) return false;
   const CUtensorMap* wrec = reinterpret_cast<const CUtensorMap*>(t.a[1]);
   const CUtensorMap* xrec = reinterpret_cast<const CUtensorMap*>(t.a[2]);
@@ -148,7 +148,7 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   w.valid = 1;
   w.a_packed = packed;
   w.block = -1;
-  w.w_fp8 = 0;
+  w.w_fp8 = A.w_fp8 != 0;   // e4m3 weights: the exec warps expand every stage to bf16 before its MMAs
   return w.k_tiles > 0 && A.epi <= kEpiRowsF32;
 }
 
@@ -1468,6 +1468,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     const int tid = threadIdx.x - 32;
     uint32_t g = 0;
     uint32_t aq = 0, ab[2] = {0, 0};
+    GemmPipe conv_pipe;
     for (uint32_t n = 0;; ++n) {
       const int s = n % kSlots;
       if (!mbar_wait_bounded(&sh.slot_full[s], (n / kSlots) & 1, abort_flag, kForever)) break;
@@ -1488,8 +1489,22 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         else softmax_role<128, 1>(w.attn, c);
         attn_advance(c.n_tiles, aq, ab);
       } else if (w.is_gemm) {
-        if (!gemm_epilogue(w.gemm, sh.bar, tmem_base, g & 1, (g >> 1) & 1, abort_flag) && tid == 0)
-          raise_error(S, kFabErrTileWait);
+        // The exec warps follow the operand ring like the producer and the MMA warp do: for e4m3
+        // weights they are the converters of every stage (then the tile's epilogue), for bf16
+        // weights they only step their cursor over the tile's stages.
+        bool ok = true;
+        if (w.gemm.w_fp8) {
+          ok = gemm_convert(w.gemm, ring, sh.bar, conv_pipe, tid, abort_flag);
+        } else {
+          const uint32_t size = gemm_stage_bytes(w.gemm);
+          for (int kt = 0; kt < w.gemm.k_tiles; ++kt) {
+            uint32_t vb, ve;
+            conv_pipe.alloc(size, vb, ve);
+            conv_pipe.advance();
+          }
+        }
+        ok = ok && gemm_epilogue(w.gemm, sh.bar, tmem_base, g & 1, (g >> 1) & 1, abort_flag);
+        if (!ok && tid == 0) raise_error(S, kFabErrTileWait);
         ++g;
       } else if (!run_core_tile(S, w, tid, worker, &sh.t0) && tid == 0) {
         raise_error(S, kFabErrBadTile);

@@ -79,6 +79,10 @@ struct GemmPipe {   // a role's cursor over the stage ring; producer and MMA war
   uint32_t slot = 0;    // barrier pair of the next stage
   uint32_t parity = 0;  // parity of that pair's current use
   uint32_t i = 0;       // stages allocated so far
+  // MMA role: one bit per barrier pair = parity of the pair's converter barrier.  That barrier
+  // completes a phase only for stages with e4m3 weights, so when bf16 and e4m3 tiles share the
+  // ring its parity is not a function of the stage's position, unlike full / empty.
+  uint32_t conv_bits = 0;
   // Next stage of `size` bytes (a multiple of 1024): its offset in the ring, and
   // the virtual interval it covers (including a skipped tail when it wraps).
   __device__ __forceinline__ uint32_t alloc(uint32_t size, uint32_t& vbegin, uint32_t& vend) {
@@ -208,10 +212,12 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
       uint32_t vb, ve;
       const uint32_t phys = pipe.alloc(size, vb, ve);
       const long long tw = wait_cycles ? clock64() : 0;
-      if (!mbar_wait_bounded(&ready[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) {
+      const uint32_t ready_parity = w.w_fp8 ? (pipe.conv_bits >> pipe.slot) & 1u : pipe.parity;
+      if (!mbar_wait_bounded(&ready[pipe.slot], ready_parity, abort_flag, kWaitBudgetNs)) {
         ok = 0;
         break;
       }
+      if (w.w_fp8) pipe.conv_bits ^= 1u << pipe.slot;
       if (wait_cycles) wait_cycles[0] += clock64() - tw;
       const long long ti = wait_cycles ? clock64() : 0;
       const uint64_t da = desc0 + ((ring_addr + phys) >> 4);
@@ -232,6 +238,7 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
   pipe.slot = __shfl_sync(0xffffffffu, pipe.slot, 0);
   pipe.parity = __shfl_sync(0xffffffffu, pipe.parity, 0);
   pipe.i = __shfl_sync(0xffffffffu, pipe.i, 0);
+  pipe.conv_bits = __shfl_sync(0xffffffffu, pipe.conv_bits, 0);
   return ok != 0;
 }
 

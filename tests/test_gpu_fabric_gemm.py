@@ -169,9 +169,91 @@ def test_dense_split_k(fab, bm):
     assert (out - ref).abs().max().item() < 0.02 * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("where", ["hbm", "cpu"])
+def test_fp8_expert_ffn(fab, where):
+    """FP8-e4m3 weights with per-output-channel fp32 scales (W8A16): the scenario of the reference's
+    tests/test_fabric_gemm.py:246-283 — w13 tiles with the SiLU-and-multiply epilogue and w2 tiles with
+    the weighted-add epilogue over quantised experts in HBM or in pinned host memory — against the
+    de-quantised weights in fp32, mixed with bf16 tiles on the same workers."""
+    from oracle import torch_path as tp
+    torch.manual_seed(7)
+    E, H, I, T, TOPK = 8, 512, 256, 64, 2
+    w13 = torch.randn(E, 2 * I, H) * 0.05
+    w2 = torch.randn(E, H, I) * 0.05
+    q13, s13, d13 = tp.quantize_fp8(w13)
+    q2, s2, d2 = tp.quantize_fp8(w2)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    topk = torch.stack([torch.randperm(E, device="cuda")[:TOPK] for _ in range(T)])
+    tw = torch.rand(T, TOPK, device="cuda")
+    pairs = sorted((int(topk[t, k]), t, float(tw[t, k])) for t in range(T) for k in range(TOPK))
+    xp = torch.zeros(len(pairs) + 64, H, device="cuda", dtype=torch.bfloat16)
+    xp[:len(pairs)] = torch.stack([x[t] for _, t, _ in pairs])
+    ptok = torch.tensor([t for _, t, _ in pairs], dtype=torch.int32, device="cuda")
+    pw = torch.tensor([wt for _, _, wt in pairs], dtype=torch.float32, device="cuda")
+    starts = {}
+    for i, (e, _, _) in enumerate(pairs):
+        starts.setdefault(e, [i, 0])[1] += 1
+    hbuf = torch.zeros(len(pairs) + 64, I, device="cuda", dtype=torch.bfloat16)
+    out32 = torch.zeros(T, H, device="cuda", dtype=torch.float32)
+    if where == "cpu":
+        k1, b13 = pinned_alias(q13)
+        k2, b2 = pinned_alias(q2)
+    else:
+        k1, k2 = q13.cuda(), q2.cuda()
+        b13, b2 = k1.data_ptr(), k2.data_ptr()
+    sc13, sc2 = s13.cuda(), s2.cuda()
+    bm = 16
+
+    def fp8_map(base, shape):   # (E, rows, K) e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
+        n_e, rows, k = shape
+        return fab.tensor_map(base, [k, rows, n_e], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0)
+
+    a13 = args_tensor(out=hbuf.data_ptr(), ld_out=I, k_tiles=H // 64, epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I,
+                      w_fp8=1)
+    a2 = args_tensor(out=out32.data_ptr(), ld_out=H, k_tiles=I // 64, epi=EPI_WADD, bm=bm, n_limit=H,
+                     pair_token=ptok.data_ptr(), pair_weight=pw.data_ptr(), w_fp8=1)
+    m13, m2 = fp8_map(b13, q13.shape), fp8_map(b2, q2.shape)
+    mx, mh = act_map(fab, xp, bm), act_map(fab, hbuf, bm)
+    t13, t2 = [], []
+    for e, (s0, cnt) in starts.items():
+        for m0 in range(s0, s0 + cnt, bm):
+            mv = min(bm, s0 + cnt - m0)
+            t13 += [Tile(KIND_GEMM, i=(f0, m0, mv, e), a=(a13.data_ptr(), m13, mx, 0, sc13.data_ptr() + e * 2 * I * 4))
+                    for f0 in range(0, I, 64)]
+            t2 += [Tile(KIND_GEMM, i=(n0, m0, mv, e), a=(a2.data_ptr(), m2, mh, 0, sc2.data_ptr() + e * H * 4))
+                   for n0 in range(0, H, 128)]
+    # a bf16 dense GEMM in a parallel stage, so that workers alternate between the two kinds of tiles
+    wd = (torch.randn(1, 256, H, device="cuda") * 0.05).to(torch.bfloat16)
+    od = torch.zeros(T, 256, device="cuda", dtype=torch.bfloat16)
+    ad = args_tensor(out=od.data_ptr(), ld_out=256, k_tiles=H // 64, epi=EPI_STORE, bm=64, n_limit=256)
+    md, mxd = weight_map(fab, wd.data_ptr(), wd.shape), act_map(fab, x, 64)
+    td = [Tile(KIND_GEMM, i=(n0, 0, T, 0), a=(ad.data_ptr(), md, mxd)) for n0 in range(0, 256, 128)] * 8
+    p = Program()
+    s_first = p.stage([Tile(0)])
+    s13_ = p.stage(t13, link=(where == "cpu"))
+    s2_ = p.stage(t2, link=(where == "cpu"))
+    sd = p.stage(td)
+    p.after(s_first, s13_)
+    p.after(s_first, sd)
+    p.after(s13_, s2_)
+    run_program(fab, p, s_first, caps=(8,))
+    ref = torch.zeros(T, H)
+    xc = x.float().cpu()
+    for t in range(T):
+        for k in range(TOPK):
+            e = int(topk[t, k])
+            ref[t] += float(tw[t, k]) * tp.ffn(xc[t:t + 1], d13[e], d2[e])[0]
+    got = out32.cpu()
+    rel = float((got - ref).norm() / ref.norm())
+    assert rel < 3e-2, rel
+    refd = xc @ wd[0].float().cpu().t()
+    rel_d = float((od.float().cpu() - refd).norm() / refd.norm())
+    assert rel_d < 1e-2, rel_d
+    del k1, k2
+
+
 def test_unsupported_gemm_tile_is_reported(fab):
-    """An FP8 tile (needs the converter warps of the stand-alone kernel) and a bad tile
-    height are reported through the error word; the program still ends."""
+    """A bad tile height is reported through the error word; the program still ends."""
     z = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
     args = args_tensor(out=z.data_ptr(), ld_out=64, k_tiles=1, epi=EPI_STORE, bm=24, n_limit=64)
     xm = act_map(fab, z, 16)
