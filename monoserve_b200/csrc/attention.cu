@@ -33,9 +33,13 @@
 //     it then leaves its unnormalised fp32 O rows and (max, sum) in a workspace and
 //     attention_combine_kernel merges the parts in part order.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issue,
-// warps 2..5 softmax / output (TMEM lane quadrant = warp % 4).  Every wait is
-// bounded; a timeout raises the status word and the CTA leaves, freeing its TMEM.
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issue, warps 2..5 and
+// 6..9 two softmax / output groups (TMEM lane quadrant = warp % 4): the two threads of a query
+// row each take half of a tile's key columns and half of the row's output, and agree on the row
+// maximum through shared memory once per tile; a quad-replicated (decode) item is done by the
+// first group alone.  One softmax warp per SM sub-partition is bound by instruction latency
+// (max, ex2, bf16 packing per element); the second group doubles what is in flight.  Every
+// wait is bounded; a timeout raises the status word and the CTA leaves, freeing its TMEM.
 #include "attention_core.cuh"
 
 namespace mf {
@@ -49,6 +53,7 @@ __device__ unsigned long long g_attn_trace[8];
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
+  __shared__ float xbuf[2 * 128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AttnWork w;
   w.q_map = &p.q_map;
@@ -74,13 +79,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   c.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   c.q_phase = 0;
   c.note = nullptr;
+  c.xbuf = xbuf;
   c.base[0] = c.base[1] = 0;
   attn_derive(w, c);
 
   if (threadIdx.x == 0) {
     sh.abort_flag = 0;
     sh.fail_site = 0;
-    attn_barriers_init(sh);
+    attn_barriers_init(sh, 128 * kAttnGroups);
   }
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, kAttnTmemCols);
@@ -97,9 +103,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
     if (lane == 0) attn_mma<2>(w, c);
     __syncwarp();
   } else if (c.rep) {
-    softmax_role<32, 2>(w, c);
+    softmax_role<true, 2, kAttnGroups>(w, c, (warp - 2) >> 2);
   } else {
-    softmax_role<128, 2>(w, c);
+    softmax_role<false, 2, kAttnGroups>(w, c, (warp - 2) >> 2);
   }
 
   tc_fence_before_sync();

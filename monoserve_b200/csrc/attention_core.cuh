@@ -11,7 +11,8 @@
 
 namespace mf {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnGroups = 2;                   // softmax warp groups of the stand-alone kernel
+constexpr int kAttnThreads = 64 + 128 * kAttnGroups;
 constexpr int kHeadDim = 128;
 constexpr int kKeysPerTile = 128;
 constexpr int kHalfBytes = 128 * 128;            // 128 rows x 64 bf16: one swizzle atom column, 16 KB
@@ -19,6 +20,7 @@ constexpr int kTileBytes = 2 * kHalfBytes;       // 128 x 128 bf16
 constexpr int kAttnSmemBytes = kTileBytes * 7 + 1024;   // Q, K x2, V x2, P x2
 constexpr int kAttnTmemCols = 512;               // S x2 (256) + O (128), allocated as a power of two
 constexpr unsigned long long kAttnWaitNs = 4000000000ull;
+constexpr float kMaxSlack = 8.f;   // how far a row maximum may exceed the reference point of its exponentials
 
 
 struct AttnShared {
@@ -68,6 +70,7 @@ struct AttnCtx {
   uint32_t q_phase;       // q_full
   uint32_t base[2];       // every per-tile barrier [s]: tiles of parity s so far
   volatile unsigned int* note;   // this role's wait note (tile << 8 | site), or NULL
+  float* xbuf;            // two softmax groups: float [2][128] for the exchange between the halves of a row
 };
 
 __device__ __forceinline__ void attn_note(const AttnCtx& c, int j, unsigned int site) {
@@ -97,7 +100,7 @@ __device__ __forceinline__ void attn_derive(const AttnWork& w, AttnCtx& c) {
 }
 
 // By one thread, once per CTA, before a CTA-wide barrier.
-__device__ __forceinline__ void attn_barriers_init(AttnShared& sh) {
+__device__ __forceinline__ void attn_barriers_init(AttnShared& sh, int softmax_threads = 128) {
   mbar_init(&sh.q_full, 1);
   for (int i = 0; i < 2; ++i) {
     mbar_init(&sh.k_full[i], 1);
@@ -105,7 +108,7 @@ __device__ __forceinline__ void attn_barriers_init(AttnShared& sh) {
     mbar_init(&sh.k_empty[i], 1);
     mbar_init(&sh.v_empty[i], 1);
     mbar_init(&sh.s_full[i], 1);
-    mbar_init(&sh.p_full[i], 128);
+    mbar_init(&sh.p_full[i], softmax_threads);
     mbar_init(&sh.o_full[i], 1);   // P V of tile j completes phase j / 2 of o_full[j % 2]
   }
   fence_barrier_init();
@@ -305,13 +308,20 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
 }
 
 __device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void named_barrier_64(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
-// The softmax / output role of the four warps 2..5.  NC = key columns of a tile one
-// thread handles: 128 (a thread owns one of 128 query rows) or 32 (quad-replicated item:
-// the thread's row is lane, its columns are quarter `quad` of the tile).
-template <int NC, int PB>
-__device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c) {
-  constexpr bool kRep = NC == 32;
+// The softmax / output role.  WG = softmax warp groups of four warps (1 inside the fabric
+// worker, 2 in the stand-alone kernel); `wg` is the caller's group.  A thread's row is its TMEM
+// lane.  kRep (quad-replicated item, at most 32 rows): the thread's row is `lane`, its columns
+// are quarter `quad` of the tile, and only group 0 works.  Otherwise the thread owns one of 128
+// query rows and, with two groups, half of the tile's key columns and half of the row's output:
+// the two threads of a row agree on the row maximum through shared memory (`c.xbuf`) and a
+// 64-thread barrier per lane quadrant, which both warps of the pair pass exactly once per
+// tile whatever else happens, so that neither can be left waiting.
+template <bool kRep, int PB, int WG>
+__device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c, int wg) {
+  constexpr int NC = kRep ? 32 : kKeysPerTile / WG;   // key columns of a tile this thread handles
+  constexpr int ND = kRep ? kHeadDim : kHeadDim / WG; // output columns of its row it rescales and stores
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
   const AttnItem& item = p.item;
@@ -324,17 +334,19 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   const int r = quad * 32 + lane;                 // TMEM lane = row of S, P and O
   const int lr = kRep ? lane : r;                 // row of the item
   const bool row_ok = lr < c.rows;
-  const bool warp_active = kRep || quad * 32 < c.rows;
+  const bool works = kRep ? wg == 0 : quad * 32 < c.rows;   // warp-uniform: false = keep the barrier protocol only
+  const bool pair = !kRep && WG == 2 && works;              // exchanges with the partner warp of its quadrant
   const int group = p.group;
   const int token = lr / group, head = item.kv_head * group + lr % group;
   const int qpos = item.pos0 + token;
-  const int c_lo = kRep ? quad * 32 : 0;
+  const int c_lo = kRep ? quad * 32 : wg * NC;
+  const int d_lo = kRep ? 0 : wg * ND;
   const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-  const uint32_t tmem_o = c.tmem_base + 256 + lane_off;
+  const uint32_t tmem_o = c.tmem_base + 256 + lane_off + d_lo;
   const int n_tiles = c.n_tiles;
   float m = -1e30f, l = 0.f;
   bool ok = true;
-  const bool tr = p.trace != nullptr && quad == 2 && lane == 0;
+  const bool tr = p.trace != nullptr && quad == 2 && wg == 0 && lane == 0;
   long long tc[5] = {0, 0, 0, 0, 0}, t_prev = clock64();
   const unsigned long long t_begin = globaltimer_ns();
   auto lap = [&](int i) {
@@ -344,8 +356,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
       t_prev = now;
     }
   };
-  if (kRep) {
-    // columns outside this thread's quarter stay zero in both P buffers
+  if (kRep && works) {
+    // columns outside this thread's quarter stay zero in the P buffers
     for (int b = 0; b < PB; ++b)
       for (int h = 0; h < 2; ++h) {
         uint4* row = reinterpret_cast<uint4*>(sP + b * kTileBytes + h * kHalfBytes + r * 128);
@@ -353,43 +365,68 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
         for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
       }
   }
-  for (int j = 0; ok && j < n_tiles; ++j) {
+  for (int j = 0; j < n_tiles; ++j) {
     const int s = j & 1;
-    if (lane == 0) attn_note(c, j, kAttnSiteSmaxS);
-    if (!warp_wait(&sh.s_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxS); break; }
-    tc_fence_after_sync();
+    if (ok) {
+      if (lane == 0) attn_note(c, j, kAttnSiteSmaxS);
+      if (!warp_wait(&sh.s_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) ok = attn_gave_up(sh, kAttnSiteSmaxS);
+      tc_fence_after_sync();
+    }
     lap(0);
-    if (!warp_active) {   // no row of this warp exists: keep the barrier protocol only
-      mbar_arrive(&sh.p_full[s]);
+    if (!works) {   // no row of this warp exists, or the other group does the item: keep the barrier protocol only
+      if (ok) mbar_arrive(&sh.p_full[s]);
       continue;
     }
     const uint32_t tmem_s = c.tmem_base + s * 128 + lane_off + c_lo;
     const int key0 = item.key_begin + j * kKeysPerTile + c_lo;
     // keys this thread may use among its NC columns: [0, lim)
     const int lim = row_ok ? min(min(c.kv_end, qpos + 1) - key0, NC) : 0;
+    if (!ok) {   // after a wait gave up: only what the partner warp may still be waiting for
+      if (pair) {
+        named_barrier_64(2 + quad);
+        named_barrier_64(2 + quad);
+      }
+      continue;
+    }
     uint32_t v[NC];
     __syncwarp();
 #pragma unroll
     for (int c0 = 0; c0 < NC; c0 += 32) tmem_ld_32x32(tmem_s + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
     tmem_ld_wait();
-    float mx = m;
+    // the scale is positive: the maximum of the scaled scores is the scaled maximum
+    float mx = -1e30f;
     if (lim >= NC) {
 #pragma unroll
-      for (int i = 0; i < NC; ++i) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+      for (int i = 0; i < NC; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
     } else {
 #pragma unroll
       for (int i = 0; i < NC; ++i)
-        if (i < lim) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+        if (i < lim) mx = fmaxf(mx, __uint_as_float(v[i]));
     }
+    mx = mx > -1e30f ? mx * p.scale_log2 : -1e30f;
+    if (pair) {   // the row maximum over both halves of the tile
+      c.xbuf[wg * 128 + r] = mx;
+      named_barrier_64(2 + quad);
+      mx = fmaxf(mx, c.xbuf[(wg ^ 1) * 128 + r]);
+      named_barrier_64(2 + quad);
+    }
+    mx = fmaxf(mx, m);
     lap(1);
-    // a row whose maximum grew rescales its part of O in TMEM, once the previous P V has landed
+    // The reference point of a row's exponentials moves only when the row's maximum has grown past
+    // it by more than kMaxSlack (in the exp2 domain): P then stays below 2^kMaxSlack, exact in fp32
+    // sums and within bf16's range, the result is the same quotient, and the rescale of the row's
+    // part of O in TMEM (which waits for the previous P V) becomes rare instead of per tile.
+    if (j > 0 && mx <= m + kMaxSlack) mx = m;
     if (j > 0 && __any_sync(0xffffffffu, mx > m)) {
       if (lane == 0) attn_note(c, j, kAttnSiteSmaxRescale);
-      if (!warp_wait(&sh.o_full[s ^ 1], attn_parity(c, j - 1), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxRescale); break; }
+      if (!warp_wait(&sh.o_full[s ^ 1], attn_parity(c, j - 1), abort_flag, kAttnWaitNs)) {
+        ok = attn_gave_up(sh, kAttnSiteSmaxRescale);
+        continue;
+      }
       tc_fence_after_sync();
       const float alpha = fast_exp2(m - mx);
 #pragma unroll
-      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+      for (int c0 = 0; c0 < ND; c0 += 32) {
         uint32_t o[32];
         __syncwarp();
         tmem_ld_32x32(tmem_o + c0, o);
@@ -405,7 +442,10 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     lap(3);
     // the P buffer is free once P V of tile j - PB has completed
     if (lane == 0) attn_note(c, j, kAttnSiteSmaxPFree);
-    if (j >= PB && !warp_wait(&sh.o_full[(j - PB) & 1], attn_parity(c, j - PB), abort_flag, kAttnWaitNs)) { ok = attn_gave_up(sh, kAttnSiteSmaxPFree); break; }
+    if (j >= PB && !warp_wait(&sh.o_full[(j - PB) & 1], attn_parity(c, j - PB), abort_flag, kAttnWaitNs)) {
+      ok = attn_gave_up(sh, kAttnSiteSmaxPFree);
+      continue;
+    }
     const float neg_mx = -mx;
     // P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
     float sum0 = 0.f, sum1 = 0.f;
@@ -465,33 +505,40 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   }
   const bool split = item.ws_row0 >= 0;
   if (!kRep) {
+    if (pair) {   // the row sum over both halves, added in the order (group 0) + (group 1)
+      c.xbuf[wg * 128 + r] = l;
+      named_barrier_64(2 + quad);
+      const float other = c.xbuf[(wg ^ 1) * 128 + r];
+      l = wg == 0 ? l + other : other + l;
+    }
     // The TMEM loads are warp-wide (.sync.aligned): they sit in code every lane of the warp
     // runs, apart from anything that depends on the lane's row, and a warp barrier separates
     // them from the per-row stores so that the two cannot be merged into one divergent region.
-    if (ok && warp_active) {
-      uint32_t o[kHeadDim];
+    if (ok && works) {
+      uint32_t o[ND];
       if (n_tiles > 0) {
 #pragma unroll
-        for (int c0 = 0; c0 < kHeadDim; c0 += 32) tmem_ld_32x32(tmem_o + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
+        for (int c0 = 0; c0 < ND; c0 += 32) tmem_ld_32x32(tmem_o + c0, *reinterpret_cast<uint32_t(*)[32]>(&o[c0]));
         tmem_ld_wait();
       } else {
 #pragma unroll
-        for (int i = 0; i < kHeadDim; ++i) o[i] = 0;
+        for (int i = 0; i < ND; ++i) o[i] = 0;
       }
       __syncwarp();
       if (row_ok) {
         if (split) {
-          float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim);
-          p.ws_ml[item.ws_row0 + lr] = make_float2(m, l);
+          float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + lr) * kHeadDim + d_lo);
+          if (wg == 0) p.ws_ml[item.ws_row0 + lr] = make_float2(m, l);
 #pragma unroll
-          for (int i = 0; i < kHeadDim / 4; ++i)
+          for (int i = 0; i < ND / 4; ++i)
             wdst[i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
                                   __uint_as_float(o[4 * i + 3]));
         } else {
           const float inv = l > 0.f ? 1.f / l : 0.f;
-          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim);
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim +
+                                                d_lo);
 #pragma unroll
-          for (int q = 0; q < kHeadDim / 8; ++q) {
+          for (int q = 0; q < ND / 8; ++q) {
             __nv_bfloat162 h[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -504,8 +551,9 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     }
     return;
   }
-  // quad-replicated item: merge the four column quarters.  Every thread takes part in
-  // both barriers, also after a timeout, so that none of them can be left waiting.
+  if (!works) return;   // the other softmax group merges the quad-replicated item
+  // quad-replicated item: merge the four column quarters.  Every thread of the group takes part
+  // in both barriers, also after a timeout, so that none of them can be left waiting.
   ml[quad][lane] = make_float2(m, l);
   named_barrier_128(1);
   float M = -1e30f;
@@ -571,8 +619,6 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     }
   }
 }
-
-
 
 // Merge of the parts of one split (request, block, KV head): one warp per output row
 // (token, q head of the group), parts added in part order.  `warp` of `n_warps` warps.

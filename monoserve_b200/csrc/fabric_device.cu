@@ -1265,6 +1265,7 @@ __device__ __forceinline__ AttnCtx attn_ctx(const AttnWork& w, AttnShared& sh, v
                                             volatile unsigned int* note) {
   AttnCtx c;
   c.note = note;
+  c.xbuf = nullptr;
   c.q_phase = q_phase;
   c.base[0] = base[0];
   c.base[1] = base[1];
@@ -1485,8 +1486,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
       if (w.is_attn) {
         AttnCtx c = attn_ctx(w.attn, sh.attn, abort_flag, ring, tmem_base, aq, ab, warp == 1 ? &sh.wait_note[2] : nullptr);
         if (tid == 0) sh.wait_ctx[2] = role_ctx(n, aq, ab);
-        if (c.rep) softmax_role<32, 1>(w.attn, c);
-        else softmax_role<128, 1>(w.attn, c);
+        if (c.rep) softmax_role<true, 1, 1>(w.attn, c, 0);
+        else softmax_role<false, 1, 1>(w.attn, c, 0);
         attn_advance(c.n_tiles, aq, ab);
       } else if (w.is_gemm) {
         // The exec warps follow the operand ring like the producer and the MMA warp do: for e4m3
