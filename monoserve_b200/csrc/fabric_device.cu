@@ -898,13 +898,16 @@ __device__ void tile_permute(const TileDesc& t, int tid) {
 
 // Combine tile (kind 47; not in the reference, which adds with fp32 atomics in the
 // w2 epilogue and finishes in AddNorm): x[t] = bf16(x2[t] + sum_k w[t][k] * y[pos(t,k)])
-// with the sum in pick order, then optionally out = rmsnorm(x) * w.
+// with the sum in pick order (plus, when `shared` is set, the fp32 row shared[t] of a shared
+// expert: the GLM-style layer, tests/test_fabric_model_glm.py:57-67), then optionally
+// out = rmsnorm(x) * w.
 __device__ void tile_combine(const TileDesc& t, int tid) {
   CombineArgs A;   // a copy in registers: the block lives in global memory
   load_block(A, t.a[0]);
   const int warp = tid >> 5, lane = tid & 31;
   const int K = static_cast<int>(A.K), H = static_cast<int>(A.H), n16 = H / 8;
   const float* y = reinterpret_cast<const float*>(A.y);
+  const float* shared = reinterpret_cast<const float*>(A.shared);
   // Without a following norm nothing ties a row to one warp: the four warps then share every
   // row, each taking a quarter of its 8-element column groups (the sums per element are the same).
   const bool split = A.w == 0;
@@ -931,6 +934,13 @@ __device__ void tile_combine(const TileDesc& t, int tid) {
         const float yv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = __fmaf_rn(wk, yv[j], acc[j]);
+      }
+      if (shared) {   // a shared expert's fp32 output row, added after the routed experts
+        const float4* sr = reinterpret_cast<const float4*>(shared + static_cast<size_t>(r) * H) + 2 * c;
+        const float4 a = __ldcs(sr), b = __ldcs(sr + 1);
+        const float sv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], sv[j]);
       }
       float f[8];
       if (x2) {

@@ -61,7 +61,8 @@ namespace mf {
 #define MF_LOGITS_ARGS(U64, U32, F32) U64(x) U64(wr) U64(logits) U32(T) U32(H) U32(E)
 
 #define MF_COMBINE_ARGS(U64, U32, F32) \
-  U64(y) U64(pair_pos) U64(topk_w) U64(x2) U64(x) U64(w) U64(out) U32(K) U32(H) F32(eps)
+  U64(y) U64(pair_pos) U64(topk_w) U64(x2) U64(x) U64(w) U64(out) U32(K) U32(H) F32(eps) U32(reserved0) \
+  U64(shared)
 
 #define MF_FIELD_U64(name) unsigned long long name;
 #define MF_FIELD_U32(name) uint32_t name;

@@ -53,7 +53,11 @@ class MoELane:
     lane.set_input(xn, x2); h = lane.build(T, iterations=1); fab.publish(..., programs=[h]) ..."""
 
     def __init__(self, fab, lane_id, hidden, intermediate, experts, top_k, max_tokens, wr, w13, w2, hot,
-                 pack_hot=True):
+                 pack_hot=True, scales=None, scoring=0, bias=None, routed_scale=1.0, shared=None):
+        """w13 / w2: bf16, or e4m3 bytes (uint8) with scales = (fp32 [E][2I], fp32 [E][H]) per output
+        channel.  scoring 1 = sigmoid with the optional fp32 [E] selection bias; routed_scale multiplies
+        the renormalised weights.  shared = (w13 bf16 [2 Is][H], w2 bf16 [H][Is]): a shared expert every
+        token passes through, added to the routed sum (tests/test_fabric_model_glm.py:29-31,57-67)."""
         self.fab, self.lane_id = fab, lane_id
         self.H, self.I, self.E, self.K, self.T = hidden, intermediate, experts, top_k, max_tokens
         H, I, E, K, T = hidden, intermediate, experts, top_k, max_tokens
@@ -65,10 +69,13 @@ class MoELane:
         self.host_w2 = w2 if w2.is_pinned() else w2.contiguous().pin_memory()
         self.hot = list(hot)
         idx = torch.tensor(self.hot if self.hot else [0])
+        self.fp8 = self.host_w13.dtype == torch.uint8
+        assert self.fp8 == (scales is not None), "e4m3 weights come with per-output-channel scales"
         hot13 = self.host_w13[idx].cuda()
         if pack_hot:
             packed = torch.empty_like(hot13)
-            _C.check(_C.lib.monofab_pack_w13(hot13.data_ptr(), packed.data_ptr(), hot13.shape[0], I, H, 2, None))
+            _C.check(_C.lib.monofab_pack_w13(hot13.data_ptr(), packed.data_ptr(), hot13.shape[0], I, H,
+                                             hot13.element_size(), None))
             torch.cuda.synchronize()
             hot13 = packed
         self.hot_w13, self.hot_w2 = hot13, self.host_w2[idx].cuda()
@@ -81,6 +88,8 @@ class MoELane:
 
         def wmap(t, base, packed=False):
             z, rows, k = t.shape
+            if t.dtype == torch.uint8:   # e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
+                return fab.tensor_map(base, [k, rows, z], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0, packed=packed)
             return fab.tensor_map(base, [k, rows, z], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
 
         self.w13_maps = _u64([wmap(self.host_w13, _C.host_device_pointer(self.host_w13.data_ptr())),
@@ -102,15 +111,26 @@ class MoELane:
         self.expand_stamps = torch.zeros(8, dtype=torch.int64, device=dev)   # phase time stamps of the expand tile
         # operand blocks
         self.logits_args = None
+        self.bias = bias.float().cuda() if bias is not None else None
         self.router_args = _block("RouterArgs", logits=self.logits, topk_ids=self.topk_ids, topk_w=self.topk_w,
-                                  counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
-                                  chunk_counts=self.chunk_counts)
+                                  counts=self.counts, bias=self.bias if self.bias is not None else 0, E=E, K=K,
+                                  scoring=scoring, renorm=1, scale=routed_scale, chunk_counts=self.chunk_counts)
+        self.scales = (scales[0].float().contiguous().cuda(), scales[1].float().contiguous().cuda()) if scales else None
+        # shared expert: two dense GEMMs over all tokens, fp32 rows that the combine tile adds
+        self.shared = None
+        if shared is not None:
+            sw13, sw2 = shared[0].to(torch.bfloat16).contiguous().cuda(), shared[1].to(torch.bfloat16).contiguous().cuda()
+            Is = sw2.shape[1]
+            self.shared = dict(w13=sw13, w2=sw2, Is=Is, h=z(T + 256, Is, dt=torch.bfloat16),
+                               y=z(T, H, dt=torch.float32),
+                               m13=fab.tensor_map(sw13.data_ptr(), [H, 2 * Is, 1], [H * 2, 2 * Is * H * 2], [64, 64, 1]),
+                               m2=fab.tensor_map(sw2.data_ptr(), [Is, H, 1], [Is * 2, H * Is * 2], [64, 64, 1]))
         self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
                                    fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
                                    src=self.xn, dst=self.xp, K=K, H=H, chunk_prefix=self.chunk_prefix,
                                    pair_pos=self.pair_pos, E=E)
         self.combine_args = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2,
-                                   x=self.x, K=K, H=H, eps=0.0)
+                                   x=self.x, K=K, H=H, eps=0.0, shared=self.shared["y"] if self.shared else 0)
         heights = [16, 32, 64, 128, 256]
         self.xp_maps = _u64([fab.tensor_map(self.xp.data_ptr(), [H, P + 256], [H * 2], [64, bm]) for bm in heights])
         self.h_maps = _u64([fab.tensor_map(self.h.data_ptr(), [I, P + 256], [I * 2], [64, bm]) for bm in heights])
@@ -118,10 +138,10 @@ class MoELane:
         a13, a2 = [], []
         for bm in heights:
             b13 = torch.frombuffer(bytearray(_C.gemm_args(out=self.h.data_ptr(), ld_out=I, k_tiles=H // 64,
-                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I)),
-                                   dtype=torch.uint8).cuda()
+                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I,
+                                                          w_fp8=int(self.fp8))), dtype=torch.uint8).cuda()
             b2 = torch.frombuffer(bytearray(_C.gemm_args(out=self.y.data_ptr(), ld_out=H, k_tiles=I // 64,
-                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H)),
+                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H, w_fp8=int(self.fp8))),
                                   dtype=torch.uint8).cuda()
             self._gemm_blocks += [b13, b2]
             a13.append(b13.data_ptr())
@@ -162,6 +182,26 @@ class MoELane:
         per_cb = max(2, -(-T // (2 * nw)))
         s_cb = p.stage(_row_tiles(K_COMBINE, self.combine_args, T, per_cb), mark=(mark_layer << 8) | 3,
                        label=("combine", mark_layer))
+        if self.shared:   # runs beside the routed chain, joins at the combine stage
+            sh = self.shared
+            bm = next(h for h in (16, 32, 64, 128, 256) if T <= h or h == 256)
+            xm = self.fab.tensor_map(self.xn.data_ptr(), [H, self.T], [H * 2], [64, bm])
+            hm = self.fab.tensor_map(sh["h"].data_ptr(), [sh["Is"], self.T + 256], [sh["Is"] * 2], [64, bm])
+            g13 = torch.frombuffer(bytearray(_C.gemm_args(out=sh["h"].data_ptr(), ld_out=sh["Is"], k_tiles=H // 64,
+                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=sh["Is"], up_offset=sh["Is"])),
+                                   dtype=torch.uint8).cuda()
+            g2 = torch.frombuffer(bytearray(_C.gemm_args(out=sh["y"].data_ptr(), ld_out=H, k_tiles=sh["Is"] // 64, epi=3,
+                                                         bm=bm, n_limit=H)), dtype=torch.uint8).cuda()
+            self._keep += [g13, g2]
+            t13 = [Tile(K_GEMM, i=(f0, m0, min(bm, T - m0), 0), a=(g13.data_ptr(), sh["m13"], xm))
+                   for m0 in range(0, T, bm) for f0 in range(0, sh["Is"], 64)]
+            t2 = [Tile(K_GEMM, i=(n0, m0, min(bm, T - m0), 0), a=(g2.data_ptr(), sh["m2"], hm))
+                  for m0 in range(0, T, bm) for n0 in range(0, H, 128)]
+            s_s13 = p.stage(t13, label=("shared_w13", mark_layer))
+            s_s2 = p.stage(t2, label=("shared_w2", mark_layer))
+            p.after(s_lg, s_s13)
+            p.after(s_s13, s_s2)
+            p.after(s_s2, s_cb)
         for e in range(E):
             p.after(s_pm, w13[e])
             p.after(w13[e], w2[e])
@@ -174,7 +214,8 @@ class MoELane:
                     host_region=REGION_HOST, w13_stage0=w13[0], w2_stage0=w2[0], red_stage0=0xffffffff,
                     dyn_first=p.dynamic_first, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb,
                     chunks=-(-T // CHUNK), chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix,
-                    red_args=self.expand_stamps)
+                    red_args=self.expand_stamps, w13_scale=self.scales[0] if self.scales else 0,
+                    w2_scale=self.scales[1] if self.scales else 0)
         ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
         torch.cuda.synchronize()
         self._keep += [logits_args, ex]

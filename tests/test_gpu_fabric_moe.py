@@ -117,3 +117,51 @@ def test_prefill_and_decode_lanes_side_by_side():
     finally:
         fab.stop()
         fab.close()
+
+
+@pytest.mark.parametrize("pack_hot", [True, False])
+def test_glm_style_layer_program(pack_hot):
+    """The GLM-style layer of the reference's tests/test_fabric_model_glm.py:57-67 as a fabric program:
+    sigmoid scoring with a selection bias and a routed scale, FP8-e4m3 experts with per-output-channel
+    scales (half of them hot, half read over the link), and a shared expert that every token passes
+    through; against the torch oracle on the de-quantised weights, FP8 tolerance rel-L2 <= 3e-2."""
+    from monoserve_b200.fabric import Fabric
+    from monoserve_b200.lane import MoELane
+    from oracle import torch_path as tp
+    T, H, I, E, K, Is = 90, 512, 256, 16, 4, 384
+    g = torch.Generator().manual_seed(31)
+    wr = (torch.randn(E, H, generator=g) * H ** -0.5).to(torch.bfloat16)
+    bias = torch.randn(E, generator=g) * 0.2
+    q13, s13, d13 = tp.quantize_fp8(torch.randn(E, 2 * I, H, generator=g) * 0.05)
+    q2, s2, d2 = tp.quantize_fp8(torch.randn(E, H, I, generator=g) * 0.05)
+    sw13 = (torch.randn(2 * Is, H, generator=g) * 0.05).to(torch.bfloat16)
+    sw2 = (torch.randn(H, Is, generator=g) * 0.05).to(torch.bfloat16)
+    xn, x2 = acts(T, H, 32)
+    fab = Fabric(pool_bytes=128 << 20)
+    fab.set_max_run(60)
+    try:
+        lane = MoELane(fab, 0, H, I, E, K, 96, wr, q13, q2, hot=list(range(1, E, 2)), pack_hot=pack_hot,
+                       scales=(s13, s2), scoring=1, bias=bias, routed_scale=2.5, shared=(sw13, sw2))
+        lane.set_input(xn.cuda(), x2.cuda())
+        h = lane.build(T, iterations=2)
+        fab.start()
+        fab.publish(map=[0] * fab.num_workers, caps=[4], order=[0], programs=[h], forms=[64])
+        wait_iterations(fab, 0, 2)
+        fab.stop()
+        assert fab.progress()["error"] == 0
+        ids, w = lane.topk_ids[:T].cpu().long(), lane.topk_w[:T].cpu()
+        tw_ref, ti_ref = tp.route(xn.float(), wr, K, scoring="sigmoid", bias=bias, renorm=True, routed_scale=2.5)
+        agree = (ids.sort(-1).values == ti_ref.sort(-1).values).all(-1).float().mean().item()
+        assert agree > 0.97, agree            # the projection's summation order differs from torch's in the last bit
+        ref, _, _ = tp.moe_layer(xn.float(), x2.float(), wr, d13, d2, K, routing=(w, ids),
+                                 shared=(sw13.float(), sw2.float()))
+        got = lane.x[:T].float().cpu()
+        rel = float((got - ref).norm() / ref.norm())
+        assert rel < 3e-2, rel
+        # the shared expert alone, bf16 weights: tight
+        sh = tp.ffn(xn.float(), sw13.float(), sw2.float())
+        rel_s = float((lane.shared["y"][:T].cpu() - sh).norm() / sh.norm())
+        assert rel_s < 1e-2, rel_s
+    finally:
+        fab.stop()
+        fab.close()
