@@ -59,57 +59,90 @@ def rope_table(theta, rot_dim, max_pos):
     return torch.stack([ang.cos(), ang.sin()], -1).contiguous()
 
 
+class Mat:
+    """A weight matrix on the device: bf16, or e4m3 bytes with an fp32 scale per output row."""
+
+    def __init__(self, data, scale=None):
+        self.data, self.scale = data, scale
+        self.fp8 = data.dtype == torch.uint8
+
+
 class ModelWeights:
     """Weights of the decoder on the device, expert stacks placed as the reference places them
     (monoserve/runtime/weights.py:100-158): the full expert set of every layer in pinned host
     memory (region 0, slot = expert id), the layer's hot experts copied to HBM (region 1,
     w13 in the packed SwiGLU row order), and a per-layer (region, slot) table.
 
-    w: an object with CPU bf16 tensors embed [V,H], lm_head [V,H], final_norm [H] and per-layer
-    lists in_norm, qkv, q_norm, k_norm, o, post_norm, router, host_w13 [E,2I,H], host_w2 [E,H,I].
+    w: an object with CPU (or CUDA) tensors embed [V,H], lm_head [V,H], final_norm [H] and per-layer lists
+    in_norm, qkv, o, post_norm, and for MoE layers router, host_w13 [E,2I,H], host_w2 [E,H,I].  A matrix is
+    a bf16 tensor, or a pair (e4m3 bytes as uint8, fp32 scale per output row); expert stacks in e4m3 come
+    with lists w13_scale [E,2I] / w2_scale [E,H].  Optional members, by model family: q_norm / k_norm
+    (per-head norms), qkv_bias, router_bias (fp32 [E], selection only), shared_w13 / shared_w2 (a shared
+    expert), mlp_w13 / mlp_w2 (the dense FFN of the first cfg.dense_layers layers).
     hot: per layer, the expert ids kept in HBM (default: all)."""
 
     def __init__(self, cfg, w, hot=None):
         self.cfg = cfg
         L, E, I, H = cfg.num_layers, cfg.num_experts, cfg.intermediate, cfg.hidden
+        self.dense_layers = getattr(cfg, "dense_layers", 0)
         # A tensor object that appears for several layers (a benchmark that cycles a few distinct
         # layers' weights) is placed once.
         dev_cache, pin_cache, hot_cache = {}, {}, {}
 
         def d(t):
             if id(t) not in dev_cache:
-                dev_cache[id(t)] = t.to(torch.bfloat16).contiguous().cuda()
+                dev_cache[id(t)] = t.contiguous().cuda() if t.dtype in (torch.uint8, torch.float32) else \
+                    t.to(torch.bfloat16).contiguous().cuda()
             return dev_cache[id(t)]
+
+        def mat(v):
+            return Mat(d(v[0]), d(v[1].float())) if isinstance(v, (tuple, list)) else Mat(d(v))
 
         def pin(t):
             if id(t) not in pin_cache:
                 pin_cache[id(t)] = t if t.is_pinned() else t.contiguous().pin_memory()
             return pin_cache[id(t)]
 
+        def per_layer(name, f, layers=range(L)):
+            src = getattr(w, name, None)
+            return [f(src[l]) if src is not None and l in layers and src[l] is not None else None for l in range(L)]
+
+        moe_layers = range(self.dense_layers, L)
         self.embed, self.lm_head, self.final_norm = d(w.embed), d(w.lm_head), d(w.final_norm)
-        for name in ("in_norm", "qkv", "q_norm", "k_norm", "o", "post_norm", "router"):
-            setattr(self, name, [d(t) for t in getattr(w, name)])
-        self.host_w13 = [pin(t) for t in w.host_w13]
-        self.host_w2 = [pin(t) for t in w.host_w2]
+        for name in ("in_norm", "post_norm", "q_norm", "k_norm", "qkv_bias"):
+            setattr(self, name, per_layer(name, d))
+        for name in ("qkv", "o"):
+            setattr(self, name, per_layer(name, mat))
+        for name in ("mlp_w13", "mlp_w2"):
+            setattr(self, name, per_layer(name, mat, range(self.dense_layers)))
+        for name in ("shared_w13", "shared_w2"):
+            setattr(self, name, per_layer(name, mat, moe_layers))
+        self.router = per_layer("router", d, moe_layers)
+        self.router_bias = per_layer("router_bias", lambda t: d(t.float()), moe_layers)
+        self.w13_scale = per_layer("w13_scale", lambda t: d(t.float()), moe_layers)
+        self.w2_scale = per_layer("w2_scale", lambda t: d(t.float()), moe_layers)
+        self.host_w13 = per_layer("host_w13", pin, moe_layers)
+        self.host_w2 = per_layer("host_w2", pin, moe_layers)
+        self.fp8_experts = any(t is not None and t.dtype == torch.uint8 for t in self.host_w13)
         self.hot = [list(h) for h in hot] if hot is not None else [list(range(E)) for _ in range(L)]
-        self.hot_w13, self.hot_w2, self.table = [], [], []
-        for l in range(L):
+        self.hot_w13, self.hot_w2, self.table = [None] * L, [None] * L, [None] * L
+        for l in moe_layers:
             idx = torch.tensor(self.hot[l] if self.hot[l] else [0])
             key = (id(w.host_w13[l]), id(w.host_w2[l]), tuple(self.hot[l]))
             if key not in hot_cache:
                 h13 = self.host_w13[l][idx].cuda()
                 packed = torch.empty_like(h13)
-                _C.check(_C.lib.monofab_pack_w13(h13.data_ptr(), packed.data_ptr(), h13.shape[0], I, H, 2, None))
+                _C.check(_C.lib.monofab_pack_w13(h13.data_ptr(), packed.data_ptr(), h13.shape[0], I, H,
+                                                 h13.element_size(), None))
                 torch.cuda.synchronize()
                 hot_cache[key] = (packed, self.host_w2[l][idx].cuda())
-            self.hot_w13.append(hot_cache[key][0])
-            self.hot_w2.append(hot_cache[key][1])
+            self.hot_w13[l], self.hot_w2[l] = hot_cache[key]
             table = torch.zeros(E, 2, dtype=torch.int32)
             table[:, 1] = torch.arange(E)
             if self.hot[l]:
                 table[idx, 0] = REGION_HOT
                 table[idx, 1] = torch.arange(len(self.hot[l]), dtype=torch.int32)
-            self.table.append(table.cuda())
+            self.table[l] = table.cuda()
 
 
 class KVCache:
@@ -158,6 +191,11 @@ class ModelLane:
         self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
         self.xp, self.h = z(P + 256, H, dt=bf), z(P + 256, I, dt=bf)
         self.y = z(P + 256, H, dt=torch.float32)
+        # dense FFN of the first layers / shared expert: hidden rows and fp32 output rows
+        self.Id, self.Is = getattr(cfg, "dense_intermediate", 0), getattr(cfg, "shared_intermediate", 0)
+        wide = max(self.Id, self.Is)
+        self.hd = z(T + 256, wide, dt=bf) if wide else None
+        self.y_shared = z(T, H, dt=torch.float32) if self.Is else None
         # token and request state
         self.tokens, self.tok_pos, self.tok_slot, self.gather = z(T), z(T), z(T), z(T)
         self.req_info = z(max(T, S), 4)
@@ -179,12 +217,16 @@ class ModelLane:
 
     # ------------------------------------------------------------------ maps and operand blocks
     def _wmap(self, t, base=None, packed=False):
+        if isinstance(t, Mat):
+            t = t.data
         if t.dim() == 2:
             rows, k, zdim = t.shape[0], t.shape[1], 1
         else:
             zdim, rows, k = t.shape
-        return self.fab.tensor_map(base if base is not None else t.data_ptr(), [k, rows, zdim], [k * 2, rows * k * 2],
-                                   [64, 64, 1], packed=packed)
+        base = base if base is not None else t.data_ptr()
+        if t.dtype == torch.uint8:   # e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
+            return self.fab.tensor_map(base, [k, rows, zdim], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0, packed=packed)
+        return self.fab.tensor_map(base, [k, rows, zdim], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
 
     def _amaps(self, t, rows, k):
         """Activation maps of a [rows][k] bf16 buffer for every row-block height."""
@@ -201,19 +243,28 @@ class ModelLane:
         self.m_qkv = [self._wmap(w.qkv[l]) for l in range(L)]
         self.m_o = [self._wmap(w.o[l]) for l in range(L)]
         self.m_lm = self._wmap(w.lm_head)
-        self.w13_maps = [_u64([self._wmap(w.host_w13[l], _C.host_device_pointer(w.host_w13[l].data_ptr())),
-                               self._wmap(w.hot_w13[l], packed=True)]) for l in range(L)]
-        self.w2_maps = [_u64([self._wmap(w.host_w2[l], _C.host_device_pointer(w.host_w2[l].data_ptr())),
-                              self._wmap(w.hot_w2[l])]) for l in range(L)]
+        opt = lambda lst, l: self._wmap(lst[l]) if lst[l] is not None else 0  # noqa: E731
+        self.m_mlp13, self.m_mlp2 = [opt(w.mlp_w13, l) for l in range(L)], [opt(w.mlp_w2, l) for l in range(L)]
+        self.m_sh13, self.m_sh2 = [opt(w.shared_w13, l) for l in range(L)], [opt(w.shared_w2, l) for l in range(L)]
+        if self.hd is not None:
+            self.m_hd = self._amaps(self.hd, T + 256, self.hd.shape[1])
+        moe = [l for l in range(L) if w.host_w13[l] is not None]
+        self.w13_maps, self.w2_maps = [None] * L, [None] * L
+        for l in moe:
+            self.w13_maps[l] = _u64([self._wmap(w.host_w13[l], _C.host_device_pointer(w.host_w13[l].data_ptr())),
+                                     self._wmap(w.hot_w13[l], packed=True)])
+            self.w2_maps[l] = _u64([self._wmap(w.host_w2[l], _C.host_device_pointer(w.host_w2[l].data_ptr())),
+                                    self._wmap(w.hot_w2[l])])
         self.xp_maps = _u64(self._amaps(self.xp, P + 256, H))
         self.h_maps = _u64(self._amaps(self.h, P + 256, I))
         a13, a2 = [], []
         for bm in HEIGHTS:
             b13 = torch.frombuffer(bytearray(_C.gemm_args(out=self.h.data_ptr(), ld_out=I, k_tiles=H // 64,
-                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I)),
-                                   dtype=torch.uint8).cuda()
+                                                          epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I,
+                                                          w_fp8=int(w.fp8_experts))), dtype=torch.uint8).cuda()
             b2 = torch.frombuffer(bytearray(_C.gemm_args(out=self.y.data_ptr(), ld_out=H, k_tiles=I // 64,
-                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H)), dtype=torch.uint8).cuda()
+                                                         epi=EPI_ROWS_F32, bm=bm, n_limit=H, w_fp8=int(w.fp8_experts))),
+                                  dtype=torch.uint8).cuda()
             self._keep += [b13, b2]
             a13.append(b13.data_ptr())
             a2.append(b2.data_ptr())
@@ -228,9 +279,11 @@ class ModelLane:
                 ws_m=self.ws.data_ptr() + self.ws_rows * 512, block_table=self.bt, req_info=self.req_info,
                 scale_log2=SCALE_LOG2, bt_stride=self.bt_stride, hq=hq, hkv=hkv, group=group,
                 max_chunks=self.max_chunks, page_size=self.kv.page, q_map_small=q_small))
-        self.router_args = _block("RouterArgs", logits=self.rl, topk_ids=self.topk_ids, topk_w=self.topk_w,
-                                  counts=self.counts, E=E, K=K, scoring=0, renorm=1, scale=1.0,
-                                  chunk_counts=self.chunk_counts)
+        scoring = {"softmax": 0, "sigmoid": 1}[getattr(cfg, "scoring", "softmax")]
+        self.router_args = [_block("RouterArgs", logits=self.rl, topk_ids=self.topk_ids, topk_w=self.topk_w,
+                                   counts=self.counts, bias=w.router_bias[l] if w.router_bias[l] is not None else 0,
+                                   E=E, K=K, scoring=scoring, renorm=1, scale=getattr(cfg, "routed_scale", 1.0),
+                                   chunk_counts=self.chunk_counts) for l in range(L)]
         self.permute_args = _block("PermuteArgs", topk_ids=self.topk_ids, topk_w=self.topk_w, starts=self.starts,
                                    fill=self.fill, pair_token=self.pair_token, pair_weight=self.pair_weight,
                                    src=self.xn, dst=self.xp, K=K, H=H, chunk_prefix=self.chunk_prefix,
@@ -245,15 +298,22 @@ class ModelLane:
                                   V=cfg.vocab, ring=self.ring)
 
     # ------------------------------------------------------------------ stage builders
-    def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None):
+    def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None,
+              mat=None, bias=None, up_offset=0):
+        """A dense GEMM stage: out[rows][n_out] = act[rows][k] x weight[n_out (x2 for SiLU-mul)][k]^T.
+        mat: the weight's Mat (e4m3 weights carry their scales into the tiles)."""
         bm = _bm(rows)
+        fp8 = mat is not None and mat.fp8
         args = torch.frombuffer(bytearray(_C.gemm_args(
             out=out.data_ptr(), ld_out=ld_out, k_tiles=k // 64, epi=epi, bm=bm, n_limit=n_out,
-            residual=residual.data_ptr() if residual is not None else 0, ld_res=ld_res)), dtype=torch.uint8).cuda()
+            residual=residual.data_ptr() if residual is not None else 0, ld_res=ld_res,
+            bias=bias.data_ptr() if bias is not None else 0, up_offset=up_offset, w_fp8=int(fp8))), dtype=torch.uint8).cuda()
         self._keep.append(args)
         xm = amaps[HEIGHTS.index(bm)]
-        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
-        tiles = tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm)
+        step = 64 if epi == EPI_SILU_MUL else 128
+        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, step), indexing="ij")
+        tiles = tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm,
+                           a4=mat.scale.data_ptr() if fp8 else 0)
         return p.stage(tiles, mark=mark, label=label)
 
     def _rows(self, kind, args, rows, per):
@@ -266,13 +326,15 @@ class ModelLane:
         H, E = cfg.hidden, cfg.num_experts
         nw = self.fab.num_workers
         lg = _block("LogitsArgs", x=self.xn, wr=self.w.router[l], logits=self.rl, T=T, H=H, E=E)
+        shared = self.w.shared_w13[l] is not None
         cb = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2, x=self.x,
-                    w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps)
+                    w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps,
+                    shared=self.y_shared if shared else 0)
         ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
         self._keep += [lg, cb, ex]
         per = max(2, -(-T // (2 * nw)))
         s_lg = p.stage(logits_tiles(lg.data_ptr(), T, E), label=("router_logits", l))
-        s_rt = p.stage(self._rows(K_ROUTER, self.router_args, T, SUB), label=("router", l))
+        s_rt = p.stage(self._rows(K_ROUTER, self.router_args[l], T, SUB), label=("router", l))
         s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", l))
         s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, SUB), label=("permute", l))
         p.after(prev, s_lg)
@@ -286,6 +348,14 @@ class ModelLane:
             p.after(s_pm, w13[e])
             p.after(w13[e], w2[e])
             p.after(w2[e], s_cb)
+        if shared:   # the shared expert runs beside the routed chain and joins at the combine stage
+            s_s13 = self._gemm(p, self.m_sh13[l], self.m_xn, T, self.Is, H, self.hd, self.hd.shape[1], EPI_SILU_MUL,
+                               ("shared_w13", l), mat=self.w.shared_w13[l], up_offset=self.Is)
+            s_s2 = self._gemm(p, self.m_sh2[l], self.m_hd, T, H, self.Is, self.y_shared, H, EPI_F32, ("shared_w2", l),
+                              mat=self.w.shared_w2[l])
+            p.after(prev, s_s13)
+            p.after(s_s13, s_s2)
+            p.after(s_s2, s_cb)
         dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
         expands.append((ex, l, T, w13[0], 0xffffffff, w2[0], s_cb, dyn))
         return s_cb
@@ -305,7 +375,9 @@ class ModelLane:
                         w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
                         I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
                         dyn_first=at, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb, chunks=-(-T // CHUNK),
-                        chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix)
+                        chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix,
+                        w13_scale=self.w.w13_scale[l] if self.w.w13_scale[l] is not None else 0,
+                        w2_scale=self.w.w2_scale[l] if self.w.w2_scale[l] is not None else 0)
             ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
             at += dyn
         for blob, fields, dyn in plans:
@@ -325,10 +397,11 @@ class ModelLane:
         expands = []
         for l in range(L):
             s_qkv = self._gemm(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv, self.qkv_dim, EPI_STORE,
-                               ("qkv", l))
+                               ("qkv", l), mat=w.qkv[l], bias=w.qkv_bias[l])
             p.after(prev, s_qkv)
             qk = _block("QkArgs", qkv=self.qkv, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
-                        q_norm=w.q_norm[l], k_norm=w.k_norm[l], tok_pos=self.tok_pos, tok_slot=self.tok_slot,
+                        q_norm=w.q_norm[l] if w.q_norm[l] is not None else 0,
+                        k_norm=w.k_norm[l] if w.k_norm[l] is not None else 0, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
                         cos_sin=self.cos_sin, ld_qkv=self.qkv_dim, hq=hq, hkv=hkv, rot_dim=cfg.rotary_dim,
                         theta=cfg.rope_theta, eps=cfg.rms_eps, max_pos=self.max_pos)
             self._keep.append(qk)
@@ -336,7 +409,7 @@ class ModelLane:
             p.after(s_qkv, s_rope)
             s_attn = attention(p, l, s_rope)
             s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
-                             residual=self.x, ld_res=H, mark=(l << 8) | 2)
+                             residual=self.x, ld_res=H, mark=(l << 8) | 2, mat=w.o[l])
             p.after(s_attn, s_o)
             nrm = _block("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
             self._keep.append(nrm)
@@ -344,6 +417,22 @@ class ModelLane:
                              label=("norm", l))
             p.after(s_o, s_norm)
             next_norm = w.in_norm[l + 1] if l + 1 < L else None
+            if w.mlp_w13[l] is not None:
+                # a dense layer: x = bf16(x2 + ffn(xn)), then the next layer's input norm
+                s_d13 = self._gemm(p, self.m_mlp13[l], self.m_xn, T, self.Id, H, self.hd, self.hd.shape[1], EPI_SILU_MUL,
+                                   ("mlp_w13", l), mat=w.mlp_w13[l], up_offset=self.Id)
+                s_d2 = self._gemm(p, self.m_mlp2[l], self.m_hd, T, H, self.Id, self.x, H, EPI_STORE, ("mlp_w2", l),
+                                  residual=self.x2, ld_res=H, mark=(l << 8) | 3, mat=w.mlp_w2[l])
+                p.after(s_norm, s_d13)
+                p.after(s_d13, s_d2)
+                prev = s_d2
+                if next_norm is not None:
+                    nn = _block("NormArgs", x=self.x, w=next_norm, out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
+                    self._keep.append(nn)
+                    prev = p.stage(self._rows(K_RMSNORM, nn, T, max(1, -(-T // (2 * self.fab.num_workers)))),
+                                   label=("in_norm", l + 1))
+                    p.after(s_d2, prev)
+                continue
             prev = self._moe(p, l, T, s_norm, next_norm, expands)
         # final norm of the rows that continue (gather), lm_head over those rows, next tokens
         R = n_rows

@@ -124,6 +124,36 @@ def model_logits(w, cfg, tokens, device="cpu"):
     return xn @ w.lm_head.float().t()
 
 
+@torch.no_grad()
+def model_logits_glm(w, cfg, tokens, device="cpu"):
+    """Whole-model logits of the GLM-4.5-style reference oracle (tests/test_fabric_model_glm.py:34-68):
+    FP8 matrices de-quantised to fp32 (`w.dequantized(name, l)`, `w.expert_weights(l)`), qkv bias, rotary
+    embedding on cfg.rotary_dim of each head and no head norm, dense FFN in the first cfg.dense_layers
+    layers, then sigmoid routing with a selection bias, renormalised and scaled, plus a shared expert."""
+    L, Kt = cfg.num_layers, cfg.top_k
+    hq, hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    n = len(tokens)
+    pos = torch.arange(n, device=device)
+    x = w.embed[torch.tensor(tokens, device=device)].float()
+    for l in range(L):
+        xn = rms(x, w.in_norm[l], cfg.rms_eps)
+        qkv = bf(xn @ w.dequantized("qkv", l).t() + w.qkv_bias[l].float())
+        q = bf(rope(qkv[:, :hq * D].view(n, hq, D), pos, cfg.rope_theta, cfg.rotary_dim))
+        k = bf(rope(qkv[:, hq * D:(hq + hkv) * D].view(n, hkv, D), pos, cfg.rope_theta, cfg.rotary_dim))
+        v = qkv[:, (hq + hkv) * D:].view(n, hkv, D)
+        ao = attention_dense(q, k, v, hq, hkv, D)
+        x2 = bf(x + ao @ w.dequantized("o", l).t())
+        xn2 = rms(x2, w.post_norm[l], cfg.rms_eps)
+        if l < cfg.dense_layers:
+            x = bf(x2 + ffn(xn2, w.dequantized("mlp_w13", l), w.dequantized("mlp_w2", l)))
+            continue
+        w13, w2 = w.expert_weights(l)
+        x, _, _ = moe_layer(xn2, x2, w.router[l], w13, w2, Kt, scoring="sigmoid", bias=w.router_bias[l], renorm=True,
+                            routed_scale=cfg.routed_scale,
+                            shared=(w.dequantized("shared_w13", l), w.dequantized("shared_w2", l)))
+    return rms(x, w.final_norm, cfg.rms_eps) @ w.lm_head.float().t()
+
+
 def quantize_fp8(w):
     """Per-output-channel e4m3 quantisation (monoserve/runtime/weights.py:218-229,
     tests/test_fabric_gemm.py:246-251): returns (raw bytes, fp32 scale per row,

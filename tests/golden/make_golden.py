@@ -96,6 +96,85 @@ def make_weights(cfg, seed):
     return w
 
 
+def quantize_fp8(w):
+    """Per-output-channel e4m3 quantisation as the reference's weights do it
+    (monoserve/runtime/weights.py:218-229): scale = amax / 448, clamped at 1e-12."""
+    s = (w.float().abs().amax(dim=-1, keepdim=True) / 448.0).clamp_min(1e-12)
+    q = (w.float() / s).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).contiguous(), s.squeeze(-1).contiguous(), q.float() * s
+
+
+def make_glm_weights(cfg, seed):
+    """Random weights of a tiny GLM-4.5-style model, drawn in this order; every matrix quantised to e4m3 with
+    per-row scales.  Returns an object that offers both what the reference's oracle reads (`dequantized`,
+    `expert_weights`, the norm / bias / router tensors) and what this library's ModelWeights reads (pairs of
+    bytes and scales)."""
+    g = torch.Generator().manual_seed(seed)
+    H, I, E, L, V = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.num_layers, cfg.vocab
+    hq, hkv, D = cfg.num_heads, cfg.num_kv_heads, 128
+    Id, Is, nd = cfg.dense_intermediate, cfg.shared_intermediate, cfg.dense_layers
+
+    def rnd(*shape, scale=1.0):
+        return torch.randn(*shape, generator=g) * scale
+
+    w = types.SimpleNamespace()
+    w.embed = rnd(V, H).to(torch.bfloat16)
+    w.lm_head = rnd(V, H, scale=H ** -0.5).to(torch.bfloat16)
+    w.final_norm = (1 + 0.1 * rnd(H)).to(torch.bfloat16)
+    deq = {}
+    for name in ("in_norm", "post_norm", "qkv", "qkv_bias", "o", "mlp_w13", "mlp_w2", "router", "router_bias",
+                 "shared_w13", "shared_w2", "host_w13", "host_w2", "w13_scale", "w2_scale"):
+        setattr(w, name, [None] * L)
+
+    def q(name, l, t):
+        b, s, d = quantize_fp8(t)
+        deq[(name, l)] = d
+        return (b, s)
+
+    for l in range(L):
+        w.in_norm[l] = (1 + 0.1 * rnd(H)).to(torch.bfloat16)
+        w.post_norm[l] = (1 + 0.1 * rnd(H)).to(torch.bfloat16)
+        w.qkv[l] = q("qkv", l, rnd((hq + 2 * hkv) * D, H, scale=H ** -0.5))
+        w.qkv_bias[l] = (0.1 * rnd((hq + 2 * hkv) * D)).to(torch.bfloat16)
+        w.o[l] = q("o", l, rnd(H, hq * D, scale=(hq * D) ** -0.5))
+        if l < nd:
+            w.mlp_w13[l] = q("mlp_w13", l, rnd(2 * Id, H, scale=H ** -0.5))
+            w.mlp_w2[l] = q("mlp_w2", l, rnd(H, Id, scale=Id ** -0.5))
+        else:
+            w.router[l] = rnd(E, H, scale=H ** -0.5).to(torch.bfloat16)
+            w.router_bias[l] = 0.1 * rnd(E)
+            w.shared_w13[l] = q("shared_w13", l, rnd(2 * Is, H, scale=H ** -0.5))
+            w.shared_w2[l] = q("shared_w2", l, rnd(H, Is, scale=Is ** -0.5))
+            b13, s13, d13 = quantize_fp8(rnd(E, 2 * I, H, scale=H ** -0.5))
+            b2, s2, d2 = quantize_fp8(rnd(E, H, I, scale=I ** -0.5))
+            w.host_w13[l], w.w13_scale[l], w.host_w2[l], w.w2_scale[l] = b13, s13, b2, s2
+            deq[("experts", l)] = (d13, d2)
+    w.dequantized = lambda name, l: deq[(name, l)]
+    w.expert_weights = lambda l: deq[("experts", l)]
+    return w
+
+
+def glm_fixture():
+    with reference_on_cpu():
+        ref = importlib.import_module("test_fabric_model_glm")
+        cfg = ref.CFG   # 3 layers (first dense), 12 / 4 heads, rotary 64, sigmoid routing x 1.5, shared expert, FP8
+        w = make_glm_weights(cfg, seed=17)
+        g = torch.Generator().manual_seed(5)
+        tokens = torch.randint(0, cfg.vocab, (45,), generator=g).tolist()
+        logits = ref.reference_logits(w, cfg, tokens)
+    out = {"tokens": np.array(tokens, dtype=np.int32), "logits": logits.numpy().astype(np.float32),
+           "cfg": np.array([cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, cfg.num_layers, cfg.num_heads,
+                            cfg.num_kv_heads, cfg.vocab, cfg.rotary_dim, cfg.dense_layers, cfg.dense_intermediate,
+                            cfg.shared_intermediate], dtype=np.int64),
+           "rope_theta": np.float64(cfg.rope_theta), "rms_eps": np.float64(cfg.rms_eps),
+           "routed_scale": np.float64(cfg.routed_scale), "weights_seed": np.int64(17),
+           "crc_embed": np.uint32(zlib.crc32(bf16_bits(w.embed).tobytes())),
+           "crc_experts": np.uint32(zlib.crc32(w.host_w13[cfg.num_layers - 1].numpy().tobytes()))}
+    np.savez_compressed(os.path.join(HERE, "glm_tiny_reference_logits.npz"), **out)
+    print("glm fixture: logits", logits.shape, "max |logit|", float(logits.abs().max()))
+
+
+
 def qwen_fixture():
     with reference_on_cpu():
         ref = importlib.import_module("test_fabric_model")
@@ -179,5 +258,6 @@ def program_fixture():
 if __name__ == "__main__":
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     qwen_fixture()
+    glm_fixture()
     helper_fixture()
     program_fixture()

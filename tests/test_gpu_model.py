@@ -103,3 +103,50 @@ def test_decode_steps_match_reference(fab):
         got.append(lane.logits[0].cpu().clone())
         assert int(lane.seq_len[2]) == i + 1
     check_logits(torch.stack(got), ref[n0:])
+
+
+@pytest.mark.parametrize("form", [64, 0])
+def test_glm_style_model_matches_reference(fab, form):
+    """The GLM-4.5-style structure of the reference's tests/test_fabric_model_glm.py:71-124 — FP8 matrices
+    with per-row scales everywhere, a dense first layer, a shared expert beside the routed ones, sigmoid
+    routing with a selection bias and routed scale, qkv bias, rotary embedding on half of each head, GQA
+    12 / 4 — as lane programs, in both kernel forms of the host-resident experts: teacher-forced prefill
+    logits of 45 tokens, then decode steps on top of a shorter prefill, against the golden logits the
+    reference's own oracle produced on the same quantised weights."""
+    from monoserve_b200.model import KVCache, ModelLane, ModelWeights
+    from tests.test_oracle_golden import glm_fixture
+    cfg, w, tokens, ref = glm_fixture()
+    hot = [[], list(range(8)), list(range(4, 12))]          # the reference test's placement
+    weights = ModelWeights(cfg, w, hot=hot)
+    kv = KVCache(cfg, n_pages=16, page_size=16)
+    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8)
+    lane.set_pages(0, [2, 9, 4])
+    h = lane.build_prefill([(0, tokens, 0)], all_logits=True)
+    fab.start()
+    before = fab.progress()["lanes"][0]["iterations"]
+    fab.publish(map=[0] * fab.num_workers, caps=[4], order=[0], programs=[h], forms=[form])
+    t0 = time.time()
+    while fab.progress()["lanes"][0]["iterations"] < before + 1:
+        assert time.time() - t0 < 30, (fab.progress()["error"], fab.wait_notes())
+        time.sleep(1e-3)
+    fab.stop()
+    assert fab.progress()["error"] == 0
+    check_logits(lane.logits[:len(tokens)].cpu(), ref)
+    # decode: prefill 40 tokens, then the last 5 positions one step at a time
+    kv2 = KVCache(cfg, n_pages=16, page_size=16)
+    lane2 = ModelLane(fab, 0, cfg, weights, kv2, max_tokens=64, max_slots=4, bt_stride=8)
+    lane2.set_pages(1, [3, 1, 7])
+    n0 = 40
+    h = lane2.build_prefill([(1, tokens[:n0], 0)])
+    fab.start()
+    run_once(fab, h)
+    fab.stop()
+    got = []
+    for i in range(n0, len(tokens)):
+        lane2.set_request(1, seq_len=i, last_token=tokens[i])
+        h = lane2.build_decode([1])
+        fab.start()
+        run_once(fab, h)
+        fab.stop()
+        got.append(lane2.logits[0].cpu().clone())
+    check_logits(torch.stack(got), ref[n0:])
