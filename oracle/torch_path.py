@@ -125,11 +125,13 @@ def model_logits(w, cfg, tokens, device="cpu"):
 
 
 @torch.no_grad()
-def model_logits_glm(w, cfg, tokens, device="cpu"):
+def model_logits_glm(w, cfg, tokens, device="cpu", gaps=None):
     """Whole-model logits of the GLM-4.5-style reference oracle (tests/test_fabric_model_glm.py:34-68):
     FP8 matrices de-quantised to fp32 (`w.dequantized(name, l)`, `w.expert_weights(l)`), qkv bias, rotary
     embedding on cfg.rotary_dim of each head and no head norm, dense FFN in the first cfg.dense_layers
-    layers, then sigmoid routing with a selection bias, renormalised and scaled, plus a shared expert."""
+    layers, then sigmoid routing with a selection bias, renormalised and scaled, plus a shared expert.
+    gaps (a list, optional) receives per MoE layer the difference between the K-th and the K+1-th
+    selection score of every row: how close each routing decision is to a tie."""
     L, Kt = cfg.num_layers, cfg.top_k
     hq, hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
     n = len(tokens)
@@ -148,6 +150,10 @@ def model_logits_glm(w, cfg, tokens, device="cpu"):
             x = bf(x2 + ffn(xn2, w.dequantized("mlp_w13", l), w.dequantized("mlp_w2", l)))
             continue
         w13, w2 = w.expert_weights(l)
+        if gaps is not None:
+            sel = torch.sigmoid(xn2 @ w.router[l].float().t()) + w.router_bias[l].float()
+            top = sel.sort(-1, descending=True).values
+            gaps.append(top[:, Kt - 1] - top[:, Kt])
         x, _, _ = moe_layer(xn2, x2, w.router[l], w13, w2, Kt, scoring="sigmoid", bias=w.router_bias[l], renorm=True,
                             routed_scale=cfg.routed_scale,
                             shared=(w.dequantized("shared_w13", l), w.dequantized("shared_w2", l)))

