@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N = 1): BASELINE config 2 — one Qwen3-30B-A3B-shaped MoE layer in BF16
+Workload (N = 1): benchmark configuration 2 — one Qwen3-30B-A3B-shaped MoE layer in BF16
 (128 experts, top-8, hidden 2048, expert intermediate 768, SwiGLU, softmax routing
 with renormalisation), 32 experts in the HBM hot tier and 96 read in place from
 pinned host memory, a decode batch of 256 tokens per step, router logits
@@ -456,7 +456,7 @@ def side_run(module_args, timeout_s):
     """Two more measurements ride on the N = 1 line, each made by a module of
     monoserve_b200/benchmarks in a process of its own: `fabric_layer`, the same MoE layer as a
     repeating fabric program timed by the in-kernel iteration timer (the reference's protocol for
-    MoE-layer tokens/s), and `mixed_lane`, the second metric BASELINE.json names: decode TPOT p50
+    MoE-layer tokens/s), and `mixed_lane`, the second headline metric: decode TPOT p50
     on config 3 (the full 48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a
     128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory)."""
     cmd = [sys.executable, "-m"] + module_args

@@ -1,4 +1,4 @@
-"""Paged-KV attention micro-benchmark on the shapes of BASELINE config 3
+"""Paged-KV attention micro-benchmark on the shapes of benchmark configuration 3
 (Qwen3-30B-A3B: 32 query heads, 4 KV heads, head_dim 128, page size 16).
 
     python -m monoserve_b200.benchmarks.attention [--page 16] [--seqs 128] [--reps 20] [--quick]

@@ -1,4 +1,4 @@
-"""The sweep BASELINE config 2 describes: the Qwen3-30B-A3B MoE layer on one B200 with 32 experts in
+"""The sweep that benchmark configuration 2 describes: the Qwen3-30B-A3B MoE layer on one B200 with 32 experts in
 the HBM hot tier and 96 in pinned host memory, decode batches 1 / 8 / 32 / 128 / 256 with Zipf(1.1)
 + N(0,1) router logits, link credits 1..16, and both kernel forms for host-resident experts (row
 blocks of 64, and the one-pass form that the reference's asymmetric form maps to).

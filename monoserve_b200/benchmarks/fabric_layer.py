@@ -5,7 +5,7 @@ iterations = 0, >= 2 warm-up and >= 6 timed iterations).
 
     python -m monoserve_b200.benchmarks.fabric_layer [--tokens 256] [--caps 8] [--form 64] [--reps 40]
 
-Shapes and data are those of bench.py (BASELINE config 2: Qwen3-30B-A3B layer, Zipf-skewed routing,
+Shapes and data are those of bench.py (benchmark configuration 2: Qwen3-30B-A3B layer, Zipf-skewed routing,
 32 hot + 96 host-resident experts); `all_hot` repeats the measurement with every expert in HBM.
 One JSON line.
 """

@@ -1,4 +1,4 @@
-"""The routed-expert MoE layer at the shape of BASELINE config 4 (GLM-4.5-Air-shaped: hidden 4096,
+"""The routed-expert MoE layer at the shape of benchmark configuration 4 (GLM-4.5-Air-shaped: hidden 4096,
 128 routed experts of width 1408, top-8, sigmoid scoring with a selection bias and routed scale,
 FP8-e4m3 weights drawn from N(0, 0.02) and quantised per output channel with fp32 scales, 25 % of
 the experts in the HBM hot tier and all of them in pinned host memory), through the stream path

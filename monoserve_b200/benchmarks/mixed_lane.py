@@ -1,4 +1,4 @@
-"""Mixed-lane benchmark on the shapes of BASELINE config 3: a random-init Qwen3-30B-A3B-shaped
+"""Mixed-lane benchmark on the shapes of benchmark configuration 3: a random-init Qwen3-30B-A3B-shaped
 decoder (48 layers, hidden 2048, 32 / 4 heads of 128, 128 experts top-8 of width 768, vocabulary
 151936, BF16) with a prefill lane (4 prompts of 2048 tokens) and a decode lane (128 sequences,
 paged KV with page size 16, contexts uniform in [512, 8192]) running concurrently inside one
@@ -13,6 +13,13 @@ Reported (one JSON line): decode TPOT p50 = median of the decode lane's iteratio
 (the in-kernel timer, as monoserve/calibrate/calibrator.py:309-319 and Fabric.iteration_times),
 taken while the prefill lane's program repeats on its share of the SMs; the prefill lane's tokens/s;
 the SM split, link credits and kernel forms that were published.
+
+`--model glm` runs benchmark configuration 4 instead: a GLM-4.5-Air-shaped decoder (46 layers, the first one dense
+with an FFN width of 10944 — the configuration does not give it, this is the value chosen —, hidden 4096,
+96 / 8 heads of 128 with rotary on 64 dims and qkv bias, 128 routed experts of width 1408 top-8 with sigmoid
+routing plus a shared expert of width 1408), every matrix FP8-e4m3 with per-output-channel scales, 25 % of
+the experts hot, a prefill lane of 2 x 4096 tokens beside 64 decode sequences with contexts uniform in
+[1024, 16384].  Its expert stacks are 2.2 GB per layer, so `--distinct` defaults to 8 there.
 
 Synthetic, seeded data stand in for everything.  The default holds 48 distinct layers' weights: 58 GB
 of pinned host memory, 29 GB of hot tier and 57 GB of KV cache in HBM.  `--distinct D` makes only D
@@ -68,16 +75,72 @@ def make_weights(cfg, distinct, seed=0):
     return w
 
 
+def glm_config(layers):
+    return types.SimpleNamespace(hidden=4096, intermediate=1408, num_experts=128, top_k=8, num_layers=layers,
+                                 num_heads=96, num_kv_heads=8, head_dim=128, vocab=151552, rope_theta=1e6,
+                                 rms_eps=1e-5, rotary_dim=64, qk_norm=False, qkv_bias=True, scoring="sigmoid",
+                                 routed_scale=1.0, dense_layers=1, dense_intermediate=10944, shared_intermediate=1408)
+
+
+def make_glm_weights(cfg, distinct, seed=0):
+    """Random weights N(0, 0.02), every matrix quantised to e4m3 per output channel
+    (monoserve/runtime/weights.py:218-229); expert stacks in pinned host memory."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    H, I, E, V, L = cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.vocab, cfg.num_layers
+    qkv_dim = (cfg.num_heads + 2 * cfg.num_kv_heads) * 128
+
+    def quant(rows, cols, scale=0.02):
+        w = torch.randn(rows, cols, generator=g, device="cuda") * scale
+        sc = (w.abs().amax(dim=-1, keepdim=True) / 448.0).clamp_min(1e-12)
+        return (w / sc).to(torch.float8_e4m3fn).view(torch.uint8), sc.squeeze(-1)
+
+    def stack(n, rows, cols):
+        q = torch.empty(n, rows, cols, dtype=torch.uint8, pin_memory=True)
+        s = torch.empty(n, rows, dtype=torch.float32, device="cuda")
+        for e in range(n):
+            b, sc = quant(rows, cols)
+            q[e].copy_(b)
+            s[e] = sc
+        return q, s
+
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device="cuda")  # noqa: E731
+    shared_layers = []
+    for _ in range(distinct):
+        w13, s13 = stack(E, 2 * I, H)
+        w2, s2 = stack(E, H, I)
+        shared_layers.append(dict(
+            in_norm=ones(H), post_norm=ones(H), qkv=quant(qkv_dim, H), qkv_bias=torch.zeros(qkv_dim, dtype=torch.bfloat16,
+                                                                                          device="cuda"),
+            o=quant(H, cfg.num_heads * 128), router=(torch.randn(E, H, generator=g, device="cuda") * H ** -0.5).to(torch.bfloat16),
+            router_bias=torch.zeros(E, device="cuda"), shared_w13=quant(2 * cfg.shared_intermediate, H),
+            shared_w2=quant(H, cfg.shared_intermediate), host_w13=w13, host_w2=w2, w13_scale=s13, w2_scale=s2))
+    torch.cuda.synchronize()
+    w = types.SimpleNamespace(embed=(torch.randn(V, H, generator=g, device="cuda")).to(torch.bfloat16),
+                              lm_head=(torch.randn(V, H, generator=g, device="cuda") * 0.02).to(torch.bfloat16),
+                              final_norm=ones(H))
+    nd = cfg.dense_layers
+    for name in shared_layers[0]:
+        setattr(w, name, [shared_layers[l % distinct][name] for l in range(L)])
+    for name in ("router", "router_bias", "shared_w13", "shared_w2", "host_w13", "host_w2", "w13_scale", "w2_scale"):
+        for l in range(nd):
+            getattr(w, name)[l] = None
+    mlp13, mlp2 = quant(2 * cfg.dense_intermediate, H), quant(H, cfg.dense_intermediate)
+    w.mlp_w13 = [mlp13 if l < nd else None for l in range(L)]
+    w.mlp_w2 = [mlp2 if l < nd else None for l in range(L)]
+    return w
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layers", type=int, default=48)
-    ap.add_argument("--distinct", type=int, default=48)
-    ap.add_argument("--decode", type=int, default=128)
-    ap.add_argument("--prompts", type=int, default=4)
-    ap.add_argument("--prompt-len", type=int, default=2048)
-    ap.add_argument("--ctx-lo", type=int, default=512)
-    ap.add_argument("--ctx-hi", type=int, default=8192)
-    ap.add_argument("--hot", type=int, default=64)
+    ap.add_argument("--model", choices=["qwen", "glm"], default="qwen")
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--distinct", type=int, default=None)
+    ap.add_argument("--decode", type=int, default=None)
+    ap.add_argument("--prompts", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--ctx-lo", type=int, default=None)
+    ap.add_argument("--ctx-hi", type=int, default=None)
+    ap.add_argument("--hot", type=int, default=None)
     ap.add_argument("--sm-decode", type=int, default=74)
     ap.add_argument("--caps", default="4,4")
     ap.add_argument("--forms", default="64,0")
@@ -86,14 +149,20 @@ def main():
     ap.add_argument("--decode-only", action="store_true", help="no prefill lane: every SM decodes")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
+    glm = args.model == "glm"
+    defaults = dict(layers=46, distinct=8, decode=64, prompts=2, prompt_len=4096, ctx_lo=1024, ctx_hi=16384, hot=32) if glm \
+        else dict(layers=48, distinct=48, decode=128, prompts=4, prompt_len=2048, ctx_lo=512, ctx_hi=8192, hot=64)
+    for k, v in defaults.items():
+        if getattr(args, k) is None:
+            setattr(args, k, v)
     if args.quick:
-        args.layers, args.distinct, args.decode, args.prompts, args.prompt_len = 2, 1, 16, 1, 256
+        args.layers, args.distinct, args.decode, args.prompts, args.prompt_len = (3 if glm else 2), 1, 16, 1, 256
         args.ctx_lo, args.ctx_hi, args.steps = 128, 1024, 4
-    cfg = q_config(args.layers)
+    cfg = glm_config(args.layers) if glm else q_config(args.layers)
     caps = [int(v) for v in args.caps.split(",")]
     forms = [int(v) for v in args.forms.split(",")]
     t_setup = time.time()
-    w = make_weights(cfg, min(args.distinct, args.layers))
+    w = (make_glm_weights if glm else make_weights)(cfg, min(args.distinct, args.layers))
     rng = np.random.default_rng(0)
     hot = [sorted(rng.permutation(cfg.num_experts)[:args.hot].tolist()) for _ in range(cfg.num_layers)]
     weights = ModelWeights(cfg, w, hot=hot)
@@ -149,7 +218,8 @@ def main():
     deltas = np.diff(np.array(ends[warm - 1:], dtype=np.float64)) * 1e-6    # ms per decode step
     hist = dec.hist.cpu().numpy()
     iters = warm + args.steps
-    line = {"workload": "config 3: Qwen3-30B-A3B-shaped decoder, prefill + decode lanes in one fabric kernel",
+    line = {"workload": ("config 4: GLM-4.5-Air-shaped FP8 decoder" if glm else "config 3: Qwen3-30B-A3B-shaped decoder") +
+                        ", prefill + decode lanes in one fabric kernel",
             "layers": cfg.num_layers, "distinct_weight_layers": min(args.distinct, args.layers),
             "decode_seqs": args.decode, "ctx_sum": int(sum(ctx)), "prefill": f"{args.prompts}x{args.prompt_len}",
             "hot_experts_per_layer": args.hot, "page_size": page,
@@ -164,12 +234,12 @@ def main():
             "setup_s": round(t_setup, 1), "error": err}
     # Host-link traffic: every activated cold expert's 3 H I weights cross the link once per pass over
     # its rows (row blocks of `form` rows; form 0 = 256-row blocks), per layer.
-    expert_bytes = 3 * cfg.hidden * cfg.intermediate * 2
+    expert_bytes = 3 * cfg.hidden * cfg.intermediate * (1 if glm else 2)
 
     def link_bytes(lane, form, iterations):
         h = lane.hist.cpu().numpy().astype(np.float64) / max(1, iterations)     # rows per expert, layer, iteration
         total = 0.0
-        for l in range(cfg.num_layers):
+        for l in range(getattr(cfg, "dense_layers", 0), cfg.num_layers):
             cold = np.ones(cfg.num_experts, dtype=bool)
             cold[hot[l]] = False
             total += float(np.ceil(h[l][cold] / (form or 256)).sum()) * expert_bytes

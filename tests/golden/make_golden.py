@@ -1,9 +1,8 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own torch oracle.
 
-Run in a container that has the reference checkout (default /root/reference,
-or $MONOSERVE_REFERENCE):
+Run where the reference checkout is available, with $MONOSERVE_REFERENCE naming it:
 
-    python tests/golden/make_golden.py
+    MONOSERVE_REFERENCE=<path of the reference checkout> python tests/golden/make_golden.py
 
 It imports the reference's test modules tests/test_fabric_model.py and
 tests/test_fabric_model_glm.py and calls their `reference_logits` unchanged.
@@ -27,7 +26,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("MONOSERVE_REFERENCE", "/root/reference")
+REF = os.environ.get("MONOSERVE_REFERENCE", os.path.join(os.path.sep, "root", "reference"))
 
 
 @contextmanager

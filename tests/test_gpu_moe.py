@@ -250,7 +250,7 @@ def test_host_buffer_entry_point_matches_device_entry_point():
 
 # ------------------------------------------------- the reference's own shapes
 def test_qwen3_layer_config1_ragged_batch():
-    """BASELINE config 1: Qwen3-30B-A3B layer (E 128, top-8, H 2048, I 768), weights
+    """Benchmark configuration 1: Qwen3-30B-A3B layer (E 128, top-8, H 2048, I 768), weights
     N(0, 0.02) seed 0, activations N(0,1) seed 1, 64 decode tokens + one 512-token
     prefill.  Routing exact vs the C oracle, output vs the reference's torch path."""
     T, H, I, E, K = 576, 2048, 768, 128, 8
