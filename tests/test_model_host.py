@@ -1,0 +1,33 @@
+"""Host-side pieces of the decoder lanes that need no GPU: the rotary table the qk_rope tile reads must
+hold exactly the cos / sin values the reference's oracle computes, for full and partial rotary."""
+import torch
+
+from oracle import torch_path as tp
+
+
+def test_rope_table_matches_oracle_rope():
+    from monoserve_b200.model import rope_table
+    g = torch.Generator().manual_seed(0)
+    for theta, rot in [(1e6, 128), (1e4, 64)]:
+        table = rope_table(theta, rot, 300)              # [pos][rot / 2][cos, sin]
+        x = torch.randn(7, 3, 128, generator=g)
+        pos = torch.tensor([0, 1, 5, 17, 64, 255, 299])
+        half = rot // 2
+        c, s = table[pos, :, 0][:, None, :], table[pos, :, 1][:, None, :]
+        x1, x2 = x[..., :half], x[..., half:rot]
+        mine = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, x[..., rot:]], -1)
+        assert torch.equal(mine, tp.rope(x, pos, theta, rot))
+
+
+def test_logits_tiles_cover_rows_and_experts_once():
+    import numpy as np
+    from monoserve_b200.lane import LOGIT_EXPERTS, LOGIT_ROWS, logits_tiles
+    for T, E in [(1, 16), (37, 128), (256, 160)]:
+        tiles = logits_tiles(0x1000, T, E)
+        seen = np.zeros((T, E), dtype=np.int32)
+        for t in tiles:
+            r0, rows = int(t[1] & 0xffffffff), int(t[1] >> 32)
+            e0, ne = int(t[2] & 0xffffffff), int(t[2] >> 32)
+            assert rows <= LOGIT_ROWS and ne <= LOGIT_EXPERTS and int(t[0] & 0xffff) == 48
+            seen[r0:r0 + rows, e0:e0 + ne] += 1
+        assert (seen == 1).all()
