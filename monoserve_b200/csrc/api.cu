@@ -164,8 +164,10 @@ int build_maps(monofab_moe* m) {
       if (!base) return fail(MONOFAB_EINVAL, "no expert weights set (monofab_moe_set_region)");
       const uint64_t dims[3] = {K, rows, static_cast<uint64_t>(slots)};
       const uint64_t strides[2] = {K * esz, rows * K * esz};
-      const uint32_t box[3] = {64, 16, 1};       // 64 elements of K: 128 bytes of bf16, 64 bytes of e4m3
-      const uint32_t box_big[3] = {64, 128, 1};
+      // 128 bytes of K per row: 64 bf16 elements (one K step), or 128 e4m3 bytes (the two K steps of a stage)
+      const uint32_t kbox = c.fp8 ? 128 : 64;
+      const uint32_t box[3] = {kbox, 16, 1};
+      const uint32_t box_big[3] = {kbox, 128, 1};
       if (int r = encode_map(&ph.w_map[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box, c.fp8 ? 0 : 128)) return r;
       if (int r = encode_map(&ph.w_map_big[region], c.fp8 ? 2 : 0, base, 3, dims, strides, box_big, c.fp8 ? 0 : 128))
         return r;

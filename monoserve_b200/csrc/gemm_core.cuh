@@ -26,7 +26,6 @@ namespace mf {
 
 constexpr int kBlockK = 64;                      // elements per K step (128 bytes of bf16)
 constexpr int kATileBytes = 128 * kBlockK * 2;   // 16 KB
-constexpr int kRawTileBytes = 128 * kBlockK;     // 8 KB: the e4m3 image of a weight tile
 constexpr int kGemmMaxN = 256;
 // Operand stages live in one byte ring: a stage takes 16 KB for the weight tile
 // plus n * 128 bytes for the activation tile, so small-n (decode) tiles keep up
@@ -116,8 +115,19 @@ struct GemmInflight {
 
 // Bytes of one stage: weight tile (bf16), activation tile, and for FP8 weights the
 // raw e4m3 tile the converter warps expand.
+// K steps (of kBlockK elements) one stage holds.  A stage of e4m3 weights holds two: a row of the raw
+// tile is then 128 bytes, which is what makes reads of host-resident weights over the link efficient
+// (64-byte reads reach 42 GB/s, 128-byte reads 51 GB/s).
+__device__ __forceinline__ int gemm_ksteps(const GemmWork& w) { return w.w_fp8 ? 2 : 1; }
+__device__ __forceinline__ int gemm_stage_count(const GemmWork& w) {
+  return w.w_fp8 ? (w.k_tiles + 1) >> 1 : w.k_tiles;
+}
+// Bytes of one stage: per K step the bf16 weight tile and the activation tile; layout: weight tiles,
+// then activation tiles.  The raw e4m3 tile (128 rows of 128 bytes) lands in the second weight tile
+// and is expanded in place: the 128-byte swizzle permutes 16-byte chunks inside a row, so row r of the
+// second K step's bf16 tile covers exactly the bytes of raw row r, which one converter thread owns.
 __device__ __forceinline__ uint32_t gemm_stage_bytes(const GemmWork& w) {
-  return kATileBytes + w.n * kBlockK * 2 + (w.w_fp8 ? kRawTileBytes : 0);
+  return gemm_ksteps(w) * (kATileBytes + w.n * kBlockK * 2);
 }
 
 struct GemmBarriers {
@@ -151,9 +161,12 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
   const int lane = threadIdx.x & 31;
   const uint32_t size = gemm_stage_bytes(w);
   const uint32_t b_bytes = w.n * kBlockK * 2;
-  // FP8 weights land as raw bytes behind the activation tile (64-byte rows, no swizzle)
-  const uint32_t a_off = w.w_fp8 ? kATileBytes + b_bytes : 0;
-  const uint32_t a_box = w.w_fp8 ? 1024 : 2048;   // bytes of one 16-row box
+  const int ks = gemm_ksteps(w);
+  // FP8 weights land as raw bytes in the second weight tile (128-byte rows = two K steps, no swizzle)
+  const uint32_t a_off = w.w_fp8 ? kATileBytes : 0;
+  const uint32_t a_box = 2048;   // bytes of one 16-row box: 128-byte rows either way
+  const uint32_t b_off = ks * kATileBytes;
+  const int n_stages = gemm_stage_count(w);
   // SwiGLU tiles of a tensor in the reference row order gather eight 16-row boxes;
   // every other tile is one 128-row box (a packed SwiGLU tensor stores gate/up
   // groups of 16 rows alternately, so its tile starts at row 2 * a_row_lo).
@@ -161,7 +174,7 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
   const int a_row = gather ? ((lane & 1) ? w.a_row_hi : w.a_row_lo) + 16 * ((lane & 7) >> 1)
                            : (w.epi == kEpiSiluMul ? 2 * w.a_row_lo : w.a_row_lo);
   const int n_a = gather ? 8 : 1;
-  for (int kt = 0; kt < w.k_tiles; ++kt) {
+  for (int st = 0; st < n_stages; ++st) {
     uint32_t vb, ve;
     const uint32_t phys = pipe.alloc(size, vb, ve);
     // room in the ring and a free barrier pair: retire the oldest stages as needed
@@ -177,13 +190,14 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
     fl.vbegin[slot] = vb;
     uint8_t* a = ring + phys;
     uint64_t* full = &bar.full[slot];
-    if (lane == 0) mbar_arrive_expect_tx(full, (w.w_fp8 ? kRawTileBytes : kATileBytes) + b_bytes);
+    // a K step past the end of an odd K range reads zeros (out-of-bounds fill) and adds nothing
+    if (lane == 0) mbar_arrive_expect_tx(full, kATileBytes + ks * b_bytes);
     __syncwarp();
-    const int x = (w.k0 + kt) * kBlockK;
+    const int x = (w.k0 + st * ks) * kBlockK;
     if (lane < n_a) {
       tma_load_3d(a + a_off + lane * a_box, w.a_map, full, x, a_row, w.a_z, pol_w);
-    } else if (lane == 8) {
-      tma_load_2d(a + kATileBytes, w.b_map, full, x, w.b_row0, pol_x);
+    } else if (lane >= 8 && lane < 8 + ks) {
+      tma_load_2d(a + b_off + (lane - 8) * b_bytes, w.b_map, full, x + (lane - 8) * kBlockK, w.b_row0, pol_x);
     }
     pipe.advance();
   }
@@ -208,7 +222,9 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
     uint64_t* ready = w.w_fp8 ? bar.conv : bar.full;
     const uint32_t ring_addr = smem_u32(ring);
     const uint64_t desc0 = umma_desc_sw128(0);
-    for (int kt = 0; ok && kt < w.k_tiles; ++kt) {
+    const int ks = gemm_ksteps(w), n_stages = gemm_stage_count(w);
+    const uint32_t b_bytes = w.n * kBlockK * 2;
+    for (int kt = 0; ok && kt < n_stages; ++kt) {
       uint32_t vb, ve;
       const uint32_t phys = pipe.alloc(size, vb, ve);
       const long long tw = wait_cycles ? clock64() : 0;
@@ -220,10 +236,12 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
       if (w.w_fp8) pipe.conv_bits ^= 1u << pipe.slot;
       if (wait_cycles) wait_cycles[0] += clock64() - tw;
       const long long ti = wait_cycles ? clock64() : 0;
-      const uint64_t da = desc0 + ((ring_addr + phys) >> 4);
-      const uint64_t db = da + (kATileBytes >> 4);
+      for (int h = 0; h < ks; ++h) {   // the K steps of the stage
+        const uint64_t da = desc0 + ((ring_addr + phys + h * kATileBytes) >> 4);
+        const uint64_t db = desc0 + ((ring_addr + phys + ks * kATileBytes + h * b_bytes) >> 4);
 #pragma unroll
-      for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+        for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | h | k) != 0);
+      }
       umma_commit(&bar.empty[pipe.slot]);
       if (wait_cycles) wait_cycles[1] += clock64() - ti;
       pipe.advance();
@@ -246,32 +264,39 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
 // warps expand the raw e4m3 tile of every stage into the bf16 weight tile with the
 // 128-byte swizzle.  Every e4m3 value is exactly a bf16 value, so the MMA sees the
 // exact weights; the per-output-channel fp32 scale is applied in the epilogue.
-// Thread t converts row t: 64 bytes in, 128 bytes out in eight 16-byte chunks,
+// Thread t converts row t: per K step 64 bytes in, 128 bytes out in eight 16-byte chunks,
 // chunk c of row r going to chunk c ^ (r & 7).
 __device__ __forceinline__ bool gemm_convert(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
                                              int row, volatile int* abort_flag) {
   const uint32_t size = gemm_stage_bytes(w);
-  const uint32_t raw_off = kATileBytes + w.n * kBlockK * 2;
-  for (int kt = 0; kt < w.k_tiles; ++kt) {
+  const int ks = gemm_ksteps(w), n_stages = gemm_stage_count(w);
+  const uint32_t raw_off = kATileBytes;
+  for (int kt = 0; kt < n_stages; ++kt) {
     uint32_t vb, ve;
     const uint32_t phys = pipe.alloc(size, vb, ve);
     if (!mbar_wait_bounded(&bar.full[pipe.slot], pipe.parity, abort_flag, kWaitBudgetNs)) return false;
-    const uint4* src = reinterpret_cast<const uint4*>(ring + phys + raw_off + row * kBlockK);
-    uint8_t* dst = ring + phys + row * 128;
+    // The row's raw bytes [64 h, 64 h + 64) are K step h.  The thread reads its whole row before it
+    // writes (the second K step's output overwrites the raw row), starting at 16-byte chunk t & 7 so
+    // that the eight threads of a shared-memory phase read eight different bank groups.
+    const uint4* src = reinterpret_cast<const uint4*>(ring + phys + raw_off + row * 128);
+    uint4 v[8];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint4 v = src[c];
-      const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < 8; ++i) v[i] = src[(i + row) & 7];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = (i + row) & 7, h = q >> 2, c = q & 3;
+      uint8_t* dst = ring + phys + h * kATileBytes + row * 128;
+      const uint32_t in[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
       uint32_t out[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[i] & 0xffffu), __NV_E4M3);
-        const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[i] >> 16), __NV_E4M3);
+      for (int j = 0; j < 4; ++j) {
+        const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[j] & 0xffffu), __NV_E4M3);
+        const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(in[j] >> 16), __NV_E4M3);
         const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&lo));
         const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&hi));
         const __nv_bfloat162 bl = __floats2bfloat162_rn(fl.x, fl.y), bh = __floats2bfloat162_rn(fh.x, fh.y);
-        out[2 * i] = *reinterpret_cast<const uint32_t*>(&bl);
-        out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&bh);
+        out[2 * j] = *reinterpret_cast<const uint32_t*>(&bl);
+        out[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&bh);
       }
       // 16 input bytes -> 32 output bytes = chunks 2c and 2c + 1 of the row
       *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(out[0], out[1], out[2], out[3]);

@@ -89,7 +89,7 @@ class MoELane:
         def wmap(t, base, packed=False):
             z, rows, k = t.shape
             if t.dtype == torch.uint8:   # e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
-                return fab.tensor_map(base, [k, rows, z], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0, packed=packed)
+                return fab.tensor_map(base, [k, rows, z], [k, rows * k], [128, 64, 1], dtype=2, swizzle=0, packed=packed)
             return fab.tensor_map(base, [k, rows, z], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
 
         self.w13_maps = _u64([wmap(self.host_w13, _C.host_device_pointer(self.host_w13.data_ptr())),

@@ -225,7 +225,7 @@ class ModelLane:
             zdim, rows, k = t.shape
         base = base if base is not None else t.data_ptr()
         if t.dtype == torch.uint8:   # e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
-            return self.fab.tensor_map(base, [k, rows, zdim], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0, packed=packed)
+            return self.fab.tensor_map(base, [k, rows, zdim], [k, rows * k], [128, 64, 1], dtype=2, swizzle=0, packed=packed)
         return self.fab.tensor_map(base, [k, rows, zdim], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
 
     def _amaps(self, t, rows, k):

@@ -206,7 +206,7 @@ def test_fp8_expert_ffn(fab, where):
 
     def fp8_map(base, shape):   # (E, rows, K) e4m3 bytes: byte strides, no swizzle (monoserve/runtime/weights.py:38-40)
         n_e, rows, k = shape
-        return fab.tensor_map(base, [k, rows, n_e], [k, rows * k], [64, 64, 1], dtype=2, swizzle=0)
+        return fab.tensor_map(base, [k, rows, n_e], [k, rows * k], [128, 64, 1], dtype=2, swizzle=0)
 
     a13 = args_tensor(out=hbuf.data_ptr(), ld_out=I, k_tiles=H // 64, epi=EPI_SILU_MUL, bm=bm, n_limit=I, up_offset=I,
                       w_fp8=1)

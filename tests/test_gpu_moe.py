@@ -394,9 +394,11 @@ def test_fp8_layer_against_dequantised_reference(hot, pack_hot, form):
     m.close()
 
 
-def test_fp8_qwen_shape_prefill_rows():
-    """GLM-like FP8 at a larger shape with long expert segments (prefill-sized rows)."""
-    T, H, I, E, K = 600, 1024, 384, 8, 2
+@pytest.mark.parametrize("I", [384, 320])
+def test_fp8_qwen_shape_prefill_rows(I):
+    """GLM-like FP8 at a larger shape with long expert segments (prefill-sized rows); I = 320 gives the
+    down projection an odd number of 64-element K steps (the last e4m3 stage is half zero fill)."""
+    T, H, E, K = 600, 1024, 8, 2
     m, wr, d13, d2 = make_fp8_layer(T, H, I, E, K, list(range(4)), seed=23)
     xn, x2 = acts(T, H, 24)
     out = m.forward(xn.cuda(), x2.cuda())
