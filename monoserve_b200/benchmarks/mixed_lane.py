@@ -147,6 +147,8 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--decode-only", action="store_true", help="no prefill lane: every SM decodes")
+    ap.add_argument("--staged", action="store_true",
+                    help="prefill lane: experts with more than 256 rows go through the HBM staging stack (form 0)")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
     glm = args.model == "glm"
@@ -194,7 +196,7 @@ def main():
     if not args.decode_only:
         T = args.prompts * args.prompt_len
         pre = ModelLane(fab, 1, cfg, weights, kv, max_tokens=T, max_slots=args.prompts, bt_stride=bt_stride,
-                        logit_rows=args.prompts, min_form=min_form)
+                        logit_rows=args.prompts, min_form=min_form, staged=args.staged)
         batch = []
         for s in range(args.prompts):
             pre.set_pages(s, perm[at - 1:at - 1 + pages_pre].tolist())
@@ -236,13 +238,16 @@ def main():
     # its rows (row blocks of `form` rows; form 0 = 256-row blocks), per layer.
     expert_bytes = 3 * cfg.hidden * cfg.intermediate * (1 if glm else 2)
 
-    def link_bytes(lane, form, iterations):
+    def link_bytes(lane, form, iterations, staged=False):
         h = lane.hist.cpu().numpy().astype(np.float64) / max(1, iterations)     # rows per expert, layer, iteration
         total = 0.0
         for l in range(getattr(cfg, "dense_layers", 0), cfg.num_layers):
             cold = np.ones(cfg.num_experts, dtype=bool)
             cold[hot[l]] = False
-            total += float(np.ceil(h[l][cold] / (form or 256)).sum()) * expert_bytes
+            passes = np.ceil(h[l][cold] / (form or 256))
+            if staged and form == 0:   # a staged expert crosses the link once
+                passes = np.minimum(passes, 1.0)
+            total += float(passes.sum()) * expert_bytes
         return total
 
     dec_iters = prog["lanes"][0]["iterations"]
@@ -253,7 +258,8 @@ def main():
         pre_ms = (pre_ends[-1] - pre_ends[-2]) * 1e-6
         line["prefill_iteration_ms"] = pre_ms
         line["prefill_tokens_per_s"] = args.prompts * args.prompt_len / pre_ms * 1e3
-        pre_link = link_bytes(pre, forms[1], prog["lanes"][1]["iterations"])
+        pre_link = link_bytes(pre, forms[1], prog["lanes"][1]["iterations"], staged=args.staged)
+        line["prefill_staged"] = bool(args.staged)
         line["prefill_link_bytes_per_iteration"] = pre_link
         link_rate += pre_link / (pre_ms * 1e-3)
     line["host_link_gbs"] = link_rate / 1e9

@@ -333,6 +333,7 @@ const std::string& layouts_json() {
     MF_JSON_STRUCT(AttnPlanArgs, MF_ATTN_PLAN_ARGS)
     MF_JSON_STRUCT(LogitsArgs, MF_LOGITS_ARGS)
     MF_JSON_STRUCT(CombineArgs, MF_COMBINE_ARGS)
+    MF_JSON_STRUCT(StagingArgs, MF_STAGING_ARGS)
     s += "}";
     return s;
   }();

@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
         w.out = ph.out;
         w.scale = ph.scale ? ph.scale + static_cast<size_t>(tile.expert) * ph.scale_ld : nullptr;
         w.w_fp8 = ph.w_fp8;
+        w.fetch = 0;
         w.bias = nullptr;
         w.residual = nullptr;
         w.pair_token = nullptr;

@@ -95,6 +95,10 @@ struct WorkerState {
   // the current claim
   const ProgramDesc* prog;
   uint32_t stage, tile_lane, link, next_index, left;
+  // the worker runs its records through a pipeline, behind the scheduler: a link slot is handed
+  // back only when the exec warps have finished the last link record issued under it
+  uint32_t link_last;                  // records issued up to and including the last link record
+  const volatile unsigned int* done;   // records the exec warps have finished
 };
 
 struct WorkSlot {
@@ -149,7 +153,36 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   w.a_packed = packed;
   w.block = -1;
   w.w_fp8 = A.w_fp8 != 0;   // e4m3 weights: the exec warps expand every stage to bf16 before its MMAs
+  w.fetch = 0;
   return w.k_tiles > 0 && A.epi <= kEpiRowsF32;
+}
+
+// Fetch tile (kind 49): i0 bytes from a[0] (host-resident weights) to a[1] (an HBM staging buffer).
+// It runs through the GEMM roles as a record without MMAs: the producer's bulk loads fill ring
+// stages, the MMA warp stores each stage to the destination, the exec warps only keep step.
+__device__ bool make_fetch_work(const TileDesc& t, GemmWork& w) {
+  w.a_map = nullptr;
+  w.b_map = nullptr;
+  w.out = reinterpret_cast<void*>(t.a[1]);
+  w.scale = nullptr;
+  w.bias = nullptr;
+  w.residual = nullptr;
+  w.pair_token = nullptr;
+  w.pair_weight = nullptr;
+  w.a_row_lo = w.a_row_hi = w.a_z = w.b_row0 = w.rows = 0;
+  w.n = 16;
+  w.k0 = 0;
+  w.k_tiles = 1;
+  w.epi = kEpiStoreBf16;
+  w.ld_out = w.ld_res = w.n_limit = 0;
+  w.valid = 1;
+  w.a_packed = 0;
+  w.block = -1;
+  w.w_fp8 = 0;
+  w.fetch = 1;
+  w.fetch_bytes = t.i0;
+  w.fetch_src = reinterpret_cast<const uint8_t*>(t.a[0]);
+  return t.i0 > 0 && ((t.i0 | t.a[0] | t.a[1]) & 15) == 0 && t.a[0] != 0 && t.a[1] != 0;
 }
 
 __device__ void trace_stage(DeviceState& S, uint32_t lane, uint32_t s, uint32_t event, uint32_t tag) {
@@ -512,6 +545,11 @@ __device__ bool acquire_slot(LaneState& L, uint32_t cap) {
 
 __device__ void release_slot(DeviceState& S, WorkerState& ws) {
   if (ws.slot_lane != kNoLane) {
+    if (ws.done && static_cast<int>(*ws.done - ws.link_last) < 0) {
+      // bounded: after a second the slot goes back regardless (the fabric is stuck or stopping)
+      const unsigned long long t0 = globaltimer_ns();
+      while (static_cast<int>(*ws.done - ws.link_last) < 0 && globaltimer_ns() - t0 < 1000000000ull) __nanosleep(64);
+    }
     atomicSub(&S.lane[ws.slot_lane].slots, 1u);
     ws.slot_lane = kNoLane;
   }
@@ -969,7 +1007,11 @@ __device__ void tile_combine(const TileDesc& t, int tid) {
 // flagged kStageSkip and taken off the join stage's dependency count.  Differences
 // from the reference: counts may come from the router tiles' chunk counts (then the
 // per-chunk prefixes are produced too, for the stable pack); form 0 maps to 256-row
-// blocks (one pass over the weights) instead of K-split tiles with a reduce stage;
+// blocks (one pass over the weights) instead of K-split tiles with a reduce stage, and,
+// when the program has fetch stages (`staging` set), a host-resident expert with more than
+// min_rows rows takes the staged form: fetch tiles copy its weights once into the HBM staging
+// stack and its GEMM tiles read that copy, so the expert crosses the link once whatever its
+// row count (what the reference's weight-stationary K-split form is for), without partial sums;
 // an overflow of the dynamic region raises an error bit instead of trapping; red_stage0 =
 // 0xffffffff says the program has no reduce stages (w2[e] follows w13[e] directly).
 __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid) {
@@ -988,6 +1030,12 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   load_block(A, t.a[0]);
   const int E = static_cast<int>(A.E);
   if (E < 1 || E > kMaxExperts) return;
+  StagingArgs G{};
+  if (A.staging) load_block(G, A.staging);
+  const bool can_stage = A.staging != 0 && G.chunk_bytes >= 16 && (G.chunk_bytes & 15) == 0;
+  // fetch tiles of a staged expert: its w13 block, then its w2 block, in chunks
+  const int nf13 = can_stage ? static_cast<int>((G.w13_bytes + G.chunk_bytes - 1) / G.chunk_bytes) : 0;
+  const int nf2 = can_stage ? static_cast<int>((G.w2_bytes + G.chunk_bytes - 1) / G.chunk_bytes) : 0;
   // the program's arrays, read once: the descriptor itself lives in global memory
   TileDesc* const p_tiles = P->tiles;
   StageStatic* const p_stages = P->stages;
@@ -1069,11 +1117,13 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
     const int M = s_cnt[e];
     const int region = table[2 * e], slot = table[2 * e + 1];
     const bool link = region == static_cast<int>(A.host_region);
+    const bool staged = link && can_stage && s_form == 0 && M > static_cast<int>(G.min_rows);
     const int bm = block_rows(M, link);
     int cls = 0;
     while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
-    s_n[e] = M > 0 ? ((M + bm - 1) / bm) * (f13 + f2) : 0;
-    s_info[e] = (slot << 12) | ((region & 0xff) << 4) | cls;
+    s_n[e] = M > 0 ? ((M + bm - 1) / bm) * (f13 + f2) + (staged ? nf13 + nf2 : 0) : 0;
+    // a staged expert's GEMM tiles read region 2 (the staging stack), slot = expert id
+    s_info[e] = staged ? (e << 12) | (1 << 11) | (2 << 4) | cls : (slot << 12) | ((region & 0x7f) << 4) | cls;
   }
   if (tid < 5) {
     s_tab[tid] = reinterpret_cast<const unsigned long long*>(A.w13_args)[tid];
@@ -1091,6 +1141,7 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   const bool has_red = A.red_stage0 != 0xffffffffu;   // the reduce stages of the reference's chain are optional here
   for (int e = tid; e < E; e += kExecThreads) {
     atomicExch(&p_runtime[A.w13_stage0 + e].tag_next, 0ull);
+    if (A.staging) atomicExch(&p_runtime[A.fetch_stage0 + e].tag_next, 0ull);
     if (has_red) atomicExch(&p_runtime[A.red_stage0 + e].tag_next, 0ull);
     atomicExch(&p_runtime[A.w2_stage0 + e].tag_next, 0ull);
   }
@@ -1113,13 +1164,37 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
       const int M = s_overflow ? 0 : s_cnt[e];
       if (M == 0) continue;
       const int info = s_info[e];
-      const int slot = info >> 12, region = (info >> 4) & 0xff, cls = info & 0xf;
+      const int slot = info >> 12, region = (info >> 4) & 0x7f, cls = info & 0xf;
+      const int nf = ((info >> 11) & 1) ? nf13 + nf2 : 0;
       const int bm = 16 << cls;
       const int blocks = (M + bm - 1) / bm;
-      const int n13 = blocks * f13, total = blocks * (f13 + f2);
+      const int n13 = blocks * f13, total = nf + blocks * (f13 + f2);
       uint4* dst = reinterpret_cast<uint4*>(p_tiles + A.dyn_first + s_off[e]);
       for (int q = lane; q < total * 4; q += 32) {
-        const int ti = q >> 2, part = q & 3;
+        const int part = q & 3;
+        if ((q >> 2) < nf) {   // a fetch tile: chunk j of the expert's w13 block, then of its w2 block
+          const int j = q >> 2;
+          const bool f13b = j < nf13;
+          const unsigned long long bytes = f13b ? G.w13_bytes : G.w2_bytes;
+          const unsigned long long at = static_cast<unsigned long long>(f13b ? j : j - nf13) * G.chunk_bytes;
+          const unsigned long long off = static_cast<unsigned long long>(e) * bytes + at;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (part == 0) {
+            v.x = kTileFetch;
+            v.z = static_cast<uint32_t>(min(static_cast<unsigned long long>(G.chunk_bytes), bytes - at));
+          } else if (part == 1) {   // a[0] source
+            const unsigned long long a0 = (f13b ? G.w13_src : G.w2_src) + off;
+            v.z = static_cast<uint32_t>(a0);
+            v.w = static_cast<uint32_t>(a0 >> 32);
+          } else if (part == 2) {   // a[1] destination
+            const unsigned long long a1 = (f13b ? G.w13_dst : G.w2_dst) + off;
+            v.x = static_cast<uint32_t>(a1);
+            v.y = static_cast<uint32_t>(a1 >> 32);
+          }
+          dst[q] = v;
+          continue;
+        }
+        const int ti = (q >> 2) - nf;
         const bool is13 = ti < n13;
         const int local = is13 ? ti : ti - n13, per = is13 ? f13 : f2;
         const int blk = local / per, f = local - blk * per;
@@ -1162,22 +1237,32 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
     while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
     const int blocks = M > 0 ? (M + bm - 1) / bm : 0;
     const int n13 = blocks * f13, n2 = blocks * f2;
-    s13.first = base;
+    const bool staged = M > 0 && ((s_info[e] >> 11) & 1);
+    const int nf = staged ? nf13 + nf2 : 0;
+    const uint32_t gemm_flags = (link && !staged) ? kStageLink : 0u;   // staged: only the fetch tiles use the link
+    const bool skip = M == 0 && active > 0;   // an unrouted expert: its chain is passed over
+    if (A.staging) {
+      StageStatic& sf = p_stages[A.fetch_stage0 + e];
+      sf.first = base;
+      sf.count = nf;
+      sf.flags = skip ? kStageSkip : kStageLink;
+    }
+    s13.first = base + nf;
     s13.count = n13;
-    s13.flags = link ? kStageLink : 0u;
-    if (M == 0 && active > 0) {   // an unrouted expert: its chain is passed over
+    s13.flags = gemm_flags;
+    if (skip) {
       s13.flags = kStageSkip;
       atomicAdd(&s_skipped, 1);
     }
     if (has_red) {
       StageStatic& sr = p_stages[A.red_stage0 + e];
-      sr.first = base + n13;
+      sr.first = base + nf + n13;
       sr.count = 0;
       sr.flags = 0u;
     }
-    s2.first = base + n13;
+    s2.first = base + nf + n13;
     s2.count = n2;
-    s2.flags = link ? kStageLink : 0u;
+    s2.flags = gemm_flags;
     if (A.hist && M > 0) atomicAdd(reinterpret_cast<int*>(A.hist) + e, M);
     counts[e] = 0;
     if (A.fill) reinterpret_cast<int*>(A.fill)[e] = 0;
@@ -1328,6 +1413,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     sh.ws.epoch = ~0ull;
     sh.ws.worker = worker;
     sh.ws.slot_lane = kNoLane;
+    sh.ws.link_last = 0;
+    sh.ws.done = &sh.tiles_done;
     sh.ws.idle_ns = 64;
     sh.ws.lane = kNoLane;
     sh.ws.n_lanes = 0;
@@ -1384,6 +1471,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           w.stage = ws.stage;
           w.tile_lane = ws.tile_lane;
           w.link = ws.link;
+          if (ws.link) ws.link_last = n + 1;
           w.index = ws.next_index;
           w.worker_lane = ws.lane;
           w.is_gemm = 0;
@@ -1395,8 +1483,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
               raise_error(S, kFabErrBadTile);
               w.tile.kind = kTileNop;
             }
-          } else if (w.tile.kind == kTileGemm) {
-            if (make_gemm_work(w.tile, w.gemm)) {
+          } else if (w.tile.kind == kTileGemm || w.tile.kind == kTileFetch) {
+            if (w.tile.kind == kTileGemm ? make_gemm_work(w.tile, w.gemm) : make_fetch_work(w.tile, w.gemm)) {
               w.is_gemm = 1;
             } else {
               raise_error(S, kFabErrBadTile);
@@ -1508,7 +1596,8 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           ok = gemm_convert(w.gemm, ring, sh.bar, conv_pipe, tid, abort_flag);
         } else {
           const uint32_t size = gemm_stage_bytes(w.gemm);
-          for (int kt = 0; kt < w.gemm.k_tiles; ++kt) {
+          const int n_stages = gemm_stage_count(w.gemm);
+          for (int kt = 0; kt < n_stages; ++kt) {
             uint32_t vb, ve;
             conv_pipe.alloc(size, vb, ve);
             conv_pipe.advance();

@@ -39,6 +39,7 @@ enum TileKind : uint16_t {
   kTileAttnPlan = 44,
   kTileCombine = 47,        // not in the reference: un-permute + weighted combine in pick order (+ RMSNorm)
   kTileRouterLogits = 48,   // not in the reference: router projection with a defined summation order
+  kTileFetch = 49,          // not in the reference: a[0] source, a[1] destination, i0 bytes; host memory -> HBM staging
 };
 constexpr int kFabChunk = 16;   // rows per router / permute tile = rank chunk of the stable pack
 

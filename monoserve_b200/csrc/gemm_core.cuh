@@ -70,6 +70,11 @@ struct GemmWork {
   int32_t a_packed;           // kEpiSiluMul: the weight rows are already interleaved in memory (one 128-row box)
   int32_t block;              // row block whose counter the epilogue bumps, or -1
   int32_t w_fp8;              // the weight tensor holds e4m3 bytes: W8A16 (exact e4m3 -> bf16 in shared memory)
+  // A fetch record moves fetch_bytes from fetch_src (host-resident weights) to `out` (an HBM staging
+  // buffer) through the operand ring, in stages of kFetchStageBytes: no MMA, no accumulator.
+  int32_t fetch;
+  uint32_t fetch_bytes;
+  const uint8_t* fetch_src;
 };
 
 struct GemmPipe {   // a role's cursor over the stage ring; producer and MMA warp replay the same sequence
@@ -118,8 +123,10 @@ struct GemmInflight {
 // K steps (of kBlockK elements) one stage holds.  A stage of e4m3 weights holds two: a row of the raw
 // tile is then 128 bytes, which is what makes reads of host-resident weights over the link efficient
 // (64-byte reads reach 42 GB/s, 128-byte reads 51 GB/s).
+constexpr uint32_t kFetchStageBytes = 32 * 1024;
 __device__ __forceinline__ int gemm_ksteps(const GemmWork& w) { return w.w_fp8 ? 2 : 1; }
 __device__ __forceinline__ int gemm_stage_count(const GemmWork& w) {
+  if (w.fetch) return static_cast<int>((w.fetch_bytes + kFetchStageBytes - 1) / kFetchStageBytes);
   return w.w_fp8 ? (w.k_tiles + 1) >> 1 : w.k_tiles;
 }
 // Bytes of one stage: per K step the bf16 weight tile and the activation tile; layout: weight tiles,
@@ -127,6 +134,7 @@ __device__ __forceinline__ int gemm_stage_count(const GemmWork& w) {
 // and is expanded in place: the 128-byte swizzle permutes 16-byte chunks inside a row, so row r of the
 // second K step's bf16 tile covers exactly the bytes of raw row r, which one converter thread owns.
 __device__ __forceinline__ uint32_t gemm_stage_bytes(const GemmWork& w) {
+  if (w.fetch) return kFetchStageBytes;
   return gemm_ksteps(w) * (kATileBytes + w.n * kBlockK * 2);
 }
 
@@ -190,6 +198,17 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
     fl.vbegin[slot] = vb;
     uint8_t* a = ring + phys;
     uint64_t* full = &bar.full[slot];
+    if (w.fetch) {
+      if (lane == 0) {
+        const uint32_t at = st * kFetchStageBytes;
+        const uint32_t bytes = min(kFetchStageBytes, w.fetch_bytes - at);
+        mbar_arrive_expect_tx(full, bytes);
+        bulk_load(a, w.fetch_src + at, bytes, full, pol_w);
+      }
+      __syncwarp();
+      pipe.advance();
+      continue;
+    }
     // a K step past the end of an odd K range reads zeros (out-of-bounds fill) and adds nothing
     if (lane == 0) mbar_arrive_expect_tx(full, kATileBytes + ks * b_bytes);
     __syncwarp();
@@ -235,6 +254,16 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
       }
       if (w.w_fp8) pipe.conv_bits ^= 1u << pipe.slot;
       if (wait_cycles) wait_cycles[0] += clock64() - tw;
+      if (w.fetch) {
+        // the stage goes on to the staging buffer; its shared memory is free once the store has read it
+        const uint32_t at = kt * kFetchStageBytes;
+        bulk_store(static_cast<uint8_t*>(w.out) + at, ring + phys, min(kFetchStageBytes, w.fetch_bytes - at));
+        bulk_commit();
+        bulk_wait_read_all();
+        mbar_arrive(&bar.empty[pipe.slot]);
+        pipe.advance();
+        continue;
+      }
       const long long ti = wait_cycles ? clock64() : 0;
       for (int h = 0; h < ks; ++h) {   // the K steps of the stage
         const uint64_t da = desc0 + ((ring_addr + phys + h * kATileBytes) >> 4);
@@ -246,7 +275,15 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
       if (wait_cycles) wait_cycles[1] += clock64() - ti;
       pipe.advance();
     }
-    if (ok) umma_commit(&bar.acc_full[buf]);
+    if (ok && w.fetch) {
+      // the record counts as done when its bytes are in the staging buffer, for readers of either proxy
+      bulk_wait_all();
+      fence_proxy_async_all();
+      __threadfence();
+      mbar_arrive(&bar.acc_full[buf]);
+    } else if (ok) {
+      umma_commit(&bar.acc_full[buf]);
+    }
   }
   // every lane follows lane 0's cursor, so that any lane could take over and the
   // warp stays convergent at tile boundaries
@@ -321,6 +358,10 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
   if (!mbar_wait_bounded(&bar.acc_full[buf], acc_parity, abort_flag, kWaitBudgetNs)) return false;
   tc_fence_after_sync();
   if (acc_seen && lane == 0) *acc_seen = globaltimer_ns();
+  if (w.fetch) {   // nothing to drain: the MMA warp has already moved the bytes
+    __syncwarp();
+    return true;
+  }
   const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * kAccCols;
   const bool silu = w.epi == kEpiSiluMul;
   // output feature of this lane, and the weight row its accumulator row came from

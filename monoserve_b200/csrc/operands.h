@@ -40,7 +40,13 @@ namespace mf {
   U64(w13_args) U64(w2_args) U64(hist) U64(w13_asym_args) U64(w2_asym_args) U64(red_args) \
   U64(w13_scale) U64(w2_scale) U32(E) U32(H) U32(I) U32(host_region) U32(w13_stage0) U32(w2_stage0) \
   U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage) U32(chunks) U64(chunk_counts) \
-  U64(chunk_prefix)
+  U64(chunk_prefix) U64(staging) U32(fetch_stage0) U32(reserved1)
+
+/* Not in the reference: the staged form of a host-resident expert with many rows.  Its weights are
+ * copied once into an HBM staging stack (slot = expert id) by fetch tiles, and its GEMM tiles read
+ * that copy, so the expert crosses the host link once however many row blocks it has. */
+#define MF_STAGING_ARGS(U64, U32, F32) \
+  U64(w13_src) U64(w13_dst) U64(w13_bytes) U64(w2_src) U64(w2_dst) U64(w2_bytes) U32(chunk_bytes) U32(min_rows)
 
 #define MF_REDUCE_ARGS(U64, U32, F32) U64(ws) U64(out) U32(I) U32(ld_ws) U32(ld_out)
 
@@ -80,7 +86,8 @@ MF_DECLARE(NormArgs, MF_NORM_ARGS, 128)
 MF_DECLARE(StepArgs, MF_STEP_ARGS, 64)
 MF_DECLARE(QkArgs, MF_QK_ARGS, 128)
 MF_DECLARE(RouterArgs, MF_ROUTER_ARGS, 128)
-MF_DECLARE(ExpandArgs, MF_EXPAND_ARGS, 192)
+MF_DECLARE(ExpandArgs, MF_EXPAND_ARGS, 256)
+MF_DECLARE(StagingArgs, MF_STAGING_ARGS, 64)
 MF_DECLARE(ReduceArgs, MF_REDUCE_ARGS, 64)
 MF_DECLARE(PermuteArgs, MF_PERMUTE_ARGS, 128)
 MF_DECLARE(SampleArgs, MF_SAMPLE_ARGS, 64)

@@ -53,11 +53,15 @@ class MoELane:
     lane.set_input(xn, x2); h = lane.build(T, iterations=1); fab.publish(..., programs=[h]) ..."""
 
     def __init__(self, fab, lane_id, hidden, intermediate, experts, top_k, max_tokens, wr, w13, w2, hot,
-                 pack_hot=True, scales=None, scoring=0, bias=None, routed_scale=1.0, shared=None):
+                 pack_hot=True, scales=None, scoring=0, bias=None, routed_scale=1.0, shared=None, staged=False,
+                 staged_min_rows=256, fetch_chunk=256 * 1024):
         """w13 / w2: bf16, or e4m3 bytes (uint8) with scales = (fp32 [E][2I], fp32 [E][H]) per output
         channel.  scoring 1 = sigmoid with the optional fp32 [E] selection bias; routed_scale multiplies
         the renormalised weights.  shared = (w13 bf16 [2 Is][H], w2 bf16 [H][Is]): a shared expert every
-        token passes through, added to the routed sum (tests/test_fabric_model_glm.py:29-31,57-67)."""
+        token passes through, added to the routed sum (tests/test_fabric_model_glm.py:29-31,57-67).
+        staged: under form 0 a host-resident expert with more than staged_min_rows rows is first copied
+        into an HBM staging stack by fetch tiles (chunks of fetch_chunk bytes) and its GEMM tiles read the
+        copy, so its weights cross the host link once whatever its row count."""
         self.fab, self.lane_id = fab, lane_id
         self.H, self.I, self.E, self.K, self.T = hidden, intermediate, experts, top_k, max_tokens
         H, I, E, K, T = hidden, intermediate, experts, top_k, max_tokens
@@ -92,10 +96,24 @@ class MoELane:
                 return fab.tensor_map(base, [k, rows, z], [k, rows * k], [128, 64, 1], dtype=2, swizzle=0, packed=packed)
             return fab.tensor_map(base, [k, rows, z], [k * 2, rows * k * 2], [64, 64, 1], packed=packed)
 
-        self.w13_maps = _u64([wmap(self.host_w13, _C.host_device_pointer(self.host_w13.data_ptr())),
-                              wmap(self.hot_w13, self.hot_w13.data_ptr(), packed=pack_hot)])
-        self.w2_maps = _u64([wmap(self.host_w2, _C.host_device_pointer(self.host_w2.data_ptr())),
-                             wmap(self.hot_w2, self.hot_w2.data_ptr())])
+        m13 = [wmap(self.host_w13, _C.host_device_pointer(self.host_w13.data_ptr())),
+               wmap(self.hot_w13, self.hot_w13.data_ptr(), packed=pack_hot), 0, 0]
+        m2 = [wmap(self.host_w2, _C.host_device_pointer(self.host_w2.data_ptr())),
+              wmap(self.hot_w2, self.hot_w2.data_ptr()), 0, 0]
+        self.staging = None
+        if staged:   # region 2: the staging stack, one slot per expert, the reference's row order
+            self.stage_w13 = torch.empty(self.host_w13.shape, dtype=self.host_w13.dtype, device=dev)
+            self.stage_w2 = torch.empty(self.host_w2.shape, dtype=self.host_w2.dtype, device=dev)
+            m13[2], m2[2] = wmap(self.stage_w13, self.stage_w13.data_ptr()), wmap(self.stage_w2, self.stage_w2.data_ptr())
+            b13 = self.host_w13[0].numel() * self.host_w13.element_size()
+            b2 = self.host_w2[0].numel() * self.host_w2.element_size()
+            self.fetch_tiles = -(-b13 // fetch_chunk) + -(-b2 // fetch_chunk)
+            self.staging = _block("StagingArgs", w13_src=_C.host_device_pointer(self.host_w13.data_ptr()),
+                                  w13_dst=self.stage_w13.data_ptr(), w13_bytes=b13,
+                                  w2_src=_C.host_device_pointer(self.host_w2.data_ptr()),
+                                  w2_dst=self.stage_w2.data_ptr(), w2_bytes=b2, chunk_bytes=fetch_chunk,
+                                  min_rows=staged_min_rows)
+        self.w13_maps, self.w2_maps = _u64(m13), _u64(m2)
         # workspaces
         z = lambda *shape, dt=torch.int32: torch.zeros(*shape, dtype=dt, device=dev)  # noqa: E731
         self.xn, self.x2, self.x = (z(T, H, dt=torch.bfloat16) for _ in range(3))
@@ -160,7 +178,8 @@ class MoELane:
 
     def dynamic_tiles(self, T):
         """Most GEMM tiles the expander can write for T tokens (form 16, ragged tails)."""
-        return (T * self.K // 16 + self.E) * (self.I // 64 + self.H // 128)
+        n = (T * self.K // 16 + self.E) * (self.I // 64 + self.H // 128)
+        return n + (self.E * self.fetch_tiles if self.staging is not None else 0)
 
     def build(self, T, iterations=1, mark_layer=0):
         """Upload the one-layer program for a batch of T tokens; returns its handle."""
@@ -202,8 +221,12 @@ class MoELane:
             p.after(s_lg, s_s13)
             p.after(s_s13, s_s2)
             p.after(s_s2, s_cb)
+        fetch = [p.stage(label=("fetch", mark_layer)) for _ in range(E)] if self.staging is not None else None
         for e in range(E):
             p.after(s_pm, w13[e])
+            if fetch:   # the copy into the staging stack starts as soon as the expert's row count is known
+                p.after(s_ex, fetch[e])
+                p.after(fetch[e], w13[e])
             p.after(w13[e], w2[e])
             p.after(w2[e], s_cb)
         dyn = self.dynamic_tiles(T)
@@ -213,6 +236,7 @@ class MoELane:
                     w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist, E=E, H=H, I=self.I,
                     host_region=REGION_HOST, w13_stage0=w13[0], w2_stage0=w2[0], red_stage0=0xffffffff,
                     dyn_first=p.dynamic_first, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb,
+                    staging=self.staging if self.staging is not None else 0, fetch_stage0=fetch[0] if fetch else 0,
                     chunks=-(-T // CHUNK), chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix,
                     red_args=self.expand_stamps, w13_scale=self.scales[0] if self.scales else 0,
                     w2_scale=self.scales[1] if self.scales else 0)

@@ -164,8 +164,12 @@ class ModelLane:
     as in the reference's lane (StepArgs, csrc/fabric/model_types.h:116-128)."""
 
     def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None,
-                 logit_rows=None, min_form=16):
+                 logit_rows=None, min_form=16, staged=False, staged_min_rows=256, fetch_chunk=256 * 1024):
+        """staged: under form 0 a host-resident expert with more than staged_min_rows rows is copied once
+        into this lane's HBM staging stack (one slot per expert, shared by all layers) by fetch tiles of
+        fetch_chunk bytes, and its GEMM tiles read the copy."""
         self.fab, self.lane_id, self.cfg, self.w, self.kv = fab, lane_id, cfg, weights, kv
+        self.staged, self.staged_min_rows, self.fetch_chunk = staged, staged_min_rows, fetch_chunk
         self.T, self.S, self.bt_stride, self.max_chunks = max_tokens, max_slots, bt_stride, max_chunks
         # rows of the lm_head (requests that continue; every row when a caller wants all logits), and the
         # smallest row-block height the published plans will use for host-resident experts
@@ -250,11 +254,26 @@ class ModelLane:
             self.m_hd = self._amaps(self.hd, T + 256, self.hd.shape[1])
         moe = [l for l in range(L) if w.host_w13[l] is not None]
         self.w13_maps, self.w2_maps = [None] * L, [None] * L
+        self.staging, self.fetch_tiles = [None] * L, 0
+        st13 = st2 = 0
+        if self.staged and moe:   # region 2: the staging stack, one slot per expert, the reference's row order
+            h13, h2 = w.host_w13[moe[0]], w.host_w2[moe[0]]
+            self.stage_w13 = torch.empty(h13.shape, dtype=h13.dtype, device="cuda")
+            self.stage_w2 = torch.empty(h2.shape, dtype=h2.dtype, device="cuda")
+            st13, st2 = self._wmap(self.stage_w13), self._wmap(self.stage_w2)
+            b13, b2 = h13[0].numel() * h13.element_size(), h2[0].numel() * h2.element_size()
+            self.fetch_tiles = -(-b13 // self.fetch_chunk) + -(-b2 // self.fetch_chunk)
         for l in moe:
             self.w13_maps[l] = _u64([self._wmap(w.host_w13[l], _C.host_device_pointer(w.host_w13[l].data_ptr())),
-                                     self._wmap(w.hot_w13[l], packed=True)])
+                                     self._wmap(w.hot_w13[l], packed=True), st13, 0])
             self.w2_maps[l] = _u64([self._wmap(w.host_w2[l], _C.host_device_pointer(w.host_w2[l].data_ptr())),
-                                    self._wmap(w.hot_w2[l])])
+                                    self._wmap(w.hot_w2[l]), st2, 0])
+            if st13:
+                self.staging[l] = _block(
+                    "StagingArgs", w13_src=_C.host_device_pointer(w.host_w13[l].data_ptr()),
+                    w13_dst=self.stage_w13.data_ptr(), w13_bytes=b13,
+                    w2_src=_C.host_device_pointer(w.host_w2[l].data_ptr()), w2_dst=self.stage_w2.data_ptr(),
+                    w2_bytes=b2, chunk_bytes=self.fetch_chunk, min_rows=self.staged_min_rows)
         self.xp_maps = _u64(self._amaps(self.xp, P + 256, H))
         self.h_maps = _u64(self._amaps(self.h, P + 256, I))
         a13, a2 = [], []
@@ -344,8 +363,12 @@ class ModelLane:
         w13 = [p.stage(label=("w13", l)) for _ in range(E)]
         w2 = [p.stage(label=("w2", l)) for _ in range(E)]
         s_cb = p.stage(self._rows(K_COMBINE, cb, T, per), mark=(l << 8) | 3, label=("combine", l))
+        fetch = [p.stage(label=("fetch", l)) for _ in range(E)] if self.staging[l] is not None else None
         for e in range(E):
             p.after(s_pm, w13[e])
+            if fetch:   # the copy into the staging stack starts as soon as the expert's row count is known
+                p.after(s_ex, fetch[e])
+                p.after(fetch[e], w13[e])
             p.after(w13[e], w2[e])
             p.after(w2[e], s_cb)
         if shared:   # the shared expert runs beside the routed chain and joins at the combine stage
@@ -357,25 +380,28 @@ class ModelLane:
             p.after(s_s13, s_s2)
             p.after(s_s2, s_cb)
         dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
-        expands.append((ex, l, T, w13[0], 0xffffffff, w2[0], s_cb, dyn))
+        if fetch:
+            dyn += E * self.fetch_tiles
+        expands.append((ex, l, T, w13[0], 0xffffffff, w2[0], s_cb, dyn, fetch[0] if fetch else 0))
         return s_cb
 
     def _finish_dynamic(self, p, expands, plans):
         """Hand each expand / plan tile its part of the dynamic region, now that every static tile is counted."""
         at = p.dynamic_first
-        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn in expands:
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0 in expands:
             p.reserve(dyn)
         for blob, fields, dyn in plans:
             p.reserve(dyn)
         cfg = self.cfg
         at = p.dynamic_first
-        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn in expands:
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0 in expands:
             blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.w.table[l],
                         w13_maps=self.w13_maps[l], w2_maps=self.w2_maps[l], xp_maps=self.xp_maps, h_maps=self.h_maps,
                         w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
                         I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
                         dyn_first=at, dyn_cap=dyn, lane=self.lane_id, join_stage=s_cb, chunks=-(-T // CHUNK),
                         chunk_counts=self.chunk_counts, chunk_prefix=self.chunk_prefix,
+                        staging=self.staging[l] if self.staging[l] is not None else 0, fetch_stage0=fetch_0,
                         w13_scale=self.w.w13_scale[l] if self.w.w13_scale[l] is not None else 0,
                         w2_scale=self.w.w2_scale[l] if self.w.w2_scale[l] is not None else 0)
             ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))

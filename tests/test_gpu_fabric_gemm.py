@@ -252,6 +252,68 @@ def test_fp8_expert_ffn(fab, where):
     del k1, k2
 
 
+def test_fetch_tiles_copy_host_memory_into_hbm(fab):
+    """Fetch tiles (kind 49) bring pinned host bytes into an HBM buffer through the operand ring, in
+    stages of 32 KB with a ragged last stage, interleaved on the same workers with GEMM tiles whose
+    output depends on the fetched weights (a GEMM stage after the fetch stage reads the copy)."""
+    torch.manual_seed(11)
+    E, N, K, M = 3, 256, 512, 96
+    w = (torch.randn(E, N, K) * 0.05).to(torch.bfloat16)
+    pin, alias = pinned_alias(w)
+    stage_buf = torch.zeros(E, N, K, dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(E, M, N, device="cuda", dtype=torch.bfloat16)
+    total = w.numel() * 2
+    chunk = 100 * 1024 + 48            # not a multiple of the 32 KB stage: ragged stages and a ragged last tile
+    fetch = [Tile(49, i=(min(chunk, total - at),), a=(alias + at, stage_buf.data_ptr() + at))
+             for at in range(0, total, chunk)]
+    wm, xm = weight_map(fab, stage_buf.data_ptr(), stage_buf.shape), act_map(fab, x, 128)
+    gemm = []
+    keep = []
+    for e in range(E):
+        a = args_tensor(out=out[e].data_ptr(), ld_out=N, k_tiles=K // 64, epi=EPI_STORE, bm=128, n_limit=N)
+        keep.append(a)
+        gemm += [Tile(KIND_GEMM, i=(n0, 0, M, e), a=(a.data_ptr(), wm, xm)) for n0 in range(0, N, 128)]
+    # a stage of GEMM tiles on weights that are already in HBM runs beside the fetch stage
+    wd = (torch.randn(1, 256, K, device="cuda") * 0.05).to(torch.bfloat16)
+    od = torch.zeros(M, 256, device="cuda", dtype=torch.bfloat16)
+    ad = args_tensor(out=od.data_ptr(), ld_out=256, k_tiles=K // 64, epi=EPI_STORE, bm=128, n_limit=256)
+    side = [Tile(KIND_GEMM, i=(n0, 0, M, 0), a=(ad.data_ptr(), weight_map(fab, wd.data_ptr(), wd.shape), xm))
+            for n0 in range(0, 256, 128)] * 6
+    p = Program()
+    s0 = p.stage([Tile(0)])
+    s_f = p.stage(fetch, link=True)
+    s_g = p.stage(gemm)
+    s_side = p.stage(side)
+    p.after(s0, s_f)
+    p.after(s0, s_side)
+    p.after(s_f, s_g)
+    run_program(fab, p, s0, caps=(4,))
+    assert torch.equal(stage_buf.cpu(), w), "the staged copy is the host tensor, byte for byte"
+    for e in range(E):
+        ref = x.float() @ w[e].float().cuda().t()
+        assert (out[e].float() - ref).abs().max().item() < 0.02 * ref.abs().max().item()
+    refd = x.float() @ wd[0].float().t()
+    assert (od.float() - refd).abs().max().item() < 0.02 * refd.abs().max().item()
+
+
+def test_bad_fetch_tile_is_reported(fab):
+    """A fetch tile whose size is not a multiple of 16 bytes is refused through the error word."""
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    pin = torch.zeros(4096, dtype=torch.uint8, pin_memory=True)
+    p = Program()
+    s = p.stage([Tile(49, i=(100,), a=(_C.host_device_pointer(pin.data_ptr()), buf.data_ptr()))])
+    h = p.upload(fab, first=s)
+    fab.start()
+    fab.publish(map=[0] * fab.num_workers, caps=[0], order=[0], programs=[h])
+    t0 = time.time()
+    while fab.progress()["lanes"][0]["iterations"] < 1:
+        assert time.time() - t0 < 30
+        time.sleep(1e-3)
+    fab.stop()
+    assert fab.progress()["error"] & 8
+
+
 def test_unsupported_gemm_tile_is_reported(fab):
     """A bad tile height is reported through the error word; the program still ends."""
     z = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)

@@ -84,6 +84,51 @@ def test_moe_layer_program(form, pack_hot):
         fab.close()
 
 
+@pytest.mark.parametrize("hot", ["none", "half"])
+def test_staged_form_reads_each_expert_once(hot):
+    """Form 0 with a staging stack: host-resident experts with more rows than the threshold are
+    copied into HBM by fetch tiles and computed from the copy.  The result is bit-identical to the
+    unstaged form-0 run (same 256-row blocks over the same bytes), and routing and packing stay
+    bit-exact against the oracle."""
+    from monoserve_b200.fabric import Fabric
+    from monoserve_b200.lane import MoELane
+    T, H, I, E, K = 900, 512, 256, 8, 2     # ~225 rows per expert; threshold 200: most are staged, some not
+    wr, w13, w2 = weights(H, I, E, 5)
+    xn, x2 = acts(T, H, 6)
+    hot_list = [] if hot == "none" else list(range(0, E, 2))
+    outs = []
+    for staged in (False, True):
+        fab = Fabric(pool_bytes=128 << 20)
+        fab.set_max_run(60)
+        try:
+            lane = MoELane(fab, 0, H, I, E, K, 1024, wr, w13, w2, hot=hot_list, staged=staged, staged_min_rows=200,
+                           fetch_chunk=96 * 1024)
+            lane.set_input(xn.cuda(), x2.cuda())
+            h = lane.build(T, iterations=2)
+            fab.start()
+            fab.publish(map=[0] * fab.num_workers, caps=[4], order=[0], programs=[h], forms=[0])
+            wait_iterations(fab, 0, 2)
+            stats = fab.lane_stats(0)
+            fab.stop()
+            assert fab.progress()["error"] == 0
+            assert stats["inflight_max"] <= 4
+            if staged:
+                check_lane(lane, wr, w13, w2, xn, x2, K)
+                counts = np.diff(lane.starts.cpu().numpy())
+                cold = [e for e in range(E) if e not in hot_list]
+                assert any(counts[e] > 200 for e in cold) and any(counts[e] <= 200 for e in range(E))
+                for e in cold:
+                    if counts[e] > 200:   # the staged copy of an expert is its host tensor
+                        assert torch.equal(lane.stage_w13[e].cpu(), w13[e])
+                        assert torch.equal(lane.stage_w2[e].cpu(), w2[e])
+            outs.append((lane.x[:T].cpu().clone(), lane.y[:T * K].cpu().clone()))
+        finally:
+            fab.stop()
+            fab.close()
+    assert torch.equal(outs[0][1], outs[1][1]), "expert outputs: staged == unstaged, bit for bit"
+    assert torch.equal(outs[0][0], outs[1][0])
+
+
 def test_prefill_and_decode_lanes_side_by_side():
     from monoserve_b200.fabric import Fabric
     from monoserve_b200.lane import MoELane
