@@ -6,7 +6,7 @@ persistent fabric kernel, half of every layer's experts in the HBM hot tier and 
 pinned host memory.
 
     python -m monoserve_b200.benchmarks.mixed_lane [--layers 48] [--distinct 48] [--decode 128]
-        [--prompts 4] [--prompt-len 2048] [--hot 64] [--sm-decode 74] [--caps 4,4] [--forms 64,0]
+        [--prompts 4] [--prompt-len 2048] [--hot 64] [--sm-decode 74] [--caps 4,4] [--forms 64,0] [--no-staged]
         [--steps 8] [--decode-only] [--quick]
 
 Reported (one JSON line): decode TPOT p50 = median of the decode lane's iteration end-time deltas
@@ -26,8 +26,10 @@ of pinned host memory, 29 GB of hot tier and 57 GB of KV cache in HBM.  `--disti
 distinct layers' weights and cycles them over the layers, for hosts with less memory (every layer still
 streams its own experts' bytes per step: one layer's hot tier, 604 MB, is far larger than the 126 MB
 L2); the output states it.  The default plan (74 + 74 SMs, 4 + 4 link credits, row-block form 64 for the
-decode lane and the one-pass form for the prefill lane) is one point of the plan space the reference's
-control plane searches; other points are a flag away.
+decode lane and form 0 for the prefill lane, where a host-resident expert with more than 256 rows is
+copied once into the lane's HBM staging stack and computed from there; `--no-staged` reads every
+256-row block over the link instead) is one point of the plan space the reference's control plane
+searches; other points are a flag away.
 """
 import argparse
 import json
@@ -147,8 +149,9 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--decode-only", action="store_true", help="no prefill lane: every SM decodes")
-    ap.add_argument("--staged", action="store_true",
-                    help="prefill lane: experts with more than 256 rows go through the HBM staging stack (form 0)")
+    ap.add_argument("--no-staged", dest="staged", action="store_false",
+                    help="prefill lane: read every 256-row block of a host-resident expert over the link instead of "
+                         "copying experts with more than 256 rows once into the HBM staging stack (form 0)")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
     glm = args.model == "glm"
