@@ -28,9 +28,10 @@ def load_fixture():
     return cfg, w, g["tokens"].tolist(), torch.from_numpy(g["logits"])
 
 
-def run_once(fab, handle, caps=(4,), timeout=30):
+def run_once(fab, handle, caps=(4,), timeout=30, forms=None):
     before = fab.progress()["lanes"][0]["iterations"]
-    fab.publish(map=[0] * fab.num_workers, caps=list(caps), order=[0], programs=[handle])
+    fab.publish(map=[0] * fab.num_workers, caps=list(caps), order=[0], programs=[handle],
+                **({"forms": list(forms)} if forms else {}))
     t0 = time.time()
     while fab.progress()["lanes"][0]["iterations"] < before + 1:
         assert time.time() - t0 < timeout, (fab.progress()["error"], fab.wait_notes())
@@ -82,19 +83,25 @@ def fab():
     f.close()
 
 
-@pytest.mark.parametrize("placement", ["all_hot", "half_host"])
+@pytest.mark.parametrize("placement", ["all_hot", "half_host", "half_host_staged"])
 def test_prefill_logits_match_reference(fab, placement):
+    """half_host_staged: form 0 with a staging stack and a threshold of 4 rows, so that most host-resident
+    experts of both layers go through fetch tiles and the shared staging stack before their GEMM tiles."""
     from monoserve_b200.model import KVCache, ModelLane, ModelWeights
     cfg, w, tokens, ref = load_fixture()
     hot = None if placement == "all_hot" else [list(range(l % 2, cfg.num_experts, 2)) for l in range(cfg.num_layers)]
     weights = ModelWeights(cfg, w, hot=hot)
     kv = KVCache(cfg, n_pages=16, page_size=16)
-    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8)
+    staged = placement == "half_host_staged"
+    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8, staged=staged,
+                     staged_min_rows=4, fetch_chunk=48 * 1024)
     lane.set_pages(1, [3, 1, 2])
     h = lane.build_prefill([(1, tokens, 0)], all_logits=True)
     fab.start()
-    run_once(fab, h)
+    run_once(fab, h, forms=[0] if staged else None)
     fab.stop()
+    if staged:
+        assert int((lane.hist[:, :] > 4).sum()) > 0, "some expert passed the staging threshold"
     check_logits(lane.logits[:len(tokens)].cpu(), ref)
     # the request's next token is the arg-max of its last row
     assert int(lane.last_token[1]) == int(lane.logits[len(tokens) - 1].argmax())
