@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
       if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
       if (!sh.work[slot].valid) break;
       trace_ev(p, 1, it, 0);
-      if (!gemm_produce(sh.work[slot], ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x)) break;
+      if (!gemm_produce<false>(sh.work[slot], ring, sh.bar, pipe, inflight, abort_flag, pol_w, pol_x)) break;
       trace_ev(p, 1, it, 1);
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.work_empty[slot]);
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
       if (!sh.work[slot].valid) break;
       trace_ev(p, 2, it, 0);
       long long waited[2] = {0, 0};
-      if (!gemm_mma(sh.work[slot], ring, sh.bar, pipe, tmem_base, buf, (it >> 1) & 1, abort_flag,
+      if (!gemm_mma<false>(sh.work[slot], ring, sh.bar, pipe, tmem_base, buf, (it >> 1) & 1, abort_flag,
                     p.trace ? waited : nullptr))
         break;
       trace_ev(p, 2, it, 1);
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
       if (warp == 2) trace_ev(p, 3, it, 0);
       unsigned long long* seen =
           (p.trace && blockIdx.x == 0 && warp == 2 && it < 32) ? &p.trace[(3 * 32 + it) * 4 + 3] : nullptr;
-      if (!gemm_epilogue(w, sh.bar, tmem_base, buf, (it >> 1) & 1, abort_flag, seen)) break;
+      if (!gemm_epilogue<false>(w, sh.bar, tmem_base, buf, (it >> 1) & 1, abort_flag, seen)) break;
       if (warp == 2) trace_ev(p, 3, it, 1);
       if (w.block >= 0) {
         // publish this warp's part of h, then count it into the row block

@@ -125,16 +125,19 @@ struct GemmInflight {
 // (64-byte reads reach 42 GB/s, 128-byte reads 51 GB/s).
 constexpr uint32_t kFetchStageBytes = 32 * 1024;
 __device__ __forceinline__ int gemm_ksteps(const GemmWork& w) { return w.w_fp8 ? 2 : 1; }
+// kFetch = false (a kernel that never sees fetch records) compiles their handling away.
+template <bool kFetch = true>
 __device__ __forceinline__ int gemm_stage_count(const GemmWork& w) {
-  if (w.fetch) return static_cast<int>((w.fetch_bytes + kFetchStageBytes - 1) / kFetchStageBytes);
+  if (kFetch && w.fetch) return static_cast<int>((w.fetch_bytes + kFetchStageBytes - 1) / kFetchStageBytes);
   return w.w_fp8 ? (w.k_tiles + 1) >> 1 : w.k_tiles;
 }
 // Bytes of one stage: per K step the bf16 weight tile and the activation tile; layout: weight tiles,
 // then activation tiles.  The raw e4m3 tile (128 rows of 128 bytes) lands in the second weight tile
 // and is expanded in place: the 128-byte swizzle permutes 16-byte chunks inside a row, so row r of the
 // second K step's bf16 tile covers exactly the bytes of raw row r, which one converter thread owns.
+template <bool kFetch = true>
 __device__ __forceinline__ uint32_t gemm_stage_bytes(const GemmWork& w) {
-  if (w.fetch) return kFetchStageBytes;
+  if (kFetch && w.fetch) return kFetchStageBytes;
   return gemm_ksteps(w) * (kATileBytes + w.n * kBlockK * 2);
 }
 
@@ -163,18 +166,19 @@ __device__ __forceinline__ void gemm_barriers_init(GemmBarriers& b) {
 // out as a single warp-wide instruction (lanes 0..7 the weight boxes, lane 8 the
 // activation box), which costs one issue slot instead of nine.
 // Returns false when a wait was abandoned.
+template <bool kFetch = true>
 __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
                                              GemmInflight& fl, volatile int* abort_flag, uint64_t pol_w,
                                              uint64_t pol_x) {
   const int lane = threadIdx.x & 31;
-  const uint32_t size = gemm_stage_bytes(w);
+  const uint32_t size = gemm_stage_bytes<kFetch>(w);
   const uint32_t b_bytes = w.n * kBlockK * 2;
   const int ks = gemm_ksteps(w);
   // FP8 weights land as raw bytes in the second weight tile (128-byte rows = two K steps, no swizzle)
   const uint32_t a_off = w.w_fp8 ? kATileBytes : 0;
   const uint32_t a_box = 2048;   // bytes of one 16-row box: 128-byte rows either way
   const uint32_t b_off = ks * kATileBytes;
-  const int n_stages = gemm_stage_count(w);
+  const int n_stages = gemm_stage_count<kFetch>(w);
   // SwiGLU tiles of a tensor in the reference row order gather eight 16-row boxes;
   // every other tile is one 128-row box (a packed SwiGLU tensor stores gate/up
   // groups of 16 rows alternately, so its tile starts at row 2 * a_row_lo).
@@ -182,6 +186,14 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
   const int a_row = gather ? ((lane & 1) ? w.a_row_hi : w.a_row_lo) + 16 * ((lane & 7) >> 1)
                            : (w.epi == kEpiSiluMul ? 2 * w.a_row_lo : w.a_row_lo);
   const int n_a = gather ? 8 : 1;
+  // read once: the record lives in shared memory and every copy below is a memory barrier to the compiler
+  const bool fetch = kFetch && w.fetch != 0;
+  const uint32_t fetch_bytes = kFetch ? w.fetch_bytes : 0;
+  const uint8_t* const fetch_src = kFetch ? w.fetch_src : nullptr;
+  const CUtensorMap* const a_map = w.a_map;
+  const CUtensorMap* const b_map = w.b_map;
+  const int a_z = w.a_z, b_row0 = w.b_row0, k0 = w.k0;
+  const uint32_t tx_bytes = kATileBytes + ks * b_bytes;
   for (int st = 0; st < n_stages; ++st) {
     uint32_t vb, ve;
     const uint32_t phys = pipe.alloc(size, vb, ve);
@@ -198,25 +210,25 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
     fl.vbegin[slot] = vb;
     uint8_t* a = ring + phys;
     uint64_t* full = &bar.full[slot];
-    if (w.fetch) {
+    if (fetch) {
       if (lane == 0) {
         const uint32_t at = st * kFetchStageBytes;
-        const uint32_t bytes = min(kFetchStageBytes, w.fetch_bytes - at);
+        const uint32_t bytes = min(kFetchStageBytes, fetch_bytes - at);
         mbar_arrive_expect_tx(full, bytes);
-        bulk_load(a, w.fetch_src + at, bytes, full, pol_w);
+        bulk_load(a, fetch_src + at, bytes, full, pol_w);
       }
       __syncwarp();
       pipe.advance();
       continue;
     }
     // a K step past the end of an odd K range reads zeros (out-of-bounds fill) and adds nothing
-    if (lane == 0) mbar_arrive_expect_tx(full, kATileBytes + ks * b_bytes);
+    if (lane == 0) mbar_arrive_expect_tx(full, tx_bytes);
     __syncwarp();
-    const int x = (w.k0 + st * ks) * kBlockK;
+    const int x = (k0 + st * ks) * kBlockK;
     if (lane < n_a) {
-      tma_load_3d(a + a_off + lane * a_box, w.a_map, full, x, a_row, w.a_z, pol_w);
+      tma_load_3d(a + a_off + lane * a_box, a_map, full, x, a_row, a_z, pol_w);
     } else if (lane >= 8 && lane < 8 + ks) {
-      tma_load_2d(a + b_off + (lane - 8) * b_bytes, w.b_map, full, x + (lane - 8) * kBlockK, w.b_row0, pol_x);
+      tma_load_2d(a + b_off + (lane - 8) * b_bytes, b_map, full, x + (lane - 8) * kBlockK, b_row0, pol_x);
     }
     pipe.advance();
   }
@@ -227,6 +239,7 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
 // it, but lane 0 alone runs the K loop (wait for a stage, four tcgen05.mma, one
 // commit): nothing in the loop needs the other lanes, and a warp-wide barrier per
 // stage would only add to the issue path, which is what bounds small-N tiles.
+template <bool kFetch = true>
 __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmBarriers& bar, GemmPipe& pipe,
                                          uint32_t tmem_base, int buf, uint32_t acc_parity, volatile int* abort_flag,
                                          long long* wait_cycles = nullptr) {
@@ -237,27 +250,31 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
     tc_fence_after_sync();
     const uint32_t idesc = umma_idesc_bf16(128, w.n);
     const uint32_t acc = tmem_base + buf * kAccCols;
-    const uint32_t size = gemm_stage_bytes(w);
+    const uint32_t size = gemm_stage_bytes<kFetch>(w);
     uint64_t* ready = w.w_fp8 ? bar.conv : bar.full;
     const uint32_t ring_addr = smem_u32(ring);
     const uint64_t desc0 = umma_desc_sw128(0);
-    const int ks = gemm_ksteps(w), n_stages = gemm_stage_count(w);
+    const int n_stages = gemm_stage_count<kFetch>(w);
     const uint32_t b_bytes = w.n * kBlockK * 2;
+    // read once: the record lives in shared memory and every wait below is a memory barrier to the compiler
+    const bool fp8 = w.w_fp8 != 0, fetch = kFetch && w.fetch != 0;
+    const uint32_t fetch_bytes = kFetch ? w.fetch_bytes : 0;
+    uint8_t* const fetch_out = static_cast<uint8_t*>(w.out);
     for (int kt = 0; ok && kt < n_stages; ++kt) {
       uint32_t vb, ve;
       const uint32_t phys = pipe.alloc(size, vb, ve);
       const long long tw = wait_cycles ? clock64() : 0;
-      const uint32_t ready_parity = w.w_fp8 ? (pipe.conv_bits >> pipe.slot) & 1u : pipe.parity;
+      const uint32_t ready_parity = fp8 ? (pipe.conv_bits >> pipe.slot) & 1u : pipe.parity;
       if (!mbar_wait_bounded(&ready[pipe.slot], ready_parity, abort_flag, kWaitBudgetNs)) {
         ok = 0;
         break;
       }
-      if (w.w_fp8) pipe.conv_bits ^= 1u << pipe.slot;
+      if (fp8) pipe.conv_bits ^= 1u << pipe.slot;
       if (wait_cycles) wait_cycles[0] += clock64() - tw;
-      if (w.fetch) {
+      if (fetch) {
         // the stage goes on to the staging buffer; its shared memory is free once the store has read it
         const uint32_t at = kt * kFetchStageBytes;
-        bulk_store(static_cast<uint8_t*>(w.out) + at, ring + phys, min(kFetchStageBytes, w.fetch_bytes - at));
+        bulk_store(fetch_out + at, ring + phys, min(kFetchStageBytes, fetch_bytes - at));
         bulk_commit();
         bulk_wait_read_all();
         mbar_arrive(&bar.empty[pipe.slot]);
@@ -265,17 +282,25 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
         continue;
       }
       const long long ti = wait_cycles ? clock64() : 0;
-      for (int h = 0; h < ks; ++h) {   // the K steps of the stage
-        const uint64_t da = desc0 + ((ring_addr + phys + h * kATileBytes) >> 4);
-        const uint64_t db = desc0 + ((ring_addr + phys + ks * kATileBytes + h * b_bytes) >> 4);
+      if (!fp8) {   // one K step: weight tile, activation tile
+        const uint64_t da = desc0 + ((ring_addr + phys) >> 4);
+        const uint64_t db = da + (kATileBytes >> 4);
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | h | k) != 0);
+        for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+      } else {      // two K steps: weight tiles 0 and 1, then activation tiles 0 and 1
+        const uint64_t da = desc0 + ((ring_addr + phys) >> 4);
+        const uint64_t db = da + (2 * kATileBytes >> 4);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k)
+          umma_bf16(acc, da + (kATileBytes >> 4) + 2 * k, db + (b_bytes >> 4) + 2 * k, idesc, true);
       }
       umma_commit(&bar.empty[pipe.slot]);
       if (wait_cycles) wait_cycles[1] += clock64() - ti;
       pipe.advance();
     }
-    if (ok && w.fetch) {
+    if (ok && fetch) {
       // the record counts as done when its bytes are in the staging buffer, for readers of either proxy
       bulk_wait_all();
       fence_proxy_async_all();
@@ -351,6 +376,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(
 
 // Epilogue of one tile from accumulator buffer `buf` (the four epilogue warps
 // call): everything except handing the buffer back to the MMA warp.
+template <bool kFetch = true>
 __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
                                                    uint32_t acc_parity, volatile int* abort_flag,
                                                    unsigned long long* acc_seen = nullptr) {
@@ -358,7 +384,7 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
   if (!mbar_wait_bounded(&bar.acc_full[buf], acc_parity, abort_flag, kWaitBudgetNs)) return false;
   tc_fence_after_sync();
   if (acc_seen && lane == 0) *acc_seen = globaltimer_ns();
-  if (w.fetch) {   // nothing to drain: the MMA warp has already moved the bytes
+  if (kFetch && w.fetch) {   // nothing to drain: the MMA warp has already moved the bytes
     __syncwarp();
     return true;
   }
@@ -460,10 +486,11 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
   return true;
 }
 
+template <bool kFetch = true>
 __device__ __forceinline__ bool gemm_epilogue(const GemmWork& w, GemmBarriers& bar, uint32_t tmem_base, int buf,
                                               uint32_t acc_parity, volatile int* abort_flag,
                                               unsigned long long* acc_seen = nullptr) {
-  if (!gemm_epilogue_body(w, bar, tmem_base, buf, acc_parity, abort_flag, acc_seen)) return false;
+  if (!gemm_epilogue_body<kFetch>(w, bar, tmem_base, buf, acc_parity, abort_flag, acc_seen)) return false;
   if ((threadIdx.x & 31) == 0) mbar_arrive(&bar.acc_empty[buf]);
   return true;
 }
