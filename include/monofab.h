@@ -333,6 +333,46 @@ int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* 
  * counterpart in the reference, whose weights have one row order. */
 int monofab_fabric_tensor_map_packed(monofab_fabric* f, uint64_t handle, int packed);
 
+/* ------------------------------------------------------------------ host loop
+ * A host thread that follows the lanes' marks ((layer << 8) | phase: 1 attention
+ * window, 2 MoE window, 3 layer done) in the fabric's pinned mirror and stages
+ * host-resident experts into a lane's HBM staging buffer with the copy engine, one
+ * expert at a time on its own stream, ahead of the layer that uses them; when an
+ * expert has landed, its entry in the lane's (region, slot) table int32
+ * [layers][experts][2] is switched with one aligned 8-byte copy, and switched back to
+ * (host_region, expert) when the layer is done (class HostLoop,
+ * csrc/host/host_loop.h:25-90, csrc/host/host_loop.cpp:18-160, bound at
+ * csrc/bindings.cpp:306-330).
+ *
+ * host_w13 / host_w2: per layer, the HOST address of the pinned [experts][...] stack,
+ * 0 for a layer without experts.  A loop created with fab = NULL makes no CUDA call:
+ * its marks are injected, it is stepped by hand and its actions are read back as a log
+ * (for tests of the staging policy on a machine without a GPU). */
+typedef struct monofab_host_loop monofab_host_loop;
+int monofab_host_loop_create(monofab_fabric* fab, int layers, int experts, size_t w13_bytes, size_t w2_bytes,
+                             const uint64_t* host_w13, const uint64_t* host_w2, int host_region,
+                             monofab_host_loop** out);
+/* A lane to stage for (HostLoop::add_lane, csrc/host/host_loop.cpp:33-40;
+ * StagingLaneConfig, csrc/host/host_loop.h:27-34): region = the region id of the lane's
+ * staging buffer, w13_dst / w2_dst = its [2 * slots] expert slots (two halves of `slots`),
+ * tables = device address of the lane's tables, order = experts to stage per layer, best
+ * first, concatenated, layer l being order[order_offsets[l] .. order_offsets[l + 1]). */
+int monofab_host_loop_add_lane(monofab_host_loop* h, int lane, int region, uint64_t w13_dst, uint64_t w2_dst,
+                               int slots, uint64_t tables, const int32_t* order, const int32_t* order_offsets);
+/* HostLoop::start / stop (csrc/host/host_loop.cpp:42-51); stop gives every half back. */
+int monofab_host_loop_start(monofab_host_loop* h, int poll_us);
+int monofab_host_loop_stop(monofab_host_loop* h);
+/* copies, bytes, flips, restores, polls (HostLoopStats, csrc/host/host_loop.h:36-38). */
+int monofab_host_loop_stats(monofab_host_loop* h, uint64_t out[5]);
+int monofab_host_loop_destroy(monofab_host_loop* h);
+/* Loops without a fabric only (no counterpart in the reference): set the mirror words of
+ * the lane added `lane_index`-th, run one poll of every lane (a copy lands two polls after
+ * it was issued), read the actions so far as records of five int32: kind (0 copy issued,
+ * 1 entry switched to the staging buffer, 2 entry switched back), lane, layer, expert, slot. */
+int monofab_host_loop_inject(monofab_host_loop* h, int lane_index, uint64_t mark, uint64_t gen, uint64_t running);
+int monofab_host_loop_step(monofab_host_loop* h);
+int monofab_host_loop_log(monofab_host_loop* h, int32_t* out, int cap, int* n);
+
 #ifdef __cplusplus
 }
 #endif

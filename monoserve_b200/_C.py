@@ -27,6 +27,9 @@ EXPORTS = [
     "monofab_fabric_reset_inflight_max", "monofab_fabric_wait_notes", "monofab_fabric_read", "monofab_fabric_write", "monofab_fabric_blob_alloc",
     "monofab_fabric_blob_free", "monofab_fabric_set_trace", "monofab_fabric_trace_count",
     "monofab_fabric_worker_tiles", "monofab_fabric_iteration_times", "monofab_fabric_tensor_map", "monofab_fabric_tensor_map_packed",
+    "monofab_host_loop_create", "monofab_host_loop_add_lane", "monofab_host_loop_start", "monofab_host_loop_stop",
+    "monofab_host_loop_stats", "monofab_host_loop_destroy", "monofab_host_loop_inject", "monofab_host_loop_step",
+    "monofab_host_loop_log",
 ]
 
 
@@ -100,6 +103,15 @@ def _load():
     lib.monofab_fabric_iteration_times.argtypes = [vp, i32, u64, i32, ctypes.c_double, vp]
     lib.monofab_fabric_tensor_map.argtypes = [vp, u64, vp, vp, vp, i32, i32, i32, P(u64)]
     lib.monofab_fabric_tensor_map_packed.argtypes = [vp, u64, i32]
+    lib.monofab_host_loop_create.argtypes = [vp, i32, i32, ctypes.c_size_t, ctypes.c_size_t, vp, vp, i32, P(vp)]
+    lib.monofab_host_loop_add_lane.argtypes = [vp, i32, i32, u64, u64, i32, u64, vp, vp]
+    lib.monofab_host_loop_start.argtypes = [vp, i32]
+    lib.monofab_host_loop_stop.argtypes = [vp]
+    lib.monofab_host_loop_stats.argtypes = [vp, vp]
+    lib.monofab_host_loop_destroy.argtypes = [vp]
+    lib.monofab_host_loop_inject.argtypes = [vp, i32, u64, u64, u64]
+    lib.monofab_host_loop_step.argtypes = [vp]
+    lib.monofab_host_loop_log.argtypes = [vp, vp, i32, P(i32)]
     return lib
 
 

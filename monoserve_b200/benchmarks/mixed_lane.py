@@ -152,6 +152,9 @@ def main():
     ap.add_argument("--no-staged", dest="staged", action="store_false",
                     help="prefill lane: read every 256-row block of a host-resident expert over the link instead of "
                          "copying experts with more than 256 rows once into the HBM staging stack (form 0)")
+    ap.add_argument("--host-loop", type=int, default=0, metavar="SLOTS",
+                    help="run the host loop beside the fabric: the copy engine stages up to SLOTS host-resident "
+                         "experts of the prefill lane's coming layer into an HBM staging buffer (two halves)")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
     glm = args.model == "glm"
@@ -171,6 +174,8 @@ def main():
     rng = np.random.default_rng(0)
     hot = [sorted(rng.permutation(cfg.num_experts)[:args.hot].tolist()) for _ in range(cfg.num_layers)]
     weights = ModelWeights(cfg, w, hot=hot)
+    if args.host_loop and not args.decode_only:
+        weights.alloc_staging(2 * args.host_loop)
     page = args.page
     ctx = rng.integers(args.ctx_lo, args.ctx_hi + 1, size=args.decode).tolist()
     grow = args.steps + 16
@@ -199,7 +204,8 @@ def main():
     if not args.decode_only:
         T = args.prompts * args.prompt_len
         pre = ModelLane(fab, 1, cfg, weights, kv, max_tokens=T, max_slots=args.prompts, bt_stride=bt_stride,
-                        logit_rows=args.prompts, min_form=min_form, staged=args.staged)
+                        logit_rows=args.prompts, min_form=min_form, staged=args.staged,
+                        staging_index=0 if args.host_loop else None)
         batch = []
         for s in range(args.prompts):
             pre.set_pages(s, perm[at - 1:at - 1 + pages_pre].tolist())
@@ -207,9 +213,16 @@ def main():
             batch.append((s, rng.integers(0, cfg.vocab, size=args.prompt_len).tolist(), 0))
         programs.append(pre.build_prefill(batch, iterations=0))
         lanes_map = [0] * args.sm_decode + [1] * (fab.num_workers - args.sm_decode)
+    loop = None
+    if args.host_loop and pre is not None:
+        from monoserve_b200.host_loop import HostLoop
+        loop = HostLoop(fab, weights)
+        loop.add_prefill_lane(pre, 0)
     torch.cuda.synchronize()
     t_setup = time.time() - t_setup
     fab.start()
+    if loop is not None:
+        loop.start(poll_us=5)
     fab.publish(map=lanes_map, caps=caps[:len(programs)], order=list(range(len(programs))), programs=programs,
                 forms=forms[:len(programs)])
     warm = 2
@@ -218,6 +231,10 @@ def main():
     prog = fab.progress()
     err = prog["error"]
     notes = fab.wait_notes() if err else {}
+    loop_stats = None
+    if loop is not None:
+        loop.stop()
+        loop_stats = loop.stats()
     fab.stop()
     torch.cuda.synchronize()
     deltas = np.diff(np.array(ends[warm - 1:], dtype=np.float64)) * 1e-6    # ms per decode step
@@ -266,6 +283,10 @@ def main():
         line["prefill_link_bytes_per_iteration"] = pre_link
         link_rate += pre_link / (pre_ms * 1e-3)
     line["host_link_gbs"] = link_rate / 1e9
+    if loop_stats is not None:
+        # experts the copy engine staged are read from HBM by the prefill lane: the figure above counts them
+        # as link reads of the kernel, so with the host loop it is an upper bound of the kernel's own reads
+        line["host_loop"] = dict(loop_stats, slots_per_half=args.host_loop)
     if notes:
         line["wait_notes"] = {str(k): v for k, v in list(notes.items())[:4]}
     print(json.dumps(line))

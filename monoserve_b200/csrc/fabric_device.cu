@@ -1115,15 +1115,18 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   };
   for (int e = tid; e < E; e += kExecThreads) {
     const int M = s_cnt[e];
-    const int region = table[2 * e], slot = table[2 * e + 1];
+    // One 8-byte read, once per layer: a host thread may move the expert between regions with a
+    // single aligned 8-byte write while the kernel runs (staging by the copy engine).
+    const unsigned long long entry = ld_volatile(reinterpret_cast<const unsigned long long*>(table) + e);
+    const int region = static_cast<int>(entry & 0xffffffffu), slot = static_cast<int>(entry >> 32);
     const bool link = region == static_cast<int>(A.host_region);
     const bool staged = link && can_stage && s_form == 0 && M > static_cast<int>(G.min_rows);
     const int bm = block_rows(M, link);
     int cls = 0;
     while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
     s_n[e] = M > 0 ? ((M + bm - 1) / bm) * (f13 + f2) + (staged ? nf13 + nf2 : 0) : 0;
-    // a staged expert's GEMM tiles read region 2 (the staging stack), slot = expert id
-    s_info[e] = staged ? (e << 12) | (1 << 11) | (2 << 4) | cls : (slot << 12) | ((region & 0x7f) << 4) | cls;
+    // a staged expert's GEMM tiles read region 3 (the lane's staging stack), slot = expert id
+    s_info[e] = staged ? (e << 12) | (1 << 11) | (3 << 4) | cls : (slot << 12) | ((region & 0x7f) << 4) | cls;
   }
   if (tid < 5) {
     s_tab[tid] = reinterpret_cast<const unsigned long long*>(A.w13_args)[tid];
@@ -1227,19 +1230,16 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   }
   for (int e = tid; e < E; e += kExecThreads) {
     const int M = s_overflow ? 0 : s_cnt[e];
-    const int region = table[2 * e];
-    const bool link = region == static_cast<int>(A.host_region);
+    const bool link = ((s_info[e] >> 4) & 0x7f) == static_cast<int>(A.host_region);   // the entry as read above
     const uint32_t base = A.dyn_first + s_off[e];
     StageStatic& s13 = p_stages[A.w13_stage0 + e];
     StageStatic& s2 = p_stages[A.w2_stage0 + e];
-    const int bm = block_rows(M, link);
-    int cls = 0;
-    while ((16 << cls) < bm) ++cls;   // 16, 32, 64, 128, 256 -> 0..4
+    const int bm = 16 << (s_info[e] & 0xf);   // the height chosen above
     const int blocks = M > 0 ? (M + bm - 1) / bm : 0;
     const int n13 = blocks * f13, n2 = blocks * f2;
     const bool staged = M > 0 && ((s_info[e] >> 11) & 1);
     const int nf = staged ? nf13 + nf2 : 0;
-    const uint32_t gemm_flags = (link && !staged) ? kStageLink : 0u;   // staged: only the fetch tiles use the link
+    const uint32_t gemm_flags = link ? kStageLink : 0u;   // staged (region 3): only the fetch tiles use the link
     const bool skip = M == 0 && active > 0;   // an unrouted expert: its chain is passed over
     if (A.staging) {
       StageStatic& sf = p_stages[A.fetch_stage0 + e];

@@ -73,6 +73,12 @@ struct monofab_fabric {
 };
 
 namespace mf {
+// for the host loop (host_loop.cu)
+const fab::HostMirror* fabric_mirror(const monofab_fabric* f) { return f->mirror; }
+int fabric_device(const monofab_fabric* f) { return f->device; }
+}  // namespace mf
+
+namespace mf {
 
 static bool pool_alloc(monofab_fabric* f, size_t bytes, size_t align, size_t* off) {
   bytes = (bytes + 63) & ~size_t(63);

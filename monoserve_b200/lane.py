@@ -101,10 +101,10 @@ class MoELane:
         m2 = [wmap(self.host_w2, _C.host_device_pointer(self.host_w2.data_ptr())),
               wmap(self.hot_w2, self.hot_w2.data_ptr()), 0, 0]
         self.staging = None
-        if staged:   # region 2: the staging stack, one slot per expert, the reference's row order
+        if staged:   # region 3: the lane's staging stack, one slot per expert, the reference's row order
             self.stage_w13 = torch.empty(self.host_w13.shape, dtype=self.host_w13.dtype, device=dev)
             self.stage_w2 = torch.empty(self.host_w2.shape, dtype=self.host_w2.dtype, device=dev)
-            m13[2], m2[2] = wmap(self.stage_w13, self.stage_w13.data_ptr()), wmap(self.stage_w2, self.stage_w2.data_ptr())
+            m13[3], m2[3] = wmap(self.stage_w13, self.stage_w13.data_ptr()), wmap(self.stage_w2, self.stage_w2.data_ptr())
             b13 = self.host_w13[0].numel() * self.host_w13.element_size()
             b2 = self.host_w2[0].numel() * self.host_w2.element_size()
             self.fetch_tiles = -(-b13 // fetch_chunk) + -(-b2 // fetch_chunk)

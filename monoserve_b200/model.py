@@ -143,6 +143,24 @@ class ModelWeights:
                 table[idx, 0] = REGION_HOT
                 table[idx, 1] = torch.arange(len(self.hot[l]), dtype=torch.int32)
             self.table[l] = table.cuda()
+        self.stage_w13, self.stage_w2, self.staging_slots = [], [], 0
+
+    def expert_bytes(self):
+        """(bytes of one expert's w13 block, of its w2 block) (monoserve/runtime/weights.py)."""
+        l = next(i for i, t in enumerate(self.host_w13) if t is not None)
+        return (self.host_w13[l][0].numel() * self.host_w13[l].element_size(),
+                self.host_w2[l][0].numel() * self.host_w2[l].element_size())
+
+    def alloc_staging(self, slots, buffers=1):
+        """Staging buffers in HBM for the host loop (regions 2, 3 ...): each holds `slots` experts in
+        the reference's row order, in two halves of slots // 2 (one layer's worth each)
+        (monoserve/runtime/weights.py: stage_w13 / stage_w2 / staging_slots)."""
+        l = next(i for i, t in enumerate(self.host_w13) if t is not None)
+        h13, h2 = self.host_w13[l], self.host_w2[l]
+        self.staging_slots = slots
+        for _ in range(buffers):
+            self.stage_w13.append(torch.zeros((slots,) + tuple(h13.shape[1:]), dtype=h13.dtype, device="cuda"))
+            self.stage_w2.append(torch.zeros((slots,) + tuple(h2.shape[1:]), dtype=h2.dtype, device="cuda"))
 
 
 class KVCache:
@@ -164,12 +182,23 @@ class ModelLane:
     as in the reference's lane (StepArgs, csrc/fabric/model_types.h:116-128)."""
 
     def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None,
-                 logit_rows=None, min_form=16, staged=False, staged_min_rows=256, fetch_chunk=256 * 1024):
-        """staged: under form 0 a host-resident expert with more than staged_min_rows rows is copied once
+                 logit_rows=None, min_form=16, staged=False, staged_min_rows=256, fetch_chunk=256 * 1024,
+                 staging_index=None):
+        """staging_index: the weights' staging buffer (ModelWeights.alloc_staging) a host loop fills for
+        this lane; its experts are region 2 of the lane's own (region, slot) tables.
+        staged: under form 0 a host-resident expert with more than staged_min_rows rows is copied once
         into this lane's HBM staging stack (one slot per expert, shared by all layers) by fetch tiles of
         fetch_chunk bytes, and its GEMM tiles read the copy."""
         self.fab, self.lane_id, self.cfg, self.w, self.kv = fab, lane_id, cfg, weights, kv
         self.staged, self.staged_min_rows, self.fetch_chunk = staged, staged_min_rows, fetch_chunk
+        self.staging_index = staging_index
+        # the lane's own (region, slot) tables int32 [layers][experts][2]: a host loop moves entries of
+        # one lane between the host region and that lane's staging buffer without touching other lanes
+        E_, L_ = cfg.num_experts, cfg.num_layers
+        self.tables = torch.zeros(L_, E_, 2, dtype=torch.int32, device="cuda")
+        for l_ in range(L_):
+            if weights.table[l_] is not None:
+                self.tables[l_].copy_(weights.table[l_])
         self.T, self.S, self.bt_stride, self.max_chunks = max_tokens, max_slots, bt_stride, max_chunks
         # rows of the lm_head (requests that continue; every row when a caller wants all logits), and the
         # smallest row-block height the published plans will use for host-resident experts
@@ -255,8 +284,10 @@ class ModelLane:
         moe = [l for l in range(L) if w.host_w13[l] is not None]
         self.w13_maps, self.w2_maps = [None] * L, [None] * L
         self.staging, self.fetch_tiles = [None] * L, 0
-        st13 = st2 = 0
-        if self.staged and moe:   # region 2: the staging stack, one slot per expert, the reference's row order
+        st13 = st2 = hl13 = hl2 = 0
+        if self.staging_index is not None:   # region 2: the staging buffer a host loop fills
+            hl13, hl2 = self._wmap(w.stage_w13[self.staging_index]), self._wmap(w.stage_w2[self.staging_index])
+        if self.staged and moe:   # region 3: the lane's own staging stack, one slot per expert, filled by fetch tiles
             h13, h2 = w.host_w13[moe[0]], w.host_w2[moe[0]]
             self.stage_w13 = torch.empty(h13.shape, dtype=h13.dtype, device="cuda")
             self.stage_w2 = torch.empty(h2.shape, dtype=h2.dtype, device="cuda")
@@ -265,9 +296,9 @@ class ModelLane:
             self.fetch_tiles = -(-b13 // self.fetch_chunk) + -(-b2 // self.fetch_chunk)
         for l in moe:
             self.w13_maps[l] = _u64([self._wmap(w.host_w13[l], _C.host_device_pointer(w.host_w13[l].data_ptr())),
-                                     self._wmap(w.hot_w13[l], packed=True), st13, 0])
+                                     self._wmap(w.hot_w13[l], packed=True), hl13, st13])
             self.w2_maps[l] = _u64([self._wmap(w.host_w2[l], _C.host_device_pointer(w.host_w2[l].data_ptr())),
-                                    self._wmap(w.hot_w2[l]), st2, 0])
+                                    self._wmap(w.hot_w2[l]), hl2, st2])
             if st13:
                 self.staging[l] = _block(
                     "StagingArgs", w13_src=_C.host_device_pointer(w.host_w13[l].data_ptr()),
@@ -395,7 +426,7 @@ class ModelLane:
         cfg = self.cfg
         at = p.dynamic_first
         for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0 in expands:
-            blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.w.table[l],
+            blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.tables[l],
                         w13_maps=self.w13_maps[l], w2_maps=self.w2_maps[l], xp_maps=self.xp_maps, h_maps=self.h_maps,
                         w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
                         I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
