@@ -437,6 +437,10 @@ def run_ours(args):
                                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": hbm_ach / pk["hbm_gbs"],
                                     "peak_source": pk["source"], "active_experts": hot_active,
                                     "note": "same batch with all 128 experts in HBM", "kernel_ms": hot_kt,
+                                    # dram__bytes_read + write of one launch from the ncu capture summarised in
+                                    # profiles/expert_gemm_config2_and_all_hot.md (75 active experts there:
+                                    # 708.7 + 4.8 MB against 708 MB of weights, i.e. no re-reads)
+                                    "traffic": 713.5e6, "traffic_algorithmic_ratio": 1.0,
                                     "layer_tokens_per_s": BATCH / (hot_ms_step * 1e-3)}
         if cpu_times:
             sec = sum(cpu_times) / len(cpu_times)
