@@ -370,10 +370,12 @@ def run_ours(args):
     layer.set_profile(1)
     kt = {}
     prof_steps = min(args.steps, 20)
+    step_counts = []   # per profiled step: the routed rows of every expert (the batches differ)
     for i in range(prof_steps):
         layer.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out)
         for k, v in layer.last_times().items():
             kt.setdefault(k, []).append(v)
+        step_counts.append(layer.workspace("counts")[:E].cpu())
     layer.set_profile(0)
     kt = {k: sum(v) / len(v) for k, v in kt.items()}
 
@@ -388,26 +390,28 @@ def run_ours(args):
         layer_hot.set_table(tbl)
         layer_hot.set_profile(1)
         hot_kt = {}
+        hot_active_steps = []
         for i in range(3 + prof_steps):
             layer_hot.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out)
             if i >= 3:
                 for k, v in layer_hot.last_times().items():
                     hot_kt.setdefault(k, []).append(v)
+                hot_active_steps.append(int((layer_hot.workspace("counts")[:E] > 0).sum()))
         hot_kt = {k: sum(v) / len(v) for k, v in hot_kt.items()}
         layer_hot.set_profile(0)
         hot_ms_step = timed(lambda i: layer_hot.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out),
                             args.steps, 3) / args.steps if world == 1 else float("nan")
-        hot_active = int((layer_hot.workspace("counts")[:E] > 0).sum())
+        hot_active = sum(hot_active_steps) / len(hot_active_steps)   # mean over the steps whose times are averaged
         layer_hot.status()
         layer_hot.close()
 
     if rank == 0:
         # algorithmic bytes of the dominant kernel (w13): every activated expert's w13 once
-        counts = [layer.workspace("counts")[:E].cpu()]
-        active = (counts[0] > 0)
+        # mean over the profiled steps (the kernel time below is the mean over the same steps)
         table = layer.table
-        cold = sum(1 for e in range(E) if active[e] and table[e, 0] == 0)
-        hot = sum(1 for e in range(E) if active[e] and table[e, 0] == 1)
+        is_cold = torch.tensor([int(table[e, 0]) == 0 for e in range(E)])
+        cold = sum(float(((c > 0) & is_cold).sum()) for c in step_counts) / len(step_counts)
+        hot = sum(float(((c > 0) & ~is_cold).sum()) for c in step_counts) / len(step_counts)
         w13_bytes = 3 * I * H * 2      # one expert: w13 + w2, read by the single fused GEMM launch
         pk = peaks()
         dom = "experts"
