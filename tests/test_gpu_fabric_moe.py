@@ -129,6 +129,61 @@ def test_staged_form_reads_each_expert_once(hot):
     assert torch.equal(outs[0][0], outs[1][0])
 
 
+def test_qwen3_shape_layer_program_staged_and_permuted():
+    """Benchmark configuration 1 shape in the fabric (E 128, top-8, H 2048, I 768; 64 decode tokens + one
+    512-token prefill; half of the experts host-resident), form 0 with the staging stack and a threshold of
+    32 rows, so the run mixes hot experts, host experts read in place and staged experts: routing and packing
+    bit-exact against the C oracle, output against the reference's torch path; then the size-independent
+    property: the layer is permutation-equivariant over tokens, bit for bit, although a permutation changes
+    every expert's row order and which tiles run where."""
+    from monoserve_b200.fabric import Fabric
+    from monoserve_b200.lane import MoELane
+    from oracle import torch_path as tp
+    T, H, I, E, K = 576, 2048, 768, 128, 8
+    g = torch.Generator().manual_seed(0)
+    wr = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    g1 = torch.Generator().manual_seed(1)
+    xn = torch.randn(T, H, generator=g1).to(torch.bfloat16)
+    x2 = torch.zeros(T, H, dtype=torch.bfloat16)
+    perm = torch.randperm(T, generator=g1)
+    fab = Fabric(pool_bytes=512 << 20)
+    fab.set_max_run(120)
+    outs = []
+    try:
+        lane = MoELane(fab, 0, H, I, E, K, T, wr, w13, w2, hot=list(range(64)), staged=True, staged_min_rows=32)
+        for x_in in (xn, xn[perm].contiguous()):
+            lane.set_input(x_in.cuda(), x2.cuda())
+            h = lane.build(T, iterations=1)
+            fab.start()
+            fab.publish(map=[0] * fab.num_workers, caps=[8], order=[0], programs=[h], forms=[0])
+            wait_iterations(fab, 0, fab.progress()["lanes"][0]["iterations"] + 1, timeout=60)
+            fab.stop()
+            assert fab.progress()["error"] == 0
+            outs.append(lane.x[:T].cpu().clone())
+            if len(outs) == 1:
+                logits = oracle.router_logits(oracle.bf16_bits(xn), oracle.bf16_bits(wr))
+                ids, w, counts = oracle.router_topk(logits, K)
+                starts = oracle.scan(counts)
+                pt, pw, pp = oracle.pack(ids, w, starts)
+                P = T * K
+                assert np.array_equal(lane.topk_ids[:T].cpu().numpy().ravel(), ids.ravel())
+                assert np.array_equal(lane.topk_w[:T].cpu().numpy().view(np.int32).ravel(), w.view(np.int32).ravel())
+                assert np.array_equal(lane.starts.cpu().numpy(), starts)
+                assert np.array_equal(lane.pair_token[:P].cpu().numpy(), pt)
+                assert np.array_equal(lane.pair_pos[:T].cpu().numpy().ravel(), pp.ravel())
+                assert (counts[64:] > 32).any() and (counts[64:] <= 32).any(), "staged and unstaged host experts"
+                routing = (torch.from_numpy(w), torch.from_numpy(ids.astype(np.int64)))
+                ref, _, _ = tp.moe_layer(xn.float(), x2.float(), wr, w13, w2, K, routing=routing)
+                rel = float((outs[0].float() - ref).norm() / ref.norm())
+                assert rel < 1e-2, rel
+    finally:
+        fab.stop()
+        fab.close()
+    assert torch.equal(outs[1], outs[0][perm])
+
+
 def test_prefill_and_decode_lanes_side_by_side():
     from monoserve_b200.fabric import Fabric
     from monoserve_b200.lane import MoELane
