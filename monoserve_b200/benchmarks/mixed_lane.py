@@ -132,6 +132,22 @@ def make_glm_weights(cfg, distinct, seed=0):
     return w
 
 
+def measure_link_peak(mib=256, reps=6):
+    """GB/s of a pinned host -> device copy of `mib` MiB by the copy engine (best of `reps`)."""
+    src = torch.empty(mib << 20, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(mib << 20, dtype=torch.uint8, device="cuda")
+    best = 0.0
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        dst.copy_(src, non_blocking=True)
+        b.record()
+        b.synchronize()
+        best = max(best, (mib << 20) / (a.elapsed_time(b) * 1e-3) / 1e9)
+    del src, dst
+    return best
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=["qwen", "glm"], default="qwen")
@@ -187,6 +203,7 @@ def main():
         kv.k[l].normal_(0, 1)
         kv.v[l].normal_(0, 1)
     bt_stride = max(max(pages_dec), pages_pre)
+    link_peak = measure_link_peak()
     fab = Fabric(pool_bytes=2 << 30)
     fab.set_max_run(600)
     min_form = min([f for f in forms if f] + [64])
@@ -255,7 +272,10 @@ def main():
             "routed_rows_per_layer_step": float(hist.sum() / max(1, cfg.num_layers) / iters),
             "setup_s": round(t_setup, 1), "error": err}
     # Host-link traffic: every activated cold expert's 3 H I weights cross the link once per pass over
-    # its rows (row blocks of `form` rows; form 0 = 256-row blocks), per layer.
+    # its rows (row blocks of `form` rows; form 0 = 256-row blocks), per layer.  Computed from the mean rows
+    # per expert and iteration, which is exact when every cold expert is activated in every iteration (the
+    # full configurations: 1024 or 512 routed decode rows over 128 experts) and an over-estimate for the
+    # `--quick` case, whose 16 sequences leave a third of the experts idle in a step.
     expert_bytes = 3 * cfg.hidden * cfg.intermediate * (1 if glm else 2)
 
     def link_bytes(lane, form, iterations, staged=False):
@@ -283,6 +303,12 @@ def main():
         line["prefill_link_bytes_per_iteration"] = pre_link
         link_rate += pre_link / (pre_ms * 1e-3)
     line["host_link_gbs"] = link_rate / 1e9
+    # Roofline of the run: both lanes are bound by the host link, so the fraction to read is the expert bytes
+    # that crossed it per second against the copy peak measured in this process; the decode step's own lower
+    # bound is its link bytes at that peak, i.e. with no prefill lane beside it and every other term hidden.
+    line["host_link_peak_gbs"] = link_peak
+    line["host_link_frac"] = link_rate / 1e9 / link_peak if link_peak else None
+    line["decode_tpot_link_bound_ms"] = dec_link / (link_peak * 1e9) * 1e3 if link_peak else None
     if loop_stats is not None:
         # experts the copy engine staged are read from HBM by the prefill lane: the figure above counts them
         # as link reads of the kernel, so with the host loop it is an upper bound of the kernel's own reads
