@@ -19,12 +19,14 @@ import time
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 
-def run(wl, hot, tokens, caps, form, reps):
+def run(wl, hot, tokens, caps, form, reps, idle_cap=0):
     from monoserve_b200.fabric import Fabric
     from monoserve_b200.lane import MoELane
     H, I, E, K = 2048, 768, 128, 8
     fab = Fabric(pool_bytes=512 << 20)
     fab.set_max_run(120)
+    if idle_cap:
+        fab.set_idle_cap(idle_cap)   # longest back-off of an idle worker's poll, ns
     lane = MoELane(fab, 0, H, I, E, K, 256, wl["wr"], wl["w13"], wl["w2"], hot=hot)
     lane.set_input(wl["xs"][0][:tokens].cuda(), wl["x2s"][0][:tokens].cuda())
     h = lane.build(tokens, iterations=0)
@@ -47,13 +49,17 @@ def main():
     ap.add_argument("--caps", type=int, default=8)
     ap.add_argument("--form", type=int, default=64)
     ap.add_argument("--reps", type=int, default=40)
+    ap.add_argument("--idle-cap", type=int, default=0, help="longest back-off of an idle worker's poll in ns (default: the library's)")
+    ap.add_argument("--only", choices=["both", "all_hot", "config2"], default="both")
     args = ap.parse_args()
     import bench
     wl = bench.make_workload()
     line = {"workload": "one MoE layer as a repeating fabric program on all SMs (config-2 shapes)", "tokens": args.tokens,
-            "caps": args.caps, "form": args.form,
-            "config2": run(wl, wl["hot"], args.tokens, args.caps, args.form, max(6, args.reps // 4)),
-            "all_hot": run(wl, list(range(128)), args.tokens, args.caps, args.form, args.reps)}
+            "caps": args.caps, "form": args.form}
+    if args.only in ("both", "config2"):
+        line["config2"] = run(wl, wl["hot"], args.tokens, args.caps, args.form, max(6, args.reps // 4), args.idle_cap)
+    if args.only in ("both", "all_hot"):
+        line["all_hot"] = run(wl, list(range(128)), args.tokens, args.caps, args.form, args.reps, args.idle_cap)
     print(json.dumps(line))
 
 
