@@ -4,7 +4,7 @@ FP8-e4m3 weights drawn from N(0, 0.02) and quantised per output channel with fp3
 the experts in the HBM hot tier and all of them in pinned host memory), through the stream path
 (`MoELayer`), for the two batch shapes of that config: 64 decode rows, and 2 x 4096 prefill rows.
 
-    python -m monoserve_b200.benchmarks.glm_layer [--reps 10] [--credits 8]
+    python -m monoserve_b200.benchmarks.glm_layer [--reps 10] [--credits 8] [--all-hot] [--only decode|prefill]
 
 The shared expert and the attention of config 4 are not part of this measurement.  Reported per
 batch: layer time (CUDA events, inputs resident), tokens/s, activated hot / cold experts, host-link
@@ -25,6 +25,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--credits", type=int, default=8)
+    ap.add_argument("--all-hot", action="store_true", help="every expert in the HBM hot tier (the FP8 kernel against HBM)")
+    ap.add_argument("--only", choices=["both", "decode", "prefill"], default="both")
     args = ap.parse_args()
     from monoserve_b200.moe import MoELayer
     from oracle import torch_path as tp            # the checker of the 64-row sample only
@@ -44,9 +46,11 @@ def main():
     torch.cuda.synchronize()
     wr = (torch.randn(E, H, generator=g, device="cuda") * H ** -0.5).to(torch.bfloat16)
     bias = torch.randn(E, generator=g, device="cuda") * 0.1
-    hot = list(range(0, E, 4))                      # 25 % hot
+    hot = list(range(E)) if args.all_hot else list(range(0, E, 4))   # 25 % hot
     results = {}
     for name, T, form in (("decode_64", 64, 64), ("prefill_2x4096", 8192, 0)):
+        if args.only != "both" and not name.startswith(args.only):
+            continue
         layer = MoELayer(H, I, E, K, T, scoring="sigmoid", renorm=True, routed_scale=2.5, fp8=True)
         layer.set_router(wr, bias)
         layer.set_experts(q13, q2, hot, scales=(s13, s2))
