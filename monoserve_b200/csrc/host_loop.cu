@@ -18,8 +18,8 @@
 //     (host_region, expert) and the half is refilled for the layer after next; a new
 //     program generation or an idle lane gives both halves back.
 // Structure that differs: the decisions are taken by `poll_lane` from a plain snapshot of
-// the three mirror words, and everything it does goes through `Effects`, so the same code
-// runs against the copy engine or, for a loop created without a fabric, against a log that
+// the three mirror words, and everything it does goes through `issue_copy`, `copy_landed` and
+// `write_entry`, so the same code runs against the copy engine or, for a loop created without a fabric, against a log that
 // a test reads (`monofab_host_loop_inject / _step / _log`): the policy is testable on a
 // machine without a GPU.
 #include <cuda_runtime.h>
@@ -44,7 +44,10 @@ using namespace mf;
 
 namespace {
 
-constexpr int kEntryRing = 256;   // pinned 8-byte table entries in flight at most
+// Pinned 8-byte table entries that may be queued on the stream at once.  Entry copies queue behind at most
+// one expert copy; in that time a lane gives back at most its two halves (2 x slots <= 2 x 256 entries) and
+// switches one entry, so 4096 covers several lanes.
+constexpr int kEntryRing = 4096;
 
 struct Flip { int expert, slot; };
 
