@@ -288,11 +288,19 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
 
 // ------------------------------------------------------------------- combine
 
+constexpr int kCombineSplit = 4;   // warps per token when no row reduction follows
+
 __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
+  // Without the fused RMSNorm a row needs no reduction, so kCombineSplit warps share a token's columns:
+  // a decode batch of a few hundred tokens otherwise leaves most of the machine idle.  Every column is
+  // computed by the same instructions either way: the result does not depend on the split.
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int split = A.norm_w ? 1 : kCombineSplit;
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t = unit / split, part = unit - t * split;
   if (t >= A.T) return;
   const int K = A.K, H = A.H, n16 = H / 8;
+  const int c_begin = part * n16 / split, c_end = (part + 1) * n16 / split;
   int pos = 0;
   float w = 0.f;
   if (lane < K) {
@@ -302,7 +310,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
   const uint4* x2 = A.x2 ? reinterpret_cast<const uint4*>(A.x2 + static_cast<size_t>(t) * H) : nullptr;
   uint4* xo = reinterpret_cast<uint4*>(A.x + static_cast<size_t>(t) * H);
   float ss = 0.f;
-  for (int c = lane; c < n16; c += 32) {
+  for (int c = c_begin + lane; c < c_end; c += 32) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -410,7 +418,8 @@ cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, i
 
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream) {
   if (A.T == 0) return cudaSuccess;
-  combine_kernel<<<(A.T + 7) / 8, 256, 0, stream>>>(A);
+  const int units = A.T * (A.norm_w ? 1 : kCombineSplit);
+  combine_kernel<<<(units + 7) / 8, 256, 0, stream>>>(A);
   return cudaGetLastError();
 }
 
