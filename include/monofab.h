@@ -28,7 +28,8 @@ extern "C" {
 
 /* Bits of a layer's device status word (monofab_moe_status). */
 #define MONOFAB_STATUS_WAIT_TIMEOUT 1  /* a bounded in-kernel wait ran out */
-#define MONOFAB_STATUS_PLAN_OVERFLOW 2 /* more GEMM tiles than the plan buffers hold */
+#define MONOFAB_STATUS_PLAN_OVERFLOW 2 /* more rows or GEMM tiles than the buffers hold, or a bad segment */
+#define MONOFAB_STATUS_BAD_ARGS 4      /* an expert id outside [0, E) reached a kernel */
 
 /* Region ids of the expert indirection table (monoserve/runtime/kinds.py:16-18). */
 #define MONOFAB_REGION_HOST 0
@@ -230,6 +231,56 @@ int monofab_moe_workspace(monofab_moe* m, const char* name, void** ptr, size_t* 
  * [5] combine. */
 int monofab_moe_set_profile(monofab_moe* m, int on);   /* bit 0: event times; bit 1: in-kernel role trace */
 int monofab_moe_last_times(monofab_moe* m, float ms[6]);
+
+/* ---- one MoE layer, experts partitioned over the GPUs of a node ------------------
+ * Expert parallelism with this library's own exchange: rank r of `world` owns experts
+ * [r * E / world, (r + 1) * E / world); routing, packing and combining stay local to a
+ * rank's tokens, and the rows travel by plain stores into the owning GPU's memory over
+ * NVLink, signalled with flags (no collective library call and no host round trip per
+ * layer).  The reference has no collective of its own: its only multi-GPU mode is stock
+ * vLLM expert parallelism (monoserve/baselines/serve_ep.py:24-28); the stage chain that is
+ * distributed here is monoserve/runtime/lane.py:340-380.
+ *
+ * Set-up, once: every rank creates its object on its own GPU, sets the weights of ITS experts
+ * on monofab_ep_local() (monofab_moe_set_region / _set_table / _set_plan, experts numbered
+ * 0 .. E / world - 1), exports a handle, gathers all ranks' handles by any means (they are plain
+ * bytes) and connects.  Ranks may be separate processes (CUDA IPC) or objects of one process.
+ * cfg describes the whole layer (E experts, top-K) and max_tokens per rank.  rows_cap = rows a
+ * rank's receive buffer takes; 0 = the worst case max_tokens * top_k * world, with which nothing
+ * can overflow.  With a smaller capacity, rows beyond it are not sent and every rank reports
+ * MONOFAB_STATUS_PLAN_OVERFLOW for that pass.
+ * A pass is collective: every rank must call it (T may differ per rank and may be 0).  A peer
+ * that never arrives ends the bounded in-kernel waits with MONOFAB_STATUS_WAIT_TIMEOUT. */
+#define MONOFAB_EP_MAX_RANKS 16
+#define MONOFAB_EP_HANDLE_BYTES 256
+typedef struct monofab_ep monofab_ep;
+int monofab_ep_create(const monofab_moe_config* cfg, int rank, int world, int rows_cap, monofab_ep** out);
+monofab_moe* monofab_ep_local(monofab_ep* ep);
+int monofab_ep_export(monofab_ep* ep, void* handle /* MONOFAB_EP_HANDLE_BYTES */);
+int monofab_ep_connect(monofab_ep* ep, const void* handles /* world x MONOFAB_EP_HANDLE_BYTES, by rank */);
+/* Closes the mappings of the peers' buffers; call on every rank, then synchronise the ranks,
+ * before any rank destroys its object. */
+int monofab_ep_disconnect(monofab_ep* ep);
+int monofab_ep_destroy(monofab_ep* ep);
+int monofab_ep_set_router(monofab_ep* ep, const void* wr_bf16, const float* bias);
+/* out bf16 [T][H] = bf16(x2 + moe(xn)) for this rank's T tokens.  Asynchronous on `stream`.
+ * Read the status word with monofab_moe_status(monofab_ep_local(ep), ...). */
+int monofab_ep_forward(monofab_ep* ep, const void* xn, const void* x2, void* out, int T, void* stream);
+/* One of the four phases of a pass (0 route + post counts, 1 dispatch rows, 2 experts + return
+ * rows, 3 combine); monofab_ep_forward runs them in order.  A process that holds several ranks on
+ * ONE GPU (a test) must run phase p of every rank before phase p + 1 of any, on one stream, because
+ * kernels of one GPU must not wait for one another. */
+int monofab_ep_phase(monofab_ep* ep, int phase, const void* xn, const void* x2, void* out, int T, void* stream);
+/* "logits" "topk_ids" "topk_w" "pair_pos" "counts" "starts" "y_back" */
+int monofab_ep_workspace(monofab_ep* ep, const char* name, void** ptr, size_t* bytes);
+/* Device times of the last pass in milliseconds (CUDA events on the launching stream):
+ * [0] router logits [1] top-k [2] counts + post [3] wait counts + dispatch [4] wait rows + plan
+ * [5] expert GEMMs [6] return [7] wait y + combine. */
+int monofab_ep_set_profile(monofab_ep* ep, int on);
+int monofab_ep_last_times(monofab_ep* ep, float ms[8]);
+/* Host arithmetic of the exchange layout, for tests: first row, in the receive buffer of the rank
+ * that owns expert e, of the rows rank `src` sends for e; counts_all int32 [world][stride]. */
+int monofab_ep_dest_base(const int32_t* counts_all, int stride, int world, int experts, int src, int e);
 
 /* ---- the persistent fabric ------------------------------------------------- */
 

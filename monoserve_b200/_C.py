@@ -30,7 +30,11 @@ EXPORTS = [
     "monofab_host_loop_create", "monofab_host_loop_add_lane", "monofab_host_loop_start", "monofab_host_loop_stop",
     "monofab_host_loop_stats", "monofab_host_loop_destroy", "monofab_host_loop_inject", "monofab_host_loop_step",
     "monofab_host_loop_log",
+    "monofab_ep_create", "monofab_ep_local", "monofab_ep_export", "monofab_ep_connect", "monofab_ep_disconnect",
+    "monofab_ep_destroy", "monofab_ep_set_router", "monofab_ep_forward", "monofab_ep_phase", "monofab_ep_workspace",
+    "monofab_ep_set_profile", "monofab_ep_last_times", "monofab_ep_dest_base",
 ]
+EP_HANDLE_BYTES = 256   # MONOFAB_EP_HANDLE_BYTES
 
 
 class MoEConfigC(ctypes.Structure):
@@ -112,6 +116,20 @@ def _load():
     lib.monofab_host_loop_inject.argtypes = [vp, i32, u64, u64, u64]
     lib.monofab_host_loop_step.argtypes = [vp]
     lib.monofab_host_loop_log.argtypes = [vp, vp, i32, P(i32)]
+    lib.monofab_ep_create.argtypes = [P(MoEConfigC), i32, i32, i32, P(vp)]
+    lib.monofab_ep_local.restype = vp
+    lib.monofab_ep_local.argtypes = [vp]
+    lib.monofab_ep_export.argtypes = [vp, vp]
+    lib.monofab_ep_connect.argtypes = [vp, vp]
+    lib.monofab_ep_disconnect.argtypes = [vp]
+    lib.monofab_ep_destroy.argtypes = [vp]
+    lib.monofab_ep_set_router.argtypes = [vp, vp, vp]
+    lib.monofab_ep_forward.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.monofab_ep_phase.argtypes = [vp, i32, vp, vp, vp, i32, vp]
+    lib.monofab_ep_workspace.argtypes = [vp, ctypes.c_char_p, P(vp), P(sz)]
+    lib.monofab_ep_set_profile.argtypes = [vp, i32]
+    lib.monofab_ep_last_times.argtypes = [vp, P(ctypes.c_float * 8)]
+    lib.monofab_ep_dest_base.argtypes = [vp, i32, i32, i32, i32, i32]
     return lib
 
 

@@ -13,6 +13,7 @@
 
 #include "../../include/monofab.h"
 #include "kernels.h"
+#include "moe_layer.h"
 #include "operands.h"
 
 namespace mf {
@@ -29,12 +30,6 @@ int fail(int code, const char* fmt, ...) {
   g_error = std::string("monofab: ") + buf;
   return code;
 }
-
-#define MF_CUDA(expr)                                                                          \
-  do {                                                                                         \
-    cudaError_t e_ = (expr);                                                                   \
-    if (e_ != cudaSuccess) return fail(MONOFAB_ECUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
-  } while (0)
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point table, so the
 // library needs no link-time dependency on libcuda.
@@ -78,63 +73,9 @@ int encode_map(CUtensorMap* map, int dtype, const void* base, int rank, const ui
   return MONOFAB_OK;
 }
 
-constexpr int kNumTimes = 6;
-
 }  // namespace mf
 
 using namespace mf;
-
-struct monofab_moe {
-  monofab_moe_config cfg{};
-  std::mutex mu;
-  int device = 0, num_sms = 0;
-  int ctas = 0, credits = 8, form = 64;
-  // weights
-  const void* router_w = nullptr;
-  const float* router_bias = nullptr;
-  const void* w13[2] = {nullptr, nullptr};   // device-visible addresses per region
-  const void* w2[2] = {nullptr, nullptr};
-  int slots[2] = {0, 0};
-  int packed[2] = {0, 0};                    // w13 of the region is in the packed SwiGLU row order
-  bool trace_on = false;
-  const float* s13 = nullptr;
-  const float* s2 = nullptr;
-  // workspaces (device)
-  float* logits = nullptr;
-  int* topk_ids = nullptr;
-  float* topk_w = nullptr;
-  int* counts = nullptr;
-  int* starts = nullptr;
-  int* chunk_counts = nullptr;
-  int* pair_rank = nullptr;
-  int* pair_token = nullptr;
-  float* pair_weight = nullptr;
-  int* pair_pos = nullptr;
-  int* table = nullptr;
-  int* hist = nullptr;
-  void* xp = nullptr;
-  void* h = nullptr;
-  float* y = nullptr;
-  void* xin = nullptr;    // staging of the host-buffer entry point
-  void* x2in = nullptr;
-  void* xout = nullptr;
-  GemmTile* tiles[2] = {nullptr, nullptr};
-  GemmQueues* queues = nullptr;
-  int* done = nullptr;
-  unsigned long long* trace = nullptr;
-  int block_cap = 0;
-  int* status = nullptr;
-  int* status_host = nullptr;
-  int tile_cap = 0;
-  size_t pairs_cap = 0;
-  bool maps_dirty = true;
-  GemmParams gp{};
-  bool profile = false;
-  cudaEvent_t ev[kNumTimes + 1] = {};
-  float times[kNumTimes] = {};
-  bool times_valid = false;
-  std::vector<void*> owned;
-};
 
 namespace mf {
 
@@ -241,37 +182,47 @@ int forward_locked(monofab_moe* m, const void* xn, const void* x2, void* out, in
   pp.I = I;
   pp.form = m->form;
   pp.tile_cap = m->tile_cap;
+  pp.n_experts = E;
+  pp.rows_cap = static_cast<int>(m->pairs_cap) - 256;
   MF_CUDA(launch_plan(pp, st));
   MF_CUDA(mark());
   PackParams kp{m->topk_ids, m->topk_w, m->pair_rank, m->chunk_counts, m->starts, static_cast<const bf16*>(xn),
                 static_cast<bf16*>(m->xp), m->pair_token,
-                m->pair_weight, m->pair_pos, T, E, K, H};
+                m->pair_weight, m->pair_pos, T, E, K, H, m->status};
   MF_CUDA(launch_pack(kp, st));
   MF_CUDA(mark());
   m->gp.cap = m->credits;
   m->gp.trace = m->trace_on ? m->trace : nullptr;
   MF_CUDA(launch_expert_gemm(m->gp, ctas, st));
   MF_CUDA(mark());
-  CombineParams cp{m->y, m->pair_pos, m->topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(out),
-                   nullptr, nullptr, T, K, H, 0.f};
+  CombineParams cp{};
+  cp.y = m->y;
+  cp.pair_pos = m->pair_pos;
+  cp.topk_w = m->topk_w;
+  cp.x2 = static_cast<const bf16*>(x2);
+  cp.x = static_cast<bf16*>(out);
+  cp.T = T;
+  cp.K = K;
+  cp.H = H;
   MF_CUDA(launch_combine(cp, st));
   MF_CUDA(mark());
   m->times_valid = prof;
   return MONOFAB_OK;
 }
 
-// Expert FFN over caller-described segments of the layer's packed-row buffer.
-int experts_locked(monofab_moe* m, const int* seg_counts, const int* seg_expert, int n_seg, cudaStream_t st) {
+// Expert FFN over caller-described segments of the layer's packed-row buffer.  `seg` carries the
+// segment description (seg_counts, seg_expert, E = number of segments, optional stride and peer
+// flags to wait for); the layer fills in its own buffers and limits.
+int experts_locked(monofab_moe* m, const PlanParams& seg, cudaStream_t st, cudaEvent_t after_plan) {
   const monofab_moe_config& c = m->cfg;
+  const int n_seg = seg.E;
   if (n_seg < 1 || n_seg > kMaxExperts) return fail(MONOFAB_EINVAL, "experts: n_seg=%d outside [1, %d]", n_seg, kMaxExperts);
-  if (!seg_counts) return fail(MONOFAB_EINVAL, "experts: seg_counts must not be NULL");
+  if (!seg.seg_counts) return fail(MONOFAB_EINVAL, "experts: seg_counts must not be NULL");
   if (c.fp8 && (!m->s13 || !m->s2)) return fail(MONOFAB_EINVAL, "FP8 experts need their scales (monofab_moe_set_scales)");
   if (m->maps_dirty)
     if (int r = build_maps(m)) return r;
   const int ctas = m->ctas > 0 && m->ctas < m->num_sms ? m->ctas : m->num_sms;
-  PlanParams pp{};
-  pp.seg_counts = seg_counts;
-  pp.seg_expert = seg_expert;
+  PlanParams pp = seg;
   pp.counts = m->counts;
   pp.starts = m->starts;
   pp.table = m->table;
@@ -281,12 +232,14 @@ int experts_locked(monofab_moe* m, const int* seg_counts, const int* seg_expert,
   pp.block_cap = m->block_cap;
   pp.q = m->queues;
   pp.status = m->status;
-  pp.E = n_seg;
   pp.H = c.hidden;
   pp.I = c.intermediate;
   pp.form = m->form;
   pp.tile_cap = m->tile_cap;
+  pp.n_experts = c.experts;
+  pp.rows_cap = static_cast<int>(m->pairs_cap) - 256;
   MF_CUDA(launch_plan(pp, st));
+  if (after_plan) MF_CUDA(cudaEventRecord(after_plan, st));
   m->gp.cap = m->credits;
   m->gp.trace = nullptr;
   MF_CUDA(launch_expert_gemm(m->gp, ctas, st));
@@ -394,8 +347,18 @@ int monofab_combine(const float* y, const int32_t* pair_pos, const float* topk_w
   if (!y || !pair_pos || !topk_w || !x) return fail(MONOFAB_EINVAL, "combine: NULL argument");
   if (norm_w && !normed) return fail(MONOFAB_EINVAL, "combine: norm_w given without an output");
   if (K < 1 || K > 32 || H <= 0 || H % 8) return fail(MONOFAB_EINVAL, "combine: bad K=%d or H=%d", K, H);
-  CombineParams cp{y, pair_pos, topk_w, static_cast<const bf16*>(x2), static_cast<bf16*>(x),
-                   static_cast<const bf16*>(norm_w), static_cast<bf16*>(normed), T, K, H, eps};
+  CombineParams cp{};
+  cp.y = y;
+  cp.pair_pos = pair_pos;
+  cp.topk_w = topk_w;
+  cp.x2 = static_cast<const bf16*>(x2);
+  cp.x = static_cast<bf16*>(x);
+  cp.norm_w = static_cast<const bf16*>(norm_w);
+  cp.normed = static_cast<bf16*>(normed);
+  cp.T = T;
+  cp.K = K;
+  cp.H = H;
+  cp.eps = eps;
   MF_CUDA(launch_combine(cp, static_cast<cudaStream_t>(stream)));
   return MONOFAB_OK;
 }
@@ -420,7 +383,7 @@ int monofab_pack_pairs(const int32_t* topk_ids, const float* topk_w, int T, int 
                 pack_scratch_bytes(T, E, K));
   if (reinterpret_cast<uintptr_t>(scratch) & 3) return fail(MONOFAB_EINVAL, "pack_pairs: scratch must be 4-byte aligned");
   MF_CUDA(launch_pack_chain(topk_ids, topk_w, T, E, K, H, static_cast<const bf16*>(src), static_cast<bf16*>(dst),
-                            counts, starts, pair_token, pair_weight, pair_pos, scratch,
+                            counts, starts, pair_token, pair_weight, pair_pos, scratch, nullptr,
                             static_cast<cudaStream_t>(stream)));
   return MONOFAB_OK;
 }
@@ -514,8 +477,9 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
   // Packed rows are addressed by TMA boxes of up to 256 rows; pad so a box that
   // starts at the last row stays inside the allocation.
   m->pairs_cap = P + 256;
-  // Row blocks: at most P/16 + E blocks (form 16, every expert with a ragged tail).
-  const size_t blocks_max = P / 16 + E;
+  // Row blocks: at most P/16 + one ragged tail per segment (form 16; monofab_moe_experts takes up
+  // to kMaxExperts segments whatever E is).
+  const size_t blocks_max = P / 16 + kMaxExperts;
   m->block_cap = static_cast<int>(blocks_max);
   m->tile_cap = static_cast<int>(blocks_max * ((I + 63) / 64 + (H + 127) / 128));
   int r = 0;
@@ -676,7 +640,11 @@ int monofab_moe_forward(monofab_moe* m, const void* xn, const void* x2, void* ou
 int monofab_moe_experts(monofab_moe* m, const int32_t* seg_counts, const int32_t* seg_expert, int n_seg, void* stream) {
   if (!m) return fail(MONOFAB_EINVAL, "experts: NULL handle");
   std::lock_guard<std::mutex> lock(m->mu);
-  return experts_locked(m, seg_counts, seg_expert, n_seg, static_cast<cudaStream_t>(stream));
+  PlanParams seg{};
+  seg.seg_counts = seg_counts;
+  seg.seg_expert = seg_expert;
+  seg.E = n_seg;
+  return experts_locked(m, seg, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int monofab_moe_forward_host(monofab_moe* m, const void* xn_host, const void* x2_host, void* out_host, int T,

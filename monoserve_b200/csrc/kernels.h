@@ -41,6 +41,16 @@ struct PlanParams {
   int form;                 // row-block height of host-resident experts: 16..128; 0 = 256 (one pass up to 256 rows)
   int tile_cap;             // capacity of each tile list
   int block_cap;            // capacity of done[]
+  int n_experts;            // rows of `table`: a segment's expert id must lie in [0, n_experts)
+  int rows_cap;             // rows the packed-row buffers hold; a plan over more rows is refused
+  // Segment counts may be the sum of several tables: segment s has
+  // sum over i < seg_tables of seg_counts[i * seg_stride + s] rows (seg_tables 0 = one table).
+  int seg_tables, seg_stride;
+  // Peer flags to wait for before the counts are read (expert parallelism: every source rank's
+  // rows have landed when wait_flags[0 .. wait_n) have reached wait_epoch); null = no wait.
+  const unsigned int* wait_flags;
+  unsigned int wait_epoch;
+  int wait_n;
 };
 
 struct PackParams {
@@ -55,6 +65,7 @@ struct PackParams {
   float* pair_weight;       // [P]
   int* pair_pos;            // [T][K] packed row of every (token, pick)
   int T, E, K, H;
+  int* status;              // device error word: kErrBadArgs when an expert id lies outside [0, E); may be null
 };
 
 struct CombineParams {
@@ -67,13 +78,20 @@ struct CombineParams {
   bf16* normed;             // bf16 [T][H] out: rmsnorm(x) * norm_w (when norm_w is set)
   int T, K, H;
   float eps;
+  int y_rows;               // rows of y: a pair_pos outside [0, y_rows) contributes nothing (0 = unchecked)
+  // Peer flags to wait for before y is read (expert parallelism: every peer has returned its
+  // rows when wait_flags[0 .. wait_n) have reached wait_epoch); null = no wait.
+  const unsigned int* wait_flags;
+  unsigned int wait_epoch;
+  int wait_n;
+  int* status;              // receives kErrWaitTimeout if the wait runs out
 };
 
 cudaError_t launch_router_logits(const void* x, const void* wr, float* logits, int T, int H, int E,
                                  cudaStream_t stream);
 cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream);
 cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_counts, int T, int E, int K,
-                              cudaStream_t stream);
+                              int* status, cudaStream_t stream);
 cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream);
 cudaError_t launch_pack(const PackParams& A, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream);
@@ -124,6 +142,6 @@ cudaError_t read_attention_trace(unsigned long long out[8]);
 size_t pack_scratch_bytes(int T, int E, int K);
 cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, int E, int K, int H, const bf16* src,
                               bf16* dst, int* counts, int* starts, int* pair_token, float* pair_weight,
-                              int* pair_pos, void* scratch, cudaStream_t stream);
+                              int* pair_pos, void* scratch, int* status, cudaStream_t stream);
 
 }  // namespace mf

@@ -22,6 +22,7 @@
 
 #include "detmath.cuh"
 #include "kernels.h"
+#include "peer_sync.cuh"
 #include "rowwise.cuh"
 
 namespace mf {
@@ -121,10 +122,12 @@ __global__ void __launch_bounds__(1024) router_topk_kernel(const RouterParams A)
 // elsewhere: one block per chunk of 32 tokens; thread p = (token, pick) counts
 // the earlier pairs of the chunk that chose the same expert, and the block
 // writes the chunk's per-expert pair counts.
+// A pair whose expert id lies outside [0, E) is dropped (rank -1, counted nowhere) and
+// reported as kErrBadArgs when a status word is given.
 __global__ void __launch_bounds__(kChunkTokens * kMaxTopK) chunk_rank_kernel(const int* __restrict__ topk_ids,
                                                                              int* __restrict__ pair_rank,
                                                                              int* __restrict__ chunk_counts,
-                                                                             int T, int E, int K) {
+                                                                             int T, int E, int K, int* status) {
   __shared__ int s_ids[kChunkTokens * kMaxTopK];
   __shared__ int s_hist[kMaxExperts];
   const int rows = min(kChunkTokens, T - static_cast<int>(blockIdx.x) * kChunkTokens);
@@ -136,10 +139,15 @@ __global__ void __launch_bounds__(kChunkTokens * kMaxTopK) chunk_rank_kernel(con
   __syncthreads();
   if (p < pairs) {
     const int me = s_ids[p];
-    int rank = 0;
-    for (int q = 0; q < p; ++q) rank += s_ids[q] == me;
-    pair_rank[base + p] = rank;
-    atomicAdd(&s_hist[me], 1);
+    if (me >= 0 && me < E) {
+      int rank = 0;
+      for (int q = 0; q < p; ++q) rank += s_ids[q] == me;
+      pair_rank[base + p] = rank;
+      atomicAdd(&s_hist[me], 1);
+    } else {
+      pair_rank[base + p] = -1;
+      if (status) atomicOr(status, kErrBadArgs);
+    }
   }
   __syncthreads();
   for (int e = p; e < E; e += blockDim.x) chunk_counts[static_cast<size_t>(blockIdx.x) * E + e] = s_hist[e];
@@ -176,8 +184,19 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   const int e = threadIdx.x;
   const int E = A.E;
   int cnt = 0;
+  bool bad = false;
+  if (A.wait_flags) {   // expert parallelism: the counts and the rows they describe come from peers
+    if (e < A.wait_n && !wait_flag(A.wait_flags + e, A.wait_epoch)) atomicOr(A.status, kErrWaitTimeout);
+    __syncthreads();
+  }
   if (e < E && A.seg_counts) {
-    cnt = A.seg_counts[e];
+    const int tables = A.seg_tables > 0 ? A.seg_tables : 1;
+    for (int i = 0; i < tables; ++i) {
+      const int c = A.seg_counts[static_cast<size_t>(i) * A.seg_stride + e];
+      bad |= c < 0;
+      cnt += c;
+    }
+    if (bad) cnt = 0;
     A.counts[e] = cnt;
   } else if (e < E) {
     for (int c = 0; c < A.chunks; ++c) {
@@ -197,7 +216,11 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   if (!A.q) return;   // scan only: counts, starts and chunk prefixes
   int tier = kTierHot, z = 0, bh = 128, nb = 0;
   const int expert = (e < E && A.seg_expert) ? A.seg_expert[e] : e;
-  if (e < E && cnt > 0) {
+  // A segment of an expert the table does not hold, a negative count or more rows than the packed-row
+  // buffers take: no tile is emitted and the layer reports a plan overflow.
+  bad |= e < E && cnt > 0 && (expert < 0 || expert >= A.n_experts);
+  const bool refuse = __syncthreads_or(bad) || total > A.rows_cap;
+  if (e < E && cnt > 0 && !refuse) {
     tier = A.table[2 * expert] == 0 ? kTierHost : kTierHot;
     z = A.table[2 * expert + 1];
     if (tier == kTierHost) bh = A.form ? A.form : 256;
@@ -212,7 +235,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
     first13[tq] = block_scan_256(mine * f13, s_warp, total13[tq]);
     first2[tq] = block_scan_256(mine * f2, s_warp, total2[tq]);
   }
-  bool overflow = blocks_total > A.block_cap;
+  bool overflow = refuse || blocks_total > A.block_cap;
   for (int tq = 0; tq < 2; ++tq) overflow |= total13[tq] + total2[tq] > A.tile_cap;
   for (int b = e; b < blocks_total && !overflow; b += blockDim.x) A.done[b] = 0;
   if (e == 0) {
@@ -259,13 +282,17 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= A.T) return;
   const int K = A.K;
-  int pos = 0;
+  int pos = -1;   // stays -1 for a pair whose expert id is outside [0, E): it is dropped
   if (lane < K) {
     const int e = A.topk_ids[static_cast<size_t>(t) * K + lane];
-    pos = A.starts[e] + A.chunk_prefix[static_cast<size_t>(t / kChunkTokens) * A.E + e] +
-          A.pair_rank[static_cast<size_t>(t) * K + lane];
-    A.pair_token[pos] = t;
-    A.pair_weight[pos] = A.topk_w[static_cast<size_t>(t) * K + lane];
+    if (e >= 0 && e < A.E) {
+      pos = A.starts[e] + A.chunk_prefix[static_cast<size_t>(t / kChunkTokens) * A.E + e] +
+            A.pair_rank[static_cast<size_t>(t) * K + lane];
+      A.pair_token[pos] = t;
+      A.pair_weight[pos] = A.topk_w[static_cast<size_t>(t) * K + lane];
+    } else if (A.status) {
+      atomicOr(A.status, kErrBadArgs);
+    }
     A.pair_pos[static_cast<size_t>(t) * K + lane] = pos;
   }
   if (!A.src) return;   // pair lists only
@@ -278,6 +305,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
       if (c0 + 32 * i + lane < n16) v[i] = src[c0 + 32 * i + lane];
     for (int k = 0; k < K; ++k) {
       const int pk = __shfl_sync(0xffffffffu, pos, k);
+      if (pk < 0) continue;
       uint4* dst = reinterpret_cast<uint4*>(A.dst + static_cast<size_t>(pk) * A.H);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -295,6 +323,11 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
   // a decode batch of a few hundred tokens otherwise leaves most of the machine idle.  Every column is
   // computed by the same instructions either way: the result does not depend on the split.
   const int lane = threadIdx.x & 31;
+  if (A.wait_flags) {   // expert parallelism: y is written by peers
+    if (static_cast<int>(threadIdx.x) < A.wait_n && !wait_flag(A.wait_flags + threadIdx.x, A.wait_epoch))
+      atomicOr(A.status, kErrWaitTimeout);
+    __syncthreads();
+  }
   const int split = A.norm_w ? 1 : kCombineSplit;
   const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int t = unit / split, part = unit - t * split;
@@ -310,13 +343,18 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
   const uint4* x2 = A.x2 ? reinterpret_cast<const uint4*>(A.x2 + static_cast<size_t>(t) * H) : nullptr;
   uint4* xo = reinterpret_cast<uint4*>(A.x + static_cast<size_t>(t) * H);
   float ss = 0.f;
-  for (int c = c_begin + lane; c < c_end; c += 32) {
+  // Same trip count in every lane: the shuffles inside need the whole warp.  A lane past the end of its
+  // part goes through the motions on the part's last column and neither stores nor counts it.
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    const int c = min(c0 + lane, c_end - 1);
+    const bool on = c0 + lane < c_end;
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < K; ++k) {
       const int pk = __shfl_sync(0xffffffffu, pos, k);
       const float wk = __shfl_sync(0xffffffffu, w, k);
+      if (pk < 0 || (A.y_rows && pk >= A.y_rows)) continue;   // a dropped pair adds nothing
       const float4* yr = reinterpret_cast<const float4*>(A.y + static_cast<size_t>(pk) * H) + 2 * c;
       const float4 a = __ldcs(yr), b = __ldcs(yr + 1);
       acc[0] = __fmaf_rn(wk, a.x, acc[0]);
@@ -338,9 +376,9 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       f[j] = round_bf16(__fadd_rn(f[j], acc[j]));
-      ss = __fmaf_rn(f[j], f[j], ss);
+      if (on) ss = __fmaf_rn(f[j], f[j], ss);
     }
-    xo[c] = pack8(f);
+    if (on) xo[c] = pack8(f);
   }
   if (!A.norm_w) return;
   norm_store_row(xo, ss, A.norm_w, A.normed + static_cast<size_t>(t) * H, nullptr, H, A.eps);
@@ -372,10 +410,10 @@ cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream) {
 }
 
 cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_counts, int T, int E, int K,
-                              cudaStream_t stream) {
+                              int* status, cudaStream_t stream) {
   if (T == 0) return cudaSuccess;
   chunk_rank_kernel<<<(T + kChunkTokens - 1) / kChunkTokens, kChunkTokens * kMaxTopK, 0, stream>>>(
-      topk_ids, pair_rank, chunk_counts, T, E, K);
+      topk_ids, pair_rank, chunk_counts, T, E, K, status);
   return cudaGetLastError();
 }
 
@@ -397,11 +435,11 @@ size_t pack_scratch_bytes(int T, int E, int K) {
 
 cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, int E, int K, int H, const bf16* src,
                               bf16* dst, int* counts, int* starts, int* pair_token, float* pair_weight,
-                              int* pair_pos, void* scratch, cudaStream_t stream) {
+                              int* pair_pos, void* scratch, int* status, cudaStream_t stream) {
   const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
   int* chunk_counts = static_cast<int*>(scratch);
   int* pair_rank = chunk_counts + static_cast<size_t>(chunks) * E;
-  cudaError_t err = launch_chunk_rank(topk_ids, pair_rank, chunk_counts, T, E, K, stream);
+  cudaError_t err = launch_chunk_rank(topk_ids, pair_rank, chunk_counts, T, E, K, status, stream);
   if (err != cudaSuccess) return err;
   PlanParams pp{};
   pp.chunk_counts = chunk_counts;
@@ -409,10 +447,11 @@ cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, i
   pp.starts = starts;
   pp.chunks = chunks;
   pp.E = E;
+  pp.n_experts = E;
   err = launch_plan(pp, stream);
   if (err != cudaSuccess) return err;
   PackParams kp{topk_ids, topk_w, pair_rank, chunk_counts, starts, src, dst, pair_token, pair_weight, pair_pos,
-                T, E, K, H};
+                T, E, K, H, status};
   return launch_pack(kp, stream);
 }
 

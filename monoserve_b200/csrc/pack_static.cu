@@ -83,7 +83,7 @@ extern "C" int monofab_pack_pairs_static(const int32_t* topk_ids, const float* t
   if (int r = scratch_address(&scratch)) return r;
   const cudaError_t e = launch_pack_chain(topk_ids, topk_w, T, E, K, H, static_cast<const bf16*>(src),
                                           static_cast<bf16*>(dst), counts, starts, pair_token, pair_weight, pair_pos,
-                                          scratch, static_cast<cudaStream_t>(stream));
+                                          scratch, nullptr, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(MONOFAB_ECUDA, "pack_pairs_static: launch: %s", cudaGetErrorString(e));
   return MONOFAB_OK;
 }

@@ -58,10 +58,26 @@ class MoELayer:
         self._keep = {}
         self.hot = []
         self.table = None
+        self._owned = True
+
+    @classmethod
+    def borrowed(cls, handle, hidden, intermediate, experts, top_k, max_tokens, fp8=False):
+        """A view of a layer that another native object owns (the local expert layer of an
+        expert-parallel layer); close() does not destroy it."""
+        self = cls.__new__(cls)
+        self.H, self.I, self.E, self.K, self.max_tokens = hidden, intermediate, experts, top_k, max_tokens
+        self.fp8 = bool(fp8)
+        self._h = ctypes.c_void_p(handle)
+        self._keep = {}
+        self.hot = []
+        self.table = None
+        self._owned = False
+        return self
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value and _C is not None and _C.lib is not None:
-            _C.lib.monofab_moe_destroy(self._h)
+            if self._owned:
+                _C.lib.monofab_moe_destroy(self._h)
             self._h = ctypes.c_void_p()
 
     __del__ = close

@@ -86,3 +86,23 @@ def test_split_plan_requires_even_partition():
     with pytest.raises(AssertionError):
         ep.split_plan(torch.ones(10, dtype=torch.int32), 4)
     assert ep.split_plan(torch.tensor([1, 2, 3, 4], dtype=torch.int32), 2) == [3, 7]
+
+
+def test_peer_exchange_layout():
+    """dest_base (and its C twin, the arithmetic the dispatch kernel does) against a receive buffer
+    built by concatenation: the owner's experts in order, inside an expert the source ranks in order."""
+    from monoserve_b200 import _C, ep
+    rng = np.random.default_rng(5)
+    for world, E in [(2, 8), (4, 16), (8, 128), (1, 4)]:
+        El = E // world
+        counts = rng.integers(0, 7, (world, E)).astype(np.int32)
+        counts[rng.integers(0, world), :] = 0          # a rank without tokens
+        for owner in range(world):
+            want, row = {}, 0
+            for e in range(owner * El, (owner + 1) * El):
+                for src in range(world):
+                    want[(src, e)] = row
+                    row += int(counts[src, e])
+            for (src, e), base in want.items():
+                assert ep.dest_base(counts, src, e) == base
+                assert _C.lib.monofab_ep_dest_base(counts.ctypes.data, E, world, E, src, e) == base
