@@ -402,6 +402,128 @@ def run_ours_ep(args, wl, world, rank, local):
     dist.destroy_process_group()
 
 
+def config1_workload():
+    """Benchmark configuration 1: weights N(0, 0.02) from seed 0 in the order router [E, H], w13 [E, 2I, H],
+    w2 [E, H, I]; activations N(0, 1) from seed 1 for a ragged batch of 64 decode tokens plus one 512-token
+    prefill (576 rows for the MoE layer)."""
+    H, I, E = SHAPE["H"], SHAPE["I"], SHAPE["E"]
+    g = torch.Generator().manual_seed(0)
+    wr = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.02).to(torch.bfloat16)
+    xn = torch.randn(576, H, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    return wr, w13, w2, xn
+
+
+def run_config1(steps):
+    """Config 1 on the GPU (every expert in HBM, stream path, CUDA events over `steps` passes) and the
+    reference's PyTorch MoE loop on the host cores on the same batch."""
+    from monoserve_b200.moe import MoELayer
+    from oracle import torch_path as tp
+    H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
+    wr, w13, w2, xn = config1_workload()
+    T = xn.shape[0]
+    layer = MoELayer(H, I, E, K, T)
+    layer.set_router(wr.cuda())
+    layer.set_region(1, layer.pack_w13(w13.cuda()), w2.cuda(), packed=True)
+    tbl = torch.ones(E, 2, dtype=torch.int32)
+    tbl[:, 1] = torch.arange(E)
+    layer.set_table(tbl)
+    xd, out = xn.cuda(), torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        layer.forward(xd, None, out)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        layer.forward(xd, None, out)
+    b.record()
+    b.synchronize()
+    layer.status()
+    ms = a.elapsed_time(b) / steps
+    layer.set_profile(1)
+    layer.forward(xd, None, out)
+    kt = layer.last_times()
+    layer.set_profile(0)
+    active = int((layer.workspace("counts")[:E] > 0).sum())
+    ids = layer.workspace("topk_ids")[:T * K].view(T, K).cpu().long()
+    tw = layer.workspace("topk_w")[:T * K].view(T, K).cpu()
+    got = out.float().cpu()
+    layer.close()
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    times = []
+    with torch.no_grad():
+        for i in range(4):
+            t0 = time.perf_counter()
+            ref, _, _ = tp.moe_layer(xn.float(), None, wr, w13, w2, K, routing=(tw, ids))
+            times.append(time.perf_counter() - t0)
+    sec = sum(times[1:]) / len(times[1:])
+    pk = peaks()
+    bytes_alg = active * 3 * H * I * 2
+    return {"workload": "BASELINE config 1: 576 rows (64 decode + one 512-token prefill), every expert in HBM",
+            "tokens": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "kernel_ms": kt, "active_experts": active,
+            "experts_kernel_hbm_gbs": bytes_alg / (kt["experts"] * 1e-3) / 1e9,
+            "experts_kernel_hbm_frac": bytes_alg / (kt["experts"] * 1e-3) / 1e9 / pk["hbm_gbs"],
+            "layer_hbm_frac": bytes_alg / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+            "rel_l2_vs_cpu_reference": float((got - ref).norm() / ref.norm()),
+            "cpu_baseline": {"value": T / sec, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": "3 passes of the same 576-row batch, oracle/torch_path.py on the host CPU"}}
+
+
+def run_sweep(args):
+    """The sweep benchmark configuration 2 describes: decode batches 1 / 8 / 32 / 128 / 256, link credits 1..16
+    and both kernel forms for host-resident experts (row blocks of 64, and the one-pass form the reference's
+    asymmetric form maps to).  Per point: layer time (CUDA events over `--steps` passes of the stream path,
+    inputs resident, the input batches rotating), tokens/s, activated hot / cold experts and the host-link rate
+    = cold experts x 9.44 MB / time.  A text table on stderr, one JSON line on stdout."""
+    from monoserve_b200.moe import MoELayer
+    H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
+    torch.cuda.set_device(0)
+    wl = make_workload()
+    layer = MoELayer(H, I, E, K, BATCH)
+    layer.set_router(wl["wr"].cuda())
+    layer.set_experts(wl["w13"], wl["w2"], wl["hot"])
+    xs, x2s = [x.cuda() for x in wl["xs"]], [x.cuda() for x in wl["x2s"]]
+    expert_bytes, hot, rows = 3 * H * I * 2, set(wl["hot"]), []
+    for T in (1, 8, 32, 128, 256):
+        out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+        for form in (64, 0):
+            for credits in (1, 2, 4, 8, 16):
+                layer.set_plan(0, credits, form)
+
+                def step(i):
+                    layer.forward(xs[i % N_BATCHES][:T].contiguous(), x2s[i % N_BATCHES][:T].contiguous(), out)
+                for i in range(3):
+                    step(i)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for i in range(args.steps):
+                    step(i)
+                b.record()
+                b.synchronize()
+                layer.status()
+                cold_sum = hot_sum = 0
+                n = min(N_BATCHES, args.steps)
+                for i in range(n):      # activated experts of the batches used
+                    step(i)
+                    counts = layer.workspace("counts")[:E].cpu()
+                    act = [e for e in range(E) if counts[e] > 0]
+                    cold_sum += sum(1 for e in act if e not in hot)
+                    hot_sum += sum(1 for e in act if e in hot)
+                ms = a.elapsed_time(b) / args.steps
+                rows.append(dict(batch=T, form=form, credits=credits, ms=ms, tokens_per_s=T / ms * 1e3,
+                                 hot_active=hot_sum / n, cold_active=cold_sum / n,
+                                 host_link_gbs=cold_sum / n * expert_bytes / (ms * 1e-3) / 1e9))
+                r = rows[-1]
+                print(f"batch {T:4d} form {form:3d} credits {credits:2d}: {ms:8.3f} ms  {r['tokens_per_s']:9.0f} tok/s  "
+                      f"cold {r['cold_active']:5.1f} hot {r['hot_active']:5.1f}  link {r['host_link_gbs']:5.1f} GB/s",
+                      file=sys.stderr)
+    print(json.dumps({"workload": "BASELINE config 2 sweep (stream path)", "rows": rows}))
+    layer.close()
+
+
 def run_ours(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -549,19 +671,20 @@ def run_ours(args):
                                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": hbm_ach / pk["hbm_gbs"],
                                     "peak_source": pk["source"], "active_experts": hot_active,
                                     "note": "same batch with all 128 experts in HBM", "kernel_ms": hot_kt,
-                                    # dram__bytes_read + write of one launch from the ncu capture summarised in
-                                    # profiles/expert_gemm_config2_and_all_hot.md (75 active experts there:
-                                    # 708.7 + 4.8 MB against 708 MB of weights, i.e. no re-reads)
-                                    "traffic": 713.5e6, "traffic_algorithmic_ratio": 1.0,
+                                    "algorithmic_bytes": hot_active * w13_bytes, "traffic": None,
                                     "layer_tokens_per_s": BATCH / (hot_ms_step * 1e-3)}
         if cpu_times:
             sec = sum(cpu_times) / len(cpu_times)
             line["cpu_baseline"] = {"value": BATCH / sec, "unit": "tokens/s", "cores": cpu_threads, "kind": "port",
                                     "sample": f"{len(cpu_times)} batches of {BATCH} tokens, whole layer, "
                                               "oracle/torch_path.py on the host CPU"}
+        if world == 1:
+            line["config1"] = run_config1(min(args.steps, 20))
         if world == 1 and not args.no_mixed_lane:
             line["fabric_layer"] = side_run(["monoserve_b200.benchmarks.fabric_layer"], 300)
-            line["mixed_lane"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--steps", "6"], 900)
+            line["attention"] = side_run(["monoserve_b200.benchmarks.attention"], 300)
+            line["mixed_lane"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--steps", "20"], 900)
+            line["config4"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--model", "glm", "--steps", "8"], 900)
         print(json.dumps(line), flush=True)
     layer.close()
     if world > 1:
@@ -569,12 +692,14 @@ def run_ours(args):
 
 
 def side_run(module_args, timeout_s):
-    """Two more measurements ride on the N = 1 line, each made by a module of
+    """More measurements ride on the N = 1 line, each made by a module of
     monoserve_b200/benchmarks in a process of its own: `fabric_layer`, the same MoE layer as a
     repeating fabric program timed by the in-kernel iteration timer (the reference's protocol for
-    MoE-layer tokens/s), and `mixed_lane`, the second headline metric: decode TPOT p50
+    MoE-layer tokens/s); `attention`, the paged-KV attention kernel on config-3 shapes (decode
+    K+V GB/s, prefill TFLOP/s); `mixed_lane`, the second headline metric: decode TPOT p50
     on config 3 (the full 48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a
-    128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory)."""
+    128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory); and `config4`,
+    the same for the GLM-4.5-Air-shaped FP8 decoder of config 4."""
     cmd = [sys.executable, "-m"] + module_args
     try:
         out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s,
@@ -597,10 +722,15 @@ def main():
                     help="profiling target: only W warm-up + K device-resident steps, no JSON line")
     ap.add_argument("--all-hot", action="store_true", help="with --ncu: place all 128 experts in HBM")
     ap.add_argument("--no-mixed-lane", action="store_true",
-                    help="skip the fabric-path runs that the N=1 line carries as `fabric_layer` and `mixed_lane`")
+                    help="skip the side runs that the N=1 line carries (`fabric_layer`, `attention`, `mixed_lane`, "
+                         "`config4`)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="the batch x credits x form sweep of benchmark configuration 2 instead of the bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.ncu:
+    if args.sweep:
+        run_sweep(args)
+    elif args.ncu:
         run_profile_target(args)
     elif args.impl == "reference":
         run_reference(args)

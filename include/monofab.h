@@ -424,6 +424,17 @@ int monofab_host_loop_inject(monofab_host_loop* h, int lane_index, uint64_t mark
 int monofab_host_loop_step(monofab_host_loop* h);
 int monofab_host_loop_log(monofab_host_loop* h, int32_t* out, int cap, int* n);
 
+/* ---- deferred releases ---------------------------------------------------------
+ * Freeing device or pinned memory and destroying streams synchronises the device, which
+ * would wait for a resident fabric kernel.  Every release inside this library therefore
+ * goes through one registry per device: at once when no fabric kernel runs there, else
+ * queued until the last one has stopped (the reference's release_when_idle,
+ * csrc/host/fabric.cpp:20-59,150-158).  This entry point drives and reads that registry
+ * without a GPU, for tests: op 0 = as if a fabric had started on `device`, 1 = as if it
+ * had stopped, 2 = hand in a release that only counts itself, 3 = out[0] queued
+ * releases, out[1] counting releases carried out so far, out[2] fabrics running. */
+int monofab_release_debug(int op, int device, uint64_t* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,7 +32,7 @@ EXPORTS = [
     "monofab_host_loop_log",
     "monofab_ep_create", "monofab_ep_local", "monofab_ep_export", "monofab_ep_connect", "monofab_ep_disconnect",
     "monofab_ep_destroy", "monofab_ep_set_router", "monofab_ep_forward", "monofab_ep_phase", "monofab_ep_workspace",
-    "monofab_ep_set_profile", "monofab_ep_last_times", "monofab_ep_dest_base",
+    "monofab_ep_set_profile", "monofab_ep_last_times", "monofab_ep_dest_base", "monofab_release_debug",
 ]
 EP_HANDLE_BYTES = 256   # MONOFAB_EP_HANDLE_BYTES
 
@@ -130,6 +130,7 @@ def _load():
     lib.monofab_ep_set_profile.argtypes = [vp, i32]
     lib.monofab_ep_last_times.argtypes = [vp, P(ctypes.c_float * 8)]
     lib.monofab_ep_dest_base.argtypes = [vp, i32, i32, i32, i32, i32]
+    lib.monofab_release_debug.argtypes = [i32, i32, P(u64 * 3)]
     return lib
 
 

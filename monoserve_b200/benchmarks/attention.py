@@ -86,6 +86,16 @@ def main():
         flops = 4 * hq * 128 * sum(n * (n + 1) // 2 for n in plens)
         line["prefill"] = {"prompts": plens, "page": args.page, "items": int(plan.items.shape[0]), "us": sec * 1e6,
                            "tflops": flops / sec / 1e12}
+    import os
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    # fractions of the peaks measured on this pool (a copy and a cuBLAS bf16 GEMM), else of an earlier measurement
+    pk, src = (json.load(open(peaks)), "measured") if os.path.exists(peaks) else \
+        ({"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback")
+    if "decode" in line:
+        line["decode"]["hbm_frac"] = line["decode"]["kv_gbs"] / pk["hbm_gbs"]
+    if "prefill" in line:
+        line["prefill"]["bf16_frac"] = line["prefill"]["tflops"] / pk["bf16_tflops"]
+    line["peaks"] = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": src}
     print(json.dumps(line))
 
 

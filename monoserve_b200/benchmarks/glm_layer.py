@@ -29,7 +29,13 @@ def main():
     ap.add_argument("--only", choices=["both", "decode", "prefill"], default="both")
     args = ap.parse_args()
     from monoserve_b200.moe import MoELayer
-    from oracle import torch_path as tp            # the checker of the 64-row sample only
+
+    def bf(t):
+        return t.to(torch.bfloat16).float()
+
+    def ffn(x, w13, w2):   # SwiGLU expert with the bf16-rounded hidden of tests/test_fabric_model_glm.py:29-31
+        width = w13.shape[0] // 2
+        return bf(torch.nn.functional.silu(x @ w13[:width].t()) * (x @ w13[width:].t())) @ w2.t()
     H, I, E, K = 4096, 1408, 128, 8
     g = torch.Generator(device="cuda").manual_seed(0)
     q13 = torch.empty(E, 2 * I, H, dtype=torch.uint8, pin_memory=True)
@@ -95,8 +101,8 @@ def main():
             acc = torch.zeros(H, device="cuda")
             for k in range(K):
                 d13, d2 = weights(int(ids[t, k]))
-                acc += float(tw[t, k]) * tp.ffn(x, d13, d2)[0]
-            ref.append(tp.bf(x2[t].float() + acc))
+                acc += float(tw[t, k]) * ffn(x, d13, d2)[0]
+            ref.append(bf(x2[t].float() + acc))
         ref = torch.stack(ref)
         rel = float((out[sample].float() - ref).norm() / ref.norm())
         del deq

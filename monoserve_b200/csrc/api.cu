@@ -14,6 +14,7 @@
 #include "../../include/monofab.h"
 #include "kernels.h"
 #include "moe_layer.h"
+#include "release.h"
 #include "operands.h"
 
 namespace mf {
@@ -531,11 +532,13 @@ int monofab_moe_create(const monofab_moe_config* cfg, monofab_moe** out) {
 
 int monofab_moe_destroy(monofab_moe* m) {
   if (!m) return MONOFAB_OK;
-  cudaDeviceSynchronize();
-  for (void* p : m->owned) cudaFree(p);
-  if (m->status_host) cudaFreeHost(m->status_host);
-  for (cudaEvent_t e : m->ev)
-    if (e) cudaEventDestroy(e);
+  // With a fabric kernel resident on the device nothing here may synchronise it: the buffers are
+  // handed to the release registry and freed when that kernel has left.  Otherwise wait for the
+  // layer's own kernels first, then free.
+  if (!fabrics_running(m->device)) cudaDeviceSynchronize();
+  for (void* p : m->owned) release_device(m->device, p);
+  release_host(m->device, m->status_host);
+  for (cudaEvent_t e : m->ev) release_event(m->device, e);
   delete m;
   return MONOFAB_OK;
 }

@@ -140,13 +140,11 @@ cudaError_t read_attention_trace(unsigned long long out[8]) {
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream) {
   if (p.n_items == 0) return cudaSuccess;
-  static bool attr = false;
-  if (!attr) {
-    const cudaError_t err =
-        cudaFuncSetAttribute(paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
-    if (err != cudaSuccess) return err;
-    attr = true;
-  }
+  static PerDeviceOnce once;
+  const cudaError_t err = once.run([] {
+    return cudaFuncSetAttribute(paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
+  });
+  if (err != cudaSuccess) return err;
   paged_attention_kernel<<<p.n_items, kAttnThreads, kAttnSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }

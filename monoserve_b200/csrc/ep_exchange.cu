@@ -42,6 +42,7 @@
 
 #include "moe_layer.h"
 #include "peer_sync.cuh"
+#include "release.h"
 
 namespace mf {
 
@@ -557,7 +558,7 @@ int monofab_ep_connect(monofab_ep* ep, const void* handles) {
 int monofab_ep_disconnect(monofab_ep* ep) {
   if (!ep) return MONOFAB_OK;
   std::lock_guard<std::mutex> lock(ep->mu);
-  cudaDeviceSynchronize();
+  if (ep->n_ipc && !fabrics_running(ep->device)) cudaDeviceSynchronize();
   for (int i = 0; i < ep->n_ipc; ++i) cudaIpcCloseMemHandle(ep->ipc_open[i]);
   ep->n_ipc = 0;
   ep->connected = false;
@@ -567,9 +568,9 @@ int monofab_ep_disconnect(monofab_ep* ep) {
 int monofab_ep_destroy(monofab_ep* ep) {
   if (!ep) return MONOFAB_OK;
   monofab_ep_disconnect(ep);
-  for (void* p : ep->owned) cudaFree(p);
-  for (cudaEvent_t e : ep->ev)
-    if (e) cudaEventDestroy(e);
+  if (!fabrics_running(ep->device)) cudaDeviceSynchronize();
+  for (void* p : ep->owned) release_device(ep->device, p);
+  for (cudaEvent_t e : ep->ev) release_event(ep->device, e);
   if (ep->local) monofab_moe_destroy(ep->local);
   delete ep;
   return MONOFAB_OK;

@@ -300,16 +300,16 @@ cudaError_t launch_pack_w13(const void* src, void* dst, int n, int I, int H, int
 }
 
 cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t stream) {
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce once;
+  const cudaError_t attr_err = once.run([] {
     cudaError_t err = cudaFuncSetAttribute(expert_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kGemmSmemBytes);
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(expert_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kGemmSmemBytes);
-    if (err != cudaSuccess) return err;
-    attr = true;
-  }
+    return err;
+  });
+  if (attr_err != cudaSuccess) return attr_err;
   if (p.ph[0].w_fp8)
     expert_gemm_kernel<true><<<ctas, kGemmThreadsFp8, kGemmSmemBytes, stream>>>(p);
   else

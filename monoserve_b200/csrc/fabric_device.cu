@@ -1644,13 +1644,11 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
 }
 
 cudaError_t launch_fabric(DeviceState* S, int workers, uint32_t first_worker, cudaStream_t stream) {
-  static bool attr = false;
-  if (!attr) {
-    const cudaError_t err =
-        cudaFuncSetAttribute(fabric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
-    if (err != cudaSuccess) return err;
-    attr = true;
-  }
+  static PerDeviceOnce once;
+  const cudaError_t err = once.run([] {
+    return cudaFuncSetAttribute(fabric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+  });
+  if (err != cudaSuccess) return err;
   fabric_kernel<<<workers, kWorkerThreads, kGemmSmemBytes, stream>>>(S, first_worker);
   return cudaGetLastError();
 }

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "../../include/monofab.h"
+#include "release.h"
 #include "fabric_types.h"
 
 namespace mf {
@@ -151,6 +152,7 @@ static int stop_locked(monofab_fabric* f) {
   if (int r = to_device(f, &f->state->shutdown, &one, 4)) return r;
   MF_CUDA(cudaStreamSynchronize(f->run_stream));
   f->running = false;
+  fabric_stopped(f->device);   // carries out the releases that were queued while this kernel was resident
   return MONOFAB_OK;
 }
 
@@ -205,13 +207,14 @@ int monofab_fabric_destroy(monofab_fabric* f) {
     std::lock_guard<std::mutex> lock(f->mu);
     stop_locked(f);
   }
-  if (f->state) cudaFree(f->state);
-  if (f->pool) cudaFree(f->pool);
-  if (f->map_table) cudaFree(f->map_table);
-  if (f->mirror) cudaFreeHost(f->mirror);
-  if (f->staging) cudaFreeHost(f->staging);
-  if (f->run_stream) cudaStreamDestroy(f->run_stream);
-  if (f->ctrl) cudaStreamDestroy(f->ctrl);
+  // another fabric may still be resident on this device: its releases wait for it
+  release_device(f->device, f->state);
+  release_device(f->device, f->pool);
+  release_device(f->device, f->map_table);
+  release_host(f->device, f->mirror);
+  release_host(f->device, f->staging);
+  release_stream(f->device, f->run_stream);
+  release_stream(f->device, f->ctrl);
   delete f;
   return MONOFAB_OK;
 }
@@ -235,6 +238,7 @@ int monofab_fabric_start(monofab_fabric* f) {
   if (int r = to_device(f, &f->state->shutdown, &zero, 4)) return r;
   MF_CUDA(launch_fabric(f->state, f->num_workers, 0, f->run_stream));
   f->running = true;
+  fabric_started(f->device);
   return MONOFAB_OK;
 }
 

@@ -32,6 +32,7 @@
 #include <vector>
 
 #include "../../include/monofab.h"
+#include "release.h"
 #include "fabric_types.h"
 
 namespace mf {
@@ -340,10 +341,10 @@ int monofab_host_loop_destroy(monofab_host_loop* h) {
   monofab_host_loop_stop(h);
   if (h->fab) {
     cudaSetDevice(h->device);
-    for (StagedLane& s : h->lanes)
-      if (s.landed) cudaEventDestroy(s.landed);
-    if (h->stream) cudaStreamDestroy(h->stream);
-    if (h->entry_ring) cudaFreeHost(h->entry_ring);
+    // the fabric this loop served may still be resident: then these wait until it has stopped
+    for (StagedLane& s : h->lanes) release_event(h->device, s.landed);
+    release_stream(h->device, h->stream);
+    release_host(h->device, h->entry_ring);
   }
   delete h;
   return MONOFAB_OK;

@@ -4,11 +4,35 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "types.h"
 
 namespace mf {
 
 using bf16 = __nv_bfloat16;
+
+// A function attribute (dynamic shared memory above 48 KB) belongs to a device's context, so it is
+// set once per DEVICE, not once per process: `configure` runs under a lock the first time the
+// current device launches the kernel.
+struct PerDeviceOnce {
+  std::mutex mu;
+  std::atomic<unsigned long long> done{0};
+  template <class F>
+  cudaError_t run(F configure) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.load(std::memory_order_relaxed) & bit) return cudaSuccess;
+    err = configure();
+    if (err == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return err;
+  }
+};
 
 struct RouterParams {
   float* logits;            // fp32 [T][E]; zeroed after reading when zero_logits is set

@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("MONOSERVE_REFERENCE", os.path.join(os.path.sep, "root", "reference"))
+REF = os.environ.get("MONOSERVE_REFERENCE")   # checkout of the reference project; required to (re)generate
 
 
 @contextmanager
@@ -255,6 +255,8 @@ def program_fixture():
 
 
 if __name__ == "__main__":
+    if not REF or not os.path.isdir(REF):
+        sys.exit("set MONOSERVE_REFERENCE to a checkout of the reference project to regenerate the fixtures")
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     qwen_fixture()
     glm_fixture()

@@ -71,3 +71,32 @@ def test_no_cpu_fallback():
     from monoserve_b200.moe import MoELayer
     with pytest.raises(RuntimeError, match="CUDA device is required"):
         MoELayer(256, 64, 8, 2, 4)
+
+
+def test_releases_wait_for_a_resident_fabric():
+    """The deferred-release registry without a GPU: a release handed in while a fabric counts as
+    running on the device is queued, survives the stop of one of two fabrics, and is carried out
+    when the last one stops; with none running it is carried out at once."""
+    import ctypes
+    from monoserve_b200 import _C
+    dev = 63    # a device index nothing else in the tests uses
+
+    def state():
+        out = (ctypes.c_uint64 * 3)()
+        assert _C.lib.monofab_release_debug(3, dev, ctypes.byref(out)) == 0
+        return list(out)
+
+    queued0, done0, running0 = state()
+    assert (queued0, running0) == (0, 0)
+    assert _C.lib.monofab_release_debug(2, dev, None) == 0            # nothing resident: at once
+    assert state() == [0, done0 + 1, 0]
+    _C.lib.monofab_release_debug(0, dev, None)                         # two fabrics start
+    _C.lib.monofab_release_debug(0, dev, None)
+    for _ in range(3):
+        _C.lib.monofab_release_debug(2, dev, None)
+    assert state() == [3, done0 + 1, 2]
+    _C.lib.monofab_release_debug(1, dev, None)                         # one stops: still queued
+    assert state() == [3, done0 + 1, 1]
+    _C.lib.monofab_release_debug(1, dev, None)                         # the last one stops: drained
+    assert state() == [0, done0 + 4, 0]
+    assert _C.lib.monofab_release_debug(3, 64, None) != 0              # device index out of range

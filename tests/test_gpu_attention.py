@@ -134,3 +134,33 @@ def test_split_kv_matches_dense_and_unsplit(hq, hkv, part_tiles):
         assert (out[row:row + n] - ref).abs().max().item() < TOL, r
         assert (whole[row:row + n] - ref).abs().max().item() < TOL, r
         row += n
+
+
+@pytest.mark.parametrize("hq,hkv,lens,prompt", [(32, 4, [8192, 512, 6000], 2048), (96, 8, [16384, 1024], 4096)])
+def test_full_size_contexts(hq, hkv, lens, prompt):
+    """The context lengths and head layouts of the full-model benchmark configurations, page size
+    16: decode rows at the longest contexts (8192 keys with 32 / 4 heads, 16384 with 96 / 8) and
+    a whole prompt (2048 / 4096 tokens), planned as the benchmark plans them (split over key
+    ranges, merged).  Prompt rows are checked on a sample of query blocks to bound the CPU time."""
+    from monoserve_b200.attention import paged_attention
+    all_lens = lens + [prompt]
+    rows = [1] * len(lens) + [prompt]
+    kc, vc, bt, dense = make_cache(all_lens, hkv, 16, seed=hq + 5)
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(sum(rows), hq, 128, generator=g).to(torch.bfloat16)
+    req_info, row = [], 0
+    for n, L in zip(rows, all_lens):
+        req_info.append((row, L - n, n, L))
+        row += n
+    out = paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), req_info).float().cpu()
+    row = 0
+    for r, (n, L) in enumerate(zip(rows, all_lens)):
+        if n == 1:
+            ref = dense_reference(q[row:row + 1].float(), dense[r][0], dense[r][1], hq, hkv, L - 1)
+            assert (out[row:row + 1] - ref).abs().max().item() < TOL, r
+        else:
+            for lo in (0, n // 2 - 64, n - 128):     # first, middle and last query blocks of the prompt
+                ref = dense_reference(q[row + lo:row + lo + 128].float(), dense[r][0][:lo + 128], dense[r][1][:lo + 128],
+                                      hq, hkv, lo)
+                assert (out[row + lo:row + lo + 128] - ref).abs().max().item() < TOL, (r, lo)
+        row += n

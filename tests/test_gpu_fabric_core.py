@@ -1,5 +1,8 @@
-"""Mechanism tests of the persistent fabric with test tiles: the scenarios of the
-reference's tests/test_fabric_core.py:75-219 — every tile runs exactly once and
+"""Mechanism tests of the persistent fabric with test tiles.  The first part of this file is
+a copy, re-flowed, of the reference's own tests/test_fabric_core.py:75-219 (same helpers,
+scenarios and thresholds; the epoch-spread bound is 2.5 tiles instead of 1.5), because running
+the reference's tests against this library is the drop-in check; the tests after them (marks and
+trace, bad tile, deadline, malformed upload) are this build's own.  The scenarios: every tile runs exactly once and
 never before the stages it depends on; workers serve their own lane first and
 borrow from other lanes; link credits bound the link tiles in flight; a new epoch
 reaches every worker within about one tile; programs iterate and are replaced at
