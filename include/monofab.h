@@ -306,6 +306,13 @@ int monofab_fabric_info(monofab_fabric* f, int32_t* num_workers, int32_t* num_sm
 int monofab_fabric_start(monofab_fabric* f);
 int monofab_fabric_stop(monofab_fabric* f);
 
+/* Launch workers [first_worker, first_worker + workers) of the persistent kernel on the caller's
+ * stream, optionally inside a driver context (a green context's CUcontext, 0 = none): the way a
+ * fabric is started beside other work, or as several partitions (Fabric.start_on,
+ * csrc/bindings.cpp:189-190, csrc/host/fabric.cpp:204-227).  monofab_fabric_stop waits for every
+ * such launch. */
+int monofab_fabric_start_on(monofab_fabric* f, uint64_t stream, uint64_t context, int workers, int first_worker);
+
 /* Longest idle back-off of a worker (Fabric.set_idle_cap, csrc/host/fabric.h:50), and
  * the run-time limit after which the kernel leaves on its own with
  * MONOFAB_FABRIC_ERR_DEADLINE (default 120 s, 0 = no limit; no counterpart in the
@@ -355,6 +362,12 @@ int monofab_fabric_blob_free(monofab_fabric* f, uint64_t addr);
 int monofab_fabric_set_trace(monofab_fabric* f, uint64_t ptr, uint32_t capacity);
 int monofab_fabric_trace_count(monofab_fabric* f, uint32_t* count);
 
+/* A lane's ring of activated stages (link != 0: the ring of its link-gated stages):
+ * counters = head, tail, reserve; up to max_entries waiting entries, oldest first, each
+ * tag << 20 | stage (Fabric.lane_ring, csrc/bindings.cpp:255-265, csrc/host/fabric.cpp:418-434). */
+int monofab_fabric_lane_ring(monofab_fabric* f, int lane, int link, int max_entries, uint64_t counters[3],
+                             uint32_t* entries, int* n_entries);
+
 /* What every worker is doing, for hang diagnosis: 256 state words and the device
  * time each state began (Fabric.worker_tiles, csrc/bindings.cpp:266-281). */
 int monofab_fabric_worker_tiles(monofab_fabric* f, uint64_t* words, uint64_t* since_ns);
@@ -366,6 +379,8 @@ int monofab_fabric_worker_tiles(monofab_fabric* f, uint64_t* words, uint64_t* si
  * The counterpart of the reference's per-warp wait notes (wait_note_address,
  * csrc/bindings.cpp:182, csrc/fabric/runtime.cuh:511-555). */
 int monofab_fabric_wait_notes(monofab_fabric* f, uint64_t* notes);
+/* Device address of those 256 x 4 words (wait_note_address, csrc/bindings.cpp:182). */
+int monofab_fabric_wait_note_address(monofab_fabric* f, uint64_t* addr);
 
 /* Device end times of `count` iterations of a lane after iteration `start`, taken
  * from the in-kernel timer (Fabric.iteration_times, csrc/host/fabric.cpp:380-403). */

@@ -27,6 +27,7 @@ EXPORTS = [
     "monofab_fabric_reset_inflight_max", "monofab_fabric_wait_notes", "monofab_fabric_read", "monofab_fabric_write", "monofab_fabric_blob_alloc",
     "monofab_fabric_blob_free", "monofab_fabric_set_trace", "monofab_fabric_trace_count",
     "monofab_fabric_worker_tiles", "monofab_fabric_iteration_times", "monofab_fabric_tensor_map", "monofab_fabric_tensor_map_packed",
+    "monofab_fabric_start_on", "monofab_fabric_lane_ring", "monofab_fabric_wait_note_address",
     "monofab_host_loop_create", "monofab_host_loop_add_lane", "monofab_host_loop_start", "monofab_host_loop_stop",
     "monofab_host_loop_stats", "monofab_host_loop_destroy", "monofab_host_loop_inject", "monofab_host_loop_step",
     "monofab_host_loop_log",
@@ -88,6 +89,9 @@ def _load():
     lib.monofab_fabric_info.argtypes = [vp, P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32), P(u64)]
     lib.monofab_fabric_start.argtypes = [vp]
     lib.monofab_fabric_stop.argtypes = [vp]
+    lib.monofab_fabric_start_on.argtypes = [vp, u64, u64, i32, i32]
+    lib.monofab_fabric_lane_ring.argtypes = [vp, i32, i32, i32, P(u64 * 3), vp, P(i32)]
+    lib.monofab_fabric_wait_note_address.argtypes = [vp, P(u64)]
     lib.monofab_fabric_set_limits.argtypes = [vp, u32, u64]
     lib.monofab_fabric_upload.argtypes = [vp, vp, i32, vp, i32, vp, i32, i32, i32, i32, P(u64)]
     lib.monofab_fabric_release.argtypes = [vp, u64]

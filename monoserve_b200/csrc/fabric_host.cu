@@ -71,6 +71,7 @@ struct monofab_fabric {
   CUtensorMap* map_table = nullptr;      // device: records of 4 slots each
   int map_count = 0, map_cap = 4096;
   uint64_t lane_handle[kMaxLanes] = {0, 0, 0, 0};
+  std::vector<cudaStream_t> caller_streams;   // launches made by start_on, waited for by stop
 };
 
 namespace mf {
@@ -151,6 +152,8 @@ static int stop_locked(monofab_fabric* f) {
   const unsigned int one = 1;
   if (int r = to_device(f, &f->state->shutdown, &one, 4)) return r;
   MF_CUDA(cudaStreamSynchronize(f->run_stream));
+  for (cudaStream_t st : f->caller_streams) MF_CUDA(cudaStreamSynchronize(st));
+  f->caller_streams.clear();
   f->running = false;
   fabric_stopped(f->device);   // carries out the releases that were queued while this kernel was resident
   return MONOFAB_OK;
@@ -239,6 +242,74 @@ int monofab_fabric_start(monofab_fabric* f) {
   MF_CUDA(launch_fabric(f->state, f->num_workers, 0, f->run_stream));
   f->running = true;
   fabric_started(f->device);
+  return MONOFAB_OK;
+}
+
+int monofab_fabric_start_on(monofab_fabric* f, uint64_t stream, uint64_t context, int workers, int first_worker) {
+  if (!f) return fail(MONOFAB_EINVAL, "fabric_start_on: NULL handle");
+  std::lock_guard<std::mutex> lock(f->mu);
+  if (workers <= 0 || first_worker < 0 || first_worker + workers > f->num_workers)
+    return fail(MONOFAB_EINVAL, "fabric_start_on: workers [%d, %d) outside [0, %d)", first_worker, first_worker + workers,
+                f->num_workers);
+  MF_CUDA(cudaSetDevice(f->device));
+  if (!f->running) {
+    const unsigned int zero = 0;
+    if (int r = to_device(f, &f->state->shutdown, &zero, 4)) return r;
+  }
+  // An optional driver context (a green context's) is made current around the launch.
+  typedef CUresult (*PushFn)(CUcontext);
+  typedef CUresult (*PopFn)(CUcontext*);
+  PushFn push = nullptr;
+  PopFn pop = nullptr;
+  if (context) {
+    void *a = nullptr, *b = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxPushCurrent", &a, cudaEnableDefault, &q) != cudaSuccess ||
+        cudaGetDriverEntryPoint("cuCtxPopCurrent", &b, cudaEnableDefault, &q) != cudaSuccess || !a || !b)
+      return fail(MONOFAB_ECUDA, "fabric_start_on: the driver's context calls are not available");
+    push = reinterpret_cast<PushFn>(a);
+    pop = reinterpret_cast<PopFn>(b);
+    if (push(reinterpret_cast<CUcontext>(context)) != CUDA_SUCCESS) return fail(MONOFAB_ECUDA, "fabric_start_on: context push failed");
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const cudaError_t e = launch_fabric(f->state, workers, static_cast<uint32_t>(first_worker), st);
+  if (context) {
+    CUcontext prev;
+    pop(&prev);
+  }
+  if (e != cudaSuccess) return fail(MONOFAB_ECUDA, "fabric_start_on: launch: %s", cudaGetErrorString(e));
+  f->caller_streams.push_back(st);
+  if (!f->running) fabric_started(f->device);
+  f->running = true;
+  return MONOFAB_OK;
+}
+
+int monofab_fabric_lane_ring(monofab_fabric* f, int lane, int link, int max_entries, uint64_t counters[3],
+                             uint32_t* entries, int* n_entries) {
+  if (!f || !counters || !n_entries) return fail(MONOFAB_EINVAL, "fabric_lane_ring: NULL argument");
+  if (lane < 0 || lane >= kMaxLanes) return fail(MONOFAB_EINVAL, "fabric_lane_ring: lane %d", lane);
+  std::lock_guard<std::mutex> lock(f->mu);
+  const Ring* ring = &f->state->lane[lane].ring[link ? 1 : 0];
+  unsigned long long head = 0, tail = 0, reserve = 0;
+  if (int r = from_device(f, &head, &ring->head, 8)) return r;
+  if (int r = from_device(f, &tail, &ring->tail, 8)) return r;
+  if (int r = from_device(f, &reserve, &ring->reserve, 8)) return r;
+  counters[0] = head;
+  counters[1] = tail;
+  counters[2] = reserve;
+  int n = 0;
+  if (entries && tail > head && max_entries > 0) {
+    std::vector<unsigned int> ids(kRingCap);
+    if (int r = from_device(f, ids.data(), ring->ids, sizeof(unsigned int) * kRingCap)) return r;
+    for (unsigned long long p = head; p < tail && n < max_entries; ++p) entries[n++] = ids[p & (kRingCap - 1)];
+  }
+  *n_entries = n;
+  return MONOFAB_OK;
+}
+
+int monofab_fabric_wait_note_address(monofab_fabric* f, uint64_t* addr) {
+  if (!f || !addr) return fail(MONOFAB_EINVAL, "fabric_wait_note_address: NULL argument");
+  *addr = reinterpret_cast<uint64_t>(&f->state->worker_wait[0][0]);
   return MONOFAB_OK;
 }
 
