@@ -601,7 +601,10 @@ int monofab_fabric_tensor_map(monofab_fabric* f, uint64_t base, const uint64_t* 
   std::memset(rec, 0, sizeof rec);
   if (int r = encode_map(&rec[0], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, box, swizzle)) return r;
   if (rank == 3 && box[2] == 1) {
-    const uint32_t b16[3] = {box[0], 16, 1}, b128[3] = {box[0], 128, 1};
+    // e4m3 weights: a stage of the GEMM holds two 64-element K steps, i.e. rows of 128 bytes, whatever
+    // K extent the caller's box has (the reference's own maps ask for 64 x 64 bytes)
+    const uint32_t kbox = dtype == 2 ? 128 : box[0];
+    const uint32_t b16[3] = {kbox, 16, 1}, b128[3] = {kbox, 128, 1};
     if (int r = encode_map(&rec[1], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b16, swizzle)) return r;
     if (int r = encode_map(&rec[2], dtype, reinterpret_cast<const void*>(base), rank, dims, strides_bytes, b128, swizzle)) return r;
   }

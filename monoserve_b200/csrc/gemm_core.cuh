@@ -221,7 +221,7 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
       pipe.advance();
       continue;
     }
-    // a K step past the end of an odd K range reads zeros (out-of-bounds fill) and adds nothing
+    // the second K step of an odd K range's last stage is loaded but not multiplied (gemm_mma)
     if (lane == 0) mbar_arrive_expect_tx(full, tx_bytes);
     __syncwarp();
     const int x = (k0 + st * ks) * kBlockK;
@@ -258,6 +258,7 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
     const uint32_t b_bytes = w.n * kBlockK * 2;
     // read once: the record lives in shared memory and every wait below is a memory barrier to the compiler
     const bool fp8 = w.w_fp8 != 0, fetch = kFetch && w.fetch != 0;
+    const int k_steps = w.k_tiles;
     const uint32_t fetch_bytes = kFetch ? w.fetch_bytes : 0;
     uint8_t* const fetch_out = static_cast<uint8_t*>(w.out);
     for (int kt = 0; ok && kt < n_stages; ++kt) {
@@ -292,9 +293,13 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
         const uint64_t db = da + (2 * kATileBytes >> 4);
 #pragma unroll
         for (int k = 0; k < kBlockK / 16; ++k) umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kt | k) != 0);
+        // the last stage of an odd K range holds one K step of the range; its second half belongs to the
+        // next range (a K split) or lies past the tensor, and is left out
+        if (2 * kt + 1 < k_steps) {
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k)
-          umma_bf16(acc, da + (kATileBytes >> 4) + 2 * k, db + (b_bytes >> 4) + 2 * k, idesc, true);
+          for (int k = 0; k < kBlockK / 16; ++k)
+            umma_bf16(acc, da + (kATileBytes >> 4) + 2 * k, db + (b_bytes >> 4) + 2 * k, idesc, true);
+        }
       }
       umma_commit(&bar.empty[pipe.slot]);
       if (wait_cycles) wait_cycles[1] += clock64() - ti;
