@@ -439,6 +439,60 @@ int monofab_host_loop_inject(monofab_host_loop* h, int lane_index, uint64_t mark
 int monofab_host_loop_step(monofab_host_loop* h);
 int monofab_host_loop_log(monofab_host_loop* h, int32_t* out, int cap, int* n);
 
+/* ---- plans: the control plane's time estimator and plan search -------------------
+ * What one lane's remaining work costs at a given SM share, link-credit grant and kernel
+ * form (Estimator, csrc/control/estimator.h:108-145, estimator.cpp:200-258), and the
+ * search for shares / grants / forms that keep every lane's deadline (PlanSearch,
+ * csrc/control/search.h:46-88, search.cpp:184-334); bound in the reference as
+ * monoserve._C.control (csrc/control/py_control.cpp:10-254).  Host code only: none of
+ * these touches a GPU.  Structured arguments are flat arrays of doubles:
+ *   model [MONOFAB_PLAN_MODEL_FIELDS]: hidden, intermediate, experts, top_k, layers, heads,
+ *     kv_heads, head_dim, vocab, dense_layers, dense_intermediate, shared_intermediate,
+ *     expert_weight_bytes, dense_weight_bytes
+ *   curve: n, through_origin, x[n], y[n]     rates: flops curve, bytes curve, q_per_sm
+ *   calibration: sms, R_H, R_C, q_max, link peak (bytes/s), reference form, layer overhead,
+ *     tail overhead, one-pass rows, one-pass bytes per row (< 0: the reference's K-split
+ *     formula); stretch curve; rates of dense, prefill attention, decode attention;
+ *     n, (form, rates) x n; n, (form, link-rate curve) x n; n, (form, credits per tile) x n
+ *   work: decode, first_layer, staging, deadline, samples; n, active[n]; n, miss[n];
+ *     passes, per pass: seqs, (tokens, context) x seqs
+ *   estimate [MONOFAB_PLAN_ESTIMATE_FIELDS]: total, attn, moe, staged, a_cmp, a_rd, m_cmp,
+ *     m_rd, m_link
+ *   plan: header [MONOFAB_PLAN_HEADER_FIELDS] = feasible, lanes, copy_rate, min_slack,
+ *     total_time, evaluations, micros, 0; per lane [MONOFAB_PLAN_LANE_FIELDS] = sms,
+ *     credits, form, cap, rate, slack, estimate
+ * Form 0 is the one-pass (the reference's asymmetric) form. */
+#define MONOFAB_PLAN_MODEL_FIELDS 14
+#define MONOFAB_PLAN_ESTIMATE_FIELDS 9
+#define MONOFAB_PLAN_HEADER_FIELDS 8
+#define MONOFAB_PLAN_LANE_FIELDS 15
+typedef struct monofab_plan_estimator monofab_plan_estimator;
+typedef struct monofab_plan_load monofab_plan_load;
+typedef struct monofab_plan_search monofab_plan_search;
+double monofab_plan_curve_at(const double* x, const double* y, int n, int through_origin, double v);
+int monofab_plan_estimator_create(const double* model, int n_model, const double* calibration, int n_calibration,
+                                  int contention_aware, double ewma, monofab_plan_estimator** out);
+int monofab_plan_estimator_destroy(monofab_plan_estimator* e);
+/* out = Q^link (saturating credits), exposure bound, bytes of one expert, KV bytes per token */
+int monofab_plan_estimator_info(monofab_plan_estimator* e, double out[4]);
+double monofab_plan_gamma_ratio(monofab_plan_estimator* e, double own_exposure);
+int monofab_plan_observe(monofab_plan_estimator* e, int decode, int moe, double ratio);
+double monofab_plan_correction(monofab_plan_estimator* e, int decode, int moe);
+int monofab_plan_load_create(monofab_plan_estimator* e, const double* work, int n_work, monofab_plan_load** out);
+int monofab_plan_load_destroy(monofab_plan_load* l);
+int monofab_plan_evaluate(monofab_plan_estimator* e, const monofab_plan_load* l, int share, double credits, int form,
+                          double out[MONOFAB_PLAN_ESTIMATE_FIELDS]);
+/* n_forms 0 / non-positive numbers / negative tolerance = the defaults (forms 16 32 64 128 0; 2; 8; 4; 0.01) */
+int monofab_plan_search_create(monofab_plan_estimator* e, const int32_t* forms, int n_forms, int pour_quantum,
+                               int pour_candidates, int decode_choices, double tolerance, monofab_plan_search** out);
+int monofab_plan_search_destroy(monofab_plan_search* s);
+/* smallest SM share that meets the lane's deadline; sms + 1 if none does */
+int monofab_plan_deadline_floor(monofab_plan_search* s, const monofab_plan_load* l, double credits, int form, int* share);
+/* lanes: at most one decode lane (first) and two prefill lanes; decode_key caches the decode lane's options (0: no cache) */
+int monofab_plan_solve(monofab_plan_search* s, const monofab_plan_load* const* lanes, int n_lanes, uint64_t decode_key,
+                       double* out, int out_cap);
+int monofab_plan_clear_cache(monofab_plan_search* s);
+
 /* ---- deferred releases ---------------------------------------------------------
  * Freeing device or pinned memory and destroying streams synchronises the device, which
  * would wait for a resident fabric kernel.  Every release inside this library therefore

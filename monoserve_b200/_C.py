@@ -34,6 +34,10 @@ EXPORTS = [
     "monofab_ep_create", "monofab_ep_local", "monofab_ep_export", "monofab_ep_connect", "monofab_ep_disconnect",
     "monofab_ep_destroy", "monofab_ep_set_router", "monofab_ep_forward", "monofab_ep_phase", "monofab_ep_workspace",
     "monofab_ep_set_profile", "monofab_ep_last_times", "monofab_ep_dest_base", "monofab_release_debug",
+    "monofab_plan_curve_at", "monofab_plan_estimator_create", "monofab_plan_estimator_destroy", "monofab_plan_estimator_info",
+    "monofab_plan_gamma_ratio", "monofab_plan_observe", "monofab_plan_correction", "monofab_plan_load_create",
+    "monofab_plan_load_destroy", "monofab_plan_evaluate", "monofab_plan_search_create", "monofab_plan_search_destroy",
+    "monofab_plan_deadline_floor", "monofab_plan_solve", "monofab_plan_clear_cache",
 ]
 EP_HANDLE_BYTES = 256   # MONOFAB_EP_HANDLE_BYTES
 
@@ -135,6 +139,25 @@ def _load():
     lib.monofab_ep_last_times.argtypes = [vp, P(ctypes.c_float * 8)]
     lib.monofab_ep_dest_base.argtypes = [vp, i32, i32, i32, i32, i32]
     lib.monofab_release_debug.argtypes = [i32, i32, P(u64 * 3)]
+    f64 = ctypes.c_double
+    lib.monofab_plan_curve_at.restype = f64
+    lib.monofab_plan_curve_at.argtypes = [vp, vp, i32, i32, f64]
+    lib.monofab_plan_estimator_create.argtypes = [vp, i32, vp, i32, i32, f64, P(vp)]
+    lib.monofab_plan_estimator_destroy.argtypes = [vp]
+    lib.monofab_plan_estimator_info.argtypes = [vp, P(f64 * 4)]
+    lib.monofab_plan_gamma_ratio.restype = f64
+    lib.monofab_plan_gamma_ratio.argtypes = [vp, f64]
+    lib.monofab_plan_observe.argtypes = [vp, i32, i32, f64]
+    lib.monofab_plan_correction.restype = f64
+    lib.monofab_plan_correction.argtypes = [vp, i32, i32]
+    lib.monofab_plan_load_create.argtypes = [vp, vp, i32, P(vp)]
+    lib.monofab_plan_load_destroy.argtypes = [vp]
+    lib.monofab_plan_evaluate.argtypes = [vp, vp, i32, f64, i32, P(f64 * 9)]
+    lib.monofab_plan_search_create.argtypes = [vp, vp, i32, i32, i32, i32, f64, P(vp)]
+    lib.monofab_plan_search_destroy.argtypes = [vp]
+    lib.monofab_plan_deadline_floor.argtypes = [vp, vp, f64, i32, P(i32)]
+    lib.monofab_plan_solve.argtypes = [vp, vp, i32, u64, vp, i32]
+    lib.monofab_plan_clear_cache.argtypes = [vp]
     return lib
 
 

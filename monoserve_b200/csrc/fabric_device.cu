@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 
 #include "attention_core.cuh"
+#include "fabric_sched.cuh"
 #include "fabric_types.h"
 #include "gemm_core.cuh"
 #include "operands.h"
@@ -40,66 +41,15 @@
 namespace mf {
 namespace fab {
 
-constexpr uint32_t kStageBits = 20;
-constexpr uint32_t kStageMask = (1u << kStageBits) - 1;
-constexpr uint32_t kTagMask = 0xfffu;
-constexpr int kScanDepth = 16;
-constexpr int kWorklistCap = 512;
-constexpr uint32_t kMaxBatch = 8;
-constexpr uint32_t kBatchDivisor = 128;
 constexpr int kExecThreads = 128;
 constexpr int kSlots = 4;   // work records the scheduler may run ahead of the exec warps
 constexpr int kWorkerThreads = 32 + kExecThreads + 64;   // scheduler, exec/epilogue, TMA producer, MMA
-constexpr unsigned long long kRingWaitBudgetNs = 2000000000ull;
-
-enum : uint32_t { kCmdRun = 0, kCmdIdle = 1, kCmdExit = 2 };
-
-template <class T>
-__device__ __forceinline__ T ld_volatile(const T* p) { return *reinterpret_cast<const volatile T*>(p); }
-
-__device__ __forceinline__ unsigned int ld_acq(const unsigned int* p) { return ld_acquire_gpu(p); }
-__device__ __forceinline__ unsigned long long ld_acq(const unsigned long long* p) { return ld_acquire_gpu64(p); }
-__device__ __forceinline__ void st_rel(unsigned int* p, unsigned int v) { st_release_gpu(p, v); }
-__device__ __forceinline__ void st_rel(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
 
 __device__ __forceinline__ unsigned int smid() {
   unsigned int v;
   asm volatile("mov.u32 %0, %smid;" : "=r"(v));
   return v;
 }
-
-__device__ void raise_error(DeviceState& S, unsigned long long bit) {
-  const unsigned long long now = atomicOr(&S.error, bit) | bit;
-  if (S.mirror) st_release_sys64(&S.mirror->error, now);   // pinned host memory
-}
-
-struct Worklist {
-  uint32_t v[kWorklistCap];
-  int n;
-  bool overflow;
-  __device__ void push(uint32_t s) {
-    if (n < kWorklistCap) v[n++] = s; else overflow = true;
-  }
-  __device__ uint32_t pop() { return v[--n]; }
-};
-
-// Scheduling state of one worker (shared memory, touched by the scheduler thread
-// and, for the lane statistics, by the completing exec thread).
-struct WorkerState {
-  unsigned long long epoch;
-  uint32_t worker, lane, n_lanes, slot_lane, idle_ns;
-  uint32_t cap[kMaxLanes], order[kMaxLanes], prog_gen[kMaxLanes];
-  ProgramDesc* prog_snap[kMaxLanes];
-  // the current claim
-  const ProgramDesc* prog;
-  uint32_t stage, tile_lane, link, next_index, left;
-  // the worker runs its records through a pipeline, behind the scheduler: a link slot is handed
-  // back only when the exec warps have finished the last link record issued under it
-  uint32_t link_last;                  // records issued up to and including the last link record
-  const volatile unsigned int* done;   // records the exec warps have finished
-};
 
 struct WorkSlot {
   TileDesc tile;
@@ -183,446 +133,6 @@ __device__ bool make_fetch_work(const TileDesc& t, GemmWork& w) {
   w.fetch_bytes = t.i0;
   w.fetch_src = reinterpret_cast<const uint8_t*>(t.a[0]);
   return t.i0 > 0 && ((t.i0 | t.a[0] | t.a[1]) & 15) == 0 && t.a[0] != 0 && t.a[1] != 0;
-}
-
-__device__ void trace_stage(DeviceState& S, uint32_t lane, uint32_t s, uint32_t event, uint32_t tag) {
-  const uint32_t cap = ld_volatile(&S.trace_cap);
-  if (cap == 0) return;
-  const uint32_t i = atomicAdd(&S.trace_n, 1u);
-  if (i >= cap) return;
-  unsigned long long* r = reinterpret_cast<unsigned long long*>(ld_volatile(&S.trace_ptr)) + 2ull * i;
-  r[0] = static_cast<unsigned long long>(s) | (static_cast<unsigned long long>(lane) << 32) |
-         (static_cast<unsigned long long>(event) << 40) | (static_cast<unsigned long long>(tag & kTagMask) << 48);
-  r[1] = globaltimer_ns();
-}
-
-__device__ void mirror_lane(DeviceState& S, uint32_t lane, int what, unsigned long long v) {
-  if (!S.mirror) return;
-  LaneMirror& m = S.mirror->lane[lane];
-  switch (what) {
-    case 0: st_release_sys64(&m.iterations, v); break;
-    case 1: st_release_sys64(&m.gen, v); break;
-    case 2: st_release_sys64(&m.running, v); break;
-    case 3:
-      st_release_sys64(&m.mark_ns, globaltimer_ns());
-      st_release_sys64(&m.mark, v);
-      break;
-  }
-}
-
-// ------------------------------------------------------------------- rings
-// Append m entries with one reservation; publish them once every earlier
-// reservation is published.  The wait for earlier producers is bounded.
-__device__ void ring_push_n(DeviceState& S, LaneState& L, bool link, const uint32_t* entries, int m) {
-  if (m == 0) return;
-  Ring& R = L.ring[link ? 1 : 0];
-  const unsigned long long pos = atomicAdd(&R.reserve, static_cast<unsigned long long>(m));
-  for (int i = 0; i < m; ++i) R.ids[(pos + i) & (kRingCap - 1)] = entries[i];
-  unsigned int ns = 32;
-  const unsigned long long t0 = globaltimer_ns();
-  while (ld_acq(&R.tail) != pos) {
-    __nanosleep(ns);
-    if (ns < 512) ns <<= 1;
-    if (globaltimer_ns() - t0 > kRingWaitBudgetNs) {
-      raise_error(S, kFabErrRingWait);
-      return;
-    }
-  }
-  st_rel(&R.tail, pos + m);
-}
-
-__device__ __forceinline__ uint32_t make_entry(uint32_t stage, uint32_t tag) {
-  return ((tag & kTagMask) << kStageBits) | (stage & kStageMask);
-}
-
-// Take the next tiles of the stage an entry names: n tiles from `index`.  Valid
-// only while the stage's runtime still carries the entry's tag.
-__device__ bool claim(const ProgramDesc* P, uint32_t entry, uint32_t& stage, uint32_t& index, uint32_t& n) {
-  const uint32_t s = entry & kStageMask, tag = entry >> kStageBits;
-  if (s >= P->n_stages) return false;
-  uint32_t count = ld_volatile(&P->stages[s].count);
-  unsigned long long* tn = &P->runtime[s].tag_next;
-  const unsigned long long v = ld_acq(tn);
-  const uint32_t next = static_cast<uint32_t>(v);
-  if ((static_cast<uint32_t>(v >> 32) & kTagMask) != tag || next >= count) return false;
-  const uint32_t left = count - next;
-  const uint32_t k = min(left, min(kMaxBatch, max(1u, left / kBatchDivisor)));
-  const unsigned long long old = atomicAdd(tn, static_cast<unsigned long long>(k));
-  const uint32_t ot = static_cast<uint32_t>(old >> 32) & kTagMask, on = static_cast<uint32_t>(old);
-  if (ot == 0) return false;
-  if (ot != tag) count = ld_volatile(&P->stages[s].count);
-  if (on >= count) return false;
-  stage = s;
-  index = ld_volatile(&P->stages[s].first) + on;
-  n = min(k, count - on);
-  return true;
-}
-
-__device__ bool take_from(LaneState& L, bool link, const ProgramDesc* P, uint32_t& stage, uint32_t& index,
-                          uint32_t& n) {
-  Ring& R = L.ring[link ? 1 : 0];
-  unsigned long long h = ld_acq(&R.head);
-  const unsigned long long t = ld_acq(&R.tail);
-  for (unsigned long long p = h; p < t && p < h + kScanDepth; ++p) {
-    const uint32_t e = ld_volatile(&R.ids[p & (kRingCap - 1)]);
-    if (claim(P, e, stage, index, n)) return true;
-    if (p == h) {   // the head entry is stale or exhausted: step past it
-      if (atomicCAS(&R.head, h, h + 1) == h) h = h + 1;
-    }
-  }
-  return false;
-}
-
-// ---------------------------------------------- activation, completion, iterations
-__device__ bool arm(DeviceState& S, uint32_t lane, const ProgramDesc* P, uint32_t s, uint32_t tag, Worklist& wl,
-                    uint32_t& entry, bool& link) {
-  trace_stage(S, lane, s, 0, tag);
-  const uint32_t count = ld_volatile(&P->stages[s].count);
-  if (count == 0) {   // nothing to run: completes at once
-    wl.push(s);
-    return false;
-  }
-  atomicExch(&P->runtime[s].tag_next, static_cast<unsigned long long>(tag & kTagMask) << 32);
-  link = (ld_volatile(&P->stages[s].flags) & kStageLink) != 0;
-  entry = make_entry(s, tag);
-  return true;
-}
-
-__device__ void latest_program(DeviceState& S, uint32_t lane, ProgramDesc*& p, uint32_t& gen) {
-  unsigned long long e = ld_acq(&S.published);
-  for (;;) {
-    const Snapshot& sn = S.snap[e & 1];
-    p = ld_volatile(&sn.prog[lane]);
-    gen = ld_volatile(&sn.prog_gen[lane]);
-    const unsigned long long e2 = ld_acq(&S.published);
-    if (e2 == e) return;
-    e = e2;
-  }
-}
-
-__device__ void begin_iteration(DeviceState& S, uint32_t lane, const ProgramDesc* P, uint32_t gen, bool fresh,
-                                Worklist& wl) {
-  LaneState& L = S.lane[lane];
-  if (fresh) {   // every entry of the previous program is exhausted: drop them
-    atomicExch(&L.ring[0].head, ld_acq(&L.ring[0].tail));
-    atomicExch(&L.ring[1].head, ld_acq(&L.ring[1].tail));
-    L.iter_in_prog = 0;
-    st_rel(&L.prog, reinterpret_cast<unsigned long long>(P));
-    st_rel(&L.gen, gen);
-    mirror_lane(S, lane, 1, gen);
-  }
-  uint32_t t = ld_volatile(&L.tag) + 1;
-  if ((t & kTagMask) == 0) ++t;   // tag 0 marks never-activated stages
-  st_rel(&L.tag, t);
-  uint32_t entry;
-  bool link;
-  if (arm(S, lane, P, P->first_stage, t & kTagMask, wl, entry, link)) ring_push_n(S, L, link, &entry, 1);
-}
-
-__device__ const ProgramDesc* end_iteration(DeviceState& S, uint32_t lane, const ProgramDesc* P, Worklist& wl) {
-  LaneState& L = S.lane[lane];
-  StageRuntime& rr = P->runtime[P->reset_stage];   // the reset tiles re-armed every other stage
-  rr.done = 0;
-  rr.deps = ld_volatile(&P->stages[P->reset_stage].deps_init);
-  const uint32_t it = L.iter_in_prog + 1;
-  L.iter_in_prog = it;
-  if (S.mirror) {   // the end time is written before the count
-    st_release_sys64(&S.mirror->lane[lane].iter_ns, globaltimer_ns());
-    mirror_lane(S, lane, 0, ld_volatile(&S.mirror->lane[lane].iterations) + 1);
-  }
-  ProgramDesc* np;
-  uint32_t ng;
-  latest_program(S, lane, np, ng);
-  if (np != nullptr && ng != ld_volatile(&L.gen)) {
-    begin_iteration(S, lane, np, ng, true, wl);
-    return np;
-  }
-  if (P->iterations != 0 && it >= P->iterations) {
-    st_rel(&L.running, 0u);
-    mirror_lane(S, lane, 2, 0);
-    return P;
-  }
-  begin_iteration(S, lane, P, ld_volatile(&L.gen), false, wl);
-  return P;
-}
-
-__device__ void drain(DeviceState& S, uint32_t lane, const ProgramDesc* P, Worklist& wl) {
-  LaneState& L = S.lane[lane];
-  constexpr int kPush = 64;
-  while (wl.n > 0) {
-    const uint32_t s = wl.pop();
-    trace_stage(S, lane, s, 1, ld_volatile(&L.tag));
-    const StageStatic& st = P->stages[s];
-    const uint32_t flags = ld_volatile(&st.flags);
-    if (flags & kStageMark) mirror_lane(S, lane, 3, ld_volatile(&st.mark));
-    if (flags & kStageReset) {
-      P = end_iteration(S, lane, P, wl);
-      continue;
-    }
-    const uint32_t tag = ld_volatile(&L.tag) & kTagMask;
-    const uint32_t sf = ld_volatile(&st.succ_first), sc = ld_volatile(&st.succ_count);
-    uint32_t ring_e[kPush], link_e[kPush];
-    int ring_n = 0, link_n = 0;
-    for (uint32_t k = 0; k < sc; ++k) {
-      const uint32_t j = P->succ[sf + k];
-      if (ld_volatile(&P->stages[j].flags) & kStageSkip) continue;
-      if (atomicSub(&P->runtime[j].deps, 1u) != 1u) continue;
-      uint32_t entry;
-      bool link;
-      if (!arm(S, lane, P, j, tag, wl, entry, link)) continue;
-      if (link) {
-        link_e[link_n++] = entry;
-        if (link_n == kPush) { ring_push_n(S, L, true, link_e, link_n); link_n = 0; }
-      } else {
-        ring_e[ring_n++] = entry;
-        if (ring_n == kPush) { ring_push_n(S, L, false, ring_e, ring_n); ring_n = 0; }
-      }
-    }
-    ring_push_n(S, L, false, ring_e, ring_n);
-    ring_push_n(S, L, true, link_e, link_n);
-  }
-  if (wl.overflow) raise_error(S, kFabErrWorklist);
-}
-
-// The same bookkeeping by one warp (the first exec warp): lane 0 owns the worklist, the
-// iteration boundary and the host mirror; the successors of a completed stage are counted
-// down and armed by the 32 lanes side by side, so that a stage with 128 successors (the
-// permute stage of an MoE layer) releases them in a few microseconds instead of one global
-// round trip after another.  Every lane of the warp must call it.
-__device__ void drain_warp(DeviceState& S, uint32_t lane_id, const ProgramDesc* P, Worklist& wl) {
-  constexpr unsigned kFull = 0xffffffffu;
-  const int lane = threadIdx.x & 31;
-  LaneState& L = S.lane[lane_id];
-  for (;;) {
-    uint32_t sf = 0, sc = 0, tag = 0;
-    int have = 0;
-    if (lane == 0) {
-      while (wl.n > 0) {
-        const uint32_t s = wl.pop();
-        trace_stage(S, lane_id, s, 1, ld_volatile(&L.tag));
-        const StageStatic& st = P->stages[s];
-        const uint32_t flags = ld_volatile(&st.flags);
-        if (flags & kStageMark) mirror_lane(S, lane_id, 3, ld_volatile(&st.mark));
-        if (flags & kStageReset) {
-          P = end_iteration(S, lane_id, P, wl);
-          continue;
-        }
-        tag = ld_volatile(&L.tag) & kTagMask;
-        sf = ld_volatile(&st.succ_first);
-        sc = ld_volatile(&st.succ_count);
-        have = 1;
-        break;
-      }
-    }
-    have = __shfl_sync(kFull, have, 0);
-    if (!have) break;
-    sf = __shfl_sync(kFull, sf, 0);
-    sc = __shfl_sync(kFull, sc, 0);
-    tag = __shfl_sync(kFull, tag, 0);
-    const ProgramDesc* Pw =
-        reinterpret_cast<const ProgramDesc*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(P), 0));
-    for (uint32_t k0 = 0; k0 < sc; k0 += 32) {
-      const uint32_t k = k0 + lane;
-      int kind = 0;   // 1 ungated ring entry, 2 link ring entry, 3 an empty stage: completes at once
-      uint32_t entry = 0, j = 0;
-      if (k < sc) {
-        j = Pw->succ[sf + k];
-        const uint32_t flags = ld_volatile(&Pw->stages[j].flags);
-        if (!(flags & kStageSkip) && atomicSub(&Pw->runtime[j].deps, 1u) == 1u) {
-          trace_stage(S, lane_id, j, 0, tag);
-          if (ld_volatile(&Pw->stages[j].count) == 0) {
-            kind = 3;
-          } else {
-            atomicExch(&Pw->runtime[j].tag_next, static_cast<unsigned long long>(tag & kTagMask) << 32);
-            __threadfence();   // armed before lane 0 publishes the entry
-            entry = make_entry(j, tag);
-            kind = (ld_volatile(&Pw->stages[j].flags) & kStageLink) ? 2 : 1;
-          }
-        }
-      }
-      for (int want = 1; want <= 3; ++want) {
-        unsigned mask = __ballot_sync(kFull, kind == want);
-        uint32_t batch[32];
-        int n = 0;
-        while (mask) {
-          const int src = __ffs(mask) - 1;
-          mask &= mask - 1;
-          const uint32_t v = __shfl_sync(kFull, want == 3 ? j : entry, src);
-          if (lane == 0) {
-            if (want == 3) wl.push(v);
-            else batch[n++] = v;
-          }
-        }
-        if (lane == 0 && want != 3) ring_push_n(S, L, want == 2, batch, n);
-      }
-    }
-  }
-  if (lane == 0 && wl.overflow) raise_error(S, kFabErrWorklist);
-}
-
-__device__ void complete_tile_warp(DeviceState& S, uint32_t lane_id, const ProgramDesc* P, uint32_t s, uint32_t n,
-                                   Worklist& wl) {
-  int last = 0;
-  if ((threadIdx.x & 31) == 0) {
-    const unsigned int d = atomicAdd(&P->runtime[s].done, n) + n;
-    last = d == ld_volatile(&P->stages[s].count);
-  }
-  last = __shfl_sync(0xffffffffu, last, 0);
-  if (!last) return;
-  __threadfence();   // acquire the other workers' tiles of the stage before releasing its successors
-  if ((threadIdx.x & 31) == 0) {
-    wl.n = 0;
-    wl.overflow = false;
-    wl.push(s);
-  }
-  __syncwarp();
-  drain_warp(S, lane_id, P, wl);
-}
-
-__device__ void complete_tile(DeviceState& S, uint32_t lane, const ProgramDesc* P, uint32_t s, uint32_t n) {
-  const unsigned int d = atomicAdd(&P->runtime[s].done, n) + n;
-  if (d == ld_volatile(&P->stages[s].count)) {
-    __threadfence();   // acquire the other workers' tiles of the stage before releasing its successors
-    Worklist wl;
-    wl.n = 0;
-    wl.overflow = false;
-    wl.push(s);
-    drain(S, lane, P, wl);
-  }
-}
-
-// ---------------------------------------------------------------- scheduling
-__device__ void refresh_epoch(DeviceState& S, WorkerState& ws) {
-  unsigned long long e = ld_acq(&S.published);
-  if (e == ws.epoch) return;
-  for (;;) {
-    const Snapshot& sn = S.snap[e & 1];
-    ws.n_lanes = ld_volatile(&sn.n_lanes);
-    ws.lane = ld_volatile(&sn.map[ws.worker]);
-    for (int l = 0; l < kMaxLanes; ++l) {
-      ws.cap[l] = ld_volatile(&sn.cap[l]);
-      ws.order[l] = ld_volatile(&sn.order[l]);
-      ws.prog_gen[l] = ld_volatile(&sn.prog_gen[l]);
-      ws.prog_snap[l] = ld_volatile(&sn.prog[l]);
-    }
-    const unsigned long long e2 = ld_acq(&S.published);
-    if (e2 == e) break;
-    e = e2;
-  }
-  ws.epoch = e;
-  if (S.mirror) {
-    st_release_sys64(&S.mirror->worker_epoch_ns[ws.worker], globaltimer_ns());
-    st_release_sys64(&S.mirror->worker_epoch[ws.worker], e);
-  }
-}
-
-__device__ void start_idle_lanes(DeviceState& S, WorkerState& ws) {
-  for (uint32_t l = 0; l < ws.n_lanes && l < kMaxLanes; ++l) {
-    ProgramDesc* P = ws.prog_snap[l];
-    if (P == nullptr) continue;
-    LaneState& L = S.lane[l];
-    if (ws.prog_gen[l] == ld_acq(&L.gen)) continue;
-    if (ld_acq(&L.running) != 0) continue;   // a running lane switches at its own boundary
-    if (atomicCAS(&L.running, 0u, 1u) != 0u) continue;
-    mirror_lane(S, l, 2, 1);
-    Worklist wl;
-    wl.n = 0;
-    wl.overflow = false;
-    begin_iteration(S, l, P, ws.prog_gen[l], true, wl);
-    drain(S, l, P, wl);
-  }
-}
-
-__device__ bool acquire_slot(LaneState& L, uint32_t cap) {
-  unsigned int s = ld_volatile(&L.slots);
-  while (s < cap) {
-    const unsigned int old = atomicCAS(&L.slots, s, s + 1);
-    if (old == s) return true;
-    s = old;
-  }
-  return false;
-}
-
-__device__ void release_slot(DeviceState& S, WorkerState& ws) {
-  if (ws.slot_lane != kNoLane) {
-    if (ws.done && static_cast<int>(*ws.done - ws.link_last) < 0) {
-      // bounded: after a second the slot goes back regardless (the fabric is stuck or stopping)
-      const unsigned long long t0 = globaltimer_ns();
-      while (static_cast<int>(*ws.done - ws.link_last) < 0 && globaltimer_ns() - t0 < 1000000000ull) __nanosleep(64);
-    }
-    atomicSub(&S.lane[ws.slot_lane].slots, 1u);
-    ws.slot_lane = kNoLane;
-  }
-}
-
-__device__ void set_claim(WorkerState& ws, const ProgramDesc* P, uint32_t stage, uint32_t index, uint32_t lane,
-                          uint32_t link, uint32_t n) {
-  ws.prog = P;
-  ws.stage = stage;
-  ws.tile_lane = lane;
-  ws.link = link;
-  ws.next_index = index;
-  ws.left = n;
-}
-
-__device__ bool try_lane(DeviceState& S, WorkerState& ws, uint32_t l) {
-  if (l >= kMaxLanes) return false;
-  LaneState& L = S.lane[l];
-  if (ld_acq(&L.running) == 0) return false;
-  const ProgramDesc* P = reinterpret_cast<const ProgramDesc*>(ld_acq(&L.prog));
-  if (P == nullptr) return false;
-  uint32_t s, idx, n;
-  if (ld_acq(&L.ring[1].tail) > ld_volatile(&L.ring[1].head)) {
-    bool held = ws.slot_lane == l;
-    if (held && ld_volatile(&L.slots) > ws.cap[l]) {   // the grant shrank
-      release_slot(S, ws);
-      held = false;
-    }
-    if (!held) {
-      release_slot(S, ws);
-      if (acquire_slot(L, ws.cap[l])) {
-        ws.slot_lane = l;
-        held = true;
-      }
-    }
-    if (held) {
-      if (take_from(L, true, P, s, idx, n)) {
-        set_claim(ws, P, s, idx, l, 1, n);
-        return true;
-      }
-      release_slot(S, ws);
-    }
-  }
-  if (take_from(L, false, P, s, idx, n)) {
-    release_slot(S, ws);
-    set_claim(ws, P, s, idx, l, 0, n);
-    return true;
-  }
-  return false;
-}
-
-__device__ uint32_t schedule(DeviceState& S, WorkerState& ws) {
-  refresh_epoch(S, ws);
-  if (ld_acq(&S.shutdown) != 0) {
-    release_slot(S, ws);
-    return kCmdExit;
-  }
-  start_idle_lanes(S, ws);
-  if (ws.lane < ws.n_lanes && try_lane(S, ws, ws.lane)) {
-    ws.idle_ns = 64;
-    return kCmdRun;
-  }
-  for (uint32_t i = 0; i < ws.n_lanes && i < kMaxLanes; ++i) {
-    const uint32_t l = ws.order[i];
-    if (l != ws.lane && try_lane(S, ws, l)) {
-      ws.idle_ns = 64;
-      return kCmdRun;
-    }
-  }
-  release_slot(S, ws);
-  __nanosleep(ws.idle_ns);
-  ws.idle_ns = min(ws.idle_ns << 1, max(64u, ld_volatile(&S.idle_cap)));
-  return kCmdIdle;
 }
 
 // ---------------------------------------------------------------- core tiles
@@ -1376,6 +886,7 @@ struct WorkerShared {
   uint64_t slot_full[kSlots], slot_empty[kSlots];
   GemmBarriers bar;
   Worklist wl;                  // completed stages the first exec warp still has to release
+  SmallWorklist sched_wl;       // the same for the scheduler warp, when it starts a lane whose first stage is empty
   AttnShared attn;              // barriers of attention items, armed once; every role counts their phases
   unsigned int wait_note[3];    // producer, MMA, first exec warp: tile << 8 | site of the current wait
   unsigned long long wait_ctx[3];   // and the record / phase counts the role had then
@@ -1433,40 +944,53 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
 
   if (warp == 0) {
     // ------------------------------------------------------------ scheduler
-    if (lane == 0) {
-      WorkerState& ws = sh.ws;
-      const unsigned long long t_start = globaltimer_ns();
-      for (uint32_t n = 0;; ++n) {
-        const int s = n % kSlots;
-        if (!mbar_wait_bounded(&sh.slot_empty[s], ((n / kSlots) & 1) ^ 1, abort_flag, kForever)) break;
-        uint32_t cmd = kCmdRun;
-        if (ws.left == 0) {
-          for (;;) {
-            cmd = schedule(S, ws);
-            if (cmd != kCmdIdle) break;
-            const unsigned long long limit = ld_volatile(&S.max_run_ns);
-            if (limit && globaltimer_ns() - t_start > limit) {
-              raise_error(S, kFabErrDeadline);
-              release_slot(S, ws);
-              cmd = kCmdExit;
-              break;
-            }
+    // The whole warp schedules (fabric_sched.cuh); lane 0 owns the worker state and the work records.
+    WorkerState& ws = sh.ws;
+    unsigned long long t_start = 0;
+    if (lane == 0) t_start = globaltimer_ns();
+    // Lane 0: has the host asked the fabric to stop, or has the run-time limit passed?
+    auto must_leave = [&](bool check_shutdown) {
+      const unsigned long long limit = ld_volatile(&S.max_run_ns);
+      const bool late = limit && globaltimer_ns() - t_start > limit;
+      if (late && !check_shutdown) raise_error(S, kFabErrDeadline);
+      return late || (check_shutdown && ld_acq(&S.shutdown) != 0);
+    };
+    for (uint32_t n = 0;; ++n) {
+      const int s = n % kSlots;
+      int go = 1;
+      if (lane == 0) go = mbar_wait_bounded(&sh.slot_empty[s], ((n / kSlots) & 1) ^ 1, abort_flag, kForever);
+      if (!__shfl_sync(kWarp, go, 0)) break;
+      uint32_t cmd = kCmdRun;
+      if (ws.left == 0) {
+        for (;;) {
+          cmd = schedule(S, ws, sh.sched_wl);
+          if (cmd != kCmdIdle) break;
+          int leave = 0;
+          if (lane == 0 && must_leave(false)) {
+            give_slot_back(S, ws);
+            leave = 1;
           }
-        } else {
-          const unsigned long long limit = ld_volatile(&S.max_run_ns);
-          if (ld_acq(&S.shutdown) != 0 || (limit && globaltimer_ns() - t_start > limit)) {
-            // leave mid-claim: the remaining tiles of the claim stay unexecuted (the fabric is stopping)
-            release_slot(S, ws);
+          if (__shfl_sync(kWarp, leave, 0)) {
             cmd = kCmdExit;
+            break;
           }
         }
-        WorkSlot& w = sh.slot[s];
+      } else {
+        // mid-claim: on a stop the remaining tiles of the claim stay unexecuted (the fabric is stopping)
+        int leave = 0;
+        if (lane == 0 && must_leave(true)) {
+          give_slot_back(S, ws);
+          leave = 1;
+        }
+        if (__shfl_sync(kWarp, leave, 0)) cmd = kCmdExit;
+      }
+      WorkSlot& w = sh.slot[s];
+      if (cmd == kCmdRun && lane < 4)   // the 64-byte descriptor, one 16-byte piece per lane
+        reinterpret_cast<uint4*>(&w.tile)[lane] = __ldcg(reinterpret_cast<const uint4*>(&ws.prog->tiles[ws.next_index]) + lane);
+      __syncwarp();
+      if (lane == 0) {
         w.cmd = cmd;
         if (cmd == kCmdRun) {
-          const uint4* src = reinterpret_cast<const uint4*>(&ws.prog->tiles[ws.next_index]);
-          uint4* dst = reinterpret_cast<uint4*>(&w.tile);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = __ldcg(src + i);
           w.prog = ws.prog;
           w.stage = ws.stage;
           w.tile_lane = ws.tile_lane;
@@ -1495,8 +1019,9 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           --ws.left;
         }
         mbar_arrive(&sh.slot_full[s]);
-        if (cmd == kCmdExit) break;
       }
+      __syncwarp();
+      if (cmd == kCmdExit) break;
     }
   } else if (warp == 5) {
     // --------------------------------------------------------- TMA producer
@@ -1617,7 +1142,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           note_tile(S, worker, w, 1ull << 62);
         }
         __syncwarp();
-        complete_tile_warp(S, w.tile_lane, w.prog, w.stage, 1, sh.wl);
+        tiles_completed(S, w.tile_lane, w.prog, w.stage, 1, sh.wl);
         if (tid == 0) {
           note_tile(S, worker, w, 0);
           *reinterpret_cast<volatile unsigned int*>(&sh.tiles_done) = n + 1;
