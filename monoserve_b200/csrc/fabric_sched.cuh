@@ -25,7 +25,7 @@ namespace fab {
 constexpr uint32_t kStageBits = 20;
 constexpr uint32_t kStageMask = (1u << kStageBits) - 1;
 constexpr uint32_t kTagMask = 0xfffu;
-constexpr int kWorklistCap = 512;
+constexpr int kWorklistCap = 448;   // bounded by the worker's shared memory; an overflow is reported, not fatal
 // A claim takes about 1/256 of what is left of a stage, at least one tile and at most
 // eight: with one worker per SM the first round over a large stage hands out eights,
 // and the tail is shared out tile by tile so that the workers finish together.
@@ -99,7 +99,7 @@ struct WorklistOf {
   __device__ uint32_t pop() { return v[--n]; }
 };
 using Worklist = WorklistOf<kWorklistCap>;
-using SmallWorklist = WorklistOf<64>;   // the scheduler's: it only ever releases the empty stages at a program's start
+using SmallWorklist = WorklistOf<16>;   // the scheduler's: it only ever releases the empty stages at a program's start
 
 // ---------------------------------------------------------------------- rings
 // Producer side, any one thread: reserve m places, fill them, and move the published tail over
