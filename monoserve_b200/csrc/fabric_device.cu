@@ -669,8 +669,8 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   stamp();
   const unsigned long long* w13_maps = reinterpret_cast<const unsigned long long*>(A.w13_maps);
   const unsigned long long* w2_maps = reinterpret_cast<const unsigned long long*>(A.w2_maps);
-  // The tiles of one expert are contiguous (blocks x (f13 + f2) descriptors of 64 bytes): a warp
-  // writes them as consecutive 16-byte pieces, one expert after the other, so the stores coalesce.
+  // The tiles of one expert are contiguous (blocks x (f13 + f2) descriptors of 64 bytes); a warp takes
+  // one expert after the other.
   {
     const int warp = tid >> 5, lane = tid & 31;
     for (int e = warp; e < E; e += kExecThreads / 32) {
@@ -682,59 +682,51 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
       const int bm = 16 << cls;
       const int blocks = (M + bm - 1) / bm;
       const int n13 = blocks * f13, total = nf + blocks * (f13 + f2);
-      uint4* dst = reinterpret_cast<uint4*>(p_tiles + A.dyn_first + s_off[e]);
-      for (int q = lane; q < total * 4; q += 32) {
-        const int part = q & 3;
-        if ((q >> 2) < nf) {   // a fetch tile: chunk j of the expert's w13 block, then of its w2 block
-          const int j = q >> 2;
-          const bool f13b = j < nf13;
+      // One lane builds one whole 64-byte descriptor and stores it as four 16-byte pieces back to back.
+      TileDesc* const out = p_tiles + A.dyn_first + s_off[e];
+      const unsigned long long scale13 = A.w13_scale ? A.w13_scale + static_cast<unsigned long long>(e) * 2 * A.I * 4 : 0ull;
+      const unsigned long long scale2 = A.w2_scale ? A.w2_scale + static_cast<unsigned long long>(e) * A.H * 4 : 0ull;
+      const unsigned long long wmap13 = region < 4 ? s_tab[20 + region] : w13_maps[region];
+      const unsigned long long wmap2 = region < 4 ? s_tab[24 + region] : w2_maps[region];
+      const int row0 = s_start[e];
+      for (int ti = lane; ti < total; ti += 32) {
+        uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0, v2 = v0, v3 = v0;
+        if (ti < nf) {   // a fetch tile: chunk ti of the expert's w13 block, then of its w2 block
+          const bool f13b = ti < nf13;
           const unsigned long long bytes = f13b ? G.w13_bytes : G.w2_bytes;
-          const unsigned long long at = static_cast<unsigned long long>(f13b ? j : j - nf13) * G.chunk_bytes;
+          const unsigned long long at = static_cast<unsigned long long>(f13b ? ti : ti - nf13) * G.chunk_bytes;
           const unsigned long long off = static_cast<unsigned long long>(e) * bytes + at;
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (part == 0) {
-            v.x = kTileFetch;
-            v.z = static_cast<uint32_t>(min(static_cast<unsigned long long>(G.chunk_bytes), bytes - at));
-          } else if (part == 1) {   // a[0] source
-            const unsigned long long a0 = (f13b ? G.w13_src : G.w2_src) + off;
-            v.z = static_cast<uint32_t>(a0);
-            v.w = static_cast<uint32_t>(a0 >> 32);
-          } else if (part == 2) {   // a[1] destination
-            const unsigned long long a1 = (f13b ? G.w13_dst : G.w2_dst) + off;
-            v.x = static_cast<uint32_t>(a1);
-            v.y = static_cast<uint32_t>(a1 >> 32);
-          }
-          dst[q] = v;
-          continue;
+          const unsigned long long a0 = (f13b ? G.w13_src : G.w2_src) + off, a1 = (f13b ? G.w13_dst : G.w2_dst) + off;
+          v0.x = kTileFetch;
+          v0.z = static_cast<uint32_t>(min(static_cast<unsigned long long>(G.chunk_bytes), bytes - at));   // i0 bytes
+          v1.z = static_cast<uint32_t>(a0);
+          v1.w = static_cast<uint32_t>(a0 >> 32);
+          v2.x = static_cast<uint32_t>(a1);
+          v2.y = static_cast<uint32_t>(a1 >> 32);
+        } else {
+          const int g = ti - nf;
+          const bool is13 = g < n13;
+          const int local = is13 ? g : g - n13, per = is13 ? f13 : f2;
+          const int blk = local / per, f = local - blk * per;
+          const unsigned long long a0 = s_tab[(is13 ? 0 : 5) + cls], a1 = is13 ? wmap13 : wmap2;
+          const unsigned long long a2 = s_tab[(is13 ? 10 : 15) + cls], a4 = is13 ? scale13 : scale2;
+          v0.x = kTileGemm;                                          // kind | lane | flags; stage (unused)
+          v0.z = static_cast<uint32_t>(is13 ? f * 64 : f * 128);     // i0 first weight row
+          v0.w = static_cast<uint32_t>(row0 + blk * bm);             // i1 first activation row
+          v1.x = static_cast<uint32_t>(min(bm, M - blk * bm));       // i2 rows
+          v1.y = static_cast<uint32_t>(slot);                        // i3 weight slot
+          v1.z = static_cast<uint32_t>(a0);                          // a[0] GemmArgs
+          v1.w = static_cast<uint32_t>(a0 >> 32);
+          v2 = make_uint4(static_cast<uint32_t>(a1), static_cast<uint32_t>(a1 >> 32),   // a[1] weight map
+                          static_cast<uint32_t>(a2), static_cast<uint32_t>(a2 >> 32));  // a[2] activation map
+          v3.z = static_cast<uint32_t>(a4);                          // a[3] K range (all); a[4] fp32 scale per weight row
+          v3.w = static_cast<uint32_t>(a4 >> 32);
         }
-        const int ti = (q >> 2) - nf;
-        const bool is13 = ti < n13;
-        const int local = is13 ? ti : ti - n13, per = is13 ? f13 : f2;
-        const int blk = local / per, f = local - blk * per;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (part == 0) {          // kind | lane | flags, stage, i0 first weight row, i1 first activation row
-          v.x = kTileGemm;
-          v.z = static_cast<uint32_t>(is13 ? f * 64 : f * 128);
-          v.w = static_cast<uint32_t>(s_start[e] + blk * bm);
-        } else if (part == 1) {   // i2 rows, i3 weight slot, a[0] GemmArgs
-          const unsigned long long a0 = s_tab[(is13 ? 0 : 5) + cls];
-          v.x = static_cast<uint32_t>(min(bm, M - blk * bm));
-          v.y = static_cast<uint32_t>(slot);
-          v.z = static_cast<uint32_t>(a0);
-          v.w = static_cast<uint32_t>(a0 >> 32);
-        } else if (part == 2) {   // a[1] weight map, a[2] activation map
-          const unsigned long long a1 = region < 4 ? s_tab[(is13 ? 20 : 24) + region] : (is13 ? w13_maps[region] : w2_maps[region]);
-          const unsigned long long a2 = s_tab[(is13 ? 10 : 15) + cls];
-          v = make_uint4(static_cast<uint32_t>(a1), static_cast<uint32_t>(a1 >> 32), static_cast<uint32_t>(a2),
-                         static_cast<uint32_t>(a2 >> 32));
-        } else {                  // a[3] K range (all), a[4] fp32 scale per weight row
-          unsigned long long a4 = 0;
-          if (is13 && A.w13_scale) a4 = A.w13_scale + static_cast<unsigned long long>(e) * 2 * A.I * 4;
-          if (!is13 && A.w2_scale) a4 = A.w2_scale + static_cast<unsigned long long>(e) * A.H * 4;
-          v.z = static_cast<uint32_t>(a4);
-          v.w = static_cast<uint32_t>(a4 >> 32);
-        }
-        dst[q] = v;
+        uint4* dst = reinterpret_cast<uint4*>(out + ti);
+        dst[0] = v0;
+        dst[1] = v1;
+        dst[2] = v2;
+        dst[3] = v3;
       }
     }
   }

@@ -24,7 +24,7 @@ K_GEMM, K_ROUTER, K_EXPAND, K_PERMUTE, K_COMBINE, K_LOGITS = 32, 38, 39, 40, 47,
 REGION_HOST, REGION_HOT = 0, 1
 CHUNK = 16    # rows of one rank chunk of the stable pack (kFabChunk)
 SUB = 4       # rows per router / permute tile: one per exec warp; divides CHUNK, so a tile stays inside a chunk
-LOGIT_ROWS, LOGIT_EXPERTS = 8, 16   # a router-projection tile: rows x experts
+LOGIT_ROWS, LOGIT_EXPERTS = 16, 16   # a router-projection tile: rows x experts (256 tokens x 128 experts: one wave of 128 tiles)
 EPI_SILU_MUL, EPI_ROWS_F32 = 1, 5
 
 
@@ -243,4 +243,5 @@ class MoELane:
         ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
         torch.cuda.synchronize()
         self._keep += [logits_args, ex]
+        self.labels = p.labels()   # stage names, for monoserve_b200.fabric.trace.summary
         return p.upload(self.fab, first=s_lg, iterations=iterations)
