@@ -27,89 +27,105 @@ __device__ __forceinline__ uint4 pack8(const float f[8]) {
   return u;
 }
 
-// Routing of one token by one warp (csrc/fabric/tiles/aux.cuh:326-417): softmax
-// or sigmoid (+ selection bias) over E <= 256 logits, K <= 16 rounds of arg-max with
-// the lowest index winning ties, renormalisation in pick order, scale.  Lane k < K
-// returns pick k in (my_id, my_w).  zero_logits: clear the row after reading it.
-__device__ __forceinline__ void route_row(float* lg, const float* bias, int E, int K, int scoring, int renorm,
-                                          float scale, int zero_logits, int& my_id, float& my_w_out) {
-  constexpr int kMaxPer = kMaxExperts / 32;
+// Routing of one token by one warp: what the reference's router tile computes
+// (csrc/fabric/tiles/aux.cuh:326-417): scores = softmax of the E <= 256 logits, or their sigmoid with
+// an optional selection bias; K <= 16 picks, each the best remaining selection score with the lowest
+// expert id winning ties; weights = the picks' scores, renormalised by their sum taken in pick
+// order, times `scale`.  Lane k < K returns pick k in (pick_id, pick_weight).  zero_logits: clear the
+// row once read.
+//
+// Lane l holds experts l, l + 32, ... (slot i = expert l + 32 i).  The floating-point order is part
+// of the result's definition (the oracle repeats it): row maximum (any order: max is exact), per lane
+// the exponentials summed over its slots in slot order, the lanes' sums by the xor butterfly 16..1,
+// one IEEE division per score.  The K arg-max rounds only compare, so they are done on integers:
+// a score and its expert id become one 64-bit key whose order is (score ascending, id descending).
+namespace route {
+
+constexpr int kSlots = kMaxExperts / 32;
+constexpr float kAbsent = -1e30f;   // stands in for experts past E
+
+// 32-bit pattern whose unsigned order is the order of the (non-NaN) floats.
+__device__ __forceinline__ unsigned int ordered_bits(float v) {
+  const unsigned int u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long pick_key(float score, int expert) {
+  return (static_cast<unsigned long long>(ordered_bits(score)) << 32) | (0xffffffffu - static_cast<unsigned int>(expert));
+}
+__device__ __forceinline__ int key_expert(unsigned long long key) { return static_cast<int>(0xffffffffu - static_cast<unsigned int>(key)); }
+
+__device__ __forceinline__ unsigned long long warp_max_key(unsigned long long k) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, k, o);
+    k = other > k ? other : k;
+  }
+  return k;
+}
+
+}  // namespace route
+
+__device__ __forceinline__ void route_row(float* logits_row, const float* bias, int E, int K, int scoring, int renorm,
+                                          float scale, int zero_logits, int& pick_id, float& pick_weight) {
+  using namespace route;
   const int lane = threadIdx.x & 31;
-  float p[kMaxPer], sel[kMaxPer];
+  float score[kSlots];
 #pragma unroll
-  for (int i = 0; i < kMaxPer; ++i) {
-    const int e = lane + 32 * i;
-    p[i] = e < E ? lg[e] : -1e30f;
+  for (int i = 0; i < kSlots; ++i) {
+    const int expert = lane + 32 * i;
+    score[i] = expert < E ? logits_row[expert] : kAbsent;
+    if (zero_logits && expert < E) logits_row[expert] = 0.f;
   }
-  if (zero_logits) {
-#pragma unroll
-    for (int i = 0; i < kMaxPer; ++i)
-      if (lane + 32 * i < E) lg[lane + 32 * i] = 0.f;
-  }
+  unsigned long long key[kSlots];   // selection key per slot; 0 once picked (below every real key)
   if (scoring == 0) {
-    float mx = -1e30f;
+    float top = kAbsent;
 #pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) mx = fmaxf(mx, p[i]);
+    for (int i = 0; i < kSlots; ++i) top = fmaxf(top, score[i]);
 #pragma unroll
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float s = 0.f;
+    for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    float lane_sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      p[i] = det_expf(__fsub_rn(p[i], mx));
-      s = __fadd_rn(s, p[i]);
+    for (int i = 0; i < kSlots; ++i) {
+      score[i] = det_expf(__fsub_rn(score[i], top));   // an absent expert gives exactly 0
+      lane_sum = __fadd_rn(lane_sum, score[i]);
     }
-    s = warp_sum_xor(s);
+    const float total = warp_sum_xor(lane_sum);
 #pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      p[i] = __fdiv_rn(p[i], s);
-      sel[i] = lane + 32 * i < E ? p[i] : -1e30f;
+    for (int i = 0; i < kSlots; ++i) {
+      score[i] = __fdiv_rn(score[i], total);
+      key[i] = pick_key(lane + 32 * i < E ? score[i] : kAbsent, lane + 32 * i);
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      const int e = lane + 32 * i;
-      p[i] = det_sigmoidf(p[i]);
-      sel[i] = e < E ? __fadd_rn(p[i], bias ? bias[e] : 0.f) : -1e30f;
+    for (int i = 0; i < kSlots; ++i) {
+      const int expert = lane + 32 * i;
+      score[i] = det_sigmoidf(score[i]);
+      key[i] = pick_key(expert < E ? __fadd_rn(score[i], bias ? bias[expert] : 0.f) : kAbsent, expert);
     }
   }
-  my_id = 0;
-  float my_w = 0.f, wsum = 0.f;
+  pick_id = 0;
+  float mine = 0.f, picked_sum = 0.f;
   for (int k = 0; k < K; ++k) {
-    float bv = -1e30f;
-    int bi = 0x7fffffff;
+    unsigned long long best = 0;
 #pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      const int e = lane + 32 * i;
-      if (sel[i] > bv || (sel[i] == bv && e < bi)) {
-        bv = sel[i];
-        bi = e;
-      }
-    }
+    for (int i = 0; i < kSlots; ++i) best = key[i] > best ? key[i] : best;
+    const int expert = key_expert(warp_max_key(best));
+    // the lane that holds the pick takes it out of the running and hands its score round
+    float held = 0.f;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
+    for (int i = 0; i < kSlots; ++i)
+      if (lane + 32 * i == expert) {
+        held = score[i];
+        key[i] = 0;
       }
-    }
-    float mine = 0.f;
-#pragma unroll
-    for (int i = 0; i < kMaxPer; ++i) {
-      if (i == (bi >> 5)) {
-        mine = p[i];
-        if (lane == (bi & 31)) sel[i] = -1e30f;
-      }
-    }
-    const float w = __shfl_sync(0xffffffffu, mine, bi & 31);
+    const float weight = __shfl_sync(0xffffffffu, held, expert & 31);
     if (lane == k) {
-      my_id = bi;
-      my_w = w;
+      pick_id = expert;
+      mine = weight;
     }
-    wsum = __fadd_rn(wsum, w);
+    picked_sum = __fadd_rn(picked_sum, weight);
   }
-  my_w_out = __fmul_rn(renorm ? __fdiv_rn(my_w, wsum) : my_w, scale);
+  pick_weight = __fmul_rn(renorm ? __fdiv_rn(mine, picked_sum) : mine, scale);
 }
 
 // RMSNorm of a bf16 row that this warp holds in `x` (H elements, lane l owns the
