@@ -194,10 +194,27 @@ def run_reference(args):
 
 
 def run_profile_target(args):
-    """A short, quiet run of the layer for `ncu` (one GPU)."""
+    """A short, quiet run of the layer for `ncu` (one GPU).  --ep: the expert-parallel layer as a single
+    rank, so that its exchange kernels (counts, dispatch, return) run with this GPU as their own peer."""
     from monoserve_b200.moe import MoELayer
     H, I, E, K = SHAPE["H"], SHAPE["I"], SHAPE["E"], SHAPE["K"]
     wl = make_workload()
+    if args.ep:
+        from monoserve_b200.ep import ExpertParallelMoE
+        ep = ExpertParallelMoE(H, I, E, K, BATCH, rank=0, world=1)
+        ep.connect([ep.export()])
+        wr = wl["wr"].cuda()
+        ep.set_router(wr)
+        ep.set_local_experts(wl["w13"], wl["w2"], list(range(E)) if args.all_hot else wl["hot"])
+        ep.set_plan(0, CREDITS, FORM)
+        out = torch.empty(BATCH, H, dtype=torch.bfloat16, device="cuda")
+        xs, x2s = [x.cuda() for x in wl["xs"]], [x.cuda() for x in wl["x2s"]]
+        for i in range(args.warmup + args.steps):
+            ep.forward(xs[i % N_BATCHES], x2s[i % N_BATCHES], out)
+        torch.cuda.synchronize()
+        ep.local.status()
+        ep.close()
+        return
     layer = MoELayer(H, I, E, K, BATCH)
     layer.set_router(wl["wr"].cuda())
     layer.set_experts(wl["w13"], wl["w2"], list(range(E)) if args.all_hot else wl["hot"])
@@ -721,6 +738,7 @@ def main():
     ap.add_argument("--ncu", action="store_true",
                     help="profiling target: only W warm-up + K device-resident steps, no JSON line")
     ap.add_argument("--all-hot", action="store_true", help="with --ncu: place all 128 experts in HBM")
+    ap.add_argument("--ep", action="store_true", help="with --ncu: run the expert-parallel layer as one rank")
     ap.add_argument("--no-mixed-lane", action="store_true",
                     help="skip the side runs that the N=1 line carries (`fabric_layer`, `attention`, `mixed_lane`, "
                          "`config4`)")
