@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(256) ep_counts_kernel(const EpDev A, int* __re
   __shared__ int s_warp[8];
   const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
   int cnt = 0;
+  chain_release();
+  chain_wait();
   if (e < A.E) {
     for (int c = 0; c < chunks; ++c) {
       int* cell = chunk_counts + static_cast<size_t>(c) * A.E + e;
@@ -166,6 +168,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDev A, const i
   __shared__ int s_total[kMaxExperts], s_base[kMaxExperts];
   const int tid = threadIdx.x, lane = tid & 31;
   unsigned char* mine = A.comm[A.rank];
+  chain_release();
+  chain_wait();
   if (tid < A.world && !wait_flag(comm_flag(mine, kFlagCounts, tid), A.epoch)) atomicOr(A.status, kErrWaitTimeout);
   __syncthreads();
   const int* call = comm_table(mine, A.epoch, 0);
@@ -230,6 +234,8 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const EpDev A, const int
   __shared__ int s_start[kMaxExperts + 1], s_cnt[kMaxExperts], s_src0[kMaxExperts];   // [source][local expert]
   const int tid = threadIdx.x, lane = tid & 31;
   const int El = A.El;
+  chain_release();
+  chain_wait();
   const int* counts_all = comm_table(A.comm[A.rank], A.epoch, 0);
   const int* starts_all = comm_table(A.comm[A.rank], A.epoch, 1);
   for (int i = tid; i <= El; i += blockDim.x) s_start[i] = seg_starts[i];
@@ -369,17 +375,15 @@ int phase_locked(monofab_ep* ep, int phase, const void* xn, const void* x2, void
                       T, E, K, c.scoring, c.renorm, c.routed_scale, 0};
       MF_CUDA(launch_router_topk(rp, st));
       MF_CUDA(mark(2));
-      ep_counts_kernel<<<1, 256, 0, st>>>(A, ep->chunk_counts, chunks, ep->counts, ep->starts);
-      MF_CUDA(cudaGetLastError());
+      MF_CUDA(launch_chained(ep_counts_kernel, 1, 256, 0, st, A, ep->chunk_counts, chunks, ep->counts, ep->starts));
       MF_CUDA(mark(3));
       return MONOFAB_OK;
     }
     case 1: {
       const int units = T * kRowSplit;
       const int blocks = units > 0 ? (units + 7) / 8 : 1;
-      ep_dispatch_kernel<<<blocks, 256, 0, st>>>(A, ep->topk_ids, ep->pair_rank, ep->chunk_counts, ep->starts,
-                                                 static_cast<const bf16*>(xn), ep->pair_pos);
-      MF_CUDA(cudaGetLastError());
+      MF_CUDA(launch_chained(ep_dispatch_kernel, blocks, 256, 0, st, A, ep->topk_ids, ep->pair_rank, ep->chunk_counts,
+                             ep->starts, static_cast<const bf16*>(xn), ep->pair_pos));
       MF_CUDA(mark(4));
       return MONOFAB_OK;
     }
@@ -397,8 +401,7 @@ int phase_locked(monofab_ep* ep, int phase, const void* xn, const void* x2, void
         if (int r = experts_locked(m, seg, st, prof ? ep->ev[5] : nullptr)) return r;
       }
       MF_CUDA(mark(6));
-      ep_return_kernel<<<2 * m->num_sms, 256, 0, st>>>(A, m->starts, m->y);
-      MF_CUDA(cudaGetLastError());
+      MF_CUDA(launch_chained(ep_return_kernel, 2 * m->num_sms, 256, 0, st, A, m->starts, m->y));
       MF_CUDA(mark(7));
       return MONOFAB_OK;
     }

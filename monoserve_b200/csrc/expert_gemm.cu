@@ -88,10 +88,12 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
     tmem_alloc(&sh.tmem_base, kTmemCols);
     tmem_relinquish();
   }
+  chain_release();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = sh.tmem_base;
+  chain_wait();   // the tile lists and the packed rows come from the kernels before this one
 
   if (warp == 6) {
     // ------------------------------------------------------------ scheduler
@@ -310,11 +312,8 @@ cudaError_t launch_expert_gemm(const GemmParams& p, int ctas, cudaStream_t strea
     return err;
   });
   if (attr_err != cudaSuccess) return attr_err;
-  if (p.ph[0].w_fp8)
-    expert_gemm_kernel<true><<<ctas, kGemmThreadsFp8, kGemmSmemBytes, stream>>>(p);
-  else
-    expert_gemm_kernel<false><<<ctas, kGemmThreads, kGemmSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  if (p.ph[0].w_fp8) return launch_chained(expert_gemm_kernel<true>, ctas, kGemmThreadsFp8, kGemmSmemBytes, stream, p);
+  return launch_chained(expert_gemm_kernel<false>, ctas, kGemmThreads, kGemmSmemBytes, stream, p);
 }
 
 }  // namespace mf

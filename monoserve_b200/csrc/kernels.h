@@ -13,6 +13,33 @@ namespace mf {
 
 using bf16 = __nv_bfloat16;
 
+// Programmatic dependent launch: the kernels of one layer pass form a chain on one stream, each reading what
+// the one before wrote.  Launched with launch_chained, a kernel may be scheduled while its predecessor is still
+// draining: its blocks run their prologue (barrier set-up, TMEM allocation, operand-block loads that do not
+// depend on the predecessor) and then stop in chain_wait() until the predecessor has completed and its writes
+// are visible.  chain_release() lets the successor start being scheduled; it is called first thing, because
+// every kernel here waits before it touches dependent data.  Without the launch attribute both are no-ops.
+#if defined(__CUDACC__)
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // A function attribute (dynamic shared memory above 48 KB) belongs to a device's context, so it is
 // set once per DEVICE, not once per process: `configure` runs under a lock the first time the
 // current device launches the kernel.

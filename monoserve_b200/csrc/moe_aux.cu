@@ -37,6 +37,8 @@ constexpr int kExpertsPerWarp = 16;
 template <int J>
 __global__ void __launch_bounds__(256) router_logits_kernel(const bf16* __restrict__ x, const bf16* __restrict__ wr,
                                                             float* __restrict__ logits, int T, int H, int E) {
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int groups = (E + kExpertsPerWarp - 1) / kExpertsPerWarp;
   const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const bf16* __restri
 __global__ void __launch_bounds__(1024) router_topk_kernel(const RouterParams A) {
   __shared__ int s_ids[kChunkTokens * kMaxTopK];
   __shared__ int s_hist[kMaxExperts];
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int E = A.E, K = A.K;
   const int r = blockIdx.x * kChunkTokens + warp;
@@ -130,6 +134,8 @@ __global__ void __launch_bounds__(kChunkTokens * kMaxTopK) chunk_rank_kernel(con
                                                                              int T, int E, int K, int* status) {
   __shared__ int s_ids[kChunkTokens * kMaxTopK];
   __shared__ int s_hist[kMaxExperts];
+  chain_release();
+  chain_wait();
   const int rows = min(kChunkTokens, T - static_cast<int>(blockIdx.x) * kChunkTokens);
   const int pairs = rows * K;
   const int p = threadIdx.x;
@@ -185,6 +191,8 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
   const int E = A.E;
   int cnt = 0;
   bool bad = false;
+  chain_release();
+  chain_wait();
   if (A.wait_flags) {   // expert parallelism: the counts and the rows they describe come from peers
     if (e < A.wait_n && !wait_flag(A.wait_flags + e, A.wait_epoch)) atomicOr(A.status, kErrWaitTimeout);
     __syncthreads();
@@ -248,29 +256,46 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
     A.q->need = 4 * f13;   // four epilogue warps arrive per w13 tile
     if (overflow) atomicOr(A.status, kErrPlanOverflow);
   }
-  if (overflow || nb == 0) return;
-  GemmTile* out13 = A.tiles[tier] + first13[tier];
-  GemmTile* out2 = A.tiles[tier] + total13[tier] + first2[tier];
-  for (int b = 0; b < nb; ++b) {
-    const int rows = min(bh, cnt - b * bh);
-    int n = 16;
-    while (n < rows) n <<= 1;
-    GemmTile t;
-    t.act_row0 = start + b * bh;
-    t.rows = rows;
-    t.n = n;
-    t.z = z;
-    t.tier_phase = tier;
-    t.expert = expert;
-    t.block = block0 + b;
-    for (int f = 0; f < f13; ++f) {
-      t.w_row0 = f * 64;
-      *out13++ = t;
-    }
-    t.tier_phase = tier | (1 << 8);
-    for (int f = 0; f < f2; ++f) {
-      t.w_row0 = f * 128;
-      *out2++ = t;
+  // Every expert's tile list is written by a warp, a tile per lane (an expert at decode batch sizes has
+  // 28 tiles; written from one thread per expert they were the longest serial stretch of the layer).
+  __shared__ int s_job[kMaxExperts][8];   // nb, bh, rows, first row, slot, tier, first w13 tile, first w2 tile (+ block0 below)
+  __shared__ int s_block0[kMaxExperts], s_expert[kMaxExperts];
+  if (e < E) {
+    s_job[e][0] = overflow ? 0 : nb;
+    s_job[e][1] = bh;
+    s_job[e][2] = cnt;
+    s_job[e][3] = start;
+    s_job[e][4] = z;
+    s_job[e][5] = tier;
+    s_job[e][6] = first13[tier];
+    s_job[e][7] = total13[tier] + first2[tier];
+    s_block0[e] = block0;
+    s_expert[e] = expert;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_block = f13 + f2;
+  for (int x = warp; x < E; x += static_cast<int>(blockDim.x >> 5)) {
+    const int x_nb = s_job[x][0];
+    if (x_nb == 0) continue;
+    const int x_bh = s_job[x][1], x_cnt = s_job[x][2], x_start = s_job[x][3], x_tier = s_job[x][5];
+    GemmTile* const list = A.tiles[x_tier];
+    for (int j = lane; j < x_nb * per_block; j += 32) {
+      const int b = j / per_block, f = j - b * per_block;
+      const bool up = f >= f13;   // a w2 tile
+      const int rows = min(x_bh, x_cnt - b * x_bh);
+      int n = 16;
+      while (n < rows) n <<= 1;
+      GemmTile t;
+      t.w_row0 = up ? (f - f13) * 128 : f * 64;
+      t.act_row0 = x_start + b * x_bh;
+      t.rows = rows;
+      t.n = n;
+      t.z = s_job[x][4];
+      t.tier_phase = x_tier | (up ? 1 << 8 : 0);
+      t.expert = s_expert[x];
+      t.block = s_block0[x] + b;
+      list[up ? s_job[x][7] + b * f2 + (f - f13) : s_job[x][6] + b * f13 + f] = t;
     }
   }
 }
@@ -278,6 +303,8 @@ __global__ void __launch_bounds__(256) plan_kernel(const PlanParams A) {
 // ---------------------------------------------------------------------- pack
 
 __global__ void __launch_bounds__(256) pack_kernel(const PackParams A) {
+  chain_release();
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= A.T) return;
@@ -323,6 +350,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams A) {
   // a decode batch of a few hundred tokens otherwise leaves most of the machine idle.  Every column is
   // computed by the same instructions either way: the result does not depend on the split.
   const int lane = threadIdx.x & 31;
+  chain_release();
+  chain_wait();
   if (A.wait_flags) {   // expert parallelism: y is written by peers
     if (static_cast<int>(threadIdx.x) < A.wait_n && !wait_flag(A.wait_flags + threadIdx.x, A.wait_epoch))
       atomicOr(A.status, kErrWaitTimeout);
@@ -394,38 +423,33 @@ cudaError_t launch_router_logits(const void* x, const void* wr, float* logits, i
   const bf16* xb = static_cast<const bf16*>(x);
   const bf16* wb = static_cast<const bf16*>(wr);
   switch (H / 256) {
-    case 2: router_logits_kernel<2><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
-    case 4: router_logits_kernel<4><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
-    case 8: router_logits_kernel<8><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
-    case 16: router_logits_kernel<16><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
-    default: router_logits_kernel<0><<<blocks, 256, 0, stream>>>(xb, wb, logits, T, H, E); break;
+    case 2: return launch_chained(router_logits_kernel<2>, blocks, 256, 0, stream, xb, wb, logits, T, H, E);
+    case 4: return launch_chained(router_logits_kernel<4>, blocks, 256, 0, stream, xb, wb, logits, T, H, E);
+    case 8: return launch_chained(router_logits_kernel<8>, blocks, 256, 0, stream, xb, wb, logits, T, H, E);
+    case 16: return launch_chained(router_logits_kernel<16>, blocks, 256, 0, stream, xb, wb, logits, T, H, E);
+    default: return launch_chained(router_logits_kernel<0>, blocks, 256, 0, stream, xb, wb, logits, T, H, E);
   }
-  return cudaGetLastError();
 }
 
 cudaError_t launch_router_topk(const RouterParams& A, cudaStream_t stream) {
   if (A.T == 0) return cudaSuccess;
-  router_topk_kernel<<<(A.T + kChunkTokens - 1) / kChunkTokens, 1024, 0, stream>>>(A);
-  return cudaGetLastError();
+  return launch_chained(router_topk_kernel, (A.T + kChunkTokens - 1) / kChunkTokens, 1024, 0, stream, A);
 }
 
 cudaError_t launch_chunk_rank(const int* topk_ids, int* pair_rank, int* chunk_counts, int T, int E, int K,
                               int* status, cudaStream_t stream) {
   if (T == 0) return cudaSuccess;
-  chunk_rank_kernel<<<(T + kChunkTokens - 1) / kChunkTokens, kChunkTokens * kMaxTopK, 0, stream>>>(
-      topk_ids, pair_rank, chunk_counts, T, E, K, status);
-  return cudaGetLastError();
+  return launch_chained(chunk_rank_kernel, (T + kChunkTokens - 1) / kChunkTokens, kChunkTokens * kMaxTopK, 0, stream,
+                        topk_ids, pair_rank, chunk_counts, T, E, K, status);
 }
 
 cudaError_t launch_plan(const PlanParams& A, cudaStream_t stream) {
-  plan_kernel<<<1, 256, 0, stream>>>(A);
-  return cudaGetLastError();
+  return launch_chained(plan_kernel, 1, 256, 0, stream, A);
 }
 
 cudaError_t launch_pack(const PackParams& A, cudaStream_t stream) {
   if (A.T == 0) return cudaSuccess;
-  pack_kernel<<<(A.T + 7) / 8, 256, 0, stream>>>(A);
-  return cudaGetLastError();
+  return launch_chained(pack_kernel, (A.T + 7) / 8, 256, 0, stream, A);
 }
 
 size_t pack_scratch_bytes(int T, int E, int K) {
@@ -458,8 +482,7 @@ cudaError_t launch_pack_chain(const int* topk_ids, const float* topk_w, int T, i
 cudaError_t launch_combine(const CombineParams& A, cudaStream_t stream) {
   if (A.T == 0) return cudaSuccess;
   const int units = A.T * (A.norm_w ? 1 : kCombineSplit);
-  combine_kernel<<<(units + 7) / 8, 256, 0, stream>>>(A);
-  return cudaGetLastError();
+  return launch_chained(combine_kernel, (units + 7) / 8, 256, 0, stream, A);
 }
 
 }  // namespace mf
