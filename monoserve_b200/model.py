@@ -41,6 +41,38 @@ def _u64(values):
     return torch.tensor([int(v) for v in values], dtype=torch.int64).cuda()
 
 
+class _Blob:
+    """A piece of device memory by address (what `pack` and the tile builders need of a tensor)."""
+
+    def __init__(self, addr, nbytes):
+        self.addr, self.nbytes = addr, nbytes
+
+    def data_ptr(self):
+        return self.addr
+
+
+class _Arena:
+    """Device memory for the operand blocks of one program build, carved from one buffer that is
+    allocated with the lane and filled through Fabric.write: a build then neither allocates device
+    memory nor launches a kernel, both of which would wait for a resident fabric kernel."""
+
+    def __init__(self, fab, nbytes):
+        self.fab, self.buf, self.at = fab, torch.zeros(nbytes, dtype=torch.uint8, device="cuda"), 0
+
+    def reset(self):
+        self.at = 0
+
+    def put(self, data):
+        data = bytes(data)
+        size = (len(data) + 255) & ~255
+        if self.at + size > self.buf.numel():
+            raise RuntimeError("monofab: the lane's operand arena is full")
+        blob = _Blob(self.buf.data_ptr() + self.at, len(data))
+        self.at += size
+        self.fab.write(blob.addr, data)
+        return blob
+
+
 def _bm(rows):
     """Row-block height of a dense GEMM over `rows` activation rows."""
     for h in HEIGHTS:
@@ -183,12 +215,15 @@ class ModelLane:
 
     def __init__(self, fab, lane_id, cfg, weights, kv, max_tokens, max_slots, bt_stride, max_chunks=8, max_pos=None,
                  logit_rows=None, min_form=16, staged=False, staged_min_rows=256, fetch_chunk=256 * 1024,
-                 staging_index=None):
+                 staging_index=None, requests=None):
         """staging_index: the weights' staging buffer (ModelWeights.alloc_staging) a host loop fills for
         this lane; its experts are region 2 of the lane's own (region, slot) tables.
         staged: under form 0 a host-resident expert with more than staged_min_rows rows is copied once
         into this lane's HBM staging stack (one slot per expert, shared by all layers) by fetch tiles of
-        fetch_chunk bytes, and its GEMM tiles read the copy."""
+        fetch_chunk bytes, and its GEMM tiles read the copy.
+        requests: a RequestTable (monoserve_b200/engine.py) whose slot-indexed request state (block table,
+        lengths, last tokens, token rings) this lane uses instead of arrays of its own, so that several
+        lanes (a prefill lane, two decode buffers) see the same requests (monoserve/runtime/requests.py)."""
         self.fab, self.lane_id, self.cfg, self.w, self.kv = fab, lane_id, cfg, weights, kv
         self.staged, self.staged_min_rows, self.fetch_chunk = staged, staged_min_rows, fetch_chunk
         self.staging_index = staging_index
@@ -233,12 +268,18 @@ class ModelLane:
         self.tokens, self.tok_pos, self.tok_slot, self.gather = z(T), z(T), z(T), z(T)
         self.req_info = z(max(T, S), 4)
         self.row_req = z(max(T, S))
-        self.bt = z(S, bt_stride)
-        self.seq_len, self.last_token, self.steps = z(S), z(S), z(S)
-        self.temperature = z(S, dt=torch.float32)
-        self.ring = 64
-        self.host_tokens = torch.zeros(S, self.ring, dtype=torch.int32).pin_memory()
-        self.host_steps = torch.zeros(S, dtype=torch.int64).pin_memory()
+        if requests is not None:
+            assert requests.slots >= S and requests.bt_stride == bt_stride
+            self.bt, self.seq_len, self.last_token, self.steps = requests.bt, requests.seq_len, requests.last_token, requests.steps
+            self.temperature, self.ring = requests.temperature, requests.ring
+            self.host_tokens, self.host_steps = requests.host_tokens, requests.host_steps
+        else:
+            self.bt = z(S, bt_stride)
+            self.seq_len, self.last_token, self.steps = z(S), z(S), z(S)
+            self.temperature = z(S, dt=torch.float32)
+            self.ring = 64
+            self.host_tokens = torch.zeros(S, self.ring, dtype=torch.int32).pin_memory()
+            self.host_steps = torch.zeros(S, dtype=torch.int64).pin_memory()
         # attention split workspace: (max, sum) pairs after the fp32 rows
         self.ws_rows = max(max_chunks * S * hq, 4 * T * hq // 8 + 1024)
         self.ws = z(self.ws_rows * 130, dt=torch.float32)
@@ -246,6 +287,7 @@ class ModelLane:
         self.max_pos = max_pos
         self.cos_sin = rope_table(cfg.rope_theta, cfg.rotary_dim, max_pos).cuda()
         self._keep = []
+        self.arena = _Arena(fab, (64 << 10) * (L + 2))
         self._maps()
 
     # ------------------------------------------------------------------ maps and operand blocks
@@ -347,6 +389,17 @@ class ModelLane:
                                   host_steps=_C.host_device_pointer(self.host_steps.data_ptr()), seed=0x5eed,
                                   V=cfg.vocab, ring=self.ring)
 
+    # ------------------------------------------------------------------ device memory of a build
+    def _dev(self, name, **fields):
+        """An operand block in the lane's arena."""
+        return self.arena.put(pack(name, **fields))
+
+    def _put(self, tensor, values, dtype=np.int32):
+        """Write the first len(values) elements of a device tensor without launching a kernel."""
+        data = np.ascontiguousarray(values, dtype=dtype)
+        if data.size:
+            self.fab.write(tensor.data_ptr(), data.tobytes())
+
     # ------------------------------------------------------------------ stage builders
     def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None,
               mat=None, bias=None, up_offset=0):
@@ -354,11 +407,10 @@ class ModelLane:
         mat: the weight's Mat (e4m3 weights carry their scales into the tiles)."""
         bm = _bm(rows)
         fp8 = mat is not None and mat.fp8
-        args = torch.frombuffer(bytearray(_C.gemm_args(
+        args = self.arena.put(_C.gemm_args(
             out=out.data_ptr(), ld_out=ld_out, k_tiles=k // 64, epi=epi, bm=bm, n_limit=n_out,
             residual=residual.data_ptr() if residual is not None else 0, ld_res=ld_res,
-            bias=bias.data_ptr() if bias is not None else 0, up_offset=up_offset, w_fp8=int(fp8))), dtype=torch.uint8).cuda()
-        self._keep.append(args)
+            bias=bias.data_ptr() if bias is not None else 0, up_offset=up_offset, w_fp8=int(fp8)))
         xm = amaps[HEIGHTS.index(bm)]
         step = 64 if epi == EPI_SILU_MUL else 128
         m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, step), indexing="ij")
@@ -375,13 +427,12 @@ class ModelLane:
         cfg = self.cfg
         H, E = cfg.hidden, cfg.num_experts
         nw = self.fab.num_workers
-        lg = _block("LogitsArgs", x=self.xn, wr=self.w.router[l], logits=self.rl, T=T, H=H, E=E)
+        lg = self._dev("LogitsArgs", x=self.xn, wr=self.w.router[l], logits=self.rl, T=T, H=H, E=E)
         shared = self.w.shared_w13[l] is not None
-        cb = _block("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2, x=self.x,
-                    w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps,
-                    shared=self.y_shared if shared else 0)
-        ex = torch.zeros(_C.struct_layouts()["ExpandArgs"][0], dtype=torch.uint8, device="cuda")
-        self._keep += [lg, cb, ex]
+        cb = self._dev("CombineArgs", y=self.y, pair_pos=self.pair_pos, topk_w=self.topk_w, x2=self.x2, x=self.x,
+                       w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps,
+                       shared=self.y_shared if shared else 0)
+        ex = self.arena.put(bytes(_C.struct_layouts()["ExpandArgs"][0]))   # filled once the dynamic region is laid out
         per = max(2, -(-T // (2 * nw)))
         s_lg = p.stage(logits_tiles(lg.data_ptr(), T, E), label=("router_logits", l))
         s_rt = p.stage(self._rows(K_ROUTER, self.router_args[l], T, SUB), label=("router", l))
@@ -435,13 +486,11 @@ class ModelLane:
                         staging=self.staging[l] if self.staging[l] is not None else 0, fetch_stage0=fetch_0,
                         w13_scale=self.w.w13_scale[l] if self.w.w13_scale[l] is not None else 0,
                         w2_scale=self.w.w2_scale[l] if self.w.w2_scale[l] is not None else 0)
-            ex.copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
+            self.fab.write(ex.data_ptr(), blob)
             at += dyn
         for blob, fields, dyn in plans:
-            blob.copy_(torch.frombuffer(bytearray(pack("AttnPlanArgs", dyn_first=at, dyn_cap=dyn, **fields)),
-                                        dtype=torch.uint8))
+            self.fab.write(blob.data_ptr(), pack("AttnPlanArgs", dyn_first=at, dyn_cap=dyn, **fields))
             at += dyn
-        torch.cuda.synchronize()
 
     def _layers(self, p, T, first_stage, attention, sample_rows, n_rows):
         """The decoder after the embedding stage; `attention(p, l, prev)` adds layer l's attention
@@ -456,20 +505,18 @@ class ModelLane:
             s_qkv = self._gemm(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv, self.qkv_dim, EPI_STORE,
                                ("qkv", l), mat=w.qkv[l], bias=w.qkv_bias[l])
             p.after(prev, s_qkv)
-            qk = _block("QkArgs", qkv=self.qkv, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
+            qk = self._dev("QkArgs", qkv=self.qkv, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
                         q_norm=w.q_norm[l] if w.q_norm[l] is not None else 0,
                         k_norm=w.k_norm[l] if w.k_norm[l] is not None else 0, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
                         cos_sin=self.cos_sin, ld_qkv=self.qkv_dim, hq=hq, hkv=hkv, rot_dim=cfg.rotary_dim,
                         theta=cfg.rope_theta, eps=cfg.rms_eps, max_pos=self.max_pos)
-            self._keep.append(qk)
             s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, ROPE_ITEMS), mark=(l << 8) | 1, label=("rope", l))
             p.after(s_qkv, s_rope)
             s_attn = attention(p, l, s_rope)
             s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
                              residual=self.x, ld_res=H, mark=(l << 8) | 2, mat=w.o[l])
             p.after(s_attn, s_o)
-            nrm = _block("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
-            self._keep.append(nrm)
+            nrm = self._dev("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
             s_norm = p.stage(self._rows(K_RMSNORM, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
                              label=("norm", l))
             p.after(s_o, s_norm)
@@ -484,8 +531,7 @@ class ModelLane:
                 p.after(s_d13, s_d2)
                 prev = s_d2
                 if next_norm is not None:
-                    nn = _block("NormArgs", x=self.x, w=next_norm, out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
-                    self._keep.append(nn)
+                    nn = self._dev("NormArgs", x=self.x, w=next_norm, out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
                     prev = p.stage(self._rows(K_RMSNORM, nn, T, max(1, -(-T // (2 * self.fab.num_workers)))),
                                    label=("in_norm", l + 1))
                     p.after(s_d2, prev)
@@ -493,9 +539,8 @@ class ModelLane:
             prev = self._moe(p, l, T, s_norm, next_norm, expands)
         # final norm of the rows that continue (gather), lm_head over those rows, next tokens
         R = n_rows
-        fin = _block("NormArgs", x=self.x, w=w.final_norm, out=self.xn, gather=self.gather, out2=self.xlast, H=H, ld=H,
+        fin = self._dev("NormArgs", x=self.x, w=w.final_norm, out=self.xn, gather=self.gather, out2=self.xlast, H=H, ld=H,
                      eps=cfg.rms_eps)
-        self._keep.append(fin)
         s_fin = p.stage(self._rows(K_RMSNORM, fin, T, max(1, -(-T // (2 * self.fab.num_workers)))), label=("final_norm", L))
         p.after(prev, s_fin)
         s_lm = self._gemm(p, self.m_lm, self.m_xlast, R, cfg.vocab, H, self.logits, cfg.vocab, EPI_F32, ("lm_head", L))
@@ -512,9 +557,10 @@ class ModelLane:
         computes the batch, appends K/V to the caches, and samples one next token per request.
         all_logits: keep the logits of every row (row r of `logits`), not only each request's last."""
         page = self.kv.page
+        self.arena.reset()   # the operand blocks of this lane's previous program: it must have ended
         tokens, pos, slots, req_info, sample_rows = [], [], [], [], []
         gather = []
-        bt = self.bt.cpu()
+        bt = np.frombuffer(self.fab.read(self.bt.data_ptr(), self.bt.numel() * 4), dtype=np.int32).reshape(self.bt.shape)
         row = 0
         for r, (slot, toks, pos0) in enumerate(batch):
             n = len(toks)
@@ -529,9 +575,11 @@ class ModelLane:
             row += n
         T = row
         assert 0 < T <= self.T and (T if all_logits else len(batch)) <= self.logit_rows
-        i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()  # noqa: E731
-        self.tokens[:T], self.tok_pos[:T], self.tok_slot[:T], self.gather[:T] = i32(tokens), i32(pos), i32(slots), i32(gather)
-        self.req_info[:len(batch)] = i32(req_info)
+        self._put(self.tokens, tokens)
+        self._put(self.tok_pos, pos)
+        self._put(self.tok_slot, slots)
+        self._put(self.gather, gather)
+        self._put(self.req_info, req_info)
         cfg = self.cfg
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
         items, merge, ws_rows = plan_items(req_info, hq, hkv, sms=self.fab.num_workers)
@@ -539,9 +587,8 @@ class ModelLane:
         slot_of = torch.tensor([b[0] for b in batch], dtype=torch.int32)
         items[:, 0] = slot_of[items[:, 0].long()]
         p = Program()
-        emb = _block("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, tokens=self.tokens,
+        emb = self._dev("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, tokens=self.tokens,
                      H=cfg.hidden, ld=cfg.hidden, eps=cfg.rms_eps)
-        self._keep.append(emb)
         s_embed = p.stage(self._rows(K_EMBED, emb, T, CHUNK), label=("embed", 0))
 
         def attention(p, l, prev):
@@ -565,19 +612,18 @@ class ModelLane:
         cfg = self.cfg
         R = len(slots)
         assert 0 < R <= min(self.T, 256, self.logit_rows)
-        self.row_req[:R] = torch.tensor(slots, dtype=torch.int32).cuda()
-        self.gather[:R] = torch.arange(R, dtype=torch.int32).cuda()
+        self.arena.reset()   # the operand blocks of this lane's previous program: it must have ended
+        self._put(self.row_req, slots)
+        self._put(self.gather, np.arange(R))
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
         p = Program()
-        emb = _block("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, step=self.step_args,
+        emb = self._dev("NormArgs", x=self.x, w=self.w.in_norm[0], out=self.xn, embed=self.w.embed, step=self.step_args,
                      H=cfg.hidden, ld=cfg.hidden, eps=cfg.rms_eps)
-        self._keep.append(emb)
         s_embed = p.stage(self._rows(K_EMBED, emb, R, CHUNK), label=("embed", 0))
         plans = []
 
         def attention(p, l, prev):
-            blob = torch.zeros(_C.struct_layouts()["AttnPlanArgs"][0], dtype=torch.uint8, device="cuda")
-            self._keep.append(blob)
+            blob = self.arena.put(bytes(_C.struct_layouts()["AttnPlanArgs"][0]))   # filled with the dynamic region
             s_plan = p.stage(tile_array(K_ATTN_PLAN, a0=blob.data_ptr()), label=("attn_plan", l))
             s_a = p.stage(label=("attn", l))
             s_m = p.stage(label=("attn_merge", l))
@@ -597,10 +643,13 @@ class ModelLane:
 
     # ------------------------------------------------------------------ request state
     def set_pages(self, slot, pages):
-        row = torch.zeros(self.bt_stride, dtype=torch.int32)
-        row[:len(pages)] = torch.tensor(pages, dtype=torch.int32)
-        self.bt[slot] = row.cuda()
+        row = np.zeros(self.bt_stride, dtype=np.int32)
+        row[:len(pages)] = pages
+        self.fab.write(self.bt.data_ptr() + 4 * slot * self.bt_stride, row.tobytes())
 
     def set_request(self, slot, seq_len, last_token, temperature=0.0):
-        self.seq_len[slot], self.last_token[slot], self.steps[slot] = seq_len, last_token, 0
-        self.temperature[slot] = temperature
+        import struct
+        self.fab.write(self.seq_len.data_ptr() + 4 * slot, struct.pack("<i", seq_len))
+        self.fab.write(self.last_token.data_ptr() + 4 * slot, struct.pack("<i", last_token))
+        self.fab.write(self.steps.data_ptr() + 4 * slot, struct.pack("<i", 0))
+        self.fab.write(self.temperature.data_ptr() + 4 * slot, struct.pack("<f", temperature))
