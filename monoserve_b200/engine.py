@@ -181,7 +181,9 @@ class Engine:
             return
         page = self.kv.page
         batch, tokens = [], 0
-        in_flight = len(self.dec_batch) + len(self.joining)
+        # rows the decode lane will need: the batch it runs (or is switching to) that has not finished, and the joiners
+        current = self.dec_pending[3] if self.dec_pending else self.dec_batch
+        in_flight = sum(1 for r in current if r.finish_time is None) + len(self.joining)
         while self.queue and self.free_slots and in_flight + len(batch) < self.max_decode:
             r = self.queue[0]
             need = -(-(len(r.prompt) + 1) // page) + LOOKAHEAD_PAGES

@@ -184,3 +184,26 @@ def test_glm_style_model_matches_reference(fab, form):
         fab.stop()
         got.append(lane2.logits[0].cpu().clone())
     check_logits_away_from_ties(torch.stack(got), ref, tie_gap, rows=range(n0, len(tokens)))
+
+
+def test_checkpoint_loader_to_logits(fab, tmp_path):
+    """A tiny Qwen3-MoE checkpoint in the Hugging Face layout goes through the checkpoint loader, the
+    placement (half of every layer's experts in HBM) and a prefill program; the logits must match the
+    reference's torch oracle run on the tensors the loader returned."""
+    from monoserve_b200.checkpoint import read_checkpoint
+    from monoserve_b200.model import KVCache, ModelLane, ModelWeights
+    from oracle import torch_path as tp
+    from tests.test_checkpoint import tiny_checkpoint
+    tiny_checkpoint(str(tmp_path), glm=False)
+    cfg, w = read_checkpoint(str(tmp_path))
+    assert w.host_w13[0].is_pinned()
+    weights = ModelWeights(cfg, w, hot=[list(range(l % 2, cfg.num_experts, 2)) for l in range(cfg.num_layers)])
+    kv = KVCache(cfg, n_pages=16, page_size=16)
+    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8)
+    lane.set_pages(0, [3, 1, 2])
+    tokens = torch.randint(0, cfg.vocab, (33,), generator=torch.Generator().manual_seed(1)).tolist()
+    h = lane.build_prefill([(0, tokens, 0)], all_logits=True)
+    fab.start()
+    run_once(fab, h)
+    fab.stop()
+    check_logits(lane.logits[:len(tokens)].cpu(), tp.model_logits(w, cfg, tokens))
