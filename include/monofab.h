@@ -493,6 +493,46 @@ int monofab_plan_solve(monofab_plan_search* s, const monofab_plan_load* const* l
                        double* out, int out_cap);
 int monofab_plan_clear_cache(monofab_plan_search* s);
 
+/* Expected activated experts per layer for a number of routed rows, from per-layer activation shares
+ * and the hot-tier mask (ProfileView, csrc/control/admission.h:26-49); out = activated, and of those
+ * outside the hot tier. */
+typedef struct monofab_plan_profile monofab_plan_profile;
+int monofab_plan_profile_create(int layers, int experts, monofab_plan_profile** out);
+int monofab_plan_profile_destroy(monofab_plan_profile* p);
+int monofab_plan_profile_set(monofab_plan_profile* p, int decode, const double* shares, int n /* layers x experts */);
+int monofab_plan_profile_set_hot(monofab_plan_profile* p, const uint8_t* hot, int n /* layers x experts */);
+int monofab_plan_profile_expected(monofab_plan_profile* p, int decode, int layer, double pairs, double out[2]);
+
+/* Admission (csrc/control/admission.h:51-161, admission.cpp:226-448): which requests join the decode
+ * batch, which prompts are batched into a prefill lane, which are rejected, and the plan to publish,
+ * decided at serving events.  config [MONOFAB_PLAN_ADMISSION_FIELDS] = max_prefill_lanes, token_budget,
+ * max_batch_requests, max_decode, staging_experts, kv_capacity, kv_bytes_per_token, workspace_capacity,
+ * lane_workspace, batch_trials, reject_checks.  Events:
+ *   ARRIVE     id = request; args = prompt, max_output, arrival, ttft, tpot, now
+ *   PASS_DONE  id = prefill lane (1, 2); args = now      FINISHED  id = request; args = now
+ *   BEHIND     id = lane; args = now
+ *   PROGRESS   id = lane; args = layers done (no decision)   GENERATED  id = request; args = tokens so far
+ * A decision comes back as int64 words: publish, feasible, decode_changed, searches; then four counted
+ * lists (the fabric lane of every plan lane; the decode batch; requests that joined it; requests
+ * rejected); then the prefill passes to start: count, and per pass its lane, its request count and per
+ * request (id, tokens, first position, 1 if the prompt ends in this pass).  The plan is laid out as by
+ * monofab_plan_solve, with the decision's microseconds in header word 7. */
+#define MONOFAB_PLAN_ADMISSION_FIELDS 11
+#define MONOFAB_PLAN_EVENT_ARRIVE 0
+#define MONOFAB_PLAN_EVENT_PASS_DONE 1
+#define MONOFAB_PLAN_EVENT_FINISHED 2
+#define MONOFAB_PLAN_EVENT_BEHIND 3
+#define MONOFAB_PLAN_EVENT_PROGRESS 4
+#define MONOFAB_PLAN_EVENT_GENERATED 5
+typedef struct monofab_plan_admission monofab_plan_admission;
+int monofab_plan_admission_create(monofab_plan_estimator* e, monofab_plan_search* s, monofab_plan_profile* p,
+                                  const double* config, int n_config, monofab_plan_admission** out);
+int monofab_plan_admission_destroy(monofab_plan_admission* a);
+/* out = queued requests, requests waiting to join, open prefill lanes, KV bytes reserved */
+int monofab_plan_admission_state(monofab_plan_admission* a, double out[4]);
+int monofab_plan_admission_event(monofab_plan_admission* a, int kind, int64_t id, const double* args, int n_args,
+                                 int64_t* out, int out_cap, int* out_n, double* plan, int plan_cap);
+
 /* ---- deferred releases ---------------------------------------------------------
  * Freeing device or pinned memory and destroying streams synchronises the device, which
  * would wait for a resident fabric kernel.  Every release inside this library therefore

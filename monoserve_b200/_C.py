@@ -38,6 +38,9 @@ EXPORTS = [
     "monofab_plan_gamma_ratio", "monofab_plan_observe", "monofab_plan_correction", "monofab_plan_load_create",
     "monofab_plan_load_destroy", "monofab_plan_evaluate", "monofab_plan_search_create", "monofab_plan_search_destroy",
     "monofab_plan_deadline_floor", "monofab_plan_solve", "monofab_plan_clear_cache",
+    "monofab_plan_profile_create", "monofab_plan_profile_destroy", "monofab_plan_profile_set", "monofab_plan_profile_set_hot",
+    "monofab_plan_profile_expected", "monofab_plan_admission_create", "monofab_plan_admission_destroy",
+    "monofab_plan_admission_state", "monofab_plan_admission_event",
 ]
 EP_HANDLE_BYTES = 256   # MONOFAB_EP_HANDLE_BYTES
 
@@ -158,6 +161,16 @@ def _load():
     lib.monofab_plan_deadline_floor.argtypes = [vp, vp, f64, i32, P(i32)]
     lib.monofab_plan_solve.argtypes = [vp, vp, i32, u64, vp, i32]
     lib.monofab_plan_clear_cache.argtypes = [vp]
+    i64 = ctypes.c_int64
+    lib.monofab_plan_profile_create.argtypes = [i32, i32, P(vp)]
+    lib.monofab_plan_profile_destroy.argtypes = [vp]
+    lib.monofab_plan_profile_set.argtypes = [vp, i32, vp, i32]
+    lib.monofab_plan_profile_set_hot.argtypes = [vp, vp, i32]
+    lib.monofab_plan_profile_expected.argtypes = [vp, i32, i32, f64, P(f64 * 2)]
+    lib.monofab_plan_admission_create.argtypes = [vp, vp, vp, vp, i32, P(vp)]
+    lib.monofab_plan_admission_destroy.argtypes = [vp]
+    lib.monofab_plan_admission_state.argtypes = [vp, P(f64 * 4)]
+    lib.monofab_plan_admission_event.argtypes = [vp, i32, i64, vp, i32, vp, i32, P(i32), vp, i32]
     return lib
 
 

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmonofab.so")
-SOURCES = ["api.cu", "moe_aux.cu", "expert_gemm.cu", "pack_static.cu", "fabric_device.cu", "fabric_host.cu", "attention.cu", "host_loop.cu", "ep_exchange.cu", "release.cu", "plan_model.cu", "plan_api.cu"]
+SOURCES = ["api.cu", "moe_aux.cu", "expert_gemm.cu", "pack_static.cu", "fabric_device.cu", "fabric_host.cu", "attention.cu", "host_loop.cu", "ep_exchange.cu", "release.cu", "plan_model.cu", "plan_admission.cu", "plan_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -8,7 +8,6 @@ the same here; `as_native_module()` returns a module object with those names for
 objects here only hold inputs and results and flatten them into the arrays the C ABI
 takes (layouts in include/monofab.h).
 
-Admission (csrc/control/admission.h) is not built.
 """
 import ctypes
 import json
@@ -256,6 +255,150 @@ class PlanSearch:
     options = property(lambda self: self._opt)
 
 
+class ProfileView:
+    """Expected activated experts per layer for a number of routed rows (csrc/control/admission.h:26-49)."""
+
+    def __init__(self, layers, experts):
+        self.layers, self.experts = layers, experts
+        self._h = ctypes.c_void_p()
+        _C.check(_C.lib.monofab_plan_profile_create(layers, experts, ctypes.byref(self._h)))
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _C.lib is not None:
+            _C.lib.monofab_plan_profile_destroy(self._h)
+            self._h = None
+
+    def set_profile(self, decode, shares):
+        _C.check(_C.lib.monofab_plan_profile_set(self._h, int(decode), _doubles([float(v) for v in shares]), len(shares)))
+
+    def set_hot(self, hot):
+        mask = (ctypes.c_uint8 * len(hot))(*[int(v) for v in hot])
+        _C.check(_C.lib.monofab_plan_profile_set_hot(self._h, mask, len(hot)))
+
+    def expected(self, decode, layer, pairs):
+        out = (ctypes.c_double * 2)()
+        _C.check(_C.lib.monofab_plan_profile_expected(self._h, int(decode), int(layer), float(pairs), ctypes.byref(out)))
+        return out[0], out[1]
+
+
+class Request:
+    def __init__(self, id=0, prompt=0, max_output=1, arrival=0.0, ttft=0.0, tpot=0.0):
+        self.id, self.prompt, self.max_output, self.arrival, self.ttft, self.tpot = id, prompt, max_output, arrival, ttft, tpot
+
+
+class AdmissionConfig:
+    _FIELDS = ("max_prefill_lanes", "token_budget", "max_batch_requests", "max_decode", "staging_experts", "kv_capacity",
+               "kv_bytes_per_token", "workspace_capacity", "lane_workspace", "batch_trials", "reject_checks")
+
+    def __init__(self):
+        self.max_prefill_lanes, self.token_budget, self.max_batch_requests, self.max_decode = 2, 16384, 64, 256
+        self.staging_experts, self.kv_capacity, self.kv_bytes_per_token = 0, 0.0, 0.0
+        self.workspace_capacity, self.lane_workspace, self.batch_trials, self.reject_checks = 0.0, 0.0, 4, 2
+
+
+class PassSpec:
+    def __init__(self, reqs, tokens, pos0, last):
+        self.reqs, self.tokens, self.pos0, self.last = reqs, tokens, pos0, last
+
+
+class Decision:
+    """What an admission event decided: publish / feasible / plan / lanes (the fabric lane of every plan
+    lane) / decode_changed / decode / joined / rejected / pass_lanes + passes (prefill passes to start) /
+    searches / micros (csrc/control/admission.h:81-95)."""
+
+    def __init__(self, words, plan):
+        it = iter(words)
+        self.publish, self.feasible, self.decode_changed, self.searches = bool(next(it)), bool(next(it)), bool(next(it)), next(it)
+        take = lambda: [next(it) for _ in range(next(it))]  # noqa: E731
+        self.lanes, self.decode, self.joined, self.rejected = take(), take(), take(), take()
+        self.pass_lanes, self.passes = [], []
+        for _ in range(next(it)):
+            self.pass_lanes.append(next(it))
+            rows = [[next(it) for _ in range(4)] for _ in range(next(it))]
+            self.passes.append(PassSpec([r[0] for r in rows], [r[1] for r in rows], [r[2] for r in rows], [r[3] for r in rows]))
+        self.micros = plan[7]
+        self.plan = Plan(plan)
+
+
+class Admission:
+    """Admission events -> decisions (csrc/control/admission.h:97-161)."""
+
+    ARRIVE, PASS_DONE, FINISHED, BEHIND, PROGRESS, GENERATED = range(6)
+
+    def __init__(self, estimator, search, profile, config=None):
+        config = config or AdmissionConfig()
+        self._keep = (estimator, search, profile)
+        cfg = [float(getattr(config, f)) for f in AdmissionConfig._FIELDS]
+        self._h = ctypes.c_void_p()
+        _C.check(_C.lib.monofab_plan_admission_create(estimator._h, search._h, profile._h, _doubles(cfg), len(cfg),
+                                                      ctypes.byref(self._h)))
+        self.config = config
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _C.lib is not None:
+            _C.lib.monofab_plan_admission_destroy(self._h)
+            self._h = None
+
+    def _event(self, kind, ident, *args):
+        a = _doubles([float(v) for v in args])
+        if kind in (self.PROGRESS, self.GENERATED):
+            _C.check(_C.lib.monofab_plan_admission_event(self._h, kind, int(ident), a, len(args), None, 0, None, None, 0))
+            return None
+        words, n = (ctypes.c_int64 * 65536)(), ctypes.c_int32()
+        plan = (ctypes.c_double * (8 + 15 * 3))()
+        _C.check(_C.lib.monofab_plan_admission_event(self._h, kind, int(ident), a, len(args), words, len(words),
+                                                     ctypes.byref(n), plan, len(plan)))
+        return Decision(list(words[:n.value]), list(plan))
+
+    def arrive(self, r, now):
+        return self._event(self.ARRIVE, r.id, r.prompt, r.max_output, r.arrival, r.ttft, r.tpot, now)
+
+    def pass_done(self, lane, now):
+        return self._event(self.PASS_DONE, lane, now)
+
+    def finished(self, ident, now):
+        return self._event(self.FINISHED, ident, now)
+
+    def behind(self, lane, now):
+        return self._event(self.BEHIND, lane, now)
+
+    def progress(self, lane, layers_done):
+        self._event(self.PROGRESS, lane, layers_done)
+
+    def generated(self, ident, tokens):
+        self._event(self.GENERATED, ident, tokens)
+
+    def _state(self):
+        out = (ctypes.c_double * 4)()
+        _C.check(_C.lib.monofab_plan_admission_state(self._h, ctypes.byref(out)))
+        return list(out)
+
+    queued = property(lambda self: int(self._state()[0]))
+    waiting = property(lambda self: int(self._state()[1]))
+    open_lanes = property(lambda self: int(self._state()[2]))
+    kv_reserved = property(lambda self: self._state()[3])
+
+
+def profile_view(decode_p, prefill_p, hot):
+    """A ProfileView from [layers, experts] activation shares of the decode and prefill profiles and the
+    hot tier (a mask of the same shape, or one list of experts per layer)
+    (monoserve/control/__init__.py:60-79)."""
+    import numpy as np
+    decode_p = np.asarray(decode_p, dtype=np.float64)
+    layers, experts = decode_p.shape
+    view = ProfileView(layers, experts)
+    view.set_profile(True, decode_p.ravel().tolist())
+    view.set_profile(False, np.asarray(prefill_p, dtype=np.float64).ravel().tolist())
+    mask = np.zeros((layers, experts), dtype=np.uint8)
+    if isinstance(hot, np.ndarray) and hot.shape == (layers, experts):
+        mask[:] = hot != 0
+    else:
+        for layer, members in enumerate(hot):
+            mask[layer, list(members)] = 1
+    view.set_hot(mask.ravel().tolist())
+    return view
+
+
 # ---- helpers of monoserve/control/__init__.py and calibration.py ----------------------
 def form_name(form):
     return "asym" if form == ASYM else f"sym{form}"
@@ -320,8 +463,9 @@ def save_calibration(data, path):
 def as_native_module():
     """A module object with the names of the reference's monoserve._C.control."""
     m = types.ModuleType("monoserve._C.control")
-    m.__doc__ = "Time estimator and plan search over libmonofab (admission is not built)."
+    m.__doc__ = "Time estimator, plan search and admission over libmonofab."
     for name in ("ASYM", "Curve", "KernelRates", "ModelShape", "Calibration", "Seq", "LaneWork", "EstimatorOptions",
-                 "Estimate", "Estimator", "SearchOptions", "LanePlan", "Plan", "PlanSearch"):
+                 "Estimate", "Estimator", "SearchOptions", "LanePlan", "Plan", "PlanSearch", "ProfileView", "Request",
+                 "AdmissionConfig", "PassSpec", "Decision", "Admission"):
         setattr(m, name, globals()[name])
     return m

@@ -6,6 +6,7 @@
 #include <string>
 
 #include "../../include/monofab.h"
+#include "plan_admission.h"
 #include "plan_model.h"
 
 namespace mf {
@@ -23,6 +24,12 @@ struct monofab_plan_load {
 };
 struct monofab_plan_search {
   std::unique_ptr<PlanSearch> search;
+};
+struct monofab_plan_profile {
+  std::unique_ptr<ProfileView> view;
+};
+struct monofab_plan_admission {
+  std::unique_ptr<Admission> adm;
 };
 
 namespace {
@@ -70,6 +77,29 @@ struct Reader {
 void put_estimate(const Estimate& e, double* out) {
   const double v[9] = {e.total, e.attn, e.moe, e.staged, e.a_cmp, e.a_rd, e.m_cmp, e.m_rd, e.m_link};
   std::memcpy(out, v, sizeof v);
+}
+
+// header [8] + lanes x [15], as monofab_plan_solve lays a plan out
+void put_plan(const Plan& p, double* out) {
+  out[0] = p.feasible;
+  out[1] = static_cast<double>(p.lanes.size());
+  out[2] = p.copy_rate;
+  out[3] = p.min_slack;
+  out[4] = p.total_time;
+  out[5] = static_cast<double>(p.evaluations);
+  out[6] = p.micros;
+  out[7] = 0;
+  double* q = out + MONOFAB_PLAN_HEADER_FIELDS;
+  for (const LanePlan& l : p.lanes) {
+    q[0] = l.sms;
+    q[1] = l.credits;
+    q[2] = l.form;
+    q[3] = l.cap;
+    q[4] = l.rate;
+    q[5] = l.slack;
+    put_estimate(l.est, q + 6);
+    q += MONOFAB_PLAN_LANE_FIELDS;
+  }
 }
 
 template <class F>
@@ -265,26 +295,7 @@ int monofab_plan_solve(monofab_plan_search* s, const monofab_plan_load* const* l
       if (!lanes[i]) return fail(MONOFAB_EINVAL, "plan_solve: lane %d is NULL", i);
       loads.push_back(lanes[i]->load);
     }
-    const Plan p = s->search->solve(loads, decode_key);
-    out[0] = p.feasible;
-    out[1] = static_cast<double>(p.lanes.size());
-    out[2] = p.copy_rate;
-    out[3] = p.min_slack;
-    out[4] = p.total_time;
-    out[5] = static_cast<double>(p.evaluations);
-    out[6] = p.micros;
-    out[7] = 0;
-    double* q = out + MONOFAB_PLAN_HEADER_FIELDS;
-    for (const LanePlan& l : p.lanes) {
-      q[0] = l.sms;
-      q[1] = l.credits;
-      q[2] = l.form;
-      q[3] = l.cap;
-      q[4] = l.rate;
-      q[5] = l.slack;
-      put_estimate(l.est, q + 6);
-      q += MONOFAB_PLAN_LANE_FIELDS;
-    }
+    put_plan(s->search->solve(loads, decode_key), out);
     return MONOFAB_OK;
   });
 }
@@ -293,6 +304,146 @@ int monofab_plan_clear_cache(monofab_plan_search* s) {
   if (!s) return fail(MONOFAB_EINVAL, "plan_clear_cache: NULL handle");
   s->search->clear_cache();
   return MONOFAB_OK;
+}
+
+int monofab_plan_profile_create(int layers, int experts, monofab_plan_profile** out) {
+  if (!out) return fail(MONOFAB_EINVAL, "plan_profile_create: NULL argument");
+  return guarded("plan_profile_create", [&] {
+    auto* h = new monofab_plan_profile();
+    h->view.reset(new ProfileView(layers, experts));
+    *out = h;
+    return MONOFAB_OK;
+  });
+}
+
+int monofab_plan_profile_destroy(monofab_plan_profile* p) {
+  delete p;
+  return MONOFAB_OK;
+}
+
+int monofab_plan_profile_set(monofab_plan_profile* p, int decode, const double* shares, int n) {
+  if (!p || !shares || n < 0) return fail(MONOFAB_EINVAL, "plan_profile_set: bad argument");
+  return guarded("plan_profile_set", [&] {
+    p->view->set_profile(decode != 0, std::vector<double>(shares, shares + n));
+    return MONOFAB_OK;
+  });
+}
+
+int monofab_plan_profile_set_hot(monofab_plan_profile* p, const uint8_t* hot, int n) {
+  if (!p || !hot || n < 0) return fail(MONOFAB_EINVAL, "plan_profile_set_hot: bad argument");
+  return guarded("plan_profile_set_hot", [&] {
+    p->view->set_hot(std::vector<uint8_t>(hot, hot + n));
+    return MONOFAB_OK;
+  });
+}
+
+int monofab_plan_profile_expected(monofab_plan_profile* p, int decode, int layer, double pairs, double out[2]) {
+  if (!p || !out) return fail(MONOFAB_EINVAL, "plan_profile_expected: NULL argument");
+  const auto v = p->view->expected(decode != 0, layer, pairs);
+  out[0] = v.first;
+  out[1] = v.second;
+  return MONOFAB_OK;
+}
+
+int monofab_plan_admission_create(monofab_plan_estimator* e, monofab_plan_search* s, monofab_plan_profile* p,
+                                  const double* config, int n_config, monofab_plan_admission** out) {
+  if (!e || !s || !p || !config || !out) return fail(MONOFAB_EINVAL, "plan_admission_create: NULL argument");
+  if (n_config != MONOFAB_PLAN_ADMISSION_FIELDS) return fail(MONOFAB_EINVAL, "plan_admission_create: the configuration takes %d fields, %d given", MONOFAB_PLAN_ADMISSION_FIELDS, n_config);
+  return guarded("plan_admission_create", [&] {
+    AdmissionConfig c;
+    c.max_prefill_lanes = static_cast<int>(config[0]);
+    c.token_budget = static_cast<int>(config[1]);
+    c.max_batch_requests = static_cast<int>(config[2]);
+    c.max_decode = static_cast<int>(config[3]);
+    c.staging_experts = static_cast<int>(config[4]);
+    c.kv_capacity = config[5];
+    c.kv_bytes_per_token = config[6];
+    c.workspace_capacity = config[7];
+    c.lane_workspace = config[8];
+    c.batch_trials = static_cast<int>(config[9]);
+    c.reject_checks = static_cast<int>(config[10]);
+    auto* h = new monofab_plan_admission();
+    h->adm.reset(new Admission(e->est.get(), s->search.get(), p->view.get(), c));
+    *out = h;
+    return MONOFAB_OK;
+  });
+}
+
+int monofab_plan_admission_destroy(monofab_plan_admission* a) {
+  delete a;
+  return MONOFAB_OK;
+}
+
+int monofab_plan_admission_state(monofab_plan_admission* a, double out[4]) {
+  if (!a || !out) return fail(MONOFAB_EINVAL, "plan_admission_state: NULL argument");
+  out[0] = static_cast<double>(a->adm->queued());
+  out[1] = static_cast<double>(a->adm->waiting());
+  out[2] = a->adm->open_lanes();
+  out[3] = a->adm->kv_reserved();
+  return MONOFAB_OK;
+}
+
+int monofab_plan_admission_event(monofab_plan_admission* a, int kind, int64_t id, const double* args, int n_args,
+                                 int64_t* out, int out_cap, int* out_n, double* plan, int plan_cap) {
+  if (!a) return fail(MONOFAB_EINVAL, "plan_admission_event: NULL handle");
+  auto arg = [&](int i) { return (args && i < n_args) ? args[i] : 0.0; };
+  if (kind == MONOFAB_PLAN_EVENT_PROGRESS) {
+    a->adm->progress(static_cast<int>(id), static_cast<int>(arg(0)));
+    return MONOFAB_OK;
+  }
+  if (kind == MONOFAB_PLAN_EVENT_GENERATED) {
+    a->adm->generated(id, static_cast<int>(arg(0)));
+    return MONOFAB_OK;
+  }
+  if (!out || !out_n || !plan || plan_cap < MONOFAB_PLAN_HEADER_FIELDS + 3 * MONOFAB_PLAN_LANE_FIELDS)
+    return fail(MONOFAB_EINVAL, "plan_admission_event: the decision needs output arrays");
+  return guarded("plan_admission_event", [&] {
+    Decision d;
+    switch (kind) {
+      case MONOFAB_PLAN_EVENT_ARRIVE: {
+        Request r;
+        r.id = id;
+        r.prompt = static_cast<int>(arg(0));
+        r.max_output = static_cast<int>(arg(1));
+        r.arrival = arg(2);
+        r.ttft = arg(3);
+        r.tpot = arg(4);
+        d = a->adm->arrive(r, arg(5));
+        break;
+      }
+      case MONOFAB_PLAN_EVENT_PASS_DONE: d = a->adm->pass_done(static_cast<int>(id), arg(0)); break;
+      case MONOFAB_PLAN_EVENT_FINISHED: d = a->adm->finished(id, arg(0)); break;
+      case MONOFAB_PLAN_EVENT_BEHIND: d = a->adm->behind(static_cast<int>(id), arg(0)); break;
+      default: return fail(MONOFAB_EINVAL, "plan_admission_event: unknown event %d", kind);
+    }
+    std::vector<int64_t> v = {d.publish, d.feasible, d.decode_changed, d.searches};
+    auto list = [&](const auto& items) {
+      v.push_back(static_cast<int64_t>(items.size()));
+      for (auto x : items) v.push_back(static_cast<int64_t>(x));
+    };
+    list(d.lanes);
+    list(d.decode);
+    list(d.joined);
+    list(d.rejected);
+    v.push_back(static_cast<int64_t>(d.passes.size()));
+    for (size_t i = 0; i < d.passes.size(); ++i) {
+      const PassSpec& p = d.passes[i];
+      v.push_back(d.pass_lanes[i]);
+      v.push_back(static_cast<int64_t>(p.reqs.size()));
+      for (size_t k = 0; k < p.reqs.size(); ++k) {
+        v.push_back(p.reqs[k]);
+        v.push_back(p.tokens[k]);
+        v.push_back(p.pos0[k]);
+        v.push_back(p.last[k]);
+      }
+    }
+    if (static_cast<int>(v.size()) > out_cap) return fail(MONOFAB_EINVAL, "plan_admission_event: the decision needs %zu words, %d given", v.size(), out_cap);
+    std::memcpy(out, v.data(), v.size() * sizeof(int64_t));
+    *out_n = static_cast<int>(v.size());
+    put_plan(d.plan, plan);
+    plan[7] = d.micros;
+    return MONOFAB_OK;
+  });
 }
 
 }  // extern "C"

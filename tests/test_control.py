@@ -2,15 +2,17 @@
 calibration whose curves have the shapes a calibration run measures (rates that rise with the
 SM share and saturate, a link rate that grows with the credits up to the link's peak, a
 read stretch that grows with exposure).  The scenarios, the calibration numbers and the
-expected values are those of the reference's tests/test_control.py:21-180, restated for this
-library's Python mirror (monoserve_b200.control); admission (its lines 183-252) is not built."""
+expected values are those of the reference's tests/test_control.py:21-252, restated for this
+library's Python mirror (monoserve_b200.control)."""
 import math
 import types
 
 import pytest
 
-from monoserve_b200.control import (ASYM, Curve, Estimator, EstimatorOptions, LaneWork, PlanSearch, Seq,
-                                    load_calibration, model_shape)
+import numpy as np
+
+from monoserve_b200.control import (ASYM, Admission, AdmissionConfig, Curve, Estimator, EstimatorOptions, LaneWork,
+                                    PlanSearch, Request, Seq, load_calibration, model_shape, profile_view)
 
 SMS = 132
 GRID = [8, 16, 24, 32, 48, 64, 96, 132]
@@ -189,3 +191,78 @@ def test_bad_inputs_are_refused(cal):
         est.evaluate(est.load(decode_work()), 8, 100.0, 48)   # no such kernel form
     with pytest.raises(RuntimeError, match="decode lane must be the first"):
         PlanSearch(est).solve([est.load(prefill_work()), est.load(decode_work())])
+
+
+# ---------------------------------------------------------------- profile view and admission
+def test_profile_view_expectations():
+    p = np.full((2, 8), 1 / 8)
+    view = profile_view(p, p, [[0, 1, 2, 3], []])
+    a, m = view.expected(True, 0, 1.0)
+    assert a == pytest.approx(1.0) and m == pytest.approx(0.5)
+    a, m = view.expected(True, 0, 4096.0)
+    assert a == pytest.approx(8, rel=1e-3) and m == pytest.approx(4, rel=1e-3)
+    a, m = view.expected(False, 1, 16.0)
+    assert m == pytest.approx(a) and a == pytest.approx(8 * (1 - (7 / 8) ** 16), rel=1e-9)
+
+
+def make_admission(est, **cfg):
+    c = AdmissionConfig()
+    c.kv_bytes_per_token = model_shape(QWEN).kv_bytes_per_token
+    for k, v in cfg.items():
+        setattr(c, k, v)
+    p = np.full((48, 128), 1 / 128)
+    return Admission(est, PlanSearch(est), profile_view(p, p, [list(range(100))] * 48), c)
+
+
+def test_admission_lanes_join_and_finish(est):
+    adm = make_admission(est, token_budget=8192, staging_experts=32)
+    d = adm.arrive(Request(1, 2000, 256, 0.0, 2.0, 0.05), 0.0)
+    assert d.publish and d.feasible and d.pass_lanes == [1] and d.passes[0].reqs == [1]
+    d = adm.arrive(Request(2, 3000, 256, 0.01, 2.0, 0.05), 0.01)
+    assert d.pass_lanes == [2] and d.lanes == [1, 2]
+    d = adm.arrive(Request(3, 1000, 256, 0.02, 2.0, 0.05), 0.02)
+    assert not d.publish and adm.queued == 1        # both prefill lanes are busy
+    d = adm.pass_done(1, 0.3)                       # request 1's first token is out
+    assert d.joined == [1] and d.pass_lanes == [1] and d.passes[0].reqs == [3]
+    assert d.lanes == [0, 2, 1] and d.feasible
+    d = adm.finished(1, 0.5)
+    assert d.publish and d.decode_changed and d.decode == []
+    assert adm.kv_reserved == pytest.approx((3000 + 256 + 1000 + 256) * model_shape(QWEN).kv_bytes_per_token)
+
+
+def test_admission_chunks_long_prompts(est):
+    adm = make_admission(est, token_budget=4096)
+    d = adm.arrive(Request(9, 10000, 16, 0.0, 30.0, 0.1), 0.0)
+    assert d.pass_lanes == [1]
+    p = d.passes[0]
+    assert (p.tokens, p.pos0, p.last) == ([3334], [0], [0])
+    d = adm.pass_done(1, 1.0)
+    assert d.pass_lanes[0] == 1 and d.passes[0].pos0 == [3334]
+    d = adm.pass_done(1, 2.0)
+    assert d.passes[0].tokens == [3332] and d.passes[0].last == [1]
+    d = adm.pass_done(1, 3.0)
+    assert d.joined == [9]
+
+
+def test_admission_rejects_only_hopeless_requests(est):
+    kv = model_shape(QWEN).kv_bytes_per_token
+    adm = make_admission(est, kv_capacity=kv * 3000)
+    d = adm.arrive(Request(1, 65536, 16, 0.0, 1e-4, 0.05), 0.0)
+    assert d.rejected == [1] and adm.queued == 0
+    d = adm.arrive(Request(2, 2000, 256, 0.0, 5.0, 0.05), 0.0)
+    assert d.pass_lanes == [1]
+    # memory, not the deadline, holds this one back: it stays queued
+    d = adm.arrive(Request(3, 2000, 256, 0.0, 5.0, 0.05), 0.0)
+    assert d.pass_lanes == [] and d.rejected == [] and adm.queued == 1
+
+
+def test_behind_republishes(est):
+    adm = make_admission(est)
+    adm.arrive(Request(1, 4000, 64, 0.0, 3.0, 0.05), 0.0)
+    adm.progress(1, 20)
+    d = adm.behind(1, 0.5)
+    assert d.publish and d.lanes == [1] and d.searches == 1
+    with pytest.raises(RuntimeError, match="already known"):
+        adm.arrive(Request(1, 10, 1, 0.0, 1.0, 0.05), 0.6)
+    with pytest.raises(RuntimeError, match="not open"):
+        adm.pass_done(2, 0.7)
