@@ -148,6 +148,36 @@ def measure_link_peak(mib=256, reps=6):
     return best
 
 
+def search_plan(cfg, args, ctx, hot, glm):
+    """The control plane's plan for this workload: one decode lane (its sequences' contexts, deadline --tpot) and
+    one prefill lane (its prompts, deadline --ttft), expected activations from uniform routing shares and the
+    hot sets, the B200 calibration measured by `python -m monoserve_b200.calibrate`."""
+    import os
+    from monoserve_b200 import control
+    cal_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "calibration", "b200.json")
+    shape = types.SimpleNamespace(**vars(cfg), fp8=glm)
+    est = control.Estimator(control.model_shape(shape), control.load_calibration(cal_path))
+    E, L = cfg.num_experts, cfg.num_layers
+    p = np.full((L, E), 1.0 / E)
+    view = control.profile_view(p, p, hot)
+    dense = getattr(cfg, "dense_layers", 0)
+
+    def work(decode, seqs, deadline, rows):
+        w = control.LaneWork()
+        w.decode, w.deadline = decode, deadline
+        w.passes = [[control.Seq(t, c) for t, c in seqs]]
+        on = [view.expected(decode, l, rows * cfg.top_k) if l >= dense else (0.0, 0.0) for l in range(L)]
+        w.active, w.miss = [a for a, _ in on], [m for _, m in on]
+        return w
+    lanes = [est.load(work(True, [(1, c) for c in ctx], args.tpot, len(ctx))),
+             est.load(work(False, [(args.prompt_len, 0)] * args.prompts, args.ttft, args.prompts * args.prompt_len))]
+    plan = control.PlanSearch(est).solve(lanes)
+    return {"feasible": plan.feasible, "sms": [l.sms for l in plan.lanes], "caps": [l.cap for l in plan.lanes],
+            "forms": [l.form for l in plan.lanes], "estimated_s": [l.est.total for l in plan.lanes],
+            "slack": [l.slack for l in plan.lanes], "evaluations": plan.evaluations, "search_us": plan.micros,
+            "deadlines_s": [args.tpot, args.ttft]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=["qwen", "glm"], default="qwen")
@@ -171,6 +201,11 @@ def main():
     ap.add_argument("--host-loop", type=int, default=0, metavar="SLOTS",
                     help="run the host loop beside the fabric: the copy engine stages up to SLOTS host-resident "
                          "experts of the prefill lane's coming layer into an HBM staging buffer (two halves)")
+    ap.add_argument("--plan", choices=["given", "search"], default="given",
+                    help="search: take the SM split, link credits and kernel forms from the control plane's plan search "
+                         "(monoserve_b200.control) over the B200 calibration, with --tpot / --ttft as the lanes' deadlines")
+    ap.add_argument("--tpot", type=float, default=1.0, help="decode deadline for --plan search, seconds per step")
+    ap.add_argument("--ttft", type=float, default=3.0, help="prefill deadline for --plan search, seconds per pass")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
     glm = args.model == "glm"
@@ -185,6 +220,7 @@ def main():
     cfg = glm_config(args.layers) if glm else q_config(args.layers)
     caps = [int(v) for v in args.caps.split(",")]
     forms = [int(v) for v in args.forms.split(",")]
+    searched = None
     # before the weights are pinned: a buffer pinned after tens of GB of weights has been seen to land where
     # the copy engine reaches only 46 GB/s, below what the kernel's own reads of the weights sustain
     link_peak = max(measure_link_peak() for _ in range(2))
@@ -232,6 +268,12 @@ def main():
             batch.append((s, rng.integers(0, cfg.vocab, size=args.prompt_len).tolist(), 0))
         programs.append(pre.build_prefill(batch, iterations=0))
         lanes_map = [0] * args.sm_decode + [1] * (fab.num_workers - args.sm_decode)
+    if args.plan == "search" and pre is not None:
+        searched = search_plan(cfg, args, ctx, hot, glm)
+        if searched["feasible"]:
+            caps, forms = searched["caps"], searched["forms"]
+            args.sm_decode = min(fab.num_workers - 1, max(1, searched["sms"][0] * fab.num_workers // sum(searched["sms"])))
+            lanes_map = [0] * args.sm_decode + [1] * (fab.num_workers - args.sm_decode)
     loop = None
     if args.host_loop and pre is not None:
         from monoserve_b200.host_loop import HostLoop
@@ -311,6 +353,8 @@ def main():
     line["host_link_peak_gbs"] = link_peak
     line["host_link_frac"] = link_rate / 1e9 / link_peak if link_peak else None
     line["decode_tpot_link_bound_ms"] = dec_link / (link_peak * 1e9) * 1e3 if link_peak else None
+    if searched is not None:
+        line["searched_plan"] = searched
     if loop_stats is not None:
         # experts the copy engine staged are read from HBM by the prefill lane: the figure above counts them
         # as link reads of the kernel, so with the host loop it is an upper bound of the kernel's own reads

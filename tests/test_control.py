@@ -266,3 +266,22 @@ def test_behind_republishes(est):
         adm.arrive(Request(1, 10, 1, 0.0, 1.0, 0.05), 0.6)
     with pytest.raises(RuntimeError, match="not open"):
         adm.pass_done(2, 0.7)
+
+
+def test_committed_b200_calibration_plans_the_mixed_workload():
+    """The calibration shipped with the package loads, and the search over it gives the offload workload
+    (128 decoding sequences beside 4 prompts of 2048 tokens, half of the experts host-resident) a feasible
+    plan that hands most link credits to the decode lane and the single-pass form to the prefill lane."""
+    from monoserve_b200.benchmarks import mixed_lane as ml
+    cfg = ml.q_config(48)
+    rng = np.random.default_rng(0)
+    hot = [sorted(rng.permutation(128)[:64].tolist()) for _ in range(48)]
+    ctx = rng.integers(512, 8193, size=128).tolist()
+    args = types.SimpleNamespace(tpot=1.0, ttft=3.0, prompt_len=2048, prompts=4)
+    plan = ml.search_plan(cfg, args, ctx, hot, False)
+    assert plan["feasible"] and sum(plan["sms"]) <= 148 and min(plan["sms"]) >= 1
+    assert plan["caps"][0] > plan["caps"][1] >= 1 and sum(plan["caps"]) <= 16
+    assert plan["forms"][1] == 0 and plan["forms"][0] in (64, 128, 256)
+    assert plan["estimated_s"][0] <= 1.0 and plan["estimated_s"][1] <= 3.0
+    args.tpot = 0.3          # below what the link alone allows for the decode lane's host-resident experts
+    assert not ml.search_plan(cfg, args, ctx, hot, False)["feasible"]
