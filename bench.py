@@ -308,12 +308,16 @@ def run_ours_ep(args, wl, world, rank, local):
         rel = all_max(rel)
         exact = all_max(0.0 if exact else 1.0) == 0.0
         res = {"parity_checked": True, "rel_l2_max_over_ranks": rel, "routing_bit_exact": exact}
-        for i in range(args.warmup):
-            step(i)
-        barrier()
+        # The timed steps take a few milliseconds, less than one nvidia-smi sample: the sampler runs over them
+        # and over `hold` untimed steps of the same kind before and after, so that its samples show the clocks
+        # under this load.
+        hold = max(0, 1500 - args.steps)
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
+        for i in range(args.warmup + hold):
+            step(i)
+        barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(args.steps):
@@ -321,7 +325,12 @@ def run_ours_ep(args, wl, world, rank, local):
         b.record()
         barrier()
         res["ms_dev"] = all_max(a.elapsed_time(b))
+        for i in range(hold):
+            step(i)
+        torch.cuda.synchronize()
         res["clocks"] = sampler.stop() if rank == 0 else {}
+        if rank == 0:
+            res["clocks"]["window"] = f"the {args.steps} timed steps and {hold} untimed steps of the same kind on either side"
         layer.local.status()
         for i in range(3):
             step_e2e(i)

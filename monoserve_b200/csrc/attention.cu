@@ -6,10 +6,14 @@
 // separately), head_dim 128, scores scaled in the exp2 domain, masked keys weight 0,
 // P rounded to bf16 before P V, bf16 output.  How it computes it is different:
 //
-//   * one CTA handles one work item = (request, KV head, block of query tokens); the
-//     MMA's 128 rows are (token, q head of the group) pairs, so the K/V tile is read
-//     once for the whole GQA group (the reference re-reads it per q head in prefill and
-//     uses `group` of 64 rows in decode);
+//   * a work item is (request, KV head, block of query tokens); the MMA's 128 rows are
+//     (token, q head of the group) pairs, so the K/V tile is read once for the whole GQA
+//     group (the reference re-reads it per q head in prefill and uses `group` of 64 rows
+//     in decode);
+//   * the kernel is persistent: one CTA per SM claims items in list order (the host sorts
+//     them longest first) and its producer warp already fetches the next item's Q, K and V
+//     while the softmax warps finish the current one, so an item boundary costs neither a
+//     CTA launch nor an empty operand ring;
 //   * S = Q K^T lands in TMEM, double-buffered (2 x 128 columns); in the 32x32b TMEM
 //     layout a thread owns one query row with all its columns, so the online softmax
 //     needs no shuffles; P goes to shared memory (double-buffered) as a K-major bf16
@@ -40,6 +44,9 @@
 // first group alone.  One softmax warp per SM sub-partition is bound by instruction latency
 // (max, ex2, bf16 packing per element); the second group doubles what is in flight.  Every
 // wait is bounded; a timeout raises the status word and the CTA leaves, freeing its TMEM.
+#include <algorithm>
+#include <atomic>
+
 #include "attention_core.cuh"
 
 namespace mf {
@@ -50,10 +57,25 @@ namespace mf {
 // AttnParams::pad is nonzero.
 __device__ unsigned long long g_attn_trace[8];
 
+// The claim ring between the producer warp, which takes the CTA's next item from the launch's
+// counter, and the MMA and softmax warps (1 + 4 * kAttnGroups readers per slot).
+struct AttnClaims {
+  uint64_t full[2], empty[2], q_empty;
+  int item[2];
+};
+constexpr int kClaimSlots = 64;
+// One counter per launch in flight (the launcher hands the slots out in turn).  A launch of n items on g
+// CTAs makes exactly n + g claims, the last g of them failing, and the counter wraps to 0 with the last one.
+__device__ unsigned int g_attn_claim[kClaimSlots];
+
+// Persistent: min(items, SMs) CTAs claim items in list order (longest first) until the list is exhausted.
+// The roles of a CTA loop over its items independently; the producer runs ahead, so the next item's Q, K
+// and V arrive while the softmax warps still merge and store the current one.
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ AttnShared sh;
-  __shared__ float xbuf[2 * 128];
+  __shared__ AttnClaims cl;
+  __shared__ __align__(16) float xbuf[2 * 128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AttnWork w;
   w.q_map = &p.q_map;
@@ -64,7 +86,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   w.out = p.out;
   w.ws_o = p.ws_o;
   w.ws_ml = p.ws_ml;
-  w.trace = (p.pad && blockIdx.x == 0) ? g_attn_trace : nullptr;
+  w.trace = nullptr;
   w.scale_log2 = p.scale_log2;
   w.bt_stride = p.bt_stride;
   w.hq = p.hq;
@@ -72,7 +94,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   w.page = p.page;
   w.q_box_rows = p.q_box_rows;
   w.rep_ok = p.rep_ok;
-  w.item = p.items[blockIdx.x];
   AttnCtx c;
   c.sh = &sh;
   c.abort_flag = &sh.abort_flag;
@@ -80,12 +101,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   c.q_phase = 0;
   c.note = nullptr;
   c.xbuf = xbuf;
+  c.q_empty = &cl.q_empty;
   c.base[0] = c.base[1] = 0;
-  attn_derive(w, c);
+  volatile int* abort_flag = &sh.abort_flag;
 
   if (threadIdx.x == 0) {
     sh.abort_flag = 0;
     sh.fail_site = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&cl.full[i], 1);
+      mbar_init(&cl.empty[i], 1 + 4 * kAttnGroups);
+    }
+    mbar_init(&cl.q_empty, 1);
     attn_barriers_init(sh, 128 * kAttnGroups);
   }
   if (warp == 1) {
@@ -97,15 +124,60 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   tc_fence_after_sync();
   c.tmem_base = sh.tmem_base;
 
+  const int n_items = p.n_items;
   if (warp == 0) {
-    attn_produce(w, c);
-  } else if (warp == 1) {
-    if (lane == 0) attn_mma<2>(w, c);
-    __syncwarp();
-  } else if (c.rep) {
-    softmax_role<true, 2, kAttnGroups>(w, c, (warp - 2) >> 2);
+    // ------------------------------------------------------ claims + TMA producer
+    unsigned int* counter = &g_attn_claim[p.claim_slot];
+    const unsigned int wrap = static_cast<unsigned int>(n_items) + gridDim.x - 1;
+    bool list_ended = false;
+    for (int it = 0;; ++it) {
+      const int slot = it & 1;
+      // the slot's previous record (item it - 2) has been read by every role
+      if (it >= 2 && !warp_wait(&cl.empty[slot], ((it >> 1) - 1) & 1u, abort_flag, kAttnWaitNs)) break;
+      int i = 0;
+      if (lane == 0) {
+        const unsigned int got = atomicInc(counter, wrap);
+        i = got < static_cast<unsigned int>(n_items) ? static_cast<int>(got) : -1;
+        cl.item[slot] = i;
+        mbar_arrive(&cl.full[slot]);
+      }
+      i = __shfl_sync(0xffffffffu, i, 0);
+      if (i < 0) {
+        list_ended = true;
+        break;
+      }
+      w.item = p.items[i];
+      attn_derive(w, c);
+      attn_produce<true>(w, c);
+      attn_advance(c.n_tiles, c.q_phase, c.base);
+      if (*abort_flag) break;
+    }
+    // a CTA that gives up still makes its failing claim, so that the counter ends at 0 for the slot's next launch
+    if (!list_ended && lane == 0)
+      while (atomicInc(counter, wrap) < static_cast<unsigned int>(n_items)) {
+      }
   } else {
-    softmax_role<false, 2, kAttnGroups>(w, c, (warp - 2) >> 2);
+    for (int it = 0;; ++it) {
+      const int slot = it & 1;
+      if (!warp_wait(&cl.full[slot], (it >> 1) & 1u, abort_flag, kAttnWaitNs)) break;
+      const int i = cl.item[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&cl.empty[slot]);   // the record is read: the slot may be refilled
+      if (i < 0) break;
+      w.item = p.items[i];
+      w.trace = (p.pad && blockIdx.x == 0 && it == 0) ? g_attn_trace : nullptr;
+      attn_derive(w, c);
+      if (warp == 1) {
+        if (lane == 0) attn_mma<2, true>(w, c);
+        __syncwarp();
+      } else if (c.rep) {
+        softmax_role<true, 2, kAttnGroups, true>(w, c, (warp - 2) >> 2);
+      } else {
+        softmax_role<false, 2, kAttnGroups, true>(w, c, (warp - 2) >> 2);
+      }
+      attn_advance(c.n_tiles, c.q_phase, c.base);
+      if (*abort_flag) break;
+    }
   }
 
   tc_fence_before_sync();
@@ -138,14 +210,20 @@ cudaError_t read_attention_trace(unsigned long long out[8]) {
   return cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(unsigned long long) * 8);
 }
 
-cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream) {
-  if (p.n_items == 0) return cudaSuccess;
+cudaError_t launch_attention(const AttnParams& params, cudaStream_t stream) {
+  if (params.n_items == 0) return cudaSuccess;
   static PerDeviceOnce once;
-  const cudaError_t err = once.run([] {
+  cudaError_t err = once.run([] {
     return cudaFuncSetAttribute(paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes);
   });
   if (err != cudaSuccess) return err;
-  paged_attention_kernel<<<p.n_items, kAttnThreads, kAttnSmemBytes, stream>>>(p);
+  int device = 0, sms = 0;
+  if ((err = cudaGetDevice(&device)) != cudaSuccess) return err;
+  if ((err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return err;
+  static std::atomic<unsigned int> ticket{0};
+  AttnParams p = params;
+  p.claim_slot = static_cast<int32_t>(ticket.fetch_add(1) % kClaimSlots);
+  paged_attention_kernel<<<std::min(p.n_items, sms), kAttnThreads, kAttnSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 

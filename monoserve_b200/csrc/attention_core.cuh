@@ -32,7 +32,7 @@ struct AttnShared {
 // Wait sites, for the diagnostics word.
 enum : unsigned int {
   kAttnSiteProdK = 1, kAttnSiteProdV, kAttnSiteMmaQ, kAttnSiteMmaK, kAttnSiteMmaSFree, kAttnSiteMmaV, kAttnSiteMmaP,
-  kAttnSiteSmaxS, kAttnSiteSmaxRescale, kAttnSiteSmaxPFree, kAttnSiteSmaxFinal, kAttnSiteMmaTail,
+  kAttnSiteSmaxS, kAttnSiteSmaxRescale, kAttnSiteSmaxPFree, kAttnSiteSmaxFinal, kAttnSiteMmaTail, kAttnSiteProdQ,
 };
 __device__ __forceinline__ bool attn_gave_up(AttnShared& sh, unsigned int site) {
   atomicCAS(&sh.fail_site, 0u, site);
@@ -71,6 +71,7 @@ struct AttnCtx {
   uint32_t base[2];       // every per-tile barrier [s]: tiles of parity s so far
   volatile unsigned int* note;   // this role's wait note (tile << 8 | site), or NULL
   float* xbuf;            // two softmax groups: float [2][128] for the exchange between the halves of a row
+  uint64_t* q_empty;      // chained items only: completes once per item, when its last S MMA has read Q
 };
 
 __device__ __forceinline__ void attn_note(const AttnCtx& c, int j, unsigned int site) {
@@ -184,6 +185,11 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // The TMA producer role: the whole warp calls it.
+// kChain: the CTA works through a list of items with no barrier between them and the producer runs ahead of
+// the other roles into the next item.  The first uses of a ring stage by an item then wait for the stage's
+// last use by the item before (the barriers count uses across items: AttnCtx::base), and Q waits until the
+// MMAs of the item before have read it.
+template <bool kChain = false>
 __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c) {
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
@@ -194,6 +200,10 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
   uint8_t* const sQ = c.smem;
   uint8_t* const sK = c.smem + kTileBytes;
   uint8_t* const sV = c.smem + 3 * kTileBytes;
+  if (kChain && c.q_phase > 0 && !warp_wait(c.q_empty, (c.q_phase - 1) & 1u, abort_flag, kAttnWaitNs)) {
+    attn_gave_up(sh, kAttnSiteProdQ);
+    return;
+  }
   if (lane == 0) {
     if (rep) {
       // the same 32 rows into every lane quadrant of the M dimension
@@ -215,9 +225,11 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
   const int tile0 = item.key_begin / kKeysPerTile;
   for (int j = 0; j < n_tiles; ++j) {
     const int s = j & 1;
-    const uint32_t prev = j >= 2 ? attn_parity(c, j - 2) : 0u;   // the stage's previous use: tile j - 2
+    const uint32_t uses = c.base[s] + (j >> 1);        // earlier uses of this stage, by this item and those before
+    const bool reuse = kChain ? uses > 0 : j >= 2;
+    const uint32_t prev = (uses - 1) & 1u;             // the stage's previous use (tile j - 2 of this item, if j >= 2)
     if (lane == 0) attn_note(c, j, kAttnSiteProdK);
-    if (j >= 2 && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
+    if (reuse && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
     if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
     __syncwarp();
     int page_id = 0;
@@ -230,7 +242,7 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
       tma_load_4d(k + kHalfBytes, p.k_map, &sh.k_full[s], 64, item.kv_head, 0, page_id);
     }
     if (lane == 0) attn_note(c, j, kAttnSiteProdV);
-    if (j >= 2 && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
+    if (reuse && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
     if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
     __syncwarp();
     if (lane < pages_per_tile) {
@@ -244,7 +256,7 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
 // The MMA role: one thread calls it; its waits are the plain per-thread ones.
 // PB = P buffers in shared memory (2: the stand-alone kernel; 1: inside the fabric
 // worker, whose operand ring holds six 32 KB tiles).
-template <int PB>
+template <int PB, bool kChain = false>
 __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
@@ -266,8 +278,10 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
       attn_note(c, j, kAttnSiteMmaK);
       if (!mbar_wait_bounded(&sh.k_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) return attn_gave_up(sh, kAttnSiteMmaK);
       attn_note(c, j, kAttnSiteMmaSFree);
-      // S[s] is free once the softmax threads have turned tile j - 2 into P
-      if (j >= 2 && !mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j - 2), abort_flag, kAttnWaitNs))
+      // S[s] is free once the softmax threads have turned its previous tile (j - 2, or, in a chain of items,
+      // the last one of the item before) into P
+      const uint32_t uses = c.base[s] + (j >> 1);
+      if ((kChain ? uses > 0 : j >= 2) && !mbar_wait_bounded(&sh.p_full[s], (uses - 1) & 1u, abort_flag, kAttnWaitNs))
         return attn_gave_up(sh, kAttnSiteMmaSFree);
       tc_fence_after_sync();
       const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
@@ -276,8 +290,10 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
         umma_bf16(tmem_base + s * 128, desc_kmajor(q_addr, i), desc_kmajor(k_addr, i), idesc_s, i != 0);
       umma_commit(&sh.s_full[s]);
       umma_commit(&sh.k_empty[s]);
+      if (kChain && j == n_tiles - 1) umma_commit(c.q_empty);   // Q has been read for the last time
       return true;
     };
+    if (kChain && ok && n_tiles == 0) mbar_arrive(c.q_empty);
     if (ok && n_tiles > 0) ok = mma_s(0);
     if (ok && n_tiles > 1) ok = mma_s(1);
     for (int j = 0; ok && j < n_tiles; ++j) {
@@ -309,6 +325,9 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
 
 __device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void named_barrier_64(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void named_barrier_n(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 // The softmax / output role.  WG = softmax warp groups of four warps (1 inside the fabric
 // worker, 2 in the stand-alone kernel); `wg` is the caller's group.  A thread's row is its TMEM
@@ -318,17 +337,23 @@ __device__ __forceinline__ void named_barrier_64(int id) { asm volatile("bar.syn
 // the two threads of a row agree on the row maximum through shared memory (`c.xbuf`) and a
 // 64-thread barrier per lane quadrant, which both warps of the pair pass exactly once per
 // tile whatever else happens, so that neither can be left waiting.
-template <bool kRep, int PB, int WG>
+// kChain (a chain of items, see attn_produce): the K / V stages already receive the next item while this one
+// ends, so the merge of a quad-replicated item uses the two P buffers (64 KB, rows XOR-swizzled by 16-byte
+// chunk instead of padded) and `c.xbuf` for the (max, sum) pairs, and every softmax thread of the CTA, working
+// or not, meets at one barrier when the merge has read them.
+template <bool kRep, int PB, int WG, bool kChain = false>
 __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c, int wg) {
+  static_assert(!kChain || PB == 2, "the chained merge needs both P buffers");
   constexpr int NC = kRep ? 32 : kKeysPerTile / WG;   // key columns of a tile this thread handles
   constexpr int ND = kRep ? kHeadDim : kHeadDim / WG; // output columns of its row it rescales and stores
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
   const AttnItem& item = p.item;
   uint8_t* const sP = c.smem + 5 * kTileBytes;
-  // merge scratch over the K / V stages, free once the last P V has completed
-  float* const scratch = reinterpret_cast<float*>(c.smem + kTileBytes);
-  float2(*const ml)[32] = reinterpret_cast<float2(*)[32]>(scratch + kPartFloats);
+  // merge scratch over the K / V stages (over the P buffers in a chain), free once the last P V has completed
+  float* const scratch = reinterpret_cast<float*>(kChain ? sP : c.smem + kTileBytes);
+  float2(*const ml)[32] = reinterpret_cast<float2(*)[32]>(kChain ? c.xbuf : scratch + kPartFloats);
+  constexpr int kLd = kChain ? kHeadDim : kPartLd;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = warp & 3;
   const int r = quad * 32 + lane;                 // TMEM lane = row of S, P and O
@@ -551,7 +576,10 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     }
     return;
   }
-  if (!works) return;   // the other softmax group merges the quad-replicated item
+  if (!works) {   // the other softmax group merges the quad-replicated item
+    if (kChain) named_barrier_n(6, 128 * WG);
+    return;
+  }
   // quad-replicated item: merge the four column quarters.  Every thread of the group takes part
   // in both barriers, also after a timeout, so that none of them can be left waiting.
   ml[quad][lane] = make_float2(m, l);
@@ -564,7 +592,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   for (int q = 0; q < 4; ++q) L += ml[q][lane].y * fast_exp2(ml[q][lane].x - M);
   {
     const float f = fast_exp2(m - M);
-    float4* mine = reinterpret_cast<float4*>(scratch + (quad * 32 + lane) * kPartLd);
+    float4* mine = reinterpret_cast<float4*>(scratch + (quad * 32 + lane) * kLd);
+    const int sw = kChain ? lane : 0;   // chunk i of a row sits at i ^ lane: conflict-free without padding
 #pragma unroll
     for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
       uint32_t o[32];
@@ -578,8 +607,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        mine[(c0 >> 2) + i] = make_float4(__uint_as_float(o[4 * i]) * f, __uint_as_float(o[4 * i + 1]) * f,
-                                          __uint_as_float(o[4 * i + 2]) * f, __uint_as_float(o[4 * i + 3]) * f);
+        mine[((c0 >> 2) + i) ^ sw] = make_float4(__uint_as_float(o[4 * i]) * f, __uint_as_float(o[4 * i + 1]) * f,
+                                                 __uint_as_float(o[4 * i + 2]) * f, __uint_as_float(o[4 * i + 3]) * f);
     }
   }
   named_barrier_128(1);
@@ -590,10 +619,11 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     for (int i = 0; i < 32; ++i) acc[i] = 0.f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float4* src = reinterpret_cast<const float4*>(scratch + (q * 32 + lane) * kPartLd + quad * 32);
+      const float4* src = reinterpret_cast<const float4*>(scratch + (q * 32 + lane) * kLd);
+      const int sw = kChain ? lane : 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float4 t = src[i];
+        const float4 t = src[(quad * 8 + i) ^ sw];
         acc[4 * i] += t.x;
         acc[4 * i + 1] += t.y;
         acc[4 * i + 2] += t.z;
@@ -618,6 +648,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
       }
     }
   }
+  // the scratch is the next item's P buffers and `ml` its exchange buffer: nobody goes on before all have read
+  if (kChain) named_barrier_n(6, 128 * WG);
 }
 
 // Merge of the parts of one split (request, block, KV head): one warp per output row

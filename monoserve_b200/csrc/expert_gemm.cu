@@ -209,16 +209,37 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issue
     GemmPipe pipe;
+    // with the trace on, every CTA also leaves a summary at trace[1024 + 8 * CTA]: entry, first and last
+    // tile of the MMA warp (device time), tiles, w2 tiles, cycles spent waiting for operands / issuing
+    unsigned long long* own = p.trace ? p.trace + 1024 + 8 * blockIdx.x : nullptr;
+    long long sum_wait = 0, sum_issue = 0, sum_acc = 0, sum_work = 0;
+    int n_w2 = 0;
+    if (own && lane == 0) own[0] = globaltimer_ns();
     for (int it = 0;; ++it) {
       const int slot = it % kWorkSlots, buf = it & 1;
+      const long long tw = own ? clock64() : 0;
       if (!mbar_wait_bounded(&sh.work_full[slot], (it / kWorkSlots) & 1, abort_flag, kWaitBudgetNs)) break;
+      if (own) sum_work += clock64() - tw;
       if (!sh.work[slot].valid) break;
       trace_ev(p, 2, it, 0);
-      long long waited[2] = {0, 0};
+      if (own && lane == 0 && it == 0) own[1] = globaltimer_ns();
+      long long waited[3] = {0, 0, 0};
       if (!gemm_mma<false>(sh.work[slot], ring, sh.bar, pipe, tmem_base, buf, (it >> 1) & 1, abort_flag,
                     p.trace ? waited : nullptr))
         break;
       trace_ev(p, 2, it, 1);
+      if (own && lane == 0) {
+        sum_wait += waited[0];
+        sum_issue += waited[1];
+        sum_acc += waited[2];
+        own[7] = sum_acc;
+        n_w2 += sh.work[slot].block < 0;
+        own[2] = globaltimer_ns();
+        own[3] = it + 1;
+        own[4] = n_w2;
+        own[5] = sum_wait;
+        own[6] = sum_issue + (static_cast<unsigned long long>(sum_work) << 32);
+      }
       if (lane == 0) {
         mbar_arrive(&sh.work_empty[slot]);
         if (p.trace && blockIdx.x == 0 && it < 32) {

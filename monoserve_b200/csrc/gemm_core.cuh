@@ -246,7 +246,9 @@ __device__ __forceinline__ bool gemm_mma(const GemmWork& w, uint8_t* ring, GemmB
   const int lane = threadIdx.x & 31;
   int ok = 1;
   if (lane == 0) {
+    const long long ta = wait_cycles ? clock64() : 0;
     if (!mbar_wait_bounded(&bar.acc_empty[buf], acc_parity ^ 1, abort_flag, kWaitBudgetNs)) ok = 0;
+    if (wait_cycles) wait_cycles[2] += clock64() - ta;
     tc_fence_after_sync();
     const uint32_t idesc = umma_idesc_bf16(128, w.n);
     const uint32_t acc = tmem_base + buf * kAccCols;

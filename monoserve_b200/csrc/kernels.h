@@ -180,7 +180,7 @@ struct AttnParams {
   float* ws_o;          // split items: unnormalised O rows, fp32 [rows][128]
   float2* ws_ml;        // and their (max, sum)
   int32_t rep_ok;       // q_map_small is valid (the group divides 32)
-  int32_t pad2;
+  int32_t claim_slot;   // which of the launch counters this launch claims its items from (set by launch_attention)
 };
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t stream);
