@@ -120,7 +120,9 @@ def fabric_maps(fab, q, k_cache, v_cache):
     dims, strides = [128, hq, T], [256, hq * 256]
     q_map = fab.tensor_map(q.data_ptr(), dims, strides, [64, group, 128 // group])
     q_small = fab.tensor_map(q.data_ptr(), dims, strides, [64, group, 32 // group]) if 32 % group == 0 else 0
-    kd, ks, kb = [128, hkv, page, n_pages], [256, hkv * 256, page * hkv * 256], [64, 1, page, 1]
+    # one box = one page's keys of one KV head, both halves of the head dimension, in groups of eight keys
+    row = hkv * 256
+    kd, ks, kb = [64, 8, 2 * hkv, page // 8, n_pages], [row, 128, 8 * row, page * row], [64, 8, 2, page // 8, 1]
     return q_map, q_small, fab.tensor_map(k_cache.data_ptr(), kd, ks, kb), fab.tensor_map(v_cache.data_ptr(), kd, ks, kb)
 
 

@@ -413,7 +413,7 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
   if (hkv < 1 || hq < hkv || hq % hkv) return fail(MONOFAB_EINVAL, "attention: hq=%d must be a multiple of hkv=%d", hq, hkv);
   const int group = hq / hkv;
   if (group > 128) return fail(MONOFAB_EINVAL, "attention: GQA group %d exceeds 128 rows", group);
-  if (page_size < 8 || page_size > 128 || 128 % page_size) return fail(MONOFAB_EINVAL, "attention: page_size=%d must divide 128 and be at least 8", page_size);
+  if (page_size < 8 || page_size > 128 || 128 % page_size) return fail(MONOFAB_EINVAL, "attention: page_size=%d must be 8, 16, 32, 64 or 128", page_size);
   if (tokens < 1 || n_pages < 1 || n_items < 0 || bt_stride < 1) return fail(MONOFAB_EINVAL, "attention: bad sizes");
   AttnParams p;
   std::memset(&p, 0, sizeof p);
@@ -430,10 +430,16 @@ int monofab_attention(const void* q, const void* k_cache, const void* v_cache, v
     }
   }
   for (int i = 0; i < 2; ++i) {
-    const uint64_t dims[4] = {128, static_cast<uint64_t>(hkv), static_cast<uint64_t>(page_size), static_cast<uint64_t>(n_pages)};
-    const uint64_t strides[3] = {256, static_cast<uint64_t>(hkv) * 256, static_cast<uint64_t>(page_size) * hkv * 256};
-    const uint32_t box[4] = {64, 1, static_cast<uint32_t>(page_size), 1};
-    if (int r = encode_map(i == 0 ? &p.k_map : &p.v_map, 0, i == 0 ? k_cache : v_cache, 4, dims, strides, box, 128)) return r;
+    // One box = one page's keys of one KV head with both halves of the head dimension, delivered as groups of
+    // eight keys: (64 d, 8 keys, the 2 halves, page / 8 groups).  The cache row of a key holds hkv heads of
+    // 128 elements, i.e. 2 hkv halves of 128 bytes, so a head's halves are coordinates 2 h and 2 h + 1 of
+    // the third dimension.
+    const uint64_t row = static_cast<uint64_t>(hkv) * 256;
+    const uint64_t dims[5] = {64, 8, 2 * static_cast<uint64_t>(hkv), static_cast<uint64_t>(page_size / 8),
+                              static_cast<uint64_t>(n_pages)};
+    const uint64_t strides[4] = {row, 128, 8 * row, static_cast<uint64_t>(page_size) * row};
+    const uint32_t box[5] = {64, 8, 2, static_cast<uint32_t>(page_size / 8), 1};
+    if (int r = encode_map(i == 0 ? &p.k_map : &p.v_map, 0, i == 0 ? k_cache : v_cache, 5, dims, strides, box, 128)) return r;
   }
   p.items = reinterpret_cast<const AttnItem*>(items);
   p.block_table = block_table;

@@ -168,8 +168,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
       w.trace = (p.pad && blockIdx.x == 0 && it == 0) ? g_attn_trace : nullptr;
       attn_derive(w, c);
       if (warp == 1) {
-        if (lane == 0) attn_mma<2, true>(w, c);
-        __syncwarp();
+        attn_mma<2, true>(w, c);
       } else if (c.rep) {
         softmax_role<true, 2, kAttnGroups, true>(w, c, (warp - 2) >> 2);
       } else {

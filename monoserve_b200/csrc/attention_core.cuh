@@ -45,7 +45,7 @@ constexpr int kPartFloats = 4 * 32 * kPartLd;   // then float2 [4][32]: (max, su
 struct AttnWork {
   const CUtensorMap* q_map;         // dims (128, hq, T), box (64, group, tokens per block)
   const CUtensorMap* q_map_small;   // box (64, group, 32 / group), or unused when rep_ok is 0
-  const CUtensorMap* k_map;         // dims (128, hkv, page, pages), box (64, 1, page, 1)
+  const CUtensorMap* k_map;         // dims (64, 8, 2 hkv, page / 8, pages), box (64, 8, 2, page / 8, 1)
   const CUtensorMap* v_map;
   const int32_t* block_table;
   __nv_bfloat16* out;               // [T][hq][128]
@@ -115,20 +115,36 @@ __device__ __forceinline__ void attn_barriers_init(AttnShared& sh, int softmax_t
   fence_barrier_init();
 }
 
-// K-major SW128 descriptor of a 128-row tile with two 64-element column halves;
+// K-major SW128 descriptor of the Q or P tile: 128 rows, two 64-element column halves 16 KB apart;
 // step = one of the eight 16-element K steps.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int step) {
   return umma_desc_sw128(tile_addr + (step >> 2) * kHalfBytes + (step & 3) * 32);
 }
 
-// MN-major SW128 descriptor of V: rows are keys (the K dimension), 128 bytes = 64 d
-// elements per row, eight-key groups 1024 bytes apart (SBO), the second d half one
-// 16 KB half-tile further (LBO).  step = one of the eight 16-key K steps.
+// A K or V tile in shared memory: 128 keys in groups of eight; a group is 2 KB: its eight 128-byte rows of
+// head-dim half 0, then those of half 1.  (One TMA box per page delivers both halves of the page's keys in
+// this order: attention.cu, the cache maps.)  So the eight-key groups of one half are 2 KB apart and the
+// other half lies 1 KB further.
+constexpr uint32_t kKvGroupBytes = 2048, kKvHalfOffset = 1024;
+
+// K as the K-major B operand of S = Q K^T (rows = keys, contraction over d): step = one of the eight
+// 16-element d steps.
+__device__ __forceinline__ uint64_t desc_k_tile(uint32_t tile_addr, int step) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>(((tile_addr + (step >> 2) * kKvHalfOffset + (step & 3) * 32) & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(kKvGroupBytes >> 4) << 32;   // stride byte offset: next 8 keys
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// V as the MN-major B operand of O += P V (rows are keys = the contraction dimension, 128 bytes = 64 d
+// elements per row): step = one of the eight 16-key K steps.
 __device__ __forceinline__ uint64_t desc_v_mnmajor(uint32_t tile_addr, int step) {
   uint64_t d = 0;
-  d |= static_cast<uint64_t>(((tile_addr + step * 2048) & 0x3ffffu) >> 4);
-  d |= static_cast<uint64_t>(kHalfBytes >> 4) << 16;   // leading byte offset: next 64 d elements
-  d |= static_cast<uint64_t>(1024u >> 4) << 32;        // stride byte offset: next 8 keys
+  d |= static_cast<uint64_t>(((tile_addr + step * 2 * kKvGroupBytes) & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(kKvHalfOffset >> 4) << 16;   // leading byte offset: next 64 d elements
+  d |= static_cast<uint64_t>(kKvGroupBytes >> 4) << 32;   // stride byte offset: next 8 keys
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
   return d;
@@ -164,6 +180,17 @@ __device__ __forceinline__ void tma_load_4d(void* smem, const void* map, uint64_
       :
       : "r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
         "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem, const void* map, uint64_t* bar, int c0, int c1, int c2, int c3,
+                                            int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3), "r"(c4)
       : "memory");
 }
 
@@ -220,7 +247,7 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
     }
   }
   const int pages_per_tile = kKeysPerTile / p.page;
-  const int page_bytes = p.page * 128;   // one d half of one page
+  const int page_bytes = p.page * 256;   // one page's keys of this head, both d halves
   const int last_page = (kv_end - 1) / p.page;
   const int tile0 = item.key_begin / kKeysPerTile;
   for (int j = 0; j < n_tiles; ++j) {
@@ -237,23 +264,21 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
       // pages past the visible range repeat the last visible page; their keys are masked
       const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
       page_id = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
-      uint8_t* k = sK + s * kTileBytes + lane * page_bytes;
-      tma_load_4d(k, p.k_map, &sh.k_full[s], 0, item.kv_head, 0, page_id);
-      tma_load_4d(k + kHalfBytes, p.k_map, &sh.k_full[s], 64, item.kv_head, 0, page_id);
+      tma_load_5d(sK + s * kTileBytes + lane * page_bytes, p.k_map, &sh.k_full[s], 0, 0, 2 * item.kv_head, 0, page_id);
     }
     if (lane == 0) attn_note(c, j, kAttnSiteProdV);
     if (reuse && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
     if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
     __syncwarp();
     if (lane < pages_per_tile) {
-      uint8_t* v = sV + s * kTileBytes + lane * page_bytes;
-      tma_load_4d(v, p.v_map, &sh.v_full[s], 0, item.kv_head, 0, page_id);
-      tma_load_4d(v + kHalfBytes, p.v_map, &sh.v_full[s], 64, item.kv_head, 0, page_id);
+      tma_load_5d(sV + s * kTileBytes + lane * page_bytes, p.v_map, &sh.v_full[s], 0, 0, 2 * item.kv_head, 0, page_id);
     }
   }
 }
 
-// The MMA role: one thread calls it; its waits are the plain per-thread ones.
+// The MMA role: the whole MMA warp calls it and runs the tile loop in step (every lane waits on the
+// barriers itself); one elected lane issues the MMAs and commits.  The loop is convergent code, so the
+// descriptors are warp-uniform values (in a single-lane branch the issue path was about twice as slow).
 // PB = P buffers in shared memory (2: the stand-alone kernel; 1: inside the fabric
 // worker, whose operand ring holds six 32 KB tiles).
 template <int PB, bool kChain = false>
@@ -261,66 +286,70 @@ __device__ __forceinline__ void attn_mma(const AttnWork& p, const AttnCtx& c) {
   AttnShared& sh = *c.sh;
   volatile int* abort_flag = c.abort_flag;
   const int n_tiles = c.n_tiles;
+  const bool leader = elect_one();
   const uint32_t tmem_base = c.tmem_base, tmem_o = c.tmem_base + 256;
   uint8_t* const sQ = c.smem;
   uint8_t* const sK = c.smem + kTileBytes;
   uint8_t* const sV = c.smem + 3 * kTileBytes;
   uint8_t* const sP = c.smem + 5 * kTileBytes;
-  {
-    // S = Q K^T: both K-major; O += P V: A K-major, B (V) MN-major
-    const uint32_t idesc_s = umma_idesc_bf16(128, 128);
-    const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
-    const uint32_t q_addr = smem_u32(sQ);
-    attn_note(c, 0, kAttnSiteMmaQ);
-    bool ok = mbar_wait_bounded(&sh.q_full, c.q_phase & 1u, abort_flag, kAttnWaitNs) || attn_gave_up(sh, kAttnSiteMmaQ);
-    auto mma_s = [&](int j) {
-      const int s = j & 1;
-      attn_note(c, j, kAttnSiteMmaK);
-      if (!mbar_wait_bounded(&sh.k_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) return attn_gave_up(sh, kAttnSiteMmaK);
-      attn_note(c, j, kAttnSiteMmaSFree);
-      // S[s] is free once the softmax threads have turned its previous tile (j - 2, or, in a chain of items,
-      // the last one of the item before) into P
-      const uint32_t uses = c.base[s] + (j >> 1);
-      if ((kChain ? uses > 0 : j >= 2) && !mbar_wait_bounded(&sh.p_full[s], (uses - 1) & 1u, abort_flag, kAttnWaitNs))
-        return attn_gave_up(sh, kAttnSiteMmaSFree);
-      tc_fence_after_sync();
-      const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
+  // S = Q K^T: both K-major; O += P V: A K-major, B (V) MN-major
+  const uint32_t idesc_s = umma_idesc_bf16(128, 128);
+  const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
+  const uint32_t q_addr = smem_u32(sQ);
+  if (leader) attn_note(c, 0, kAttnSiteMmaQ);
+  bool ok = mbar_wait_bounded(&sh.q_full, c.q_phase & 1u, abort_flag, kAttnWaitNs) || attn_gave_up(sh, kAttnSiteMmaQ);
+  auto mma_s = [&](int j) {
+    const int s = j & 1;
+    if (leader) attn_note(c, j, kAttnSiteMmaK);
+    if (!mbar_wait_bounded(&sh.k_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) return attn_gave_up(sh, kAttnSiteMmaK);
+    if (leader) attn_note(c, j, kAttnSiteMmaSFree);
+    // S[s] is free once the softmax threads have turned its previous tile (j - 2, or, in a chain of items,
+    // the last one of the item before) into P
+    const uint32_t uses = c.base[s] + (j >> 1);
+    if ((kChain ? uses > 0 : j >= 2) && !mbar_wait_bounded(&sh.p_full[s], (uses - 1) & 1u, abort_flag, kAttnWaitNs))
+      return attn_gave_up(sh, kAttnSiteMmaSFree);
+    tc_fence_after_sync();
+    const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
+    if (leader) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        umma_bf16(tmem_base + s * 128, desc_kmajor(q_addr, i), desc_kmajor(k_addr, i), idesc_s, i != 0);
+        umma_bf16(tmem_base + s * 128, desc_kmajor(q_addr, i), desc_k_tile(k_addr, i), idesc_s, i != 0);
       umma_commit(&sh.s_full[s]);
       umma_commit(&sh.k_empty[s]);
       if (kChain && j == n_tiles - 1) umma_commit(c.q_empty);   // Q has been read for the last time
-      return true;
-    };
-    if (kChain && ok && n_tiles == 0) mbar_arrive(c.q_empty);
-    if (ok && n_tiles > 0) ok = mma_s(0);
-    if (ok && n_tiles > 1) ok = mma_s(1);
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int s = j & 1;
-      attn_note(c, j, kAttnSiteMmaV);
-      if (!mbar_wait_bounded(&sh.v_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaV); break; }
-      attn_note(c, j, kAttnSiteMmaP);
-      if (!mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaP); break; }
-      tc_fence_after_sync();
-      const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + (j % PB) * kTileBytes);
+    }
+    return true;
+  };
+  if (kChain && ok && n_tiles == 0 && leader) mbar_arrive(c.q_empty);
+  if (ok && n_tiles > 0) ok = mma_s(0);
+  if (ok && n_tiles > 1) ok = mma_s(1);
+  for (int j = 0; ok && j < n_tiles; ++j) {
+    const int s = j & 1;
+    if (leader) attn_note(c, j, kAttnSiteMmaV);
+    if (!mbar_wait_bounded(&sh.v_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaV); break; }
+    if (leader) attn_note(c, j, kAttnSiteMmaP);
+    if (!mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaP); break; }
+    tc_fence_after_sync();
+    const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + (j % PB) * kTileBytes);
+    if (leader) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
         umma_bf16(tmem_o, desc_kmajor(p_addr, i), desc_v_mnmajor(v_addr, i), idesc_o, (j | i) != 0);
       umma_commit(&sh.o_full[s]);
       umma_commit(&sh.v_empty[s]);
-      if (j + 2 < n_tiles && !mma_s(j + 2)) break;
     }
-    // Leave only after the last commits have arrived on their barriers: a caller that re-arms
-    // the barriers for its next item must not see a late arrival from this one.
-    for (int j = max(0, n_tiles - 2); ok && j < n_tiles; ++j) {
-      attn_note(c, j, kAttnSiteMmaTail);
-      ok = (mbar_wait_bounded(&sh.k_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
-            attn_gave_up(sh, kAttnSiteMmaTail)) &&
-           (mbar_wait_bounded(&sh.v_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
-            attn_gave_up(sh, kAttnSiteMmaTail + 16));
-    }
+    if (j + 2 < n_tiles && !mma_s(j + 2)) break;
   }
+  // Leave only after the last commits have arrived on their barriers: a caller that re-arms
+  // the barriers for its next item must not see a late arrival from this one.
+  for (int j = max(0, n_tiles - 2); ok && j < n_tiles; ++j) {
+    if (leader) attn_note(c, j, kAttnSiteMmaTail);
+    ok = (mbar_wait_bounded(&sh.k_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+          attn_gave_up(sh, kAttnSiteMmaTail)) &&
+         (mbar_wait_bounded(&sh.v_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+          attn_gave_up(sh, kAttnSiteMmaTail + 16));
+  }
+  __syncwarp();
 }
 
 __device__ __forceinline__ void named_barrier_128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }

@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
     long long sum_wait = 0, sum_issue = 0, sum_acc = 0, sum_work = 0;
     int n_w2 = 0;
     if (own && lane == 0) own[0] = globaltimer_ns();
+    const long long c_begin = own ? clock64() : 0;
     for (int it = 0;; ++it) {
       const int slot = it % kWorkSlots, buf = it & 1;
       const long long tw = own ? clock64() : 0;
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
       if (own && lane == 0 && it == 0) own[1] = globaltimer_ns();
       long long waited[3] = {0, 0, 0};
       if (!gemm_mma<false>(sh.work[slot], ring, sh.bar, pipe, tmem_base, buf, (it >> 1) & 1, abort_flag,
-                    p.trace ? waited : nullptr))
+                           p.trace ? waited : nullptr))
         break;
       trace_ev(p, 2, it, 1);
       if (own && lane == 0) {
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(FP8 ? kGemmThreadsFp8 : kGemmThreads, 1)
         n_w2 += sh.work[slot].block < 0;
         own[2] = globaltimer_ns();
         own[3] = it + 1;
-        own[4] = n_w2;
+        own[4] = static_cast<unsigned long long>(n_w2) | (static_cast<unsigned long long>(clock64() - c_begin) << 16);
         own[5] = sum_wait;
         own[6] = sum_issue + (static_cast<unsigned long long>(sum_work) << 32);
       }

@@ -1067,8 +1067,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
         // so waiting for them is all the ordering this role needs
         AttnCtx c = attn_ctx(w.attn, sh.attn, abort_flag, ring, tmem_base, aq, ab, &sh.wait_note[1]);
         if (lane == 0) sh.wait_ctx[1] = role_ctx(n, aq, ab);
-        if (lane == 0) attn_mma<1>(w.attn, c);
-        __syncwarp();
+        attn_mma<1>(w.attn, c);
         attn_advance(c.n_tiles, aq, ab);
       } else if (w.is_gemm) {
         ok = gemm_mma(w.gemm, ring, sh.bar, pipe, tmem_base, g & 1, (g >> 1) & 1, abort_flag);

@@ -166,7 +166,7 @@ static_assert(sizeof(AttnItem) == 48, "AttnItem is twelve int32");
 
 struct AttnParams {
   CUtensorMap q_map;    // dims (128, hq, T), box (64, group, tokens per block)
-  CUtensorMap k_map;    // dims (128, hkv, page, pages), box (64, 1, page, 1)
+  CUtensorMap k_map;    // dims (64, 8, 2 hkv, page / 8, pages), box (64, 8, 2, page / 8, 1): see monofab_attention
   CUtensorMap v_map;
   CUtensorMap q_map_small;   // box (64, group, 32 / group): items of at most 32 rows
   const AttnItem* items;
