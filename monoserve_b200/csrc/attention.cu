@@ -72,10 +72,12 @@ __device__ unsigned int g_attn_claim[kClaimSlots];
 // The roles of a CTA loop over its items independently; the producer runs ahead, so the next item's Q, K
 // and V arrive while the softmax warps still merge and store the current one.
 __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const __grid_constant__ AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  // The operand tiles need 1024-byte alignment (128-byte swizzle); static shared memory (under 3 KB) comes
+  // first, so the seven tiles end exactly at the 227 KB a CTA may have.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ AttnShared sh;
   __shared__ AttnClaims cl;
-  __shared__ __align__(16) float xbuf[2 * 128];
+  __shared__ __align__(16) float xbuf[kAttnGroups * 128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AttnWork w;
   w.q_map = &p.q_map;
@@ -97,7 +99,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   AttnCtx c;
   c.sh = &sh;
   c.abort_flag = &sh.abort_flag;
-  c.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  c.smem = smem_raw;
+  if (smem_u32(smem_raw) & 1023u) {   // never seen; the tiles would not be where the descriptors say
+    if (threadIdx.x == 0) atomicOr(p.status, kErrBadArgs);
+    return;
+  }
   c.q_phase = 0;
   c.note = nullptr;
   c.xbuf = xbuf;

@@ -17,7 +17,7 @@ constexpr int kHeadDim = 128;
 constexpr int kKeysPerTile = 128;
 constexpr int kHalfBytes = 128 * 128;            // 128 rows x 64 bf16: one swizzle atom column, 16 KB
 constexpr int kTileBytes = 2 * kHalfBytes;       // 128 x 128 bf16
-constexpr int kAttnSmemBytes = kTileBytes * 7 + 1024;   // Q, K x2, V x2, P x2
+constexpr int kAttnSmemBytes = kTileBytes * 7;   // Q, K x2, V x2, P x2; the kernel declares the array 1024-byte aligned
 constexpr int kAttnTmemCols = 512;               // S x2 (256) + O (128), allocated as a power of two
 constexpr unsigned long long kAttnWaitNs = 4000000000ull;
 constexpr float kMaxSlack = 8.f;   // how far a row maximum may exceed the reference point of its exponentials
@@ -61,7 +61,7 @@ struct AttnWork {
 struct AttnCtx {
   AttnShared* sh;
   volatile int* abort_flag;
-  uint8_t* smem;          // 1024-byte aligned, kAttnSmemBytes - 1024 bytes: Q, K x2, V x2, P x2
+  uint8_t* smem;          // 1024-byte aligned, seven 32 KB tiles: Q, K x2, V x2, P x2
   uint32_t tmem_base;     // 384 columns: S x2, O
   int n_tiles, rows, kv_end;
   bool rep;
@@ -70,7 +70,7 @@ struct AttnCtx {
   uint32_t q_phase;       // q_full
   uint32_t base[2];       // every per-tile barrier [s]: tiles of parity s so far
   volatile unsigned int* note;   // this role's wait note (tile << 8 | site), or NULL
-  float* xbuf;            // two softmax groups: float [2][128] for the exchange between the halves of a row
+  float* xbuf;            // several softmax groups: float [groups][128] for the exchange between the parts of a row
   uint64_t* q_empty;      // chained items only: completes once per item, when its last S MMA has read Q
 };
 
@@ -359,13 +359,15 @@ __device__ __forceinline__ void named_barrier_n(int id, int threads) {
 }
 
 // The softmax / output role.  WG = softmax warp groups of four warps (1 inside the fabric
-// worker, 2 in the stand-alone kernel); `wg` is the caller's group.  A thread's row is its TMEM
-// lane.  kRep (quad-replicated item, at most 32 rows): the thread's row is `lane`, its columns
-// are quarter `quad` of the tile, and only group 0 works.  Otherwise the thread owns one of 128
-// query rows and, with two groups, half of the tile's key columns and half of the row's output:
-// the two threads of a row agree on the row maximum through shared memory (`c.xbuf`) and a
-// 64-thread barrier per lane quadrant, which both warps of the pair pass exactly once per
-// tile whatever else happens, so that neither can be left waiting.
+// worker, kAttnGroups in the stand-alone kernel); `wg` is the caller's group.  A thread's row is
+// its TMEM lane.  kRep (quad-replicated item, at most 32 rows): the thread's row is `lane`, its
+// columns are quarter `quad` of the tile, and only group 0 works.  Otherwise the thread owns one
+// of 128 query rows and, with WG groups, 1 / WG of the tile's key columns and of the row's output:
+// the WG threads of a row agree on the row maximum through shared memory (`c.xbuf`) and a
+// barrier per lane quadrant, which all warps of the quadrant pass exactly twice per tile
+// whatever else happens, so that none can be left waiting.  (Two groups: with four, 576 threads
+// leave 96 registers each and the spills cost more than the extra warps hide: decode 517 us
+// against 226, prefill 301 us against 253 on the benchmark shapes.)
 // kChain (a chain of items, see attn_produce): the K / V stages already receive the next item while this one
 // ends, so the merge of a quad-replicated item uses the two P buffers (64 KB, rows XOR-swizzled by 16-byte
 // chunk instead of padded) and `c.xbuf` for the (max, sum) pairs, and every softmax thread of the CTA, working
@@ -389,7 +391,7 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   const int lr = kRep ? lane : r;                 // row of the item
   const bool row_ok = lr < c.rows;
   const bool works = kRep ? wg == 0 : quad * 32 < c.rows;   // warp-uniform: false = keep the barrier protocol only
-  const bool pair = !kRep && WG == 2 && works;              // exchanges with the partner warp of its quadrant
+  const bool pair = !kRep && WG > 1 && works;               // exchanges with the other warps of its quadrant
   const int group = p.group;
   const int token = lr / group, head = item.kv_head * group + lr % group;
   const int qpos = item.pos0 + token;
@@ -437,8 +439,8 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     const int lim = row_ok ? min(min(c.kv_end, qpos + 1) - key0, NC) : 0;
     if (!ok) {   // after a wait gave up: only what the partner warp may still be waiting for
       if (pair) {
-        named_barrier_64(2 + quad);
-        named_barrier_64(2 + quad);
+        named_barrier_n(2 + quad, 32 * WG);
+        named_barrier_n(2 + quad, 32 * WG);
       }
       continue;
     }
@@ -458,11 +460,12 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
         if (i < lim) mx = fmaxf(mx, __uint_as_float(v[i]));
     }
     mx = mx > -1e30f ? mx * p.scale_log2 : -1e30f;
-    if (pair) {   // the row maximum over both halves of the tile
+    if (pair) {   // the row maximum over all parts of the tile
       c.xbuf[wg * 128 + r] = mx;
-      named_barrier_64(2 + quad);
-      mx = fmaxf(mx, c.xbuf[(wg ^ 1) * 128 + r]);
-      named_barrier_64(2 + quad);
+      named_barrier_n(2 + quad, 32 * WG);
+#pragma unroll
+      for (int g = 0; g < WG; ++g) mx = fmaxf(mx, c.xbuf[g * 128 + r]);
+      named_barrier_n(2 + quad, 32 * WG);
     }
     mx = fmaxf(mx, m);
     lap(1);
@@ -559,11 +562,13 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   }
   const bool split = item.ws_row0 >= 0;
   if (!kRep) {
-    if (pair) {   // the row sum over both halves, added in the order (group 0) + (group 1)
+    if (pair) {   // the row sum over all parts, added in group order
       c.xbuf[wg * 128 + r] = l;
-      named_barrier_64(2 + quad);
-      const float other = c.xbuf[(wg ^ 1) * 128 + r];
-      l = wg == 0 ? l + other : other + l;
+      named_barrier_n(2 + quad, 32 * WG);
+      l = 0.f;
+#pragma unroll
+      for (int g = 0; g < WG; ++g) l += c.xbuf[g * 128 + r];
+      if (kChain) named_barrier_n(2 + quad, 32 * WG);   // the next item's first exchange reuses the slots
     }
     // The TMEM loads are warp-wide (.sync.aligned): they sit in code every lane of the warp
     // runs, apart from anything that depends on the lane's row, and a warp barrier separates
