@@ -15,9 +15,10 @@ from monoserve_b200.fabric import Fabric as _Fabric
 from monoserve_b200.fabric import args as _args
 
 DEVIATIONS = {
-    "tile kinds 45 / 46": "the reference's K-split weight-stationary tile and its reduce tile are not in this "
-                          "library's tile ABI; form 0 maps to 256-row blocks and the staged form (kind 49). A "
-                          "program that contains them is reported through the mirror's error word as a bad tile.",
+    "tile kinds 45 / 46": "taken, with one difference in how they run: a K-split tile of kind 45 is executed as one "
+                          "symmetric K-range record per block of bm rows, so the weight slice is read once per row "
+                          "block, not once per tile (from L2 when it is in HBM); results are the same sums. This "
+                          "library's own builders use 256-row blocks and the staged form (kind 49) instead.",
     "attention tiles": "kinds 33 / 34 take this library's work items (monoserve_b200.attention.fabric_tiles), not "
                        "AttnArgs blocks; attn_args() still packs the reference's struct for callers that only "
                        "inspect it.",

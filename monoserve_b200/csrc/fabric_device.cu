@@ -57,6 +57,7 @@ struct WorkSlot {
   AttnWork attn;          // filled by the scheduler for attention work items
   const ProgramDesc* prog;
   uint32_t stage, tile_lane, link, index, cmd, worker_lane, is_gemm, is_attn;
+  uint32_t counts, pad;   // counts: this record completes its tile (0 for all but the last row block of a kind-45 tile)
 };
 
 // A GEMM tile (kind 32) in the reference's operand convention
@@ -67,7 +68,14 @@ struct WorkSlot {
 // 128-byte slots (monofab_fabric_tensor_map): [0] the caller's box, [1] box
 // (64, 16, 1), [2] box (64, 128, 1), [3] flags: word 0 = 1 when a w13 tensor is
 // stored in the packed SwiGLU row order (monofab_pack_w13).
-__device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
+// A tile of kind 45 (csrc/fabric/model_types.h:47-49: one K range of the slice against all i2 rows of its
+// expert) runs as one record per block of bm rows, `block` naming the record's block: the same symmetric tile
+// with the K range a[3], rows [i1 + block * bm, ...).  Its epilogue adds (kEpiAtomicF32 / kEpiWeightedAdd), so
+// the blocks and K ranges may complete in any order.  With up_offset set and kEpiAtomicF32 the slice is the
+// 64 gate rows at i0 and the 64 up rows at up_offset + i0, and a partial sum goes to column = weight row (the
+// layout the reduce tile, kind 46, reads).  The weights of the slice are re-read per row block (from L2 when
+// they are in HBM); the staged form is this library's own answer to reading a host-resident expert once.
+__device__ bool make_gemm_work(const TileDesc& t, GemmWork& w, uint32_t block = 0) {
   GemmArgs A;
   const uint4* src = reinterpret_cast<const uint4*>(t.a[0]);
   uint4* dst = reinterpret_cast<uint4*>(&A);
@@ -77,8 +85,9 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   const CUtensorMap* wrec = reinterpret_cast<const CUtensorMap*>(t.a[1]);
   const CUtensorMap* xrec = reinterpret_cast<const CUtensorMap*>(t.a[2]);
   const bool silu = A.epi == kEpiSiluMul;
+  const bool atomic_slabs = A.epi == kEpiAtomicF32 && A.up_offset != 0;
   const bool packed = silu && __ldcg(reinterpret_cast<const unsigned int*>(wrec + 3)) != 0;
-  w.a_map = (silu && !packed) ? wrec + 1 : wrec + 2;
+  w.a_map = ((silu && !packed) || atomic_slabs) ? wrec + 1 : wrec + 2;
   w.b_map = xrec;
   w.out = reinterpret_cast<void*>(A.out);
   w.scale = reinterpret_cast<const float*>(t.a[4]);
@@ -89,8 +98,10 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   w.a_row_lo = t.i0;
   w.a_row_hi = A.up_offset + t.i0;
   w.a_z = t.i3;
-  w.b_row0 = t.i1;
-  w.rows = t.i2 < A.bm ? t.i2 : A.bm;
+  const uint32_t row_off = block * A.bm;
+  if (row_off >= t.i2 && t.i2 != 0) return false;
+  w.b_row0 = t.i1 + row_off;
+  w.rows = t.i2 - row_off < A.bm ? t.i2 - row_off : A.bm;
   w.n = A.bm;
   const uint32_t k0 = static_cast<uint32_t>(t.a[3] & 0xffff), kn = static_cast<uint32_t>((t.a[3] >> 16) & 0xffff);
   w.k0 = kn ? k0 : 0;
@@ -100,7 +111,7 @@ __device__ bool make_gemm_work(const TileDesc& t, GemmWork& w) {
   w.ld_res = A.ld_res;
   w.n_limit = A.n_limit;
   w.valid = 1;
-  w.a_packed = packed;
+  w.a_packed = (packed ? 1 : 0) | (atomic_slabs ? 4 : 0);
   w.block = -1;
   w.w_fp8 = A.w_fp8 != 0;   // e4m3 weights: the exec warps expand every stage to bf16 before its MMAs
   w.fetch = 0;
@@ -176,6 +187,7 @@ __device__ void tile_norm(const TileDesc& t, int tid, bool add);
 __device__ void tile_router_logits(const TileDesc& t, int tid);
 __device__ void tile_permute(const TileDesc& t, int tid);
 __device__ void tile_combine(const TileDesc& t, int tid);
+__device__ void tile_asym_reduce(const TileDesc& t, int tid);
 __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid);
 
 // tid: index among the exec threads.
@@ -239,6 +251,9 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
     case kTileCombine:
       tile_combine(t, tid);
       return true;
+    case kTileAsymReduce:
+      tile_asym_reduce(t, tid);
+      return true;
     case kTileExpand:
       tile_expand(t, w.prog, S, tid);
       return true;
@@ -271,6 +286,26 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
 // ----------------------------------------------------------- row-wise model tiles
 // Row-wise tiles name rows [i0, i0 + i1); a[0] is the operand block.  One warp per
 // row, the four exec warps striding over the rows.
+
+// Reduce tile of the K-split w13 (kind 46, csrc/fabric/model_types.h:196-204, ReduceArgs) for rows
+// [i0, i0 + i1): h[r][f] = bf16(silu(gate) * up) from the fp32 partial sums ws[r][f] and ws[r][I + f],
+// whose row is then zeroed for the next layer.  One warp per row.
+__device__ void tile_asym_reduce(const TileDesc& t, int tid) {
+  ReduceArgs A;
+  load_block(A, t.a[0]);
+  const int warp = tid >> 5, lane = tid & 31;
+  const uint32_t I = A.I;
+  for (uint32_t r = t.i0 + warp; r < t.i0 + t.i1; r += kExecThreads / 32) {
+    float* ws = reinterpret_cast<float*>(A.ws) + static_cast<size_t>(r) * A.ld_ws;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(A.out) + static_cast<size_t>(r) * A.ld_out;
+    for (uint32_t f = lane; f < I; f += 32) {
+      const float g = __ldcg(ws + f), u = __ldcg(ws + I + f);
+      out[f] = __float2bfloat16(silu_mul(g, u));
+      ws[f] = 0.f;
+      ws[I + f] = 0.f;
+    }
+  }
+}
 
 // Router tile (kind 38, csrc/fabric/tiles/aux.cuh:326-417, RouterArgs): scores,
 // top-K, renormalisation, per-expert counts; the logits row is zeroed once read.
@@ -923,6 +958,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
     sh.ws.lane = kNoLane;
     sh.ws.n_lanes = 0;
     sh.ws.left = 0;
+    sh.ws.row_block = 0;
     fence_barrier_init();
   }
   if (warp == 6) {
@@ -983,6 +1019,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
       __syncwarp();
       if (lane == 0) {
         w.cmd = cmd;
+        w.counts = 1;
         if (cmd == kCmdRun) {
           w.prog = ws.prog;
           w.stage = ws.stage;
@@ -1007,9 +1044,25 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
               raise_error(S, kFabErrBadTile);
               w.tile.kind = kTileNop;   // completes without running, so the program still ends
             }
+          } else if (w.tile.kind == kTileGemmAsym) {
+            // one record per row block; the tile is done with its last block's record
+            if (make_gemm_work(w.tile, w.gemm, ws.row_block)) {
+              w.is_gemm = 1;
+              const uint32_t blocks = (w.tile.i2 + w.gemm.n - 1) / static_cast<uint32_t>(w.gemm.n);
+              if (ws.row_block + 1 < blocks) {
+                ++ws.row_block;
+                w.counts = 0;
+              }
+            } else {
+              raise_error(S, kFabErrBadTile);
+              w.tile.kind = kTileNop;
+            }
           }
-          ++ws.next_index;
-          --ws.left;
+          if (w.counts) {
+            ws.row_block = 0;
+            ++ws.next_index;
+            --ws.left;
+          }
         }
         mbar_arrive(&sh.slot_full[s]);
       }
@@ -1134,7 +1187,7 @@ __global__ void __launch_bounds__(kWorkerThreads, 1) fabric_kernel(DeviceState* 
           note_tile(S, worker, w, 1ull << 62);
         }
         __syncwarp();
-        tiles_completed(S, w.tile_lane, w.prog, w.stage, 1, sh.wl);
+        if (w.counts) tiles_completed(S, w.tile_lane, w.prog, w.stage, 1, sh.wl);
         if (tid == 0) {
           note_tile(S, worker, w, 0);
           *reinterpret_cast<volatile unsigned int*>(&sh.tiles_done) = n + 1;

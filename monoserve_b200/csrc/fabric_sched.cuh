@@ -370,6 +370,7 @@ struct WorkerState {
   // the current claim
   const ProgramDesc* prog;
   uint32_t stage, tile_lane, link, next_index, left;
+  uint32_t row_block;   // a kind-45 tile runs as one record per row block: the block of its next record
   // The link slot this worker holds (kNoLane = none).  The worker runs its records through a pipeline
   // behind the scheduler, so the slot goes back only when the exec warps have finished the last link
   // record issued under it.

@@ -37,6 +37,8 @@ enum TileKind : uint16_t {
   kTileEmbed = 42,
   kTileSample = 43,
   kTileAttnPlan = 44,
+  kTileGemmAsym = 45,       // a K range of a 128-row weight slice against ALL i2 rows of its expert, in blocks of bm rows
+  kTileAsymReduce = 46,     // rows [i0, i0 + i1): h = silu(gate) * up from fp32 partial sums, which are zeroed
   kTileCombine = 47,        // not in the reference: un-permute + weighted combine in pick order (+ RMSNorm)
   kTileRouterLogits = 48,   // not in the reference: router projection with a defined summation order
   kTileFetch = 49,          // not in the reference: a[0] source, a[1] destination, i0 bytes; host memory -> HBM staging

@@ -67,7 +67,9 @@ struct GemmWork {
   int32_t ld_out, ld_res;
   int32_t n_limit;            // valid output features
   int32_t valid;              // 0: no tile (the consumer roles stop or skip)
-  int32_t a_packed;           // kEpiSiluMul: the weight rows are already interleaved in memory (one 128-row box)
+  int32_t a_packed;           // bit 0 (two slabs): the weight rows are already interleaved in memory (one 128-row box);
+                              // bit 2: two slabs (64 rows at a_row_lo, 64 at a_row_hi) under kEpiAtomicF32, whose
+                              // partial sums go to column = weight row (kEpiSiluMul always reads two slabs)
   int32_t block;              // row block whose counter the epilogue bumps, or -1
   int32_t w_fp8;              // the weight tensor holds e4m3 bytes: W8A16 (exact e4m3 -> bf16 in shared memory)
   // A fetch record moves fetch_bytes from fetch_src (host-resident weights) to `out` (an HBM staging
@@ -182,9 +184,10 @@ __device__ __forceinline__ bool gemm_produce(const GemmWork& w, uint8_t* ring, G
   // SwiGLU tiles of a tensor in the reference row order gather eight 16-row boxes;
   // every other tile is one 128-row box (a packed SwiGLU tensor stores gate/up
   // groups of 16 rows alternately, so its tile starts at row 2 * a_row_lo).
-  const bool gather = w.epi == kEpiSiluMul && !w.a_packed;
+  const bool slab2 = w.epi == kEpiSiluMul || (w.a_packed & 4);
+  const bool gather = slab2 && !(w.a_packed & 1);
   const int a_row = gather ? ((lane & 1) ? w.a_row_hi : w.a_row_lo) + 16 * ((lane & 7) >> 1)
-                           : (w.epi == kEpiSiluMul ? 2 * w.a_row_lo : w.a_row_lo);
+                           : (slab2 ? 2 * w.a_row_lo : w.a_row_lo);
   const int n_a = gather ? 8 : 1;
   // read once: the record lives in shared memory and every copy below is a memory barrier to the compiler
   const bool fetch = kFetch && w.fetch != 0;
@@ -397,7 +400,7 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
   const bool silu = w.epi == kEpiSiluMul;
   // output feature of this lane, and the weight row its accumulator row came from
   int f, wrow;
-  if (silu) {
+  if (silu || (w.a_packed & 4)) {
     f = w.a_row_lo + 16 * quad + (lane & 15);
     wrow = (lane < 16 ? w.a_row_lo : w.a_row_hi) + 16 * quad + (lane & 15);
   } else {
@@ -470,7 +473,8 @@ __device__ __forceinline__ bool gemm_epilogue_body(const GemmWork& w, GemmBarrie
         }
       }
     } else if (w.epi == kEpiAtomicF32) {
-      float* out = reinterpret_cast<float*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + f;
+      // a two-slab tile (partial sums of a SwiGLU pair) adds into the column of its weight row
+      float* out = reinterpret_cast<float*>(w.out) + static_cast<size_t>(w.b_row0 + c0) * w.ld_out + ((w.a_packed & 4) ? wrow : f);
       if (f_ok) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)

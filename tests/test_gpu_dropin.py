@@ -3,10 +3,9 @@
 tests/dropin/prepare.py lays a copy of the reference's pure-Python package and of its test files
 out under baseline/_ref/ (git-ignored) and puts monoserve_b200.compat._C where the reference keeps
 its compiled extension.  Here each copied test file runs in a process of its own with that folder
-first on the path; every test must pass except the ones listed below, which exercise the
-reference's K-split weight-stationary tiles (kinds 45 / 46): this library replaces that form by
-256-row blocks and the staged form and does not take those tile kinds (a documented deviation of
-the tile ABI).  Skipped when the layout is absent (a checkout of the reference is needed to make it).
+first on the path; every test must pass, the ones that drive the reference's K-split tiles (kinds 45 / 46)
+included: this library runs such a tile as one symmetric K-range record per row block.
+Skipped when the layout is absent (a checkout of the reference is needed to make it).
 """
 import os
 import re
@@ -18,11 +17,6 @@ import pytest
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
-
-# tests of the reference that drive tile kinds 45 / 46
-ASYM = {"test_asymmetric_expert_ffn[16-hbm]", "test_asymmetric_expert_ffn[16-cpu]", "test_asymmetric_expert_ffn[64-hbm]",
-        "test_asymmetric_expert_ffn[64-cpu]", "test_expert_ffn_fp8[hbm-asym]", "test_expert_ffn_fp8[cpu-asym]"}
-
 
 def run_reference_tests(name, select=None):
     path = os.path.join(REF, "tests", name)
@@ -51,11 +45,11 @@ def test_reference_mechanism_tests_pass_unchanged():
 
 def test_reference_gemm_tests_pass_unchanged():
     """tests/test_fabric_gemm.py of the reference: every case that uses the symmetric GEMM tile
-    (bf16 and e4m3, HBM and pinned host operands, all epilogues, K ranges) passes unchanged;
-    the cases built on the K-split weight-stationary tiles are the documented deviation."""
+    (bf16 and e4m3, HBM and pinned host operands, all epilogues, K ranges) and every case built on the
+    K-split tiles of kinds 45 / 46 and their reduce passes unchanged."""
     outcome, log = run_reference_tests("test_fabric_gemm.py")
     assert len(outcome) >= 28
-    wrong = {k: v for k, v in outcome.items() if (v != "PASSED") != (k in ASYM)}
+    wrong = {k: v for k, v in outcome.items() if v != "PASSED"}
     assert not wrong, (wrong, log[-3000:])
 
 

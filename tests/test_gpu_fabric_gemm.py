@@ -14,6 +14,7 @@ from monoserve_b200.fabric import Fabric, Program, Tile
 pytestmark = pytest.mark.gpu
 
 KIND_GEMM = 32
+KIND_GEMM_ASYM, KIND_ASYM_REDUCE = 45, 46
 EPI_STORE, EPI_SILU_MUL, EPI_WADD, EPI_F32, EPI_ATOMIC = 0, 1, 2, 3, 4
 
 
@@ -141,6 +142,72 @@ def test_expert_ffn(fab, where):
             ref[t] += float(tw[t, k]) * (hh @ w2[e].float().t())
     err = (out32 - ref).abs().max().item()
     assert err < 0.03 * ref.abs().max().item(), err
+    assert float((out32 - ref).norm() / ref.norm()) < 1e-2
+    del k1, k2
+
+
+@pytest.mark.parametrize("where", ["hbm", "cpu"])
+@pytest.mark.parametrize("bm", [16, 64])
+def test_k_split_expert_ffn(fab, where, bm):
+    """The reference's K-split form (tests/test_fabric_gemm.py:177-250): w13 tiles of kind 45 add fp32 partial
+    sums of gate and up rows over K ranges, for ALL rows of their expert; the reduce tiles (kind 46) turn them
+    into h = silu(gate) * up and zero them; w2 tiles of kind 45 add routing-weighted outputs over K ranges."""
+    from monoserve_b200.fabric.args import pack
+    torch.manual_seed(2)
+    E, H, I, T, TOPK = 4, 1024, 640, 48, 2   # experts get about 24 rows each: two row blocks at bm = 16
+    w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, device="cuda") * 0.03).to(torch.bfloat16)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    topk = torch.stack([torch.randperm(E, device="cuda")[:TOPK] for _ in range(T)])
+    tw = torch.rand(T, TOPK, device="cuda")
+    pairs = sorted((int(topk[t, k]), t, float(tw[t, k])) for t in range(T) for k in range(TOPK))
+    xp = torch.zeros(len(pairs) + 64, H, device="cuda", dtype=torch.bfloat16)
+    xp[:len(pairs)] = torch.stack([x[t] for _, t, _ in pairs])
+    ptok = torch.tensor([t for _, t, _ in pairs], dtype=torch.int32, device="cuda")
+    pw = torch.tensor([wt for _, _, wt in pairs], dtype=torch.float32, device="cuda")
+    starts = {}
+    for i, (e, _, _) in enumerate(pairs):
+        starts.setdefault(e, [i, 0])[1] += 1
+    ws = torch.zeros(len(pairs), 2 * I, device="cuda", dtype=torch.float32)
+    hbuf = torch.zeros(len(pairs) + 64, I, device="cuda", dtype=torch.bfloat16)
+    out32 = torch.zeros(T, H, device="cuda", dtype=torch.float32)
+    if where == "cpu":
+        k1, b13 = pinned_alias(w13)
+        k2, b2 = pinned_alias(w2)
+    else:
+        k1 = k2 = None
+        b13, b2 = w13.data_ptr(), w2.data_ptr()
+    a13 = args_tensor(out=ws.data_ptr(), ld_out=2 * I, k_tiles=H // 64, epi=EPI_ATOMIC, bm=bm, n_limit=I, up_offset=I)
+    a2 = args_tensor(out=out32.data_ptr(), ld_out=H, k_tiles=I // 64, epi=EPI_WADD, bm=bm, n_limit=H,
+                     pair_token=ptok.data_ptr(), pair_weight=pw.data_ptr())
+    red = torch.frombuffer(bytearray(pack("ReduceArgs", ws=ws, out=hbuf, I=I, ld_ws=2 * I, ld_out=I)), dtype=torch.uint8).cuda()
+    m13, m2 = weight_map(fab, b13, w13.shape), weight_map(fab, b2, w2.shape)
+    mx, mh = act_map(fab, xp, bm), act_map(fab, hbuf, bm)
+
+    def splits(kt, most=8):   # K ranges of at most `most` K tiles
+        return [(k0, min(most, kt - k0)) for k0 in range(0, kt, most)]
+    t13, tr, t2 = [], [], []
+    for e, (s0, cnt) in starts.items():
+        t13 += [Tile(KIND_GEMM_ASYM, i=(f0, s0, cnt, e), a=(a13.data_ptr(), m13, mx, k0 | (kt << 16)))
+                for f0 in range(0, I, 64) for k0, kt in splits(H // 64)]
+        tr += [Tile(KIND_ASYM_REDUCE, i=(r0, min(64, s0 + cnt - r0)), a=(red.data_ptr(),)) for r0 in range(s0, s0 + cnt, 64)]
+        t2 += [Tile(KIND_GEMM_ASYM, i=(n0, s0, cnt, e), a=(a2.data_ptr(), m2, mh, k0 | (kt << 16)))
+               for n0 in range(0, H, 128) for k0, kt in splits(I // 64)]
+    p = Program()
+    s13, sr, s2 = p.stage(t13, link=(where == "cpu")), p.stage(tr), p.stage(t2, link=(where == "cpu"))
+    p.after(s13, sr)
+    p.after(sr, s2)
+    run_program(fab, p, s13, caps=(8,))
+    e_of = torch.tensor([e for e, _, _ in pairs], device="cuda")
+    xr = xp[:len(pairs)].float()
+    g = torch.einsum("mh,mih->mi", xr, w13[e_of, :I].float())
+    u = torch.einsum("mh,mih->mi", xr, w13[e_of, I:].float())
+    h_ref = torch.nn.functional.silu(g) * u
+    assert (hbuf[:len(pairs)].float() - h_ref).abs().max().item() < 0.02 * h_ref.abs().max().item()
+    assert ws.abs().max().item() == 0.0   # the reduce zeroed the partial sums
+    y = torch.einsum("mi,mhi->mh", h_ref.to(torch.bfloat16).float(), w2[e_of].float()) * pw[:, None]
+    ref = torch.zeros(T, H, device="cuda").index_add_(0, ptok.long(), y)
+    assert (out32 - ref).abs().max().item() < 0.03 * ref.abs().max().item()
     assert float((out32 - ref).norm() / ref.norm()) < 1e-2
     del k1, k2
 
