@@ -125,10 +125,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
     tmem_alloc(&sh.tmem_base, kAttnTmemCols);
     tmem_relinquish();
   }
+  chain_release();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   c.tmem_base = sh.tmem_base;
+  chain_wait();   // q and the caches may come from the kernel before this one
 
   const int n_items = p.n_items;
   if (warp == 0) {
@@ -200,6 +202,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
 __global__ void attention_combine_kernel(const int32_t* __restrict__ items, int n_items, const float* __restrict__ ws_o,
                                          const float2* __restrict__ ws_ml, __nv_bfloat16* __restrict__ out, int hq,
                                          int group) {
+  chain_release();
+  chain_wait();   // the parts come from the attention kernel launched just before
   const int32_t* it = items + static_cast<size_t>(blockIdx.x) * 8;
   attn_merge_rows(it[0], it[1], it[2], it[3], it[4], it[5], ws_o, ws_ml, out, hq, group, threadIdx.x >> 5, blockDim.x >> 5);
 }
@@ -207,8 +211,7 @@ __global__ void attention_combine_kernel(const int32_t* __restrict__ items, int 
 cudaError_t launch_attention_combine(const int32_t* items, int n_items, const float* ws_o, const float2* ws_ml,
                                      __nv_bfloat16* out, int hq, int group, cudaStream_t stream) {
   if (n_items == 0) return cudaSuccess;
-  attention_combine_kernel<<<n_items, 256, 0, stream>>>(items, n_items, ws_o, ws_ml, out, hq, group);
-  return cudaGetLastError();
+  return launch_chained(attention_combine_kernel, n_items, 256, 0, stream, items, n_items, ws_o, ws_ml, out, hq, group);
 }
 
 cudaError_t read_attention_trace(unsigned long long out[8]) {
@@ -228,8 +231,7 @@ cudaError_t launch_attention(const AttnParams& params, cudaStream_t stream) {
   static std::atomic<unsigned int> ticket{0};
   AttnParams p = params;
   p.claim_slot = static_cast<int32_t>(ticket.fetch_add(1) % kClaimSlots);
-  paged_attention_kernel<<<std::min(p.n_items, sms), kAttnThreads, kAttnSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  return launch_chained(paged_attention_kernel, std::min(p.n_items, sms), kAttnThreads, kAttnSmemBytes, stream, p);
 }
 
 }  // namespace mf
