@@ -32,6 +32,7 @@ copied once into the lane's HBM staging stack and computed from there; `--no-sta
 searches; other points are a flag away.
 """
 import argparse
+import sys
 import json
 import time
 import types
@@ -206,6 +207,8 @@ def main():
                          "(monoserve_b200.control) over the B200 calibration, with --tpot / --ttft as the lanes' deadlines")
     ap.add_argument("--tpot", type=float, default=1.0, help="decode deadline for --plan search, seconds per step")
     ap.add_argument("--ttft", type=float, default=3.0, help="prefill deadline for --plan search, seconds per pass")
+    ap.add_argument("--trace", action="store_true",
+                    help="also print the decode lane's stage timeline summary (per stage name: count, mean / p50 / max span) on stderr")
     ap.add_argument("--quick", action="store_true", help="2 layers, 16 sequences, 1 prompt of 256: a smoke run")
     args = ap.parse_args()
     glm = args.model == "glm"
@@ -281,6 +284,11 @@ def main():
         loop.add_prefill_lane(pre, 0)
     torch.cuda.synchronize()
     t_setup = time.time() - t_setup
+    tr = None
+    if args.trace:
+        from monoserve_b200.fabric.trace import StageTrace
+        tr = StageTrace(capacity=1 << 21)
+        tr.start(fab)
     fab.start()
     if loop is not None:
         loop.start(poll_us=5)
@@ -298,6 +306,9 @@ def main():
         loop_stats = loop.stats()
     fab.stop()
     torch.cuda.synchronize()
+    if tr is not None:
+        from monoserve_b200.fabric.trace import summary
+        print(summary(tr.stop(fab), dec.labels, lane=0), file=sys.stderr)
     deltas = np.diff(np.array(ends[warm - 1:], dtype=np.float64)) * 1e-6    # ms per decode step
     hist = dec.hist.cpu().numpy()
     iters = warm + args.steps

@@ -159,13 +159,12 @@ __device__ __forceinline__ bool claim_tiles(const ProgramDesc* P, uint32_t word,
 // head is dropped with one compare-and-swap; the first entry that still has tiles is claimed.
 __device__ __forceinline__ bool ring_take(Ring& R, const ProgramDesc* P, Claim& c) {
   const int lane = threadIdx.x & 31;
-  unsigned long long head = 0, tail = 0;
-  if (lane == 0) {
-    head = ld_acq(&R.head);
-    tail = ld_acq(&R.tail);
-  }
-  head = __shfl_sync(kWarp, head, 0);
-  tail = __shfl_sync(kWarp, tail, 0);
+  // head and tail by two lanes at once (one round trip): a pair read out of step only looks empty, or
+  // begins at entries that are exhausted and fail the compare-and-swap below
+  unsigned long long word01 = 0;
+  if (lane == 0) word01 = ld_acq(&R.head);
+  else if (lane == 1) word01 = ld_acq(&R.tail);
+  const unsigned long long head = __shfl_sync(kWarp, word01, 0), tail = __shfl_sync(kWarp, word01, 1);
   if (tail <= head) return false;
   const int n = static_cast<int>(min(tail - head, 32ull));
   uint32_t word = 0, left = 0;
@@ -466,16 +465,21 @@ __device__ __forceinline__ void start_waiting_lanes(DeviceState& S, WorkerState&
 __device__ __forceinline__ bool look_in_lane(DeviceState& S, WorkerState& ws, uint32_t l) {
   const int lane = threadIdx.x & 31;
   LaneState& L = S.lane[l];
+  // `running` and the link ring's ends by three lanes at once, then the program (which is read after
+  // `running`, as before): two round trips instead of four
+  unsigned long long v = 0;
+  if (lane == 0) v = ld_acq(&L.running);
+  else if (lane == 1) v = ld_acq(&L.ring[1].tail);
+  else if (lane == 2) v = ld_volatile(&L.ring[1].head);
+  const bool running = __shfl_sync(kWarp, v, 0) != 0;
+  if (!running) return false;
+  const bool link_waiting = __shfl_sync(kWarp, v, 1) > __shfl_sync(kWarp, v, 2);
   unsigned long long prog = 0;
-  int link_waiting = 0;
-  if (lane == 0 && ld_acq(&L.running) != 0) {
-    prog = ld_acq(&L.prog);
-    link_waiting = ld_acq(&L.ring[1].tail) > ld_volatile(&L.ring[1].head);
-  }
+  if (lane == 0) prog = ld_acq(&L.prog);
   const ProgramDesc* P = reinterpret_cast<const ProgramDesc*>(__shfl_sync(kWarp, prog, 0));
   if (P == nullptr) return false;
   Claim c;
-  if (__shfl_sync(kWarp, link_waiting, 0)) {
+  if (link_waiting) {
     int held = 0;
     if (lane == 0) {
       held = ws.slot_lane == l;

@@ -350,8 +350,7 @@ __device__ void tile_sample(const TileDesc& t, int tid) {
   const int step = steps ? steps[slot] : 0;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < V; i += kExecThreads) {
-    float v = __ldcs(lg + i);
+  auto consider = [&](float v, int i) {
     if (temp > 0.f) {
       const unsigned long long h = splitmix64(A.seed ^ (static_cast<unsigned long long>(slot) << 40) ^
                                               (static_cast<unsigned long long>(step) << 20) ^ static_cast<unsigned long long>(i));
@@ -362,6 +361,31 @@ __device__ void tile_sample(const TileDesc& t, int tid) {
       bv = v;
       bi = i;
     }
+  };
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+    // four 16-byte loads in flight per thread: a row of 150 k logits is otherwise a chain of 1200 exposed loads
+    const float4* lg4 = reinterpret_cast<const float4*>(lg);
+    const int n4 = V >> 2;
+    for (int i0 = tid; i0 < n4; i0 += 4 * kExecThreads) {
+      float4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kExecThreads;
+        q[u] = i < n4 ? __ldcs(lg4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kExecThreads;
+        if (i < n4) {
+          consider(q[u].x, 4 * i);
+          consider(q[u].y, 4 * i + 1);
+          consider(q[u].z, 4 * i + 2);
+          consider(q[u].w, 4 * i + 3);
+        }
+      }
+    }
+  } else {
+    for (int i = tid; i < V; i += kExecThreads) consider(__ldcs(lg + i), i);
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) {

@@ -603,6 +603,7 @@ class ModelLane:
         last, expands = self._layers(p, T, s_embed, attention, sample_rows, n_rows)
         self._finish_dynamic(p, expands, [])
         self.rows_out = n_rows
+        self.labels = p.labels()   # stage names, for monoserve_b200.fabric.trace.summary
         return p.upload(self.fab, first=s_embed, iterations=iterations)
 
     def build_decode(self, slots, iterations=1, chunk_keys=0):
@@ -627,8 +628,12 @@ class ModelLane:
             s_plan = p.stage(tile_array(K_ATTN_PLAN, a0=blob.data_ptr()), label=("attn_plan", l))
             s_a = p.stage(label=("attn", l))
             s_m = p.stage(label=("attn_merge", l))
-            p.after(prev, s_plan)
+            # The plan needs the step's sequence lengths only (the embed tiles' bookkeeping), so every layer's
+            # plan tile runs right after the embed stage, beside the layers before it, instead of between the
+            # layer's rope and attention stages.
+            p.after(s_embed, s_plan)
             p.after(s_plan, s_a)
+            p.after(prev, s_a)
             p.after(s_a, s_m)
             fields = dict(attn=self.attn_args[l].data_ptr(), req_info=self.req_info.data_ptr(), rows=R, hkv=hkv,
                           chunk_keys=chunk_keys, stage_attn=s_a, stage_comb=s_m, workers=self.fab.num_workers,
@@ -639,6 +644,7 @@ class ModelLane:
         last, expands = self._layers(p, R, s_embed, attention, [(r, s) for r, s in enumerate(slots)], R)
         self._finish_dynamic(p, expands, plans)
         self.rows_out = R
+        self.labels = p.labels()
         return p.upload(self.fab, first=s_embed, iterations=iterations)
 
     # ------------------------------------------------------------------ request state
