@@ -827,18 +827,29 @@ __device__ void tile_norm(const TileDesc& t, int tid, bool add) {
       const uint4* x2 = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(A.x2) + o);
       float4* acc = reinterpret_cast<float4*>(reinterpret_cast<float*>(A.acc) + static_cast<size_t>(r) * H);
       const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int parts = static_cast<int>(A.acc_parts);
+      const size_t slab = static_cast<size_t>(A.acc_rows) * H / 4;   // float4 per slab
       for (int c = lane; c < n16; c += 32) {
         float f[8];
         unpack8(x2[c], f);
-        const float4 a0 = acc[2 * c], a1 = acc[2 * c + 1];
+        float4 a0 = acc[2 * c], a1 = acc[2 * c + 1];
+        if (parts > 1) {
+          // the partial sums of a K-split GEMM, one slab per K range, added in slab order
+          for (int q = 1; q < parts; ++q) {
+            const float4 b0 = acc[q * slab + 2 * c], b1 = acc[q * slab + 2 * c + 1];
+            a0 = make_float4(__fadd_rn(a0.x, b0.x), __fadd_rn(a0.y, b0.y), __fadd_rn(a0.z, b0.z), __fadd_rn(a0.w, b0.w));
+            a1 = make_float4(__fadd_rn(a1.x, b1.x), __fadd_rn(a1.y, b1.y), __fadd_rn(a1.z, b1.z), __fadd_rn(a1.w, b1.w));
+          }
+        } else {
+          acc[2 * c] = zero;
+          acc[2 * c + 1] = zero;
+        }
         const float sv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           f[j] = round_bf16(__fadd_rn(f[j], sv[j]));
           ss = __fmaf_rn(f[j], f[j], ss);
         }
-        acc[2 * c] = zero;
-        acc[2 * c + 1] = zero;
         x[c] = pack8(f);
       }
     } else {

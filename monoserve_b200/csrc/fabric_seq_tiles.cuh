@@ -123,6 +123,17 @@ __device__ void tile_attn_plan(const TileDesc& t, const ProgramDesc* P, DeviceSt
     } else {
       const int workers = A.workers ? static_cast<int>(A.workers) : 148;
       part = max(4, static_cast<int>((total + 2 * workers - 1) / (2 * workers)));
+      // A small step fits one round: the shortest parts (4 .. 16 tiles) that give every worker at most one
+      // item.  An item costs about as much to start as six tiles take, so a second round of short items is
+      // worse than one round of items twice as long.
+      for (int cand = 4; cand <= 16; ++cand) {
+        int items = 0;
+        for (int r = 0; r < R; ++r) items += hkv * (s_tiles[r] >= 8 ? (s_tiles[r] + cand - 1) / cand : 1);
+        if (items <= workers) {
+          part = cand;
+          break;
+        }
+      }
     }
     s_part_tiles = part;
     int items = 0, merges = 0;
@@ -268,7 +279,20 @@ __device__ void tile_qk_rope(const TileDesc& t, int tid) {
   const float* cos_sin = reinterpret_cast<const float*>(A.cos_sin);
   for (uint32_t it = t.i0 + warp; it < t.i0 + t.i1; it += kExecThreads / 32) {
     const int row = static_cast<int>(it / heads), head = static_cast<int>(it % heads);
-    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(row) * A.ld_qkv + head * 128 + 4 * lane);
+    uint2 raw;
+    if (A.qkv_parts > 1) {
+      const float* part = reinterpret_cast<const float*>(A.qkv) + static_cast<size_t>(row) * A.ld_qkv + head * 128 + 4 * lane;
+      const size_t slab = static_cast<size_t>(A.qkv_rows) * A.ld_qkv;
+      float4 a = *reinterpret_cast<const float4*>(part);
+      for (uint32_t q = 1; q < A.qkv_parts; ++q) {
+        const float4 b = *reinterpret_cast<const float4*>(part + q * slab);
+        a = make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+      }
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+      raw = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+      raw = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(row) * A.ld_qkv + head * 128 + 4 * lane);
+    }
     const bool is_q = head < hq, is_k = !is_q && head < hq + hkv;
     __nv_bfloat16* dst;
     if (is_q) {

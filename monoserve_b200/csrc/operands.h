@@ -19,17 +19,24 @@ namespace mf {
   F32(scale_log2) U32(bt_stride) U32(hq) U32(hkv) U32(group) U32(chunk_blocks) U32(max_chunks) \
   U32(page_size) U64(q_map_small)
 
+/* acc_parts / acc_rows are not in the reference: with acc_parts > 1 the add-norm tile's `acc` is that many
+ * fp32 slabs of acc_rows rows (the partial sums of a K-split GEMM, one slab per K range), added in slab order
+ * and left as they are; otherwise it is one accumulator, zeroed once read. */
 #define MF_NORM_ARGS(U64, U32, F32) \
   U64(x) U64(x2) U64(acc) U64(w) U64(out) U64(embed) U64(tokens) U64(gather) U64(out2) U64(step) \
-  U32(H) U32(ld) F32(eps)
+  U32(H) U32(ld) F32(eps) U32(acc_parts) U32(acc_rows)
 
 #define MF_STEP_ARGS(U64, U32, F32) \
   U64(row_req) U64(last_token) U64(seq_len) U64(block_table) U64(tok_pos) U64(tok_slot) U64(req_info) \
   U32(bt_stride) U32(page_size)
 
+/* qkv_parts / qkv_rows are not in the reference: with qkv_parts > 1 `qkv` is that many fp32 slabs of qkv_rows
+ * rows (the partial sums of a K-split projection, one slab per K range, the first with the bias); the tile adds
+ * them in slab order and rounds the sum to bf16, which is the value a one-range projection would have stored. */
 #define MF_QK_ARGS(U64, U32, F32) \
   U64(qkv) U64(q_out) U64(k_cache) U64(v_cache) U64(q_norm) U64(k_norm) U64(tok_pos) U64(tok_slot) \
-  U64(cos_sin) U32(ld_qkv) U32(hq) U32(hkv) U32(rot_dim) F32(theta) F32(eps) U32(max_pos)
+  U64(cos_sin) U32(ld_qkv) U32(hq) U32(hkv) U32(rot_dim) F32(theta) F32(eps) U32(max_pos) U32(qkv_parts) \
+  U32(qkv_rows)
 
 #define MF_ROUTER_ARGS(U64, U32, F32) \
   U64(logits) U64(topk_ids) U64(topk_w) U64(counts) U64(bias) U32(E) U32(K) U32(scoring) U32(renorm) \

@@ -25,6 +25,8 @@ from monoserve_b200.fabric.args import pack
 from monoserve_b200.lane import SUB, logits_tiles
 
 K_GEMM, K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE, K_RMSNORM, K_QKROPE = 32, 33, 34, 35, 36, 37
+K_ADDNORM = 41
+SPLIT_ROWS, SPLIT_PARTS, QKV_PARTS = 64, 8, 2   # a dense GEMM of at most SPLIT_ROWS rows may run as up to SPLIT_PARTS K ranges
 K_ROUTER, K_EXPAND, K_PERMUTE, K_EMBED, K_SAMPLE, K_ATTN_PLAN, K_COMBINE, K_LOGITS = 38, 39, 40, 42, 43, 44, 47, 48
 EPI_STORE, EPI_SILU_MUL, EPI_F32, EPI_ROWS_F32 = 0, 1, 3, 5
 REGION_HOST, REGION_HOT = 0, 1
@@ -259,6 +261,8 @@ class ModelLane:
         self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
         self.xp, self.h = z(P + 256, H, dt=bf), z(P + 256, I, dt=bf)
         self.y = z(P + 256, H, dt=torch.float32)
+        self.o_slabs = z(SPLIT_PARTS * SPLIT_ROWS, H, dt=torch.float32)   # K-split partial sums of the o projection
+        self.qkv_slabs = z(QKV_PARTS * SPLIT_ROWS, self.qkv_dim, dt=torch.float32)   # and of the qkv projection
         # dense FFN of the first layers / shared expert: hidden rows and fp32 output rows
         self.Id, self.Is = getattr(cfg, "dense_intermediate", 0), getattr(cfg, "shared_intermediate", 0)
         wide = max(self.Id, self.Is)
@@ -401,6 +405,27 @@ class ModelLane:
             self.fab.write(tensor.data_ptr(), data.tobytes())
 
     # ------------------------------------------------------------------ stage builders
+    def _gemm_split(self, p, wmap, amaps, rows, n_out, k, slabs, parts, label, mark=None, mat=None, bias=None):
+        """The same product for few rows as `parts` K ranges, every range storing its fp32 partial sums in its own
+        slab of `slabs` ([parts][SPLIT_ROWS][n_out]); the add-norm tile behind it adds the slabs in order.  A 128-row
+        weight slice over all of K is a megabyte that one worker streams alone; the ranges spread it over
+        parts x n_out / 128 workers, and the sum keeps a defined order (no atomics)."""
+        bm = _bm(rows)
+        fp8 = mat is not None and mat.fp8
+        xm = amaps[HEIGHTS.index(bm)]
+        kt = k // 64
+        per = -(-kt // parts)
+        tiles = []
+        for q in range(parts):
+            k0, kn = q * per, min(per, kt - q * per)
+            args = self.arena.put(_C.gemm_args(out=slabs.data_ptr() + 4 * q * SPLIT_ROWS * n_out, ld_out=n_out, k_tiles=kt,
+                                               epi=EPI_F32, bm=bm, n_limit=n_out, w_fp8=int(fp8),
+                                               bias=bias.data_ptr() if bias is not None else 0))   # added by the first range
+            m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
+            tiles.append(tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm,
+                                    a3=k0 | (kn << 16), a4=mat.scale.data_ptr() if fp8 else 0))
+        return p.stage(np.concatenate(tiles), mark=mark, label=label)
+
     def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None,
               mat=None, bias=None, up_offset=0):
         """A dense GEMM stage: out[rows][n_out] = act[rows][k] x weight[n_out (x2 for SiLU-mul)][k]^T.
@@ -502,10 +527,16 @@ class ModelLane:
         prev = first_stage
         expands = []
         for l in range(L):
-            s_qkv = self._gemm(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv, self.qkv_dim, EPI_STORE,
-                               ("qkv", l), mat=w.qkv[l], bias=w.qkv_bias[l])
+            qkv_parts = min(QKV_PARTS, (H // 64) // 8) if T <= SPLIT_ROWS else 1
+            if qkv_parts > 1:
+                s_qkv = self._gemm_split(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv_slabs, qkv_parts,
+                                         ("qkv", l), mat=w.qkv[l], bias=w.qkv_bias[l])
+            else:
+                s_qkv = self._gemm(p, self.m_qkv[l], self.m_xn, T, self.qkv_dim, H, self.qkv, self.qkv_dim, EPI_STORE,
+                                   ("qkv", l), mat=w.qkv[l], bias=w.qkv_bias[l])
             p.after(prev, s_qkv)
-            qk = self._dev("QkArgs", qkv=self.qkv, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
+            qk = self._dev("QkArgs", qkv=self.qkv_slabs if qkv_parts > 1 else self.qkv, qkv_parts=qkv_parts,
+                        qkv_rows=SPLIT_ROWS, q_out=self.q, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
                         q_norm=w.q_norm[l] if w.q_norm[l] is not None else 0,
                         k_norm=w.k_norm[l] if w.k_norm[l] is not None else 0, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
                         cos_sin=self.cos_sin, ld_qkv=self.qkv_dim, hq=hq, hkv=hkv, rot_dim=cfg.rotary_dim,
@@ -513,11 +544,21 @@ class ModelLane:
             s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, ROPE_ITEMS), mark=(l << 8) | 1, label=("rope", l))
             p.after(s_qkv, s_rope)
             s_attn = attention(p, l, s_rope)
-            s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
-                             residual=self.x, ld_res=H, mark=(l << 8) | 2, mat=w.o[l])
+            o_parts = min(SPLIT_PARTS, (hq * 128 // 64) // 8) if T <= SPLIT_ROWS else 1
+            if o_parts > 1:
+                # few rows: K ranges into fp32 slabs, then x2 = bf16(x + sum of the slabs) and its norm in one tile
+                s_o = self._gemm_split(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.o_slabs, o_parts, ("o", l),
+                                       mark=(l << 8) | 2, mat=w.o[l])
+                nrm = self._dev("NormArgs", x=self.x2, x2=self.x, acc=self.o_slabs, w=w.post_norm[l], out=self.xn, H=H, ld=H,
+                                eps=cfg.rms_eps, acc_parts=o_parts, acc_rows=SPLIT_ROWS)
+                norm_kind = K_ADDNORM
+            else:
+                s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
+                                 residual=self.x, ld_res=H, mark=(l << 8) | 2, mat=w.o[l])
+                nrm = self._dev("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
+                norm_kind = K_RMSNORM
             p.after(s_attn, s_o)
-            nrm = self._dev("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
-            s_norm = p.stage(self._rows(K_RMSNORM, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
+            s_norm = p.stage(self._rows(norm_kind, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
                              label=("norm", l))
             p.after(s_o, s_norm)
             next_norm = w.in_norm[l + 1] if l + 1 < L else None

@@ -207,3 +207,36 @@ def test_checkpoint_loader_to_logits(fab, tmp_path):
     run_once(fab, h)
     fab.stop()
     check_logits(lane.logits[:len(tokens)].cpu(), tp.model_logits(w, cfg, tokens))
+
+
+def test_k_split_projections_match_reference(fab):
+    """A model wide enough (hidden 1024, 8 query heads) for the few-row form of the dense projections: qkv and o
+    run as K ranges into fp32 slabs that the rope tile and the add-norm tile add in slab order.  Prefill of 20
+    tokens, then decode steps (whose attention plans run beside the layers): logits against the torch oracle."""
+    from monoserve_b200.model import KVCache, ModelLane, ModelWeights
+    from oracle import torch_path as tp
+    from tests.test_oracle_golden import _load_make_golden
+    cfg = types.SimpleNamespace(hidden=1024, intermediate=128, num_experts=8, top_k=2, num_layers=2, num_heads=8,
+                                num_kv_heads=2, head_dim=128, vocab=512, rope_theta=1e6, rms_eps=1e-6, rotary_dim=128)
+    w = _load_make_golden().make_weights(cfg, 11)
+    weights = ModelWeights(cfg, w)
+    kv = KVCache(cfg, n_pages=16, page_size=16)
+    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8)
+    lane.set_pages(0, [3, 1, 2, 5])
+    tokens = torch.randint(0, cfg.vocab, (26,), generator=torch.Generator().manual_seed(3)).tolist()
+    ref = tp.model_logits(w, cfg, tokens)
+    n0 = 20
+    h = lane.build_prefill([(0, tokens[:n0], 0)], all_logits=True)
+    fab.start()
+    run_once(fab, h)
+    fab.stop()
+    check_logits(lane.logits[:n0].cpu(), ref[:n0])
+    got = []
+    for i in range(n0, len(tokens)):   # teacher-forced decode steps, each its own run
+        lane.set_request(0, seq_len=i, last_token=tokens[i])
+        h = lane.build_decode([0])
+        fab.start()
+        run_once(fab, h)
+        fab.stop()
+        got.append(lane.logits[0].cpu().clone())
+    check_logits(torch.stack(got), ref[n0:])
