@@ -185,11 +185,17 @@ def check(code):
     return code
 
 
+_layouts = None
+
+
 def struct_layouts():
     """{name: (sizeof, {field: (offset, "u64" | "u32" | "f32")})}
-    (csrc/bindings.cpp:66-168)."""
-    raw = json.loads(lib.monofab_struct_layouts_json().decode())
-    return {k: (v[0], {f: (o, t) for f, (o, t) in v[1].items()}) for k, v in raw.items()}
+    (csrc/bindings.cpp:66-168).  The table belongs to the build of the library: parsed once."""
+    global _layouts
+    if _layouts is None:
+        raw = json.loads(lib.monofab_struct_layouts_json().decode())
+        _layouts = {k: (v[0], {f: (o, t) for f, (o, t) in v[1].items()}) for k, v in raw.items()}
+    return _layouts
 
 
 def host_device_pointer(host_addr):

@@ -79,6 +79,10 @@ def main():
             line.update(rate_per_s=rate, prompt_tokens=int(prompts.sum()),
                         decode_programs=eng.stats["decode_programs"] - before["decode_programs"],
                         prefill_passes=eng.stats["prefill_passes"] - before["prefill_passes"])
+            # host time to build one program (numpy tile arrays + writes through the fabric's staging ring)
+            for kind, count in (("prefill", "prefill_passes"), ("decode", "decode_programs")):
+                made = line[count]
+                line[f"{kind}_build_ms"] = 1e3 * (eng.stats[f"{kind}_build_s"] - before[f"{kind}_build_s"]) / made if made else None
             results.append(line)
         err = fab.progress()["error"]
     finally:

@@ -137,7 +137,8 @@ class Engine:
         self.dec_pending = None                                            # (handle, gen, buffer, batch, old handle)
         self.retired = []                                                  # (requests to free once the switch is through)
         self.t0 = time.perf_counter()
-        self.stats = dict(published=0, decode_programs=0, prefill_passes=0, switch_waits=0)
+        self.stats = dict(published=0, decode_programs=0, prefill_passes=0, switch_waits=0, prefill_build_s=0.0,
+                          decode_build_s=0.0)   # *_build_s: host time spent building programs
         torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ requests
@@ -199,7 +200,9 @@ class Engine:
             return
         del self.pre._keep[self.pre.keep_base:]   # the operand blocks of the lane's previous pass: that program has ended
         self.pre_iter0 = self._lane_state(PREFILL)["iterations"]
+        t_build = time.perf_counter()
         self.pre_handle = self.pre.build_prefill([(r.slot, r.prompt, 0) for r in batch], iterations=1)
+        self.stats["prefill_build_s"] += time.perf_counter() - t_build
         self.prefilling = batch
         self.stats["prefill_passes"] += 1
         self._publish()
@@ -228,7 +231,9 @@ class Engine:
         if target:
             lane = self.dec[buf]
             del lane._keep[lane.keep_base:]   # this buffer's previous program was replaced a switch ago
+            t_build = time.perf_counter()
             h = lane.build_decode([r.slot for r in target], iterations=0)
+            self.stats["decode_build_s"] += time.perf_counter() - t_build
             self.stats["decode_programs"] += 1
         else:
             h = self.idle_program.upload(self.fab, first=0, iterations=1)

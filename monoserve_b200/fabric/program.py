@@ -31,21 +31,37 @@ class Tile:
         self.kind, self.i, self.a, self.flags = kind, tuple(i), tuple(a), flags
 
 
+def _column(value, shape):
+    """One operand as a flat uint64 column of prod(shape) entries, or a scalar when it is one."""
+    a = np.asarray(value)
+    if a.ndim == 0:
+        return np.uint64(int(a) & 0xFFFFFFFFFFFFFFFF)
+    return np.broadcast_to(a.astype(np.int64, copy=False), shape).reshape(-1).astype(np.uint64)
+
+
 def tile_array(kind, i0=0, i1=0, i2=0, i3=0, a0=0, a1=0, a2=0, a3=0, a4=0):
     """(n, 8) uint64 tiles from broadcastable operand arrays."""
-    ops = np.broadcast_arrays(*[np.asarray(v, dtype=np.int64) for v in (i0, i1, i2, i3, a0, a1, a2, a3, a4)])
-    cols = [np.ascontiguousarray(o).reshape(-1).astype(np.uint64) for o in ops]
-    out = np.zeros((cols[0].size, 8), dtype=np.uint64)
+    ops = (i0, i1, i2, i3, a0, a1, a2, a3, a4)
+    shape = np.broadcast_shapes(*[np.shape(v) for v in ops])
+    c = [_column(v, shape) for v in ops]
+    out = np.zeros((int(np.prod(shape, dtype=np.int64)), 8), dtype=np.uint64)
     out[:, 0] = np.uint64(kind & 0xFFFF)
-    out[:, 1] = (cols[0] & _LOW32) | ((cols[1] & _LOW32) << np.uint64(32))
-    out[:, 2] = (cols[2] & _LOW32) | ((cols[3] & _LOW32) << np.uint64(32))
-    out[:, 3:8] = np.stack(cols[4:9], axis=1)
+    out[:, 1] = (c[0] & _LOW32) | ((c[1] & _LOW32) << np.uint64(32))
+    out[:, 2] = (c[2] & _LOW32) | ((c[3] & _LOW32) << np.uint64(32))
+    for j in range(5):
+        out[:, 3 + j] = c[4 + j]
     return out
+
+
+_NO_TILES = np.zeros((0, 8), dtype=np.uint64)
+_NO_TILES.setflags(write=False)
 
 
 def _as_tile_rows(tiles):
     if isinstance(tiles, np.ndarray):
         return tiles.astype(np.uint64, copy=False)
+    if len(tiles) == 0:
+        return _NO_TILES
     rows = np.zeros((len(tiles), 8), dtype=np.uint64)
     for n, t in enumerate(tiles):
         i = (list(t.i) + [0] * 4)[:4]
@@ -71,6 +87,34 @@ class Program:
         self._labels.append(label)
         return len(self._tiles) - 1
 
+    def stages(self, n, link=False, label=None):
+        """n empty stages (their tiles are written at run time) with consecutive ids; returns the first id."""
+        first = len(self._tiles)
+        self._tiles.extend([_NO_TILES] * n)
+        self._flags.extend([STAGE_LINK if link else 0] * n)
+        self._marks.extend([0] * n)
+        self._succ.extend([] for _ in range(n))
+        self._preds.extend([0] * n)
+        self._labels.extend([label] * n)
+        return first
+
+    def fan_out(self, pred, first, n):
+        """pred -> each of the stages first .. first + n - 1."""
+        self._succ[pred].extend(range(first, first + n))
+        self._preds[first:first + n] = [d + 1 for d in self._preds[first:first + n]]
+
+    def pairwise(self, first_a, first_b, n):
+        """first_a + i -> first_b + i for i < n."""
+        for i in range(n):
+            self._succ[first_a + i].append(first_b + i)
+        self._preds[first_b:first_b + n] = [d + 1 for d in self._preds[first_b:first_b + n]]
+
+    def fan_in(self, first, n, succ):
+        """each of the stages first .. first + n - 1 -> succ."""
+        for i in range(first, first + n):
+            self._succ[i].append(succ)
+        self._preds[succ] += n
+
     def labels(self):
         return list(self._labels) + [("reset", -1)]
 
@@ -90,37 +134,49 @@ class Program:
     def pack(self, first, iterations=1, reset_tiles=8):
         """(tiles int64 [n, 8], stages int32 [m, 8], succ int32 [k], first, reset, iterations)."""
         n_user = len(self._tiles)
-        for sid in range(n_user):
-            if sid != first and self._preds[sid] == 0:
-                raise ValueError(f"stage {sid} has no predecessor and is not the first stage, "
-                                 f"so it would never become ready")
+        preds_user = np.asarray(self._preds, dtype=np.int64)
+        orphan = np.flatnonzero(preds_user == 0)
+        orphan = orphan[orphan != first]
+        if orphan.size:
+            raise ValueError(f"stage {int(orphan[0])} has no predecessor and is not the first stage, "
+                             f"so it would never become ready")
         reset = n_user
         n_all = n_user + 1
-        sinks = [s for s in range(n_user) if not self._succ[s]]
         per = -(-n_all // max(1, reset_tiles))
         zero = [Tile(KIND["zero_runtime"], i=(b, min(n_all, b + per), reset, 0)) for b in range(0, n_all, per)]
         tiles = self._tiles + [_as_tile_rows(zero)]
         flags = self._flags + [STAGE_RESET]
         marks = self._marks + [0]
-        preds = self._preds + [len(sinks)]
-        succ = [list(s) for s in self._succ] + [[]]
-        for s in sinks:
-            succ[s].append(reset)
-        blocks, rows, flat = [], [], []
-        at = 0
-        for sid, t in enumerate(tiles):
+        # every sink gets the reset stage as its only successor
+        n_succ = np.fromiter((len(x) for x in self._succ), dtype=np.int64, count=n_user)
+        sinks = n_succ == 0
+        flat = []
+        for sid, mine in enumerate(self._succ):
+            if mine:
+                flat.extend(mine)
+            else:
+                flat.append(reset)
+        n_succ = np.concatenate((np.where(sinks, 1, n_succ), [0]))
+        preds = np.concatenate((preds_user, [int(sinks.sum())]))
+        # tile blocks in stage order (the dynamic region before the reset stage's), every tile stamped with its stage
+        counts = np.fromiter((len(t) for t in tiles), dtype=np.int64, count=n_all)
+        firsts = np.concatenate(([0], np.cumsum(counts)[:-1]))
+        firsts[reset] += self.reserved
+        blocks = []
+        for sid in np.flatnonzero(counts).tolist():
             if sid == reset and self.reserved:
                 blocks.append(np.zeros((self.reserved, 8), dtype=np.uint64))   # the dynamic region
-                at += self.reserved
-            t = t.copy()
-            if len(t):
-                t[:, 0] = (t[:, 0] & _LOW32) | (np.uint64(sid) << np.uint64(32))
+            t = tiles[sid].copy()
+            t[:, 0] = (t[:, 0] & _LOW32) | (np.uint64(sid) << np.uint64(32))
             blocks.append(t)
-            rows.append([at, len(t), len(flat), len(succ[sid]), preds[sid], flags[sid], marks[sid], 0])
-            flat.extend(succ[sid])
-            at += len(t)
+        if self.reserved and counts[reset] == 0:
+            blocks.append(np.zeros((self.reserved, 8), dtype=np.uint64))
+        rows = np.zeros((n_all, 8), dtype=np.int64)
+        rows[:, 0], rows[:, 1] = firsts, counts
+        rows[:, 2] = np.concatenate(([0], np.cumsum(n_succ)[:-1]))
+        rows[:, 3], rows[:, 4], rows[:, 5], rows[:, 6] = n_succ, preds, flags, marks
         packed = np.concatenate(blocks) if blocks else np.zeros((0, 8), dtype=np.uint64)
-        return (torch.from_numpy(packed.view(np.int64).copy()), torch.tensor(rows, dtype=torch.int64).to(torch.int32),
+        return (torch.from_numpy(packed.view(np.int64).copy()), torch.from_numpy(rows).to(torch.int32),
                 torch.tensor(flat if flat else [0], dtype=torch.int32), first, reset, iterations)
 
     def upload(self, fabric, first, iterations=1, reset_tiles=8):

@@ -60,19 +60,32 @@ class _Arena:
 
     def __init__(self, fab, nbytes):
         self.fab, self.buf, self.at = fab, torch.zeros(nbytes, dtype=torch.uint8, device="cuda"), 0
+        self.host, self.flushed = bytearray(nbytes), 0   # the blocks of the current build; [flushed, at) not yet written
 
     def reset(self):
-        self.at = 0
+        self.at = self.flushed = 0
 
     def put(self, data):
-        data = bytes(data)
+        """Room for `data` in the arena; the bytes reach the device with the next flush()."""
         size = (len(data) + 255) & ~255
         if self.at + size > self.buf.numel():
             raise RuntimeError("monofab: the lane's operand arena is full")
         blob = _Blob(self.buf.data_ptr() + self.at, len(data))
+        self.host[self.at:self.at + len(data)] = data
         self.at += size
-        self.fab.write(blob.addr, data)
         return blob
+
+    def patch(self, blob, data):
+        """Replace the contents of a block put earlier in this build."""
+        at = blob.addr - self.buf.data_ptr()
+        assert self.flushed <= at and at + len(data) <= self.at, "the block is not of the current build"
+        self.host[at:at + len(data)] = data
+
+    def flush(self):
+        """One write of everything put since the last flush (a build has hundreds of blocks of 64 to 256 bytes)."""
+        if self.at > self.flushed:
+            self.fab.write(self.buf.data_ptr() + self.flushed, bytes(self.host[self.flushed:self.at]))
+            self.flushed = self.at
 
 
 def _bm(rows):
@@ -415,16 +428,19 @@ class ModelLane:
         xm = amaps[HEIGHTS.index(bm)]
         kt = k // 64
         per = -(-kt // parts)
-        tiles = []
+        ptrs, ranges = [], []
         for q in range(parts):
             k0, kn = q * per, min(per, kt - q * per)
             args = self.arena.put(_C.gemm_args(out=slabs.data_ptr() + 4 * q * SPLIT_ROWS * n_out, ld_out=n_out, k_tiles=kt,
                                                epi=EPI_F32, bm=bm, n_limit=n_out, w_fp8=int(fp8),
                                                bias=bias.data_ptr() if bias is not None else 0))   # added by the first range
-            m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
-            tiles.append(tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm,
-                                    a3=k0 | (kn << 16), a4=mat.scale.data_ptr() if fp8 else 0))
-        return p.stage(np.concatenate(tiles), mark=mark, label=label)
+            ptrs.append(args.data_ptr())
+            ranges.append(k0 | (kn << 16))
+        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
+        by_range = lambda v: np.asarray(v, dtype=np.int64)[:, None, None]   # noqa: E731  (range, row block, slice)
+        tiles = tile_array(K_GEMM, i0=n0[None], i1=m0[None], i2=np.minimum(bm, rows - m0)[None], a0=by_range(ptrs), a1=wmap,
+                           a2=xm, a3=by_range(ranges), a4=mat.scale.data_ptr() if fp8 else 0)
+        return p.stage(tiles, mark=mark, label=label)
 
     def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None,
               mat=None, bias=None, up_offset=0):
@@ -467,17 +483,16 @@ class ModelLane:
         p.after(s_lg, s_rt)
         p.after(s_rt, s_ex)
         p.after(s_ex, s_pm)
-        w13 = [p.stage(label=("w13", l)) for _ in range(E)]
-        w2 = [p.stage(label=("w2", l)) for _ in range(E)]
+        w13_0 = p.stages(E, label=("w13", l))
+        w2_0 = p.stages(E, label=("w2", l))
         s_cb = p.stage(self._rows(K_COMBINE, cb, T, per), mark=(l << 8) | 3, label=("combine", l))
-        fetch = [p.stage(label=("fetch", l)) for _ in range(E)] if self.staging[l] is not None else None
-        for e in range(E):
-            p.after(s_pm, w13[e])
-            if fetch:   # the copy into the staging stack starts as soon as the expert's row count is known
-                p.after(s_ex, fetch[e])
-                p.after(fetch[e], w13[e])
-            p.after(w13[e], w2[e])
-            p.after(w2[e], s_cb)
+        fetch_0 = p.stages(E, label=("fetch", l)) if self.staging[l] is not None else None
+        p.fan_out(s_pm, w13_0, E)
+        if fetch_0 is not None:   # the copy into the staging stack starts as soon as the expert's row count is known
+            p.fan_out(s_ex, fetch_0, E)
+            p.pairwise(fetch_0, w13_0, E)
+        p.pairwise(w13_0, w2_0, E)
+        p.fan_in(w2_0, E, s_cb)
         if shared:   # the shared expert runs beside the routed chain and joins at the combine stage
             s_s13 = self._gemm(p, self.m_sh13[l], self.m_xn, T, self.Is, H, self.hd, self.hd.shape[1], EPI_SILU_MUL,
                                ("shared_w13", l), mat=self.w.shared_w13[l], up_offset=self.Is)
@@ -487,9 +502,9 @@ class ModelLane:
             p.after(s_s13, s_s2)
             p.after(s_s2, s_cb)
         dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
-        if fetch:
+        if fetch_0 is not None:
             dyn += E * self.fetch_tiles
-        expands.append((ex, l, T, w13[0], 0xffffffff, w2[0], s_cb, dyn, fetch[0] if fetch else 0))
+        expands.append((ex, l, T, w13_0, 0xffffffff, w2_0, s_cb, dyn, fetch_0 if fetch_0 is not None else 0))
         return s_cb
 
     def _finish_dynamic(self, p, expands, plans):
@@ -511,10 +526,10 @@ class ModelLane:
                         staging=self.staging[l] if self.staging[l] is not None else 0, fetch_stage0=fetch_0,
                         w13_scale=self.w.w13_scale[l] if self.w.w13_scale[l] is not None else 0,
                         w2_scale=self.w.w2_scale[l] if self.w.w2_scale[l] is not None else 0)
-            self.fab.write(ex.data_ptr(), blob)
+            self.arena.patch(ex, blob)
             at += dyn
         for blob, fields, dyn in plans:
-            self.fab.write(blob.data_ptr(), pack("AttnPlanArgs", dyn_first=at, dyn_cap=dyn, **fields))
+            self.arena.patch(blob, pack("AttnPlanArgs", dyn_first=at, dyn_cap=dyn, **fields))
             at += dyn
 
     def _layers(self, p, T, first_stage, attention, sample_rows, n_rows):
@@ -645,6 +660,7 @@ class ModelLane:
         self._finish_dynamic(p, expands, [])
         self.rows_out = n_rows
         self.labels = p.labels()   # stage names, for monoserve_b200.fabric.trace.summary
+        self.arena.flush()
         return p.upload(self.fab, first=s_embed, iterations=iterations)
 
     def build_decode(self, slots, iterations=1, chunk_keys=0):
@@ -686,6 +702,7 @@ class ModelLane:
         self._finish_dynamic(p, expands, plans)
         self.rows_out = R
         self.labels = p.labels()
+        self.arena.flush()
         return p.upload(self.fab, first=s_embed, iterations=iterations)
 
     # ------------------------------------------------------------------ request state

@@ -70,3 +70,28 @@ def test_pack_matches_the_reference_builder():
         assert np.array_equal(stages.numpy(), g[name + "_stages"]), name
         assert np.array_equal(succ.numpy(), g[name + "_succ"]), name
         assert [first, reset, it] == g[name + "_meta"].tolist()
+
+
+def test_bulk_stage_calls_build_the_same_program():
+    """stages / fan_out / pairwise / fan_in (what a lane uses for a layer's 2 x E expert stages) against the
+    same DAG built stage by stage."""
+    one, bulk = Program(), Program()
+    a = one.stage([Tile(KIND["nop"])])
+    w = [one.stage() for _ in range(5)]
+    v = [one.stage(link=True) for _ in range(5)]
+    c = one.stage([Tile(KIND["nop"])], mark=3)
+    for e in range(5):
+        one.after(a, w[e])
+        one.after(w[e], v[e])
+        one.after(v[e], c)
+    a2 = bulk.stage([Tile(KIND["nop"])])
+    w0, v0 = bulk.stages(5), bulk.stages(5, link=True)
+    c2 = bulk.stage([Tile(KIND["nop"])], mark=3)
+    bulk.fan_out(a2, w0, 5)
+    bulk.pairwise(w0, v0, 5)
+    bulk.fan_in(v0, 5, c2)
+    for x, y in zip(one.pack(a), bulk.pack(a2)):
+        if hasattr(x, "numpy"):
+            assert x.dtype == y.dtype and (x.numpy() == y.numpy()).all()
+        else:
+            assert x == y
