@@ -162,21 +162,20 @@ class Program:
         counts = np.fromiter((len(t) for t in tiles), dtype=np.int64, count=n_all)
         firsts = np.concatenate(([0], np.cumsum(counts)[:-1]))
         firsts[reset] += self.reserved
-        blocks = []
-        for sid in np.flatnonzero(counts).tolist():
-            if sid == reset and self.reserved:
-                blocks.append(np.zeros((self.reserved, 8), dtype=np.uint64))   # the dynamic region
-            t = tiles[sid].copy()
-            t[:, 0] = (t[:, 0] & _LOW32) | (np.uint64(sid) << np.uint64(32))
-            blocks.append(t)
-        if self.reserved and counts[reset] == 0:
-            blocks.append(np.zeros((self.reserved, 8), dtype=np.uint64))
+        live = np.flatnonzero(counts)
+        blocks = [tiles[sid] for sid in live.tolist()]
+        stamp = np.repeat(live.astype(np.uint64), counts[live])
+        if self.reserved:   # the dynamic region: zero tiles in front of the reset stage's
+            at = int(np.searchsorted(live, reset))
+            blocks.insert(at, np.zeros((self.reserved, 8), dtype=np.uint64))
+            stamp = np.insert(stamp, int(counts[live[:at]].sum()), np.zeros(self.reserved, dtype=np.uint64))
+        packed = np.concatenate(blocks) if blocks else np.zeros((0, 8), dtype=np.uint64)
+        packed[:, 0] = (packed[:, 0] & _LOW32) | (stamp << np.uint64(32))
         rows = np.zeros((n_all, 8), dtype=np.int64)
         rows[:, 0], rows[:, 1] = firsts, counts
         rows[:, 2] = np.concatenate(([0], np.cumsum(n_succ)[:-1]))
         rows[:, 3], rows[:, 4], rows[:, 5], rows[:, 6] = n_succ, preds, flags, marks
-        packed = np.concatenate(blocks) if blocks else np.zeros((0, 8), dtype=np.uint64)
-        return (torch.from_numpy(packed.view(np.int64).copy()), torch.from_numpy(rows).to(torch.int32),
+        return (torch.from_numpy(packed.view(np.int64)), torch.from_numpy(rows).to(torch.int32),
                 torch.tensor(flat if flat else [0], dtype=torch.int32), first, reset, iterations)
 
     def upload(self, fabric, first, iterations=1, reset_tiles=8):

@@ -96,6 +96,16 @@ def _bm(rows):
     return HEIGHTS[-1]
 
 
+def _retarget(template, a0=None, a1=None, a2=None, a4=None):
+    """A copy of a tile array with other operand addresses.  The tiles of a stage depend on the layer only
+    through the addresses they name, so a lane keeps one array per shape and re-addresses a copy per layer."""
+    t = template.copy()
+    for col, v in ((3, a0), (4, a1), (5, a2), (7, a4)):
+        if v is not None:
+            t[:, col] = v
+    return t
+
+
 def rope_table(theta, rot_dim, max_pos):
     """cos/sin fp32 [max_pos][rot_dim / 2][2], computed as the reference's oracle does
     (tests/test_fabric_model.py:35-42; the lane's host table: monoserve/runtime/lane.py:36-48)."""
@@ -305,6 +315,7 @@ class ModelLane:
         self.cos_sin = rope_table(cfg.rope_theta, cfg.rotary_dim, max_pos).cuda()
         self._keep = []
         self.arena = _Arena(fab, (64 << 10) * (L + 2))
+        self._templates = {}   # tile arrays by shape, re-addressed per layer (_retarget)
         self._maps()
 
     # ------------------------------------------------------------------ maps and operand blocks
@@ -436,10 +447,16 @@ class ModelLane:
                                                bias=bias.data_ptr() if bias is not None else 0))   # added by the first range
             ptrs.append(args.data_ptr())
             ranges.append(k0 | (kn << 16))
-        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
-        by_range = lambda v: np.asarray(v, dtype=np.int64)[:, None, None]   # noqa: E731  (range, row block, slice)
-        tiles = tile_array(K_GEMM, i0=n0[None], i1=m0[None], i2=np.minimum(bm, rows - m0)[None], a0=by_range(ptrs), a1=wmap,
-                           a2=xm, a3=by_range(ranges), a4=mat.scale.data_ptr() if fp8 else 0)
+        key = ("split", rows, bm, n_out, parts, kt)
+        tmpl = self._templates.get(key)
+        if tmpl is None:
+            m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, 128), indexing="ij")
+            by_range = np.asarray(ranges, dtype=np.int64)[:, None, None]   # (range, row block, slice)
+            tmpl = self._templates[key] = tile_array(K_GEMM, i0=n0[None], i1=m0[None], i2=np.minimum(bm, rows - m0)[None],
+                                                     a3=by_range)
+        per_range = len(tmpl) // parts
+        tiles = _retarget(tmpl, a0=np.repeat(np.asarray(ptrs, dtype=np.uint64), per_range), a1=wmap, a2=xm,
+                          a4=mat.scale.data_ptr() if fp8 else 0)
         return p.stage(tiles, mark=mark, label=label)
 
     def _gemm(self, p, wmap, amaps, rows, n_out, k, out, ld_out, epi, label, residual=None, ld_res=0, mark=None,
@@ -454,14 +471,36 @@ class ModelLane:
             bias=bias.data_ptr() if bias is not None else 0, up_offset=up_offset, w_fp8=int(fp8)))
         xm = amaps[HEIGHTS.index(bm)]
         step = 64 if epi == EPI_SILU_MUL else 128
-        m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, step), indexing="ij")
-        tiles = tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0), a0=args.data_ptr(), a1=wmap, a2=xm,
-                           a4=mat.scale.data_ptr() if fp8 else 0)
+        key = ("gemm", rows, bm, n_out, step)
+        tmpl = self._templates.get(key)
+        if tmpl is None:
+            m0, n0 = np.meshgrid(np.arange(0, rows, bm), np.arange(0, n_out, step), indexing="ij")
+            tmpl = self._templates[key] = tile_array(K_GEMM, i0=n0, i1=m0, i2=np.minimum(bm, rows - m0))
+        tiles = _retarget(tmpl, a0=args.data_ptr(), a1=wmap, a2=xm, a4=mat.scale.data_ptr() if fp8 else 0)
         return p.stage(tiles, mark=mark, label=label)
 
     def _rows(self, kind, args, rows, per):
-        r0 = np.arange(0, rows, per)
-        return tile_array(kind, i0=r0, i1=np.minimum(per, rows - r0), a0=args.data_ptr())
+        key = ("rows", kind, rows, per)
+        tmpl = self._templates.get(key)
+        if tmpl is None:
+            r0 = np.arange(0, rows, per)
+            tmpl = self._templates[key] = tile_array(kind, i0=r0, i1=np.minimum(per, rows - r0))
+        return _retarget(tmpl, a0=args.data_ptr())
+
+    def _one(self, kind, args):
+        """The single tile of an expand or plan stage."""
+        key = ("one", kind)
+        tmpl = self._templates.get(key)
+        if tmpl is None:
+            tmpl = self._templates[key] = tile_array(kind)
+        return _retarget(tmpl, a0=args.data_ptr())
+
+    def _logits(self, args, T, E):
+        key = ("logits", T, E)
+        tmpl = self._templates.get(key)
+        if tmpl is None:
+            tmpl = self._templates[key] = logits_tiles(0, T, E)
+        return _retarget(tmpl, a0=args.data_ptr())
 
     def _moe(self, p, l, T, prev, norm_w, expands):
         """Stages of layer l's MoE block after `prev` (xn, x2 ready); returns the combine stage."""
@@ -475,9 +514,9 @@ class ModelLane:
                        shared=self.y_shared if shared else 0)
         ex = self.arena.put(bytes(_C.struct_layouts()["ExpandArgs"][0]))   # filled once the dynamic region is laid out
         per = max(2, -(-T // (2 * nw)))
-        s_lg = p.stage(logits_tiles(lg.data_ptr(), T, E), label=("router_logits", l))
+        s_lg = p.stage(self._logits(lg, T, E), label=("router_logits", l))
         s_rt = p.stage(self._rows(K_ROUTER, self.router_args[l], T, SUB), label=("router", l))
-        s_ex = p.stage(tile_array(K_EXPAND, a0=ex.data_ptr()), label=("expand", l))
+        s_ex = p.stage(self._one(K_EXPAND, ex), label=("expand", l))
         s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, SUB), label=("permute", l))
         p.after(prev, s_lg)
         p.after(s_lg, s_rt)
@@ -614,6 +653,8 @@ class ModelLane:
         all_logits: keep the logits of every row (row r of `logits`), not only each request's last."""
         page = self.kv.page
         self.arena.reset()   # the operand blocks of this lane's previous program: it must have ended
+        if len(self._templates) > 256:   # shapes of many different batches: start over rather than grow
+            self._templates.clear()
         tokens, pos, slots, req_info, sample_rows = [], [], [], [], []
         gather = []
         bt = np.frombuffer(self.fab.read(self.bt.data_ptr(), self.bt.numel() * 4), dtype=np.int32).reshape(self.bt.shape)
@@ -647,10 +688,12 @@ class ModelLane:
                      H=cfg.hidden, ld=cfg.hidden, eps=cfg.rms_eps)
         s_embed = p.stage(self._rows(K_EMBED, emb, T, CHUNK), label=("embed", 0))
 
+        item_tiles, merge_tiles = fabric_tiles(items, merge, 0, K_ATTN_PREFILL)   # the same work list in every layer
+
         def attention(p, l, prev):
-            tiles, merges = fabric_tiles(items, merge, self.attn_args[l].data_ptr(), K_ATTN_PREFILL)
-            s_a = p.stage(tiles, label=("attn", l))
-            s_m = p.stage(merges, label=("attn_merge", l))
+            at = self.attn_args[l].data_ptr()
+            s_a = p.stage(_retarget(item_tiles, a0=at), label=("attn", l))
+            s_m = p.stage(_retarget(merge_tiles, a0=at), label=("attn_merge", l))
             p.after(prev, s_a)
             p.after(s_a, s_m)
             return s_m
@@ -671,6 +714,8 @@ class ModelLane:
         R = len(slots)
         assert 0 < R <= min(self.T, 256, self.logit_rows)
         self.arena.reset()   # the operand blocks of this lane's previous program: it must have ended
+        if len(self._templates) > 256:   # shapes of many different batches: start over rather than grow
+            self._templates.clear()
         self._put(self.row_req, slots)
         self._put(self.gather, np.arange(R))
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
@@ -682,7 +727,7 @@ class ModelLane:
 
         def attention(p, l, prev):
             blob = self.arena.put(bytes(_C.struct_layouts()["AttnPlanArgs"][0]))   # filled with the dynamic region
-            s_plan = p.stage(tile_array(K_ATTN_PLAN, a0=blob.data_ptr()), label=("attn_plan", l))
+            s_plan = p.stage(self._one(K_ATTN_PLAN, blob), label=("attn_plan", l))
             s_a = p.stage(label=("attn", l))
             s_m = p.stage(label=("attn_merge", l))
             # The plan needs the step's sequence lengths only (the embed tiles' bookkeeping), so every layer's
