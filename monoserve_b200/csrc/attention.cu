@@ -65,7 +65,11 @@ struct AttnClaims {
 };
 constexpr int kClaimSlots = 64;
 // One counter per launch in flight (the launcher hands the slots out in turn).  A launch of n items on g
-// CTAs makes exactly n + g claims, the last g of them failing, and the counter wraps to 0 with the last one.
+// CTAs makes exactly n + g claims, the last g of them failing, and the counter wraps to 0 with the last one,
+// so nothing resets it between launches; a CTA that gives up early still makes its failing claim.  Limits:
+// at most kClaimSlots launches of this kernel in flight on a device at a time, and a launch captured into a
+// CUDA graph keeps the slot it was captured with (replays of one graph follow one another, but two graphs
+// captured kClaimSlots launches apart must not run at the same time).
 __device__ unsigned int g_attn_claim[kClaimSlots];
 
 // Persistent: min(items, SMs) CTAs claim items in list order (longest first) until the list is exhausted.
@@ -101,7 +105,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   c.abort_flag = &sh.abort_flag;
   c.smem = smem_raw;
   if (smem_u32(smem_raw) & 1023u) {   // never seen; the tiles would not be where the descriptors say
-    if (threadIdx.x == 0) atomicOr(p.status, kErrBadArgs);
+    if (threadIdx.x == 0) {
+      atomicOr(p.status, kErrBadArgs);
+      // this CTA's share of the claims, so that the launch still leaves its counter at 0
+      const unsigned int wrap = static_cast<unsigned int>(p.n_items) + gridDim.x - 1;
+      while (atomicInc(&g_attn_claim[p.claim_slot], wrap) < static_cast<unsigned int>(p.n_items)) {
+      }
+    }
     return;
   }
   c.q_phase = 0;

@@ -188,6 +188,7 @@ __device__ void tile_router_logits(const TileDesc& t, int tid);
 __device__ void tile_permute(const TileDesc& t, int tid);
 __device__ void tile_combine(const TileDesc& t, int tid);
 __device__ void tile_asym_reduce(const TileDesc& t, int tid);
+__device__ void tile_norm_logits(const TileDesc& t, int tid);
 __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState& S, int tid);
 
 // tid: index among the exec threads.
@@ -253,6 +254,9 @@ __device__ bool run_core_tile(DeviceState& S, const WorkSlot& w, int tid, uint32
       return true;
     case kTileAsymReduce:
       tile_asym_reduce(t, tid);
+      return true;
+    case kTileNormLogits:
+      tile_norm_logits(t, tid);
       return true;
     case kTileExpand:
       tile_expand(t, w.prog, S, tid);
@@ -807,7 +811,41 @@ __device__ void tile_expand(const TileDesc& t, const ProgramDesc* P, DeviceState
   __threadfence();
   exec_sync();
   stamp();
-  if (tid == 0 && s_skipped > 0) atomicSub(&p_runtime[A.join_stage].deps, static_cast<unsigned int>(s_skipped));
+  const unsigned int skipped = static_cast<unsigned int>(s_skipped);   // the scratch is reused below
+  exec_sync();
+  if (A.permute_args) {
+    // a small batch: the permute of every row, chunk by chunk, with the prefixes written above
+    for (uint32_t r0 = 0; r0 < A.permute_rows; r0 += kFabChunk) {
+      TileDesc pm = t;
+      pm.a[0] = A.permute_args;
+      pm.i0 = r0;
+      pm.i1 = min(static_cast<uint32_t>(kFabChunk), A.permute_rows - r0);
+      tile_permute(pm, tid);
+      exec_sync();
+    }
+    __threadfence();
+  }
+  if (tid == 0 && skipped > 0) atomicSub(&p_runtime[A.join_stage].deps, skipped);
+}
+
+// Fused tile (kind 50): the norm of rows [i0, i0 + i1), then the router projection of those rows against the
+// tile's expert range.  For a small batch this folds the norm stage into the projection's tiles: the tiles of a
+// row group (one per expert range) all compute the same norm and write the same bytes, which costs a few
+// microseconds each and saves a stage.  The norm must be one that can be repeated: plain (36), or add-norm (41)
+// over slabs, which it only reads.
+__device__ void tile_norm_logits(const TileDesc& t, int tid) {
+  TileDesc part = t;
+  const bool add = t.a[3] == kTileAddNorm;
+  if (add) {   // an accumulator that is zeroed once read cannot be read by several tiles
+    NormArgs A;
+    load_block(A, t.a[0]);
+    if (A.acc_parts <= 1) return;
+  }
+  tile_norm(part, tid, add);
+  __threadfence_block();
+  exec_sync();
+  part.a[0] = t.a[1];
+  tile_router_logits(part, tid);
 }
 
 // RMSNorm tile (kind 36) and AddNorm tile (kind 41), NormArgs
@@ -834,11 +872,25 @@ __device__ void tile_norm(const TileDesc& t, int tid, bool add) {
         unpack8(x2[c], f);
         float4 a0 = acc[2 * c], a1 = acc[2 * c + 1];
         if (parts > 1) {
-          // the partial sums of a K-split GEMM, one slab per K range, added in slab order
-          for (int q = 1; q < parts; ++q) {
-            const float4 b0 = acc[q * slab + 2 * c], b1 = acc[q * slab + 2 * c + 1];
-            a0 = make_float4(__fadd_rn(a0.x, b0.x), __fadd_rn(a0.y, b0.y), __fadd_rn(a0.z, b0.z), __fadd_rn(a0.w, b0.w));
-            a1 = make_float4(__fadd_rn(a1.x, b1.x), __fadd_rn(a1.y, b1.y), __fadd_rn(a1.z, b1.z), __fadd_rn(a1.w, b1.w));
+          // the partial sums of a K-split GEMM, one slab per K range, added in slab order; four slabs' loads
+          // are issued before the first of them is used
+          for (int q0 = 1; q0 < parts; q0 += 4) {
+            float4 b0[4], b1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int q = min(q0 + i, parts - 1);
+              b0[i] = acc[q * slab + 2 * c];
+              b1[i] = acc[q * slab + 2 * c + 1];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (q0 + i < parts) {
+                a0 = make_float4(__fadd_rn(a0.x, b0[i].x), __fadd_rn(a0.y, b0[i].y), __fadd_rn(a0.z, b0[i].z),
+                                 __fadd_rn(a0.w, b0[i].w));
+                a1 = make_float4(__fadd_rn(a1.x, b1[i].x), __fadd_rn(a1.y, b1[i].y), __fadd_rn(a1.z, b1[i].z),
+                                 __fadd_rn(a1.w, b1[i].w));
+              }
+            }
           }
         } else {
           acc[2 * c] = zero;

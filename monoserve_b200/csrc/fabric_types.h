@@ -42,6 +42,10 @@ enum TileKind : uint16_t {
   kTileCombine = 47,        // not in the reference: un-permute + weighted combine in pick order (+ RMSNorm)
   kTileRouterLogits = 48,   // not in the reference: router projection with a defined summation order
   kTileFetch = 49,          // not in the reference: a[0] source, a[1] destination, i0 bytes; host memory -> HBM staging
+  kTileNormLogits = 50,     // not in the reference: for rows [i0, i0 + i1) the norm tile (a[0] NormArgs, kind a[3] = 36
+                            // or 41 with slabs) and then the router projection of those rows against experts
+                            // [i2, i2 + i3) (a[1] LogitsArgs): the norm stage of a small batch folded into the
+                            // projection's tiles (every expert-range tile of a row group writes the same norm)
 };
 constexpr int kFabChunk = 16;   // rows per router / permute tile = rank chunk of the stable pack
 

@@ -47,8 +47,11 @@ namespace mf {
   U64(w13_args) U64(w2_args) U64(hist) U64(w13_asym_args) U64(w2_asym_args) U64(red_args) \
   U64(w13_scale) U64(w2_scale) U32(E) U32(H) U32(I) U32(host_region) U32(w13_stage0) U32(w2_stage0) \
   U32(red_stage0) U32(dyn_first) U32(dyn_cap) U32(lane) U32(join_stage) U32(chunks) U64(chunk_counts) \
-  U64(chunk_prefix) U64(staging) U32(fetch_stage0) U32(reserved1)
+  U64(chunk_prefix) U64(staging) U32(fetch_stage0) U32(permute_rows) U64(permute_args)
 
+/* ExpandArgs::permute_args / permute_rows are not in the reference: when set, the expand tile itself runs the
+ * permute of rows [0, permute_rows) once its prefixes are written (the batch is small and a stage costs more than
+ * the copy), and the program has no permute stage. */
 /* Not in the reference: the staged form of a host-resident expert with many rows.  Its weights are
  * copied once into an HBM staging stack (slot = expert id) by fetch tiles, and its GEMM tiles read
  * that copy, so the expert crosses the host link once however many row blocks it has. */

@@ -25,7 +25,8 @@ from monoserve_b200.fabric.args import pack
 from monoserve_b200.lane import SUB, logits_tiles
 
 K_GEMM, K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE, K_RMSNORM, K_QKROPE = 32, 33, 34, 35, 36, 37
-K_ADDNORM = 41
+K_ADDNORM, K_NORM_LOGITS = 41, 50
+FUSE_ROWS, FUSE_PERMUTE_ROWS = 32, 16   # batches this small fold the norm into the projection's tiles, and the permute into expand
 SPLIT_ROWS, SPLIT_PARTS, QKV_PARTS = 64, 8, 2   # a dense GEMM of at most SPLIT_ROWS rows may run as up to SPLIT_PARTS K ranges
 K_ROUTER, K_EXPAND, K_PERMUTE, K_EMBED, K_SAMPLE, K_ATTN_PLAN, K_COMBINE, K_LOGITS = 38, 39, 40, 42, 43, 44, 47, 48
 EPI_STORE, EPI_SILU_MUL, EPI_F32, EPI_ROWS_F32 = 0, 1, 3, 5
@@ -502,8 +503,11 @@ class ModelLane:
             tmpl = self._templates[key] = logits_tiles(0, T, E)
         return _retarget(tmpl, a0=args.data_ptr())
 
-    def _moe(self, p, l, T, prev, norm_w, expands):
-        """Stages of layer l's MoE block after `prev` (xn, x2 ready); returns the combine stage."""
+    def _moe(self, p, l, T, prev, norm_w, expands, fuse_norm=None):
+        """Stages of layer l's MoE block after `prev` (xn, x2 ready); returns the combine stage.
+        fuse_norm = (norm tile kind, its NormArgs): `prev` is the stage BEFORE the post-attention norm, and that norm
+        is folded into the router projection's tiles (a small batch: a stage hop costs more than repeating the
+        norm of a few rows in each expert-range tile)."""
         cfg = self.cfg
         H, E = cfg.hidden, cfg.num_experts
         nw = self.fab.num_workers
@@ -514,14 +518,30 @@ class ModelLane:
                        shared=self.y_shared if shared else 0)
         ex = self.arena.put(bytes(_C.struct_layouts()["ExpandArgs"][0]))   # filled once the dynamic region is laid out
         per = max(2, -(-T // (2 * nw)))
-        s_lg = p.stage(self._logits(lg, T, E), label=("router_logits", l))
+        if fuse_norm is not None:
+            kind, nrm = fuse_norm
+            key = ("norm_logits", T, E)
+            tmpl = self._templates.get(key)
+            if tmpl is None:
+                tmpl = self._templates[key] = logits_tiles(0, T, E)
+                tmpl[:, 0] = (tmpl[:, 0] & np.uint64(0xFFFFFFFFFFFF0000)) | np.uint64(K_NORM_LOGITS)
+            tiles = _retarget(tmpl, a0=nrm.data_ptr(), a1=lg.data_ptr())
+            tiles[:, 6] = kind   # a[3]: which norm
+            s_lg = p.stage(tiles, label=("norm_logits", l))
+        else:
+            s_lg = p.stage(self._logits(lg, T, E), label=("router_logits", l))
         s_rt = p.stage(self._rows(K_ROUTER, self.router_args[l], T, SUB), label=("router", l))
-        s_ex = p.stage(self._one(K_EXPAND, ex), label=("expand", l))
-        s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, SUB), label=("permute", l))
         p.after(prev, s_lg)
         p.after(s_lg, s_rt)
+        xn_ready = s_lg if fuse_norm is not None else prev
+        s_ex = p.stage(self._one(K_EXPAND, ex), label=("expand", l))
         p.after(s_rt, s_ex)
-        p.after(s_ex, s_pm)
+        permute_in_expand = T <= FUSE_PERMUTE_ROWS
+        if permute_in_expand:
+            s_pm = s_ex
+        else:
+            s_pm = p.stage(self._rows(K_PERMUTE, self.permute_args, T, SUB), label=("permute", l))
+            p.after(s_ex, s_pm)
         w13_0 = p.stages(E, label=("w13", l))
         w2_0 = p.stages(E, label=("w2", l))
         s_cb = p.stage(self._rows(K_COMBINE, cb, T, per), mark=(l << 8) | 3, label=("combine", l))
@@ -537,26 +557,27 @@ class ModelLane:
                                ("shared_w13", l), mat=self.w.shared_w13[l], up_offset=self.Is)
             s_s2 = self._gemm(p, self.m_sh2[l], self.m_hd, T, H, self.Is, self.y_shared, H, EPI_F32, ("shared_w2", l),
                               mat=self.w.shared_w2[l])
-            p.after(prev, s_s13)
+            p.after(xn_ready, s_s13)
             p.after(s_s13, s_s2)
             p.after(s_s2, s_cb)
         dyn = (T * cfg.top_k // self.min_form + E) * (cfg.intermediate // 64 + H // 128)
         if fetch_0 is not None:
             dyn += E * self.fetch_tiles
-        expands.append((ex, l, T, w13_0, 0xffffffff, w2_0, s_cb, dyn, fetch_0 if fetch_0 is not None else 0))
+        expands.append((ex, l, T, w13_0, 0xffffffff, w2_0, s_cb, dyn, fetch_0 if fetch_0 is not None else 0,
+                        permute_in_expand))
         return s_cb
 
     def _finish_dynamic(self, p, expands, plans):
         """Hand each expand / plan tile its part of the dynamic region, now that every static tile is counted."""
         at = p.dynamic_first
-        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0 in expands:
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0, pm_in in expands:
             p.reserve(dyn)
         for blob, fields, dyn in plans:
             p.reserve(dyn)
         cfg = self.cfg
         at = p.dynamic_first
-        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0 in expands:
-            blob = pack("ExpandArgs", counts=self.counts, starts=self.starts, fill=self.fill, table=self.tables[l],
+        for ex, l, T, w13_0, red_0, w2_0, s_cb, dyn, fetch_0, pm_in in expands:
+            blob = pack("ExpandArgs", permute_args=self.permute_args if pm_in else 0, permute_rows=T if pm_in else 0, counts=self.counts, starts=self.starts, fill=self.fill, table=self.tables[l],
                         w13_maps=self.w13_maps[l], w2_maps=self.w2_maps[l], xp_maps=self.xp_maps, h_maps=self.h_maps,
                         w13_args=self.w13_args, w2_args=self.w2_args, hist=self.hist[l], E=cfg.num_experts, H=cfg.hidden,
                         I=cfg.intermediate, host_region=REGION_HOST, w13_stage0=w13_0, w2_stage0=w2_0, red_stage0=red_0,
@@ -612,6 +633,10 @@ class ModelLane:
                 nrm = self._dev("NormArgs", x=self.x2, w=w.post_norm[l], out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
                 norm_kind = K_RMSNORM
             p.after(s_attn, s_o)
+            next_norm = w.in_norm[l + 1] if l + 1 < L else None
+            if w.mlp_w13[l] is None and T <= FUSE_ROWS:
+                prev = self._moe(p, l, T, s_o, next_norm, expands, fuse_norm=(norm_kind, nrm))
+                continue
             s_norm = p.stage(self._rows(norm_kind, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
                              label=("norm", l))
             p.after(s_o, s_norm)

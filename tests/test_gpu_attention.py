@@ -164,3 +164,29 @@ def test_full_size_contexts(hq, hkv, lens, prompt):
                                       hq, hkv, lo)
                 assert (out[row + lo:row + lo + 128] - ref).abs().max().item() < TOL, (r, lo)
         row += n
+
+
+def test_many_items_per_cta_mixed_kinds():
+    """The kernel is persistent: with far more work items than SMs every CTA works through a chain of items,
+    decode items (quad-replicated rows, merged through shared memory) and prefill blocks in turn, while its
+    producer already loads the next item.  240 decode rows with contexts of 17 .. 700 keys and two prompts of
+    300 and 150 tokens: about 1000 items on 148 CTAs."""
+    from monoserve_b200.attention import paged_attention
+    hq, hkv, page = 32, 4, 16
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(17, 701, (240,), generator=g).tolist() + [300, 150]
+    rows = [1] * 240 + [300, 150]
+    kc, vc, bt, dense = make_cache(lens, hkv, page, seed=5)
+    T = sum(rows)
+    q = torch.randn(T, hq, 128, generator=g).to(torch.bfloat16)
+    req_info, row = [], 0
+    for n, L in zip(rows, lens):
+        req_info.append((row, L - n, n, L))
+        row += n
+    out = paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), req_info).float().cpu()
+    row = 0
+    for r, (n, L) in enumerate(zip(rows, lens)):
+        ref = dense_reference(q[row:row + n].float(), dense[r][0], dense[r][1], hq, hkv, L - n)
+        err = (out[row:row + n] - ref).abs().max().item()
+        assert err < TOL, (r, err)
+        row += n
