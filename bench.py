@@ -711,6 +711,7 @@ def run_ours(args):
             line["attention"] = side_run(["monoserve_b200.benchmarks.attention"], 300)
             line["mixed_lane"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--steps", "20"], 900)
             line["config4"] = side_run(["monoserve_b200.benchmarks.mixed_lane", "--model", "glm", "--steps", "8"], 900)
+            line["serve"] = side_run(["monoserve_b200.benchmarks.serve", "--rates", "2,8"], 600)
         print(json.dumps(line), flush=True)
     layer.close()
     if world > 1:
@@ -724,8 +725,10 @@ def side_run(module_args, timeout_s):
     MoE-layer tokens/s); `attention`, the paged-KV attention kernel on config-3 shapes (decode
     K+V GB/s, prefill TFLOP/s); `mixed_lane`, the second headline metric: decode TPOT p50
     on config 3 (the full 48-layer Qwen3-30B-A3B-shaped decoder, a 4 x 2048 prefill lane beside a
-    128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory); and `config4`,
-    the same for the GLM-4.5-Air-shaped FP8 decoder of config 4."""
+    128-sequence decode lane in one persistent kernel; it pins 58 GB of host memory); `config4`,
+    the same for the GLM-4.5-Air-shaped FP8 decoder of config 4; and `serve`, config 5 at N = 1:
+    continuous batching under Poisson arrivals at 2 and 8 requests/s (TTFT, time per output token,
+    output tokens/s, host time per program build)."""
     cmd = [sys.executable, "-m"] + module_args
     try:
         out = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s,
@@ -750,7 +753,7 @@ def main():
     ap.add_argument("--ep", action="store_true", help="with --ncu: run the expert-parallel layer as one rank")
     ap.add_argument("--no-mixed-lane", action="store_true",
                     help="skip the side runs that the N=1 line carries (`fabric_layer`, `attention`, `mixed_lane`, "
-                         "`config4`)")
+                         "`config4`, `serve`)")
     ap.add_argument("--sweep", action="store_true",
                     help="the batch x credits x form sweep of benchmark configuration 2 instead of the bench line")
     args = ap.parse_args()
