@@ -95,11 +95,13 @@ def attention_dense(q, k, v, hq, hkv, D):
 
 
 @torch.no_grad()
-def model_logits(w, cfg, tokens, device="cpu"):
+def model_logits(w, cfg, tokens, device="cpu", gaps=None):
     """Whole-model logits with teacher forcing: the Qwen3-style reference oracle
     (tests/test_fabric_model.py:46-82).  `w` is any object with the attributes
     that function reads (embed, in_norm, qkv, q_norm, k_norm, o, post_norm, router,
-    host_w13, host_w2, final_norm, lm_head)."""
+    host_w13, host_w2, final_norm, lm_head).
+    gaps (a list, optional) receives per layer the difference between the K-th and the K+1-th
+    router logit of every row: how close each routing decision is to a tie."""
     L, Kt = cfg.num_layers, cfg.top_k
     hq, hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
     n = len(tokens)
@@ -119,6 +121,9 @@ def model_logits(w, cfg, tokens, device="cpu"):
         ao = attention_dense(q, k, v, hq, hkv, D)
         x2 = bf(x + ao @ w.o[l].float().t())
         xn2 = rms(x2, w.post_norm[l], cfg.rms_eps)
+        if gaps is not None:
+            top = (xn2 @ w.router[l].float().t()).sort(-1, descending=True).values
+            gaps.append(top[:, Kt - 1] - top[:, Kt])
         x, _, _ = moe_layer(xn2, x2, w.router[l], w.host_w13[l], w.host_w2[l], Kt)
     xn = rms(x, w.final_norm, cfg.rms_eps)
     return xn @ w.lm_head.float().t()
