@@ -283,3 +283,41 @@ def test_full_width_layers_match_reference(fab):
         fab.stop()
         got.append(lane.logits[0].cpu().clone())
     check_logits_away_from_ties(torch.stack(got), ref, tie_gap, rows=range(n0, len(tokens)), min_gap=0.012, min_clear=0.25)
+
+
+def test_glm_style_wide_model_takes_the_few_row_paths(fab):
+    """The GLM-4.5 structure on a model wide enough (hidden 1024, 8 / 4 heads) for the few-row forms with FP8
+    matrices: K-split qkv (its bias added by the first range) and o projections into fp32 slabs, the norm folded
+    into the router projection's tiles with the shared expert waiting for it, the permute inside expand; a dense
+    first layer beside them.  20-token prefill and three decode steps against the GLM oracle, tie-aware."""
+    from monoserve_b200.model import KVCache, ModelLane, ModelWeights
+    from oracle import torch_path as tp
+    from tests.test_oracle_golden import _load_make_golden
+    cfg = types.SimpleNamespace(hidden=1024, intermediate=128, num_experts=16, top_k=4, num_layers=3, num_heads=8,
+                                num_kv_heads=4, head_dim=128, vocab=512, rope_theta=1e6, rms_eps=1e-6, rotary_dim=64,
+                                dense_layers=1, dense_intermediate=256, shared_intermediate=128, scoring="sigmoid",
+                                routed_scale=1.5, qk_norm=False, qkv_bias=True)
+    w = _load_make_golden().make_glm_weights(cfg, 23)
+    tokens = torch.randint(0, cfg.vocab, (23,), generator=torch.Generator().manual_seed(4)).tolist()
+    gaps = []
+    ref = tp.model_logits_glm(w, cfg, tokens, gaps=gaps)
+    tie_gap = torch.stack(gaps).min(0).values
+    weights = ModelWeights(cfg, w, hot=[[], list(range(8)), list(range(4, 12))])
+    kv = KVCache(cfg, n_pages=16, page_size=16)
+    lane = ModelLane(fab, 0, cfg, weights, kv, max_tokens=64, max_slots=4, bt_stride=8)
+    lane.set_pages(0, [2, 9, 4])
+    n0 = 20
+    h = lane.build_prefill([(0, tokens[:n0], 0)], all_logits=True)
+    fab.start()
+    run_once(fab, h)
+    fab.stop()
+    check_logits_away_from_ties(lane.logits[:n0].cpu(), ref, tie_gap, rows=range(n0), min_clear=0.5)
+    got = []
+    for i in range(n0, len(tokens)):
+        lane.set_request(0, seq_len=i, last_token=tokens[i])
+        h = lane.build_decode([0])
+        fab.start()
+        run_once(fab, h)
+        fab.stop()
+        got.append(lane.logits[0].cpu().clone())
+    check_logits_away_from_ties(torch.stack(got), ref, tie_gap, rows=range(n0, len(tokens)), min_clear=0.0)
