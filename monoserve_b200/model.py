@@ -28,6 +28,7 @@ K_GEMM, K_ATTN_PREFILL, K_ATTN_DECODE, K_ATTN_MERGE, K_RMSNORM, K_QKROPE = 32, 3
 K_ADDNORM, K_NORM_LOGITS = 41, 50
 FUSE_ROWS, FUSE_PERMUTE_ROWS = 32, 16   # batches this small fold the norm into the projection's tiles, and the permute into expand
 SPLIT_ROWS, SPLIT_PARTS, QKV_PARTS = 64, 8, 2   # a dense GEMM of at most SPLIT_ROWS rows may run as up to SPLIT_PARTS K ranges
+O_SPLIT_ROWS, O_WIDE_PARTS = 512, 4   # the o projection (a residual epilogue of 2-byte loads and stores) keeps the form up to here
 K_ROUTER, K_EXPAND, K_PERMUTE, K_EMBED, K_SAMPLE, K_ATTN_PLAN, K_COMBINE, K_LOGITS = 38, 39, 40, 42, 43, 44, 47, 48
 EPI_STORE, EPI_SILU_MUL, EPI_F32, EPI_ROWS_F32 = 0, 1, 3, 5
 REGION_HOST, REGION_HOT = 0, 1
@@ -285,7 +286,8 @@ class ModelLane:
         self.pair_token, self.pair_weight, self.pair_pos = z(P), z(P, dt=torch.float32), z(T, K)
         self.xp, self.h = z(P + 256, H, dt=bf), z(P + 256, I, dt=bf)
         self.y = z(P + 256, H, dt=torch.float32)
-        self.o_slabs = z(SPLIT_PARTS * SPLIT_ROWS, H, dt=torch.float32)   # K-split partial sums of the o projection
+        self.o_rows = min(O_SPLIT_ROWS, (T + 63) // 64 * 64)
+        self.o_slabs = z(SPLIT_PARTS * self.o_rows, H, dt=torch.float32)   # K-split partial sums of the o projection
         self.qkv_slabs = z(QKV_PARTS * SPLIT_ROWS, self.qkv_dim, dt=torch.float32)   # and of the qkv projection
         # dense FFN of the first layers / shared expert: hidden rows and fp32 output rows
         self.Id, self.Is = getattr(cfg, "dense_intermediate", 0), getattr(cfg, "shared_intermediate", 0)
@@ -430,9 +432,10 @@ class ModelLane:
             self.fab.write(tensor.data_ptr(), data.tobytes())
 
     # ------------------------------------------------------------------ stage builders
-    def _gemm_split(self, p, wmap, amaps, rows, n_out, k, slabs, parts, label, mark=None, mat=None, bias=None):
+    def _gemm_split(self, p, wmap, amaps, rows, n_out, k, slabs, parts, label, mark=None, mat=None, bias=None,
+                    slab_rows=SPLIT_ROWS):
         """The same product for few rows as `parts` K ranges, every range storing its fp32 partial sums in its own
-        slab of `slabs` ([parts][SPLIT_ROWS][n_out]); the add-norm tile behind it adds the slabs in order.  A 128-row
+        slab of `slabs` ([parts][slab_rows][n_out]); the add-norm tile behind it adds the slabs in order.  A 128-row
         weight slice over all of K is a megabyte that one worker streams alone; the ranges spread it over
         parts x n_out / 128 workers, and the sum keeps a defined order (no atomics)."""
         bm = _bm(rows)
@@ -443,7 +446,7 @@ class ModelLane:
         ptrs, ranges = [], []
         for q in range(parts):
             k0, kn = q * per, min(per, kt - q * per)
-            args = self.arena.put(_C.gemm_args(out=slabs.data_ptr() + 4 * q * SPLIT_ROWS * n_out, ld_out=n_out, k_tiles=kt,
+            args = self.arena.put(_C.gemm_args(out=slabs.data_ptr() + 4 * q * slab_rows * n_out, ld_out=n_out, k_tiles=kt,
                                                epi=EPI_F32, bm=bm, n_limit=n_out, w_fp8=int(fp8),
                                                bias=bias.data_ptr() if bias is not None else 0))   # added by the first range
             ptrs.append(args.data_ptr())
@@ -619,13 +622,13 @@ class ModelLane:
             s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, ROPE_ITEMS), mark=(l << 8) | 1, label=("rope", l))
             p.after(s_qkv, s_rope)
             s_attn = attention(p, l, s_rope)
-            o_parts = min(SPLIT_PARTS, (hq * 128 // 64) // 8) if T <= SPLIT_ROWS else 1
+            o_parts = min(SPLIT_PARTS if T <= SPLIT_ROWS else O_WIDE_PARTS, (hq * 128 // 64) // 8) if T <= self.o_rows else 1
             if o_parts > 1:
                 # few rows: K ranges into fp32 slabs, then x2 = bf16(x + sum of the slabs) and its norm in one tile
                 s_o = self._gemm_split(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.o_slabs, o_parts, ("o", l),
-                                       mark=(l << 8) | 2, mat=w.o[l])
+                                       mark=(l << 8) | 2, mat=w.o[l], slab_rows=self.o_rows)
                 nrm = self._dev("NormArgs", x=self.x2, x2=self.x, acc=self.o_slabs, w=w.post_norm[l], out=self.xn, H=H, ld=H,
-                                eps=cfg.rms_eps, acc_parts=o_parts, acc_rows=SPLIT_ROWS)
+                                eps=cfg.rms_eps, acc_parts=o_parts, acc_rows=self.o_rows)
                 norm_kind = K_ADDNORM
             else:
                 s_o = self._gemm(p, self.m_o[l], self.m_ao, T, H, hq * 128, self.x2, H, EPI_STORE, ("o", l),
