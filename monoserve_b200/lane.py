@@ -36,11 +36,11 @@ def _u64(values):
     return torch.tensor([int(v) for v in values], dtype=torch.int64).cuda()
 
 
-def logits_tiles(args_ptr, T, E):
-    """Router-projection tiles (kind 48): blocks of LOGIT_ROWS rows x LOGIT_EXPERTS experts."""
+def logits_tiles(args_ptr, T, E, rows=LOGIT_ROWS):
+    """Router-projection tiles (kind 48): blocks of `rows` rows x LOGIT_EXPERTS experts."""
     import numpy as np
-    r0, e0 = np.meshgrid(np.arange(0, T, LOGIT_ROWS), np.arange(0, E, LOGIT_EXPERTS), indexing="ij")
-    return tile_array(K_LOGITS, i0=r0, i1=np.minimum(LOGIT_ROWS, T - r0), i2=e0, i3=np.minimum(LOGIT_EXPERTS, E - e0),
+    r0, e0 = np.meshgrid(np.arange(0, T, rows), np.arange(0, E, LOGIT_EXPERTS), indexing="ij")
+    return tile_array(K_LOGITS, i0=r0, i1=np.minimum(rows, T - r0), i2=e0, i3=np.minimum(LOGIT_EXPERTS, E - e0),
                       a0=args_ptr)
 
 

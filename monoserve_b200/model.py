@@ -526,7 +526,8 @@ class ModelLane:
             key = ("norm_logits", T, E)
             tmpl = self._templates.get(key)
             if tmpl is None:
-                tmpl = self._templates[key] = logits_tiles(0, T, E)
+                # four rows per tile: one row's norm per exec warp, then their projection
+                tmpl = self._templates[key] = logits_tiles(0, T, E, rows=4)
                 tmpl[:, 0] = (tmpl[:, 0] & np.uint64(0xFFFFFFFFFFFF0000)) | np.uint64(K_NORM_LOGITS)
             tiles = _retarget(tmpl, a0=nrm.data_ptr(), a1=lg.data_ptr())
             tiles[:, 6] = kind   # a[3]: which norm
