@@ -620,7 +620,9 @@ class ModelLane:
                         k_norm=w.k_norm[l] if w.k_norm[l] is not None else 0, tok_pos=self.tok_pos, tok_slot=self.tok_slot,
                         cos_sin=self.cos_sin, ld_qkv=self.qkv_dim, hq=hq, hkv=hkv, rot_dim=cfg.rotary_dim,
                         theta=cfg.rope_theta, eps=cfg.rms_eps, max_pos=self.max_pos)
-            s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, ROPE_ITEMS), mark=(l << 8) | 1, label=("rope", l))
+            # a small batch: few items per tile, so that every worker has one (an item is a chain of exposed loads)
+            rope_items = min(ROPE_ITEMS, max(4, -(-(T * heads) // (4 * self.fab.num_workers)) * 4))
+            s_rope = p.stage(self._rows(K_QKROPE, qk, T * heads, rope_items), mark=(l << 8) | 1, label=("rope", l))
             p.after(s_qkv, s_rope)
             s_attn = attention(p, l, s_rope)
             o_parts = min(SPLIT_PARTS if T <= SPLIT_ROWS else O_WIDE_PARTS, (hq * 128 // 64) // 8) if T <= self.o_rows else 1
