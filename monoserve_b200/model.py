@@ -491,6 +491,26 @@ class ModelLane:
             tmpl = self._templates[key] = tile_array(kind, i0=r0, i1=np.minimum(per, rows - r0))
         return _retarget(tmpl, a0=args.data_ptr())
 
+    def _per(self, T):
+        """Rows per tile of a stage whose tiles give each exec warp one row at a time: up to four rows per tile
+        while that keeps the stage to one round of tiles over the workers (150 tiles on 148 workers are two
+        rounds), a multiple of four beyond."""
+        nw = self.fab.num_workers
+        if T <= 4 * nw:
+            return max(1, -(-T // nw))
+        return -(-(-(-T // (2 * nw))) // 4) * 4
+
+    def _logit_rows(self, T, E):
+        """Rows per router-projection tile (of 16 experts): the height in 8 .. 32 that costs the fewest rounds x
+        (rows + 4), the 4 standing for what a tile costs before its first row."""
+        nw, groups = self.fab.num_workers, -(-E // 16)
+        best = None
+        for rows in range(8, 33, 2):
+            cost = -(-(-(-T // rows) * groups) // nw) * (rows + 4)
+            if best is None or cost < best[0]:
+                best = (cost, rows)
+        return best[1]
+
     def _one(self, kind, args):
         """The single tile of an expand or plan stage."""
         key = ("one", kind)
@@ -503,7 +523,7 @@ class ModelLane:
         key = ("logits", T, E)
         tmpl = self._templates.get(key)
         if tmpl is None:
-            tmpl = self._templates[key] = logits_tiles(0, T, E)
+            tmpl = self._templates[key] = logits_tiles(0, T, E, rows=self._logit_rows(T, E))
         return _retarget(tmpl, a0=args.data_ptr())
 
     def _moe(self, p, l, T, prev, norm_w, expands, fuse_norm=None):
@@ -520,7 +540,7 @@ class ModelLane:
                        w=norm_w if norm_w is not None else 0, out=self.xn, K=cfg.top_k, H=H, eps=cfg.rms_eps,
                        shared=self.y_shared if shared else 0)
         ex = self.arena.put(bytes(_C.struct_layouts()["ExpandArgs"][0]))   # filled once the dynamic region is laid out
-        per = max(2, -(-T // (2 * nw)))
+        per = self._per(T)
         if fuse_norm is not None:
             kind, nrm = fuse_norm
             key = ("norm_logits", T, E)
@@ -643,7 +663,7 @@ class ModelLane:
             if w.mlp_w13[l] is None and T <= FUSE_ROWS:
                 prev = self._moe(p, l, T, s_o, next_norm, expands, fuse_norm=(norm_kind, nrm))
                 continue
-            s_norm = p.stage(self._rows(norm_kind, nrm, T, max(1, -(-T // (2 * self.fab.num_workers)))),
+            s_norm = p.stage(self._rows(norm_kind, nrm, T, self._per(T)),
                              label=("norm", l))
             p.after(s_o, s_norm)
             next_norm = w.in_norm[l + 1] if l + 1 < L else None
@@ -658,7 +678,7 @@ class ModelLane:
                 prev = s_d2
                 if next_norm is not None:
                     nn = self._dev("NormArgs", x=self.x, w=next_norm, out=self.xn, H=H, ld=H, eps=cfg.rms_eps)
-                    prev = p.stage(self._rows(K_RMSNORM, nn, T, max(1, -(-T // (2 * self.fab.num_workers)))),
+                    prev = p.stage(self._rows(K_RMSNORM, nn, T, self._per(T)),
                                    label=("in_norm", l + 1))
                     p.after(s_d2, prev)
                 continue
@@ -667,7 +687,7 @@ class ModelLane:
         R = n_rows
         fin = self._dev("NormArgs", x=self.x, w=w.final_norm, out=self.xn, gather=self.gather, out2=self.xlast, H=H, ld=H,
                      eps=cfg.rms_eps)
-        s_fin = p.stage(self._rows(K_RMSNORM, fin, T, max(1, -(-T // (2 * self.fab.num_workers)))), label=("final_norm", L))
+        s_fin = p.stage(self._rows(K_RMSNORM, fin, T, self._per(T)), label=("final_norm", L))
         p.after(prev, s_fin)
         s_lm = self._gemm(p, self.m_lm, self.m_xlast, R, cfg.vocab, H, self.logits, cfg.vocab, EPI_F32, ("lm_head", L))
         p.after(s_fin, s_lm)
