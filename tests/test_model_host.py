@@ -31,3 +31,30 @@ def test_logits_tiles_cover_rows_and_experts_once():
             assert rows <= LOGIT_ROWS and ne <= LOGIT_EXPERTS and int(t[0] & 0xffff) == 48
             seen[r0:r0 + rows, e0:e0 + ne] += 1
         assert (seen == 1).all()
+
+
+def test_rows_per_tile_keep_a_stage_to_whole_rounds():
+    """The lane picks the rows per tile of its row-wise stages so that a stage does not spill a few tiles into
+    another round over the workers, and the router projection's tile height by rounds x rows; every choice must
+    still cover all rows (the tile builder takes care of the last, shorter tile)."""
+    import types
+    import numpy as np
+    from monoserve_b200.lane import logits_tiles
+    from monoserve_b200.model import ModelLane, _retarget
+    lane = types.SimpleNamespace(fab=types.SimpleNamespace(num_workers=148))
+    for T in (1, 8, 148, 149, 300, 592, 593, 4096):
+        per = ModelLane._per(lane, T)
+        tiles = -(-T // per)
+        assert per >= 1 and (tiles <= 148 or per % 4 == 0)
+        assert tiles <= 148 or tiles <= 2 * 148 + 148          # beyond one round: about two
+        rows = ModelLane._logit_rows(lane, T, 128)
+        assert 8 <= rows <= 32
+        seen = np.zeros((T, 128), dtype=np.int32)
+        for t in logits_tiles(0, T, 128, rows=rows):
+            r0, n = int(t[1] & 0xffffffff), int(t[1] >> 32)
+            e0, ne = int(t[2] & 0xffffffff), int(t[2] >> 32)
+            seen[r0:r0 + n, e0:e0 + ne] += 1
+        assert (seen == 1).all()
+    assert ModelLane._per(lane, 300) == 3 and ModelLane._logit_rows(lane, 300, 128) == 18   # 100 and 136 tiles
+    a = logits_tiles(777, 20, 128)
+    assert (a == _retarget(logits_tiles(0, 20, 128), a0=777)).all()   # a template re-addressed = built with the address
