@@ -73,17 +73,18 @@ def _as_tile_rows(tiles):
 
 class Program:
     def __init__(self):
-        self._tiles, self._flags, self._marks, self._succ, self._preds, self._labels = [], [], [], [], [], []
+        self._tiles, self._counts, self._flags, self._marks, self._labels = [], [], [], [], []
+        self._edge_from, self._edge_to = [], []   # the DAG's edges in the order they were added
         self.reserved = 0
 
     def stage(self, tiles=(), link=False, mark=None, label=None):
         """Add a stage; returns its id.  link: its tiles read host memory (gated by
         link credits); mark: value reported to the host when the stage completes."""
-        self._tiles.append(_as_tile_rows(tiles))
+        rows = _as_tile_rows(tiles)
+        self._tiles.append(rows)
+        self._counts.append(len(rows))
         self._flags.append((STAGE_LINK if link else 0) | (STAGE_MARK if mark is not None else 0))
         self._marks.append(mark or 0)
-        self._succ.append([])
-        self._preds.append(0)
         self._labels.append(label)
         return len(self._tiles) - 1
 
@@ -91,37 +92,34 @@ class Program:
         """n empty stages (their tiles are written at run time) with consecutive ids; returns the first id."""
         first = len(self._tiles)
         self._tiles.extend([_NO_TILES] * n)
+        self._counts.extend([0] * n)
         self._flags.extend([STAGE_LINK if link else 0] * n)
         self._marks.extend([0] * n)
-        self._succ.extend([] for _ in range(n))
-        self._preds.extend([0] * n)
         self._labels.extend([label] * n)
         return first
 
+    def after(self, pred, succ):
+        """succ becomes ready only after pred has completed."""
+        self._edge_from.append(pred)
+        self._edge_to.append(succ)
+
     def fan_out(self, pred, first, n):
         """pred -> each of the stages first .. first + n - 1."""
-        self._succ[pred].extend(range(first, first + n))
-        self._preds[first:first + n] = [d + 1 for d in self._preds[first:first + n]]
+        self._edge_from.extend([pred] * n)
+        self._edge_to.extend(range(first, first + n))
 
     def pairwise(self, first_a, first_b, n):
         """first_a + i -> first_b + i for i < n."""
-        for i in range(n):
-            self._succ[first_a + i].append(first_b + i)
-        self._preds[first_b:first_b + n] = [d + 1 for d in self._preds[first_b:first_b + n]]
+        self._edge_from.extend(range(first_a, first_a + n))
+        self._edge_to.extend(range(first_b, first_b + n))
 
     def fan_in(self, first, n, succ):
         """each of the stages first .. first + n - 1 -> succ."""
-        for i in range(first, first + n):
-            self._succ[i].append(succ)
-        self._preds[succ] += n
+        self._edge_from.extend(range(first, first + n))
+        self._edge_to.extend([succ] * n)
 
     def labels(self):
         return list(self._labels) + [("reset", -1)]
-
-    def after(self, pred, succ):
-        """succ becomes ready only after pred has completed."""
-        self._succ[pred].append(succ)
-        self._preds[succ] += 1
 
     def reserve(self, n):
         """Reserve n tiles that device tiles fill at run time (see dynamic_first)."""
@@ -129,37 +127,35 @@ class Program:
 
     @property
     def dynamic_first(self):
-        return sum(len(t) for t in self._tiles)
+        return sum(self._counts)
 
     def pack(self, first, iterations=1, reset_tiles=8):
         """(tiles int64 [n, 8], stages int32 [m, 8], succ int32 [k], first, reset, iterations)."""
         n_user = len(self._tiles)
-        preds_user = np.asarray(self._preds, dtype=np.int64)
+        reset = n_user
+        n_all = n_user + 1
+        e_from = np.asarray(self._edge_from, dtype=np.int64)
+        e_to = np.asarray(self._edge_to, dtype=np.int64)
+        preds_user = np.bincount(e_to, minlength=n_user)
         orphan = np.flatnonzero(preds_user == 0)
         orphan = orphan[orphan != first]
         if orphan.size:
             raise ValueError(f"stage {int(orphan[0])} has no predecessor and is not the first stage, "
                              f"so it would never become ready")
-        reset = n_user
-        n_all = n_user + 1
+        # every sink gets the reset stage as its only successor; a stage's successors keep the order they were added in
+        sinks = np.flatnonzero(np.bincount(e_from, minlength=n_user) == 0)
+        e_from = np.concatenate((e_from, sinks))
+        e_to = np.concatenate((e_to, np.full(sinks.size, reset, dtype=np.int64)))
+        flat = e_to[np.argsort(e_from, kind="stable")]
+        n_succ = np.bincount(e_from, minlength=n_all)
+        preds = np.concatenate((preds_user, [sinks.size]))
         per = -(-n_all // max(1, reset_tiles))
         zero = [Tile(KIND["zero_runtime"], i=(b, min(n_all, b + per), reset, 0)) for b in range(0, n_all, per)]
         tiles = self._tiles + [_as_tile_rows(zero)]
         flags = self._flags + [STAGE_RESET]
         marks = self._marks + [0]
-        # every sink gets the reset stage as its only successor
-        n_succ = np.fromiter((len(x) for x in self._succ), dtype=np.int64, count=n_user)
-        sinks = n_succ == 0
-        flat = []
-        for sid, mine in enumerate(self._succ):
-            if mine:
-                flat.extend(mine)
-            else:
-                flat.append(reset)
-        n_succ = np.concatenate((np.where(sinks, 1, n_succ), [0]))
-        preds = np.concatenate((preds_user, [int(sinks.sum())]))
         # tile blocks in stage order (the dynamic region before the reset stage's), every tile stamped with its stage
-        counts = np.fromiter((len(t) for t in tiles), dtype=np.int64, count=n_all)
+        counts = np.asarray(self._counts + [len(zero)], dtype=np.int64)
         firsts = np.concatenate(([0], np.cumsum(counts)[:-1]))
         firsts[reset] += self.reserved
         live = np.flatnonzero(counts)
@@ -175,8 +171,9 @@ class Program:
         rows[:, 0], rows[:, 1] = firsts, counts
         rows[:, 2] = np.concatenate(([0], np.cumsum(n_succ)[:-1]))
         rows[:, 3], rows[:, 4], rows[:, 5], rows[:, 6] = n_succ, preds, flags, marks
-        return (torch.from_numpy(packed.view(np.int64)), torch.from_numpy(rows).to(torch.int32),
-                torch.tensor(flat if flat else [0], dtype=torch.int32), first, reset, iterations)
+        succ = torch.from_numpy(flat).to(torch.int32) if flat.size else torch.tensor([0], dtype=torch.int32)
+        return (torch.from_numpy(packed.view(np.int64)), torch.from_numpy(rows).to(torch.int32), succ, first, reset,
+                iterations)
 
     def upload(self, fabric, first, iterations=1, reset_tiles=8):
         return fabric.upload(*self.pack(first, iterations, reset_tiles))
