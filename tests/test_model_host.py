@@ -58,3 +58,39 @@ def test_rows_per_tile_keep_a_stage_to_whole_rounds():
     assert ModelLane._per(lane, 300) == 3 and ModelLane._logit_rows(lane, 300, 128) == 18   # 100 and 136 tiles
     a = logits_tiles(777, 20, 128)
     assert (a == _retarget(logits_tiles(0, 20, 128), a0=777)).all()   # a template re-addressed = built with the address
+
+
+def test_operand_arena_batches_its_writes():
+    """A build puts hundreds of operand blocks; they reach the device in one write per flush, blocks put earlier in
+    the build can still be patched, and a block of an earlier build cannot."""
+    import pytest
+    from monoserve_b200.model import _Arena
+
+    class FakeFabric:
+        def __init__(self):
+            self.writes = []
+
+        def write(self, dst, data):
+            self.writes.append((dst, bytes(data)))
+
+    arena = _Arena.__new__(_Arena)            # no device buffer here: only the bookkeeping is under test
+    arena.fab, arena.at, arena.flushed, arena.host = FakeFabric(), 0, 0, bytearray(4096)
+    arena.buf = type("Buf", (), {"data_ptr": lambda self: 0x10000, "numel": lambda self: 4096})()
+    a = arena.put(b"\x01" * 100)
+    b = arena.put(b"\x02" * 300)
+    assert (a.data_ptr(), b.data_ptr()) == (0x10000, 0x10000 + 256) and arena.fab.writes == []
+    arena.patch(a, b"\x07" * 100)
+    arena.flush()
+    (dst, data), = arena.fab.writes
+    assert dst == 0x10000 and len(data) == 256 + 512 and data[:100] == b"\x07" * 100 and data[256:556] == b"\x02" * 300
+    c = arena.put(b"\x03" * 16)
+    with pytest.raises(AssertionError):
+        arena.patch(a, b"\x00")               # already flushed: the device copy would not follow
+    arena.flush()
+    assert arena.fab.writes[1] == (0x10000 + 768, b"\x03" * 16 + bytes(240))
+    arena.flush()
+    assert len(arena.fab.writes) == 2         # nothing new, nothing written
+    with pytest.raises(RuntimeError):
+        arena.put(bytes(4096))
+    arena.reset()
+    assert arena.put(b"x").data_ptr() == 0x10000 and c.data_ptr() == 0x10000 + 768
