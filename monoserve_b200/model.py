@@ -708,25 +708,31 @@ class ModelLane:
             self._templates.clear()
         tokens, pos, slots, req_info, sample_rows = [], [], [], [], []
         gather = []
-        bt = np.frombuffer(self.fab.read(self.bt.data_ptr(), self.bt.numel() * 4), dtype=np.int32).reshape(self.bt.shape)
+        stride = self.bt.shape[1]
         row = 0
         for r, (slot, toks, pos0) in enumerate(batch):
             n = len(toks)
             req_info.append((row, pos0, n, pos0 + n))
-            for i, t in enumerate(toks):
-                ppos = pos0 + i
-                tokens.append(t)
-                pos.append(ppos)
-                slots.append(int(bt[slot, ppos // page]) * page + ppos % page)
-                gather.append(row + i if all_logits else (r if i == n - 1 else -1))
+            # the request's row of the block table (read through the fabric: nothing may be launched beside it)
+            pages = np.frombuffer(self.fab.read(self.bt.data_ptr() + 4 * slot * stride, 4 * stride), dtype=np.int32)
+            ppos = pos0 + np.arange(n)
+            tokens.append(np.asarray(toks, dtype=np.int32))
+            pos.append(ppos.astype(np.int32))
+            slots.append((pages[ppos // page].astype(np.int64) * page + ppos % page).astype(np.int32))
+            if all_logits:
+                gather.append(np.arange(row, row + n, dtype=np.int32))
+            else:
+                g = np.full(n, -1, dtype=np.int32)
+                g[n - 1] = r
+                gather.append(g)
             sample_rows.append((row + n - 1 if all_logits else r, slot))
             row += n
         T = row
         assert 0 < T <= self.T and (T if all_logits else len(batch)) <= self.logit_rows
-        self._put(self.tokens, tokens)
-        self._put(self.tok_pos, pos)
-        self._put(self.tok_slot, slots)
-        self._put(self.gather, gather)
+        self._put(self.tokens, np.concatenate(tokens))
+        self._put(self.tok_pos, np.concatenate(pos))
+        self._put(self.tok_slot, np.concatenate(slots))
+        self._put(self.gather, np.concatenate(gather))
         self._put(self.req_info, req_info)
         cfg = self.cfg
         hq, hkv = cfg.num_heads, cfg.num_kv_heads
