@@ -38,6 +38,11 @@ def main():
     ap.add_argument("--token-budget", type=int, default=4096)
     ap.add_argument("--pages", type=int, default=24000)
     ap.add_argument("--spare-sms", type=int, default=8, help="SMs left to the host's copies and fills while the fabric runs")
+    ap.add_argument("--plan", choices=["fixed", "search"], default="fixed",
+                    help="search: the SM split of the decode and prefill lanes comes from the control plane's plan search "
+                         "(deadlines --tpot / --ttft) whenever both lanes run, instead of half / half")
+    ap.add_argument("--tpot", type=float, default=0.05, help="decode deadline for --plan search, seconds per step")
+    ap.add_argument("--ttft", type=float, default=0.5, help="prefill deadline for --plan search, seconds per pass")
     ap.add_argument("--quick", action="store_true", help="4 layers, short lengths, one rate: a smoke run")
     args = ap.parse_args()
     prompt_clip, output_clip = (16, 4096), (8, 2048)
@@ -59,8 +64,13 @@ def main():
     table = RequestTable(fab, slots, bt_stride)
     results = []
     try:
+        planner = None
+        if args.plan == "search":
+            from monoserve_b200.engine import SearchPlanner
+            planner = SearchPlanner(cfg, [list(range(cfg.num_experts)) for _ in range(cfg.num_layers)], tpot_s=args.tpot,
+                                    ttft_s=args.ttft)
         eng = Engine(fab, cfg, weights, kv, table, PagePool(args.pages), max_decode=args.max_decode,
-                     token_budget=args.token_budget, max_len=max_len)
+                     token_budget=args.token_budget, max_len=max_len, planner=planner)
         torch.cuda.synchronize()
         t_setup = time.time() - t_setup
         fab.start()
@@ -83,6 +93,8 @@ def main():
             for kind, count in (("prefill", "prefill_passes"), ("decode", "decode_programs")):
                 made = line[count]
                 line[f"{kind}_build_ms"] = 1e3 * (eng.stats[f"{kind}_build_s"] - before[f"{kind}_build_s"]) / made if made else None
+            if planner is not None:
+                line["plan_search"] = dict(planner.stats, sm_decode_last=eng.map.count(0))
             results.append(line)
         err = fab.progress()["error"]
     finally:

@@ -155,7 +155,7 @@ class LaneLoad:
         self._h, self.decode, self.staging, self.deadline = handle, work.decode, work.staging, work.deadline
 
     def __del__(self):
-        if getattr(self, "_h", None) and _C.lib is not None:
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:   # (module globals go first at exit)
             _C.lib.monofab_plan_load_destroy(self._h)
             self._h = None
 
@@ -174,7 +174,7 @@ class Estimator:
         self.link_credits, self.exposure_bound = info[0], info[1]
 
     def __del__(self):
-        if getattr(self, "_h", None) and _C.lib is not None:
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:   # (module globals go first at exit)
             _C.lib.monofab_plan_estimator_destroy(self._h)
             self._h = None
 
@@ -232,7 +232,7 @@ class PlanSearch:
                                                    ctypes.byref(self._h)))
 
     def __del__(self):
-        if getattr(self, "_h", None) and _C.lib is not None:
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:   # (module globals go first at exit)
             _C.lib.monofab_plan_search_destroy(self._h)
             self._h = None
 
@@ -264,7 +264,7 @@ class ProfileView:
         _C.check(_C.lib.monofab_plan_profile_create(layers, experts, ctypes.byref(self._h)))
 
     def __del__(self):
-        if getattr(self, "_h", None) and _C.lib is not None:
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:   # (module globals go first at exit)
             _C.lib.monofab_plan_profile_destroy(self._h)
             self._h = None
 
@@ -335,7 +335,7 @@ class Admission:
         self.config = config
 
     def __del__(self):
-        if getattr(self, "_h", None) and _C.lib is not None:
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:   # (module globals go first at exit)
             _C.lib.monofab_plan_admission_destroy(self._h)
             self._h = None
 

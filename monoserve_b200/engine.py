@@ -108,11 +108,58 @@ class _Req:
         self.tokens, self.token_times, self.first_time, self.finish_time = [], [], None, None
 
 
+class SearchPlanner:
+    """The SM split of the two lanes from the control plane's plan search (monoserve_b200/control.py: the time
+    estimator over a calibration, Algorithm 1), asked whenever both lanes have a program: the decode lane's work is
+    the contexts of its batch with the deadline `tpot_s` per step, the prefill lane's its pass with the deadline
+    `ttft_s`; expected expert activations come from uniform routing shares and the hot sets.  The reference's
+    engine takes its plans from the same search through its admission policy (monoserve/engine.py:303-527); here
+    only the split is taken, the queue stays first come first served."""
+
+    def __init__(self, cfg, hot, tpot_s=0.05, ttft_s=0.5, calibration=None, fp8=False):
+        import os
+        import types
+        from monoserve_b200 import control
+        path = calibration or os.path.join(os.path.dirname(os.path.abspath(__file__)), "calibration", "b200.json")
+        self.control, self.cfg, self.tpot_s, self.ttft_s = control, cfg, tpot_s, ttft_s
+        self.est = control.Estimator(control.model_shape(types.SimpleNamespace(**vars(cfg), fp8=fp8)),
+                                     control.load_calibration(path))
+        shares = np.full((cfg.num_layers, cfg.num_experts), 1.0 / cfg.num_experts)
+        self.view = control.profile_view(shares, shares, hot)
+        self.search = control.PlanSearch(self.est)
+        self.dense = getattr(cfg, "dense_layers", 0)
+        self.stats = dict(searches=0, infeasible=0, micros=0.0)
+
+    def _work(self, decode, seqs, deadline, rows):
+        w = self.control.LaneWork()
+        w.decode, w.deadline = decode, deadline
+        w.passes = [[self.control.Seq(t, c) for t, c in seqs]]
+        on = [self.view.expected(decode, l, rows * self.cfg.top_k) if l >= self.dense else (0.0, 0.0)
+              for l in range(self.cfg.num_layers)]
+        w.active, w.miss = [a for a, _ in on], [m for _, m in on]
+        return w
+
+    def split(self, contexts, prompts, workers):
+        """Workers of the decode lane out of `workers`, for a decode batch with these context lengths beside a
+        prefill pass with these prompt lengths; None when either lane is empty."""
+        if not contexts or not prompts:
+            return None
+        lanes = [self.est.load(self._work(True, [(1, c) for c in contexts], self.tpot_s, len(contexts))),
+                 self.est.load(self._work(False, [(n, 0) for n in prompts], self.ttft_s, sum(prompts)))]
+        plan = self.search.solve(lanes)
+        self.stats["searches"] += 1
+        self.stats["micros"] += plan.micros
+        if not plan.feasible:
+            self.stats["infeasible"] += 1   # the search's fallback split is still the best it found
+        sms = [l.sms for l in plan.lanes]
+        return min(workers - 1, max(1, round(sms[0] * workers / max(1, sum(sms)))))
+
+
 class Engine:
     """One GPU, one prefill lane, one decode lane with two program buffers."""
 
     def __init__(self, fab, cfg, weights, kv, table, pool, max_decode=64, token_budget=2048, max_len=None,
-                 sm_decode=None, caps=(8, 8), forms=(64, 0)):
+                 sm_decode=None, caps=(8, 8), forms=(64, 0), planner=None):
         self.fab, self.cfg, self.kv, self.table, self.pool = fab, cfg, kv, table, pool
         self.max_decode, self.token_budget = max_decode, token_budget
         self.max_len = max_len or table.bt_stride * kv.page
@@ -127,6 +174,7 @@ class Engine:
         self.sm_decode = sm_decode if sm_decode is not None else n // 2
         self.map = [DECODE] * self.sm_decode + [PREFILL] * (n - self.sm_decode)
         self.caps, self.forms = list(caps), list(forms)
+        self.planner = planner   # a SearchPlanner: the split follows the lanes' work instead of staying at sm_decode
         idle = Program()
         idle.stage([Tile(0)])
         self.idle_program = idle   # a one-tile program that ends a lane: published when the decode batch is empty
@@ -171,6 +219,14 @@ class Engine:
 
     def _publish(self):
         programs = [self.dec_pending[0] if self.dec_pending else (self.dec_handle or 0), self.pre_handle or 0]
+        if self.planner is not None:
+            batch = self.dec_pending[3] if self.dec_pending else self.dec_batch
+            contexts = [len(r.prompt) + r.delivered for r in batch if r.finish_time is None]
+            prompts = [len(r.prompt) for r in self.prefilling] if self.pre_handle else []
+            n = self.fab.num_workers
+            dec = self.planner.split(contexts, prompts, n)
+            if dec is not None:
+                self.map = [DECODE] * dec + [PREFILL] * (n - dec)
         self.fab.publish(map=self.map, caps=self.caps, order=[DECODE, PREFILL], programs=programs, forms=self.forms)
         self.stats["published"] += 1
 

@@ -31,3 +31,17 @@ def test_page_pool_never_hands_out_the_sink_or_a_page_twice():
         pool.take(1)
     pool.give(a)
     assert sorted(pool.take(4)) == sorted(a)
+
+
+def test_search_planner_splits_the_workers_between_the_lanes():
+    """The engine's planner: the control plane's plan search over the committed B200 calibration gives the decode
+    lane a share that grows with its batch and shrinks when the prefill pass grows; one lane alone needs no split."""
+    from monoserve_b200.benchmarks.mixed_lane import q_config
+    from monoserve_b200.engine import SearchPlanner
+    cfg = q_config(48)
+    planner = SearchPlanner(cfg, [list(range(cfg.num_experts))] * cfg.num_layers, tpot_s=0.05, ttft_s=0.5)
+    assert planner.split([], [300], 140) is None and planner.split([100], [], 140) is None
+    small = planner.split([1000] * 4, [4000], 140)
+    large = planner.split([4000] * 128, [300], 140)
+    assert 1 <= small < 140 and 1 <= large < 140 and large >= small
+    assert planner.stats["searches"] == 2 and planner.stats["micros"] > 0
