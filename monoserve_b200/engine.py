@@ -102,8 +102,9 @@ class RequestTable:
 
 
 class _Req:
-    def __init__(self, rid, prompt, max_tokens, arrival):
+    def __init__(self, rid, prompt, max_tokens, arrival, eos=()):
         self.rid, self.prompt, self.max_tokens, self.arrival = rid, list(prompt), max_tokens, arrival
+        self.eos, self.reason = frozenset(eos), None   # reason: "stop" (an eos token), "length" (max_tokens, or no KV page left)
         self.slot, self.pages, self.delivered = None, [], 0
         self.tokens, self.token_times, self.first_time, self.finish_time = [], [], None, None
 
@@ -193,12 +194,12 @@ class Engine:
     def now(self):
         return time.perf_counter() - self.t0
 
-    def submit(self, rid, prompt, max_tokens, arrival=None):
+    def submit(self, rid, prompt, max_tokens, arrival=None, eos=()):
         if len(prompt) + max_tokens > self.max_len:
             raise ValueError(f"request {rid}: {len(prompt)} + {max_tokens} tokens exceed max_len {self.max_len}")
         if len(prompt) > self.token_budget:
             raise ValueError(f"request {rid}: a prompt of {len(prompt)} tokens exceeds the pass budget {self.token_budget}")
-        r = _Req(rid, prompt, max_tokens, self.now() if arrival is None else arrival)
+        r = _Req(rid, prompt, max_tokens, self.now() if arrival is None else arrival, eos)
         self.reqs[rid] = r
         self.queue.append(r)
 
@@ -333,21 +334,35 @@ class Engine:
             seen.add(r.rid)
             n = min(self.table.produced(r.slot), r.max_tokens)
             if n > r.delivered:
-                r.tokens += self.table.tokens(r.slot, r.delivered, n)
-                r.token_times += [now] * (n - r.delivered)
-                r.delivered = n
-            if r.delivered >= r.max_tokens:
+                new = self.table.tokens(r.slot, r.delivered, n)
+                stop = next((i for i, t in enumerate(new) if t in r.eos), None)
+                if stop is not None:   # the tokens the lane sampled after an eos are dropped
+                    new, r.reason = new[:stop + 1], "stop"
+                r.tokens += new
+                r.token_times += [now] * len(new)
+                r.delivered += len(new)
+            if r.reason is None and r.delivered >= r.max_tokens:
+                r.reason = "length"
+            if r.reason is None and not self._ensure_pages(r, len(r.prompt) + r.delivered):
+                r.reason = "length"   # the cache has no page left for the sequence to grow into
+            if r.reason is not None:
                 r.finish_time = now
                 done.append(r)
-            else:
-                self._ensure_pages(r, len(r.prompt) + r.delivered)
         return done
 
     def _ensure_pages(self, r, length):
-        need = min(-(-(length + 1) // self.kv.page) + LOOKAHEAD_PAGES, self.table.bt_stride)
-        if need > len(r.pages) and need - len(r.pages) <= self.pool.available():
-            r.pages += self.pool.take(need - len(r.pages))
-            self.table.set_pages(r.slot, r.pages)   # entries in use keep their values; new ones lie ahead of the sequence
+        """Keeps LOOKAHEAD_PAGES pages ahead of a decoding sequence of `length` tokens.  False when the pool has none
+        left and less than a page of room remains ahead of the sequence (monoserve/engine.py:509-516 ends the request
+        with "length" then): the lane may run a page's worth of steps before the host sees the tokens."""
+        page = self.kv.page
+        need = min(-(-(length + 1) // page) + LOOKAHEAD_PAGES, self.table.bt_stride)
+        if need <= len(r.pages):
+            return True
+        if need - len(r.pages) > self.pool.available():
+            return length + page <= len(r.pages) * page
+        r.pages += self.pool.take(need - len(r.pages))
+        self.table.set_pages(r.slot, r.pages)   # entries in use keep their values; new ones lie ahead of the sequence
+        return True
 
     # ------------------------------------------------------------------ a whole run
     def serve(self, requests, poll_s=2e-4, timeout_s=600.0):
@@ -373,7 +388,8 @@ class Engine:
             self.step()
             time.sleep(poll_s)
         return {r.rid: dict(arrival=r.arrival, first_token=r.first_time, finish=r.finish_time, tokens=r.tokens,
-                            token_times=r.token_times, prompt_len=len(r.prompt)) for r in self.reqs.values()}
+                            token_times=r.token_times, prompt_len=len(r.prompt), reason=r.reason)
+                for r in self.reqs.values()}
 
 
 def summarize(records):

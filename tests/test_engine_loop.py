@@ -266,3 +266,33 @@ def test_planner_split_is_published_while_both_lanes_run(monkeypatch):
     for contexts, prompts in both:
         assert all(c >= 10 for c in contexts) and set(prompts) <= {20, 40, 10}
     assert h.fab.maps[0] == 8 and any(m == 4 for m in h.fab.maps), "the decode lane's share follows the planner"
+
+
+def test_an_eos_token_ends_the_request_and_later_tokens_are_dropped(monkeypatch):
+    """The model's lanes sample token n at step n: with eos {5} the request ends after six tokens with reason
+    "stop", whatever the lane went on to sample before the loop saw it; the others run to their lengths."""
+    h = Harness(monkeypatch)
+    h.eng.submit("stops", list(range(20)), 30, arrival=0.0, eos={5})
+    h.eng.submit("runs", list(range(20)), 12, arrival=0.0)
+    finished, _ = h.run([])
+    assert sorted(r.rid for r in finished) == ["runs", "stops"]
+    a, b = h.eng.reqs["stops"], h.eng.reqs["runs"]
+    assert a.tokens == [0, 1, 2, 3, 4, 5] and a.reason == "stop"
+    assert b.tokens == list(range(12)) and b.reason == "length"
+    assert h.pool.available() == 63 and h.fab.programs == {}
+
+
+def test_a_request_ends_when_the_cache_has_no_page_left_to_grow_into(monkeypatch):
+    """Two long generations in a pool too small for both: one of them ends early with reason "length" once no page is
+    left and less than a page of room remains ahead of it, before any of its tokens could land outside its
+    pages; its pages then let the other one run to the end."""
+    h = Harness(monkeypatch, pages=10)   # 9 usable pages of 16 tokens; each request starts with 3
+    reqs = [(0, "q0", 10, 100), (0, "q1", 10, 100)]
+    finished, _ = h.run(reqs)
+    assert len(finished) == 2
+    lengths = sorted(len(h.eng.reqs[rid].tokens) for _, rid, _, _ in reqs)
+    assert lengths[1] == 100 and lengths[0] < 100   # 110 tokens need 9 pages with the look-ahead: the whole pool
+    for _, rid, _, _ in reqs:
+        r = h.eng.reqs[rid]
+        assert r.tokens == list(range(len(r.tokens))) and r.reason == "length"
+    assert h.pool.available() == 9
