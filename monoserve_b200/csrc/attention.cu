@@ -60,7 +60,7 @@ __device__ unsigned long long g_attn_trace[8];
 // The claim ring between the producer warp, which takes the CTA's next item from the launch's
 // counter, and the MMA and softmax warps (1 + 4 * kAttnGroups readers per slot).
 struct AttnClaims {
-  uint64_t full[2], empty[2], q_empty;
+  uint64_t full[2], empty[2], q_empty, s_free[2];
   int item[2];
 };
 constexpr int kClaimSlots = 64;
@@ -81,7 +81,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ AttnShared sh;
   __shared__ AttnClaims cl;
-  __shared__ __align__(16) float xbuf[kAttnGroups * 128];
+  // (max, sum) pairs: the four column quarters of a quad-replicated item, or the two groups' halves of an item's rows;
+  // every item ends with a barrier of all softmax threads after its last read
+  __shared__ __align__(16) float2 xbuf[kAttnGroups * 128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AttnWork w;
   w.q_map = &p.q_map;
@@ -116,8 +118,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   }
   c.q_phase = 0;
   c.note = nullptr;
-  c.xbuf = xbuf;
+  c.xbuf = reinterpret_cast<float*>(xbuf);
   c.q_empty = &cl.q_empty;
+  c.s_free = cl.s_free;
   c.base[0] = c.base[1] = 0;
   volatile int* abort_flag = &sh.abort_flag;
 
@@ -129,7 +132,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
       mbar_init(&cl.empty[i], 1 + 4 * kAttnGroups);
     }
     mbar_init(&cl.q_empty, 1);
-    attn_barriers_init(sh, 128 * kAttnGroups);
+    for (int i = 0; i < 2; ++i) mbar_init(&cl.s_free[i], 128);
+    attn_barriers_init(sh, 128);   // P of a tile comes from one softmax group
   }
   if (warp == 1) {
     tmem_alloc(&sh.tmem_base, kAttnTmemCols);
@@ -186,11 +190,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
       w.trace = (p.pad && blockIdx.x == 0 && it == 0) ? g_attn_trace : nullptr;
       attn_derive(w, c);
       if (warp == 1) {
-        attn_mma<2, true>(w, c);
+        if (c.rep) attn_mma<2, true>(w, c);
+        else attn_mma_alt<true>(w, c);
       } else if (c.rep) {
-        softmax_role<true, 2, kAttnGroups, true>(w, c, (warp - 2) >> 2);
+        softmax_role<true, 2, kAttnGroups, true, true>(w, c, (warp - 2) >> 2);
       } else {
-        softmax_role<false, 2, kAttnGroups, true>(w, c, (warp - 2) >> 2);
+        softmax_alt<true>(w, c, (warp - 2) >> 2, xbuf);
       }
       attn_advance(c.n_tiles, c.q_phase, c.base);
       if (*abort_flag) break;

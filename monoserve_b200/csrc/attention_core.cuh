@@ -72,6 +72,7 @@ struct AttnCtx {
   volatile unsigned int* note;   // this role's wait note (tile << 8 | site), or NULL
   float* xbuf;            // several softmax groups: float [groups][128] for the exchange between the parts of a row
   uint64_t* q_empty;      // chained items only: completes once per item, when its last S MMA has read Q
+  uint64_t* s_free;       // alternating softmax groups only: [2], S[s] of a tile has been read into registers
 };
 
 __device__ __forceinline__ void attn_note(const AttnCtx& c, int j, unsigned int site) {
@@ -250,28 +251,42 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
   const int page_bytes = p.page * 256;   // one page's keys of this head, both d halves
   const int last_page = (kv_end - 1) / p.page;
   const int tile0 = item.key_begin / kKeysPerTile;
-  for (int j = 0; j < n_tiles; ++j) {
-    const int s = j & 1;
-    const uint32_t uses = c.base[s] + (j >> 1);        // earlier uses of this stage, by this item and those before
-    const bool reuse = kChain ? uses > 0 : j >= 2;
-    const uint32_t prev = (uses - 1) & 1u;             // the stage's previous use (tile j - 2 of this item, if j >= 2)
-    if (lane == 0) attn_note(c, j, kAttnSiteProdK);
-    if (reuse && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
-    if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
-    __syncwarp();
-    int page_id = 0;
-    if (lane < pages_per_tile) {
-      // pages past the visible range repeat the last visible page; their keys are masked
-      const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
-      page_id = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
-      tma_load_5d(sK + s * kTileBytes + lane * page_bytes, p.k_map, &sh.k_full[s], 0, 0, 2 * item.kv_head, 0, page_id);
+  // K runs one tile ahead of V: K of tile j + 1 is requested before the wait for V's stage of tile j, which is
+  // released only by the P V product two tiles back, so that the next S never waits for a K tile that could
+  // have been on its way.
+  int page_k = 0, page_v = 0;
+  for (int step = 0; step <= n_tiles; ++step) {
+    if (step < n_tiles) {
+      const int j = step, s = j & 1;
+      const uint32_t uses = c.base[s] + (j >> 1);        // earlier uses of this stage, by this item and those before
+      const bool reuse = kChain ? uses > 0 : j >= 2;
+      const uint32_t prev = (uses - 1) & 1u;             // the stage's previous use (tile j - 2 of this item, if j >= 2)
+      if (lane == 0) attn_note(c, j, kAttnSiteProdK);
+      if (reuse && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
+      if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
+      __syncwarp();
+      page_v = page_k;
+      if (lane < pages_per_tile) {
+        // pages past the visible range repeat the last visible page; their keys are masked
+        const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
+        page_k = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
+        tma_load_5d(sK + s * kTileBytes + lane * page_bytes, p.k_map, &sh.k_full[s], 0, 0, 2 * item.kv_head, 0, page_k);
+      }
+    } else {
+      page_v = page_k;
     }
-    if (lane == 0) attn_note(c, j, kAttnSiteProdV);
-    if (reuse && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
-    if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
-    __syncwarp();
-    if (lane < pages_per_tile) {
-      tma_load_5d(sV + s * kTileBytes + lane * page_bytes, p.v_map, &sh.v_full[s], 0, 0, 2 * item.kv_head, 0, page_id);
+    if (step >= 1) {
+      const int j = step - 1, s = j & 1;
+      const uint32_t uses = c.base[s] + (j >> 1);
+      const bool reuse = kChain ? uses > 0 : j >= 2;
+      const uint32_t prev = (uses - 1) & 1u;
+      if (lane == 0) attn_note(c, j, kAttnSiteProdV);
+      if (reuse && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
+      if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        tma_load_5d(sV + s * kTileBytes + lane * page_bytes, p.v_map, &sh.v_full[s], 0, 0, 2 * item.kv_head, 0, page_v);
+      }
     }
   }
 }
@@ -372,9 +387,17 @@ __device__ __forceinline__ void named_barrier_n(int id, int threads) {
 // ends, so the merge of a quad-replicated item uses the two P buffers (64 KB, rows XOR-swizzled by 16-byte
 // chunk instead of padded) and `c.xbuf` for the (max, sum) pairs, and every softmax thread of the CTA, working
 // or not, meets at one barrier when the merge has read them.
-template <bool kRep, int PB, int WG, bool kChain = false>
+// kAlt: the kernel's other items run softmax_alt, whose barriers count one group (128 arrivals); a quad-replicated
+// item is then done by group 0 alone, which also completes the s_free phases, and group 1 only joins the barrier
+// at the end.
+template <bool kRep, int PB, int WG, bool kChain = false, bool kAlt = false>
 __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c, int wg) {
   static_assert(!kChain || PB == 2, "the chained merge needs both P buffers");
+  static_assert(!kAlt || (kRep && kChain), "kAlt: the quad-replicated items of the alternating kernel");
+  if (kAlt && wg != 0) {
+    named_barrier_n(6, 128 * WG);
+    return;
+  }
   constexpr int NC = kRep ? 32 : kKeysPerTile / WG;   // key columns of a tile this thread handles
   constexpr int ND = kRep ? kHeadDim : kHeadDim / WG; // output columns of its row it rescales and stores
   AttnShared& sh = *c.sh;
@@ -547,6 +570,7 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
     tc_fence_before_sync();
     fence_proxy_async_smem();
     mbar_arrive(&sh.p_full[s]);
+    if (kAlt) mbar_arrive(&c.s_free[s]);
     lap(2);
   }
   if (lane == 0) attn_note(c, n_tiles, kAttnSiteSmaxFinal);
@@ -684,6 +708,323 @@ __device__ __forceinline__ void softmax_role(const AttnWork& p, const AttnCtx& c
   }
   // the scratch is the next item's P buffers and `ml` its exchange buffer: nobody goes on before all have read
   if (kChain) named_barrier_n(6, 128 * WG);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Alternating softmax groups (the stand-alone kernel's items with more than 32 rows).  Group g owns the tiles
+// j = g, g + 2, ... of an item: S[g], P[g] and an accumulator O[g] of its own (TMEM columns 256 + 128 g), with its
+// own running (max, sum) per row, so the two groups never talk inside the tile loop and one group's exponentials
+// overlap the other's; at the end of the item the two threads of a row exchange (max, sum) and each merges and
+// stores half of the row's output from both accumulators.  A thread reads its row of S in two passes of 64-column
+// halves (maximum, then exponentials) and releases S[g] after the last load, before the exponentials, so that the
+// next S MMA of the group does not wait for them.
+
+// The MMA role of such an item (the whole warp, one elected lane issues).  S of tile j + 2 is issued before
+// P V of tile j: it needs the S buffer (s_free), not P.
+template <bool kChain>
+__device__ __forceinline__ void attn_mma_alt(const AttnWork& p, const AttnCtx& c) {
+  AttnShared& sh = *c.sh;
+  volatile int* abort_flag = c.abort_flag;
+  const int n_tiles = c.n_tiles;
+  const bool leader = elect_one();
+  const uint32_t tmem_base = c.tmem_base, tmem_o = c.tmem_base + 256;
+  uint8_t* const sQ = c.smem;
+  uint8_t* const sK = c.smem + kTileBytes;
+  uint8_t* const sV = c.smem + 3 * kTileBytes;
+  uint8_t* const sP = c.smem + 5 * kTileBytes;
+  const uint32_t idesc_s = umma_idesc_bf16(128, 128);
+  const uint32_t idesc_o = umma_idesc_bf16(128, 128) | (1u << 16);
+  const uint32_t q_addr = smem_u32(sQ);
+  if (leader) attn_note(c, 0, kAttnSiteMmaQ);
+  bool ok = mbar_wait_bounded(&sh.q_full, c.q_phase & 1u, abort_flag, kAttnWaitNs) || attn_gave_up(sh, kAttnSiteMmaQ);
+  auto mma_s = [&](int j) {
+    const int s = j & 1;
+    if (leader) attn_note(c, j, kAttnSiteMmaK);
+    if (!mbar_wait_bounded(&sh.k_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) return attn_gave_up(sh, kAttnSiteMmaK);
+    if (leader) attn_note(c, j, kAttnSiteMmaSFree);
+    const uint32_t uses = c.base[s] + (j >> 1);   // the buffer's previous tile has been read into registers
+    if ((kChain ? uses > 0 : j >= 2) && !mbar_wait_bounded(&c.s_free[s], (uses - 1) & 1u, abort_flag, kAttnWaitNs))
+      return attn_gave_up(sh, kAttnSiteMmaSFree);
+    tc_fence_after_sync();
+    const uint32_t k_addr = smem_u32(sK + s * kTileBytes);
+    if (leader) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        umma_bf16(tmem_base + s * 128, desc_kmajor(q_addr, i), desc_k_tile(k_addr, i), idesc_s, i != 0);
+      umma_commit(&sh.s_full[s]);
+      umma_commit(&sh.k_empty[s]);
+      if (kChain && j == n_tiles - 1) umma_commit(c.q_empty);
+    }
+    return true;
+  };
+  if (kChain && ok && n_tiles == 0 && leader) mbar_arrive(c.q_empty);
+  if (ok && n_tiles > 0) ok = mma_s(0);
+  if (ok && n_tiles > 1) ok = mma_s(1);
+  for (int j = 0; ok && j < n_tiles; ++j) {
+    const int s = j & 1;
+    if (j + 2 < n_tiles && !mma_s(j + 2)) break;
+    if (leader) attn_note(c, j, kAttnSiteMmaV);
+    if (!mbar_wait_bounded(&sh.v_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaV); break; }
+    if (leader) attn_note(c, j, kAttnSiteMmaP);
+    if (!mbar_wait_bounded(&sh.p_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteMmaP); break; }
+    tc_fence_after_sync();
+    const uint32_t v_addr = smem_u32(sV + s * kTileBytes), p_addr = smem_u32(sP + s * kTileBytes);
+    if (leader) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        umma_bf16(tmem_o + s * 128, desc_kmajor(p_addr, i), desc_v_mnmajor(v_addr, i), idesc_o, ((j >> 1) | i) != 0);
+      umma_commit(&sh.o_full[s]);
+      umma_commit(&sh.v_empty[s]);
+    }
+  }
+  for (int j = max(0, n_tiles - 2); ok && j < n_tiles; ++j) {
+    if (leader) attn_note(c, j, kAttnSiteMmaTail);
+    ok = (mbar_wait_bounded(&sh.k_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+          attn_gave_up(sh, kAttnSiteMmaTail)) &&
+         (mbar_wait_bounded(&sh.v_empty[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) ||
+          attn_gave_up(sh, kAttnSiteMmaTail + 16));
+  }
+  __syncwarp();
+}
+
+// The softmax / output role of such an item: group `wg` of two.  `ml`: float2 [2][128] for the (max, sum) exchange.
+// Every thread passes the quadrant barrier once and the barrier of all softmax threads once per item, whatever
+// else happens.
+template <bool kChain>
+__device__ __forceinline__ void softmax_alt(const AttnWork& p, const AttnCtx& c, int wg, float2* ml) {
+  AttnShared& sh = *c.sh;
+  volatile int* abort_flag = c.abort_flag;
+  const AttnItem& item = p.item;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad = warp & 3;
+  const int r = quad * 32 + lane;                 // TMEM lane = row of S, P and O = row of the item
+  const bool row_ok = r < c.rows;
+  const bool works = quad * 32 < c.rows;          // warp-uniform
+  const int group = p.group;
+  const int token = r / group, head = item.kv_head * group + r % group;
+  const int qpos = item.pos0 + token;
+  const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+  const uint32_t tmem_s = c.tmem_base + wg * 128 + lane_off;
+  const uint32_t tmem_o = c.tmem_base + 256 + lane_off;   // O[0]; O[1] is 128 columns further
+  const int n_tiles = c.n_tiles;
+  const int s = wg;
+  uint8_t* const p_tile = c.smem + (5 + wg) * kTileBytes;
+  float m = -1e30f, l = 0.f;
+  bool ok = true;
+  const bool tr = p.trace != nullptr && quad == 2 && wg == 0 && lane == 0;
+  long long tc[5] = {0, 0, 0, 0, 0}, t_prev = clock64();
+  const unsigned long long t_begin = globaltimer_ns();
+  auto lap = [&](int i) {
+    if (tr) {
+      const long long now = clock64();
+      tc[i] += now - t_prev;
+      t_prev = now;
+    }
+  };
+  for (int j = wg; j < n_tiles; j += 2) {
+    if (!ok) break;
+    if (lane == 0) attn_note(c, j, kAttnSiteSmaxS);
+    if (!warp_wait(&sh.s_full[s], attn_parity(c, j), abort_flag, kAttnWaitNs)) {
+      ok = attn_gave_up(sh, kAttnSiteSmaxS);
+      break;
+    }
+    tc_fence_after_sync();
+    lap(0);
+    if (!works) {
+      // No row of this warp exists: keep the barrier protocol only.  S of this tile was issued when the buffer's
+      // previous tile had been read, which is before that tile's P is complete: the arrival for this tile's P
+      // must not land in that phase, so it waits, like a working warp, for the P V of the previous tile.
+      mbar_arrive(&c.s_free[s]);
+      if (j >= 2 && !warp_wait(&sh.o_full[s], attn_parity(c, j - 2), abort_flag, kAttnWaitNs)) {
+        ok = attn_gave_up(sh, kAttnSiteSmaxPFree);
+        break;
+      }
+      mbar_arrive(&sh.p_full[s]);
+      continue;
+    }
+    const int key0 = item.key_begin + j * kKeysPerTile;
+    const int lim = row_ok ? min(min(c.kv_end, qpos + 1) - key0, kKeysPerTile) : 0;   // keys [0, lim) of the tile count
+    uint32_t v[64];
+    // pass 1: the row maximum (the scale is positive: the maximum of the scaled scores is the scaled maximum)
+    float mx0 = -1e30f, mx1 = -1e30f, mx2 = -1e30f, mx3 = -1e30f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      __syncwarp();
+      tmem_ld_32x32(tmem_s + 64 * h, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+      tmem_ld_32x32(tmem_s + 64 * h + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      tmem_ld_wait();
+      const int lh = lim - 64 * h;
+      if (lh >= 64) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < lh) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+      }
+    }
+    float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+    mx = mx > -1e30f ? mx * p.scale_log2 : -1e30f;
+    mx = fmaxf(mx, m);
+    lap(1);
+    // the reference point of the row's exponentials moves only when the maximum has grown past it by more than
+    // kMaxSlack (see softmax_role); the group's accumulator is rescaled then, after its previous P V
+    if (j >= 2 && mx <= m + kMaxSlack) mx = m;
+    if (j >= 2 && __any_sync(0xffffffffu, mx > m)) {
+      if (lane == 0) attn_note(c, j, kAttnSiteSmaxRescale);
+      if (!warp_wait(&sh.o_full[s], attn_parity(c, j - 2), abort_flag, kAttnWaitNs)) {
+        ok = attn_gave_up(sh, kAttnSiteSmaxRescale);
+        break;
+      }
+      tc_fence_after_sync();
+      const float alpha = fast_exp2(m - mx);
+#pragma unroll
+      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+        uint32_t o[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_o + s * 128 + c0, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32(tmem_o + s * 128 + c0, o);
+      }
+      tmem_st_wait();
+      l *= alpha;
+    }
+    m = mx;
+    lap(3);
+    // the group's P buffer is free once P V of its previous tile has completed
+    if (lane == 0) attn_note(c, j, kAttnSiteSmaxPFree);
+    if (j >= 2 && !warp_wait(&sh.o_full[s], attn_parity(c, j - 2), abort_flag, kAttnWaitNs)) {
+      ok = attn_gave_up(sh, kAttnSiteSmaxPFree);
+      break;
+    }
+    const float neg_mx = -mx;
+    float sum0 = 0.f, sum1 = 0.f;
+    // pass 2: P = exp2(s - max) as bf16 into shared memory (K-major, 128-byte swizzle); row sum of the rounded P
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      __syncwarp();
+      tmem_ld_32x32(tmem_s + 64 * h, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+      tmem_ld_32x32(tmem_s + 64 * h + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      tmem_ld_wait();
+      if (h == 1) {   // S has been read for the last time: the MMA warp may overwrite it
+        tc_fence_before_sync();
+        mbar_arrive(&c.s_free[s]);
+      }
+      const int lh = lim - 64 * h;
+      uint8_t* row_base = p_tile + h * kHalfBytes + r * 128;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t packed[16];
+        if (c0 + 32 <= lh) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx));
+            const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
+            sum0 += __uint_as_float(u << 16);
+            sum1 += __uint_as_float(u & 0xffff0000u);
+            packed[i >> 1] = u;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = c0 + i < lh ? fast_exp2(fmaf(__uint_as_float(v[c0 + i]), p.scale_log2, neg_mx)) : 0.f;
+            const float p1 = c0 + i + 1 < lh ? fast_exp2(fmaf(__uint_as_float(v[c0 + i + 1]), p.scale_log2, neg_mx)) : 0.f;
+            const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(&b);
+            sum0 += __uint_as_float(u << 16);
+            sum1 += __uint_as_float(u & 0xffff0000u);
+            packed[i >> 1] = u;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c0 >> 3) + q;
+          *reinterpret_cast<uint4*>(row_base + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+    }
+    l += sum0 + sum1;
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    mbar_arrive(&sh.p_full[s]);
+    lap(2);
+  }
+  // both accumulators are complete once the last tile of each parity has been multiplied
+  if (lane == 0) attn_note(c, n_tiles, kAttnSiteSmaxFinal);
+  for (int j = max(0, n_tiles - 2); ok && j < n_tiles; ++j)
+    ok = warp_wait(&sh.o_full[j & 1], attn_parity(c, j), abort_flag, kAttnWaitNs) || attn_gave_up(sh, kAttnSiteSmaxFinal);
+  tc_fence_after_sync();
+  lap(4);
+  if (tr) {
+    for (int i = 0; i < 5; ++i) p.trace[i] = tc[i];
+    p.trace[5] = n_tiles;
+    p.trace[6] = globaltimer_ns() - t_begin;
+  }
+  ml[wg * 128 + r] = make_float2(m, l);
+  named_barrier_n(2 + quad, 64);
+  const float2 a = ml[r], b = ml[128 + r];          // group 0's and group 1's (max, sum) of this row
+  const float M = fmaxf(a.x, b.x);
+  const float wa = fast_exp2(a.x - M), wb = fast_exp2(b.x - M);
+  const float L = a.y * wa + b.y * wb;
+  const int d_lo = wg * 64;                          // the half of the row's output this thread merges and stores
+  uint32_t oa[64], ob[64];
+  __syncwarp();
+  if (ok && works && n_tiles > 0) {
+    tmem_ld_32x32(tmem_o + d_lo, *reinterpret_cast<uint32_t(*)[32]>(&oa[0]));
+    tmem_ld_32x32(tmem_o + d_lo + 32, *reinterpret_cast<uint32_t(*)[32]>(&oa[32]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) oa[i] = 0;
+  }
+  if (ok && works && n_tiles > 1) {
+    tmem_ld_32x32(tmem_o + 128 + d_lo, *reinterpret_cast<uint32_t(*)[32]>(&ob[0]));
+    tmem_ld_32x32(tmem_o + 128 + d_lo + 32, *reinterpret_cast<uint32_t(*)[32]>(&ob[32]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) ob[i] = 0;
+  }
+  tmem_ld_wait();
+  tc_fence_before_sync();
+  // nobody goes on to the next item (whose MMAs overwrite the accumulators, and whose exchange reuses `ml`)
+  // before every thread has read both
+  named_barrier_n(6, 256);
+  if (ok && row_ok) {
+    const bool split = item.ws_row0 >= 0;
+    if (split) {
+      float4* wdst = reinterpret_cast<float4*>(p.ws_o + static_cast<size_t>(item.ws_row0 + r) * kHeadDim + d_lo);
+      if (wg == 0) p.ws_ml[item.ws_row0 + r] = make_float2(M, L);
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        wdst[i] = make_float4(__uint_as_float(oa[4 * i]) * wa + __uint_as_float(ob[4 * i]) * wb,
+                              __uint_as_float(oa[4 * i + 1]) * wa + __uint_as_float(ob[4 * i + 1]) * wb,
+                              __uint_as_float(oa[4 * i + 2]) * wa + __uint_as_float(ob[4 * i + 2]) * wb,
+                              __uint_as_float(oa[4 * i + 3]) * wa + __uint_as_float(ob[4 * i + 3]) * wb);
+    } else {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      const float fa = wa * inv, fb = wb * inv;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(item.q_row0 + token) * p.hq + head) * kHeadDim + d_lo);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          h[i] = __floats2bfloat162_rn(
+              __uint_as_float(oa[8 * q + 2 * i]) * fa + __uint_as_float(ob[8 * q + 2 * i]) * fb,
+              __uint_as_float(oa[8 * q + 2 * i + 1]) * fa + __uint_as_float(ob[8 * q + 2 * i + 1]) * fb);
+        dst[q] = *reinterpret_cast<const uint4*>(h);
+      }
+    }
+  }
 }
 
 // Merge of the parts of one split (request, block, KV head): one warp per output row

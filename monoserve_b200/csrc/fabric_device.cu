@@ -962,6 +962,7 @@ __device__ __forceinline__ AttnCtx attn_ctx(const AttnWork& w, AttnShared& sh, v
   c.note = note;
   c.xbuf = nullptr;
   c.q_empty = nullptr;
+  c.s_free = nullptr;
   c.q_phase = q_phase;
   c.base[0] = base[0];
   c.base[1] = base[1];
