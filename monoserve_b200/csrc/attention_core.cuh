@@ -251,11 +251,18 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
   const int page_bytes = p.page * 256;   // one page's keys of this head, both d halves
   const int last_page = (kv_end - 1) / p.page;
   const int tile0 = item.key_begin / kKeysPerTile;
-  // K runs one tile ahead of V: K of tile j + 1 is requested before the wait for V's stage of tile j, which is
+  // K runs ahead of V: K of tile j + lead is requested before the wait for V's stage of tile j, which is
   // released only by the P V product two tiles back, so that the next S never waits for a K tile that could
-  // have been on its way.
-  int page_k = 0, page_v = 0;
-  for (int step = 0; step <= n_tiles; ++step) {
+  // have been on its way.  One tile ahead where the tile loop is bound by the loads (a quad-replicated item,
+  // and inside the fabric worker), two under the alternating softmax groups, whose S of tile j + 2 goes out
+  // before P V of tile j.
+  const int lead = (kChain && !rep) ? 2 : 1;
+  auto page_of = [&](int j) {
+    // pages past the visible range repeat the last visible page; their keys are masked
+    const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
+    return p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
+  };
+  for (int step = 0; step < n_tiles + lead; ++step) {
     if (step < n_tiles) {
       const int j = step, s = j & 1;
       const uint32_t uses = c.base[s] + (j >> 1);        // earlier uses of this stage, by this item and those before
@@ -265,18 +272,11 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
       if (reuse && !warp_wait(&sh.k_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdK); break; }
       if (lane == 0) mbar_arrive_expect_tx(&sh.k_full[s], kTileBytes);
       __syncwarp();
-      page_v = page_k;
-      if (lane < pages_per_tile) {
-        // pages past the visible range repeat the last visible page; their keys are masked
-        const int pg = min((tile0 + j) * pages_per_tile + lane, last_page);
-        page_k = p.block_table[static_cast<size_t>(item.req) * p.bt_stride + pg];
-        tma_load_5d(sK + s * kTileBytes + lane * page_bytes, p.k_map, &sh.k_full[s], 0, 0, 2 * item.kv_head, 0, page_k);
-      }
-    } else {
-      page_v = page_k;
+      if (lane < pages_per_tile)
+        tma_load_5d(sK + s * kTileBytes + lane * page_bytes, p.k_map, &sh.k_full[s], 0, 0, 2 * item.kv_head, 0, page_of(j));
     }
-    if (step >= 1) {
-      const int j = step - 1, s = j & 1;
+    if (step >= lead) {
+      const int j = step - lead, s = j & 1;
       const uint32_t uses = c.base[s] + (j >> 1);
       const bool reuse = kChain ? uses > 0 : j >= 2;
       const uint32_t prev = (uses - 1) & 1u;
@@ -284,9 +284,8 @@ __device__ __forceinline__ void attn_produce(const AttnWork& p, const AttnCtx& c
       if (reuse && !warp_wait(&sh.v_empty[s], prev, abort_flag, kAttnWaitNs)) { attn_gave_up(sh, kAttnSiteProdV); break; }
       if (lane == 0) mbar_arrive_expect_tx(&sh.v_full[s], kTileBytes);
       __syncwarp();
-      if (lane < pages_per_tile) {
-        tma_load_5d(sV + s * kTileBytes + lane * page_bytes, p.v_map, &sh.v_full[s], 0, 0, 2 * item.kv_head, 0, page_v);
-      }
+      if (lane < pages_per_tile)
+        tma_load_5d(sV + s * kTileBytes + lane * page_bytes, p.v_map, &sh.v_full[s], 0, 0, 2 * item.kv_head, 0, page_of(j));
     }
   }
 }
@@ -862,10 +861,14 @@ __device__ __forceinline__ void softmax_alt(const AttnWork& p, const AttnCtx& c,
           mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
           mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
         }
-      } else {
+      } else if (lh > 0) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i < lh) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+        for (int i = 0; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, i < lh ? __uint_as_float(v[i]) : -1e30f);
+          mx1 = fmaxf(mx1, i + 1 < lh ? __uint_as_float(v[i + 1]) : -1e30f);
+          mx2 = fmaxf(mx2, i + 2 < lh ? __uint_as_float(v[i + 2]) : -1e30f);
+          mx3 = fmaxf(mx3, i + 3 < lh ? __uint_as_float(v[i + 3]) : -1e30f);
+        }
       }
     }
     float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
@@ -933,6 +936,9 @@ __device__ __forceinline__ void softmax_alt(const AttnWork& p, const AttnCtx& c,
             sum1 += __uint_as_float(u & 0xffff0000u);
             packed[i >> 1] = u;
           }
+        } else if (lh <= c0) {   // every key of the chunk is masked (half of a diagonal tile, on average)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) packed[i] = 0;
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
