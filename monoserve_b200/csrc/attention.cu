@@ -18,10 +18,19 @@
 //     layout a thread owns one query row with all its columns, so the online softmax
 //     needs no shuffles; P goes to shared memory (double-buffered) as a K-major bf16
 //     operand;
-//   * O = sum over tiles of P V accumulates in a third TMEM region across the whole item
-//     (tcgen05.mma with accumulate); a row is rescaled in TMEM (tcgen05.ld / st) only in
-//     a tile where its running maximum grows, which after the first tiles is rare, so the
-//     softmax threads normally never wait for the P V product;
+//   * the two softmax groups of an item with more than 32 rows take alternate key tiles
+//     (group g: tiles g, g + 2, ...), each with its own S buffer, P buffer, running
+//     (max, sum) per row and accumulator O[g] = sum over its tiles of P V in TMEM
+//     (tcgen05.mma with accumulate), so nothing passes between the groups inside the
+//     tile loop and one group's exponentials overlap the other's; S[g] is released as
+//     soon as its rows are in registers, and the S MMA of tile j + 2 is issued before
+//     P V of tile j; at the end of the item the two threads of a row exchange (max, sum)
+//     and each merges and stores half of the row's output from both accumulators;
+//   * a row's part of O[g] is rescaled in TMEM (tcgen05.ld / st) only in a tile where
+//     its running maximum grows past the reference point by more than 2^8, which after
+//     the first tiles is rare, so the softmax threads normally never wait for P V;
+//   * the producer requests K ahead of V (K of tile j + 1 or j + 2 before it waits for
+//     the V stage of tile j, which only the P V product two tiles back releases);
 //   * V is used in place from the cache layout as an MN-major B operand (keys are the
 //     contraction dimension), so no transposed copy of V exists anywhere;
 //   * the page size is a parameter (16 and 64 are tested); pages of one 128-key tile
@@ -38,12 +47,11 @@
 //     attention_combine_kernel merges the parts in part order.
 //
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM owner + MMA issue, warps 2..5 and
-// 6..9 two softmax / output groups (TMEM lane quadrant = warp % 4): the two threads of a query
-// row each take half of a tile's key columns and half of the row's output, and agree on the row
-// maximum through shared memory once per tile; a quad-replicated (decode) item is done by the
-// first group alone.  One softmax warp per SM sub-partition is bound by instruction latency
-// (max, ex2, bf16 packing per element); the second group doubles what is in flight.  Every
-// wait is bounded; a timeout raises the status word and the CTA leaves, freeing its TMEM.
+// 6..9 two softmax / output groups (TMEM lane quadrant = warp % 4) that take alternate key tiles
+// of an item; a quad-replicated (decode) item is done by the first group alone.  One softmax
+// warp per SM sub-partition is bound by instruction latency (max, ex2, bf16 packing per element);
+// the second group doubles what is in flight.  Every wait is bounded; a timeout raises the status
+// word and the CTA leaves, freeing its TMEM.
 #include <algorithm>
 #include <atomic>
 

@@ -18,7 +18,7 @@ constexpr int kKeysPerTile = 128;
 constexpr int kHalfBytes = 128 * 128;            // 128 rows x 64 bf16: one swizzle atom column, 16 KB
 constexpr int kTileBytes = 2 * kHalfBytes;       // 128 x 128 bf16
 constexpr int kAttnSmemBytes = kTileBytes * 7;   // Q, K x2, V x2, P x2; the kernel declares the array 1024-byte aligned
-constexpr int kAttnTmemCols = 512;               // S x2 (256) + O (128), allocated as a power of two
+constexpr int kAttnTmemCols = 512;               // S x2 (256) + O x2 (256: one accumulator per softmax group; the fabric worker uses one)
 constexpr unsigned long long kAttnWaitNs = 4000000000ull;
 constexpr float kMaxSlack = 8.f;   // how far a row maximum may exceed the reference point of its exponentials
 
@@ -62,7 +62,7 @@ struct AttnCtx {
   AttnShared* sh;
   volatile int* abort_flag;
   uint8_t* smem;          // 1024-byte aligned, seven 32 KB tiles: Q, K x2, V x2, P x2
-  uint32_t tmem_base;     // 384 columns: S x2, O
+  uint32_t tmem_base;     // S x2 at columns 0 and 128, O at 256 (and a second O at 384 under alternating groups)
   int n_tiles, rows, kv_end;
   bool rep;
   // Phases the barriers have completed before this item: the barriers are armed once per
@@ -381,7 +381,9 @@ __device__ __forceinline__ void named_barrier_n(int id, int threads) {
 // barrier per lane quadrant, which all warps of the quadrant pass exactly twice per tile
 // whatever else happens, so that none can be left waiting.  (Two groups: with four, 576 threads
 // leave 96 registers each and the spills cost more than the extra warps hide: decode 517 us
-// against 226, prefill 301 us against 253 on the benchmark shapes.)
+// against 226, prefill 301 us against 253 on the benchmark shapes.  The stand-alone kernel no longer splits
+// columns between its groups: its items with more than 32 rows run softmax_alt below, 634 TFLOP/s against 542
+// on the prefill benchmark.)
 // kChain (a chain of items, see attn_produce): the K / V stages already receive the next item while this one
 // ends, so the merge of a quad-replicated item uses the two P buffers (64 KB, rows XOR-swizzled by 16-byte
 // chunk instead of padded) and `c.xbuf` for the (max, sum) pairs, and every softmax thread of the CTA, working
