@@ -6,7 +6,6 @@ produced token is the oracle's arg-max, or its logit is within 2 % of the logit 
 maximum - the rule of the reference's tests/test_fabric_model.py:135-137)."""
 import numpy as np
 import pytest
-import torch
 
 pytestmark = pytest.mark.gpu
 

@@ -5,8 +5,6 @@ and the exactly-defined floating point (router logits, routing weights, the
 combine given the expert outputs) must be BIT-EXACT.  The tensor-core GEMMs are
 compared within the stated tolerance: rel-L2 <= 1e-2 per layer output in BF16.
 """
-import ctypes
-
 import numpy as np
 import pytest
 import torch
