@@ -80,6 +80,22 @@ constexpr int kClaimSlots = 64;
 // captured kClaimSlots launches apart must not run at the same time).
 __device__ unsigned int g_attn_claim[kClaimSlots];
 
+// A barrier of the CTA's softmax threads that also tells each of them whether any passed `flag`.
+__device__ __forceinline__ bool softmax_threads_any(bool flag) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P, Q;\n\t"
+      "setp.ne.u32 Q, %1, 0;\n\t"
+      "bar.red.or.pred P, 7, %2, Q;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(any)
+      : "r"(static_cast<uint32_t>(flag)), "r"(128 * kAttnGroups)
+      : "memory");
+  return any != 0;
+}
+
 // Persistent: min(items, SMs) CTAs claim items in list order (longest first) until the list is exhausted.
 // The roles of a CTA loop over its items independently; the producer runs ahead, so the next item's Q, K
 // and V arrive while the softmax warps still merge and store the current one.
@@ -189,10 +205,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
   } else {
     for (int it = 0;; ++it) {
       const int slot = it & 1;
-      if (!warp_wait(&cl.full[slot], (it >> 1) & 1u, abort_flag, kAttnWaitNs)) break;
-      const int i = cl.item[slot];
+      const bool got = warp_wait(&cl.full[slot], (it >> 1) & 1u, abort_flag, kAttnWaitNs);
+      const int i = got ? cl.item[slot] : -1;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&cl.empty[slot]);   // the record is read: the slot may be refilled
+      if (got && lane == 0) mbar_arrive(&cl.empty[slot]);   // the record is read: the slot may be refilled
+      // The softmax threads meet at named barriers inside an item, so they leave together or not at all: one
+      // decision per item, taken by all of them at a barrier, on whether any of them has seen a wait give up.
+      if (warp >= 2 ? softmax_threads_any(!got || *abort_flag != 0) : !got) break;
       if (i < 0) break;
       w.item = p.items[i];
       w.trace = (p.pad && blockIdx.x == 0 && it == 0) ? g_attn_trace : nullptr;
@@ -206,7 +225,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) paged_attention_kernel(const 
         softmax_alt<true>(w, c, (warp - 2) >> 2, xbuf);
       }
       attn_advance(c.n_tiles, c.q_phase, c.base);
-      if (*abort_flag) break;
+      if (warp == 1 && *abort_flag) break;   // the softmax threads decide at the top of the loop
     }
   }
 
